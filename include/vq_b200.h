@@ -1,0 +1,157 @@
+/*
+ * C ABI of the B200 (sm_100a) quantized-ops library, libvq_b200.so.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*), launches on that stream and returns 0 on success or a
+ * negative VQ_E* code; vq_last_error() then describes the failure.  Nothing
+ * here synchronises the device or allocates device memory unless stated.
+ * Inputs are never written.  Tensors are dense row-major unless stated.
+ *
+ * Each declaration names the operator of the reference project
+ * (voyager_compiler, paths relative to its checkout) whose arithmetic the
+ * entry point reproduces bit for bit.
+ */
+#ifndef VQ_B200_H
+#define VQ_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* storage dtypes of tensors crossing the ABI */
+enum { VQ_BF16 = 0, VQ_F16 = 1, VQ_F32 = 2 };
+
+/* error codes */
+enum {
+  VQ_OK = 0,
+  VQ_EINVAL = -1,     /* bad argument (shape, dtype, alignment, mode) */
+  VQ_ECUDA = -2,      /* a CUDA runtime/driver call failed */
+  VQ_EUNSUPPORTED = -3,
+  VQ_ETIMEOUT = -4    /* a bounded device-side wait ran out */
+};
+
+/*
+ * How a value is rounded onto a format's grid.  VQ_ROUND_TABLE gathers from
+ * the caller's 65 536-entry bfloat16 table (always exact for any table); the
+ * other modes are arithmetic forms that the host selects only after checking
+ * that they reproduce the supplied table on all 65 536 bfloat16 inputs.
+ */
+enum {
+  VQ_ROUND_NONE = 0,      /* keep the scaled value */
+  VQ_ROUND_TABLE = 1,     /* table[bits(bf16(v))] */
+  VQ_ROUND_INT = 2,       /* clamp(rint(v), lo, hi), zero keeps its sign */
+  VQ_ROUND_MINIFLOAT = 3, /* saturating RNE onto an (emin, mbits, max) grid */
+  VQ_ROUND_STEPS = 4,     /* <= 32 levels: threshold search on the bf16 bits */
+  VQ_ROUND_SEARCH = 5,    /* searchsorted over float edges (codebook encode) */
+  VQ_ROUND_STOCHASTIC = 6 /* Philox stochastic rounding between sorted levels */
+};
+
+#define VQ_MAX_STEPS 32
+
+typedef struct VqRound {
+  int32_t mode;
+  const void* table;      /* TABLE: device uint16[65536] (bf16 bits) */
+  float lo, hi;           /* INT: bounds */
+  int32_t emin, mbits;    /* MINIFLOAT: min normal exponent, mantissa bits */
+  float max_norm;         /* MINIFLOAT: saturation magnitude */
+  int32_t is_signed;      /* MINIFLOAT: 0 takes |v| first */
+  /* STEPS: level k is chosen for sign-magnitude-ordered bf16 keys in
+     [step_key[k-1], step_key[k]); step_value holds the levels as bf16 bits;
+     nan_value the result for a NaN input. */
+  int32_t n_steps;
+  uint16_t step_key[VQ_MAX_STEPS];
+  uint16_t step_value[VQ_MAX_STEPS];
+  uint16_t nan_value;
+  /* SEARCH / STOCHASTIC: device float arrays */
+  const float* edges;     /* SEARCH: ascending edges, result = #edges < v */
+  const float* levels;    /* SEARCH (optional: value per index) / STOCHASTIC */
+  int32_t n_edges;
+  int32_t n_levels;
+  const int64_t* seed;    /* STOCHASTIC: device int64 scalar */
+} VqRound;
+
+/* Broadcast geometry of a per-block parameter tensor against a dense input
+ * viewed as up to VQ_MAX_DIMS collapsed dimensions (outermost first):
+ * parameter index = sum_d (coord_d / div[d]) * stride[d]. */
+#define VQ_MAX_DIMS 5
+typedef struct VqBroadcast {
+  int32_t ndim;
+  int64_t size[VQ_MAX_DIMS];
+  int64_t div[VQ_MAX_DIMS];
+  int64_t stride[VQ_MAX_DIMS];
+} VqBroadcast;
+
+const char* vq_last_error(void);
+int vq_version(void);
+
+/* quantized_ops::vmap -- src/voyager_compiler/ops/quantized.py:151-184.
+ * out[i] = T(table[bits(bf16(in[i]))]); in/out are n elements of `dtype`. */
+int vq_vmap(const void* in, void* out, int dtype, const VqRound* round, int64_t n, void* stream);
+
+/* quantized_ops::quantize -- ops/quantized.py:458-515 (with repeat_per_block
+ * :124-144).  out = round(in / scale [+ zero_point]) with every step rounded to
+ * `dtype`.  `zero_point` may be NULL.  `geom` maps an element to its scale.
+ * `param_dtype` is the dtype of scale and zero_point: equal to `dtype`, or
+ * VQ_F32 for a single-element scale used at full precision. */
+int vq_quantize(const void* in, const void* scale, const void* zero_point, void* out, int dtype,
+                int param_dtype, const VqBroadcast* geom, const VqRound* round, void* stream);
+
+/* quantized_ops::dequantize -- ops/quantized.py:527-571.
+ * out = round_out((round_in(in) - zero_point) * scale). */
+int vq_dequantize(const void* in, const void* scale, const void* zero_point, void* out, int dtype,
+                  int param_dtype, const VqBroadcast* geom, const VqRound* round_in,
+                  const VqRound* round_out, void* stream);
+
+/* Microscaling block geometry: the input is a dense [O, A, M, B, I] tensor
+ * whose blocks span block_a consecutive indices of A and block_b of B (1 =
+ * axis not blocked); scales are dense [O, ceil(A/block_a), M, ceil(B/block_b), I]. */
+typedef struct VqBlocks {
+  int64_t O, A, M, B, I;
+  int32_t block_a, block_b;
+} VqBlocks;
+
+/* Scale rule of calculate_mx_qparam -- ops/quantized.py:966-1031 with
+ * quantization/mx_utils.py:16-125. */
+typedef struct VqScaleRule {
+  float quant_max;
+  int32_t power_of_two;       /* 2**(floor(log2 amax) - floor(log2 quant_max)) */
+  const void* global_scale;   /* device scalar, or NULL */
+  int32_t global_scale_dtype; /* its dtype */
+  VqRound scale_round;        /* rounding of the scale (NONE or a table form) */
+} VqScaleRule;
+
+/* quantized_ops::calculate_mx_qparam -- ops/quantized.py:966-1031. */
+int vq_mx_qparam(const void* in, void* scale_out, int dtype, const VqBlocks* blocks,
+                 const VqScaleRule* rule, void* stream);
+
+/* quantized_ops::quantize_mx -- ops/quantized.py:1080-1115: per-block scale,
+ * then codes = round(in / (scale [* global_scale])). */
+int vq_quantize_mx(const void* in, void* scale_out, void* codes_out, int dtype, const VqBlocks* blocks,
+                   const VqScaleRule* rule, const VqRound* round, void* stream);
+
+/* quantized_ops::quantize_affine -- ops/quantized.py:1227-1283: per-block
+ * min/max -> scale and zero point (optionally table-rounded) -> codes.
+ * Blocks lie along B only (block_a must be 1). */
+int vq_quantize_affine(const void* in, void* scale_out, void* zero_out, void* codes_out, int dtype,
+                       const VqBlocks* blocks, float quant_min, float quant_max,
+                       const VqRound* scale_round, const VqRound* round, void* stream);
+
+/* quantized_ops::dequantize_mx / _decode_and_scale -- ops/quantized.py:574-591,
+ * 1125-1149.  out = code[in] * scale [* global_scale]; `code` (n_code entries of
+ * `dtype`), `scale` and `global_scale` may each be NULL. */
+int vq_dequantize_mx(const void* in, const void* scale, const void* code, int32_t n_code,
+                     const void* global_scale, int global_scale_dtype, void* out, int dtype,
+                     const VqBroadcast* geom, void* stream);
+
+/* max |x| over n elements, written as a float to *out (device).  The amax
+ * that calculate_global_scale (quantization/fake_quantize.py:142-160) and the
+ * per-tensor scale rule (fake_quantize.py:406-437) start from.  `out` must
+ * be zeroed by the caller; NaN inputs give NaN. */
+int vq_amax(const void* in, int dtype, int64_t n, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VQ_B200_H */

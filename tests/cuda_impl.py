@@ -1,0 +1,45 @@
+"""The product's operators under the names ``cases.run_case`` uses; every
+tensor argument is moved to the GPU and results come back to the host."""
+
+import torch
+
+import voyager_b200  # noqa: F401  (registers torch.ops.quantized_ops)
+
+Q = torch.ops.quantized_ops
+DEV = "cuda"
+
+
+def _to_dev(a):
+    if isinstance(a, torch.Tensor):
+        return a.to(DEV)
+    if isinstance(a, (list, tuple)) and a and isinstance(a[0], torch.Tensor):
+        return type(a)(_to_dev(v) for v in a)
+    return a
+
+
+def _to_host(o):
+    if isinstance(o, torch.Tensor):
+        return o.cpu()
+    if isinstance(o, (list, tuple)):
+        return tuple(_to_host(v) for v in o)
+    return o
+
+
+def _wrap(fn):
+    def call(*args, **kwargs):
+        out = fn(*[_to_dev(a) for a in args], **{k: _to_dev(v) for k, v in kwargs.items()})
+        torch.cuda.synchronize()
+        return _to_host(out)
+
+    return call
+
+
+class CudaImpl:
+    vmap = staticmethod(_wrap(Q.vmap))
+    quantize = staticmethod(_wrap(Q.quantize))
+    dequantize = staticmethod(_wrap(Q.dequantize))
+    calculate_mx_qparam = staticmethod(_wrap(Q.calculate_mx_qparam))
+    quantize_mx = staticmethod(_wrap(Q.quantize_mx))
+    dequantize_mx = staticmethod(_wrap(Q.dequantize_mx))
+    quantize_affine = staticmethod(_wrap(Q.quantize_affine))
+    calculate_global_scale = staticmethod(_wrap(voyager_b200.calculate_global_scale))

@@ -1,0 +1,22 @@
+"""B200-native (sm_100a) kernels behind voyager_compiler's ``quantized_ops`` operators.
+
+Importing the package registers the ``quantized_ops`` torch library with CUDA
+kernels (see ``ops``).  The directory name is not a Python identifier; import
+it through the ``voyager_b200`` module at the repository root.
+"""
+
+from . import _native, formats, rounding  # noqa: F401
+from . import ops  # noqa: F401  (registers torch.ops.quantized_ops.*)
+from ._native import build  # noqa: F401
+from .formats import (  # noqa: F401
+    QScheme,
+    entry_levels,
+    float_format,
+    get_quantization_map,
+    int_range,
+    parse_codebook_dtype,
+    parse_spec_fields,
+    posit_format,
+    qmap_levels,
+)
+from .ops import calculate_global_scale, tensor_amax  # noqa: F401

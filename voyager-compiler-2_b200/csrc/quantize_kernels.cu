@@ -1,0 +1,796 @@
+// Quantizer kernels for sm_100a: table rounding (vmap), scale/zero-point
+// quantize and dequantize with block-broadcast parameters, the one-pass
+// microscaling quantizer (block amax -> scale -> codes), the group-wise affine
+// quantizer used for 2-bit KV caches, codebook read-back, and a tensor amax.
+//
+// All of these are HBM-bound: every kernel reads its input once with 16-byte
+// accesses where the layout allows and writes each output once.
+
+#include "vq_common.cuh"
+
+#include <cmath>
+
+namespace vq {
+
+// ---------------------------------------------------------------------------
+// error plumbing
+// ---------------------------------------------------------------------------
+static thread_local char g_error[512];
+char* error_buffer() { return g_error; }
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(VQ_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+  return VQ_OK;
+}
+
+int validate_round(const VqRound* r, const char* what) {
+  if (r == nullptr) return VQ_OK;
+  switch (r->mode) {
+    case VQ_ROUND_NONE:
+    case VQ_ROUND_INT:
+      return VQ_OK;
+    case VQ_ROUND_TABLE:
+      if (!r->table) return fail(VQ_EINVAL, "%s: table rounding without a table", what);
+      return VQ_OK;
+    case VQ_ROUND_MINIFLOAT:
+      // The kernel scales by 2^(mbits - e) built directly from exponent bits,
+      // which must stay a normal float for every exponent e the format has.
+      if (r->mbits < 0 || r->mbits > 10 || !(r->max_norm > 0.0f) || r->emin - r->mbits < -126 ||
+          ilogbf(r->max_norm) - r->mbits > 126 || ilogbf(r->max_norm) < r->emin)
+        return fail(VQ_EINVAL, "%s: minifloat parameters out of range", what);
+      return VQ_OK;
+    case VQ_ROUND_STEPS:
+      if (r->n_steps < 1 || r->n_steps > VQ_MAX_STEPS)
+        return fail(VQ_EINVAL, "%s: %d steps (max %d)", what, r->n_steps, VQ_MAX_STEPS);
+      return VQ_OK;
+    case VQ_ROUND_SEARCH:
+      if (r->n_edges < 0 || (r->n_edges > 0 && !r->edges))
+        return fail(VQ_EINVAL, "%s: search rounding without edges", what);
+      return VQ_OK;
+    case VQ_ROUND_STOCHASTIC:
+      if (!r->levels || r->n_levels < 1 || !r->seed)
+        return fail(VQ_EINVAL, "%s: stochastic rounding needs levels and a seed", what);
+      return VQ_OK;
+  }
+  return fail(VQ_EINVAL, "%s: unknown rounding mode %d", what, r->mode);
+}
+
+static inline int grid_for(int64_t work_items, int threads, int per_sm = 8) {
+  int64_t blocks = (work_items + threads - 1) / threads;
+  int64_t cap = (int64_t)kSmCount * per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+// ---------------------------------------------------------------------------
+// 16-byte vector access
+// ---------------------------------------------------------------------------
+template <int DT> struct Vec {
+  using E = Elem<DT>;
+  uint4 raw;
+  __device__ __forceinline__ float get(int i) const {
+    if constexpr (DT == VQ_F32) {
+      return reinterpret_cast<const float*>(&raw)[i];
+    } else {
+      return E::to_float(reinterpret_cast<const typename E::T*>(&raw)[i]);
+    }
+  }
+  __device__ __forceinline__ void set(int i, float v) {
+    if constexpr (DT == VQ_F32) {
+      reinterpret_cast<float*>(&raw)[i] = v;
+    } else {
+      reinterpret_cast<typename E::T*>(&raw)[i] = E::from_float(v);
+    }
+  }
+};
+
+template <int DT>
+__device__ __forceinline__ float load1(const void* p, int64_t i) {
+  return Elem<DT>::to_float(static_cast<const typename Elem<DT>::T*>(p)[i]);
+}
+template <int DT>
+__device__ __forceinline__ void store1(void* p, int64_t i, float v) {
+  static_cast<typename Elem<DT>::T*>(p)[i] = Elem<DT>::from_float(v);
+}
+
+// A parameter (scale, zero point, global scale) whose dtype is only known at
+// run time: a 0-d float32 scale next to bfloat16 data is used at full
+// precision, as torch does for scalar operands.
+__device__ __forceinline__ float loadp(const void* p, int64_t i, int pdt) {
+  if (pdt == VQ_F32) return static_cast<const float*>(p)[i];
+  if (pdt == VQ_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+// ---------------------------------------------------------------------------
+// vmap
+// ---------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(256) vmap_kernel(const void* __restrict__ in, void* __restrict__ out,
+                                                   Round r, int64_t n, int vec_ok) {
+  using E = Elem<DT>;
+  constexpr int V = E::kVec;
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    int64_t nvec = n / V;
+    for (int64_t v = tid; v < nvec; v += stride) {
+      Vec<DT> x, y;
+      x.raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) y.set(j, apply_round(r, x.get(j), v * V + j));
+      reinterpret_cast<uint4*>(out)[v] = y.raw;
+    }
+    for (int64_t i = nvec * V + tid; i < n; i += stride)
+      store1<DT>(out, i, apply_round(r, load1<DT>(in, i), i));
+  } else {
+    for (int64_t i = tid; i < n; i += stride)
+      store1<DT>(out, i, apply_round(r, load1<DT>(in, i), i));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// quantize / dequantize with broadcast parameters
+// ---------------------------------------------------------------------------
+struct Geom {
+  int ndim;
+  int64_t size[VQ_MAX_DIMS];
+  int64_t div[VQ_MAX_DIMS];
+  int64_t stride[VQ_MAX_DIMS];
+};
+
+__device__ __forceinline__ int64_t param_index(const Geom& g, int64_t flat) {
+  int64_t idx = 0;
+#pragma unroll
+  for (int d = VQ_MAX_DIMS - 1; d >= 0; --d) {
+    if (d < g.ndim) {
+      int64_t c = flat % g.size[d];
+      flat /= g.size[d];
+      idx += (c / g.div[d]) * g.stride[d];
+    }
+  }
+  return idx;
+}
+
+// kind 0: out = round(in / scale [+ zp]);  kind 1: out = round_out((round_in(in) - zp) * scale)
+template <int DT, int KIND>
+__global__ void __launch_bounds__(256)
+scale_map_kernel(const void* __restrict__ in, const void* __restrict__ scale, const void* __restrict__ zp,
+                 void* __restrict__ out, Geom g, Round r_in, Round r_out, int64_t n, int scalar_param,
+                 int vec_ok, int pdt) {
+  using E = Elem<DT>;
+  constexpr int V = E::kVec;
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+
+  auto one = [&](float x, float s, float z, bool has_z, int64_t flat) -> float {
+    if (KIND == 0) {
+      float y = E::round(__fdiv_rn(x, s));
+      if (has_z) y = E::round(__fadd_rn(y, z));
+      return apply_round(r_out, y, flat);
+    } else {
+      float y = apply_round(r_in, x, flat);
+      if (has_z) y = E::round(__fsub_rn(y, z));
+      y = E::round(__fmul_rn(y, s));
+      return apply_round(r_out, y, flat);
+    }
+  };
+  const bool has_z = zp != nullptr;
+
+  if (scalar_param) {
+    const float s = loadp(scale, 0, pdt);
+    const float z = has_z ? loadp(zp, 0, pdt) : 0.0f;
+    if (vec_ok) {
+      int64_t nvec = n / V;
+      for (int64_t v = tid; v < nvec; v += stride) {
+        Vec<DT> x, y;
+        x.raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
+#pragma unroll
+        for (int j = 0; j < V; ++j) y.set(j, one(x.get(j), s, z, has_z, v * V + j));
+        reinterpret_cast<uint4*>(out)[v] = y.raw;
+      }
+      for (int64_t i = nvec * V + tid; i < n; i += stride)
+        store1<DT>(out, i, one(load1<DT>(in, i), s, z, has_z, i));
+    } else {
+      for (int64_t i = tid; i < n; i += stride) store1<DT>(out, i, one(load1<DT>(in, i), s, z, has_z, i));
+    }
+    return;
+  }
+
+  // Vector path: the innermost collapsed dimension is a multiple of V, so a
+  // vector never straddles an outer coordinate; the parameter index of the
+  // vector's first element is computed once and advanced along the last dim.
+  if (vec_ok) {
+    const int last = g.ndim - 1;
+    const int64_t inner = g.size[last], idiv = g.div[last], istr = g.stride[last];
+    int64_t nvec = n / V;
+    for (int64_t v = tid; v < nvec; v += stride) {
+      int64_t flat = v * V;
+      int64_t c = flat % inner;
+      int64_t outer = flat / inner;
+      int64_t base = 0;
+      for (int d = last - 1; d >= 0; --d) {
+        int64_t cc = outer % g.size[d];
+        outer /= g.size[d];
+        base += (cc / g.div[d]) * g.stride[d];
+      }
+      Vec<DT> x, y;
+      x.raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
+      int64_t prev = -1;
+      float s = 0.f, z = 0.f;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        int64_t pi = base + ((c + j) / idiv) * istr;
+        if (pi != prev) {
+          s = loadp(scale, pi, pdt);
+          if (has_z) z = loadp(zp, pi, pdt);
+          prev = pi;
+        }
+        y.set(j, one(x.get(j), s, z, has_z, flat + j));
+      }
+      reinterpret_cast<uint4*>(out)[v] = y.raw;
+    }
+    return;
+  }
+
+  for (int64_t i = tid; i < n; i += stride) {
+    int64_t pi = param_index(g, i);
+    float s = loadp(scale, pi, pdt);
+    float z = has_z ? loadp(zp, pi, pdt) : 0.0f;
+    store1<DT>(out, i, one(load1<DT>(in, i), s, z, has_z, i));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// microscaling: scale rule
+// ---------------------------------------------------------------------------
+struct ScaleRule {
+  float quant_max;
+  int power_of_two;
+  int qmax_exp;  // floor(log2(quant_max))
+  const void* global_scale;
+  int global_scale_dtype;
+  Round scale_round;
+};
+
+// amax_bits: |amax| as float bits (NaN patterns compare above inf, so an
+// integer max over |x| bits propagates NaN like torch.amax).
+// Returns the block scale (value of dtype DT, as float); *elem_scale gets the
+// divisor of the elements (scale * global_scale when present).
+template <int DT>
+__device__ __forceinline__ float block_scale(uint32_t amax_bits, const ScaleRule& rule, float* elem_scale) {
+  using E = Elem<DT>;
+  float amax = __uint_as_float(amax_bits);
+  float scale;
+  float gs = 0.f;
+  const bool has_gs = rule.global_scale != nullptr;
+  if (has_gs) gs = loadp(rule.global_scale, 0, rule.global_scale_dtype);
+  if (rule.power_of_two) {
+    if (amax != amax) {
+      scale = amax;
+    } else if (amax_bits == 0x7F800000u) {
+      scale = amax;  // infinite block -> infinite scale
+    } else {
+      int e = (amax == 0.0f) ? -126 : ilogbf(amax);
+      scale = E::round(ldexpf(1.0f, e - rule.qmax_exp));
+    }
+  } else {
+    scale = E::round(__fdiv_rn(amax, rule.quant_max));
+    if (has_gs) scale = E::round(__fdiv_rn(scale, gs));
+    if (rule.scale_round.mode != VQ_ROUND_NONE) scale = E::round(apply_round(rule.scale_round, scale, 0));
+  }
+  scale = (scale > 0.0f) ? scale : 1.0f;
+  *elem_scale = has_gs ? E::round(__fmul_rn(scale, gs)) : scale;
+  return scale;
+}
+
+__device__ __forceinline__ uint32_t abs_bits(float v) { return __float_as_uint(v) & 0x7FFFFFFFu; }
+
+// Fast path: blocks along the contiguous last axis; row length K a multiple of
+// the vector width; a block is covered by G = block/V consecutive lanes.
+// Each row owns `slots_per_row` = ceil(K/block) * G thread slots so groups are
+// lane-aligned; slots past the row's end only take part in the shuffles.
+template <int DT, bool WRITE_CODES>
+__global__ void __launch_bounds__(256)
+mx_rows_kernel(const void* __restrict__ in, void* __restrict__ scale_out, void* __restrict__ codes_out,
+               int64_t rows, int64_t K, int block, int G, int64_t slots_per_row, int64_t total_slots,
+               ScaleRule rule, Round r) {
+  using E = Elem<DT>;
+  constexpr int V = E::kVec;
+  const int64_t nblk = slots_per_row / G;
+  const int64_t row_vecs = K / V;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // total_slots is rounded up to a multiple of 32 by the launcher, so whole
+  // warps enter and leave the loop together.
+  for (int64_t slot = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; slot < total_slots; slot += stride) {
+    int64_t row = slot / slots_per_row;
+    int64_t s_in_row = slot - row * slots_per_row;
+    const bool active = row < rows && s_in_row < row_vecs;
+    Vec<DT> x;
+    x.raw = make_uint4(0, 0, 0, 0);
+    if (active) x.raw = __ldg(reinterpret_cast<const uint4*>(in) + row * row_vecs + s_in_row);
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < V; ++j) m = max(m, abs_bits(x.get(j)));
+    for (int off = 1; off < G; off <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+    float es;
+    float scale = block_scale<DT>(m, rule, &es);
+    if (active && (s_in_row % G) == 0)
+      store1<DT>(scale_out, row * nblk + s_in_row / G, scale);
+    if (WRITE_CODES && active) {
+      Vec<DT> y;
+      const int64_t flat = (row * row_vecs + s_in_row) * V;
+      // Dividing by a power of two with a representable reciprocal is the
+      // same correctly rounded result as the product with that reciprocal.
+      uint32_t sb = __float_as_uint(es);
+      const bool pow2 = (sb & 0x007FFFFFu) == 0 && (sb >> 23) >= 1 && (sb >> 23) <= 253;
+      if (pow2) {
+        float inv = __uint_as_float((254u - (sb >> 23)) << 23);
+#pragma unroll
+        for (int j = 0; j < V; ++j) y.set(j, apply_round(r, E::round(__fmul_rn(x.get(j), inv)), flat + j));
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) y.set(j, apply_round(r, E::round(__fdiv_rn(x.get(j), es)), flat + j));
+      }
+      reinterpret_cast<uint4*>(codes_out)[row * row_vecs + s_in_row] = y.raw;
+    }
+  }
+}
+
+// Generic path: one thread per (o, a-block, m, b-block, i); threads are
+// consecutive along i, then b-block.  Two passes over the block (the second
+// is served from cache).
+struct Blocks {
+  int64_t O, A, M, B, I;
+  int bA, bB;
+  int64_t nA, nB;
+};
+
+template <int DT, bool WRITE_CODES>
+__global__ void __launch_bounds__(256)
+mx_generic_kernel(const void* __restrict__ in, void* __restrict__ scale_out, void* __restrict__ codes_out,
+                  Blocks g, ScaleRule rule, Round r) {
+  using E = Elem<DT>;
+  const int64_t total = g.O * g.nA * g.M * g.nB * g.I;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    int64_t i = t % g.I;
+    int64_t q = t / g.I;
+    int64_t nb = q % g.nB; q /= g.nB;
+    int64_t m = q % g.M;   q /= g.M;
+    int64_t na = q % g.nA;
+    int64_t o = q / g.nA;
+    const int64_t a0 = na * g.bA, b0 = nb * g.bB;
+    const int64_t a1 = min(a0 + (int64_t)g.bA, g.A), b1 = min(b0 + (int64_t)g.bB, g.B);
+    uint32_t mx = 0;
+    for (int64_t a = a0; a < a1; ++a) {
+      int64_t base = (((o * g.A + a) * g.M + m) * g.B) * g.I + i;
+      for (int64_t b = b0; b < b1; ++b) mx = max(mx, abs_bits(load1<DT>(in, base + b * g.I)));
+    }
+    float es;
+    float scale = block_scale<DT>(mx, rule, &es);
+    store1<DT>(scale_out, t, scale);
+    if (WRITE_CODES) {
+      for (int64_t a = a0; a < a1; ++a) {
+        int64_t base = (((o * g.A + a) * g.M + m) * g.B) * g.I + i;
+        for (int64_t b = b0; b < b1; ++b) {
+          int64_t flat = base + b * g.I;
+          float y = E::round(__fdiv_rn(load1<DT>(in, flat), es));
+          store1<DT>(codes_out, flat, apply_round(r, y, flat));
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// group-wise affine (KIVI)
+// ---------------------------------------------------------------------------
+// torch.amin/amax propagate NaN.
+__device__ __forceinline__ float nan_min(float a, float b) { return (a != a || b != b) ? (a + b) : fminf(a, b); }
+__device__ __forceinline__ float nan_max(float a, float b) { return (a != a || b != b) ? (a + b) : fmaxf(a, b); }
+
+template <int DT>
+__device__ __forceinline__ void affine_params(float low, float high, float qmin, float qmax,
+                                              const Round& sr, float* scale, float* zero) {
+  using E = Elem<DT>;
+  float range = E::round(__fsub_rn(high, low));
+  float s = E::round(__fdiv_rn(range, __fsub_rn(qmax, qmin)));
+  s = (s > 0.0f) ? s : 1.0f;
+  if (sr.mode != VQ_ROUND_NONE) {
+    s = E::round(apply_round(sr, s, 0));
+    s = (s > 0.0f) ? s : 1.0f;
+  }
+  float z = E::round(__fdiv_rn(-low, s));
+  z = E::round(__fadd_rn(z, qmin));
+  if (sr.mode != VQ_ROUND_NONE) z = E::round(apply_round(sr, z, 0));
+  *scale = s;
+  *zero = z;
+}
+
+// Blocks of `block` along B in a dense [O, B, I] view; thread per (o, b-block, i).
+template <int DT>
+__global__ void __launch_bounds__(256)
+affine_generic_kernel(const void* __restrict__ in, void* __restrict__ scale_out, void* __restrict__ zero_out,
+                      void* __restrict__ codes_out, int64_t O, int64_t B, int64_t I, int block, int64_t nB,
+                      float qmin, float qmax, Round sr, Round r) {
+  using E = Elem<DT>;
+  const int64_t total = O * nB * I;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    int64_t i = t % I;
+    int64_t q = t / I;
+    int64_t nb = q % nB;
+    int64_t o = q / nB;
+    int64_t b0 = nb * block, b1 = min(b0 + (int64_t)block, B);
+    // A short last block is zero padded before the reduction.
+    float low = (b1 - b0 < block) ? 0.0f : INFINITY;
+    float high = (b1 - b0 < block) ? 0.0f : -INFINITY;
+    for (int64_t b = b0; b < b1; ++b) {
+      float v = load1<DT>(in, (o * B + b) * I + i);
+      low = nan_min(low, v);
+      high = nan_max(high, v);
+    }
+    float s, z;
+    affine_params<DT>(low, high, qmin, qmax, sr, &s, &z);
+    store1<DT>(scale_out, t, s);
+    store1<DT>(zero_out, t, z);
+    for (int64_t b = b0; b < b1; ++b) {
+      int64_t flat = (o * B + b) * I + i;
+      float y = E::round(__fdiv_rn(load1<DT>(in, flat), s));
+      y = E::round(__fadd_rn(y, z));
+      store1<DT>(codes_out, flat, apply_round(r, y, flat));
+    }
+  }
+}
+
+// Fast path, I == 1: blocks along the contiguous axis, G lanes per block.
+template <int DT>
+__global__ void __launch_bounds__(256)
+affine_rows_kernel(const void* __restrict__ in, void* __restrict__ scale_out, void* __restrict__ zero_out,
+                   void* __restrict__ codes_out, int64_t rows, int64_t K, int block, int G,
+                   int64_t slots_per_row, int64_t total_slots, float qmin, float qmax, Round sr, Round r) {
+  using E = Elem<DT>;
+  constexpr int V = E::kVec;
+  const int64_t nblk = slots_per_row / G;
+  const int64_t row_vecs = K / V;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t slot = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; slot < total_slots; slot += stride) {
+    int64_t row = slot / slots_per_row;
+    int64_t s_in_row = slot - row * slots_per_row;
+    const bool active = row < rows && s_in_row < row_vecs;
+    Vec<DT> x;
+    x.raw = make_uint4(0, 0, 0, 0);  // padding of a short last block is zero
+    if (active) x.raw = __ldg(reinterpret_cast<const uint4*>(in) + row * row_vecs + s_in_row);
+    float low = x.get(0), high = x.get(0);
+#pragma unroll
+    for (int j = 1; j < V; ++j) {
+      low = nan_min(low, x.get(j));
+      high = nan_max(high, x.get(j));
+    }
+    for (int off = 1; off < G; off <<= 1) {
+      low = nan_min(low, __shfl_xor_sync(0xFFFFFFFFu, low, off));
+      high = nan_max(high, __shfl_xor_sync(0xFFFFFFFFu, high, off));
+    }
+    float s, z;
+    affine_params<DT>(low, high, qmin, qmax, sr, &s, &z);
+    if (active && (s_in_row % G) == 0) {
+      store1<DT>(scale_out, row * nblk + s_in_row / G, s);
+      store1<DT>(zero_out, row * nblk + s_in_row / G, z);
+    }
+    if (active) {
+      Vec<DT> y;
+      const int64_t flat = (row * row_vecs + s_in_row) * V;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float q = E::round(__fdiv_rn(x.get(j), s));
+        q = E::round(__fadd_rn(q, z));
+        y.set(j, apply_round(r, q, flat + j));
+      }
+      reinterpret_cast<uint4*>(codes_out)[row * row_vecs + s_in_row] = y.raw;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// codebook read-back
+// ---------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(256)
+dequantize_mx_kernel(const void* __restrict__ in, const void* __restrict__ scale, const void* __restrict__ code,
+                     int n_code, const void* __restrict__ gscale, int gdt, void* __restrict__ out, Geom g,
+                     int64_t n) {
+  using E = Elem<DT>;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const bool has_g = gscale != nullptr;
+  const float gs = has_g ? loadp(gscale, 0, gdt) : 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v = load1<DT>(in, i);
+    if (code) {
+      long long idx = (long long)v;  // Tensor.to(long) truncates
+      idx = idx < 0 ? idx + n_code : idx;
+      idx = idx < 0 ? 0 : (idx >= n_code ? n_code - 1 : idx);
+      v = load1<DT>(code, idx);
+    }
+    if (scale) v = E::round(__fmul_rn(v, load1<DT>(scale, param_index(g, i))));
+    if (has_g) v = E::round(__fmul_rn(v, gs));
+    store1<DT>(out, i, v);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// tensor amax
+// ---------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(256) amax_kernel(const void* __restrict__ in, int64_t n, int vec_ok,
+                                                   uint32_t* __restrict__ out) {
+  using E = Elem<DT>;
+  constexpr int V = E::kVec;
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  uint32_t m = 0;
+  int64_t done = 0;
+  if (vec_ok) {
+    int64_t nvec = n / V;
+    for (int64_t v = tid; v < nvec; v += stride) {
+      Vec<DT> x;
+      x.raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
+#pragma unroll
+      for (int j = 0; j < V; ++j) m = max(m, abs_bits(x.get(j)));
+    }
+    done = nvec * V;
+  }
+  for (int64_t i = done + tid; i < n; i += stride) m = max(m, abs_bits(load1<DT>(in, i)));
+  for (int off = 16; off; off >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+  __shared__ uint32_t warp_max[8];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = max(m, warp_max[w]);
+    atomicMax(out, m);  // non-negative float bits order like unsigned ints
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host launchers
+// ---------------------------------------------------------------------------
+static int to_geom(const VqBroadcast* b, Geom* g, int64_t* n) {
+  if (!b || b->ndim < 1 || b->ndim > VQ_MAX_DIMS) return fail(VQ_EINVAL, "broadcast geometry: ndim out of range");
+  g->ndim = b->ndim;
+  int64_t total = 1;
+  for (int d = 0; d < VQ_MAX_DIMS; ++d) {
+    if (d < b->ndim) {
+      if (b->size[d] < 0 || b->div[d] < 1) return fail(VQ_EINVAL, "broadcast geometry: bad size/div at dim %d", d);
+      g->size[d] = b->size[d];
+      g->div[d] = b->div[d];
+      g->stride[d] = b->stride[d];
+      total *= b->size[d];
+    } else {
+      g->size[d] = 1;
+      g->div[d] = 1;
+      g->stride[d] = 0;
+    }
+  }
+  *n = total;
+  return VQ_OK;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+#define VQ_DISPATCH_DTYPE(dtype, ...)                                    \
+  switch (dtype) {                                                       \
+    case VQ_BF16: { constexpr int DT = VQ_BF16; __VA_ARGS__; break; }    \
+    case VQ_F16:  { constexpr int DT = VQ_F16;  __VA_ARGS__; break; }    \
+    case VQ_F32:  { constexpr int DT = VQ_F32;  __VA_ARGS__; break; }    \
+    default: return vq::fail(VQ_EINVAL, "unknown dtype %d", dtype);      \
+  }
+
+static inline int vec_width(int dtype) { return dtype == VQ_F32 ? 4 : 8; }
+
+static int to_rule(const VqScaleRule* rule, ScaleRule* out) {
+  if (!rule) return fail(VQ_EINVAL, "scale rule missing");
+  if (!(rule->quant_max > 0.0f)) return fail(VQ_EINVAL, "quant_max must be positive");
+  if (int e = validate_round(&rule->scale_round, "scale rounding")) return e;
+  out->quant_max = rule->quant_max;
+  out->power_of_two = rule->power_of_two;
+  int ex;
+  // floor(log2(quant_max)) as the reference computes it in double precision
+  frexp((double)rule->quant_max, &ex);
+  out->qmax_exp = ex - 1;
+  out->global_scale = rule->global_scale;
+  out->global_scale_dtype = rule->global_scale_dtype;
+  out->scale_round = make_round(&rule->scale_round);
+  return VQ_OK;
+}
+
+static int launch_mx(const void* in, void* scale_out, void* codes_out, int dtype, const VqBlocks* b,
+                     const VqScaleRule* rule, const VqRound* round, bool write_codes, cudaStream_t st) {
+  if (!b) return fail(VQ_EINVAL, "block geometry missing");
+  VQ_REQUIRE(b->O >= 0 && b->A >= 0 && b->M >= 0 && b->B >= 0 && b->I >= 0, "negative extent");
+  VQ_REQUIRE(b->block_a >= 1 && b->block_b >= 1, "block sizes must be >= 1");
+  ScaleRule sr;
+  if (int e = to_rule(rule, &sr)) return e;
+  if (int e = validate_round(round, "element rounding")) return e;
+  Round r = make_round(round);
+  const int64_t n = b->O * b->A * b->M * b->B * b->I;
+  if (n == 0) return VQ_OK;
+  const int V = vec_width(dtype);
+  const bool rows_ok = b->I == 1 && b->block_a == 1 && (b->B % V) == 0 && (b->block_b % V) == 0 &&
+                       aligned16(in) && (!write_codes || aligned16(codes_out));
+  int G = rows_ok ? b->block_b / V : 0;
+  const bool g_ok = rows_ok && G >= 1 && G <= 32 && (G & (G - 1)) == 0;
+  if (g_ok) {
+    const int64_t rows = b->O * b->A * b->M;
+    const int64_t nblk = (b->B + b->block_b - 1) / b->block_b;
+    const int64_t slots_per_row = nblk * G;
+    int64_t total = rows * slots_per_row;
+    total = (total + 31) / 32 * 32;
+    int grid = grid_for(total, 256, 8);
+    VQ_DISPATCH_DTYPE(dtype, {
+      if (write_codes)
+        mx_rows_kernel<DT, true><<<grid, 256, 0, st>>>(in, scale_out, codes_out, rows, b->B, b->block_b, G,
+                                                       slots_per_row, total, sr, r);
+      else
+        mx_rows_kernel<DT, false><<<grid, 256, 0, st>>>(in, scale_out, codes_out, rows, b->B, b->block_b, G,
+                                                        slots_per_row, total, sr, r);
+    });
+    return check_launch("mx_rows_kernel");
+  }
+  Blocks g{b->O, b->A, b->M, b->B, b->I, b->block_a, b->block_b,
+           (b->A + b->block_a - 1) / b->block_a, (b->B + b->block_b - 1) / b->block_b};
+  const int64_t total = g.O * g.nA * g.M * g.nB * g.I;
+  int grid = grid_for(total, 256, 8);
+  VQ_DISPATCH_DTYPE(dtype, {
+    if (write_codes)
+      mx_generic_kernel<DT, true><<<grid, 256, 0, st>>>(in, scale_out, codes_out, g, sr, r);
+    else
+      mx_generic_kernel<DT, false><<<grid, 256, 0, st>>>(in, scale_out, codes_out, g, sr, r);
+  });
+  return check_launch("mx_generic_kernel");
+}
+
+}  // namespace vq
+
+using namespace vq;
+
+extern "C" {
+
+const char* vq_last_error(void) { return error_buffer(); }
+int vq_version(void) { return 1; }
+
+int vq_vmap(const void* in, void* out, int dtype, const VqRound* round, int64_t n, void* stream) {
+  VQ_REQUIRE(n >= 0, "vq_vmap: negative size");
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(in && out && round, "vq_vmap: null argument");
+  if (int e = validate_round(round, "vq_vmap")) return e;
+  Round r = make_round(round);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int vec_ok = aligned16(in) && aligned16(out);
+  int grid = grid_for((n + vec_width(dtype) - 1) / vec_width(dtype), 256, 8);
+  VQ_DISPATCH_DTYPE(dtype, (vmap_kernel<DT><<<grid, 256, 0, st>>>(in, out, r, n, vec_ok)));
+  return check_launch("vmap_kernel");
+}
+
+static int scale_map(int kind, const void* in, const void* scale, const void* zp, void* out, int dtype,
+                     int param_dtype, const VqBroadcast* geom, const VqRound* r_in, const VqRound* r_out, void* stream) {
+  Geom g;
+  int64_t n;
+  if (int e = to_geom(geom, &g, &n)) return e;
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(in && scale && out, "quantize/dequantize: null argument");
+  VQ_REQUIRE(param_dtype >= VQ_BF16 && param_dtype <= VQ_F32, "quantize/dequantize: bad parameter dtype");
+  if (int e = validate_round(r_in, "input rounding")) return e;
+  if (int e = validate_round(r_out, "output rounding")) return e;
+  Round ri = make_round(r_in), ro = make_round(r_out);
+  int scalar = 1;
+  for (int d = 0; d < g.ndim; ++d)
+    if (g.stride[d] != 0 && g.size[d] > 1 && (g.size[d] + g.div[d] - 1) / g.div[d] > 1) scalar = 0;
+  const int V = vec_width(dtype);
+  int vec_ok = aligned16(in) && aligned16(out);
+  if (!scalar) vec_ok = vec_ok && (g.size[g.ndim - 1] % V) == 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int grid = grid_for(vec_ok ? (n + V - 1) / V : n, 256, 8);
+  VQ_DISPATCH_DTYPE(dtype, {
+    if (kind == 0)
+      scale_map_kernel<DT, 0><<<grid, 256, 0, st>>>(in, scale, zp, out, g, ri, ro, n, scalar, vec_ok, param_dtype);
+    else
+      scale_map_kernel<DT, 1><<<grid, 256, 0, st>>>(in, scale, zp, out, g, ri, ro, n, scalar, vec_ok, param_dtype);
+  });
+  return check_launch("scale_map_kernel");
+}
+
+int vq_quantize(const void* in, const void* scale, const void* zero_point, void* out, int dtype,
+                int param_dtype, const VqBroadcast* geom, const VqRound* round, void* stream) {
+  return scale_map(0, in, scale, zero_point, out, dtype, param_dtype, geom, nullptr, round, stream);
+}
+
+int vq_dequantize(const void* in, const void* scale, const void* zero_point, void* out, int dtype,
+                  int param_dtype, const VqBroadcast* geom, const VqRound* round_in, const VqRound* round_out,
+                  void* stream) {
+  return scale_map(1, in, scale, zero_point, out, dtype, param_dtype, geom, round_in, round_out, stream);
+}
+
+int vq_mx_qparam(const void* in, void* scale_out, int dtype, const VqBlocks* blocks, const VqScaleRule* rule,
+                 void* stream) {
+  VQ_REQUIRE(in && scale_out, "vq_mx_qparam: null argument");
+  return launch_mx(in, scale_out, nullptr, dtype, blocks, rule, nullptr, false, static_cast<cudaStream_t>(stream));
+}
+
+int vq_quantize_mx(const void* in, void* scale_out, void* codes_out, int dtype, const VqBlocks* blocks,
+                   const VqScaleRule* rule, const VqRound* round, void* stream) {
+  VQ_REQUIRE(in && scale_out && codes_out, "vq_quantize_mx: null argument");
+  return launch_mx(in, scale_out, codes_out, dtype, blocks, rule, round, true, static_cast<cudaStream_t>(stream));
+}
+
+int vq_quantize_affine(const void* in, void* scale_out, void* zero_out, void* codes_out, int dtype,
+                       const VqBlocks* b, float quant_min, float quant_max, const VqRound* scale_round,
+                       const VqRound* round, void* stream) {
+  VQ_REQUIRE(in && scale_out && zero_out && codes_out && b, "vq_quantize_affine: null argument");
+  VQ_REQUIRE(b->block_a == 1 && b->A == 1 && b->M == 1, "vq_quantize_affine: blocks lie along one axis (B)");
+  VQ_REQUIRE(b->block_b >= 1, "vq_quantize_affine: block size must be >= 1");
+  VQ_REQUIRE(quant_max > quant_min, "vq_quantize_affine: empty code range");
+  if (int e = validate_round(scale_round, "scale rounding")) return e;
+  if (int e = validate_round(round, "element rounding")) return e;
+  Round sr = make_round(scale_round), r = make_round(round);
+  const int64_t n = b->O * b->B * b->I;
+  if (n == 0) return VQ_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int V = vec_width(dtype);
+  const int64_t nB = (b->B + b->block_b - 1) / b->block_b;
+  int G = b->block_b / V;
+  const bool rows_ok = b->I == 1 && (b->B % V) == 0 && (b->block_b % V) == 0 && G >= 1 && G <= 32 &&
+                       (G & (G - 1)) == 0 && aligned16(in) && aligned16(codes_out);
+  if (rows_ok) {
+    const int64_t slots_per_row = nB * G;
+    int64_t total = b->O * slots_per_row;
+    total = (total + 31) / 32 * 32;
+    int grid = grid_for(total, 256, 8);
+    VQ_DISPATCH_DTYPE(dtype, (affine_rows_kernel<DT><<<grid, 256, 0, st>>>(
+        in, scale_out, zero_out, codes_out, b->O, b->B, b->block_b, G, slots_per_row, total, quant_min,
+        quant_max, sr, r)));
+    return check_launch("affine_rows_kernel");
+  }
+  int grid = grid_for(b->O * nB * b->I, 256, 8);
+  VQ_DISPATCH_DTYPE(dtype, (affine_generic_kernel<DT><<<grid, 256, 0, st>>>(
+      in, scale_out, zero_out, codes_out, b->O, b->B, b->I, b->block_b, nB, quant_min, quant_max, sr, r)));
+  return check_launch("affine_generic_kernel");
+}
+
+int vq_dequantize_mx(const void* in, const void* scale, const void* code, int32_t n_code,
+                     const void* global_scale, int global_scale_dtype, void* out, int dtype,
+                     const VqBroadcast* geom, void* stream) {
+  Geom g;
+  int64_t n;
+  if (int e = to_geom(geom, &g, &n)) return e;
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(in && out, "vq_dequantize_mx: null argument");
+  VQ_REQUIRE(!code || n_code > 0, "vq_dequantize_mx: empty codebook");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int grid = grid_for(n, 256, 8);
+  VQ_DISPATCH_DTYPE(dtype, (dequantize_mx_kernel<DT><<<grid, 256, 0, st>>>(in, scale, code, n_code, global_scale,
+                                                                         global_scale_dtype, out, g, n)));
+  return check_launch("dequantize_mx_kernel");
+}
+
+int vq_amax(const void* in, int dtype, int64_t n, float* out, void* stream) {
+  VQ_REQUIRE(n >= 0 && out, "vq_amax: bad argument");
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(in != nullptr, "vq_amax: null input");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int vec_ok = aligned16(in);
+  int grid = grid_for((n + vec_width(dtype) - 1) / vec_width(dtype), 256, 4);
+  VQ_DISPATCH_DTYPE(dtype, (amax_kernel<DT><<<grid, 256, 0, st>>>(in, n, vec_ok, reinterpret_cast<uint32_t*>(out))));
+  return check_launch("amax_kernel");
+}
+
+}  // extern "C"

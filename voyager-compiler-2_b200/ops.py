@@ -1,0 +1,541 @@
+"""The ``quantized_ops`` torch library, backed by sm_100a CUDA kernels.
+
+Defines the same operator names and schemas as the reference's
+``src/voyager_compiler/ops/quantized.py`` (``Library("quantized_ops", "DEF")``
+at ``:97``) and ``ops/layout.py`` (the ``FRAGMENT`` at ``:140``), so a graph
+produced by the reference's ``convert_pt2e`` runs unchanged.  Only the ``CUDA``
+dispatch key gets kernels (calls into ``libvq_b200.so``) plus ``Meta`` shape
+functions for tracing; there is deliberately no CPU implementation.
+
+Do not import this module in a process that has imported the reference's
+``voyager_compiler.ops``: both define the ``quantized_ops`` namespace.
+"""
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+from torch.library import Library
+
+from . import _native as N
+from . import rounding as R
+
+LINEAR_LAYOUT = "xc,kc->xk"
+MATMUL_LAYOUT = "xc,ck->xk"
+DEFAULT_TENSOR_LAYOUT = "nchw"
+QMAP_SIZE = 1 << 16
+HADAMARD_SIZE = 16
+
+quantized_ops_lib = Library("quantized_ops", "DEF")
+
+_DTYPE_ID = {torch.bfloat16: N.VQ_BF16, torch.float16: N.VQ_F16, torch.float32: N.VQ_F32}
+
+
+def _dtype_id(dtype):
+    try:
+        return _DTYPE_ID[dtype]
+    except KeyError:
+        raise TypeError(f"quantized_ops kernels take bfloat16, float16 or float32 tensors, not {dtype}") from None
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _dense_like(x):
+    """``x`` in a dense layout an elementwise kernel can walk in memory order,
+    and an empty output with the same strides."""
+    if not x.is_non_overlapping_and_dense():
+        x = x.contiguous()
+    return x, torch.empty_like(x)
+
+
+# ---------------------------------------------------------------------------
+# rounding selection from operator arguments
+# ---------------------------------------------------------------------------
+def _is_table(qmap):
+    return qmap.numel() == QMAP_SIZE and qmap.dim() == 1
+
+
+def _element_round(qmap, output_code, seed):
+    if qmap is None:
+        return R.none_round()
+    if seed is not None:
+        return R.stochastic_round(qmap, seed)
+    if _is_table(qmap):
+        return R.table_round(qmap)
+    if qmap.dim() == 1:
+        return R.search_round(qmap, output_code)
+    raise NotImplementedError("region codebooks are handled by the caller")
+
+
+# ---------------------------------------------------------------------------
+# vmap
+# ---------------------------------------------------------------------------
+quantized_ops_lib.define("vmap(Tensor self, Tensor other) -> Tensor")
+
+
+def vmap(input: torch.Tensor, qmap: torch.Tensor) -> torch.Tensor:
+    """Round through a 65 536-entry table (reference ``quantized.py:151-184``)."""
+    x, out = _dense_like(input)
+    spec = R.table_round(qmap)
+    N.check(N.lib().vq_vmap(x.data_ptr(), out.data_ptr(), _dtype_id(x.dtype), spec.ref, x.numel(), _stream()),
+            "vq_vmap")
+    return out
+
+
+quantized_ops_lib.impl("vmap", vmap, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::vmap")
+def _(input, qmap):
+    return torch.empty_like(input)
+
+
+# ---------------------------------------------------------------------------
+# broadcast geometry of scale / zero point against the input
+# ---------------------------------------------------------------------------
+def _broadcast_geometry(shape: Sequence[int], param: torch.Tensor, block_size: Optional[int]):
+    """Collapse (input shape, parameter shape/strides, block size) into at most
+    ``N.MAX_DIMS`` groups ``(size, div, stride)`` with
+    ``param_index = sum (coord // div) * stride``."""
+    nd = len(shape)
+    pshape = list(param.shape)
+    pstride = list(param.stride())
+    if len(pshape) > nd:
+        raise ValueError(f"parameter of shape {tuple(param.shape)} has more axes than the input {tuple(shape)}")
+    pad = nd - len(pshape)
+    pshape = [1] * pad + pshape
+    pstride = [0] * pad + pstride
+    dims = []
+    for size, ps, st in zip(shape, pshape, pstride):
+        if ps == size:
+            dims.append((size, 1, st if size > 1 else 0))
+        elif block_size is not None:
+            blocks = -(-size // block_size)
+            if ps != blocks and not (ps == 1 and size <= block_size):
+                raise ValueError(
+                    f"parameter extent {ps} does not match {size} elements in blocks of {block_size}")
+            dims.append((size, block_size, st if ps > 1 else 0))
+        elif ps == 1:
+            dims.append((size, 1, 0))
+        else:
+            raise ValueError(f"parameter of shape {tuple(param.shape)} does not broadcast to {tuple(shape)}")
+    # collapse: drop size-1 dims; merge neighbours that are both broadcast
+    # (stride 0) or both dense-unblocked with compatible strides
+    merged = []
+    for size, div, st in dims:
+        if size == 1:
+            continue
+        if merged:
+            psize, pdiv, pst = merged[-1]
+            if st == 0 and pst == 0:
+                merged[-1] = (psize * size, 1, 0)
+                continue
+            if div == 1 and pdiv == 1 and st != 0 and pst == st * size:
+                merged[-1] = (psize * size, 1, st)
+                continue
+        merged.append((size, div if st != 0 else 1, st))
+    if not merged:
+        merged = [(1, 1, 0)]
+    if len(merged) > N.MAX_DIMS:
+        raise NotImplementedError(f"parameter broadcast needs {len(merged)} index groups (max {N.MAX_DIMS})")
+    g = N.VqBroadcast()
+    g.ndim = len(merged)
+    for i, (size, div, st) in enumerate(merged):
+        g.size[i], g.div[i], g.stride[i] = size, div, st
+    return g
+
+
+def _prepare_params(x, scale, zero_point):
+    """Compute dtype and parameter tensors for ``x (op) scale``: torch's type
+    promotion, except that a single-element float32 scale next to 16-bit data
+    is used at full precision without widening the result."""
+    if zero_point is not None and (zero_point.shape != scale.shape or zero_point.dtype != scale.dtype):
+        shape = torch.broadcast_shapes(scale.shape, zero_point.shape)
+        dtype = torch.promote_types(scale.dtype, zero_point.dtype)
+        scale = scale.to(dtype).expand(shape).contiguous()
+        zero_point = zero_point.to(dtype).expand(shape).contiguous()
+    out_dtype = torch.result_type(x, scale)
+    if zero_point is not None:
+        out_dtype = torch.promote_types(out_dtype, torch.result_type(x, zero_point))
+    if x.dtype != out_dtype:
+        x = x.to(out_dtype)
+    if scale.dtype != out_dtype:
+        if scale.dim() == 0 and scale.dtype == torch.float32 and scale.is_floating_point():
+            pass  # used at float32 precision
+        else:
+            scale = scale.to(out_dtype)
+            zero_point = None if zero_point is None else zero_point.to(out_dtype)
+    return x, scale, zero_point
+
+
+def _region_apply(input, codebook, fn):
+    """Apply ``fn(flat_region_rows, region_index)`` per codebook region of a
+    ``[*counts, k]`` codebook and put the results back in place."""
+    counts = tuple(codebook.shape[:-1])
+    if len(counts) != input.dim():
+        raise ValueError(
+            f"a {list(counts)} region codebook tiles {len(counts)} axes, but the tensor reaching it has "
+            f"{input.dim()}")
+    if any(extent % count for extent, count in zip(input.shape, counts)):
+        raise ValueError(f"a {list(counts)} region codebook does not divide the {list(input.shape)} tensor reaching it")
+    split = []
+    for extent, count in zip(input.shape, counts):
+        split += [count, extent // count]
+    n = len(counts)
+    order = list(range(0, 2 * n, 2)) + list(range(1, 2 * n, 2))
+    inverse = [order.index(i) for i in range(2 * n)]
+    moved = input.reshape(split).permute(order)
+    regions = math.prod(counts)
+    flat = moved.reshape(regions, -1).contiguous()
+    out = torch.empty_like(flat)
+    for r in range(regions):
+        out[r] = fn(flat[r], r)
+    return out.view(moved.shape).permute(inverse).reshape(input.shape)
+
+
+# ---------------------------------------------------------------------------
+# quantize / dequantize
+# ---------------------------------------------------------------------------
+quantized_ops_lib.define(
+    "quantize(Tensor input, Tensor scale, Tensor? zero_point=None, "
+    "SymInt[]? axes=None, int? block_size=None, Tensor? qmap=None, "
+    "Tensor? output_code=None, Tensor? seed=None) -> Tensor"
+)
+
+
+def _quantize_with(x, scale, zero_point, block_size, spec):
+    x, scale, zero_point = _prepare_params(x, scale, zero_point)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    geom = _broadcast_geometry(x.shape, scale, block_size)
+    N.check(N.lib().vq_quantize(x.data_ptr(), scale.data_ptr(), _ptr(zero_point), out.data_ptr(),
+                                _dtype_id(x.dtype), _dtype_id(scale.dtype), geom, spec.ref, _stream()),
+            "vq_quantize")
+    return out
+
+
+def quantize(input, scale, zero_point=None, axes=None, block_size=None, qmap=None, output_code=None, seed=None):
+    """``round(input / scale [+ zero_point])`` (reference ``quantized.py:458-515``)."""
+    if qmap is not None and seed is None and not _is_table(qmap) and qmap.dim() > 1:
+        # One codebook per region (e.g. per attention head): scale first, then
+        # search each region against its own entries.
+        scaled = _quantize_with(input, scale, zero_point, block_size, R.none_round())
+        tables = qmap.reshape(-1, qmap.shape[-1])
+        bounds = None if output_code is None else output_code.reshape(tables.shape[0], -1)
+
+        def per_region(rows, r):
+            spec = R.search_round(tables[r], None if bounds is None else bounds[r])
+            return _quantize_with(rows, rows.new_ones(()), None, None, spec)
+
+        return _region_apply(scaled, qmap, per_region)
+    return _quantize_with(input, scale, zero_point, block_size, _element_round(qmap, output_code, seed))
+
+
+quantized_ops_lib.impl("quantize", quantize, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::quantize")
+def _(input, scale, zero_point=None, axes=None, block_size=None, qmap=None, output_code=None, seed=None):
+    dtype = torch.result_type(input, scale)
+    return torch.empty_like(input, dtype=dtype, memory_format=torch.contiguous_format)
+
+
+quantized_ops_lib.define(
+    "dequantize(Tensor input, Tensor scale, Tensor? zero_point=None, "
+    "SymInt[]? axes=None, int? block_size=None, Tensor? input_qmap=None, "
+    "Tensor? output_qmap=None) -> Tensor"
+)
+
+
+def dequantize(input, scale, zero_point=None, axes=None, block_size=None, input_qmap=None, output_qmap=None):
+    """``round_out((round_in(input) - zero_point) * scale)`` (reference ``quantized.py:527-571``)."""
+    x = input
+    if input_qmap is not None and torch.result_type(x, scale) != x.dtype:
+        x = vmap(x, input_qmap)  # rounds in the input's dtype before the promotion
+        input_qmap = None
+    x, scale, zero_point = _prepare_params(x, scale, zero_point)
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    geom = _broadcast_geometry(x.shape, scale, block_size)
+    r_in = R.none_round() if input_qmap is None else R.table_round(input_qmap)
+    r_out = R.none_round() if output_qmap is None else R.table_round(output_qmap)
+    N.check(N.lib().vq_dequantize(x.data_ptr(), scale.data_ptr(), _ptr(zero_point), out.data_ptr(),
+                                  _dtype_id(x.dtype), _dtype_id(scale.dtype), geom, r_in.ref, r_out.ref, _stream()),
+            "vq_dequantize")
+    return out
+
+
+quantized_ops_lib.impl("dequantize", dequantize, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::dequantize")
+def _(input, scale, zero_point=None, axes=None, block_size=None, input_qmap=None, output_qmap=None):
+    dtype = torch.result_type(input, scale)
+    return torch.empty_like(input, dtype=dtype, memory_format=torch.contiguous_format)
+
+
+# ---------------------------------------------------------------------------
+# microscaling
+# ---------------------------------------------------------------------------
+def _block_geometry(shape, axes, block_size):
+    """``(VqBlocks, scale_shape)`` for blocks of ``block_size`` along one or two axes."""
+    nd = len(shape)
+    axes = [axes] if isinstance(axes, int) else list(axes)
+    axes = sorted({a + nd if a < 0 else a for a in axes})
+    if not axes or len(axes) > 2 or any(a < 0 or a >= nd for a in axes):
+        raise NotImplementedError(f"blocks along axes {axes} of a {nd}-d tensor")
+    b = N.VqBlocks()
+    prod = lambda xs: int(math.prod(xs))  # noqa: E731
+    if len(axes) == 1:
+        (a,) = axes
+        b.O, b.A, b.M, b.B, b.I = prod(shape[:a]), 1, 1, shape[a], prod(shape[a + 1:])
+        b.block_a, b.block_b = 1, block_size
+    else:
+        a0, a1 = axes
+        b.O, b.A, b.M = prod(shape[:a0]), shape[a0], prod(shape[a0 + 1:a1])
+        b.B, b.I = shape[a1], prod(shape[a1 + 1:])
+        b.block_a, b.block_b = block_size, block_size
+    scale_shape = list(shape)
+    for a in axes:
+        scale_shape[a] = -(-shape[a] // block_size)
+    return b, scale_shape
+
+
+def _scale_rule(x, quant_max, power_of_two, scale_qmap, global_scale):
+    rule = N.VqScaleRule()
+    rule.quant_max = float(quant_max)
+    rule.power_of_two = int(bool(power_of_two))
+    keep = []
+    if global_scale is not None:
+        if global_scale.numel() != 1:
+            raise ValueError("global_scale must hold one element")
+        gs = global_scale
+        if gs.dtype not in _DTYPE_ID:
+            gs = gs.to(x.dtype)
+        if gs.dtype != x.dtype and not (gs.dim() == 0 and gs.dtype == torch.float32):
+            gs = gs.to(torch.promote_types(gs.dtype, x.dtype))
+        gs = gs.to(x.device)
+        rule.global_scale = gs.data_ptr()
+        rule.global_scale_dtype = _dtype_id(gs.dtype)
+        keep.append(gs)
+    if scale_qmap is not None and not power_of_two:
+        spec = R.table_round(scale_qmap)
+        rule.scale_round = spec.c
+        keep.append(spec)
+    else:
+        rule.scale_round.mode = N.ROUND_NONE
+    return rule, keep
+
+
+quantized_ops_lib.define(
+    "calculate_mx_qparam(Tensor self, SymInt[] axes, int block_size, "
+    "float quant_max, bool force_scale_power_of_two=False, "
+    "Tensor scale_qmap=None, Tensor? global_scale=None) -> Tensor"
+)
+
+
+def _mx_compute_dtype(x, global_scale):
+    if global_scale is not None and global_scale.dim() > 0 and global_scale.is_floating_point():
+        return torch.promote_types(x.dtype, global_scale.dtype)
+    return x.dtype
+
+
+def calculate_mx_qparam(input, axes, block_size, quant_max, force_scale_power_of_two=False, scale_qmap=None,
+                        global_scale=None):
+    """Per-block scale (reference ``quantized.py:966-1031``)."""
+    assert block_size > 0
+    x = input.contiguous()
+    blocks, scale_shape = _block_geometry(x.shape, axes, block_size)
+    rule, keep = _scale_rule(x, quant_max, force_scale_power_of_two, scale_qmap, global_scale)
+    scale = torch.empty(scale_shape, dtype=x.dtype, device=x.device)
+    N.check(N.lib().vq_mx_qparam(x.data_ptr(), scale.data_ptr(), _dtype_id(x.dtype), blocks, rule, _stream()),
+            "vq_mx_qparam")
+    del keep
+    return scale
+
+
+quantized_ops_lib.impl("calculate_mx_qparam", calculate_mx_qparam, "CUDA")
+
+
+def _scale_shape(shape, axes, block_size):
+    nd = len(shape)
+    axes = [axes] if isinstance(axes, int) else list(axes)
+    out = list(shape)
+    for a in axes:
+        out[a % nd] = -(-shape[a % nd] // block_size)
+    return out
+
+
+@torch.library.register_fake("quantized_ops::calculate_mx_qparam")
+def _(input, axes, block_size, quant_max, force_scale_power_of_two=False, scale_qmap=None, global_scale=None):
+    return input.new_empty(_scale_shape(input.shape, axes, block_size))
+
+
+quantized_ops_lib.define(
+    "quantize_mx(Tensor self, Tensor qmap, SymInt[] axes, int block_size, "
+    "float quant_max, bool force_scale_power_of_two=False, "
+    "Tensor scale_qmap=None, Tensor output_code=None, Tensor? seed=None, "
+    "Tensor? global_scale=None) -> (Tensor, Tensor)"
+)
+
+
+def quantize_mx(input, qmap, axes, block_size, quant_max, force_scale_power_of_two=False, scale_qmap=None,
+                output_code=None, seed=None, global_scale=None):
+    """One pass: block amax -> scale -> codes (reference ``quantized.py:1080-1115``).
+    Returns ``(scale, codes)``."""
+    assert block_size > 0
+    x = input.contiguous()
+    if qmap is not None and seed is None and not _is_table(qmap) and qmap.dim() > 1:
+        scale = calculate_mx_qparam(x, axes, block_size, quant_max, force_scale_power_of_two, scale_qmap,
+                                    global_scale)
+        element_scale = scale if global_scale is None else scale * global_scale
+        return scale, quantize(x, element_scale, None, axes, block_size, qmap, output_code, None)
+    blocks, scale_shape = _block_geometry(x.shape, axes, block_size)
+    rule, keep = _scale_rule(x, quant_max, force_scale_power_of_two, scale_qmap, global_scale)
+    spec = _element_round(qmap, output_code, seed)
+    scale = torch.empty(scale_shape, dtype=x.dtype, device=x.device)
+    codes = torch.empty_like(x)
+    N.check(N.lib().vq_quantize_mx(x.data_ptr(), scale.data_ptr(), codes.data_ptr(), _dtype_id(x.dtype), blocks,
+                                   rule, spec.ref, _stream()), "vq_quantize_mx")
+    del keep
+    return scale, codes
+
+
+quantized_ops_lib.impl("quantize_mx", quantize_mx, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::quantize_mx")
+def _(input, qmap, axes, block_size, quant_max, force_scale_power_of_two=False, scale_qmap=None,
+      output_code=None, seed=None, global_scale=None):
+    return (input.new_empty(_scale_shape(input.shape, axes, block_size)),
+            torch.empty_like(input, memory_format=torch.contiguous_format))
+
+
+quantized_ops_lib.define(
+    "dequantize_mx(Tensor self, Tensor scale, int block_size, "
+    "Tensor? code=None, Tensor? global_scale=None) -> Tensor"
+)
+
+
+def _decode_and_scale(x, scale, code, block_size, global_scale=None):
+    """``code[x] * scale [* global_scale]`` with each product rounded to the
+    operand dtype (reference ``quantized.py:574-591``)."""
+    if code is not None and code.dim() != 1:
+        tables = code.reshape(-1, code.shape[-1])
+        x = _region_apply(x.contiguous(), code,
+                          lambda rows, r: _decode_and_scale(rows, None, tables[r].contiguous(), None))
+        code = None
+        if scale is None and global_scale is None:
+            return x
+    dtype = x.dtype
+    if scale is not None:
+        dtype = torch.promote_types(dtype, scale.dtype) if scale.dim() > 0 else dtype
+    if global_scale is not None and global_scale.dim() > 0:
+        dtype = torch.promote_types(dtype, global_scale.dtype)
+    x = x.contiguous()
+    if dtype != x.dtype:
+        if code is not None:
+            x = _decode_and_scale(x, None, code, None)  # entries are read in the code's dtype first
+            code = None
+        x = x.to(dtype)
+    if scale is not None and scale.dtype != dtype:
+        scale = scale.to(dtype)
+    if code is not None and code.dtype != dtype:
+        code = code.to(dtype)
+    out = torch.empty_like(x)
+    if scale is not None:
+        geom = _broadcast_geometry(x.shape, scale, block_size)
+    else:
+        geom = N.VqBroadcast()
+        geom.ndim = 1
+        geom.size[0], geom.div[0], geom.stride[0] = x.numel(), 1, 0
+    gs_dtype = 0
+    if global_scale is not None:
+        if global_scale.dtype != dtype and not (global_scale.dim() == 0 and global_scale.dtype == torch.float32):
+            global_scale = global_scale.to(dtype)
+        gs_dtype = _dtype_id(global_scale.dtype)
+    N.check(N.lib().vq_dequantize_mx(x.data_ptr(), _ptr(scale), None if code is None else code.contiguous().data_ptr(),
+                                     0 if code is None else code.numel(), _ptr(global_scale), gs_dtype,
+                                     out.data_ptr(), _dtype_id(dtype), geom, _stream()), "vq_dequantize_mx")
+    return out
+
+
+def dequantize_mx(input, scale, block_size, code=None, global_scale=None):
+    """Read codes back as values (reference ``quantized.py:1125-1149``)."""
+    return _decode_and_scale(input, scale, code, block_size, global_scale)
+
+
+quantized_ops_lib.impl("dequantize_mx", dequantize_mx, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::dequantize_mx")
+def _(input, scale, block_size, code=None, global_scale=None):
+    dtype = torch.promote_types(input.dtype, scale.dtype)
+    if global_scale is not None:
+        dtype = torch.promote_types(dtype, global_scale.dtype)
+    return input.new_empty(input.shape, dtype=dtype)
+
+
+# ---------------------------------------------------------------------------
+# group-wise affine (KIVI)
+# ---------------------------------------------------------------------------
+quantized_ops_lib.define(
+    "quantize_affine(Tensor self, Tensor qmap, SymInt[] axes, int block_size, "
+    "float quant_min, float quant_max, Tensor scale_qmap=None) "
+    "-> (Tensor, Tensor, Tensor)"
+)
+
+
+def quantize_affine(input, qmap, axes, block_size, quant_min, quant_max, scale_qmap=None):
+    """Per-block ``[min, max] -> [quant_min, quant_max]`` (reference
+    ``quantized.py:1227-1283``).  Returns ``(scale, zero_point, codes)``."""
+    assert block_size > 0
+    (axis,) = axes
+    x = input.contiguous()
+    blocks, scale_shape = _block_geometry(x.shape, [axis], block_size)
+    spec = R.table_round(qmap)
+    sspec = R.none_round() if scale_qmap is None else R.table_round(scale_qmap)
+    scale = torch.empty(scale_shape, dtype=x.dtype, device=x.device)
+    zero = torch.empty_like(scale)
+    codes = torch.empty_like(x)
+    N.check(N.lib().vq_quantize_affine(x.data_ptr(), scale.data_ptr(), zero.data_ptr(), codes.data_ptr(),
+                                       _dtype_id(x.dtype), blocks, float(quant_min), float(quant_max), sspec.ref,
+                                       spec.ref, _stream()), "vq_quantize_affine")
+    return scale, zero, codes
+
+
+quantized_ops_lib.impl("quantize_affine", quantize_affine, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::quantize_affine")
+def _(input, qmap, axes, block_size, quant_min, quant_max, scale_qmap=None):
+    shape = _scale_shape(input.shape, axes, block_size)
+    return (input.new_empty(shape), input.new_empty(shape),
+            torch.empty_like(input, memory_format=torch.contiguous_format))
+
+
+# ---------------------------------------------------------------------------
+# tensor amax and the NVFP4 global scale
+# ---------------------------------------------------------------------------
+def tensor_amax(x: torch.Tensor) -> torch.Tensor:
+    """``max |x|`` as a 0-d float32 tensor (one kernel, no host sync)."""
+    x = x if x.is_non_overlapping_and_dense() else x.contiguous()
+    out = torch.zeros((), dtype=torch.float32, device=x.device)
+    N.check(N.lib().vq_amax(x.data_ptr(), _dtype_id(x.dtype), x.numel(), out.data_ptr(), _stream()), "vq_amax")
+    return out
+
+
+def calculate_global_scale(input: torch.Tensor, quant_max: float, scale_max: float) -> torch.Tensor:
+    """NVFP4's per-tensor scale ``amax / (quant_max * scale_max)`` in the
+    input's dtype (reference ``fake_quantize.py:142-160``)."""
+    amax = tensor_amax(input).to(input.dtype).reshape(1)
+    # A correctly rounded division by the float32 divisor, as the CPU op does.
+    divisor = torch.full((), float(quant_max * scale_max), dtype=torch.float32, device=input.device)
+    ratio = _quantize_with(amax, divisor, None, None, R.none_round()).reshape(())
+    return ratio.clamp_min(torch.finfo(torch.float32).tiny)
