@@ -57,12 +57,12 @@ typedef struct VqRound {
   int32_t emin, mbits;    /* MINIFLOAT: min normal exponent, mantissa bits */
   float max_norm;         /* MINIFLOAT: saturation magnitude */
   int32_t is_signed;      /* MINIFLOAT: 0 takes |v| first */
-  /* STEPS: level k is chosen for sign-magnitude-ordered bf16 keys in
-     [step_key[k-1], step_key[k]); step_value holds the levels as bf16 bits;
-     nan_value the result for a NaN input. */
+  /* STEPS: device uint16[2 * n_steps]: first n_steps exclusive upper keys (in
+     the value-ordered key space of bf16 bit patterns: negatives below
+     positives), then n_steps level values as bf16 bits.  Level k is chosen for
+     keys in [key[k-1], key[k]); nan_value is the result for a NaN input. */
   int32_t n_steps;
-  uint16_t step_key[VQ_MAX_STEPS];
-  uint16_t step_value[VQ_MAX_STEPS];
+  const void* steps;
   uint16_t nan_value;
   /* SEARCH / STOCHASTIC: device float arrays */
   const float* edges;     /* SEARCH: ascending edges, result = #edges < v */
@@ -150,6 +150,30 @@ int vq_dequantize_mx(const void* in, const void* scale, const void* code, int32_
  * per-tensor scale rule (fake_quantize.py:406-437) start from.  `out` must
  * be zeroed by the caller; NaN inputs give NaN. */
 int vq_amax(const void* in, int dtype, int64_t n, float* out, void* stream);
+
+/* operand element kinds of the tensor-core GEMM */
+enum { VQ_IN_BF16 = 0, VQ_IN_F16 = 1, VQ_IN_E4M3 = 2, VQ_IN_E5M2 = 3 };
+
+/* The contraction of quantized_ops::linear_mx / matmul_mx (ops/quantized.py:662-805,
+ * through quantized_ops::linear / matmul, ops/layout.py:231-284) and of the
+ * real-FP8 linear (backend/gpu/fp8.py:372-429):
+ *   C[b][m][n] = round(alpha * sum_k A[b][m][k] * B[b][n][k] + bias[n])
+ * A is [batch, M, K] and B is [batch, N, K], both K-contiguous with leading
+ * dimensions lda / ldb and batch strides strideA / strideB (in elements; a
+ * batch stride of 0 shares the operand).  Products are accumulated in fp32 on
+ * the tensor cores; alpha (device scalar, may be NULL) and bias (device [N],
+ * may be NULL) are applied in fp32 as two separately rounded operations; the
+ * result is rounded once to out_dtype.  Operand pointers, leading dimensions
+ * and batch strides must be multiples of 16 bytes. */
+int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype, int64_t M, int64_t N,
+               int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA,
+               int64_t strideB, int64_t strideC, const void* alpha, int alpha_dtype, const void* bias,
+               int bias_dtype, void* stream);
+
+/* Synchronising health check for the GEMM kernels: returns VQ_ETIMEOUT if any
+ * launch since the last reset gave up on a bounded barrier wait (its output is
+ * then invalid).  No counterpart in the reference. */
+int vq_gemm_status(int reset);
 
 #ifdef __cplusplus
 }

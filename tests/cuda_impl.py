@@ -43,3 +43,9 @@ class CudaImpl:
     dequantize_mx = staticmethod(_wrap(Q.dequantize_mx))
     quantize_affine = staticmethod(_wrap(Q.quantize_affine))
     calculate_global_scale = staticmethod(_wrap(voyager_b200.calculate_global_scale))
+
+
+CudaImpl.linear_mx = staticmethod(_wrap(Q.linear_mx))
+CudaImpl.matmul_mx = staticmethod(_wrap(Q.matmul_mx))
+CudaImpl.linear = staticmethod(_wrap(Q.linear))
+CudaImpl.matmul = staticmethod(_wrap(Q.matmul))

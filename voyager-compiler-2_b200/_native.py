@@ -39,8 +39,7 @@ class VqRound(ctypes.Structure):
         ("max_norm", ctypes.c_float),
         ("is_signed", ctypes.c_int32),
         ("n_steps", ctypes.c_int32),
-        ("step_key", ctypes.c_uint16 * MAX_STEPS),
-        ("step_value", ctypes.c_uint16 * MAX_STEPS),
+        ("steps", ctypes.c_void_p),
         ("nan_value", ctypes.c_uint16),
         ("edges", ctypes.c_void_p),
         ("levels", ctypes.c_void_p),
@@ -96,7 +95,10 @@ SIGNATURES = {
                            ctypes.POINTER(VqRound), _P],
     "vq_dequantize_mx": [_P, _P, _P, ctypes.c_int32, _P, _I, _P, _I, ctypes.POINTER(VqBroadcast), _P],
     "vq_amax": [_P, _I, _I64, _P, _P],
+    "vq_gemm_tn": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
+    "vq_gemm_status": [_I],
 }
+IN_BF16, IN_F16, IN_E4M3, IN_E5M2 = range(4)
 
 
 def sources():

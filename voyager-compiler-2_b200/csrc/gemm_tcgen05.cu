@@ -1,0 +1,361 @@
+// Dense GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+//   C[b][m][n] = alpha * sum_k A[b][m][k] * B[b][n][k]  (+ bias[n])
+//
+// A and B are K-contiguous ("TN"): 16-bit (bf16 / f16) or 8-bit (e4m3 / e5m2)
+// elements; accumulation is fp32 in tensor memory; the result is rounded once.
+// This is the contraction behind quantized_ops::linear_mx / matmul_mx
+// (operands first read back through their codebooks and block scales, which
+// are exact bf16 values) and behind the real-FP8 linear.
+//
+// Structure: a persistent kernel, one CTA per SM, 128x256 output tiles.
+//   warp 0   : TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, 4 stages)
+//   warp 1   : MMA issuer    (one thread; tcgen05.mma 128x256x{16|32}), owns TMEM
+//   warps 2-5: epilogue      (tcgen05.ld -> alpha/bias -> global), overlapped with
+//              the next tile's main loop through two TMEM accumulator buffers.
+// TMA zero-fills out-of-range rows/columns, so M, N, K tails need no special
+// main-loop code; the epilogue predicates its stores.
+// Every mbarrier wait is bounded; on timeout the kernel records an error code
+// in a device flag, drains, frees TMEM and exits.
+
+#include "sm100_ptx.cuh"
+#include "vq_common.cuh"
+
+namespace vq {
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK_BYTES = 128;          // one swizzle row per operand row per stage
+constexpr int STAGES = 4;
+constexpr int MMA_K_BYTES = 32;        // K extent of one tcgen05.mma in bytes (16 x 16-bit / 32 x 8-bit)
+constexpr int A_STAGE_BYTES = BM * BK_BYTES;   // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK_BYTES;   // 32 KB
+constexpr int TMEM_COLS = 512;         // two 128x256 fp32 accumulators
+constexpr int NUM_THREADS = 192;
+constexpr size_t SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+
+__device__ int g_gemm_error = 0;
+
+struct GemmParams {
+  void* C;
+  int M, N, K;          // K in elements
+  int elem_bytes;       // 2 or 1
+  int64_t ldc, strideC;
+  int batch;
+  const void* alpha;
+  int alpha_dt;
+  const void* bias;
+  int bias_dt;
+  int out_dt;
+  uint32_t idesc;
+  int kind_f8;
+};
+
+__device__ __forceinline__ float load_param(const void* p, int64_t i, int dt) {
+  if (dt == VQ_F32) return static_cast<const float*>(p)[i];
+  if (dt == VQ_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint64_t* full_bar = bars;                 // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;       // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;    // [2]
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n * p.batch;
+  const int k_elems_per_stage = BK_BYTES / p.elem_bytes;
+  const int k_blocks = (p.K + k_elems_per_stage - 1) / k_elems_per_stage;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = (int)(tile % tiles_m);
+        const int n_blk = (int)((tile / tiles_m) % tiles_n);
+        const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full_bar[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+          tma_load_3d(smem_a + stage * A_STAGE_BYTES, &map_a, &full_bar[stage], kb * k_elems_per_stage, m_blk * BM, b);
+          tma_load_3d(smem_b + stage * B_STAGE_BYTES, &map_b, &full_bar[stage], kb * k_elems_per_stage, n_blk * BN, b);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Drain: let copies already issued land before the CTA's shared memory goes away.
+        for (int s = 0; s < STAGES; ++s)
+          for (int spin = 0; spin < (1 << 14); ++spin) {
+            if (mbar_try_wait(&full_bar[s], 0) || mbar_try_wait(&full_bar[s], 1)) break;
+          }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK_BYTES / MMA_K_BYTES; ++k) {
+            const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
+            const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            if (p.kind_f8) mma_f8f6f4_ss(tmem_acc, da, db, p.idesc, accumulate);
+            else mma_f16_ss(tmem_acc, da, db, p.idesc, accumulate);
+          }
+          mma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&acc_full[acc]);  // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) are this warp's
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool has_alpha = p.alpha != nullptr;
+    const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m_blk = (int)(tile % tiles_m);
+      const int n_blk = (int)((tile / tiles_m) % tiles_n);
+      const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      // The warp must stay convergent for the .sync.aligned TMEM loads below.
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m_blk * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
+      uint8_t* c_row = static_cast<uint8_t*>(p.C) +
+                       ((int64_t)b * p.strideC + (int64_t)row * p.ldc) * (p.out_dt == VQ_F32 ? 4 : 2);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + (uint32_t)c0, v);
+        tmem_ld_wait();
+        const int col0 = n_blk * BN + c0;
+        if (row < p.M && col0 < p.N) {
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(v[j]);
+            if (has_alpha) x = __fmul_rn(x, alpha);
+            f[j] = x;
+          }
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) f[j] = __fadd_rn(f[j], load_param(p.bias, col0 + j, p.bias_dt));
+          }
+          const bool full = (col0 + 32 <= p.N);
+          if (p.out_dt == VQ_F32) {
+            float* dst = reinterpret_cast<float*>(c_row) + col0;
+            if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = f[j];
+            }
+          } else {
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (p.out_dt == VQ_BF16) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+                packed[j] = *reinterpret_cast<uint32_t*>(&h);
+              } else {
+                __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+                packed[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+            }
+            uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
+            if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = (uint16_t)(packed[j >> 1] >> (16 * (j & 1)));
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// Tensor map over a [batch, rows, k] K-contiguous operand; box = 128 bytes of K x box_rows rows.
+int make_operand_map(CUtensorMap* map, const void* base, int elem_kind, int elem_bytes, int64_t rows, int64_t k,
+                     int64_t ld, int64_t batch, int64_t batch_stride, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                           : (elem_kind == VQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                  : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)(ld * elem_bytes), (cuuint64_t)((batch > 1 ? batch_stride : ld * rows) * elem_bytes)};
+  cuuint32_t box[3] = {(cuuint32_t)(BK_BYTES / elem_bytes), (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return VQ_OK;
+}
+
+}  // namespace
+}  // namespace vq
+
+using namespace vq;
+
+extern "C" {
+
+int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype, int64_t M, int64_t N, int64_t K,
+               int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA, int64_t strideB,
+               int64_t strideC, const void* alpha, int alpha_dtype, const void* bias, int bias_dtype,
+               void* stream) {
+  VQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && batch >= 0, "vq_gemm_tn: negative extent");
+  if (M == 0 || N == 0 || batch == 0) return VQ_OK;
+  VQ_REQUIRE(A && B && C, "vq_gemm_tn: null operand");
+  VQ_REQUIRE(K > 0, "vq_gemm_tn: empty contraction");
+  VQ_REQUIRE(in_kind == VQ_IN_BF16 || in_kind == VQ_IN_F16 || in_kind == VQ_IN_E4M3 || in_kind == VQ_IN_E5M2,
+             "vq_gemm_tn: unknown operand kind %d", in_kind);
+  VQ_REQUIRE(out_dtype == VQ_BF16 || out_dtype == VQ_F16 || out_dtype == VQ_F32, "vq_gemm_tn: bad output dtype");
+  const int eb = (in_kind == VQ_IN_E4M3 || in_kind == VQ_IN_E5M2) ? 1 : 2;
+  VQ_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0,
+             "vq_gemm_tn: operands must be 16-byte aligned");
+  VQ_REQUIRE((lda * eb) % 16 == 0 && (ldb * eb) % 16 == 0 && (strideA * eb) % 16 == 0 && (strideB * eb) % 16 == 0,
+             "vq_gemm_tn: leading dimensions and batch strides must be multiples of 16 bytes");
+  VQ_REQUIRE(lda >= K && ldb >= K && ldc >= N, "vq_gemm_tn: leading dimension smaller than the row");
+  VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && batch < (1ll << 31), "vq_gemm_tn: extent too large");
+
+  CUtensorMap map_a, map_b;
+  const int kind = in_kind == VQ_IN_F16 ? VQ_F16 : VQ_BF16;
+  if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
+  if (int e = make_operand_map(&map_b, B, kind, eb, N, K, ldb, batch, strideB, BN)) return e;
+
+  GemmParams p{};
+  p.C = C;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.elem_bytes = eb;
+  p.ldc = ldc; p.strideC = strideC;
+  p.batch = (int)batch;
+  p.alpha = alpha; p.alpha_dt = alpha_dtype;
+  p.bias = bias; p.bias_dt = bias_dtype;
+  p.out_dt = out_dtype;
+  p.kind_f8 = eb == 1;
+  const int fmt = in_kind == VQ_IN_BF16 ? 1 : in_kind == VQ_IN_F16 ? 0 : in_kind == VQ_IN_E4M3 ? 0 : 1;
+  p.idesc = sm100::make_idesc(BM, BN, fmt, fmt, 0, 0);
+
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
+  const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
+  gemm_tn_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+  return check_launch("gemm_tn_kernel");
+}
+
+int vq_gemm_status(int reset) {
+  int value = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&value, g_gemm_error, sizeof(int));
+  if (e != cudaSuccess) return fail(VQ_ECUDA, "vq_gemm_status: %s", cudaGetErrorString(e));
+  if (reset && value != 0) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+  }
+  if (value != 0) return fail(value, "a tensor-core GEMM gave up waiting on a barrier");
+  return VQ_OK;
+}
+
+}  // extern "C"

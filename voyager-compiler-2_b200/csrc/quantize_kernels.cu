@@ -49,8 +49,8 @@ int validate_round(const VqRound* r, const char* what) {
         return fail(VQ_EINVAL, "%s: minifloat parameters out of range", what);
       return VQ_OK;
     case VQ_ROUND_STEPS:
-      if (r->n_steps < 1 || r->n_steps > VQ_MAX_STEPS)
-        return fail(VQ_EINVAL, "%s: %d steps (max %d)", what, r->n_steps, VQ_MAX_STEPS);
+      if (r->n_steps < 1 || r->n_steps > VQ_MAX_STEPS || !r->steps)
+        return fail(VQ_EINVAL, "%s: %d steps (max %d) or no step table", what, r->n_steps, VQ_MAX_STEPS);
       return VQ_OK;
     case VQ_ROUND_SEARCH:
       if (r->n_edges < 0 || (r->n_edges > 0 && !r->edges))
@@ -113,34 +113,7 @@ __device__ __forceinline__ float loadp(const void* p, int64_t i, int pdt) {
 }
 
 // ---------------------------------------------------------------------------
-// vmap
-// ---------------------------------------------------------------------------
-template <int DT>
-__global__ void __launch_bounds__(256) vmap_kernel(const void* __restrict__ in, void* __restrict__ out,
-                                                   Round r, int64_t n, int vec_ok) {
-  using E = Elem<DT>;
-  constexpr int V = E::kVec;
-  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  if (vec_ok) {
-    int64_t nvec = n / V;
-    for (int64_t v = tid; v < nvec; v += stride) {
-      Vec<DT> x, y;
-      x.raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
-#pragma unroll
-      for (int j = 0; j < V; ++j) y.set(j, apply_round(r, x.get(j), v * V + j));
-      reinterpret_cast<uint4*>(out)[v] = y.raw;
-    }
-    for (int64_t i = nvec * V + tid; i < n; i += stride)
-      store1<DT>(out, i, apply_round(r, load1<DT>(in, i), i));
-  } else {
-    for (int64_t i = tid; i < n; i += stride)
-      store1<DT>(out, i, apply_round(r, load1<DT>(in, i), i));
-  }
-}
-
-// ---------------------------------------------------------------------------
-// quantize / dequantize with broadcast parameters
+// streaming elementwise kernels: vmap, quantize, dequantize
 // ---------------------------------------------------------------------------
 struct Geom {
   int ndim;
@@ -162,92 +135,119 @@ __device__ __forceinline__ int64_t param_index(const Geom& g, int64_t flat) {
   return idx;
 }
 
-// kind 0: out = round(in / scale [+ zp]);  kind 1: out = round_out((round_in(in) - zp) * scale)
+// How the parameter (scale / zero point) index follows from the flat element
+// index on the fast path.
+enum { PI_SCALAR = 0, PI_DIV = 1, PI_MOD = 2, PI_GENERIC = 3 };
+struct ParamIndex {
+  int kind;
+  uint32_t d;      // PI_DIV: index = flat / d (d a multiple of the vector width)
+  int shift;       // PI_DIV: log2(d) when d is a power of two, else -1
+  uint32_t c;      // PI_MOD: index = flat % c (c a multiple of the vector width)
+};
+
+constexpr int kUnroll = 4;
+constexpr int kThreads = 256;
+
+// KIND 0: out = round(in / scale [+ zp])
+// KIND 1: out = round_out((round_in(in) - zp) * scale)
+// KIND 2: out = round_out(in)                       (vmap)
 template <int DT, int KIND>
-__global__ void __launch_bounds__(256)
-scale_map_kernel(const void* __restrict__ in, const void* __restrict__ scale, const void* __restrict__ zp,
-                 void* __restrict__ out, Geom g, Round r_in, Round r_out, int64_t n, int scalar_param,
-                 int vec_ok, int pdt) {
+__device__ __forceinline__ float map_one(float x, float s, float z, bool has_z, const Round& r_in,
+                                         const Round& r_out, int64_t flat) {
+  using E = Elem<DT>;
+  if (KIND == 0) {
+    float y = E::round(__fdiv_rn(x, s));
+    if (has_z) y = E::round(__fadd_rn(y, z));
+    return apply_round(r_out, y, flat);
+  } else if (KIND == 1) {
+    float y = apply_round(r_in, x, flat);
+    if (has_z) y = E::round(__fsub_rn(y, z));
+    y = E::round(__fmul_rn(y, s));
+    return apply_round(r_out, y, flat);
+  } else {
+    return apply_round(r_out, x, flat);
+  }
+}
+
+template <int DT, int KIND>
+__global__ void __launch_bounds__(kThreads, 4)
+stream_map_kernel(const void* __restrict__ in, const void* __restrict__ scale, const void* __restrict__ zp,
+                  void* __restrict__ out, Round r_in, Round r_out, int64_t n, ParamIndex pidx, int pdt,
+                  int n_is_32bit) {
   using E = Elem<DT>;
   constexpr int V = E::kVec;
-  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
-
-  auto one = [&](float x, float s, float z, bool has_z, int64_t flat) -> float {
-    if (KIND == 0) {
-      float y = E::round(__fdiv_rn(x, s));
-      if (has_z) y = E::round(__fadd_rn(y, z));
-      return apply_round(r_out, y, flat);
-    } else {
-      float y = apply_round(r_in, x, flat);
-      if (has_z) y = E::round(__fsub_rn(y, z));
-      y = E::round(__fmul_rn(y, s));
-      return apply_round(r_out, y, flat);
-    }
-  };
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  stage_steps(r_in, s_steps[0]);
+  stage_steps(r_out, s_steps[1]);
   const bool has_z = zp != nullptr;
-
-  if (scalar_param) {
-    const float s = loadp(scale, 0, pdt);
-    const float z = has_z ? loadp(zp, 0, pdt) : 0.0f;
-    if (vec_ok) {
-      int64_t nvec = n / V;
-      for (int64_t v = tid; v < nvec; v += stride) {
-        Vec<DT> x, y;
-        x.raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
-#pragma unroll
-        for (int j = 0; j < V; ++j) y.set(j, one(x.get(j), s, z, has_z, v * V + j));
-        reinterpret_cast<uint4*>(out)[v] = y.raw;
-      }
-      for (int64_t i = nvec * V + tid; i < n; i += stride)
-        store1<DT>(out, i, one(load1<DT>(in, i), s, z, has_z, i));
-    } else {
-      for (int64_t i = tid; i < n; i += stride) store1<DT>(out, i, one(load1<DT>(in, i), s, z, has_z, i));
-    }
-    return;
+  float s0 = 1.0f, z0 = 0.0f;
+  if (KIND != 2 && pidx.kind == PI_SCALAR) {
+    s0 = loadp(scale, 0, pdt);
+    if (has_z) z0 = loadp(zp, 0, pdt);
   }
-
-  // Vector path: the innermost collapsed dimension is a multiple of V, so a
-  // vector never straddles an outer coordinate; the parameter index of the
-  // vector's first element is computed once and advanced along the last dim.
-  if (vec_ok) {
-    const int last = g.ndim - 1;
-    const int64_t inner = g.size[last], idiv = g.div[last], istr = g.stride[last];
-    int64_t nvec = n / V;
-    for (int64_t v = tid; v < nvec; v += stride) {
-      int64_t flat = v * V;
-      int64_t c = flat % inner;
-      int64_t outer = flat / inner;
-      int64_t base = 0;
-      for (int d = last - 1; d >= 0; --d) {
-        int64_t cc = outer % g.size[d];
-        outer /= g.size[d];
-        base += (cc / g.div[d]) * g.stride[d];
-      }
-      Vec<DT> x, y;
-      x.raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
-      int64_t prev = -1;
-      float s = 0.f, z = 0.f;
+  const int64_t nvec = n / V;
+  const int64_t chunk = (int64_t)kThreads * kUnroll;
+  for (int64_t base = (int64_t)blockIdx.x * chunk; base < nvec; base += (int64_t)gridDim.x * chunk) {
+    Vec<DT> x[kUnroll];
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        int64_t pi = base + ((c + j) / idiv) * istr;
-        if (pi != prev) {
-          s = loadp(scale, pi, pdt);
-          if (has_z) z = loadp(zp, pi, pdt);
-          prev = pi;
+    for (int u = 0; u < kUnroll; ++u) {
+      int64_t v = base + u * kThreads + threadIdx.x;
+      if (v < nvec) x[u].raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      int64_t v = base + u * kThreads + threadIdx.x;
+      if (v >= nvec) continue;
+      const int64_t flat = v * V;
+      Vec<DT> y;
+      if (KIND == 2 || pidx.kind == PI_SCALAR) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) y.set(j, map_one<DT, KIND>(x[u].get(j), s0, z0, has_z, r_in, r_out, flat + j));
+      } else if (pidx.kind == PI_DIV) {
+        int64_t pi;
+        if (pidx.shift >= 0) pi = flat >> pidx.shift;
+        else pi = n_is_32bit ? (int64_t)((uint32_t)flat / pidx.d) : flat / pidx.d;
+        float s = loadp(scale, pi, pdt);
+        float z = has_z ? loadp(zp, pi, pdt) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) y.set(j, map_one<DT, KIND>(x[u].get(j), s, z, has_z, r_in, r_out, flat + j));
+      } else {  // PI_MOD: V consecutive parameters
+        int64_t pi = n_is_32bit ? (int64_t)((uint32_t)flat % pidx.c) : flat % pidx.c;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float s = loadp(scale, pi + j, pdt);
+          float z = has_z ? loadp(zp, pi + j, pdt) : 0.0f;
+          y.set(j, map_one<DT, KIND>(x[u].get(j), s, z, has_z, r_in, r_out, flat + j));
         }
-        y.set(j, one(x.get(j), s, z, has_z, flat + j));
       }
       reinterpret_cast<uint4*>(out)[v] = y.raw;
     }
-    return;
   }
+  // tail elements (n not a multiple of V): scalar parameters only reach here
+  if (blockIdx.x == 0) {
+    for (int64_t i = nvec * V + threadIdx.x; i < n; i += kThreads)
+      store1<DT>(out, i, map_one<DT, KIND>(load1<DT>(in, i), s0, z0, has_z, r_in, r_out, i));
+  }
+}
 
-  for (int64_t i = tid; i < n; i += stride) {
-    int64_t pi = param_index(g, i);
-    float s = loadp(scale, pi, pdt);
-    float z = has_z ? loadp(zp, pi, pdt) : 0.0f;
-    store1<DT>(out, i, one(load1<DT>(in, i), s, z, has_z, i));
+// Any broadcast, one element per thread step.
+template <int DT, int KIND>
+__global__ void __launch_bounds__(kThreads, 4)
+generic_map_kernel(const void* __restrict__ in, const void* __restrict__ scale, const void* __restrict__ zp,
+                   void* __restrict__ out, Geom g, Round r_in, Round r_out, int64_t n, int pdt) {
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  stage_steps(r_in, s_steps[0]);
+  stage_steps(r_out, s_steps[1]);
+  const bool has_z = zp != nullptr;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float s = 1.0f, z = 0.0f;
+    if (KIND != 2) {
+      int64_t pi = param_index(g, i);
+      s = loadp(scale, pi, pdt);
+      if (has_z) z = loadp(zp, pi, pdt);
+    }
+    store1<DT>(out, i, map_one<DT, KIND>(load1<DT>(in, i), s, z, has_z, r_in, r_out, i));
   }
 }
 
@@ -296,7 +296,61 @@ __device__ __forceinline__ float block_scale(uint32_t amax_bits, const ScaleRule
 
 __device__ __forceinline__ uint32_t abs_bits(float v) { return __float_as_uint(v) & 0x7FFFFFFFu; }
 
-// Fast path: blocks along the contiguous last axis; row length K a multiple of
+// Fastest path: blocks along the contiguous last axis and K a whole number of
+// blocks, so the tensor is a flat run of blocks: vector v belongs to block
+// v / G (G = block / V lanes, a power of two) and no row arithmetic is needed.
+// Each thread keeps kUnroll 16-byte loads in flight.
+template <int DT, bool WRITE_CODES>
+__global__ void __launch_bounds__(kThreads, 4)
+mx_flat_kernel(const void* __restrict__ in, void* __restrict__ scale_out, void* __restrict__ codes_out,
+               int64_t nvec, int G, int gshift, ScaleRule rule, Round r) {
+  using E = Elem<DT>;
+  constexpr int V = E::kVec;
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  stage_steps(r, s_steps[0]);
+  stage_steps(rule.scale_round, s_steps[1]);
+  const int64_t chunk = (int64_t)kThreads * kUnroll;
+  // nvec is a multiple of G and chunk boundaries are multiples of 32, so a
+  // block's G lanes are always either all inside or all outside the tensor.
+  for (int64_t base = (int64_t)blockIdx.x * chunk; base < nvec; base += (int64_t)gridDim.x * chunk) {
+    Vec<DT> x[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      int64_t v = base + u * kThreads + threadIdx.x;
+      x[u].raw = make_uint4(0, 0, 0, 0);
+      if (v < nvec) x[u].raw = __ldg(reinterpret_cast<const uint4*>(in) + v);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      int64_t v = base + u * kThreads + threadIdx.x;
+      uint32_t m = 0;
+#pragma unroll
+      for (int j = 0; j < V; ++j) m = max(m, abs_bits(x[u].get(j)));
+      for (int off = 1; off < G; off <<= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+      float es;
+      float scale = block_scale<DT>(m, rule, &es);
+      const bool active = v < nvec;
+      if (active && (threadIdx.x & (G - 1)) == 0) store1<DT>(scale_out, v >> gshift, scale);
+      if (WRITE_CODES && active) {
+        Vec<DT> y;
+        const int64_t flat = v * V;
+        uint32_t sb = __float_as_uint(es);
+        const bool pow2 = (sb & 0x007FFFFFu) == 0 && (sb >> 23) >= 1 && (sb >> 23) <= 253;
+        if (pow2) {
+          float inv = __uint_as_float((254u - (sb >> 23)) << 23);
+#pragma unroll
+          for (int j = 0; j < V; ++j) y.set(j, apply_round(r, E::round(__fmul_rn(x[u].get(j), inv)), flat + j));
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) y.set(j, apply_round(r, E::round(__fdiv_rn(x[u].get(j), es)), flat + j));
+        }
+        reinterpret_cast<uint4*>(codes_out)[v] = y.raw;
+      }
+    }
+  }
+}
+
+// Ragged path: blocks along the contiguous last axis; row length K a multiple of
 // the vector width; a block is covered by G = block/V consecutive lanes.
 // Each row owns `slots_per_row` = ceil(K/block) * G thread slots so groups are
 // lane-aligned; slots past the row's end only take part in the shuffles.
@@ -306,6 +360,10 @@ mx_rows_kernel(const void* __restrict__ in, void* __restrict__ scale_out, void* 
                int64_t rows, int64_t K, int block, int G, int64_t slots_per_row, int64_t total_slots,
                ScaleRule rule, Round r) {
   using E = Elem<DT>;
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  stage_steps(r, s_steps[0]);
+  stage_steps(rule.scale_round, s_steps[1]);
+
   constexpr int V = E::kVec;
   const int64_t nblk = slots_per_row / G;
   const int64_t row_vecs = K / V;
@@ -361,6 +419,10 @@ __global__ void __launch_bounds__(256)
 mx_generic_kernel(const void* __restrict__ in, void* __restrict__ scale_out, void* __restrict__ codes_out,
                   Blocks g, ScaleRule rule, Round r) {
   using E = Elem<DT>;
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  stage_steps(r, s_steps[0]);
+  stage_steps(rule.scale_round, s_steps[1]);
+
   const int64_t total = g.O * g.nA * g.M * g.nB * g.I;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
@@ -425,6 +487,10 @@ affine_generic_kernel(const void* __restrict__ in, void* __restrict__ scale_out,
                       void* __restrict__ codes_out, int64_t O, int64_t B, int64_t I, int block, int64_t nB,
                       float qmin, float qmax, Round sr, Round r) {
   using E = Elem<DT>;
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  stage_steps(r, s_steps[0]);
+  stage_steps(sr, s_steps[1]);
+
   const int64_t total = O * nB * I;
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
@@ -461,6 +527,10 @@ affine_rows_kernel(const void* __restrict__ in, void* __restrict__ scale_out, vo
                    void* __restrict__ codes_out, int64_t rows, int64_t K, int block, int G,
                    int64_t slots_per_row, int64_t total_slots, float qmin, float qmax, Round sr, Round r) {
   using E = Elem<DT>;
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  stage_steps(r, s_steps[0]);
+  stage_steps(sr, s_steps[1]);
+
   constexpr int V = E::kVec;
   const int64_t nblk = slots_per_row / G;
   const int64_t row_vecs = K / V;
@@ -629,6 +699,19 @@ static int launch_mx(const void* in, void* scale_out, void* codes_out, int dtype
                        aligned16(in) && (!write_codes || aligned16(codes_out));
   int G = rows_ok ? b->block_b / V : 0;
   const bool g_ok = rows_ok && G >= 1 && G <= 32 && (G & (G - 1)) == 0;
+  if (g_ok && (b->B % b->block_b) == 0) {
+    const int64_t nvec = n / V;
+    int gshift = 0;
+    while ((1 << gshift) < G) ++gshift;
+    int grid = grid_for(nvec, kThreads * kUnroll, 8);
+    VQ_DISPATCH_DTYPE(dtype, {
+      if (write_codes)
+        mx_flat_kernel<DT, true><<<grid, kThreads, 0, st>>>(in, scale_out, codes_out, nvec, G, gshift, sr, r);
+      else
+        mx_flat_kernel<DT, false><<<grid, kThreads, 0, st>>>(in, scale_out, codes_out, nvec, G, gshift, sr, r);
+    });
+    return check_launch("mx_flat_kernel");
+  }
   if (g_ok) {
     const int64_t rows = b->O * b->A * b->M;
     const int64_t nblk = (b->B + b->block_b - 1) / b->block_b;
@@ -668,17 +751,78 @@ extern "C" {
 const char* vq_last_error(void) { return error_buffer(); }
 int vq_version(void) { return 1; }
 
+static int launch_stream(int kind, const void* in, const void* scale, const void* zp, void* out, int dtype,
+                         int pdt, const Geom* g, const Round& ri, const Round& ro, int64_t n, cudaStream_t st) {
+  const int V = vec_width(dtype);
+  ParamIndex pi{PI_SCALAR, 1, 0, 1};
+  bool fast = aligned16(in) && aligned16(out);
+  if (kind != 2) {
+    // reduce the collapsed broadcast to scalar / flat-div / flat-mod when possible
+    bool scalar = true;
+    for (int d = 0; d < g->ndim; ++d)
+      if (g->stride[d] != 0 && (g->size[d] + g->div[d] - 1) / g->div[d] > 1) scalar = false;
+    if (scalar) {
+      pi.kind = PI_SCALAR;
+    } else if (g->ndim == 1 && g->stride[0] == 1) {
+      pi.kind = PI_DIV;
+      pi.d = (uint32_t)g->div[0];
+    } else if (g->ndim == 2 && g->div[0] == 1 && g->stride[1] == 1 && g->size[1] % g->div[1] == 0 &&
+               g->stride[0] == g->size[1] / g->div[1]) {
+      pi.kind = PI_DIV;  // dense per-block parameters of a [rows, K] tensor
+      pi.d = (uint32_t)g->div[1];
+    } else if (g->ndim == 2 && g->div[0] == 1 && g->stride[0] == 1 && g->stride[1] == 0) {
+      pi.kind = PI_DIV;  // one parameter per row
+      pi.d = (uint32_t)g->size[1];
+    } else if (g->ndim == 2 && g->stride[0] == 0 && g->div[1] == 1 && g->stride[1] == 1) {
+      pi.kind = PI_MOD;  // one parameter per column
+      pi.c = (uint32_t)g->size[1];
+    } else if (g->ndim == 1 && g->div[0] == 1 && g->stride[0] == 1) {
+      pi.kind = PI_MOD;
+      pi.c = (uint32_t)g->size[0];
+    } else {
+      pi.kind = PI_GENERIC;
+    }
+    if (pi.kind == PI_DIV) {
+      if (pi.d == 0 || pi.d % V != 0 || g->div[g->ndim - 1] > 0x7FFFFFFF) pi.kind = PI_GENERIC;
+      pi.shift = -1;
+      if ((pi.d & (pi.d - 1)) == 0) { pi.shift = 0; while ((1u << pi.shift) < pi.d) ++pi.shift; }
+    }
+    if (pi.kind == PI_MOD && (pi.c % V != 0)) pi.kind = PI_GENERIC;
+    if (pi.kind != PI_SCALAR && (n % V) != 0) pi.kind = PI_GENERIC;
+  }
+  if (!fast || pi.kind == PI_GENERIC) {
+    if (kind == 2) {
+      Geom gg{};
+      gg.ndim = 1; gg.size[0] = n; gg.div[0] = 1; gg.stride[0] = 0;
+      int grid = grid_for(n, kThreads, 8);
+      VQ_DISPATCH_DTYPE(dtype, (generic_map_kernel<DT, 2><<<grid, kThreads, 0, st>>>(in, scale, zp, out, gg, ri, ro, n, pdt)));
+      return check_launch("generic_map_kernel");
+    }
+    int grid = grid_for(n, kThreads, 8);
+    VQ_DISPATCH_DTYPE(dtype, {
+      if (kind == 0) generic_map_kernel<DT, 0><<<grid, kThreads, 0, st>>>(in, scale, zp, out, *g, ri, ro, n, pdt);
+      else generic_map_kernel<DT, 1><<<grid, kThreads, 0, st>>>(in, scale, zp, out, *g, ri, ro, n, pdt);
+    });
+    return check_launch("generic_map_kernel");
+  }
+  const int n32 = n < 0xFFFFFFFFll;
+  int grid = grid_for((n + V - 1) / V, kThreads * kUnroll, 8);
+  VQ_DISPATCH_DTYPE(dtype, {
+    if (kind == 0) stream_map_kernel<DT, 0><<<grid, kThreads, 0, st>>>(in, scale, zp, out, ri, ro, n, pi, pdt, n32);
+    else if (kind == 1) stream_map_kernel<DT, 1><<<grid, kThreads, 0, st>>>(in, scale, zp, out, ri, ro, n, pi, pdt, n32);
+    else stream_map_kernel<DT, 2><<<grid, kThreads, 0, st>>>(in, scale, zp, out, ri, ro, n, pi, pdt, n32);
+  });
+  return check_launch("stream_map_kernel");
+}
+
 int vq_vmap(const void* in, void* out, int dtype, const VqRound* round, int64_t n, void* stream) {
   VQ_REQUIRE(n >= 0, "vq_vmap: negative size");
   if (n == 0) return VQ_OK;
   VQ_REQUIRE(in && out && round, "vq_vmap: null argument");
   if (int e = validate_round(round, "vq_vmap")) return e;
-  Round r = make_round(round);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int vec_ok = aligned16(in) && aligned16(out);
-  int grid = grid_for((n + vec_width(dtype) - 1) / vec_width(dtype), 256, 8);
-  VQ_DISPATCH_DTYPE(dtype, (vmap_kernel<DT><<<grid, 256, 0, st>>>(in, out, r, n, vec_ok)));
-  return check_launch("vmap_kernel");
+  Round none = make_round(nullptr);
+  return launch_stream(2, in, nullptr, nullptr, out, dtype, dtype, nullptr, none, make_round(round), n,
+                       static_cast<cudaStream_t>(stream));
 }
 
 static int scale_map(int kind, const void* in, const void* scale, const void* zp, void* out, int dtype,
@@ -692,21 +836,7 @@ static int scale_map(int kind, const void* in, const void* scale, const void* zp
   if (int e = validate_round(r_in, "input rounding")) return e;
   if (int e = validate_round(r_out, "output rounding")) return e;
   Round ri = make_round(r_in), ro = make_round(r_out);
-  int scalar = 1;
-  for (int d = 0; d < g.ndim; ++d)
-    if (g.stride[d] != 0 && g.size[d] > 1 && (g.size[d] + g.div[d] - 1) / g.div[d] > 1) scalar = 0;
-  const int V = vec_width(dtype);
-  int vec_ok = aligned16(in) && aligned16(out);
-  if (!scalar) vec_ok = vec_ok && (g.size[g.ndim - 1] % V) == 0;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int grid = grid_for(vec_ok ? (n + V - 1) / V : n, 256, 8);
-  VQ_DISPATCH_DTYPE(dtype, {
-    if (kind == 0)
-      scale_map_kernel<DT, 0><<<grid, 256, 0, st>>>(in, scale, zp, out, g, ri, ro, n, scalar, vec_ok, param_dtype);
-    else
-      scale_map_kernel<DT, 1><<<grid, 256, 0, st>>>(in, scale, zp, out, g, ri, ro, n, scalar, vec_ok, param_dtype);
-  });
-  return check_launch("scale_map_kernel");
+  return launch_stream(kind, in, scale, zp, out, dtype, param_dtype, &g, ri, ro, n, static_cast<cudaStream_t>(stream));
 }
 
 int vq_quantize(const void* in, const void* scale, const void* zero_point, void* out, int dtype,
@@ -720,14 +850,20 @@ int vq_dequantize(const void* in, const void* scale, const void* zero_point, voi
   return scale_map(1, in, scale, zero_point, out, dtype, param_dtype, geom, round_in, round_out, stream);
 }
 
+static inline bool empty_blocks(const VqBlocks* b) {
+  return b && (b->O == 0 || b->A == 0 || b->M == 0 || b->B == 0 || b->I == 0);
+}
+
 int vq_mx_qparam(const void* in, void* scale_out, int dtype, const VqBlocks* blocks, const VqScaleRule* rule,
                  void* stream) {
+  if (empty_blocks(blocks)) return VQ_OK;
   VQ_REQUIRE(in && scale_out, "vq_mx_qparam: null argument");
   return launch_mx(in, scale_out, nullptr, dtype, blocks, rule, nullptr, false, static_cast<cudaStream_t>(stream));
 }
 
 int vq_quantize_mx(const void* in, void* scale_out, void* codes_out, int dtype, const VqBlocks* blocks,
                    const VqScaleRule* rule, const VqRound* round, void* stream) {
+  if (empty_blocks(blocks)) return VQ_OK;
   VQ_REQUIRE(in && scale_out && codes_out, "vq_quantize_mx: null argument");
   return launch_mx(in, scale_out, codes_out, dtype, blocks, rule, round, true, static_cast<cudaStream_t>(stream));
 }
@@ -735,6 +871,7 @@ int vq_quantize_mx(const void* in, void* scale_out, void* codes_out, int dtype, 
 int vq_quantize_affine(const void* in, void* scale_out, void* zero_out, void* codes_out, int dtype,
                        const VqBlocks* b, float quant_min, float quant_max, const VqRound* scale_round,
                        const VqRound* round, void* stream) {
+  if (empty_blocks(b)) return VQ_OK;
   VQ_REQUIRE(in && scale_out && zero_out && codes_out && b, "vq_quantize_affine: null argument");
   VQ_REQUIRE(b->block_a == 1 && b->A == 1 && b->M == 1, "vq_quantize_affine: blocks lie along one axis (B)");
   VQ_REQUIRE(b->block_b >= 1, "vq_quantize_affine: block size must be >= 1");

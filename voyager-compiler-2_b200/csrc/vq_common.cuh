@@ -65,13 +65,6 @@ __device__ __forceinline__ float bf16_from_bits(uint32_t b) {
 // ---------------------------------------------------------------------------
 // rounding onto a format's grid
 // ---------------------------------------------------------------------------
-struct StepTable {
-  int32_t n;
-  uint16_t key[VQ_MAX_STEPS];
-  uint16_t value[VQ_MAX_STEPS];
-  uint16_t nan_value;
-};
-
 // Device-side copy of VqRound (passed by value as a kernel parameter).
 struct Round {
   int32_t mode;
@@ -84,7 +77,9 @@ struct Round {
   const float* levels;
   int32_t n_edges, n_levels;
   const int64_t* seed;
-  StepTable steps;
+  const uint16_t* steps;  // n_steps keys then n_steps values (global or shared)
+  int32_t n_steps;
+  uint32_t nan_value;
 };
 
 inline Round make_round(const VqRound* r) {
@@ -106,12 +101,9 @@ inline Round make_round(const VqRound* r) {
   d.n_edges = r->n_edges;
   d.n_levels = r->n_levels;
   d.seed = r->seed;
-  d.steps.n = r->n_steps;
-  for (int i = 0; i < VQ_MAX_STEPS; ++i) {
-    d.steps.key[i] = r->step_key[i];
-    d.steps.value[i] = r->step_value[i];
-  }
-  d.steps.nan_value = r->nan_value;
+  d.steps = static_cast<const uint16_t*>(r->steps);
+  d.n_steps = r->n_steps;
+  d.nan_value = r->nan_value;
   return d;
 }
 
@@ -175,8 +167,11 @@ __device__ __forceinline__ uint32_t philox_byte(uint64_t index, uint64_t seed) {
 // v: the scaled value, already rounded to the storage dtype.  `flat` is the
 // element's index in the input's logical row-major order (stochastic only).
 // Returns the grid value (or codebook index) as a float, exact in bf16.
+// MODE >= 0 fixes the rounding mode at compile time; -1 switches at run time.
+template <int MODE = -1>
 __device__ __forceinline__ float apply_round(const Round& r, float v, int64_t flat) {
-  switch (r.mode) {
+  const int mode = MODE >= 0 ? MODE : r.mode;
+  switch (mode) {
     case VQ_ROUND_NONE:
       return v;
     case VQ_ROUND_TABLE:
@@ -187,14 +182,14 @@ __device__ __forceinline__ float apply_round(const Round& r, float v, int64_t fl
       return round_minifloat(bf16_from_bits(bf16_bits(v)), r.emin, r.mbits, r.max_norm, r.is_signed);
     case VQ_ROUND_STEPS: {
       uint32_t bits = bf16_bits(v);
-      if ((bits & 0x7FFFu) > 0x7F80u) return bf16_from_bits(r.steps.nan_value);
+      if ((bits & 0x7FFFu) > 0x7F80u) return bf16_from_bits(r.nan_value);
       uint32_t key = ordered_key(bits);
-      int lo = 0, hi = r.steps.n - 1;  // first k with key < step_key[k]
+      int lo = 0, hi = r.n_steps - 1;  // first k with key < steps[k]
       while (lo < hi) {
         int mid = (lo + hi) >> 1;
-        if (key < r.steps.key[mid]) hi = mid; else lo = mid + 1;
+        if (key < r.steps[mid]) hi = mid; else lo = mid + 1;
       }
-      return bf16_from_bits(r.steps.value[lo]);
+      return bf16_from_bits(r.steps[r.n_steps + lo]);
     }
     case VQ_ROUND_SEARCH: {
       float x = bf16_from_bits(bf16_bits(v));
@@ -226,6 +221,16 @@ __device__ __forceinline__ float apply_round(const Round& r, float v, int64_t fl
     }
   }
   return v;
+}
+
+// Step tables are searched from shared memory: copy them once per CTA.  Every
+// thread of the CTA must call this (it synchronises when the mode is STEPS).
+__device__ __forceinline__ void stage_steps(Round& r, uint16_t* smem /* 2*VQ_MAX_STEPS */) {
+  if (r.mode == VQ_ROUND_STEPS) {
+    for (int i = threadIdx.x; i < 2 * r.n_steps; i += blockDim.x) smem[i] = r.steps[i];
+    __syncthreads();
+    r.steps = smem;
+  }
 }
 
 }  // namespace vq

@@ -46,10 +46,24 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+def _is_dense(x):
+    """True when ``x`` covers its storage range exactly once (any axis order)."""
+    if x.is_contiguous():
+        return True
+    expected = 1
+    for size, stride in sorted(zip(x.shape, x.stride()), key=lambda p: p[1]):
+        if size == 1:
+            continue
+        if stride != expected:
+            return False
+        expected *= size
+    return True
+
+
 def _dense_like(x):
     """``x`` in a dense layout an elementwise kernel can walk in memory order,
     and an empty output with the same strides."""
-    if not x.is_non_overlapping_and_dense():
+    if not _is_dense(x):
         x = x.contiguous()
     return x, torch.empty_like(x)
 
@@ -525,7 +539,7 @@ def _(input, qmap, axes, block_size, quant_min, quant_max, scale_qmap=None):
 # ---------------------------------------------------------------------------
 def tensor_amax(x: torch.Tensor) -> torch.Tensor:
     """``max |x|`` as a 0-d float32 tensor (one kernel, no host sync)."""
-    x = x if x.is_non_overlapping_and_dense() else x.contiguous()
+    x = x if _is_dense(x) else x.contiguous()
     out = torch.zeros((), dtype=torch.float32, device=x.device)
     N.check(N.lib().vq_amax(x.data_ptr(), _dtype_id(x.dtype), x.numel(), out.data_ptr(), _stream()), "vq_amax")
     return out
@@ -539,3 +553,216 @@ def calculate_global_scale(input: torch.Tensor, quant_max: float, scale_max: flo
     divisor = torch.full((), float(quant_max * scale_max), dtype=torch.float32, device=input.device)
     ratio = _quantize_with(amax, divisor, None, None, R.none_round()).reshape(())
     return ratio.clamp_min(torch.finfo(torch.float32).tiny)
+
+
+# ---------------------------------------------------------------------------
+# GEMMs
+# ---------------------------------------------------------------------------
+_ACT_LAYOUTS, _WGT_LAYOUTS, _OUT_LAYOUTS = ("xc", "cx"), ("kc", "ck"), ("xk", "kx")
+_IN_KIND = {torch.bfloat16: N.IN_BF16, torch.float16: N.IN_F16}
+
+
+def _parse_layout(layout: str):
+    operands, out = layout.split("->")
+    act, wgt = operands.split(",")
+    assert act in _ACT_LAYOUTS, layout
+    assert wgt in _WGT_LAYOUTS, layout
+    assert out in _OUT_LAYOUTS, layout
+    return act, wgt, out
+
+
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None):
+    """``out[..., m, n] = alpha * sum_k a[..., m, k] * b[..., n, k] + bias[n]`` on the
+    tensor cores (fp32 accumulation, one rounding to ``out_dtype``).
+
+    ``a`` is ``[*batch, M, K]`` and ``b`` ``[*batch, N, K]`` or ``[N, K]``; both are
+    used K-contiguous.  ``in_kind`` overrides the operand element kind for 8-bit
+    operands stored as ``uint8``/``float8`` bytes.
+    """
+    if in_kind is None:
+        if a.dtype != b.dtype or a.dtype not in _IN_KIND:
+            raise NotImplementedError(
+                f"the tensor-core GEMM takes bfloat16 or float16 operands of one dtype, not {a.dtype} x {b.dtype}")
+        in_kind = _IN_KIND[a.dtype]
+    elem = a.element_size()
+    m, k = a.shape[-2], a.shape[-1]
+    n = b.shape[-2]
+    if b.shape[-1] != k:
+        raise ValueError(f"contraction extents differ: {tuple(a.shape)} x {tuple(b.shape)}")
+    pad = (-k) % (16 // elem)
+    if pad:  # rows must be multiples of 16 bytes for the TMA descriptors
+        a = torch.nn.functional.pad(a, (0, pad))
+        b = torch.nn.functional.pad(b, (0, pad))
+        k += pad
+    batch_shape = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    if b.dim() == 2:
+        # shared weight: fold the batch into the rows
+        a2 = a.reshape(-1, k).contiguous()
+        b2 = b.contiguous()
+        batch, rows = 1, a2.shape[0]
+        stride_a = stride_b = 0
+    else:
+        a2 = a.expand(*batch_shape, m, k).reshape(-1, m, k).contiguous()
+        b2 = b.expand(*batch_shape, n, k).reshape(-1, n, k).contiguous()
+        batch, rows = a2.shape[0], m
+        stride_a, stride_b = m * k, n * k
+    out_dtype = out_dtype or (a.dtype if a.dtype in _DTYPE_ID else torch.bfloat16)
+    out = torch.empty((batch, rows, n), dtype=out_dtype, device=a.device)
+    if bias is not None:
+        bias = bias.contiguous()
+    if out.numel():
+        if k == 0:
+            out.zero_()
+        else:
+            N.check(N.lib().vq_gemm_tn(
+                a2.data_ptr(), b2.data_ptr(), out.data_ptr(), in_kind, _dtype_id(out_dtype), rows, n, k, k, k, n,
+                batch, stride_a, stride_b, rows * n, _ptr(alpha), 0 if alpha is None else _dtype_id(alpha.dtype),
+                _ptr(bias), 0 if bias is None else _dtype_id(bias.dtype), _stream()), "vq_gemm_tn")
+    return out.reshape(*batch_shape, m, n) if b.dim() > 2 else out.reshape(*a.shape[:-1], n)
+
+
+def _as_scalar_param(t, device):
+    if t is None:
+        return None
+    if t.numel() != 1:
+        raise NotImplementedError("alpha must hold one element")
+    if t.dtype not in _DTYPE_ID:
+        t = t.float()
+    return t.to(device).reshape(())
+
+
+def _gemm_in_layout(native, activation, weight, layout, out_dtype, bias=None, alpha=None):
+    act, wgt, out_l = _parse_layout(layout)
+    n_act, n_wgt, n_out = _parse_layout(native)
+    if act == "cx":
+        activation = activation.mT
+    # the kernel wants the weight [out, contraction]
+    w = weight if wgt == "kc" else weight.mT
+    y = gemm_tn(activation, w, out_dtype=out_dtype, alpha=alpha, bias=bias)
+    return y.mT.contiguous() if out_l != n_out else y
+
+
+quantized_ops_lib.define(
+    f'linear(Tensor input, Tensor weight, Tensor? bias=None, *, str layout="{LINEAR_LAYOUT}", '
+    "ScalarType? out_dtype=None) -> Tensor"
+)
+quantized_ops_lib.define(
+    f'matmul(Tensor self, Tensor other, *, str layout="{MATMUL_LAYOUT}", ScalarType? out_dtype=None) -> Tensor'
+)
+
+
+def linear(input, weight, bias=None, *, layout=LINEAR_LAYOUT, out_dtype=None):
+    """``aten.linear`` on operands stored as ``layout`` says (reference ``ops/layout.py:266-278``)."""
+    return _gemm_in_layout(LINEAR_LAYOUT, input, weight, layout, out_dtype, bias)
+
+
+def matmul(input, other, *, layout=MATMUL_LAYOUT, out_dtype=None):
+    """``aten.matmul`` on operands stored as ``layout`` says (reference ``ops/layout.py:281-290``)."""
+    return _gemm_in_layout(MATMUL_LAYOUT, input, other, layout, out_dtype)
+
+
+quantized_ops_lib.impl("linear", linear, "CUDA")
+quantized_ops_lib.impl("matmul", matmul, "CUDA")
+
+
+def _gemm_out_shape(activation, weight, layout, weight_is_matrix):
+    act, wgt, out_l = _parse_layout(layout)
+    a_shape = list(activation.shape)
+    if act == "cx":
+        a_shape[-2], a_shape[-1] = a_shape[-1], a_shape[-2]
+    n = weight.shape[-2] if wgt == "kc" else weight.shape[-1]
+    if weight.dim() > 2:
+        batch = torch.broadcast_shapes(tuple(a_shape[:-2]), tuple(weight.shape[:-2]))
+        shape = [*batch, a_shape[-2], n]
+    else:
+        shape = [*a_shape[:-1], n]
+    if out_l == "kx":
+        shape[-2], shape[-1] = shape[-1], shape[-2]
+    return shape
+
+
+@torch.library.register_fake("quantized_ops::linear")
+def _(input, weight, bias=None, *, layout=LINEAR_LAYOUT, out_dtype=None):
+    return input.new_empty(_gemm_out_shape(input, weight, layout, True), dtype=out_dtype or input.dtype)
+
+
+@torch.library.register_fake("quantized_ops::matmul")
+def _(input, other, *, layout=MATMUL_LAYOUT, out_dtype=None):
+    return input.new_empty(_gemm_out_shape(input, other, layout, False), dtype=out_dtype or input.dtype)
+
+
+quantized_ops_lib.define(
+    "linear_mx(Tensor input, Tensor weight, Tensor? bias=None, *, "
+    "Tensor? input_scale=None, Tensor? weight_scale=None, "
+    "int? block_size=None, Tensor? input_code=None, Tensor? weight_code=None, "
+    "Tensor? alpha=None, Tensor? A_data=None, Tensor? A_indices=None, "
+    f'Tensor? A_indptr=None, str layout="{LINEAR_LAYOUT}", '
+    "ScalarType? out_dtype=None) -> Tensor"
+)
+quantized_ops_lib.define(
+    "matmul_mx(Tensor self, Tensor other, *, Tensor? input_scale=None, "
+    "Tensor? weight_scale=None, int? block_size=None, Tensor? input_code=None, "
+    "Tensor? weight_code=None, Tensor? alpha=None, Tensor? A_data=None, "
+    "Tensor? A_indices=None, Tensor? A_indptr=None, "
+    f'str layout="{MATMUL_LAYOUT}", ScalarType? out_dtype=None) -> Tensor'
+)
+
+
+def _read_operand(x, scale, code, block_size):
+    if scale is None and code is None:
+        return x
+    return _decode_and_scale(x, scale, code, block_size)
+
+
+def _mx_gemm(native, a, b, bias, input_scale, weight_scale, block_size, input_code, weight_code, alpha, outliers,
+             layout, out_dtype):
+    if any(t is not None for t in outliers):
+        raise NotImplementedError("the outlier CSR side stream (A_data / A_indices / A_indptr) is not built")
+    a = _read_operand(a, input_scale, input_code, block_size)
+    b = _read_operand(b, weight_scale, weight_code, block_size)
+    dtype = a.dtype if out_dtype is None else out_dtype
+    if dtype not in _DTYPE_ID:
+        raise NotImplementedError(f"output dtype {dtype}")
+    return _gemm_in_layout(native, a, b, layout, dtype, bias, _as_scalar_param(alpha, a.device))
+
+
+def linear_mx(input, weight, bias=None, *, input_scale=None, weight_scale=None, block_size=None, input_code=None,
+              weight_code=None, alpha=None, A_data=None, A_indices=None, A_indptr=None, layout=LINEAR_LAYOUT,
+              out_dtype=None):
+    """Microscaling linear: both operands are read back through their codebook
+    and block scales (each product rounded to the operand dtype), multiplied
+    with fp32 accumulation, scaled by ``alpha``, biased and rounded once
+    (reference ``quantized.py:662-723``)."""
+    return _mx_gemm(LINEAR_LAYOUT, input, weight, bias, input_scale, weight_scale, block_size, input_code,
+                    weight_code, alpha, (A_data, A_indices, A_indptr), layout, out_dtype)
+
+
+def matmul_mx(self, other, *, input_scale=None, weight_scale=None, block_size=None, input_code=None,
+              weight_code=None, alpha=None, A_data=None, A_indices=None, A_indptr=None, layout=MATMUL_LAYOUT,
+              out_dtype=None):
+    """Microscaling matmul (reference ``quantized.py:752-805``)."""
+    return _mx_gemm(MATMUL_LAYOUT, self, other, None, input_scale, weight_scale, block_size, input_code,
+                    weight_code, alpha, (A_data, A_indices, A_indptr), layout, out_dtype)
+
+
+quantized_ops_lib.impl("linear_mx", linear_mx, "CUDA")
+quantized_ops_lib.impl("matmul_mx", matmul_mx, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::linear_mx")
+def _(input, weight, bias=None, **kwargs):
+    layout = kwargs.get("layout", LINEAR_LAYOUT)
+    return input.new_empty(_gemm_out_shape(input, weight, layout, True), dtype=kwargs.get("out_dtype") or input.dtype)
+
+
+@torch.library.register_fake("quantized_ops::matmul_mx")
+def _(self, other, **kwargs):
+    layout = kwargs.get("layout", MATMUL_LAYOUT)
+    return self.new_empty(_gemm_out_shape(self, other, layout, False), dtype=kwargs.get("out_dtype") or self.dtype)
+
+
+def gemm_status(reset=True):
+    """Raise if a tensor-core GEMM launched earlier gave up on a barrier wait
+    (synchronises the device)."""
+    torch.cuda.synchronize()
+    N.check(N.lib().vq_gemm_status(int(reset)), "vq_gemm_status")

@@ -130,13 +130,13 @@ def _classify_table(table_bf16: torch.Tensor, allow_arithmetic=True) -> RoundSpe
     steps = _steps_of(bits)
     if steps is not None:
         values, uppers, nan_value = steps
+        packed = np.concatenate([uppers, values]).astype(np.uint16).view(np.int16)
+        steps = torch.from_numpy(packed.copy()).to(table_bf16.device)
         c.mode = N.ROUND_STEPS
         c.n_steps = len(values)
-        for i, (v, u) in enumerate(zip(values, uppers)):
-            c.step_value[i] = int(v)
-            c.step_key[i] = int(u)
+        c.steps = steps.data_ptr()
         c.nan_value = nan_value
-        return RoundSpec(c, (table_bf16,))
+        return RoundSpec(c, (table_bf16, steps))
     return RoundSpec(c, (table_bf16,))
 
 
@@ -153,7 +153,7 @@ def table_round(qmap: torch.Tensor, allow_arithmetic=True) -> RoundSpec:
     table = qmap if qmap.dtype == torch.bfloat16 else qmap.to(torch.bfloat16)
     table = table.contiguous()
     spec = _classify_table(table, allow_arithmetic)
-    spec.keep = (qmap, table)
+    spec.keep = (qmap, table) + tuple(spec.keep)
     if len(_table_cache) > 256:
         _table_cache.clear()
     _table_cache[key] = spec
