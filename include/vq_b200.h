@@ -170,6 +170,17 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
                int64_t strideB, int64_t strideC, const void* alpha, int alpha_dtype, const void* bias,
                int bias_dtype, void* stream);
 
+/* Real FP8 codes for the tensor-core GEMM, the cast the reference's GPU backend
+ * makes before torch._scaled_mm (backend/gpu/fp8.py:253-309): out[i] is the
+ * e4m3 / e5m2 byte of round_bf16(in[i] / scale), i.e. the byte encoding of the
+ * value quantized_ops::quantize (ops/quantized.py:458-515) yields with that
+ * format's table.  `in` is bfloat16, `format` VQ_IN_E4M3 or VQ_IN_E5M2, `scale`
+ * holds one element (elems_per_scale = 0) or one per elems_per_scale consecutive
+ * elements (a multiple of 16; per-row scales of a weight).  n must be a multiple
+ * of 16 and both buffers 16-byte aligned. */
+int vq_quantize_fp8(const void* in, const void* scale, int scale_dtype, void* out, int format, int64_t n,
+                    int64_t elems_per_scale, void* stream);
+
 /* Synchronising health check for the GEMM kernels: returns VQ_ETIMEOUT if any
  * launch since the last reset gave up on a bounded barrier wait (its output is
  * then invalid).  No counterpart in the reference. */

@@ -1,0 +1,63 @@
+"""Oracle: a per-tensor FP8 quantized Llama decoder layer as its converted graph computes it.
+
+TEST INFRASTRUCTURE ONLY (see the package docstring).
+
+Restates, with the oracle's CPU operators, the node pattern that the reference's
+``convert_pt2e`` emits for per-tensor symmetric quantization
+(``src/voyager_compiler/quantization/quantize_pt2e.py:526-626``):
+``quantize(x, s_a, qmap)`` -> ``aten.linear / aten.matmul`` on the bfloat16-valued
+codes -> ``dequantize(y, s_a * s_w, output_qmap=identity)``, applied to the seven
+linears and the two attention matmuls of a Llama layer with HF eager attention
+(``scripts/models/clm.py:286-331`` prepares that graph).  RMSNorm, RoPE, softmax
+and SwiGLU are plain bfloat16 torch ops, as in the graph.
+"""
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import quantizers as OQ
+from . import tables as OT
+
+
+def fp8_decoder_layer(x, params, scales, shape, rope, mask):
+    """x: [T, hidden] bfloat16 on the CPU.  ``scales``: bfloat16 0-d tensors keyed
+    'h','q','k','v','p','ctx','h2','act' and 'w_<linear>'.  ``rope`` = (cos, sin)."""
+    e4m3 = OT.quantization_map("fp8_e4m3")
+    ident = OT.quantization_map(None)
+    T = x.shape[0]
+    cos, sin = rope
+
+    def quant(t, name):
+        return OQ.quantize(t, scales[name], None, None, None, e4m3)
+
+    weights = {n: quant(params[n], "w_" + n) for n in ("q", "k", "v", "o", "gate", "up", "down")}
+
+    def qlinear(codes, act_name, w_name):
+        y = F.linear(codes, weights[w_name])
+        return OQ.dequantize(y, scales[act_name] * scales["w_" + w_name], None, None, None, None, ident)
+
+    def rope_apply(t):
+        half = t.shape[-1] // 2
+        rot = torch.cat([-t[..., half:], t[..., :half]], -1)
+        return t * cos[:, None, :] + rot * sin[:, None, :]
+
+    h = quant(F.rms_norm(x, (shape.hidden,), params["ln1"], shape.eps), "h")
+    q = qlinear(h, "h", "q").view(T, shape.heads, shape.head_dim)
+    k = qlinear(h, "h", "k").view(T, shape.kv_heads, shape.head_dim)
+    v = qlinear(h, "h", "v").view(T, shape.kv_heads, shape.head_dim)
+    q, k = rope_apply(q), rope_apply(k)
+    g = shape.heads // shape.kv_heads
+    qh = quant(q.transpose(0, 1), "q")                                # [heads, T, d]
+    kt = quant(k.repeat_interleave(g, 1).permute(1, 2, 0), "k")       # [heads, d, T]
+    vh = quant(v.repeat_interleave(g, 1).transpose(0, 1), "v")        # [heads, T, d]
+    scores = OQ.dequantize(torch.matmul(qh, kt), scales["q"] * scales["k"], None, None, None, None, ident)
+    scores = scores * (1.0 / math.sqrt(shape.head_dim)) + mask
+    p = quant(torch.softmax(scores.float(), -1).to(x.dtype), "p")
+    ctx = OQ.dequantize(torch.matmul(p, vh), scales["p"] * scales["v"], None, None, None, None, ident)
+    ctx = ctx.transpose(0, 1).reshape(T, shape.heads * shape.head_dim)
+    x1 = x + qlinear(quant(ctx, "ctx"), "ctx", "o")
+    h2 = quant(F.rms_norm(x1, (shape.hidden,), params["ln2"], shape.eps), "h2")
+    act = F.silu(qlinear(h2, "h2", "gate")) * qlinear(h2, "h2", "up")
+    return x1 + qlinear(quant(act, "act"), "act", "down")

@@ -81,7 +81,7 @@ def test_table_fingerprinting():
     spec = R.table_round(voyager_b200.get_quantization_map("fp8_e4m3"))
     assert spec.mode == N.ROUND_MINIFLOAT and spec.c.mbits == 3 and spec.c.emin == -6
     assert R.table_round(voyager_b200.get_quantization_map("fp8_e5m3")).mode == N.ROUND_MINIFLOAT
-    assert R.table_round(voyager_b200.get_quantization_map("lut4_to_int6")).mode == N.ROUND_STEPS
+    assert R.table_round(voyager_b200.get_quantization_map("lut4_to_int6")).mode == N.ROUND_TABLE
     assert R.table_round(voyager_b200.get_quantization_map("posit8_1")).mode == N.ROUND_TABLE
     assert R.table_round(voyager_b200.get_quantization_map("fp8_e8m0")).mode == N.ROUND_TABLE
     # a perturbed int8 table is no longer recognised and is gathered
@@ -90,8 +90,14 @@ def test_table_fingerprinting():
     assert R.table_round(t).mode == N.ROUND_TABLE
     # the index form of a lookup format is a step function too
     idx, levels = voyager_b200.formats.index_table(voyager_b200.get_quantization_map("lut4_to_int6"))
-    s = R.table_round(idx)
-    assert s.mode == N.ROUND_STEPS and s.c.n_steps <= 32
+    R.PREFER_STEPS = True
+    try:
+        R._table_cache.clear()
+        s = R.table_round(idx)
+        assert s.mode == N.ROUND_STEPS and s.c.n_steps <= 32
+    finally:
+        R.PREFER_STEPS = False
+        R._table_cache.clear()
 
 
 def test_steps_reproduce_table_on_host():

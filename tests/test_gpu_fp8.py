@@ -1,0 +1,84 @@
+"""Real-FP8 path: the cast's bytes encode exactly the codes the table quantizer
+yields, the FP8 GEMM matches an fp64 product of the decoded bytes, and the FP8
+decoder layer tracks the converted-graph semantics (oracle) within the
+per-tensor-FP8 tolerance."""
+
+import pytest
+import torch
+
+from oracle import layers as OL
+from oracle import quantizers as OQ
+from oracle import tables as OT
+
+pytestmark = pytest.mark.gpu
+
+
+def _vb():
+    import voyager_b200
+
+    return voyager_b200
+
+
+def rel_err(got, want):
+    return float((got.double() - want.double()).abs().max() / want.double().abs().max().clamp_min(1e-30))
+
+
+@pytest.mark.parametrize("dtype,torch_dtype", [("fp8_e4m3", torch.float8_e4m3fn), ("fp8_e5m2", torch.float8_e5m2)])
+def test_fp8_cast_bytes_are_the_table_codes(dtype, torch_dtype):
+    vb = _vb()
+    table = OT.quantization_map(dtype)
+    x = torch.cat([OT.all_bf16(), OT.all_bf16().flip(0)])  # every bf16 value, twice
+    x = torch.where(torch.isnan(x), torch.zeros_like(x), x)
+    for s in (1.0, 0.0123, 3.3e-5, 7.7e3):
+        for sdt in (torch.bfloat16, torch.float32):
+            scale = torch.tensor(s, dtype=sdt)
+            want = OQ.quantize(x, scale, qmap=table)
+            got = vb.fp8.quantize_fp8(x.cuda(), scale.cuda(), dtype).cpu()
+            decoded = got.view(torch_dtype).float()
+            assert torch.equal(decoded, want.float()), (dtype, s, sdt)
+            # -0 never appears from a -0 input; tiny negatives keep their sign, as in the table
+            assert torch.equal(torch.signbit(decoded), torch.signbit(want.float()))
+
+
+def test_fp8_cast_per_row_scales():
+    vb = _vb()
+    g = torch.Generator().manual_seed(1)
+    w = (torch.randn(48, 64, generator=g) * 0.02).bfloat16()
+    s = (w.abs().amax(1, keepdim=True) / 448.0)
+    want = OQ.quantize(w, s, qmap=OT.quantization_map("fp8_e4m3"))
+    got = vb.fp8.quantize_fp8(w.cuda(), s.cuda()).cpu().view(torch.float8_e4m3fn).float()
+    assert torch.equal(got, want.float())
+
+
+@pytest.mark.parametrize("m,n,k,batch", [(64, 48, 128, 1), (300, 520, 272, 1), (256, 128, 2048, 3), (130, 2048, 128, 2)])
+def test_fp8_gemm(m, n, k, batch):
+    vb = _vb()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(batch, m, k, generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(batch, n, k, generator=g).to(torch.float8_e4m3fn)
+    alpha = torch.tensor(0.37, dtype=torch.bfloat16)
+    want = torch.matmul(a.double(), b.double().transpose(-1, -2)) * float(alpha)
+    got = vb.fp8.fp8_gemm(a.view(torch.uint8).cuda(), b.view(torch.uint8).cuda(), alpha.cuda(),
+                          out_dtype=torch.float32).cpu()
+    vb.ops.gemm_status()
+    assert got.shape == (batch, m, n)
+    assert rel_err(got, want) <= 2e-5, rel_err(got, want)
+
+
+def test_fp8_decoder_layer_matches_converted_graph():
+    vb = _vb()
+    W = vb.workloads
+    shape = W.TINY
+    T = 64
+    params = W.make_layer_params(0, shape)
+    x = W.make_hidden_states(1, T, shape)
+    scales = W.calibrate_fp8_scales(x, params, shape)
+    want = OL.fp8_decoder_layer(x, params, scales, shape, W.rope_tables(T, shape, "cpu"), W.causal_mask(T, "cpu"))
+    layer = W.Fp8DecoderLayer({k: v.cuda() for k, v in params.items()}, {k: v.cuda() for k, v in scales.items()}, shape)
+    got = layer(x.cuda()).cpu()
+    vb.ops.gemm_status()
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    # The graph rounds each GEMM to bfloat16 before its scale; the FP8 GEMM rounds once after it.
+    assert rel_err(got, want) <= 2e-2, rel_err(got, want)
+    ref = W.bf16_layer_forward(x, params, shape)
+    assert rel_err(got, ref) <= 0.15

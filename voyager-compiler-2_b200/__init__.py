@@ -7,6 +7,8 @@ it through the ``voyager_b200`` module at the repository root.
 
 from . import _native, formats, rounding  # noqa: F401
 from . import ops  # noqa: F401  (registers torch.ops.quantized_ops.*)
+from . import fp8  # noqa: F401
+from . import workloads  # noqa: F401
 from ._native import build  # noqa: F401
 from .formats import (  # noqa: F401
     QScheme,

@@ -6,7 +6,7 @@
 // All of these are HBM-bound: every kernel reads its input once with 16-byte
 // accesses where the layout allows and writes each output once.
 
-#include "vq_common.cuh"
+#include "quantize_shared.cuh"
 
 #include <cmath>
 
@@ -70,46 +70,6 @@ static inline int grid_for(int64_t work_items, int threads, int per_sm = 8) {
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return (int)blocks;
-}
-
-// ---------------------------------------------------------------------------
-// 16-byte vector access
-// ---------------------------------------------------------------------------
-template <int DT> struct Vec {
-  using E = Elem<DT>;
-  uint4 raw;
-  __device__ __forceinline__ float get(int i) const {
-    if constexpr (DT == VQ_F32) {
-      return reinterpret_cast<const float*>(&raw)[i];
-    } else {
-      return E::to_float(reinterpret_cast<const typename E::T*>(&raw)[i]);
-    }
-  }
-  __device__ __forceinline__ void set(int i, float v) {
-    if constexpr (DT == VQ_F32) {
-      reinterpret_cast<float*>(&raw)[i] = v;
-    } else {
-      reinterpret_cast<typename E::T*>(&raw)[i] = E::from_float(v);
-    }
-  }
-};
-
-template <int DT>
-__device__ __forceinline__ float load1(const void* p, int64_t i) {
-  return Elem<DT>::to_float(static_cast<const typename Elem<DT>::T*>(p)[i]);
-}
-template <int DT>
-__device__ __forceinline__ void store1(void* p, int64_t i, float v) {
-  static_cast<typename Elem<DT>::T*>(p)[i] = Elem<DT>::from_float(v);
-}
-
-// A parameter (scale, zero point, global scale) whose dtype is only known at
-// run time: a 0-d float32 scale next to bfloat16 data is used at full
-// precision, as torch does for scalar operands.
-__device__ __forceinline__ float loadp(const void* p, int64_t i, int pdt) {
-  if (pdt == VQ_F32) return static_cast<const float*>(p)[i];
-  if (pdt == VQ_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
-  return __half2float(static_cast<const __half*>(p)[i]);
 }
 
 // ---------------------------------------------------------------------------
@@ -250,51 +210,6 @@ generic_map_kernel(const void* __restrict__ in, const void* __restrict__ scale, 
     store1<DT>(out, i, map_one<DT, KIND>(load1<DT>(in, i), s, z, has_z, r_in, r_out, i));
   }
 }
-
-// ---------------------------------------------------------------------------
-// microscaling: scale rule
-// ---------------------------------------------------------------------------
-struct ScaleRule {
-  float quant_max;
-  int power_of_two;
-  int qmax_exp;  // floor(log2(quant_max))
-  const void* global_scale;
-  int global_scale_dtype;
-  Round scale_round;
-};
-
-// amax_bits: |amax| as float bits (NaN patterns compare above inf, so an
-// integer max over |x| bits propagates NaN like torch.amax).
-// Returns the block scale (value of dtype DT, as float); *elem_scale gets the
-// divisor of the elements (scale * global_scale when present).
-template <int DT>
-__device__ __forceinline__ float block_scale(uint32_t amax_bits, const ScaleRule& rule, float* elem_scale) {
-  using E = Elem<DT>;
-  float amax = __uint_as_float(amax_bits);
-  float scale;
-  float gs = 0.f;
-  const bool has_gs = rule.global_scale != nullptr;
-  if (has_gs) gs = loadp(rule.global_scale, 0, rule.global_scale_dtype);
-  if (rule.power_of_two) {
-    if (amax != amax) {
-      scale = amax;
-    } else if (amax_bits == 0x7F800000u) {
-      scale = amax;  // infinite block -> infinite scale
-    } else {
-      int e = (amax == 0.0f) ? -126 : ilogbf(amax);
-      scale = E::round(ldexpf(1.0f, e - rule.qmax_exp));
-    }
-  } else {
-    scale = E::round(__fdiv_rn(amax, rule.quant_max));
-    if (has_gs) scale = E::round(__fdiv_rn(scale, gs));
-    if (rule.scale_round.mode != VQ_ROUND_NONE) scale = E::round(apply_round(rule.scale_round, scale, 0));
-  }
-  scale = (scale > 0.0f) ? scale : 1.0f;
-  *elem_scale = has_gs ? E::round(__fmul_rn(scale, gs)) : scale;
-  return scale;
-}
-
-__device__ __forceinline__ uint32_t abs_bits(float v) { return __float_as_uint(v) & 0x7FFFFFFFu; }
 
 // Fastest path: blocks along the contiguous last axis and K a whole number of
 // blocks, so the tensor is a flat run of blocks: vector v belongs to block
@@ -680,6 +595,11 @@ static int to_rule(const VqScaleRule* rule, ScaleRule* out) {
   out->global_scale = rule->global_scale;
   out->global_scale_dtype = rule->global_scale_dtype;
   out->scale_round = make_round(&rule->scale_round);
+  // An all-zero block under the power-of-two rule: amax is read as 2^-126, so the
+  // scale is 2^(-126 - qexp) rounded to bfloat16 (whose smallest value is 2^-133;
+  // 2^-134 ties to zero), and a scale of zero is replaced by one.
+  const int ze = -126 - out->qmax_exp;
+  out->zero_scale_bf16 = ze >= -133 ? ldexpf(1.0f, ze) : 1.0f;
   return VQ_OK;
 }
 
@@ -703,6 +623,11 @@ static int launch_mx(const void* in, void* scale_out, void* codes_out, int dtype
     const int64_t nvec = n / V;
     int gshift = 0;
     while ((1 << gshift) < G) ++gshift;
+    if (dtype == VQ_BF16) {
+      const int fm = fast_mode_of(round);
+      if (r.mode != VQ_ROUND_STOCHASTIC && r.mode != VQ_ROUND_SEARCH)
+        return fast_mx_flat_bf16(in, scale_out, codes_out, nvec, G, gshift, sr, r, fm, write_codes, st);
+    }
     int grid = grid_for(nvec, kThreads * kUnroll, 8);
     VQ_DISPATCH_DTYPE(dtype, {
       if (write_codes)
@@ -752,7 +677,8 @@ const char* vq_last_error(void) { return error_buffer(); }
 int vq_version(void) { return 1; }
 
 static int launch_stream(int kind, const void* in, const void* scale, const void* zp, void* out, int dtype,
-                         int pdt, const Geom* g, const Round& ri, const Round& ro, int64_t n, cudaStream_t st) {
+                         int pdt, const Geom* g, const Round& ri, const Round& ro, int64_t n, cudaStream_t st,
+                         int fast_mode = 7 /* FAST_GENERIC */) {
   const int V = vec_width(dtype);
   ParamIndex pi{PI_SCALAR, 1, 0, 1};
   bool fast = aligned16(in) && aligned16(out);
@@ -805,6 +731,11 @@ static int launch_stream(int kind, const void* in, const void* scale, const void
     });
     return check_launch("generic_map_kernel");
   }
+  if (kind == 0 && dtype == VQ_BF16 && zp == nullptr && (n % V) == 0 && ro.mode != VQ_ROUND_STOCHASTIC &&
+      ro.mode != VQ_ROUND_SEARCH && (pi.kind == PI_SCALAR || pi.kind == PI_DIV)) {
+    const uint32_t vps = pi.kind == PI_SCALAR ? 0u : pi.d / (uint32_t)V;
+    return fast_quantize_bf16(in, scale, pdt, out, n / V, vps, ro, fast_mode, st);
+  }
   const int n32 = n < 0xFFFFFFFFll;
   int grid = grid_for((n + V - 1) / V, kThreads * kUnroll, 8);
   VQ_DISPATCH_DTYPE(dtype, {
@@ -836,7 +767,8 @@ static int scale_map(int kind, const void* in, const void* scale, const void* zp
   if (int e = validate_round(r_in, "input rounding")) return e;
   if (int e = validate_round(r_out, "output rounding")) return e;
   Round ri = make_round(r_in), ro = make_round(r_out);
-  return launch_stream(kind, in, scale, zp, out, dtype, param_dtype, &g, ri, ro, n, static_cast<cudaStream_t>(stream));
+  return launch_stream(kind, in, scale, zp, out, dtype, param_dtype, &g, ri, ro, n, static_cast<cudaStream_t>(stream),
+                       fast_mode_of(r_out));
 }
 
 int vq_quantize(const void* in, const void* scale, const void* zero_point, void* out, int dtype,
@@ -913,6 +845,15 @@ int vq_dequantize_mx(const void* in, const void* scale, const void* code, int32_
   VQ_REQUIRE(in && out, "vq_dequantize_mx: null argument");
   VQ_REQUIRE(!code || n_code > 0, "vq_dequantize_mx: empty codebook");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == VQ_BF16 && !code && scale && !global_scale && (n % 8) == 0 && aligned16(in) && aligned16(out)) {
+    // dense per-block scales along the last axis: parameter index = flat / block
+    int64_t d = 0;
+    if (g.ndim == 1 && g.stride[0] == 1) d = g.div[0];
+    else if (g.ndim == 2 && g.div[0] == 1 && g.stride[1] == 1 && g.size[1] % g.div[1] == 0 &&
+             g.stride[0] == g.size[1] / g.div[1]) d = g.div[1];
+    if (d >= 8 && d % 8 == 0 && d < (1ll << 31))
+      return fast_scale_bf16(in, scale, out, n / 8, (uint32_t)(d / 8), st);
+  }
   int grid = grid_for(n, 256, 8);
   VQ_DISPATCH_DTYPE(dtype, (dequantize_mx_kernel<DT><<<grid, 256, 0, st>>>(in, scale, code, n_code, global_scale,
                                                                          global_scale_dtype, out, g, n)));

@@ -1,0 +1,64 @@
+"""Real-FP8 execution of per-tensor / per-channel quantized GEMMs.
+
+A converted per-tensor graph runs ``quantize -> aten.linear / aten.matmul ->
+dequantize`` on bfloat16 tensors that merely hold FP8 values.  The reference's
+GPU backend replaces each such site by a cast to FP8 bytes and one scaled FP8
+GEMM (``backend/gpu/fp8.py``: ``quantize_fp8:253``, ``fp8_linear:372``,
+``fp8_bmm:403``).  These functions are that replacement on hand-written
+sm_100a kernels: the cast writes the exact byte encoding of the value the
+``quantize`` op would have produced, and the GEMM is a tcgen05 ``kind::f8f6f4``
+MMA with fp32 accumulation whose epilogue applies ``scale_a * scale_b`` and the
+bias before a single rounding.
+"""
+
+from typing import Optional
+
+import torch
+
+from . import _native as N
+from .ops import _DTYPE_ID, _dtype_id, _ptr, _stream, gemm_tn
+
+_FORMATS = {"fp8_e4m3": N.IN_E4M3, "fp8_e5m2": N.IN_E5M2}
+
+
+def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype: str = "fp8_e4m3") -> torch.Tensor:
+    """Cast ``x / scale`` to FP8 bytes (``uint8`` tensor of ``x``'s shape).
+
+    ``scale`` holds one element, or one per row of the last axis
+    (shape ``[..., 1]``, per-channel weights).
+    """
+    if x.dtype != torch.bfloat16:
+        raise NotImplementedError("quantize_fp8 takes bfloat16 input")
+    x = x.contiguous()
+    n = x.numel()
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    if scale.numel() == 1:
+        per = 0
+    else:
+        rows = n // x.shape[-1]
+        if scale.numel() != rows:
+            raise ValueError(f"scale of shape {tuple(scale.shape)} is neither one value nor one per row of {tuple(x.shape)}")
+        per = x.shape[-1]
+        scale = scale.contiguous()
+    if scale.dtype not in _DTYPE_ID:
+        scale = scale.float()
+    if n % 16 or (per % 16):
+        raise NotImplementedError("quantize_fp8 needs element counts that are multiples of 16")
+    N.check(N.lib().vq_quantize_fp8(x.data_ptr(), scale.data_ptr(), _dtype_id(scale.dtype), out.data_ptr(),
+                                    _FORMATS[dtype], n, per, _stream()), "vq_quantize_fp8")
+    return out
+
+
+def fp8_gemm(a: torch.Tensor, b: torch.Tensor, alpha: Optional[torch.Tensor] = None,
+             bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, dtype: str = "fp8_e4m3") -> torch.Tensor:
+    """``alpha * (a @ b^T) + bias`` for FP8 byte operands ``a [*batch, M, K]`` and
+    ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation, one rounding."""
+    return gemm_tn(a, b, out_dtype=out_dtype, alpha=alpha, bias=bias, in_kind=_FORMATS[dtype])
+
+
+def fp8_linear(x8: torch.Tensor, w8: torch.Tensor, scale_a: torch.Tensor, scale_w: torch.Tensor,
+               bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """One FP8 linear: ``(x8 @ w8^T) * (scale_a * scale_w) + bias`` with tensor-wise scales
+    (reference ``backend/gpu/fp8.py:372-400``)."""
+    alpha = (scale_a * scale_w).reshape(())
+    return fp8_gemm(x8, w8, alpha, bias, out_dtype)

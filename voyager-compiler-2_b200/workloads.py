@@ -1,0 +1,188 @@
+"""Synthetic Llama-shaped decoder layers that exercise the quantized hot path.
+
+These are the callers the benchmark and the tests drive: random-init weights
+of a Llama-3.1-8B-shaped layer (hidden 4096, 32 query / 8 KV heads of 128,
+SwiGLU 14336, RMSNorm, RoPE theta 5e5), quantized the way the reference's
+converted graphs are (``scripts/models/clm.py:353-389`` builds them;
+``quantization/quantize_pt2e.py:526-626`` emits the per-tensor node pattern).
+
+``Fp8DecoderLayer`` is the FP8 per-tensor layer: every linear and both attention
+matmuls run as FP8 casts + tcgen05 FP8 GEMMs (the replacement the reference's
+``backend/gpu`` makes for ``quantize -> aten.linear -> dequantize`` sites);
+RMSNorm, RoPE, softmax and SwiGLU stay bfloat16 torch ops, as in the graph.
+"""
+
+import dataclasses
+import math
+
+import torch
+import torch.nn.functional as F
+
+from . import fp8 as FP8
+from . import formats
+
+E4M3_MAX = 448.0
+
+
+@dataclasses.dataclass(frozen=True)
+class LlamaShape:
+    hidden: int = 4096
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    intermediate: int = 14336
+    rope_theta: float = 5e5
+    eps: float = 1e-5
+    vocab: int = 128256
+
+    @property
+    def groups(self):
+        return self.heads // self.kv_heads
+
+
+LLAMA_8B = LlamaShape()
+TINY = LlamaShape(hidden=256, heads=4, kv_heads=2, head_dim=64, intermediate=512, vocab=1024)
+
+LINEARS = ("q", "k", "v", "o", "gate", "up", "down")
+
+
+def linear_shapes(shape: LlamaShape):
+    h, d = shape.hidden, shape.head_dim
+    return {"q": (shape.heads * d, h), "k": (shape.kv_heads * d, h), "v": (shape.kv_heads * d, h),
+            "o": (h, shape.heads * d), "gate": (shape.intermediate, h), "up": (shape.intermediate, h),
+            "down": (h, shape.intermediate)}
+
+
+def make_layer_params(seed: int, shape: LlamaShape, device="cpu"):
+    """Random-init weights ~N(0, 0.02) and unit RMSNorm gains, generated on the CPU."""
+    g = torch.Generator().manual_seed(seed)
+    params = {name: (torch.randn(*dims, generator=g) * 0.02).bfloat16().to(device)
+              for name, dims in linear_shapes(shape).items()}
+    params["ln1"] = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+    params["ln2"] = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+    return params
+
+
+def make_hidden_states(seed: int, tokens: int, shape: LlamaShape, device="cpu"):
+    """Layer input for ``tokens`` random token ids: embedding rows of distinct ids
+    drawn from an N(0,1) table are i.i.d. normal rows, which is what is generated
+    (no vocabulary-sized table is materialised)."""
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(tokens, shape.hidden, generator=g).bfloat16().to(device)
+
+
+def rope_tables(tokens: int, shape: LlamaShape, device):
+    inv = 1.0 / (shape.rope_theta ** (torch.arange(0, shape.head_dim, 2, dtype=torch.float32) / shape.head_dim))
+    angle = torch.arange(tokens, dtype=torch.float32)[:, None] * inv[None, :]
+    emb = torch.cat([angle, angle], -1)
+    return emb.cos().bfloat16().to(device), emb.sin().bfloat16().to(device)
+
+
+def apply_rope(x, cos, sin):
+    """x: [T, heads, head_dim]; HF Llama's rotate-half form."""
+    half = x.shape[-1] // 2
+    rot = torch.cat([-x[..., half:], x[..., :half]], -1)
+    return x * cos[:, None, :] + rot * sin[:, None, :]
+
+
+def causal_mask(tokens: int, device, dtype=torch.bfloat16):
+    m = torch.full((tokens, tokens), float("-inf"), dtype=dtype, device=device)
+    return torch.triu(m, 1)
+
+
+def _amax_scale(t, qmax=E4M3_MAX):
+    return (t.abs().amax() / qmax).to(torch.bfloat16)
+
+
+def bf16_layer_forward(x, params, shape: LlamaShape, record=None):
+    """The unquantized bfloat16 layer (calibration pass).  ``record(name, tensor)``
+    sees every tensor that the quantized layer quantizes."""
+    T = x.shape[0]
+    rec = record or (lambda name, t: None)
+    cos, sin = rope_tables(T, shape, x.device)
+    h = F.rms_norm(x, (shape.hidden,), params["ln1"], shape.eps)
+    rec("h", h)
+    q = F.linear(h, params["q"]).view(T, shape.heads, shape.head_dim)
+    k = F.linear(h, params["k"]).view(T, shape.kv_heads, shape.head_dim)
+    v = F.linear(h, params["v"]).view(T, shape.kv_heads, shape.head_dim)
+    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    rec("q", q), rec("k", k), rec("v", v)
+    kk = k.repeat_interleave(shape.groups, 1)
+    vv = v.repeat_interleave(shape.groups, 1)
+    scores = torch.matmul(q.transpose(0, 1), kk.permute(1, 2, 0)) * (1.0 / math.sqrt(shape.head_dim))
+    scores = scores + causal_mask(T, x.device)
+    p = torch.softmax(scores.float(), -1).to(x.dtype)
+    rec("p", p)
+    ctx = torch.matmul(p, vv.transpose(0, 1)).transpose(0, 1).reshape(T, shape.heads * shape.head_dim)
+    rec("ctx", ctx)
+    x1 = x + F.linear(ctx, params["o"])
+    h2 = F.rms_norm(x1, (shape.hidden,), params["ln2"], shape.eps)
+    rec("h2", h2)
+    act = F.silu(F.linear(h2, params["gate"])) * F.linear(h2, params["up"])
+    rec("act", act)
+    return x1 + F.linear(act, params["down"])
+
+
+def calibrate_fp8_scales(x, params, shape: LlamaShape):
+    """Per-tensor scales ``amax / 448`` in bfloat16 for every quantized tensor
+    (activations from one bfloat16 forward of ``x``; weights from their own amax)."""
+    scales = {}
+    bf16_layer_forward(x, params, shape, lambda name, t: scales.__setitem__(name, _amax_scale(t)))
+    for name in LINEARS:
+        scales["w_" + name] = _amax_scale(params[name])
+    return scales
+
+
+class Fp8DecoderLayer:
+    """FP8 per-tensor decoder layer on the CUDA kernels (prefill, batch 1)."""
+
+    def __init__(self, params, scales, shape: LlamaShape):
+        self.shape = shape
+        self.scales = scales
+        self.ln1, self.ln2 = params["ln1"], params["ln2"]
+        # weights are cast once, as convert_pt2e bakes them
+        self.w8 = {name: FP8.quantize_fp8(params[name], scales["w_" + name]) for name in LINEARS}
+        s = scales
+        self.alpha = {name: (s[src] * s["w_" + name]).reshape(()) for name, src in
+                      (("q", "h"), ("k", "h"), ("v", "h"), ("o", "ctx"), ("gate", "h2"), ("up", "h2"), ("down", "act"))}
+        self.alpha_qk = (s["q"] * s["k"]).reshape(())
+        self.alpha_pv = (s["p"] * s["v"]).reshape(())
+        self._rope = None
+        self._mask = None
+
+    #: kernels of this package launched per forward (casts + GEMMs)
+    LAUNCHES = 8 + 9
+
+    def _tables(self, T, device):
+        if self._rope is None or self._rope[0].shape[0] != T:
+            self._rope = rope_tables(T, self.shape, device)
+            self._mask = causal_mask(T, device)
+        return self._rope, self._mask
+
+    def forward(self, x):
+        sh, s = self.shape, self.scales
+        T = x.shape[0]
+        (cos, sin), mask = self._tables(T, x.device)
+        h8 = FP8.quantize_fp8(F.rms_norm(x, (sh.hidden,), self.ln1, sh.eps), s["h"])
+        q = FP8.fp8_gemm(h8, self.w8["q"], self.alpha["q"]).view(T, sh.heads, sh.head_dim)
+        k = FP8.fp8_gemm(h8, self.w8["k"], self.alpha["k"]).view(T, sh.kv_heads, sh.head_dim)
+        v = FP8.fp8_gemm(h8, self.w8["v"], self.alpha["v"]).view(T, sh.kv_heads, sh.head_dim)
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+        # query heads of one KV group are stacked along the rows: [kv, groups*T, d]
+        q8 = FP8.quantize_fp8(q.view(T, sh.kv_heads, sh.groups, sh.head_dim).permute(1, 2, 0, 3)
+                              .reshape(sh.kv_heads, sh.groups * T, sh.head_dim), s["q"])
+        k8 = FP8.quantize_fp8(k.transpose(0, 1), s["k"])                    # [kv, T, d]
+        vt8 = FP8.quantize_fp8(v.permute(1, 2, 0), s["v"])                  # [kv, d, T]
+        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk)                        # [kv, groups*T, T]
+        scores = scores.view(sh.kv_heads, sh.groups, T, T) * (1.0 / math.sqrt(sh.head_dim)) + mask
+        p = torch.softmax(scores.float(), -1).to(x.dtype)
+        p8 = FP8.quantize_fp8(p.view(sh.kv_heads, sh.groups * T, T), s["p"])
+        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv)                          # [kv, groups*T, d]
+        ctx = ctx.view(sh.kv_heads, sh.groups, T, sh.head_dim).permute(2, 0, 1, 3).reshape(T, sh.heads * sh.head_dim)
+        x1 = x + FP8.fp8_gemm(FP8.quantize_fp8(ctx, s["ctx"]), self.w8["o"], self.alpha["o"])
+        h28 = FP8.quantize_fp8(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps), s["h2"])
+        act = F.silu(FP8.fp8_gemm(h28, self.w8["gate"], self.alpha["gate"])) * \
+            FP8.fp8_gemm(h28, self.w8["up"], self.alpha["up"])
+        return x1 + FP8.fp8_gemm(FP8.quantize_fp8(act, s["act"]), self.w8["down"], self.alpha["down"])
+
+    __call__ = forward
