@@ -1,28 +1,35 @@
 """Benchmark of the quantized hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1]
 
 One "step" is one pass of the hot path over one batch of synthetic input.
+
+Workload ``c2`` (default; BASELINE.json configs[1]): one FP8 E4M3 per-tensor
+quantized Llama-3.1-8B-shaped decoder layer, prefill of 1 x 2048 tokens,
+random-init weights ~N(0,0.02); all seven linears and both attention matmuls
+run as FP8 casts + FP8 tensor-core GEMMs, bf16 elsewhere.
+
 Workload ``c1`` (BASELINE.json configs[0]): X [2048,4096] bf16 ~N(0,1) with
 0.1 % of entries x20, W [4096,4096] ~N(0,0.02); both are quantized to int8
 microscaling (block 16 along K, power-of-two scales) and multiplied to
 Y [2048,4096] bf16 -- ``quantize_mx`` x2 + ``linear_mx``.
 
-With N > 1 (launched under torchrun, one rank per GPU) every rank processes its
-own batches: the path shards by rows with no exchange, so scaling is weak and
+Each step is replayed from a CUDA graph captured once per input set.  With
+N > 1 (launched under torchrun, one rank per GPU) every rank processes its own
+batches: the path shards by token rows with no exchange, so scaling is weak and
 ``value`` is the sum over ranks.  The timed region is K steps bracketed by a
 barrier and a device synchronize; time is taken with CUDA events and the
-maximum over ranks.  Successive steps use different input sets whose combined
-size exceeds the 126 MB L2, so no step finds its inputs cached.
+maximum over ranks.  Successive steps use different input sets and the
+tensors touched per step exceed the 126 MB L2 several times over, so no step
+finds its inputs cached.
 
 ``--impl reference`` times the CPU oracle (a port of the reference's CPU
-operators) on the host cores for the same workload.
+operators) on the host cores for the same workload, on a bounded sample.
 """
 
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -32,9 +39,10 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# ncu-measured DRAM traffic (bytes per launch) of the dominant kernel, from the
-# capture summarised under profiles/; None until one has been taken.
-NCU_TRAFFIC_BYTES = {"c1": None}
+# ncu-measured DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, bytes per
+# launch) of each workload's dominant kernel, from the captures summarised under
+# profiles/; None until one has been taken.
+NCU_TRAFFIC_BYTES = {"c1": 52.3e6, "c2": None}
 
 
 def measured_peaks():
@@ -48,28 +56,41 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
-
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons through NVML while a region runs."""
 
     def __init__(self, index):
         self.index = index
-        self.samples = []
+        self.sm, self.max_sm, self.reasons = [], None, set()
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
-                    capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([f.strip() for f in out.split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.index
+            if visible:
+                try:
+                    index = int(visible.split(",")[self.index])
+                except ValueError:
+                    pass
+            h = nv.nvmlDeviceGetHandleByIndex(index)
+            self.max_sm = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+            while not self._stop.is_set():
+                self.sm.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self._stop.wait(0.02)
+        except Exception as exc:  # no NVML: report what we have
+            self.error = repr(exc)
 
     def __enter__(self):
         self._thread.start()
@@ -80,91 +101,236 @@ class ClockSampler:
         self._thread.join(timeout=10)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            try:
-                sm.append(float(s[0]))
-                mx.append(float(s[1]))
-            except (ValueError, IndexError):
-                continue
-            for name, flag in zip(names, s[2:6]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        if not self.sm:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_sm, "reasons": [], "samples": 0,
+                    "note": getattr(self, "error", "no samples")}
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": self.max_sm, "reasons": sorted(self.reasons),
+                "samples": len(sm)}
+
+
+def time_region(fn, steps, barrier):
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for i in range(steps):
+        fn(i)
+    stop.record()
+    barrier()
+    return start.elapsed_time(stop) * 1e-3
+
+
+def capture(fn):
+    """Capture ``fn()`` into a CUDA graph (after a warm-up call on a side stream);
+    returns (graph, outputs)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = fn()
+    return graph, out
 
 
 # ---------------------------------------------------------------------------
 # workload c1: MXINT8 quantized linear
 # ---------------------------------------------------------------------------
-C1 = dict(tokens=2048, k=4096, n=4096, block=16, qmax=127.0)
+class C1:
+    name = "c1"
+    description = ("c1: MXINT8 (int8, bs=16, power-of-two scales) quantize_mx x2 + linear_mx, "
+                   "X[2048,4096] W[4096,4096] per GPU")
+    tokens = 2048
+    K, N, BLOCK, QMAX = 4096, 4096, 16, 127.0
+    launches_per_step = 5  # quantize_mx x2, operand read-back x2, tensor-core GEMM
+    n_sets = 6
+    dtype = "bf16"
+    cpu_sample = "full c1 steps"
+    cpu_tokens = 2048
+
+    @staticmethod
+    def inputs(seed, device="cpu"):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(C1.tokens, C1.K, generator=g)
+        x = torch.where(torch.rand(C1.tokens, C1.K, generator=g) < 0.001, x * 20, x).bfloat16()
+        w = (torch.randn(C1.N, C1.K, generator=g) * 0.02).bfloat16()
+        return x.to(device), w.to(device)
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        self.Q = torch.ops.quantized_ops
+        self.table = voyager_b200.get_quantization_map("int8", dev)
+        self.sets = [self.inputs(1000 * rank + i, dev) for i in range(self.n_sets)]
+        self.host_x = [s[0].cpu().pin_memory() for s in self.sets]
+        self.host_y = torch.empty(self.tokens, self.N, dtype=torch.bfloat16).pin_memory()
+        self.h2d_bytes = self.tokens * self.K * 2
+        self.d2h_bytes = self.tokens * self.N * 2
+        for x, w in self.sets[:2]:
+            self._run(x, w)
+        self.graphs = [capture(lambda x=x, w=w: self._run(x, w)) for x, w in self.sets]
+
+    def _run(self, x, w):
+        Q = self.Q
+        sx, cx = Q.quantize_mx(x, self.table, [-1], self.BLOCK, self.QMAX, True)
+        sw, cw = Q.quantize_mx(w, self.table, [-1], self.BLOCK, self.QMAX, True)
+        return Q.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=self.BLOCK)
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        j = i % self.n_sets
+        self.sets[j][0].copy_(self.host_x[j], non_blocking=True)
+        self.graphs[j][0].replay()
+        self.host_y.copy_(self.graphs[j][1], non_blocking=True)
+
+    def roofline(self, peaks, reps):
+        ops, Q = self.vb.ops, self.Q
+        pairs = []
+        for x, w in self.sets:
+            sx, cx = Q.quantize_mx(x, self.table, [-1], self.BLOCK, self.QMAX, True)
+            sw, cw = Q.quantize_mx(w, self.table, [-1], self.BLOCK, self.QMAX, True)
+            pairs.append((ops._decode_and_scale(cx, sx, None, self.BLOCK), ops._decode_and_scale(cw, sw, None, self.BLOCK)))
+        for a, b in pairs[:3]:
+            ops.gemm_tn(a, b)
+        secs = time_region(lambda i: ops.gemm_tn(*pairs[i % len(pairs)]), reps, torch.cuda.synchronize) / reps
+        flops = 2.0 * self.tokens * self.N * self.K
+        achieved = flops / secs / 1e12
+        return secs, {"kernel": "gemm_tn_kernel (tcgen05 kind::f16 bf16, 2048x4096x4096)", "bound": "tensor",
+                      "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                      "frac": achieved / peaks["bf16_tflops"],
+                      "peak_source": f"{peaks['source']} bf16 cuBLAS burst", "traffic": NCU_TRAFFIC_BYTES["c1"]}
+
+    @staticmethod
+    def cpu_setup():
+        from oracle import tables as OT
+
+        x, w = C1.inputs(0)
+        return x, w, OT.quantization_map("int8")
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import gemm as OG
+        from oracle import quantizers as OQ
+
+        x, w, table = state
+        sx, cx = OQ.quantize_mx(x, table, [-1], C1.BLOCK, C1.QMAX, True)
+        sw, cw = OQ.quantize_mx(w, table, [-1], C1.BLOCK, C1.QMAX, True)
+        return OG.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=C1.BLOCK)
 
 
-def c1_inputs(seed, device="cpu"):
-    g = torch.Generator().manual_seed(seed)
-    x = torch.randn(C1["tokens"], C1["k"], generator=g)
-    x = torch.where(torch.rand(C1["tokens"], C1["k"], generator=g) < 0.001, x * 20, x).bfloat16()
-    w = (torch.randn(C1["n"], C1["k"], generator=g) * 0.02).bfloat16()
-    return x.to(device), w.to(device)
+# ---------------------------------------------------------------------------
+# workload c2: FP8 per-tensor Llama-3.1-8B-shaped decoder layer, prefill 2048
+# ---------------------------------------------------------------------------
+class C2:
+    name = "c2"
+    description = ("c2: FP8 E4M3 per-tensor quantized Llama-3.1-8B-shaped decoder layer (hidden 4096, 32q/8kv heads "
+                   "x128, SwiGLU 14336), prefill 1x2048 tokens per GPU, 7 linears + QK^T + PV as FP8 tensor-core GEMMs")
+    tokens = 2048
+    n_sets = 4
+    dtype = "fp8_e4m3 (fp32 accumulate), bf16 elsewhere"
+    cpu_tokens = 256
+    cpu_sample = "decoder-layer forwards of a 256-token prefill (1/8 of the GPU step's tokens)"
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        W = voyager_b200.workloads
+        self.shape = W.LLAMA_8B
+        params = W.make_layer_params(7 + rank, self.shape, dev)
+        self.x = [W.make_hidden_states(100 * rank + i, self.tokens, self.shape, dev) for i in range(self.n_sets)]
+        scales = W.calibrate_fp8_scales(self.x[0], params, self.shape)
+        self.layer = W.Fp8DecoderLayer(params, scales, self.shape)
+        del params
+        self.launches_per_step = self.layer.LAUNCHES
+        self.host_x = [x.cpu().pin_memory() for x in self.x]
+        self.host_y = torch.empty(self.tokens, self.shape.hidden, dtype=torch.bfloat16).pin_memory()
+        self.h2d_bytes = self.tokens * self.shape.hidden * 2
+        self.d2h_bytes = self.tokens * self.shape.hidden * 2
+        self.layer(self.x[0])
+        self.graphs = [capture(lambda x=x: self.layer(x)) for x in self.x]
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        j = i % self.n_sets
+        self.x[j].copy_(self.host_x[j], non_blocking=True)
+        self.graphs[j][0].replay()
+        self.host_y.copy_(self.graphs[j][1], non_blocking=True)
+
+    def roofline(self, peaks, reps):
+        # the dominant kernel is the FP8 GEMM; its largest launch is gate/up: [2048,4096] x [14336,4096]^T
+        FP8 = self.vb.fp8
+        sh, s = self.shape, self.layer.scales
+        acts = [FP8.quantize_fp8(torch.nn.functional.rms_norm(x, (sh.hidden,)), s["h2"]) for x in self.x]
+        w = [self.layer.w8["gate"], self.layer.w8["up"]]
+        for a in acts[:3]:
+            FP8.fp8_gemm(a, w[0], self.layer.alpha["gate"])
+        secs = time_region(lambda i: FP8.fp8_gemm(acts[i % len(acts)], w[i % 2], self.layer.alpha["gate"]), reps,
+                           torch.cuda.synchronize) / reps
+        flops = 2.0 * self.tokens * sh.intermediate * sh.hidden
+        achieved = flops / secs / 1e12
+        peak = 2.0 * peaks["bf16_tflops"]
+        return secs, {"kernel": "gemm_tn_kernel (tcgen05 kind::f8f6f4 e4m3, 2048x14336x4096 gate/up projection)",
+                      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                      "peak_source": f"2 x {peaks['source']} bf16 cuBLAS burst (no FP8 peak was measured)",
+                      "traffic": NCU_TRAFFIC_BYTES["c2"]}
+
+    @staticmethod
+    def cpu_setup():
+        import voyager_b200  # host-side workload definitions only; no kernel runs on this path
+
+        W = voyager_b200.workloads
+        shape = W.LLAMA_8B
+        params = W.make_layer_params(7, shape)
+        x = W.make_hidden_states(100, C2.cpu_tokens, shape)
+        scales = W.calibrate_fp8_scales(x, params, shape)
+        return x, params, scales, shape, W.rope_tables(C2.cpu_tokens, shape, "cpu"), W.causal_mask(C2.cpu_tokens, "cpu")
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import layers as OL
+
+        return OL.fp8_decoder_layer(*state)
 
 
-def c1_step_gpu(Q, x, w, table):
-    sx, cx = Q.quantize_mx(x, table, [-1], C1["block"], C1["qmax"], True)
-    sw, cw = Q.quantize_mx(w, table, [-1], C1["block"], C1["qmax"], True)
-    return Q.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=C1["block"])
+WORKLOADS = {"c1": C1, "c2": C2}
 
 
-C1_LAUNCHES_PER_STEP = 5  # quantize_mx x2, operand read-back x2, tensor-core GEMM
-
-
-def c1_step_cpu(x, w, table):
-    from oracle import gemm as OG
-    from oracle import quantizers as OQ
-
-    sx, cx = OQ.quantize_mx(x, table, [-1], C1["block"], C1["qmax"], True)
-    sw, cw = OQ.quantize_mx(w, table, [-1], C1["block"], C1["qmax"], True)
-    return OG.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=C1["block"])
-
-
-def time_cpu_baseline(reps):
-    """The CPU port of the reference operators on the host cores: ``reps`` full
-    c1 steps after one warm-up."""
-    from oracle import tables as OT
-
+def time_cpu_baseline(workload, reps):
+    """The CPU port of the reference operators on the host cores."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    x, w = c1_inputs(0)
-    table = OT.quantization_map("int8")
-    c1_step_cpu(x, w, table)
+    state = workload.cpu_setup()
+    workload.cpu_step(state)
     t0 = time.perf_counter()
     for _ in range(reps):
-        c1_step_cpu(x, w, table)
+        workload.cpu_step(state)
     dt = (time.perf_counter() - t0) / reps
-    return dt, cores
+    return workload.cpu_tokens / dt, dt, cores
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    reps = max(1, args.steps)
-    for _ in range(max(0, args.warmup - 1)):
-        pass
-    dt, cores = time_cpu_baseline(reps)
-    value = C1["tokens"] / dt
-    line = {
-        "impl": "reference", "metric": "tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": reps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "c1: MXINT8 (int8, bs=16, pot) quantize_mx x2 + linear_mx, X[2048,4096] W[4096,4096]"},
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
-                         "sample": f"{reps} full c1 steps after 1 warm-up"},
+    wl = WORKLOADS[args.workload]
+    reps = max(1, min(args.steps, 5))
+    value, dt, cores = time_cpu_baseline(wl, reps)
+    sample = f"{reps} {wl.cpu_sample} after 1 warm-up"
+    print(json.dumps({
+        "impl": "reference", "metric": "tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": reps,
+        "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": wl.dtype, "data": "synthetic", "config": {"workload": wl.description, "cpu_sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }
-    print(json.dumps(line))
+    }))
 
 
 def run_ours(args, rank, world, local_rank):
@@ -177,103 +343,52 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    import voyager_b200
-
-    Q = torch.ops.quantized_ops
-    table = voyager_b200.get_quantization_map("int8", dev)
-    n_sets = 6  # ~120 MB of tensors touched per step -> 6 sets exceed L2 several times over
-    sets = [c1_inputs(1000 * rank + i, dev) for i in range(n_sets)]
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        c1_step_gpu(Q, *sets[i % n_sets], table)
-    voyager_b200.ops.gemm_status()
+    wl = WORKLOADS[args.workload](dev, rank)
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
+        wl.step(i)
+    wl.vb.ops.gemm_status()
 
-    # ---- device-resident timing (the `value`) ----
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
-        barrier()
-        start.record()
-        for i in range(args.steps):
-            c1_step_gpu(Q, *sets[i % n_sets], table)
-        stop.record()
-        barrier()
-    elapsed = start.elapsed_time(stop) * 1e-3
-    voyager_b200.ops.gemm_status()
+        elapsed = time_region(wl.step, args.steps, barrier)
+    wl.vb.ops.gemm_status()
 
-    # ---- end to end through the operator API with host buffers ----
-    host_x = [s[0].cpu().pin_memory() for s in sets]
-    weights = [s[1] for s in sets]
-    host_y = torch.empty(C1["tokens"], C1["n"], dtype=torch.bfloat16).pin_memory()
     for i in range(3):
-        y = c1_step_gpu(Q, host_x[i].to(dev, non_blocking=True), weights[i], table)
-        host_y.copy_(y, non_blocking=True)
-    barrier()
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for i in range(args.steps):
-        xd = host_x[i % n_sets].to(dev, non_blocking=True)
-        y = c1_step_gpu(Q, xd, weights[i % n_sets], table)
-        host_y.copy_(y, non_blocking=True)
-    e_stop.record()
-    barrier()
-    e2e_elapsed = e_start.elapsed_time(e_stop) * 1e-3
+        wl.e2e_step(i)
+    e2e_elapsed = time_region(wl.e2e_step, args.steps, barrier)
 
-    # ---- the dominant kernel alone (roofline) ----
-    ops = voyager_b200.ops
+    peaks = measured_peaks()
+    kernel_s, roof = wl.roofline(peaks, max(12, min(args.steps, 50)))
 
-    def dequantized_pair(x, w):
-        sx, cx = Q.quantize_mx(x, table, [-1], C1["block"], C1["qmax"], True)
-        sw, cw = Q.quantize_mx(w, table, [-1], C1["block"], C1["qmax"], True)
-        return (ops._decode_and_scale(cx, sx, None, C1["block"]), ops._decode_and_scale(cw, sw, None, C1["block"]))
-
-    deq = [dequantized_pair(*s) for s in sets]
-    for a, b in deq[:3]:
-        ops.gemm_tn(a, b)
-    torch.cuda.synchronize()
-    g_start, g_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = max(args.steps, 12)
-    g_start.record()
-    for i in range(reps):
-        ops.gemm_tn(*deq[i % n_sets])
-    g_stop.record()
-    torch.cuda.synchronize()
-    gemm_s = g_start.elapsed_time(g_stop) * 1e-3 / reps
-    flops = 2.0 * C1["tokens"] * C1["n"] * C1["k"]
-
-    times = torch.tensor([elapsed, e2e_elapsed, gemm_s], dtype=torch.float64, device=dev)
+    times = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed, e2e_elapsed, gemm_s = times.tolist()
+    elapsed, e2e_elapsed = times.tolist()
 
     if rank == 0:
-        peaks = measured_peaks()
-        tokens_total = C1["tokens"] * args.steps * world
-        cpu_dt, cores = time_cpu_baseline(5) if world == 1 else (None, None)
-        achieved = flops / gemm_s / 1e12
+        tokens_total = wl.tokens * args.steps * world
         line = {
-            "metric": "tok/s", "value": tokens_total / elapsed, "unit": "tok/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "c1: MXINT8 (int8, bs=16, pot) quantize_mx x2 + linear_mx, "
-                                   "X[2048,4096] W[4096,4096] per GPU",
-                       "l2": f"{n_sets} rotating input sets (~120 MB touched per step) exceed the 126 MB L2"},
-            "e2e": {"value": tokens_total / e2e_elapsed, "unit": "tok/s",
-                    "h2d_bytes_per_step": C1["tokens"] * C1["k"] * 2, "d2h_bytes_per_step": C1["tokens"] * C1["n"] * 2},
-            "gpu_launches": C1_LAUNCHES_PER_STEP * args.steps,
-            "roofline": {"kernel": "gemm_tn_kernel (tcgen05 bf16, 2048x4096x4096)", "bound": "tensor",
-                         "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
-                         "traffic": NCU_TRAFFIC_BYTES["c1"]},
+            "metric": "tok/s", "value": tokens_total / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "config": {"workload": wl.description,
+                       "l2": f"{wl.n_sets} rotating input sets; tensors touched per step exceed the 126 MB L2",
+                       "launch": "CUDA graph replay per step"},
+            "e2e": {"value": tokens_total / e2e_elapsed, "unit": "tok/s", "h2d_bytes_per_step": wl.h2d_bytes,
+                    "d2h_bytes_per_step": wl.d2h_bytes},
+            "gpu_launches": wl.launches_per_step * args.steps,
+            "roofline": roof,
             "clocks": clocks.summary(),
         }
-        if cpu_dt is not None:
-            line["cpu_baseline"] = {"value": C1["tokens"] / cpu_dt, "unit": "tok/s", "cores": cores, "kind": "port",
-                                    "sample": "5 full c1 steps after 1 warm-up"}
+        if world == 1:
+            value, dt, cores = time_cpu_baseline(WORKLOADS[args.workload], 3)
+            line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
+                                    "sample": f"3 {wl.cpu_sample} after 1 warm-up"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -282,10 +397,10 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1", choices=["c1"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
