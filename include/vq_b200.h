@@ -181,6 +181,20 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
 int vq_quantize_fp8(const void* in, const void* scale, int scale_dtype, void* out, int format, int64_t n,
                     int64_t elems_per_scale, void* stream);
 
+/* Attention probabilities as FP8 codes in one pass over the scores: per row,
+ *   s = bf16(score * score_scale); s = bf16(s + mask[row % mask_rows]);
+ *   p = bf16(softmax_fp32(s)); out = fp8(bf16(p / out_scale))
+ * -- the scale / mask / softmax / quantize sequence between the two attention
+ * matmuls of an eager-attention graph (ops/quantized.py:900-925 has the same
+ * sequence inside sdpa_mx), whose last step is the FP8 cast of
+ * backend/gpu/fp8.py:253-309.  scores: bfloat16 [rows, cols]; out: bytes
+ * [rows, cols]; mask: bfloat16 [mask_rows, cols] or NULL; causal_period T > 0
+ * additionally masks columns > (row % T) without reading them.  cols must be a
+ * multiple of 8 and at most 4096. */
+int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t rows, int64_t cols, float score_scale,
+                            const void* mask, int64_t mask_rows, int64_t causal_period,
+                            const void* out_scale, int out_scale_dtype, int format, void* stream);
+
 /* Synchronising health check for the GEMM kernels: returns VQ_ETIMEOUT if any
  * launch since the last reset gave up on a bounded barrier wait (its output is
  * then invalid).  No counterpart in the reference. */

@@ -82,3 +82,32 @@ def test_fp8_decoder_layer_matches_converted_graph():
     assert rel_err(got, want) <= 2e-2, rel_err(got, want)
     ref = W.bf16_layer_forward(x, params, shape)
     assert rel_err(got, ref) <= 0.15
+
+
+@pytest.mark.parametrize("rows,cols,period", [(8, 64, 0), (96, 256, 32), (64, 2048, 64), (10, 520, 0), (12, 4096, 0)])
+def test_softmax_quantize_fused_matches_unfused(rows, cols, period):
+    """The fused pass against the unfused bf16 op sequence on the CPU oracle."""
+    vb = _vb()
+    g = torch.Generator().manual_seed(rows + cols)
+    scores = (torch.randn(rows, cols, generator=g) * 6).bfloat16()
+    scale = 0.125
+    sp = torch.tensor(1.0 / 448.0, dtype=torch.bfloat16)
+    mask = None
+    if period:
+        t = torch.arange(rows) % period
+        mask = torch.where(torch.arange(cols)[None, :] > t[:, None], float("-inf"), 0.0).bfloat16()
+    s = scores * scale
+    if mask is not None:
+        s = s + mask
+    p = torch.softmax(s.float(), -1).bfloat16()
+    want = OQ.quantize(p, sp, qmap=OT.quantization_map("fp8_e4m3")).float()
+    got = vb.fp8.softmax_quantize_fp8(scores.cuda(), scale, sp.cuda(), causal_period=period).cpu()
+    got = got.view(torch.float8_e4m3fn).float()
+    # expf may differ from the CPU's in the last bit: allow a single FP8 step on a tiny fraction of entries
+    diff = (got - want).abs()
+    step = torch.maximum(want.abs(), got.abs()) * 0.126 + 2.0 ** -9
+    assert bool((diff <= step).all()), float(diff.max())
+    assert float((diff > 0).float().mean()) < 2e-3
+    if mask is not None:
+        got2 = vb.fp8.softmax_quantize_fp8(scores.cuda(), scale, sp.cuda(), mask=mask.cuda()).cpu()
+        assert torch.equal(got2.view(torch.float8_e4m3fn).float(), got)

@@ -98,6 +98,7 @@ SIGNATURES = {
     "vq_gemm_tn": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
     "vq_gemm_status": [_I],
     "vq_quantize_fp8": [_P, _P, _I, _P, _I, _I64, _I64, _P],
+    "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],
 }
 IN_BF16, IN_F16, IN_E4M3, IN_E5M2 = range(4)
 

@@ -95,19 +95,6 @@ __device__ __forceinline__ uint32_t round_pair(float a, float b, const Round& r,
   }
 }
 
-// round_bf16(x / s) for a normal, finite, positive s with rcp = 1/s correctly
-// rounded.  x * rcp is within 2 ulp of the correctly rounded quotient; when it
-// is that close to the midpoint between two bfloat16 values, or not a normal
-// number, the exact division decides.
-__device__ __forceinline__ float div_to_bf16(float x, float s, float rcp) {
-  float q = __fmul_rn(x, rcp);
-  uint32_t b = __float_as_uint(q);
-  uint32_t ex = (b >> 23) & 0xFFu;
-  uint32_t low = b & 0xFFFFu;
-  if (ex == 0u || ex == 0xFFu || (low - 0x7FFDu) <= 6u) q = __fdiv_rn(x, s);
-  return __bfloat162float(__float2bfloat16_rn(q));
-}
-
 // Exact generic treatment of one 16-byte vector (8 elements) given its block's amax.
 __device__ __noinline__ uint4 slow_vector(uint4 raw, uint32_t amax_bits, const ScaleRule& rule, const Round& r,
                                           int64_t flat, float* scale_out) {

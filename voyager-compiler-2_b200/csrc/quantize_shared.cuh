@@ -92,6 +92,25 @@ __device__ __forceinline__ float block_scale(uint32_t amax_bits, const ScaleRule
 __device__ __forceinline__ uint32_t abs_bits(float v) { return __float_as_uint(v) & 0x7FFFFFFFu; }
 
 
+// round_bf16(x / s) for a normal, finite, positive s with rcp = 1/s correctly
+// rounded.  x * rcp is within 2 ulp of the correctly rounded quotient; when it
+// is that close to the midpoint between two bfloat16 values, or not a normal
+// number, the exact division decides.
+__device__ __forceinline__ float div_to_bf16(float x, float s, float rcp) {
+  float q = __fmul_rn(x, rcp);
+  uint32_t b = __float_as_uint(q);
+  uint32_t ex = (b >> 23) & 0xFFu;
+  uint32_t low = b & 0xFFFFu;
+  if (ex == 0u || ex == 0xFFu || (low - 0x7FFDu) <= 6u) q = __fdiv_rn(x, s);
+  return __bfloat162float(__float2bfloat16_rn(q));
+}
+
+// True when s is a normal, finite, positive float whose reciprocal is normal too.
+__device__ __forceinline__ bool ordinary_divisor(float s) {
+  const uint32_t ex = (__float_as_uint(s) >> 23) & 0xFFu;
+  return ex >= 1u && ex <= 253u && s > 0.0f;
+}
+
 // bfloat16 fast paths (quantize_fast.cu)
 int fast_mode_of(const VqRound* r);
 int fast_mx_flat_bf16(const void* in, void* scale_out, void* codes_out, int64_t nvec, int G, int gshift,

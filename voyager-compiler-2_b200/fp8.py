@@ -62,3 +62,29 @@ def fp8_linear(x8: torch.Tensor, w8: torch.Tensor, scale_a: torch.Tensor, scale_
     (reference ``backend/gpu/fp8.py:372-400``)."""
     alpha = (scale_a * scale_w).reshape(())
     return fp8_gemm(x8, w8, alpha, bias, out_dtype)
+
+
+def softmax_quantize_fp8(scores: torch.Tensor, score_scale: float, out_scale: torch.Tensor,
+                         mask: Optional[torch.Tensor] = None, causal_period: int = 0,
+                         dtype: str = "fp8_e4m3") -> torch.Tensor:
+    """FP8 codes of ``softmax(scores * score_scale + mask)`` along the last axis in one pass
+    (every intermediate rounded to bfloat16 as the unfused graph does).  ``mask`` is a
+    ``[rows, cols]`` bfloat16 tensor applied cyclically over the score rows; ``causal_period``
+    ``T`` masks columns beyond ``row % T``."""
+    if scores.dtype != torch.bfloat16:
+        raise NotImplementedError("softmax_quantize_fp8 takes bfloat16 scores")
+    scores = scores.contiguous()
+    cols = scores.shape[-1]
+    rows = scores.numel() // max(cols, 1)
+    out = torch.empty(scores.shape, dtype=torch.uint8, device=scores.device)
+    mask_rows = 0
+    if mask is not None:
+        mask = mask.to(torch.bfloat16).reshape(-1, cols).contiguous()
+        mask_rows = mask.shape[0]
+    if out_scale.dtype not in _DTYPE_ID:
+        out_scale = out_scale.float()
+    N.check(N.lib().vq_softmax_quantize_fp8(scores.data_ptr(), out.data_ptr(), rows, cols, float(score_scale),
+                                            _ptr(mask), mask_rows, int(causal_period), out_scale.data_ptr(),
+                                            _dtype_id(out_scale.dtype), _FORMATS[dtype], _stream()),
+            "vq_softmax_quantize_fp8")
+    return out

@@ -151,7 +151,7 @@ class Fp8DecoderLayer:
         self._mask = None
 
     #: kernels of this package launched per forward (casts + GEMMs)
-    LAUNCHES = 8 + 9
+    LAUNCHES = 7 + 1 + 9
 
     def _tables(self, T, device):
         if self._rope is None or self._rope[0].shape[0] != T:
@@ -174,9 +174,8 @@ class Fp8DecoderLayer:
         k8 = FP8.quantize_fp8(k.transpose(0, 1), s["k"])                    # [kv, T, d]
         vt8 = FP8.quantize_fp8(v.permute(1, 2, 0), s["v"])                  # [kv, d, T]
         scores = FP8.fp8_gemm(q8, k8, self.alpha_qk)                        # [kv, groups*T, T]
-        scores = scores.view(sh.kv_heads, sh.groups, T, T) * (1.0 / math.sqrt(sh.head_dim)) + mask
-        p = torch.softmax(scores.float(), -1).to(x.dtype)
-        p8 = FP8.quantize_fp8(p.view(sh.kv_heads, sh.groups * T, T), s["p"])
+        # scale, causal mask, softmax and the FP8 cast of the probabilities in one pass
+        p8 = FP8.softmax_quantize_fp8(scores, 1.0 / math.sqrt(sh.head_dim), s["p"], causal_period=T)
         ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv)                          # [kv, groups*T, d]
         ctx = ctx.view(sh.kv_heads, sh.groups, T, sh.head_dim).permute(2, 0, 1, 3).reshape(T, sh.heads * sh.head_dim)
         x1 = x + FP8.fp8_gemm(FP8.quantize_fp8(ctx, s["ctx"]), self.w8["o"], self.alpha["o"])
