@@ -18,6 +18,8 @@
 // Every mbarrier wait is bounded; on timeout the kernel records an error code
 // in a device flag, drains, frees TMEM and exits.
 
+#include <cstdlib>
+
 #include "sm100_ptx.cuh"
 #include "vq_common.cuh"
 
@@ -58,6 +60,59 @@ __device__ __forceinline__ float load_param(const void* p, int64_t i, int dt) {
   if (dt == VQ_F32) return static_cast<const float*>(p)[i];
   if (dt == VQ_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
   return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+// Epilogue for 32 consecutive accumulator columns of one output row:
+// alpha, bias, one rounding, 16-byte stores where the row allows.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t (&v)[32], uint8_t* c_row, int row,
+                                            int col0, bool has_alpha, float alpha) {
+  if (row < p.M && col0 < p.N) {
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float x = __uint_as_float(v[j]);
+      if (has_alpha) x = __fmul_rn(x, alpha);
+      f[j] = x;
+    }
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) f[j] = __fadd_rn(f[j], load_param(p.bias, col0 + j, p.bias_dt));
+    }
+    const bool full = (col0 + 32 <= p.N);
+    if (p.out_dt == VQ_F32) {
+      float* dst = reinterpret_cast<float*>(c_row) + col0;
+      if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) dst[j] = f[j];
+      }
+    } else {
+      uint32_t packed[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (p.out_dt == VQ_BF16) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+          packed[j] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+          packed[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
+      if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+      } else {
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) dst[j] = (uint16_t)(packed[j >> 1] >> (16 * (j & 1)));
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -189,54 +244,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t v[32];
         tmem_ld_32x32(taddr + (uint32_t)c0, v);
         tmem_ld_wait();
-        const int col0 = n_blk * BN + c0;
-        if (row < p.M && col0 < p.N) {
-          float f[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(v[j]);
-            if (has_alpha) x = __fmul_rn(x, alpha);
-            f[j] = x;
-          }
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) f[j] = __fadd_rn(f[j], load_param(p.bias, col0 + j, p.bias_dt));
-          }
-          const bool full = (col0 + 32 <= p.N);
-          if (p.out_dt == VQ_F32) {
-            float* dst = reinterpret_cast<float*>(c_row) + col0;
-            if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = f[j];
-            }
-          } else {
-            uint32_t packed[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (p.out_dt == VQ_BF16) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-                packed[j] = *reinterpret_cast<uint32_t*>(&h);
-              } else {
-                __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
-                packed[j] = *reinterpret_cast<uint32_t*>(&h);
-              }
-            }
-            uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
-            if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4)
-                *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = (uint16_t)(packed[j >> 1] >> (16 * (j & 1)));
-            }
-          }
-        }
+        store_chunk(p, v, c_row, row, n_blk * BN + c0, has_alpha, alpha);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -250,6 +258,169 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant: two CTAs (a cluster of 2 on neighbouring SMs) share one
+// 256x256 tile.  Each CTA loads its own 128 rows of A and its own 128 of the
+// tile's 256 B rows (32 KB per stage, so twice the flops per byte fetched from
+// L2), the even CTA's thread issues tcgen05.mma.cta_group::2 (M = 256), and each
+// CTA's tensor memory receives its 128 rows of the accumulator.
+//   full barrier  : lives in the even CTA; both CTAs' TMA loads complete on it
+//   empty barrier : one per CTA, released by a tcgen05.commit sent to both CTAs
+//   acc_full      : one per CTA, same commit mechanism
+//   acc_empty     : lives in the even CTA; 8 arrivals (4 epilogue warps x 2 CTAs)
+// ---------------------------------------------------------------------------
+constexpr int P_STAGES = 6;
+constexpr int P_A_BYTES = 128 * BK_BYTES;  // 16 KB
+constexpr int P_B_BYTES = 128 * BK_BYTES;  // 16 KB (half of the tile's B rows)
+constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + P_STAGES * P_A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * (P_A_BYTES + P_B_BYTES));
+  uint64_t* full_bar = bars;                        // [P_STAGES] (used in the even CTA)
+  uint64_t* empty_bar = bars + P_STAGES;            // [P_STAGES]
+  uint64_t* acc_full = bars + 2 * P_STAGES;         // [2]
+  uint64_t* acc_empty = bars + 2 * P_STAGES + 2;    // [2] (used in the even CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = even (leader), 1 = odd
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n * p.batch;
+  const int k_elems_per_stage = BK_BYTES / p.elem_bytes;
+  const int k_blocks = (p.K + k_elems_per_stage - 1) / k_elems_per_stage;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();  // the peer's barriers are initialised before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m_blk = (int)(tile % tiles_m);
+        const int n_blk = (int)((tile / tiles_m) % tiles_n);
+        const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+        const int m0 = m_blk * 2 * BM + (int)rank * BM;
+        const int n0 = n_blk * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          // the even CTA arms its barrier for the bytes of both CTAs
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (P_A_BYTES + P_B_BYTES));
+          const uint32_t leader_full = map_to_cta(&full_bar[stage], 0);
+          tma_load_3d_pair(smem_a + stage * P_A_BYTES, &map_a, leader_full, kb * k_elems_per_stage, m0, b);
+          tma_load_3d_pair(smem_b + stage * P_B_BYTES, &map_b, leader_full, kb * k_elems_per_stage, n0, b);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + stage * P_A_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + stage * P_B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK_BYTES / MMA_K_BYTES; ++k) {
+            const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
+            const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            if (p.kind_f8) mma_f8f6f4_ss_pair(tmem_acc, da, db, p.idesc, accumulate);
+            else mma_f16_ss_pair(tmem_acc, da, db, p.idesc, accumulate);
+          }
+          mma_commit_pair(&empty_bar[stage], 0x3);  // both CTAs may refill this stage
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit_pair(&acc_full[acc], 0x3);  // both CTAs' epilogues may read their rows
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ----------------------
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool has_alpha = p.alpha != nullptr;
+    const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int m_blk = (int)(tile % tiles_m);
+      const int n_blk = (int)((tile / tiles_m) % tiles_n);
+      const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = m_blk * 2 * BM + (int)rank * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
+      uint8_t* c_row = static_cast<uint8_t*>(p.C) +
+                       ((int64_t)b * p.strideC + (int64_t)row * p.ldc) * (p.out_dt == VQ_F32 ? 4 : 2);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + (uint32_t)c0, v);
+        tmem_ld_wait();
+        store_chunk(p, v, c_row, row, n_blk * BN + c0, has_alpha, alpha);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
+  cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its tiles
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
@@ -316,11 +487,7 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
   VQ_REQUIRE(lda >= K && ldb >= K && ldc >= N, "vq_gemm_tn: leading dimension smaller than the row");
   VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && batch < (1ll << 31), "vq_gemm_tn: extent too large");
 
-  CUtensorMap map_a, map_b;
   const int kind = in_kind == VQ_IN_F16 ? VQ_F16 : VQ_BF16;
-  if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
-  if (int e = make_operand_map(&map_b, B, kind, eb, N, K, ldb, batch, strideB, BN)) return e;
-
   GemmParams p{};
   p.C = C;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
@@ -332,8 +499,53 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
   p.out_dt = out_dtype;
   p.kind_f8 = eb == 1;
   const int fmt = in_kind == VQ_IN_BF16 ? 1 : in_kind == VQ_IN_F16 ? 0 : in_kind == VQ_IN_E4M3 ? 0 : 1;
-  p.idesc = sm100::make_idesc(BM, BN, fmt, fmt, 0, 0);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
 
+  // CTA pairs (256x256 tiles) when there is more than one 128-row block of output;
+  // VQ_GEMM_PAIR=0 forces the single-CTA kernel.
+  static int pair_mode = -1;        // -1 unknown, 0 off, 1 on
+  static int max_clusters = 0;
+  if (pair_mode < 0) {
+    const char* env = getenv("VQ_GEMM_PAIR");
+    pair_mode = (env && env[0] == '0') ? 0 : 1;
+    if (pair_mode) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)P_SMEM_BYTES);
+      if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(kSmCount, 1, 1);
+      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = P_SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, gemm_tn_pair_kernel, &cfg);
+      if (e != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        pair_mode = 0;
+      } else {
+        max_clusters = n < kSmCount / 2 ? n : kSmCount / 2;
+      }
+    }
+  }
+  if (pair_mode == 1 && M > BM) {
+    CUtensorMap map_a, map_b;
+    if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
+    if (int e = make_operand_map(&map_b, B, kind, eb, N, K, ldb, batch, strideB, BN / 2)) return e;
+    p.idesc = sm100::make_idesc(2 * BM, BN, fmt, fmt, 0, 0);
+    const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
+    const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
+    gemm_tn_pair_kernel<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, p);
+    return check_launch("gemm_tn_pair_kernel");
+  }
+
+  CUtensorMap map_a, map_b;
+  if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
+  if (int e = make_operand_map(&map_b, B, kind, eb, N, K, ldb, batch, strideB, BN)) return e;
+  p.idesc = sm100::make_idesc(BM, BN, fmt, fmt, 0, 0);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
@@ -342,7 +554,7 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
-  gemm_tn_kernel<<<grid, NUM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+  gemm_tn_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
   return check_launch("gemm_tn_kernel");
 }
 
