@@ -151,6 +151,33 @@ int vq_dequantize_mx(const void* in, const void* scale, const void* code, int32_
  * be zeroed by the caller; NaN inputs give NaN. */
 int vq_amax(const void* in, int dtype, int64_t n, float* out, void* stream);
 
+/* hadamard_rotate -- ops/quantized.py:1038-1067: each run of 16 elements along the
+ * middle axis of a dense [O, A, I] tensor is multiplied by the float32 16x16
+ * `matrix` (device, row-major; out_j = sum_k in_k * matrix[k][j]) in fp32; A is
+ * zero padded to a multiple of 16 and `out` is dense [O, ceil16(A), I]. */
+int vq_hadamard_rotate(const void* in, void* out, int dtype, const float* matrix, int64_t O, int64_t A,
+                       int64_t I, void* stream);
+
+/* One block of the GPTQ column sweep -- quantization/gptq.py: block_scale (85-143)
+ * and quantize_block (189-220), as compensate_weight (223-308) calls them.
+ * work/out are fp32 [rows, K]; columns [start, start+n) (n <= 128) are rounded one
+ * by one against each row's scale, errors over the pivots of U (fp32 [K, K], the
+ * upper Cholesky factor of the inverse Hessian) are propagated inside the block and
+ * written to deltas (fp32 [rows, n]).  affine = 0: microscaling scale amax/quant_max
+ * through scale_round (shrink = 1 adds the reference's five-candidate search, weighted
+ * by salience[K]); affine = 1: group-wise affine scale and zero point
+ * (ops/quantized.py:1268-1281 applied to the block), which the reference's GPTQ lacks. */
+int vq_gptq_block(float* work, float* out, float* deltas, const float* U, const float* salience,
+                  int64_t rows, int64_t K, int64_t start, int64_t n, int affine, float quant_min,
+                  float quant_max, int shrink, const VqRound* scale_round, const VqRound* round,
+                  void* stream);
+
+/* The trailing update of compensate_weight (quantization/gptq.py:302-303):
+ * work[:, start+n:] -= deltas @ U[start:start+n, start+n:], fp32, products summed in
+ * ascending column order. */
+int vq_gptq_update(float* work, const float* deltas, const float* U, int64_t rows, int64_t K,
+                   int64_t start, int64_t n, void* stream);
+
 /* operand element kinds of the tensor-core GEMM */
 enum { VQ_IN_BF16 = 0, VQ_IN_F16 = 1, VQ_IN_E4M3 = 2, VQ_IN_E5M2 = 3 };
 

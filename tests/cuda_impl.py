@@ -49,3 +49,7 @@ CudaImpl.linear_mx = staticmethod(_wrap(Q.linear_mx))
 CudaImpl.matmul_mx = staticmethod(_wrap(Q.matmul_mx))
 CudaImpl.linear = staticmethod(_wrap(Q.linear))
 CudaImpl.matmul = staticmethod(_wrap(Q.matmul))
+CudaImpl.sdpa_mx = staticmethod(_wrap(Q.sdpa_mx))
+CudaImpl.quantize_mx_transpose = staticmethod(_wrap(Q.quantize_mx_transpose))
+CudaImpl.hadamard_rotate = staticmethod(_wrap(voyager_b200.ops.hadamard_rotate))
+CudaImpl.hadamard_matrix = staticmethod(voyager_b200.ops.hadamard_matrix)

@@ -97,6 +97,10 @@ SIGNATURES = {
     "vq_amax": [_P, _I, _I64, _P, _P],
     "vq_gemm_tn": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
     "vq_gemm_status": [_I],
+    "vq_gptq_block": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _F, _F, _I, ctypes.POINTER(VqRound),
+                      ctypes.POINTER(VqRound), _P],
+    "vq_gptq_update": [_P, _P, _P, _I64, _I64, _I64, _I64, _P],
+    "vq_hadamard_rotate": [_P, _P, _I, _P, _I64, _I64, _I64, _P],
     "vq_quantize_fp8": [_P, _P, _I, _P, _I, _I64, _I64, _P],
     "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],
 }

@@ -546,6 +546,43 @@ __global__ void __launch_bounds__(256) amax_kernel(const void* __restrict__ in, 
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// 16-point random-Hadamard rotation along one axis
+// ---------------------------------------------------------------------------
+// Dense [O, A, I] input, runs of 16 along A (zero padded to Ap = ceil16(A)):
+// out[o][16 r + j][i] = sum_k in[o][16 r + k][i] * m[k][j], accumulated in fp32
+// in ascending k, rounded once to the storage dtype.
+template <int DT>
+__global__ void __launch_bounds__(256)
+hadamard_kernel(const void* __restrict__ in, void* __restrict__ out, const float* __restrict__ matrix, int64_t O,
+                int64_t A, int64_t Ap, int64_t I) {
+  __shared__ float m[16][16];
+  for (int t = threadIdx.x; t < 256; t += blockDim.x) m[t >> 4][t & 15] = matrix[t];
+  __syncthreads();
+  const int64_t runs = Ap / 16;
+  const int64_t total = O * runs * I;
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int64_t i = t % I;
+    const int64_t r = (t / I) % runs;
+    const int64_t o = t / (I * runs);
+    float x[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int64_t a = r * 16 + k;
+      x[k] = a < A ? load1<DT>(in, (o * A + a) * I + i) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float acc = 0.0f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) acc = fmaf(x[k], m[k][j], acc);
+      store1<DT>(out, (o * Ap + r * 16 + j) * I + i, acc);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // host launchers
 // ---------------------------------------------------------------------------
@@ -869,6 +906,18 @@ int vq_amax(const void* in, int dtype, int64_t n, float* out, void* stream) {
   int grid = grid_for((n + vec_width(dtype) - 1) / vec_width(dtype), 256, 4);
   VQ_DISPATCH_DTYPE(dtype, (amax_kernel<DT><<<grid, 256, 0, st>>>(in, n, vec_ok, reinterpret_cast<uint32_t*>(out))));
   return check_launch("amax_kernel");
+}
+
+int vq_hadamard_rotate(const void* in, void* out, int dtype, const float* matrix, int64_t O, int64_t A, int64_t I,
+                       void* stream) {
+  VQ_REQUIRE(O >= 0 && A >= 0 && I >= 0, "vq_hadamard_rotate: negative extent");
+  if (O == 0 || A == 0 || I == 0) return VQ_OK;
+  VQ_REQUIRE(in && out && matrix, "vq_hadamard_rotate: null argument");
+  const int64_t Ap = (A + 15) / 16 * 16;
+  int grid = grid_for(O * (Ap / 16) * I, 256, 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  VQ_DISPATCH_DTYPE(dtype, (hadamard_kernel<DT><<<grid, 256, 0, st>>>(in, out, matrix, O, A, Ap, I)));
+  return check_launch("hadamard_kernel");
 }
 
 }  // extern "C"

@@ -766,3 +766,147 @@ def gemm_status(reset=True):
     (synchronises the device)."""
     torch.cuda.synchronize()
     N.check(N.lib().vq_gemm_status(int(reset)), "vq_gemm_status")
+
+
+# ---------------------------------------------------------------------------
+# Hadamard rotation, two-layout quantize, attention
+# ---------------------------------------------------------------------------
+HADAMARD_SIGNS = (1, 1, 1, -1, 1, -1, -1, -1, -1, -1, -1, 1, -1, 1, -1, -1)
+
+
+def hadamard_matrix(device=None) -> torch.Tensor:
+    """``diag(signs) @ H16 / 4``: Sylvester's 16x16 Hadamard matrix with Transformer
+    Engine's fixed sign vector (reference ``fake_quantize.py:47-65``)."""
+    h = torch.ones(1, 1)
+    while h.shape[0] < HADAMARD_SIZE:
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)])
+    signs = torch.tensor(HADAMARD_SIGNS, dtype=torch.float32)
+    return (signs[:, None] * h / math.sqrt(HADAMARD_SIZE)).to(device)
+
+
+def hadamard_rotate(x: torch.Tensor, axis: int, matrix: torch.Tensor) -> torch.Tensor:
+    """Multiply each run of 16 elements along ``axis`` (the last or second-to-last) by
+    ``matrix`` in fp32; the axis is zero padded to whole runs and keeps the padded
+    length (reference ``quantized.py:1038-1067``)."""
+    axis %= x.dim()
+    if axis < x.dim() - 2:
+        raise ValueError(f"cannot rotate along axis {axis} of {x.dim()}")
+    x = x.contiguous()
+    A = x.shape[axis]
+    O = int(math.prod(x.shape[:axis]))
+    I = int(math.prod(x.shape[axis + 1:]))
+    padded = -(-A // HADAMARD_SIZE) * HADAMARD_SIZE
+    out = torch.empty(*x.shape[:axis], padded, *x.shape[axis + 1:], dtype=x.dtype, device=x.device)
+    m = matrix.to(device=x.device, dtype=torch.float32).contiguous()
+    N.check(N.lib().vq_hadamard_rotate(x.data_ptr(), out.data_ptr(), _dtype_id(x.dtype), m.data_ptr(), O, A, I,
+                                       _stream()), "vq_hadamard_rotate")
+    return out
+
+
+quantized_ops_lib.define(
+    "quantize_mx_transpose(Tensor self, Tensor qmap, int block_size, "
+    "float quant_max, bool force_scale_power_of_two=False, "
+    "Tensor scale_qmap=None, Tensor output_code=None, Tensor? seed=None, "
+    "Tensor? global_scale=None, Tensor? transpose_seed=None, "
+    "Tensor? transpose_global_scale=None, Tensor? hadamard=None) "
+    "-> (Tensor, Tensor, Tensor, Tensor)"
+)
+
+
+def quantize_mx_transpose(input, qmap, block_size, quant_max, force_scale_power_of_two=False, scale_qmap=None,
+                          output_code=None, seed=None, global_scale=None, transpose_seed=None,
+                          transpose_global_scale=None, hadamard=None):
+    """``quantize_mx`` of the input along its last axis and of its transpose (optionally
+    Hadamard-rotated) along the transpose's last axis (reference ``quantized.py:1171-1215``)."""
+    t = input.mT.contiguous()
+    if hadamard is not None:
+        t = hadamard_rotate(t, -1, hadamard)
+    common = (qmap, (-1,), block_size, quant_max, force_scale_power_of_two, scale_qmap, output_code)
+    return (*quantize_mx(input, *common, seed, global_scale),
+            *quantize_mx(t, *common, transpose_seed, transpose_global_scale))
+
+
+quantized_ops_lib.impl("quantize_mx_transpose", quantize_mx_transpose, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::quantize_mx_transpose")
+def _(input, qmap, block_size, quant_max, force_scale_power_of_two=False, scale_qmap=None, output_code=None,
+      seed=None, global_scale=None, transpose_seed=None, transpose_global_scale=None, hadamard=None):
+    t_shape = list(input.shape)
+    t_shape[-1], t_shape[-2] = t_shape[-2], t_shape[-1]
+    if hadamard is not None:
+        t_shape[-1] = -(-t_shape[-1] // HADAMARD_SIZE) * HADAMARD_SIZE
+    return (input.new_empty(_scale_shape(input.shape, [-1], block_size)), torch.empty_like(input),
+            input.new_empty(_scale_shape(t_shape, [-1], block_size)), input.new_empty(t_shape))
+
+
+quantized_ops_lib.define(
+    "sdpa_mx(Tensor query, Tensor key, Tensor value, Tensor? attn_mask=None, "
+    "float dropout_p=0., bool is_causal=False, Tensor? query_residual=None, "
+    "Tensor? key_residual=None, Tensor? value_residual=None, "
+    "Tensor? residual_mask=None, *, float? scale=None, "
+    "bool enable_gqa=False, Tensor? query_scale=None, Tensor? key_scale=None, "
+    "Tensor? value_scale=None, int? block_size=None, Tensor? input_code=None, "
+    "Tensor? weight_code=None, Tensor? probs_qmap=None, "
+    "float? probs_quant_max=None, Tensor? probs_scale_qmap=None, "
+    "Tensor? probs_code=None, bool force_scale_power_of_two=False) -> Tensor"
+)
+
+
+def _masked(scores, mask):
+    if mask is None:
+        return scores
+    if mask.dtype == torch.bool:
+        return scores.masked_fill(~mask, float("-inf"))
+    return scores + mask
+
+
+def sdpa_mx(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, query_residual=None,
+            key_residual=None, value_residual=None, residual_mask=None, *, scale=None, enable_gqa=False,
+            query_scale=None, key_scale=None, value_scale=None, block_size=None, input_code=None,
+            weight_code=None, probs_qmap=None, probs_quant_max=None, probs_scale_qmap=None, probs_code=None,
+            force_scale_power_of_two=False):
+    """Attention over microscaling operands: read back q/k/v, scores and PV on the tensor
+    cores, one softmax over main and residual keys, probabilities re-quantized with
+    ``quantize_mx`` before the value matmul (reference ``quantized.py:836-928``)."""
+    if is_causal and attn_mask is not None:
+        raise ValueError("is_causal excludes an explicit attn_mask")
+    q = _read_operand(query, query_scale, input_code, block_size)
+    k = _read_operand(key, key_scale, weight_code, block_size)
+    v = _read_operand(value, value_scale, weight_code, block_size)
+    residual = key_residual is not None
+    if enable_gqa:
+        g = q.shape[-3] // k.shape[-3]
+        k, v = k.repeat_interleave(g, dim=-3), v.repeat_interleave(g, dim=-3)
+        if residual:
+            key_residual = key_residual.repeat_interleave(g, dim=-3)
+            value_residual = value_residual.repeat_interleave(g, dim=-3)
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    scores = gemm_tn(q, k) * scale
+    if is_causal:
+        attn_mask = torch.ones(scores.shape[-2:], dtype=torch.bool, device=scores.device).tril()
+    scores = _masked(scores, attn_mask)
+    keys = scores.shape[-1]
+    if residual:
+        res = _masked(gemm_tn(query_residual, key_residual) * scale, residual_mask)
+        scores = torch.cat([scores, res], dim=-1)
+    probs = torch.softmax(scores, dim=-1)
+    probs, res_probs = probs[..., :keys], probs[..., keys:]
+    if probs_qmap is not None:
+        p_scale, probs = quantize_mx(probs, probs_qmap, [-1], block_size, probs_quant_max,
+                                     force_scale_power_of_two, probs_scale_qmap, probs_code)
+        probs = _read_operand(probs, p_scale, input_code, block_size)
+    out = gemm_tn(probs.contiguous(), v.mT)
+    if residual:
+        out = out + gemm_tn(res_probs.contiguous(), value_residual.mT)
+    return out
+
+
+quantized_ops_lib.impl("sdpa_mx", sdpa_mx, "CUDA")
+
+
+@torch.library.register_fake("quantized_ops::sdpa_mx")
+def _(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, query_residual=None, key_residual=None,
+      value_residual=None, residual_mask=None, **kwargs):
+    return query.new_empty(*query.shape[:-1], value.shape[-1])
