@@ -1,0 +1,79 @@
+"""Shared driver of the tensor-parallel tests: one SwiGLU MLP, sharded over the ranks of a
+process group, against the unsharded computation."""
+
+import os
+import types
+
+import torch
+import torch.distributed as dist
+
+from oracle import gemm as OG
+from oracle import quantizers as OQ
+from oracle import tables as OT
+
+
+def oracle_ops():
+    return types.SimpleNamespace(quantize_mx=OQ.quantize_mx, linear_mx=OG.linear_mx)
+
+
+def problem(scheme, device="cpu"):
+    import voyager_b200
+
+    P = voyager_b200.parallel
+    g = torch.Generator().manual_seed(21)
+    T, H, I = 64, 128, 256
+    x = torch.randn(T, H, generator=g).bfloat16().to(device)
+    gate = (torch.randn(I, H, generator=g) * 0.05).bfloat16().to(device)
+    up = (torch.randn(I, H, generator=g) * 0.05).bfloat16().to(device)
+    down = (torch.randn(H, I, generator=g) * 0.05).bfloat16().to(device)
+    if scheme == "mxint8":
+        spec = P.MXSpec(qmap=OT.quantization_map("int8").to(device), block_size=16, quant_max=127.0, power_of_two=True)
+    elif scheme == "nvfp4":
+        spec = P.MXSpec(qmap=OT.quantization_map("fp4_e2m1").to(device), block_size=16, quant_max=6.0,
+                        scale_qmap=OT.quantization_map("fp8_e4m3").to(device), global_scale_max=448.0)
+    else:
+        raise ValueError(scheme)
+    return x, gate, up, down, spec
+
+
+def run_rank(rank, world, backend, scheme, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group(backend, rank=rank, world_size=world)
+    try:
+        import voyager_b200
+
+        P = voyager_b200.parallel
+        device = f"cuda:{rank}" if backend == "nccl" else "cpu"
+        ops = None if backend == "nccl" else oracle_ops()
+        x, gate, up, down, spec = problem(scheme, device)
+        mlp = P.TensorParallelMLP(gate, up, down, spec, spec, ops=ops)
+        full = mlp(x, scatter_output=False)
+        part = mlp(x, scatter_output=True)
+        gathered = P.all_gather_rows(part)
+        # token-sharded input: codes and scales are gathered instead of values
+        lo, hi = P.shard_bounds(x.shape[0], rank, world)
+        col = P.column_parallel_linear(x[lo:hi], *mlp.shards["gate"][:2], spec, spec, gather_input=True,
+                                       ops=ops) if spec.global_scale_max is None else None
+        col_ref = P.column_parallel_linear(x, *mlp.shards["gate"][:2], spec, spec, ops=ops) \
+            if spec.global_scale_max is None else None
+        if rank == 0:
+            results["full"] = full.cpu()
+            results["gathered"] = gathered.cpu()
+            if col is not None:
+                results["col_equal"] = bool(torch.equal(col.cpu(), col_ref.cpu()))
+    finally:
+        dist.destroy_process_group()
+
+
+def single_process_reference(scheme):
+    """The unsharded MLP on the CPU oracle."""
+    import voyager_b200
+
+    P = voyager_b200.parallel
+    x, gate, up, down, spec = problem(scheme)
+    mlp = P.TensorParallelMLP(gate, up, down, spec, spec, ops=oracle_ops())
+    return mlp(x)

@@ -10,6 +10,7 @@ from . import ops  # noqa: F401  (registers torch.ops.quantized_ops.*)
 from . import fp8  # noqa: F401
 from . import workloads  # noqa: F401
 from . import gptq  # noqa: F401
+from . import parallel  # noqa: F401
 from ._native import build  # noqa: F401
 from .formats import (  # noqa: F401
     QScheme,

@@ -1,0 +1,186 @@
+"""Tensor-parallel microscaling linears over one multi-GPU box.
+
+The reference has no distributed execution (its ``modeling.py`` only places
+layers on devices).  This module shards the quantized linears of a Llama-shaped
+layer the Megatron way, one process per GPU with ``torch.distributed``:
+
+* **column-parallel** (q/k/v, gate/up): the weight's codes and block scales are
+  split along the output features; blocks run along K, so a shard is a row
+  slice.  The activation is quantized once (or its codes and scales are
+  all-gathered from token shards, 2.1 B/element instead of 2 + 2).
+* **row-parallel** (o_proj, down_proj): weight and activation are split along K
+  in whole blocks, so each rank's block scales and codes are exactly those of
+  the unsharded tensor; ranks produce fp32 partial products that are
+  reduce-scattered over token rows (or all-reduced) and rounded once, which is
+  the single-GPU result up to fp32 summation order.
+* a per-tensor global scale (NVFP4) on a K-sharded activation needs the global
+  amax: one scalar all-reduce(max) keeps it, and therefore every code, identical
+  to the single-GPU run.
+
+Collectives are NCCL on GPUs (NVLink/NVSwitch); the same code runs on the gloo
+backend for the CPU tests, where the operator namespace is injected.
+"""
+
+import dataclasses
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclasses.dataclass(frozen=True)
+class MXSpec:
+    """Arguments of ``quantize_mx`` / ``linear_mx`` for one tensor."""
+
+    qmap: torch.Tensor
+    block_size: int
+    quant_max: float
+    power_of_two: bool = False
+    scale_qmap: Optional[torch.Tensor] = None
+    output_code: Optional[torch.Tensor] = None
+    code: Optional[torch.Tensor] = None          # codebook for read-back (lookup formats)
+    global_scale_max: Optional[float] = None     # NVFP4: largest value of the scale dtype (448)
+
+
+def _ops(ops):
+    return torch.ops.quantized_ops if ops is None else ops
+
+
+def shard_bounds(extent: int, rank: int, world: int, multiple: int = 1):
+    """Contiguous shard ``[lo, hi)`` of ``extent`` for ``rank``; every shard is a whole
+    number of ``multiple`` (blocks must not straddle ranks)."""
+    if extent % (world * multiple):
+        raise ValueError(f"{extent} does not split into {world} shards of whole {multiple}-element blocks")
+    per = extent // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_weight(codes, scale, mode: str, rank: int, world: int, block_size: int):
+    """Slice a quantized weight ``codes [N, K]`` / ``scale [N, K/bs]`` for ``rank``.
+    ``mode`` is ``"column"`` (split N) or ``"row"`` (split K)."""
+    if mode == "column":
+        lo, hi = shard_bounds(codes.shape[0], rank, world)
+        return codes[lo:hi].contiguous(), scale[lo:hi].contiguous()
+    if mode == "row":
+        lo, hi = shard_bounds(codes.shape[1], rank, world, block_size)
+        return codes[:, lo:hi].contiguous(), scale[:, lo // block_size:hi // block_size].contiguous()
+    raise ValueError(mode)
+
+
+def global_amax_scale(x, spec: MXSpec, group=None):
+    """NVFP4's per-tensor scale ``amax / (quant_max * scale_max)`` of a tensor whose K
+    axis is sharded over ``group``: the amax is all-reduced so that every rank gets the
+    value the unsharded tensor would give."""
+    if x.is_cuda:
+        from .ops import tensor_amax  # one pass, no intermediate |x| tensor
+
+        amax = tensor_amax(x)
+    else:
+        amax = x.abs().amax().float()
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    ratio = (amax.to(x.dtype) / (spec.quant_max * spec.global_scale_max))
+    return ratio.clamp_min(torch.finfo(torch.float32).tiny)
+
+
+def quantize_activation(x, spec: MXSpec, ops=None, group=None):
+    """``(scale, codes, global_scale)`` of an activation blocked along its last axis."""
+    gs = None if spec.global_scale_max is None else global_amax_scale(x, spec, group)
+    scale, codes = _ops(ops).quantize_mx(x, spec.qmap, [-1], spec.block_size, spec.quant_max, spec.power_of_two,
+                                         spec.scale_qmap, spec.output_code, None, gs)
+    return scale, codes, gs
+
+
+def all_gather_rows(t, group=None):
+    """Concatenate every rank's token rows (first axis)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return t
+    out = torch.empty((world * t.shape[0], *t.shape[1:]), dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+    return out
+
+
+def reduce_scatter_rows(t, group=None):
+    """Sum over ranks and keep this rank's slice of the token rows (first axis)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return t
+    if t.shape[0] % world:
+        raise ValueError(f"{t.shape[0]} token rows do not split over {world} ranks")
+    out = torch.empty((t.shape[0] // world, *t.shape[1:]), dtype=t.dtype, device=t.device)
+    if dist.get_backend(group) == "gloo":  # gloo has no reduce_scatter_tensor
+        full = t.contiguous().clone()
+        dist.all_reduce(full, group=group)
+        rank = dist.get_rank(group)
+        return full[rank * out.shape[0]:(rank + 1) * out.shape[0]].contiguous()
+    dist.reduce_scatter_tensor(out, t.contiguous(), group=group)
+    return out
+
+
+def column_parallel_linear(x, w_codes, w_scale, act: MXSpec, wgt: MXSpec, *, weight_global_scale=None,
+                           gather_input=False, group=None, ops=None, quantized=None):
+    """``x @ W[shard]^T`` for a weight split along its output features.  ``x`` is the full
+    activation ``[T, K]`` (or this rank's token rows when ``gather_input``: codes and scales
+    are gathered, not the bfloat16 values).  ``quantized`` reuses an activation already
+    quantized by ``quantize_activation`` (linears sharing one input).  Returns ``[T, N / world]``."""
+    scale, codes, gs = quantized if quantized is not None else quantize_activation(x, act, ops, None)
+    if gather_input:
+        if gs is not None:
+            raise ValueError("a global scale must be computed over the gathered activation")
+        scale, codes = all_gather_rows(scale, group), all_gather_rows(codes, group)
+    alpha = None if gs is None else gs * weight_global_scale
+    return _ops(ops).linear_mx(codes, w_codes, None, input_scale=scale, weight_scale=w_scale,
+                               block_size=act.block_size, input_code=act.code, weight_code=wgt.code, alpha=alpha)
+
+
+def row_parallel_linear(x_shard, w_codes, w_scale, act: MXSpec, wgt: MXSpec, *, weight_global_scale=None,
+                        scatter_output=True, group=None, ops=None):
+    """``x @ W^T`` for activation and weight split along K: fp32 partial products are
+    reduce-scattered over token rows (or all-reduced) and rounded once to ``x``'s dtype."""
+    scale, codes, gs = quantize_activation(x_shard, act, ops, group)
+    alpha = None if gs is None else gs * weight_global_scale
+    partial = _ops(ops).linear_mx(codes, w_codes, None, input_scale=scale, weight_scale=w_scale,
+                                  block_size=act.block_size, input_code=act.code, weight_code=wgt.code,
+                                  alpha=alpha, out_dtype=torch.float32)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world > 1:
+        if scatter_output:
+            partial = reduce_scatter_rows(partial, group)
+        else:
+            dist.all_reduce(partial, group=group)
+    return partial.to(x_shard.dtype)
+
+
+class TensorParallelMLP:
+    """SwiGLU MLP with gate/up column-parallel and down row-parallel.  Weights are
+    quantized once on the full tensors (so block and global scales are the single-GPU
+    ones) and then sliced per rank."""
+
+    def __init__(self, gate, up, down, act: MXSpec, wgt: MXSpec, group=None, ops=None):
+        self.act, self.wgt, self.group, self.ops = act, wgt, group, ops
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        q = _ops(ops)
+        self.shards = {}
+        for name, w, mode in (("gate", gate, "column"), ("up", up, "column"), ("down", down, "row")):
+            gs = None
+            if wgt.global_scale_max is not None:
+                gs = global_amax_scale(w, wgt, None)  # the full weight is present on every rank here
+            s, c = q.quantize_mx(w, wgt.qmap, [-1], wgt.block_size, wgt.quant_max, wgt.power_of_two, wgt.scale_qmap,
+                                 wgt.output_code, None, gs)
+            cs, ss = shard_weight(c, s, mode, self.rank, self.world, wgt.block_size)
+            self.shards[name] = (cs, ss, gs)
+
+    def forward(self, x, scatter_output=False):
+        a, w = self.act, self.wgt
+        xq = quantize_activation(x, a, self.ops, None)           # gate and up read one quantized input
+        g = column_parallel_linear(x, *self.shards["gate"][:2], a, w, weight_global_scale=self.shards["gate"][2],
+                                   group=self.group, ops=self.ops, quantized=xq)
+        u = column_parallel_linear(x, *self.shards["up"][:2], a, w, weight_global_scale=self.shards["up"][2],
+                                   group=self.group, ops=self.ops, quantized=xq)
+        h = torch.nn.functional.silu(g) * u                      # [T, I / world]: already K-sharded for down
+        return row_parallel_linear(h, *self.shards["down"][:2], a, w, weight_global_scale=self.shards["down"][2],
+                                   scatter_output=scatter_output, group=self.group, ops=self.ops)
+
+    __call__ = forward
