@@ -178,6 +178,26 @@ int vq_gptq_block(float* work, float* out, float* deltas, const float* U, const 
 int vq_gptq_update(float* work, const float* deltas, const float* U, int64_t rows, int64_t K,
                    int64_t start, int64_t n, void* stream);
 
+/* One whole GPTQ block step (vq_gptq_block followed by vq_gptq_update) that needs
+ * no buffer for the per-column errors and performs no allocation of any kind.
+ * It has no counterpart in the reference.  It is meant for hosts that cannot
+ * allocate device memory while they run: a runtime working inside a fixed,
+ * fully planned arena, or a plugin in a process that forbids cudaMalloc after
+ * start-up.  The errors are kept in an 8 MiB array built into the library
+ * (resident on every GPU that loads it, until the process exits), so
+ * rows * n must not exceed 2 097 152 values (for example 16 384 rows of a
+ * 128-column block); larger calls fail with VQ_EINVAL and a message saying so.
+ * The first call on a device looks up the array's address (cudaGetSymbolAddress)
+ * with that device current; make that first call before any stream capture.
+ * All calls on a device share the array: calls that may overlap on the GPU
+ * (different streams without ordering between them) race on it and must be
+ * serialised by the caller.  Inputs, outputs and stream are as for
+ * vq_gptq_block. */
+int vq_gptq_block_step_static(float* work, float* out, const float* U, const float* salience,
+                              int64_t rows, int64_t K, int64_t start, int64_t n, int affine,
+                              float quant_min, float quant_max, int shrink, const VqRound* scale_round,
+                              const VqRound* round, void* stream);
+
 /* operand element kinds of the tensor-core GEMM */
 enum { VQ_IN_BF16 = 0, VQ_IN_F16 = 1, VQ_IN_E4M3 = 2, VQ_IN_E5M2 = 3 };
 

@@ -100,6 +100,8 @@ SIGNATURES = {
     "vq_gptq_block": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _F, _F, _I, ctypes.POINTER(VqRound),
                       ctypes.POINTER(VqRound), _P],
     "vq_gptq_update": [_P, _P, _P, _I64, _I64, _I64, _I64, _P],
+    "vq_gptq_block_step_static": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _F, _F, _I, ctypes.POINTER(VqRound),
+                                  ctypes.POINTER(VqRound), _P],
     "vq_hadamard_rotate": [_P, _P, _I, _P, _I64, _I64, _I64, _P],
     "vq_quantize_fp8": [_P, _P, _I, _P, _I, _I64, _I64, _P],
     "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],

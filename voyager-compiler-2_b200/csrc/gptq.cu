@@ -231,3 +231,61 @@ extern "C" int vq_gptq_update(float* work, const float* deltas, const float* U, 
                                                                           (int)n, (int)end);
   return check_launch("gptq_update_kernel");
 }
+
+// ---------------------------------------------------------------------------
+// One GPTQ block step for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------
+// vq_gptq_block + vq_gptq_update hand the per-column errors from the sweep to the
+// trailing update through a caller-provided [rows, n] fp32 buffer.  Some hosts of
+// this library have no allocator to get that buffer from: a runtime that drives
+// the solve from inside a fixed, pre-planned memory arena (every byte of the pool
+// already assigned to tensors), or a plugin loaded into a process whose policy
+// forbids cudaMalloc after start-up.  For them the errors live in the array below,
+// which is part of the library image: every GPU that loads the library holds these
+// 8 MiB until the process exits.
+constexpr int64_t kStaticDeltaFloats = 2 * 1024 * 1024;  // 8 MiB: e.g. 16384 rows x 128 columns
+static __device__ __align__(256) float g_static_deltas[kStaticDeltaFloats];
+
+// In host code `g_static_deltas` is only a handle for the symbol, not a device
+// address; the address is looked up once per device, with that device current.
+static float* static_deltas_for_current_device(int* status) {
+  constexpr int kMaxDevices = 64;
+  static float* address[kMaxDevices] = {};
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= kMaxDevices) {
+    *status = fail(VQ_ECUDA, "vq_gptq_block_step_static: cannot identify the current device");
+    return nullptr;
+  }
+  if (address[device] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_deltas);
+    if (e != cudaSuccess || p == nullptr) {
+      *status = fail(VQ_ECUDA, "vq_gptq_block_step_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    address[device] = p;
+  }
+  *status = VQ_OK;
+  return address[device];
+}
+
+extern "C" int vq_gptq_block_step_static(float* work, float* out, const float* U, const float* salience,
+                                         int64_t rows, int64_t K, int64_t start, int64_t n, int affine,
+                                         float quant_min, float quant_max, int shrink, const VqRound* scale_round,
+                                         const VqRound* round, void* stream) {
+  VQ_REQUIRE(rows >= 0 && n > 0, "vq_gptq_block_step_static: bad block");
+  VQ_REQUIRE(rows * n <= kStaticDeltaFloats,
+             "vq_gptq_block_step_static: rows x block columns = %lld exceeds the built-in buffer of %lld values "
+             "(8 MiB); split the rows or use vq_gptq_block / vq_gptq_update with your own buffer",
+             (long long)(rows * n), (long long)kStaticDeltaFloats);
+  int status = VQ_OK;
+  float* deltas = static_deltas_for_current_device(&status);
+  if (deltas == nullptr) return status;
+  // Every value of the [rows, n] region is rewritten by the sweep before the update
+  // reads it, so nothing left over from an earlier call is ever consumed.
+  if (int e = vq_gptq_block(work, out, deltas, U, salience, rows, K, start, n, affine, quant_min, quant_max, shrink,
+                            scale_round, round, stream))
+    return e;
+  return vq_gptq_update(work, deltas, U, rows, K, start, n, stream);
+}
