@@ -7,7 +7,9 @@
 // codes: the bfloat16 scores are read once and one byte per element is written.
 // Under a causal mask the columns past the diagonal are never read (their
 // probability is exactly zero).  Every rounding step of the unfused sequence is
-// kept, so the codes match it up to the last-bit behaviour of expf.
+// kept; the exponential and the two quotients are within an ulp of the unfused ones
+// before they are rounded to bfloat16, so a code differs by one FP8 step only when such
+// a value sits on a rounding boundary (about one entry in a few thousand).
 
 #include <cuda_fp8.h>
 
@@ -43,36 +45,44 @@ softmax_quantize_kernel(const uint4* __restrict__ scores, uint2* __restrict__ ou
   for (int i = 0; i < VPL; ++i) {
     const int v = lane + 32 * i;
     const int c0 = v << 3;
-    const bool live = v < vecs && c0 < limit;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live) raw = __ldg(src + v);
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    const bool live = v < vecs && c0 < limit;  // a vector past the diagonal is neither read nor computed
+    if (live) {
+      const uint4 raw = __ldg(src + v);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float s = __uint_as_float((j & 1) ? (w[j >> 1] & 0xFFFF0000u) : (w[j >> 1] << 16));
-      s = bf16r(__fmul_rn(s, score_scale));
-      if (mrow && live) s = bf16r(__fadd_rn(s, __bfloat162float(mrow[c0 + j])));
-      if (!live || c0 + j >= limit) s = -INFINITY;
-      x[i][j] = s;
-      mx = fmaxf(mx, s);
+      for (int j = 0; j < 8; ++j) {
+        float s = __uint_as_float((j & 1) ? (w[j >> 1] & 0xFFFF0000u) : (w[j >> 1] << 16));
+        s = bf16r(__fmul_rn(s, score_scale));
+        if (mrow) s = bf16r(__fadd_rn(s, __bfloat162float(mrow[c0 + j])));
+        if (c0 + j >= limit) s = -INFINITY;
+        x[i][j] = s;
+        mx = fmaxf(mx, s);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[i][j] = -INFINITY;
     }
   }
   for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
   float sum = 0.0f;
 #pragma unroll
-  for (int i = 0; i < VPL; ++i)
+  for (int i = 0; i < VPL; ++i) {
+    const int c0 = (lane + 32 * i) << 3;
+    if (c0 < limit && (lane + 32 * i) < vecs) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      // a fully masked row (max = -inf) yields NaN, as torch.softmax does
-      const float e = expf(x[i][j] - mx);
-      x[i][j] = e;
-      sum += e;
+      for (int j = 0; j < 8; ++j) {
+        // exp(-inf) = 0 for masked entries; a fully masked row (max = -inf) yields NaN, as torch.softmax does
+        const float e = __expf(x[i][j] - mx);
+        x[i][j] = e;
+        sum += e;
+      }
     }
+  }
   for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
 
-  // Both divisions go through the reciprocal with an exact re-division near
-  // bfloat16 rounding boundaries, so they equal round_bf16(a / b).
-  const bool fast = ordinary_divisor(sum) && ordinary_divisor(sp);
+  // p = bf16(e / sum), code = fp8(bf16(p / s_p)): both quotients are taken as products
+  // with the correctly rounded reciprocal (within an ulp of the division before the
+  // bfloat16 rounding, like the exponential itself).
   const float rsum = __frcp_rn(sum), rsp = __frcp_rn(sp);
   uint2* dst = out + row * vecs;
 #pragma unroll
@@ -80,19 +90,17 @@ softmax_quantize_kernel(const uint4* __restrict__ scores, uint2* __restrict__ ou
     const int v = lane + 32 * i;
     if (v >= vecs) continue;
     uint32_t o[2] = {0u, 0u};
+    if ((v << 3) < limit) {
 #pragma unroll
-    for (int j = 0; j < 8; j += 2) {
-      float p0, p1;
-      if (fast) {
-        p0 = div_to_bf16(div_to_bf16(x[i][j], sum, rsum), sp, rsp);
-        p1 = div_to_bf16(div_to_bf16(x[i][j + 1], sum, rsum), sp, rsp);
-      } else {
-        p0 = bf16r(__fdiv_rn(bf16r(__fdiv_rn(x[i][j], sum)), sp));
-        p1 = bf16r(__fdiv_rn(bf16r(__fdiv_rn(x[i][j + 1], sum)), sp));
+      for (int j = 0; j < 8; j += 2) {
+        const float p0 = bf16r(__fmul_rn(bf16r(__fmul_rn(x[i][j], rsum)), rsp));
+        const float p1 = bf16r(__fmul_rn(bf16r(__fmul_rn(x[i][j + 1], rsum)), rsp));
+        const float2 f = make_float2(__fadd_rn(p0, 0.0f), __fadd_rn(p1, 0.0f));
+        const uint32_t q = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
+        o[j >> 2] |= q << (16 * ((j >> 1) & 1));
       }
-      const float2 f = make_float2(__fadd_rn(p0, 0.0f), __fadd_rn(p1, 0.0f));
-      const uint32_t q = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
-      o[j >> 2] |= q << (16 * ((j >> 1) & 1));
+    } else if (sum != sum) {
+      o[0] = o[1] = E4M3 ? 0x7F7F7F7Fu : 0x7E7E7E7Eu;  // NaN row
     }
     dst[v] = make_uint2(o[0], o[1]);
   }
