@@ -11,7 +11,7 @@
 // Structure: a persistent kernel, one CTA per SM, 128x256 output tiles.
 //   warp 0   : TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, 4 stages)
 //   warp 1   : MMA issuer    (one thread; tcgen05.mma 128x256x{16|32}), owns TMEM
-//   warps 2-5: epilogue      (tcgen05.ld -> alpha/bias -> global), overlapped with
+//   warps 2-9: epilogue      (tcgen05.ld -> alpha/bias -> global), overlapped with
 //              the next tile's main loop through two TMEM accumulator buffers.
 // TMA zero-fills out-of-range rows/columns, so M, N, K tails need no special
 // main-loop code; the epilogue predicates its stores.
@@ -36,8 +36,10 @@ constexpr int MMA_K_BYTES = 32;        // K extent of one tcgen05.mma in bytes (
 constexpr int A_STAGE_BYTES = BM * BK_BYTES;   // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK_BYTES;   // 32 KB
 constexpr int TMEM_COLS = 512;         // two 128x256 fp32 accumulators
-constexpr int NUM_THREADS = 192;
-constexpr size_t SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
+constexpr int NUM_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;              // two per tensor-memory lane quadrant, one per half of the tile's columns
+constexpr int EPI_STAGE_BYTES = EPI_WARPS * 32 * 128;   // per epilogue warp: 32 rows x 128 bytes of output
+constexpr size_t SMEM_BYTES = 1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + EPI_STAGE_BYTES;
 
 __device__ int g_gemm_error = 0;
 
@@ -115,6 +117,97 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t 
   }
 }
 
+// The epilogue of one warp for one tile: its 32 accumulator rows x BN columns.
+// A thread owns a row in tensor memory, which would make every 16-byte store of a
+// warp touch 32 different rows of C.  Rows are therefore staged in shared memory
+// (32 rows x 128 bytes, 16-byte units XOR-swizzled by the row so that both phases
+// are conflict-free) and written back with eight consecutive lanes covering 128
+// contiguous bytes of one row.  Unaligned outputs fall back to per-row stores.
+__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, uint32_t taddr, uint8_t* stage, int row0,
+                                                   int lane, int n0, int b, bool has_alpha, float alpha, int c_begin,
+                                                   int c_end) {
+  const int esz = p.out_dt == VQ_F32 ? 4 : 2;
+  const int64_t row_stride = p.ldc * esz;
+  uint8_t* c_batch = static_cast<uint8_t*>(p.C) + (int64_t)b * p.strideC * esz;
+  const bool staged = ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)row_stride | (uintptr_t)(p.strideC * esz)) & 15) == 0;
+  const int my_row = row0 + lane;
+  const int cols_per_round = 128 / esz;  // output columns per 128-byte staged row
+#pragma unroll 1
+  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+    uint32_t v[32];
+    tmem_ld_32x32(taddr + (uint32_t)c0, v);
+    tmem_ld_wait();
+    const int col0 = n0 + c0;
+    if (col0 >= p.N) continue;  // warp-uniform
+    if (!staged) {
+      store_chunk(p, v, c_batch + (int64_t)my_row * row_stride, my_row, col0, has_alpha, alpha);
+      continue;
+    }
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float x = __uint_as_float(v[j]);
+      if (has_alpha) x = __fmul_rn(x, alpha);
+      f[j] = x;
+    }
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) f[j] = __fadd_rn(f[j], load_param(p.bias, col0 + j, p.bias_dt));
+    }
+    // ---- phase 1: this thread's row -> shared memory ----
+    uint8_t* srow = stage + lane * 128;
+    if (esz == 4) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        *reinterpret_cast<float4*>(srow + ((u ^ (lane & 7)) << 4)) =
+            make_float4(f[4 * u], f[4 * u + 1], f[4 * u + 2], f[4 * u + 3]);
+    } else {
+      const int half = (c0 >> 5) & 1;  // a 128-byte row holds two 32-column chunks
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (p.out_dt == VQ_BF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(f[8 * u + 2 * k], f[8 * u + 2 * k + 1]);
+            w[k] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(f[8 * u + 2 * k], f[8 * u + 2 * k + 1]);
+            w[k] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      // wait for the second chunk of the row unless it lies beyond N
+      if (half == 0 && col0 + 32 < p.N) continue;
+    }
+    __syncwarp();
+    // ---- phase 2: eight lanes per row write 128 contiguous bytes ----
+    const int round_col0 = esz == 4 ? col0 : col0 - (((c0 >> 5) & 1) << 5);
+    const int unit_cols = 16 / esz;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = 4 * i + (lane >> 3);
+      const int u = lane & 7;
+      const int row = row0 + r;
+      const int col = round_col0 + u * unit_cols;
+      if (row < p.M && col < p.N) {
+        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 128 + ((u ^ (r & 7)) << 4));
+        uint8_t* dst = c_batch + (int64_t)row * row_stride + (int64_t)col * esz;
+        if (col + unit_cols <= p.N) {
+          *reinterpret_cast<uint4*>(dst) = val;
+        } else {
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(&val);
+          for (int e = 0; e < (p.N - col) * esz; ++e) dst[e] = src[e];
+        }
+      }
+    }
+    __syncwarp();
+    (void)cols_per_round;
+  }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -128,6 +221,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -146,7 +240,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[a], EPI_WARPS);  // one arrival per epilogue warp
     }
     fence_barrier_init();
   }
@@ -223,6 +317,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) are this warp's
+    const int chalf = (warp - 2) >> 2;  // which half of the tile's columns
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -235,17 +330,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // The warp must stay convergent for the .sync.aligned TMEM loads below.
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
-      const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      uint8_t* c_row = static_cast<uint8_t*>(p.C) +
-                       ((int64_t)b * p.strideC + (int64_t)row * p.ldc) * (p.out_dt == VQ_F32 ? 4 : 2);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + (uint32_t)c0, v);
-        tmem_ld_wait();
-        store_chunk(p, v, c_row, row, n_blk * BN + c0, has_alpha, alpha);
-      }
+      epilogue_warp_tile(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * BN, b,
+                         has_alpha, alpha, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -275,7 +362,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 constexpr int P_STAGES = 6;
 constexpr int P_A_BYTES = 128 * BK_BYTES;  // 16 KB
 constexpr int P_B_BYTES = 128 * BK_BYTES;  // 16 KB (half of the tile's B rows)
-constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256;
+constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256 + EPI_STAGE_BYTES;
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
@@ -290,6 +377,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* acc_empty = bars + 2 * P_STAGES + 2;    // [2] (used in the even CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -311,7 +399,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 8);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);
     }
     fence_barrier_init();
   }
@@ -386,6 +474,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else {
     // ------------------------------ epilogue (both CTAs) ----------------------
     const int quarter = warp & 3;
+    const int chalf = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -397,17 +486,9 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
-      const int row = m_blk * 2 * BM + (int)rank * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      uint8_t* c_row = static_cast<uint8_t*>(p.C) +
-                       ((int64_t)b * p.strideC + (int64_t)row * p.ldc) * (p.out_dt == VQ_F32 ? 4 : 2);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + (uint32_t)c0, v);
-        tmem_ld_wait();
-        store_chunk(p, v, c_row, row, n_blk * BN + c0, has_alpha, alpha);
-      }
+      epilogue_warp_tile(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * 2 * BM + (int)rank * BM + quarter * 32,
+                         lane, n_blk * BN, b, has_alpha, alpha, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
