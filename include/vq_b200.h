@@ -242,6 +242,37 @@ int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t rows, int64_t
                             const void* mask, int64_t mask_rows, int64_t causal_period,
                             const void* out_scale, int out_scale_dtype, int format, void* stream);
 
+/* NVFP4 operands for the block-scaled GEMM, the cast of the reference's
+ * backend/gpu/nvfp4.py (cast_nvfp4:683-739, _cast_tile:262-372): codes are e2m1,
+ * two per byte (even element in the low nibble), rows of K/2 bytes; scales are
+ * e4m3 bytes, one per 16 elements, in 512-byte tiles of 128 rows x 4 scales
+ * (byte (r%32)*16 + (r/32)*4 + s of tile row_block * K/64 + k64_block).
+ * vq_nvfp4_scale_bytes gives the size of that buffer, which the caller zeroes
+ * when rows is not a multiple of 128.  K must be a multiple of 64.
+ *
+ * vq_quantize_nvfp4 casts bfloat16 [rows, K] with the arithmetic of
+ * quantized_ops::quantize_mx (ops/quantized.py:1080-1115) for an e2m1 table,
+ * an e4m3 scale table, quant_max 6 and the given global scale (device scalar).
+ * vq_pack_nvfp4 packs that operator's own outputs (bfloat16-valued codes
+ * [rows, K], bfloat16 scales [rows, K/16]) and sets *bad_flag (device int) to 1
+ * if a value is not representable (pack_nvfp4, backend/gpu/nvfp4.py:1045-1091). */
+int64_t vq_nvfp4_scale_bytes(int64_t rows, int64_t K);
+int vq_quantize_nvfp4(const void* in, const void* global_scale, int global_scale_dtype, void* codes,
+                      void* scales, int64_t rows, int64_t K, void* stream);
+int vq_pack_nvfp4(const void* codes_in, const void* scales_in, void* codes, void* scales, int64_t rows,
+                  int64_t K, int* bad_flag, void* stream);
+
+/* NVFP4 linear on the tensor cores' native block-scaled MMA (nvfp4_linear,
+ * backend/gpu/nvfp4.py:1101-1151; numerically linear_mx, ops/quantized.py:662-723,
+ * on the same codes and scales):
+ *   C[b][m][n] = round(alpha * sum_k (A[b][m][k] sa[b][m][k/16]) (B[b][n][k] sb[b][n][k/16]) + bias[n])
+ * A [batch, M, K/2] and B [batch, N, K/2] are packed codes, sfa / sfb their scale
+ * tiles (per batch element, as above), alpha the product of the two global scales
+ * (device scalar or NULL), fp32 accumulation, one rounding to out_dtype. */
+int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int out_dtype,
+                  int64_t M, int64_t N, int64_t K, int64_t ldc, int64_t batch, int64_t strideC,
+                  const void* alpha, int alpha_dtype, const void* bias, int bias_dtype, void* stream);
+
 /* Synchronising health check for the GEMM kernels: returns VQ_ETIMEOUT if any
  * launch since the last reset gave up on a bounded barrier wait (its output is
  * then invalid).  No counterpart in the reference. */

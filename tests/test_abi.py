@@ -20,7 +20,7 @@ def _declared_symbols():
     for fn in os.listdir(os.path.join(ROOT, "include")):
         if fn.endswith(".h"):
             text = open(os.path.join(ROOT, "include", fn)).read()
-            names += re.findall(r"^(?:int|const char\*)\s+(vq_\w+)\s*\(", text, flags=re.M)
+            names += re.findall(r"^(?:int|int64_t|const char\*)\s+(vq_\w+)\s*\(", text, flags=re.M)
     return sorted(set(names))
 
 

@@ -1,0 +1,90 @@
+"""NVFP4: the fused cast and the packer reproduce quantize_mx's codes and scales bit for bit,
+and the native block-scaled GEMM matches linear_mx on the same operands."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases as C
+from oracle import gemm as OG
+from oracle import quantizers as OQ
+from oracle import tables as OT
+
+pytestmark = pytest.mark.gpu
+
+E2M1_VALUES = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+def _vb():
+    import voyager_b200
+
+    return voyager_b200
+
+
+def unpack(packed, rows, k):
+    """Decode packed codes / scale tiles back to float tensors [rows, K] and [rows, K/16]."""
+    codes = packed.codes.cpu().reshape(rows, k // 2)
+    lo, hi = codes & 0xF, codes >> 4
+    nib = torch.stack([lo, hi], -1).reshape(rows, k).long()
+    val = E2M1_VALUES[nib & 7] * torch.where(nib & 8 != 0, -1.0, 1.0)
+    sbytes = packed.scales.cpu().reshape(-1)
+    r = torch.arange(rows)[:, None]
+    kb = torch.arange(k // 16)[None, :]
+    off = ((r // 128) * (k // 64) + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
+    scale = sbytes[off].view(torch.float8_e4m3fn).float()
+    return val, scale
+
+
+def reference_quantize(x):
+    e2m1, e4m3 = OT.quantization_map("fp4_e2m1"), OT.quantization_map("fp8_e4m3")
+    t = OQ.calculate_global_scale(x, 6.0, 448.0)
+    scale, codes = OQ.quantize_mx(x, e2m1, [-1], 16, 6.0, False, e4m3, None, None, t)
+    return t, scale, codes
+
+
+@pytest.mark.parametrize("rows,k,seed", [(128, 256, 1), (200, 64, 2), (64, 1024, 3), (300, 320, 4)])
+def test_fused_cast_matches_quantize_mx(rows, k, seed):
+    vb = _vb()
+    x = C.randn(seed, rows, k, outliers=0.002)
+    x[0, :16] = 0  # an all-zero block
+    t, scale, codes = reference_quantize(x)
+    packed = vb.nvfp4.quantize_nvfp4(x.cuda(), t.cuda())
+    val, sc = unpack(packed, rows, k)
+    assert torch.equal(sc, scale.float())
+    assert torch.equal(val, codes.float())
+    repacked = vb.nvfp4.pack_nvfp4(codes.cuda(), scale.cuda())
+    val2, sc2 = unpack(repacked, rows, k)
+    assert torch.equal(sc2, scale.float()) and torch.equal(val2, codes.float())
+
+
+def test_packer_rejects_unrepresentable_values():
+    vb = _vb()
+    codes = torch.full((128, 64), 2.5, dtype=torch.bfloat16, device="cuda")
+    scale = torch.ones(128, 4, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        vb.nvfp4.pack_nvfp4(codes, scale)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (64, 48, 64), (300, 264, 320), (256, 512, 4096), (2048, 1024, 1024)])
+def test_native_gemm_matches_linear_mx(m, n, k):
+    vb = _vb()
+    x = C.randn(10 + m, m, k, outliers=0.002)
+    w = C.randn(20 + n, n, k, std=0.02)
+    tx, sx, cx = reference_quantize(x)
+    tw, sw, cw = reference_quantize(w)
+    alpha = tx * tw
+    bias = C.randn(5, n, std=0.1)
+    want = OG.linear_mx(cx, cw, bias, input_scale=sx, weight_scale=sw, block_size=16, alpha=alpha)
+    a = vb.nvfp4.quantize_nvfp4(x.cuda(), tx.cuda())
+    b = vb.nvfp4.quantize_nvfp4(w.cuda(), tw.cuda())
+    got = vb.nvfp4.nvfp4_gemm(a, b, alpha.cuda(), bias.cuda()).cpu()
+    vb.ops.gemm_status()
+    assert got.shape == want.shape and got.dtype == want.dtype
+    err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+    assert err <= 1e-2, err
+    got32 = vb.nvfp4.nvfp4_gemm(a, b, None, None, out_dtype=torch.float32).cpu()
+    da = (cx.double() * OQ.expand_blocks(sx, cx, 16).double())
+    db = (cw.double() * OQ.expand_blocks(sw, cw, 16).double())
+    ref = da @ db.T
+    err32 = float((got32.double() - ref).abs().max() / ref.abs().max())
+    assert err32 <= 1e-4, err32

@@ -11,6 +11,7 @@ from . import fp8  # noqa: F401
 from . import workloads  # noqa: F401
 from . import gptq  # noqa: F401
 from . import parallel  # noqa: F401
+from . import nvfp4  # noqa: F401
 from ._native import build  # noqa: F401
 from .formats import (  # noqa: F401
     QScheme,

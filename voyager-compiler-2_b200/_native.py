@@ -97,6 +97,10 @@ SIGNATURES = {
     "vq_amax": [_P, _I, _I64, _P, _P],
     "vq_gemm_tn": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
     "vq_gemm_status": [_I],
+    "vq_nvfp4_scale_bytes": [_I64, _I64],
+    "vq_quantize_nvfp4": [_P, _P, _I, _P, _P, _I64, _I64, _P],
+    "vq_pack_nvfp4": [_P, _P, _P, _P, _I64, _I64, _P, _P],
+    "vq_gemm_nvfp4": [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
     "vq_gptq_block": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _F, _F, _I, ctypes.POINTER(VqRound),
                       ctypes.POINTER(VqRound), _P],
     "vq_gptq_update": [_P, _P, _P, _I64, _I64, _I64, _I64, _P],
@@ -163,7 +167,7 @@ def lib():
         for name, argtypes in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
-            fn.restype = ctypes.c_int
+            fn.restype = ctypes.c_int64 if name == "vq_nvfp4_scale_bytes" else ctypes.c_int
         handle.vq_last_error.restype = ctypes.c_char_p
         handle.vq_last_error.argtypes = []
         _lib = handle

@@ -506,6 +506,176 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------
+// NVFP4 block-scaled GEMM: packed e2m1 operands (two per byte, K-contiguous), one
+// ue4m3 scale per 16 elements, multiplied by the tensor cores' native
+// kind::mxf4nvf4 MMA (K = 64 per instruction).  128x128 tiles, one CTA per SM.
+// A stage holds 256 elements of K: 128-byte operand rows (TMA, 128-byte swizzle)
+// plus four 512-byte scale tiles per operand (bulk copies).  The MMA thread
+// moves a stage's scale tiles into tensor memory (tcgen05.cp) right before it
+// issues the stage's MMAs; tcgen05 operations of one thread execute in order, so
+// the next stage's copies cannot overtake MMAs still reading the scales.
+// Tensor-memory columns: [0,256) two accumulators, [256,272) A scales,
+// [272,288) B scales.
+// ---------------------------------------------------------------------------
+constexpr int Q_BN = 128;
+constexpr int Q_STAGES = 5;
+constexpr int Q_A_BYTES = 128 * BK_BYTES;     // 16 KB
+constexpr int Q_B_BYTES = Q_BN * BK_BYTES;    // 16 KB
+constexpr int Q_SF_BYTES = 4 * 512;           // 128 rows x 16 scales
+constexpr int Q_STAGE_BYTES = Q_A_BYTES + Q_B_BYTES + 2 * Q_SF_BYTES;
+constexpr size_t Q_SMEM_BYTES = 1024 + Q_STAGES * Q_STAGE_BYTES + 256 + EPI_STAGE_BYTES;
+constexpr uint32_t Q_SFA_COL = 256, Q_SFB_COL = 272;
+
+struct ScaledOperands {
+  const uint8_t* sfa;   // scale tiles of A: [batch][M/128][K/64][512]
+  const uint8_t* sfb;   // scale tiles of B: [batch][N/128][K/64][512]
+  int64_t sfa_batch_stride, sfb_batch_stride;  // bytes
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p,
+                  ScaledOperands sf) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem_a + Q_STAGES * Q_A_BYTES;
+  uint8_t* smem_sfa = smem_b + Q_STAGES * Q_B_BYTES;
+  uint8_t* smem_sfb = smem_sfa + Q_STAGES * Q_SF_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_STAGES * Q_STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Q_STAGES;
+  uint64_t* acc_full = bars + 2 * Q_STAGES;
+  uint64_t* acc_empty = bars + 2 * Q_STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Q_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + Q_STAGES * Q_STAGE_BYTES + 256;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + Q_BN - 1) / Q_BN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n * p.batch;
+  const int k64_total = p.K / 64;               // K is a multiple of 64
+  const int k_blocks = (k64_total + 3) / 4;     // stages of 256 elements
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < Q_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], EPI_WARPS);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = (int)(tile % tiles_m);
+        const int n_blk = (int)((tile / tiles_m) % tiles_n);
+        const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+        const uint8_t* sfa_row = sf.sfa + (int64_t)b * sf.sfa_batch_stride + (int64_t)m_blk * k64_total * 512;
+        const uint8_t* sfb_row = sf.sfb + (int64_t)b * sf.sfb_batch_stride + (int64_t)n_blk * k64_total * 512;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          const int steps = min(4, k64_total - kb * 4);
+          const uint32_t sf_bytes = (uint32_t)steps * 512u;
+          mbar_arrive_expect_tx(&full_bar[stage], Q_A_BYTES + Q_B_BYTES + 2 * sf_bytes);
+          // operand rows are K/2 bytes; a stage is 128 bytes of each row
+          tma_load_3d(smem_a + stage * Q_A_BYTES, &map_a, &full_bar[stage], kb * BK_BYTES, m_blk * BM, b);
+          tma_load_3d(smem_b + stage * Q_B_BYTES, &map_b, &full_bar[stage], kb * BK_BYTES, n_blk * Q_BN, b);
+          bulk_load(smem_sfa + stage * Q_SF_BYTES, sfa_row + (int64_t)kb * 4 * 512, sf_bytes, &full_bar[stage]);
+          bulk_load(smem_sfb + stage * Q_SF_BYTES, sfb_row + (int64_t)kb * 4 * 512, sf_bytes, &full_bar[stage]);
+          if (++stage == Q_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * Q_BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const int steps = min(4, k64_total - kb * 4);
+          const uint32_t a_addr = smem_u32(smem_a + stage * Q_A_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + stage * Q_B_BYTES);
+          const uint32_t sfa_addr = smem_u32(smem_sfa + stage * Q_SF_BYTES);
+          const uint32_t sfb_addr = smem_u32(smem_sfb + stage * Q_SF_BYTES);
+          for (int k = 0; k < steps; ++k) {
+            tmem_copy_sf(tmem_base + Q_SFA_COL + 4 * k, smem_desc_sf_chunk(sfa_addr + k * 512));
+            tmem_copy_sf(tmem_base + Q_SFB_COL + 4 * k, smem_desc_sf_chunk(sfb_addr + k * 512));
+          }
+          for (int k = 0; k < steps; ++k) {
+            const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
+            const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
+            mma_nvfp4_ss(tmem_acc, da, db, p.idesc, tmem_base + Q_SFA_COL + 4 * k, tmem_base + Q_SFB_COL + 4 * k,
+                         (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit(&empty_bar[stage]);
+          if (++stage == Q_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool has_alpha = p.alpha != nullptr;
+    const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m_blk = (int)(tile % tiles_m);
+      const int n_blk = (int)((tile / tiles_m) % tiles_n);
+      const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * Q_BN) + ((uint32_t)(quarter * 32) << 16);
+      epilogue_warp_tile(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * Q_BN, b,
+                         has_alpha, alpha, chalf * (Q_BN / 2), (chalf + 1) * (Q_BN / 2));
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -637,6 +807,49 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
   gemm_tn_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
   return check_launch("gemm_tn_kernel");
+}
+
+int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int out_dtype, int64_t M,
+                  int64_t N, int64_t K, int64_t ldc, int64_t batch, int64_t strideC, const void* alpha,
+                  int alpha_dtype, const void* bias, int bias_dtype, void* stream) {
+  VQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && batch >= 0, "vq_gemm_nvfp4: negative extent");
+  if (M == 0 || N == 0 || batch == 0) return VQ_OK;
+  VQ_REQUIRE(A && B && C && sfa && sfb, "vq_gemm_nvfp4: null operand");
+  VQ_REQUIRE(K > 0 && K % 64 == 0, "vq_gemm_nvfp4: K must be a positive multiple of 64");
+  VQ_REQUIRE(out_dtype == VQ_BF16 || out_dtype == VQ_F16 || out_dtype == VQ_F32, "vq_gemm_nvfp4: bad output dtype");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(sfa) |
+               reinterpret_cast<uintptr_t>(sfb)) & 15) == 0, "vq_gemm_nvfp4: operands must be 16-byte aligned");
+  VQ_REQUIRE(ldc >= N, "vq_gemm_nvfp4: leading dimension smaller than the row");
+  VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && batch < (1ll << 31), "vq_gemm_nvfp4: extent too large");
+  const int64_t row_bytes = K / 2;
+  CUtensorMap map_a, map_b;
+  if (int e = make_operand_map(&map_a, A, VQ_BF16, 1, M, row_bytes, row_bytes, batch, M * row_bytes, BM)) return e;
+  if (int e = make_operand_map(&map_b, B, VQ_BF16, 1, N, row_bytes, row_bytes, batch, N * row_bytes, Q_BN)) return e;
+  GemmParams p{};
+  p.C = C;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.elem_bytes = 1;
+  p.ldc = ldc; p.strideC = strideC;
+  p.batch = (int)batch;
+  p.alpha = alpha; p.alpha_dt = alpha_dtype;
+  p.bias = bias; p.bias_dt = bias_dtype;
+  p.out_dt = out_dtype;
+  p.idesc = sm100::make_idesc_nvfp4(BM, Q_BN);
+  ScaledOperands sf{};
+  sf.sfa = static_cast<const uint8_t*>(sfa);
+  sf.sfb = static_cast<const uint8_t*>(sfb);
+  sf.sfa_batch_stride = ((M + 127) / 128) * (K / 64) * 512;
+  sf.sfb_batch_stride = ((N + 127) / 128) * (K / 64) * 512;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Q_SMEM_BYTES);
+    if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + Q_BN - 1) / Q_BN) * batch;
+  const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
+  gemm_nvfp4_kernel<<<grid, NUM_THREADS, Q_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p, sf);
+  return check_launch("gemm_nvfp4_kernel");
 }
 
 int vq_gemm_status(int reset) {

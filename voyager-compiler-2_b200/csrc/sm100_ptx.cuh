@@ -235,6 +235,47 @@ __device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask
       : "memory");
 }
 
+// ---- block-scaled MMA (NVFP4) -------------------------------------------------
+// Untiled bulk copy global -> shared (16-byte aligned addresses, size a multiple
+// of 16), completion counted on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// Descriptor of a 32-row x 16-byte scale-factor chunk stored as 512 contiguous bytes
+// (no swizzle; groups of 8 rows are 128 bytes apart).
+__device__ __forceinline__ uint64_t smem_desc_sf_chunk(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;          // leading byte offset (single 16-byte column)
+  d |= static_cast<uint64_t>(128 >> 4) << 32;   // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;          // descriptor version
+  return d;                                      // layout type 0: no swizzle
+}
+// Copy one scale-factor chunk (32 rows x 128 bits) into tensor memory columns
+// [taddr, taddr + 4), replicated to all four 32-lane quadrants.
+__device__ __forceinline__ void tmem_copy_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// Instruction descriptor of kind::mxf4nvf4 (e2m1 x e2m1, ue4m3 scales per 16 elements, K = 64).
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(int m, int n) {
+  return (1u << 7) | (1u << 10)                                   // A, B format: e2m1
+         | (static_cast<uint32_t>(n >> 3) << 17) | (0u << 23)     // N; scale format ue4m3
+         | (static_cast<uint32_t>(m >> 4) << 24);                 // M; scale-factor ids 0; K = 64
+}
+__device__ __forceinline__ void mma_nvfp4_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
 // Arrive on `bar` once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
