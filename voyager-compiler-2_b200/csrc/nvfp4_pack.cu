@@ -33,45 +33,54 @@ __device__ __forceinline__ int64_t scale_tile_offset(int64_t row, int64_t k64, i
   return ((row >> 7) * k64_blocks + k64) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4;
 }
 
-// One thread = 64 consecutive elements of a row = four 16-element blocks:
-// 128 bytes in, 32 bytes of codes and 4 scale bytes out.
-__global__ void __launch_bounds__(128)
+// One thread = one 16-byte vector (8 elements); two neighbouring lanes share a
+// 16-element block (amax by one shuffle) and eight lanes a 64-element group, whose
+// four scale bytes its first lane collects and writes as one word.  Loads and
+// stores of a warp are contiguous: 512 bytes in, 128 bytes of codes out.
+__global__ void __launch_bounds__(256, 4)
 quantize_nvfp4_kernel(const uint4* __restrict__ in, const void* __restrict__ global_scale, int gs_dt,
-                      uint4* __restrict__ codes, uint8_t* __restrict__ scales, int64_t rows, int64_t K) {
+                      uint32_t* __restrict__ codes, uint8_t* __restrict__ scales, int64_t rows, int64_t K) {
+  constexpr int U = 4;
   const int64_t k64_blocks = K >> 6;
-  const int64_t total = rows * k64_blocks;
+  const int64_t nvec = rows * (K >> 3);
   const float t = loadp(global_scale, 0, gs_dt);
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = idx / k64_blocks;
-    const int64_t k64 = idx - row * k64_blocks;
-    const uint4* src = in + idx * 8;
-    uint4 x[8];
+  const bool t_ordinary = ordinary_divisor(t);
+  const bool small = (nvec >> 3) < 0x7FFFFFFFll && k64_blocks < 0x7FFFFFFFll;
+  const float rcp_t = __frcp_rn(t), rcp6 = __frcp_rn(6.0f);
+  const int64_t chunk = (int64_t)blockDim.x * U;
+  for (int64_t base = (int64_t)blockIdx.x * chunk; base < nvec; base += (int64_t)gridDim.x * chunk) {
+    uint4 x[U];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] = __ldg(src + i);
-    uint32_t sbytes = 0;
-    uint32_t packed[8];
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = base + u * blockDim.x + threadIdx.x;
+      x[u] = make_uint4(0, 0, 0, 0);
+      if (v < nvec) x[u] = __ldg(in + v);
+    }
 #pragma unroll
-    for (int blk = 0; blk < 4; ++blk) {
-      const uint32_t w[8] = {x[2 * blk].x, x[2 * blk].y, x[2 * blk].z, x[2 * blk].w,
-                             x[2 * blk + 1].x, x[2 * blk + 1].y, x[2 * blk + 1].z, x[2 * blk + 1].w};
-      uint32_t m2 = 0;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) m2 = __vmaxu2(m2, w[j] & 0x7FFF7FFFu);
-      const uint32_t m = max(m2 & 0xFFFFu, m2 >> 16);
+    for (int u = 0; u < U; ++u) {
+      const int64_t v = base + u * blockDim.x + threadIdx.x;
+      const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+      uint32_t m2 = __vmaxu2(__vmaxu2(w[0] & 0x7FFF7FFFu, w[1] & 0x7FFF7FFFu),
+                             __vmaxu2(w[2] & 0x7FFF7FFFu, w[3] & 0x7FFF7FFFu));
+      uint32_t m = max(m2 & 0xFFFFu, m2 >> 16);
+      m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
       // scale = e4m3(bf16(bf16(amax / 6) / t)), replaced by 1 when it is not positive
-      float s = bf16r(__fdiv_rn(__uint_as_float(m << 16), 6.0f));
-      s = bf16r(__fdiv_rn(s, t));
+      const float amax = __uint_as_float(m << 16);
+      float s;
+      if (t_ordinary && (m >> 7) >= 1u && (m >> 7) <= 254u) {
+        s = div_to_bf16(div_to_bf16(amax, 6.0f, rcp6), t, rcp_t);  // exact quotients, no true division
+      } else {
+        s = bf16r(__fdiv_rn(bf16r(__fdiv_rn(amax, 6.0f)), t));
+      }
       uint32_t sb = (uint32_t)__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3);
       s = e4m3_to_float(sb);
       if (!(s > 0.0f)) { s = 1.0f; sb = 0x38u; }
-      sbytes |= sb << (8 * blk);
       const float es = bf16r(__fmul_rn(s, t));
       const bool ordinary = ordinary_divisor(es);
       const float rcp = __frcp_rn(es);
       uint32_t nib = 0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 4; ++j) {
         const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xFFFF0000u);
         float a, b;
         if (ordinary) {
@@ -82,14 +91,24 @@ quantize_nvfp4_kernel(const uint4* __restrict__ in, const void* __restrict__ glo
           b = bf16r(__fdiv_rn(hi, es));
         }
         const float2 f = make_float2(__fadd_rn(a, 0.0f), __fadd_rn(b, 0.0f));
-        nib |= (uint32_t)__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest) << (8 * (j & 3));
-        if ((j & 3) == 3) { packed[2 * blk + (j >> 2)] = nib; nib = 0; }
+        nib |= (uint32_t)__nv_cvt_float2_to_fp4x2(f, __NV_E2M1, cudaRoundNearest) << (8 * j);
+      }
+      // the group's four scale bytes sit in lanes 0, 2, 4, 6 of each aligned group of 8 lanes
+      const int lane8 = threadIdx.x & 7;
+      const int first = (threadIdx.x & 31) & ~7;
+      uint32_t sbytes = __shfl_sync(0xFFFFFFFFu, sb, first) | (__shfl_sync(0xFFFFFFFFu, sb, first + 2) << 8) |
+                        (__shfl_sync(0xFFFFFFFFu, sb, first + 4) << 16) | (__shfl_sync(0xFFFFFFFFu, sb, first + 6) << 24);
+      if (v < nvec) {
+        codes[v] = nib;
+        if (lane8 == 0) {
+          const int64_t g = v >> 3;  // 64-element group index
+          // 64-bit division is ~100 instructions; almost every tensor fits 32 bits
+          const int64_t row = small ? (int64_t)((uint32_t)g / (uint32_t)k64_blocks) : g / k64_blocks;
+          const int64_t k64 = g - row * k64_blocks;
+          *reinterpret_cast<uint32_t*>(scales + scale_tile_offset(row, k64, k64_blocks)) = sbytes;
+        }
       }
     }
-    uint4* dst = codes + idx * 2;
-    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    *reinterpret_cast<uint32_t*>(scales + scale_tile_offset(row, k64, k64_blocks)) = sbytes;
   }
 }
 
@@ -165,8 +184,12 @@ extern "C" int vq_quantize_nvfp4(const void* in, const void* global_scale, int g
   VQ_REQUIRE(K % 64 == 0, "vq_quantize_nvfp4: K must be a multiple of 64");
   VQ_REQUIRE(((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(codes) |
                reinterpret_cast<uintptr_t>(scales)) & 15) == 0, "vq_quantize_nvfp4: misaligned buffers");
-  quantize_nvfp4_kernel<<<grid_for_items(rows * (K / 64)), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(in), global_scale, global_scale_dtype, static_cast<uint4*>(codes),
+  const int64_t nvec = rows * (K / 8);
+  int64_t blocks = (nvec + 1023) / 1024;
+  const int64_t cap = (int64_t)kSmCount * 4;
+  const int grid = (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+  quantize_nvfp4_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(in), global_scale, global_scale_dtype, static_cast<uint32_t*>(codes),
       static_cast<uint8_t*>(scales), rows, K);
   return check_launch("quantize_nvfp4_kernel");
 }
