@@ -242,6 +242,42 @@ int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t rows, int64_t
                             const void* mask, int64_t mask_rows, int64_t causal_period,
                             const void* out_scale, int out_scale_dtype, int format, void* stream);
 
+/* FP8 casts fused with the bfloat16 operation that feeds them in a per-tensor FP8
+ * decoder layer.  The reference's converted graph runs the producer (RMSNorm,
+ * rotary embedding, SiLU * up, a transpose) as separate aten nodes and then
+ * quantized_ops::quantize (ops/quantized.py:458-515), whose FP8 byte form is
+ * backend/gpu/fp8.py:253-261; its one fused cast is the cast + transpose of
+ * backend/gpu/fp8.py:272-369.  Each entry keeps the
+ * bfloat16 roundings of the unfused sequence and writes e4m3 bytes of
+ * round_bf16(y / scale); scale holds one element of scale_dtype.  All inputs are
+ * bfloat16, contiguous and 16-byte aligned.
+ *
+ * vq_rmsnorm_quantize_fp8: y = bf16(x * rsqrt(mean(x^2) + eps) * weight), x [rows, cols],
+ *   cols a multiple of 8 and at most 8192.
+ * vq_silu_mul_quantize_fp8: y = bf16(bf16(silu(gate)) * up) over n elements (multiple of 8).
+ * vq_rope_quantize_fp8: element (t, h, j) of a [T, heads, d] activation is read at
+ *   x[t * in_stride_t + h * in_stride_h + j] and its byte written at
+ *   out[t * out_stride_t + h * out_stride_h + j] (strides in elements, multiples of 8),
+ *   so one call also moves between token-major [T, heads, d] and head-major
+ *   [heads, T, d] layouts.  cos / sin are [T, d] or both NULL (no rotation);
+ *   y = bf16(bf16(x * cos) + bf16(rotate_half(x) * sin)).  d must be a multiple of 16.
+ * vq_transpose_quantize_fp8: x [T, heads, d] -> out bytes [heads, d, T] (the value
+ *   operand of P @ V as a K-major B matrix; heads = 1 is the matrix transpose of
+ *   quantize_fp8_transpose, backend/gpu/fp8.py:342-369).  codes, if not NULL, also
+ *   receives the bytes in x's own layout; amax_bits, if not NULL, is an int32 the
+ *   caller has zeroed that is raised to the bfloat16 bit pattern of max |x| (NaN
+ *   orders above every number).  format is VQ_IN_E4M3 or VQ_IN_E5M2; no alignment
+ *   or divisibility requirement. */
+int vq_rmsnorm_quantize_fp8(const void* x, const void* weight, void* out, int64_t rows, int64_t cols, float eps,
+                            const void* scale, int scale_dtype, void* stream);
+int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* out, int64_t n, const void* scale,
+                             int scale_dtype, void* stream);
+int vq_rope_quantize_fp8(const void* x, const void* cosv, const void* sinv, void* out, int64_t T, int64_t heads,
+                         int64_t d, int64_t in_stride_t, int64_t in_stride_h, int64_t out_stride_t,
+                         int64_t out_stride_h, const void* scale, int scale_dtype, void* stream);
+int vq_transpose_quantize_fp8(const void* x, void* out, void* codes, void* amax_bits, int format, int64_t T,
+                              int64_t heads, int64_t d, const void* scale, int scale_dtype, void* stream);
+
 /* NVFP4 operands for the block-scaled GEMM, the cast of the reference's
  * backend/gpu/nvfp4.py (cast_nvfp4:683-739, _cast_tile:262-372): codes are e2m1,
  * two per byte (even element in the low nibble), rows of K/2 bytes; scales are

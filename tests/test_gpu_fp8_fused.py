@@ -1,0 +1,162 @@
+"""FP8 casts fused with their bfloat16 producer: the bytes are those of the unfused
+sequence (the producer run by torch, then the plain cast, which the oracle pins to
+the table quantizer).  Rotary embedding, transposes and layout moves are exact;
+RMSNorm and SiLU go through rsqrt / exp and may differ from torch's kernels in the
+last bfloat16 bit of a few values, so those compare code for code with a bound on
+the fraction and size of the differences."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from oracle import quantizers as OQ
+from oracle import tables as OT
+
+pytestmark = pytest.mark.gpu
+
+
+def _vb():
+    import voyager_b200
+
+    return voyager_b200
+
+
+def _decode(codes, torch_dtype=torch.float8_e4m3fn):
+    return codes.view(torch_dtype).float()
+
+
+def _close_codes(got, want, max_fraction=2e-3):
+    """Same bytes except for a small fraction that sits one FP8 step away."""
+    g, w = _decode(got), _decode(want)
+    differ = g != w
+    frac = differ.float().mean().item()
+    assert frac <= max_fraction, f"{frac:.2e} of the codes differ"
+    if differ.any():
+        step = (g[differ] - w[differ]).abs() / w[differ].abs().clamp_min(2.0 ** -9)
+        assert step.max().item() <= 0.126, f"largest difference {step.max().item():.3f} of the value"
+
+
+@pytest.mark.parametrize("rows,cols", [(7, 64), (129, 4096), (33, 1000), (5, 8192)])
+def test_rmsnorm_quantize(rows, cols):
+    vb = _vb()
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=g) * 1.7).bfloat16().cuda()
+    w = (1.0 + 0.1 * torch.randn(cols, generator=g)).bfloat16().cuda()
+    y = F.rms_norm(x, (cols,), w, 1e-5)
+    scale = (y.abs().amax() / 448.0).to(torch.bfloat16)
+    want = vb.fp8.quantize_fp8(y, scale) if cols % 16 == 0 else \
+        OQ.quantize(y.cpu(), scale.cpu(), qmap=OT.quantization_map("fp8_e4m3")).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    got = vb.fp8.rmsnorm_quantize_fp8(x, w, 1e-5, scale)
+    _close_codes(got, want)
+
+
+def test_rmsnorm_quantize_against_oracle_arithmetic():
+    """fp32 restatement of the norm on the CPU, then the oracle's table quantizer."""
+    vb = _vb()
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(64, 512, generator=g) * 3).bfloat16()
+    w = (1.0 + 0.1 * torch.randn(512, generator=g)).bfloat16()
+    xf = x.float()
+    y = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()).bfloat16()
+    scale = torch.tensor(0.011, dtype=torch.bfloat16)
+    want = OQ.quantize(y, scale, qmap=OT.quantization_map("fp8_e4m3")).to(torch.float8_e4m3fn).view(torch.uint8)
+    got = vb.fp8.rmsnorm_quantize_fp8(x.cuda(), w.cuda(), 1e-5, scale.cuda()).cpu()
+    _close_codes(got, want)
+
+
+@pytest.mark.parametrize("shape", [(3, 64), (257, 1024), (2, 5, 24)])
+def test_silu_mul_quantize(shape):
+    vb = _vb()
+    g = torch.Generator().manual_seed(sum(shape))
+    gate = (torch.randn(*shape, generator=g) * 3).bfloat16().cuda()
+    up = torch.randn(*shape, generator=g).bfloat16().cuda()
+    act = F.silu(gate) * up
+    scale = (act.abs().amax() / 448.0).to(torch.bfloat16)
+    want = OQ.quantize(act.cpu(), scale.cpu(), qmap=OT.quantization_map("fp8_e4m3")).to(torch.float8_e4m3fn).view(torch.uint8)
+    got = vb.fp8.silu_mul_quantize_fp8(gate, up, scale).cpu()
+    assert got.shape == act.shape
+    _close_codes(got, want)
+
+
+@pytest.mark.parametrize("T,heads,d", [(5, 3, 16), (64, 8, 128), (130, 4, 64)])
+def test_rope_quantize_is_exact(T, heads, d):
+    vb = _vb()
+    W = vb.workloads
+    g = torch.Generator().manual_seed(T + heads + d)
+    x = torch.randn(T, heads, d, generator=g).bfloat16().cuda()
+    shape = W.LlamaShape(hidden=heads * d, heads=heads, kv_heads=heads, head_dim=d, intermediate=64)
+    cos, sin = W.rope_tables(T, shape, "cuda")
+    y = W.apply_rope(x, cos, sin)
+    scale = (y.abs().amax() / 448.0).to(torch.bfloat16)
+    want = OQ.quantize(y.transpose(0, 1).contiguous().cpu(), scale.cpu(), qmap=OT.quantization_map("fp8_e4m3"))
+    got = vb.fp8.rope_quantize_fp8(x, cos, sin, scale).cpu()
+    assert got.shape == (heads, T, d)
+    assert torch.equal(_decode(got), want.float())
+    # without tables: a cast that only moves to the head-major layout
+    plain = vb.fp8.rope_quantize_fp8(x, None, None, scale).cpu()
+    want_plain = OQ.quantize(x.transpose(0, 1).contiguous().cpu(), scale.cpu(), qmap=OT.quantization_map("fp8_e4m3"))
+    assert torch.equal(_decode(plain), want_plain.float())
+
+
+def test_transpose_heads_quantize_is_exact():
+    vb = _vb()
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(6, 37, 32, generator=g).bfloat16().cuda()       # [heads, T, d]
+    scale = torch.tensor(0.0091, dtype=torch.bfloat16).cuda()
+    want = OQ.quantize(x.permute(1, 0, 2).reshape(37, 6 * 32).cpu(), scale.cpu(), qmap=OT.quantization_map("fp8_e4m3"))
+    got = vb.fp8.transpose_heads_quantize_fp8(x, scale).cpu()
+    assert got.shape == (37, 192)
+    assert torch.equal(_decode(got), want.float())
+
+
+@pytest.mark.parametrize("T,heads,d", [(64, 2, 64), (100, 3, 40), (7, 1, 5), (257, 2, 130)])
+def test_transpose_quantize_is_exact(T, heads, d):
+    vb = _vb()
+    g = torch.Generator().manual_seed(T * d)
+    x = torch.randn(T, heads, d, generator=g).bfloat16().cuda()
+    scale = torch.tensor(0.0123, dtype=torch.bfloat16).cuda()
+    want = OQ.quantize(x.permute(1, 2, 0).contiguous().cpu(), scale.cpu(), qmap=OT.quantization_map("fp8_e4m3"))
+    got = vb.fp8.transpose_quantize_fp8(x, scale).cpu()
+    assert got.shape == (heads, d, T)
+    assert torch.equal(_decode(got), want.float())
+
+
+@pytest.mark.parametrize("dtype,torch_dtype", [("fp8_e4m3", torch.float8_e4m3fn), ("fp8_e5m2", torch.float8_e5m2)])
+@pytest.mark.parametrize("rows,cols", [(128, 256), (75, 100), (1, 3), (300, 64)])
+def test_quantize_fp8_transpose(dtype, torch_dtype, rows, cols):
+    """codes, the transpose's codes and the amax of one matrix from one pass."""
+    vb = _vb()
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=g) * 5).bfloat16()
+    scale = torch.tensor(0.02, dtype=torch.bfloat16)
+    want = OQ.quantize(x, scale, qmap=OT.quantization_map(dtype)).float()
+    codes, transpose, amax = vb.fp8.quantize_fp8_transpose(x.cuda(), scale.cuda(), dtype)
+    assert torch.equal(_decode(codes.cpu(), torch_dtype), want)
+    assert torch.equal(_decode(transpose.cpu(), torch_dtype), want.t())
+    assert amax.dtype == torch.bfloat16 and amax.ndim == 0
+    assert torch.equal(amax.cpu(), x.abs().amax())
+
+
+def test_quantize_fp8_transpose_empty_and_nan():
+    vb = _vb()
+    scale = torch.tensor(1.0, dtype=torch.bfloat16).cuda()
+    codes, transpose, amax = vb.fp8.quantize_fp8_transpose(torch.empty(0, 8, dtype=torch.bfloat16).cuda(), scale)
+    assert codes.shape == (0, 8) and transpose.shape == (8, 0) and float(amax) == 0.0
+    x = torch.ones(4, 4, dtype=torch.bfloat16)
+    x[1, 2] = float("nan")
+    _, _, amax = vb.fp8.quantize_fp8_transpose(x.cuda(), scale)
+    assert torch.isnan(amax).item()
+
+
+def test_fused_layer_tracks_unfused_layer():
+    vb = _vb()
+    W = vb.workloads
+    shape = W.TINY
+    params = W.make_layer_params(0, shape)
+    x = W.make_hidden_states(1, 96, shape)
+    scales = W.calibrate_fp8_scales(x, params, shape)
+    layer = W.Fp8DecoderLayer({k: v.cuda() for k, v in params.items()}, {k: v.cuda() for k, v in scales.items()}, shape)
+    fused, unfused = layer.forward(x.cuda()), layer.forward_unfused(x.cuda())
+    vb.ops.gemm_status()
+    err = float((fused.double() - unfused.double()).abs().max() / unfused.double().abs().max())
+    assert err <= 2e-2, err

@@ -1,0 +1,306 @@
+// FP8 casts fused with the bfloat16 operation that produces their input.
+//
+// In a per-tensor FP8 decoder layer every quantized tensor is produced by a cheap
+// bfloat16 operation (RMSNorm, rotary embedding, SiLU * up, a head transpose) and
+// immediately cast.  Running them as separate passes writes and re-reads every
+// activation several times; here each pair is one kernel that reads the
+// bfloat16 input once and writes one byte per element, in the layout the next
+// GEMM wants.  Each kernel keeps the bfloat16 rounding steps of the unfused
+// sequence (products, sums and the normalised value are rounded to bfloat16
+// before the division by the scale), so the codes are those of the unfused
+// graph up to the last-bit behaviour of expf / rsqrtf.
+
+#include <cuda_fp8.h>
+
+#include "quantize_shared.cuh"
+
+namespace vq {
+namespace {
+
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ float lo_of(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_of(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+struct Divisor {
+  float s, rcp;
+  bool ordinary;
+};
+__device__ __forceinline__ Divisor make_divisor(const void* scale, int dt) {
+  Divisor d;
+  d.s = loadp(scale, 0, dt);
+  d.ordinary = ordinary_divisor(d.s);
+  d.rcp = __frcp_rn(d.s);
+  return d;
+}
+__device__ __forceinline__ float quot(float x, const Divisor& d) {
+  return d.ordinary ? div_to_bf16(x, d.s, d.rcp) : bf16r(__fdiv_rn(x, d.s));
+}
+template <bool E4M3>
+__device__ __forceinline__ uint32_t fp8_pair(float a, float b) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fadd_rn(a, 0.0f), __fadd_rn(b, 0.0f)), __NV_SATFINITE,
+                                            E4M3 ? __NV_E4M3 : __NV_E5M2);
+}
+
+// ---- RMSNorm + cast: one CTA per row ------------------------------------------
+// y = bf16(x * rsqrt(mean(x^2) + eps) * w) in fp32 as torch's rms_norm computes it.
+// A thread keeps its VPT vectors of the row in registers between the two phases.
+template <int VPT>
+__global__ void __launch_bounds__(256)
+rmsnorm_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ weight, uint2* __restrict__ out,
+                        int cols, float eps, const void* __restrict__ scale, int scale_dt) {
+  __shared__ float warp_sums[8];
+  const int64_t row = blockIdx.x;
+  const int vecs = cols >> 3;
+  const Divisor d = make_divisor(scale, scale_dt);
+  uint4 raw[VPT];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + blockDim.x * i;
+    raw[i] = make_uint4(0, 0, 0, 0);
+    if (v < vecs) raw[i] = __ldg(x + row * vecs + v);
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = lo_of(w[j]), b = hi_of(w[j]);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+  for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.0f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += warp_sums[w];   // same order in every thread
+  const float inv = rsqrtf(total / (float)cols + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + blockDim.x * i;
+    if (v >= vecs) continue;
+    const uint4 wv = __ldg(weight + v);
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    const uint32_t g[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = bf16r(lo_of(w[j]) * inv * lo_of(g[j]));
+      const float b = bf16r(hi_of(w[j]) * inv * hi_of(g[j]));
+      o[j >> 1] |= fp8_pair<true>(quot(a, d), quot(b, d)) << (16 * (j & 1));
+    }
+    out[row * vecs + v] = make_uint2(o[0], o[1]);
+  }
+}
+
+// ---- SiLU(gate) * up + cast ---------------------------------------------------
+__global__ void __launch_bounds__(256, 4)
+silu_mul_quantize_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint2* __restrict__ out,
+                         int64_t nvec, const void* __restrict__ scale, int scale_dt) {
+  const Divisor d = make_divisor(scale, scale_dt);
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 gv = __ldg(gate + v), uv = __ldg(up + v);
+    const uint32_t g[4] = {gv.x, gv.y, gv.z, gv.w};
+    const uint32_t u[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t o[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g0 = lo_of(g[j]), g1 = hi_of(g[j]);
+      const float s0 = bf16r(__fdividef(g0, 1.0f + __expf(-g0)));
+      const float s1 = bf16r(__fdividef(g1, 1.0f + __expf(-g1)));
+      const float a = bf16r(__fmul_rn(s0, lo_of(u[j])));
+      const float b = bf16r(__fmul_rn(s1, hi_of(u[j])));
+      o[j >> 1] |= fp8_pair<true>(quot(a, d), quot(b, d)) << (16 * (j & 1));
+    }
+    out[v] = make_uint2(o[0], o[1]);
+  }
+}
+
+// ---- rotary embedding + cast + head/token layout change ----------------------
+// Element (t, h, j) is read at x[t * in_t + h * in_h + j] and its byte written at
+// out[t * out_t + h * out_h + j]; cos/sin: [T, d] bf16 or absent (no rotation).
+// y = bf16(bf16(x * cos) + bf16(rot(x) * sin)), rot(x) = (-x[d/2:], x[:d/2]).
+__global__ void __launch_bounds__(256)
+rope_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv, const uint4* __restrict__ sinv,
+                     uint2* __restrict__ out, int T, int heads, int d, int64_t in_t, int64_t in_h, int64_t out_t,
+                     int64_t out_h, int apply_rope, const void* __restrict__ scale, int scale_dt) {
+  const Divisor dv = make_divisor(scale, scale_dt);
+  const int vpd = d >> 3;          // 8-element vectors per head row; strides are in vectors here
+  const int half = vpd >> 1;
+  const int64_t total = (int64_t)T * heads * vpd;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % vpd);
+    const int h = (int)((idx / vpd) % heads);
+    const int t = (int)(idx / ((int64_t)vpd * heads));
+    const uint4* row = x + t * in_t + h * in_h;
+    const uint4 xv = __ldg(row + v);
+    uint32_t o[2] = {0, 0};
+    const uint32_t a[4] = {xv.x, xv.y, xv.z, xv.w};
+    if (apply_rope) {
+      const uint4 pvv = __ldg(row + (v < half ? v + half : v - half));   // partner in the other half
+      const uint4 cv = __ldg(cosv + (int64_t)t * vpd + v), sv = __ldg(sinv + (int64_t)t * vpd + v);
+      const uint32_t p[4] = {pvv.x, pvv.y, pvv.z, pvv.w};
+      const uint32_t c[4] = {cv.x, cv.y, cv.z, cv.w};
+      const uint32_t s[4] = {sv.x, sv.y, sv.z, sv.w};
+      const float sign = v < half ? -1.0f : 1.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float y0 = bf16r(__fadd_rn(bf16r(__fmul_rn(lo_of(a[j]), lo_of(c[j]))),
+                                         bf16r(__fmul_rn(sign * lo_of(p[j]), lo_of(s[j])))));
+        const float y1 = bf16r(__fadd_rn(bf16r(__fmul_rn(hi_of(a[j]), hi_of(c[j]))),
+                                         bf16r(__fmul_rn(sign * hi_of(p[j]), hi_of(s[j])))));
+        o[j >> 1] |= fp8_pair<true>(quot(y0, dv), quot(y1, dv)) << (16 * (j & 1));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j >> 1] |= fp8_pair<true>(quot(lo_of(a[j]), dv), quot(hi_of(a[j]), dv)) << (16 * (j & 1));
+    }
+    out[t * out_t + h * out_h + v] = make_uint2(o[0], o[1]);
+  }
+}
+
+// ---- cast + transpose: x [T, heads, d] bf16 -> transposed fp8 [heads, d, T] ----
+// Optionally also the codes in x's own layout and the bit pattern of max |x|
+// (bfloat16 magnitudes order as their bit patterns do, NaN above all).
+template <bool E4M3>
+__global__ void __launch_bounds__(256)
+transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out, uint8_t* __restrict__ codes,
+                          int* __restrict__ amax_bits, int T, int heads, int d, const void* __restrict__ scale,
+                          int scale_dt) {
+  __shared__ __align__(16) uint8_t tile[64][64 + 4];
+  __shared__ int block_max;
+  const Divisor dv = make_divisor(scale, scale_dt);
+  const int h = blockIdx.z;
+  const int t0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
+  if (threadIdx.x == 0) block_max = 0;
+  int local_max = 0;
+  for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
+    const int tt = i >> 6, jj = i & 63;
+    uint32_t q = 0;
+    if (t0 + tt < T && j0 + jj < d) {
+      const int64_t at = ((int64_t)(t0 + tt) * heads + h) * d + j0 + jj;
+      const uint16_t raw = reinterpret_cast<const uint16_t*>(x)[at];
+      local_max = max(local_max, (int)(raw & 0x7FFFu));
+      q = fp8_pair<E4M3>(quot(__uint_as_float((uint32_t)raw << 16), dv), 0.0f) & 0xFFu;
+      if (codes != nullptr) codes[at] = (uint8_t)q;
+    }
+    tile[jj][tt] = (uint8_t)q;
+  }
+  __syncthreads();
+  if (amax_bits != nullptr) {
+    for (int off = 16; off; off >>= 1) local_max = max(local_max, __shfl_xor_sync(0xFFFFFFFFu, local_max, off));
+    if ((threadIdx.x & 31) == 0) atomicMax(&block_max, local_max);
+  }
+  const bool wide = (T & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0;
+  if (wide) {
+    for (int i = threadIdx.x; i < 64 * 16; i += blockDim.x) {
+      const int jj = i >> 4, tq = (i & 15) << 2;
+      if (t0 + tq < T && j0 + jj < d)   // T % 4 == 0: a group of four is inside or outside as a whole
+        *reinterpret_cast<uint32_t*>(out + ((int64_t)h * d + j0 + jj) * T + t0 + tq) =
+            *reinterpret_cast<const uint32_t*>(&tile[jj][tq]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
+      const int jj = i >> 6, tt = i & 63;
+      if (t0 + tt < T && j0 + jj < d) out[((int64_t)h * d + j0 + jj) * T + t0 + tt] = tile[jj][tt];
+    }
+  }
+  if (amax_bits != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) atomicMax(amax_bits, block_max);
+  }
+}
+
+inline int stream_grid(int64_t items, int threads, int per_sm) {
+  int64_t blocks = (items + threads - 1) / threads;
+  const int64_t cap = (int64_t)kSmCount * per_sm;
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+}  // namespace
+}  // namespace vq
+
+using namespace vq;
+
+extern "C" int vq_rmsnorm_quantize_fp8(const void* x, const void* weight, void* out, int64_t rows, int64_t cols,
+                                       float eps, const void* scale, int scale_dtype, void* stream) {
+  VQ_REQUIRE(rows >= 0 && cols > 0, "vq_rmsnorm_quantize_fp8: bad extent");
+  if (rows == 0) return VQ_OK;
+  VQ_REQUIRE(x && weight && out && scale, "vq_rmsnorm_quantize_fp8: null argument");
+  VQ_REQUIRE(cols % 8 == 0 && cols <= 32 * 8 * 32, "vq_rmsnorm_quantize_fp8: the row length must be a multiple of 8, at most 8192");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(out) & 7) == 0, "vq_rmsnorm_quantize_fp8: misaligned buffers");
+  const int vecs = (int)(cols / 8);
+  int threads = ((vecs + 31) / 32) * 32;
+  if (threads > 256) threads = 256;
+  const int vpt = (vecs + threads - 1) / threads;   // <= 4 for cols <= 8192
+  const unsigned grid = (unsigned)rows;
+  VQ_REQUIRE(rows < (1ll << 31), "vq_rmsnorm_quantize_fp8: too many rows");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint4* xi = static_cast<const uint4*>(x);
+  const uint4* wi = static_cast<const uint4*>(weight);
+  uint2* o = static_cast<uint2*>(out);
+  switch (vpt) {
+    case 1: rmsnorm_quantize_kernel<1><<<grid, threads, 0, st>>>(xi, wi, o, (int)cols, eps, scale, scale_dtype); break;
+    case 2: rmsnorm_quantize_kernel<2><<<grid, threads, 0, st>>>(xi, wi, o, (int)cols, eps, scale, scale_dtype); break;
+    default: rmsnorm_quantize_kernel<4><<<grid, threads, 0, st>>>(xi, wi, o, (int)cols, eps, scale, scale_dtype); break;
+  }
+  return check_launch("rmsnorm_quantize_kernel");
+}
+
+extern "C" int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* out, int64_t n, const void* scale,
+                                        int scale_dtype, void* stream) {
+  VQ_REQUIRE(n >= 0, "vq_silu_mul_quantize_fp8: negative size");
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(gate && up && out && scale, "vq_silu_mul_quantize_fp8: null argument");
+  VQ_REQUIRE(n % 8 == 0, "vq_silu_mul_quantize_fp8: the element count must be a multiple of 8");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(out) & 7) == 0, "vq_silu_mul_quantize_fp8: misaligned buffers");
+  silu_mul_quantize_kernel<<<stream_grid(n / 8, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint2*>(out), n / 8, scale,
+      scale_dtype);
+  return check_launch("silu_mul_quantize_kernel");
+}
+
+extern "C" int vq_rope_quantize_fp8(const void* x, const void* cosv, const void* sinv, void* out, int64_t T,
+                                    int64_t heads, int64_t d, int64_t in_stride_t, int64_t in_stride_h,
+                                    int64_t out_stride_t, int64_t out_stride_h, const void* scale, int scale_dtype,
+                                    void* stream) {
+  VQ_REQUIRE(T >= 0 && heads >= 0 && d > 0, "vq_rope_quantize_fp8: bad extent");
+  if (T == 0 || heads == 0) return VQ_OK;
+  VQ_REQUIRE(x && out && scale, "vq_rope_quantize_fp8: null argument");
+  VQ_REQUIRE((cosv == nullptr) == (sinv == nullptr), "vq_rope_quantize_fp8: cos and sin come together");
+  VQ_REQUIRE(d % 16 == 0, "vq_rope_quantize_fp8: head_dim must be a multiple of 16");
+  VQ_REQUIRE(((in_stride_t | in_stride_h | out_stride_t | out_stride_h) & 7) == 0 && in_stride_t >= 0 &&
+             in_stride_h >= 0 && out_stride_t >= 0 && out_stride_h >= 0,
+             "vq_rope_quantize_fp8: strides must be non-negative multiples of 8 elements");
+  VQ_REQUIRE(T < (1ll << 31) && heads < 65536 && d < 65536, "vq_rope_quantize_fp8: extent too large");
+  VQ_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0 &&
+             ((reinterpret_cast<uintptr_t>(cosv) | reinterpret_cast<uintptr_t>(sinv)) & 15) == 0,
+             "vq_rope_quantize_fp8: misaligned buffers");
+  rope_quantize_kernel<<<stream_grid(T * heads * (d / 8), 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(cosv), static_cast<const uint4*>(sinv),
+      static_cast<uint2*>(out), (int)T, (int)heads, (int)d, in_stride_t / 8, in_stride_h / 8, out_stride_t / 8,
+      out_stride_h / 8, cosv != nullptr, scale, scale_dtype);
+  return check_launch("rope_quantize_kernel");
+}
+
+extern "C" int vq_transpose_quantize_fp8(const void* x, void* out, void* codes, void* amax_bits, int format, int64_t T,
+                                         int64_t heads, int64_t d, const void* scale, int scale_dtype, void* stream) {
+  VQ_REQUIRE(T >= 0 && heads >= 0 && d >= 0, "vq_transpose_quantize_fp8: bad extent");
+  if (T == 0 || heads == 0 || d == 0) return VQ_OK;
+  VQ_REQUIRE(x && out && scale, "vq_transpose_quantize_fp8: null argument");
+  VQ_REQUIRE(format == VQ_IN_E4M3 || format == VQ_IN_E5M2, "vq_transpose_quantize_fp8: format must be e4m3 or e5m2");
+  VQ_REQUIRE(T < (1ll << 31) && heads < 65536 && d < (1 << 22), "vq_transpose_quantize_fp8: extent too large");
+  dim3 grid((unsigned)((T + 63) / 64), (unsigned)((d + 63) / 64), (unsigned)heads);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (format == VQ_IN_E4M3)
+    transpose_quantize_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(out),
+                                                          static_cast<uint8_t*>(codes), static_cast<int*>(amax_bits),
+                                                          (int)T, (int)heads, (int)d, scale, scale_dtype);
+  else
+    transpose_quantize_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(out),
+                                                           static_cast<uint8_t*>(codes), static_cast<int*>(amax_bits),
+                                                           (int)T, (int)heads, (int)d, scale, scale_dtype);
+  return check_launch("transpose_quantize_kernel");
+}

@@ -88,3 +88,95 @@ def softmax_quantize_fp8(scores: torch.Tensor, score_scale: float, out_scale: to
                                             _dtype_id(out_scale.dtype), _FORMATS[dtype], _stream()),
             "vq_softmax_quantize_fp8")
     return out
+
+
+def _scale_arg(scale: torch.Tensor) -> torch.Tensor:
+    if scale.numel() != 1:
+        raise ValueError("the fused FP8 casts take one per-tensor scale")
+    return scale if scale.dtype in _DTYPE_ID else scale.float()
+
+
+def _bf16_input(name: str, t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.bfloat16:
+        raise NotImplementedError(f"{name} takes bfloat16 input")
+    return t.contiguous()
+
+
+def rmsnorm_quantize_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 bytes of ``rms_norm(x, weight, eps) / scale`` in one pass over ``x [..., H]``."""
+    x, weight, scale = _bf16_input("rmsnorm_quantize_fp8", x), _bf16_input("rmsnorm_quantize_fp8", weight), _scale_arg(scale)
+    cols = x.shape[-1]
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    N.check(N.lib().vq_rmsnorm_quantize_fp8(x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.numel() // max(cols, 1),
+                                            cols, float(eps), scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
+            "vq_rmsnorm_quantize_fp8")
+    return out
+
+
+def silu_mul_quantize_fp8(gate: torch.Tensor, up: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 bytes of ``(silu(gate) * up) / scale`` in one pass."""
+    gate, up, scale = _bf16_input("silu_mul_quantize_fp8", gate), _bf16_input("silu_mul_quantize_fp8", up), _scale_arg(scale)
+    if gate.shape != up.shape:
+        raise ValueError("gate and up differ in shape")
+    out = torch.empty(gate.shape, dtype=torch.uint8, device=gate.device)
+    N.check(N.lib().vq_silu_mul_quantize_fp8(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(),
+                                             scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
+            "vq_silu_mul_quantize_fp8")
+    return out
+
+
+def rope_quantize_fp8(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                      scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 bytes of the rotary embedding of ``x [T, heads, d]`` (rotate-half form, ``cos`` /
+    ``sin`` ``[T, d]``; ``None`` skips the rotation), laid out head-major ``[heads, T, d]``."""
+    x, scale = _bf16_input("rope_quantize_fp8", x), _scale_arg(scale)
+    T, heads, d = x.shape
+    if cos is not None:
+        cos, sin = _bf16_input("rope_quantize_fp8", cos), _bf16_input("rope_quantize_fp8", sin)
+        if tuple(cos.shape) != (T, d) or tuple(sin.shape) != (T, d):
+            raise ValueError("cos / sin must be [T, head_dim]")
+    out = torch.empty((heads, T, d), dtype=torch.uint8, device=x.device)
+    N.check(N.lib().vq_rope_quantize_fp8(x.data_ptr(), _ptr(cos), _ptr(sin), out.data_ptr(), T, heads, d,
+                                         heads * d, d, d, T * d, scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
+            "vq_rope_quantize_fp8")
+    return out
+
+
+def transpose_heads_quantize_fp8(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """e4m3 bytes of a head-major ``x [heads, T, d] / scale`` laid out token-major ``[T, heads * d]``."""
+    x, scale = _bf16_input("transpose_heads_quantize_fp8", x), _scale_arg(scale)
+    heads, T, d = x.shape
+    out = torch.empty((T, heads * d), dtype=torch.uint8, device=x.device)
+    N.check(N.lib().vq_rope_quantize_fp8(x.data_ptr(), None, None, out.data_ptr(), T, heads, d, d, T * d,
+                                         heads * d, d, scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
+            "vq_rope_quantize_fp8")
+    return out
+
+
+def transpose_quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype: str = "fp8_e4m3") -> torch.Tensor:
+    """FP8 bytes of ``x [T, heads, d] / scale`` laid out ``[heads, d, T]``."""
+    x, scale = _bf16_input("transpose_quantize_fp8", x), _scale_arg(scale)
+    T, heads, d = x.shape
+    out = torch.empty((heads, d, T), dtype=torch.uint8, device=x.device)
+    N.check(N.lib().vq_transpose_quantize_fp8(x.data_ptr(), out.data_ptr(), None, None, _FORMATS[dtype], T, heads, d,
+                                              scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
+            "vq_transpose_quantize_fp8")
+    return out
+
+
+def quantize_fp8_transpose(input: torch.Tensor, scale: torch.Tensor, dtype: str = "fp8_e4m3"):
+    """``(codes [M, N], transpose [N, M], amax)`` of a matrix in one pass over it: the FP8 bytes
+    of ``input / scale`` in both layouts and ``amax(|input|)`` as a 0-d tensor of ``input``'s dtype
+    (reference ``backend/gpu/fp8.py:342-369``)."""
+    x, scale = _bf16_input("quantize_fp8_transpose", input), _scale_arg(scale)
+    if x.ndim != 2:
+        raise ValueError("quantize_fp8_transpose takes a matrix")
+    rows, cols = x.shape
+    codes = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    transpose = torch.empty((cols, rows), dtype=torch.uint8, device=x.device)
+    amax = torch.zeros((), dtype=torch.int32, device=x.device)
+    N.check(N.lib().vq_transpose_quantize_fp8(x.data_ptr(), transpose.data_ptr(), codes.data_ptr(), amax.data_ptr(),
+                                              _FORMATS[dtype], rows, 1, cols, scale.data_ptr(),
+                                              _dtype_id(scale.dtype), _stream()),
+            "vq_transpose_quantize_fp8")
+    return codes, transpose, amax.to(torch.int16).view(torch.bfloat16)

@@ -150,7 +150,7 @@ class Fp8DecoderLayer:
         self._rope = None
         self._mask = None
 
-    #: kernels of this package launched per forward (casts + GEMMs)
+    #: kernels of this package launched per forward (7 fused casts + softmax + 9 GEMMs)
     LAUNCHES = 7 + 1 + 9
 
     def _tables(self, T, device):
@@ -160,6 +160,32 @@ class Fp8DecoderLayer:
         return self._rope, self._mask
 
     def forward(self, x):
+        """Every FP8 cast is fused with the bfloat16 operation that produces its input."""
+        sh, s = self.shape, self.scales
+        T = x.shape[0]
+        (cos, sin), _ = self._tables(T, x.device)
+        h8 = FP8.rmsnorm_quantize_fp8(x, self.ln1, sh.eps, s["h"])
+        q = FP8.fp8_gemm(h8, self.w8["q"], self.alpha["q"]).view(T, sh.heads, sh.head_dim)
+        k = FP8.fp8_gemm(h8, self.w8["k"], self.alpha["k"]).view(T, sh.kv_heads, sh.head_dim)
+        v = FP8.fp8_gemm(h8, self.w8["v"], self.alpha["v"]).view(T, sh.kv_heads, sh.head_dim)
+        # query heads of one KV group are stacked along the rows: [kv, groups*T, d]
+        q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(sh.kv_heads, sh.groups * T, sh.head_dim)
+        k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                     # [kv, T, d]
+        vt8 = FP8.transpose_quantize_fp8(v, s["v"])                         # [kv, d, T]
+        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk)                        # [kv, groups*T, T]
+        # scale, causal mask, softmax and the FP8 cast of the probabilities in one pass
+        p8 = FP8.softmax_quantize_fp8(scores, 1.0 / math.sqrt(sh.head_dim), s["p"], causal_period=T)
+        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv)                          # [kv, groups*T, d]
+        # the cast of the context undoes the head-major layout: [kv*groups, T, d] -> [T, heads*d]
+        ctx8 = FP8.transpose_heads_quantize_fp8(ctx.view(sh.heads, T, sh.head_dim), s["ctx"])
+        x1 = x + FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"])
+        h28 = FP8.rmsnorm_quantize_fp8(x1, self.ln2, sh.eps, s["h2"])
+        act8 = FP8.silu_mul_quantize_fp8(FP8.fp8_gemm(h28, self.w8["gate"], self.alpha["gate"]),
+                                         FP8.fp8_gemm(h28, self.w8["up"], self.alpha["up"]), s["act"])
+        return x1 + FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"])
+
+    def forward_unfused(self, x):
+        """The same layer with every producer run by torch and a plain cast after it."""
         sh, s = self.shape, self.scales
         T = x.shape[0]
         (cos, sin), mask = self._tables(T, x.device)
@@ -168,13 +194,11 @@ class Fp8DecoderLayer:
         k = FP8.fp8_gemm(h8, self.w8["k"], self.alpha["k"]).view(T, sh.kv_heads, sh.head_dim)
         v = FP8.fp8_gemm(h8, self.w8["v"], self.alpha["v"]).view(T, sh.kv_heads, sh.head_dim)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
-        # query heads of one KV group are stacked along the rows: [kv, groups*T, d]
         q8 = FP8.quantize_fp8(q.view(T, sh.kv_heads, sh.groups, sh.head_dim).permute(1, 2, 0, 3)
                               .reshape(sh.kv_heads, sh.groups * T, sh.head_dim), s["q"])
         k8 = FP8.quantize_fp8(k.transpose(0, 1), s["k"])                    # [kv, T, d]
         vt8 = FP8.quantize_fp8(v.permute(1, 2, 0), s["v"])                  # [kv, d, T]
         scores = FP8.fp8_gemm(q8, k8, self.alpha_qk)                        # [kv, groups*T, T]
-        # scale, causal mask, softmax and the FP8 cast of the probabilities in one pass
         p8 = FP8.softmax_quantize_fp8(scores, 1.0 / math.sqrt(sh.head_dim), s["p"], causal_period=T)
         ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv)                          # [kv, groups*T, d]
         ctx = ctx.view(sh.kv_heads, sh.groups, T, sh.head_dim).permute(2, 0, 1, 3).reshape(T, sh.heads * sh.head_dim)
