@@ -217,6 +217,26 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
                int64_t strideB, int64_t strideC, const void* alpha, int alpha_dtype, const void* bias,
                int bias_dtype, void* stream);
 
+/* vq_gemm_tn with a richer epilogue.  alpha_cols (device [N] of alpha_cols_dtype,
+ * may be NULL) multiplies column n after alpha and before the bias: the
+ * per-output-channel scale of fp8_linear (backend/gpu/fp8.py:372-400, scale
+ * [1, N]), and what lets linears that share an input and differ in their
+ * per-tensor scales run as one GEMM.  residual (device [batch, M, N] of the
+ * output dtype with leading dimension ldr and batch stride strideR, may be NULL,
+ * must not alias C) is added after the rounding to out_dtype and the sum is
+ * rounded again, which is `x + linear(...)` of a decoder layer in one pass.
+ * epi == NULL is vq_gemm_tn. */
+typedef struct VqGemmEpilogue {
+  const void* alpha_cols;
+  int32_t alpha_cols_dtype;
+  const void* residual;
+  int64_t ldr, strideR;
+} VqGemmEpilogue;
+int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dtype, int64_t M, int64_t N,
+                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA,
+                  int64_t strideB, int64_t strideC, const void* alpha, int alpha_dtype, const void* bias,
+                  int bias_dtype, const VqGemmEpilogue* epi, void* stream);
+
 /* Real FP8 codes for the tensor-core GEMM, the cast the reference's GPU backend
  * makes before torch._scaled_mm (backend/gpu/fp8.py:253-309): out[i] is the
  * e4m3 / e5m2 byte of round_bf16(in[i] / scale), i.e. the byte encoding of the
@@ -254,14 +274,17 @@ int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t rows, int64_t
  *
  * vq_rmsnorm_quantize_fp8: y = bf16(x * rsqrt(mean(x^2) + eps) * weight), x [rows, cols],
  *   cols a multiple of 8 and at most 8192.
- * vq_silu_mul_quantize_fp8: y = bf16(bf16(silu(gate)) * up) over n elements (multiple of 8).
+ * vq_silu_mul_quantize_fp8: y = bf16(bf16(silu(gate)) * up); gate / up are [rows, cols]
+ *   with row strides ld_gate / ld_up (two halves of one merged projection's output),
+ *   out is dense; cols and the strides are multiples of 8.
  * vq_rope_quantize_fp8: element (t, h, j) of a [T, heads, d] activation is read at
  *   x[t * in_stride_t + h * in_stride_h + j] and its byte written at
  *   out[t * out_stride_t + h * out_stride_h + j] (strides in elements, multiples of 8),
  *   so one call also moves between token-major [T, heads, d] and head-major
  *   [heads, T, d] layouts.  cos / sin are [T, d] or both NULL (no rotation);
  *   y = bf16(bf16(x * cos) + bf16(rotate_half(x) * sin)).  d must be a multiple of 16.
- * vq_transpose_quantize_fp8: x [T, heads, d] -> out bytes [heads, d, T] (the value
+ * vq_transpose_quantize_fp8: x [T, heads, d] with ldx elements between consecutive t
+ *   (heads * d when dense) -> out bytes [heads, d, T] (the value
  *   operand of P @ V as a K-major B matrix; heads = 1 is the matrix transpose of
  *   quantize_fp8_transpose, backend/gpu/fp8.py:342-369).  codes, if not NULL, also
  *   receives the bytes in x's own layout; amax_bits, if not NULL, is an int32 the
@@ -270,13 +293,14 @@ int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t rows, int64_t
  *   or divisibility requirement. */
 int vq_rmsnorm_quantize_fp8(const void* x, const void* weight, void* out, int64_t rows, int64_t cols, float eps,
                             const void* scale, int scale_dtype, void* stream);
-int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* out, int64_t n, const void* scale,
-                             int scale_dtype, void* stream);
+int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
+                             int64_t ld_gate, int64_t ld_up, const void* scale, int scale_dtype, void* stream);
 int vq_rope_quantize_fp8(const void* x, const void* cosv, const void* sinv, void* out, int64_t T, int64_t heads,
                          int64_t d, int64_t in_stride_t, int64_t in_stride_h, int64_t out_stride_t,
                          int64_t out_stride_h, const void* scale, int scale_dtype, void* stream);
 int vq_transpose_quantize_fp8(const void* x, void* out, void* codes, void* amax_bits, int format, int64_t T,
-                              int64_t heads, int64_t d, const void* scale, int scale_dtype, void* stream);
+                              int64_t heads, int64_t d, int64_t ldx, const void* scale, int scale_dtype,
+                              void* stream);
 
 /* NVFP4 operands for the block-scaled GEMM, the cast of the reference's
  * backend/gpu/nvfp4.py (cast_nvfp4:683-739, _cast_tile:262-372): codes are e2m1,

@@ -66,6 +66,13 @@ class VqBlocks(ctypes.Structure):
     ]
 
 
+class VqGemmEpilogue(ctypes.Structure):
+    _fields_ = [
+        ("alpha_cols", ctypes.c_void_p), ("alpha_cols_dtype", ctypes.c_int32),
+        ("residual", ctypes.c_void_p), ("ldr", ctypes.c_int64), ("strideR", ctypes.c_int64),
+    ]
+
+
 class VqScaleRule(ctypes.Structure):
     _fields_ = [
         ("quant_max", ctypes.c_float),
@@ -96,6 +103,8 @@ SIGNATURES = {
     "vq_dequantize_mx": [_P, _P, _P, ctypes.c_int32, _P, _I, _P, _I, ctypes.POINTER(VqBroadcast), _P],
     "vq_amax": [_P, _I, _I64, _P, _P],
     "vq_gemm_tn": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
+    "vq_gemm_tn_ex": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I,
+                      ctypes.POINTER(VqGemmEpilogue), _P],
     "vq_gemm_status": [_I],
     "vq_nvfp4_scale_bytes": [_I64, _I64],
     "vq_quantize_nvfp4": [_P, _P, _I, _P, _P, _I64, _I64, _P],
@@ -110,9 +119,9 @@ SIGNATURES = {
     "vq_quantize_fp8": [_P, _P, _I, _P, _I, _I64, _I64, _P],
     "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],
     "vq_rmsnorm_quantize_fp8": [_P, _P, _P, _I64, _I64, _F, _P, _I, _P],
-    "vq_silu_mul_quantize_fp8": [_P, _P, _P, _I64, _P, _I, _P],
+    "vq_silu_mul_quantize_fp8": [_P, _P, _P, _I64, _I64, _I64, _I64, _P, _I, _P],
     "vq_rope_quantize_fp8": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P],
-    "vq_transpose_quantize_fp8": [_P, _P, _P, _P, _I, _I64, _I64, _I64, _P, _I, _P],
+    "vq_transpose_quantize_fp8": [_P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _P, _I, _P],
 }
 IN_BF16, IN_F16, IN_E4M3, IN_E5M2 = range(4)
 

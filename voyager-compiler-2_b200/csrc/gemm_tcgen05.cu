@@ -53,6 +53,10 @@ struct GemmParams {
   int alpha_dt;
   const void* bias;
   int bias_dt;
+  const void* alpha_cols;   // per-column factor [N], or null
+  int alpha_cols_dt;
+  const void* residual;     // [batch, M, N] of the output dtype added after the first rounding, or null
+  int64_t ldr, strideR;
   int out_dt;
   uint32_t idesc;
   int kind_f8;
@@ -64,31 +68,69 @@ __device__ __forceinline__ float load_param(const void* p, int64_t i, int dt) {
   return __half2float(static_cast<const __half*>(p)[i]);
 }
 
+// alpha, the per-column factor and the bias for 32 consecutive accumulator columns.
+// Every lane of a warp works on the same 32 columns (one row each): lane j fetches
+// column j's factor and bias with one coalesced load and the warp shares them by
+// shuffle.  All 32 lanes must call this together.
+__device__ __forceinline__ void scale_chunk(const GemmParams& p, const uint32_t (&v)[32], float (&f)[32], int col0,
+                                            bool has_alpha, float alpha) {
+  const int lane = threadIdx.x & 31;
+  float col_factor = 1.0f, col_bias = 0.0f;
+  if (p.alpha_cols != nullptr && col0 + lane < p.N) col_factor = load_param(p.alpha_cols, col0 + lane, p.alpha_cols_dt);
+  if (p.bias != nullptr && col0 + lane < p.N) col_bias = load_param(p.bias, col0 + lane, p.bias_dt);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float x = __uint_as_float(v[j]);
+    if (has_alpha) x = __fmul_rn(x, alpha);
+    f[j] = x;
+  }
+  if (p.alpha_cols != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(f[j], __shfl_sync(0xFFFFFFFFu, col_factor, j));
+  }
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __fadd_rn(f[j], __shfl_sync(0xFFFFFFFFu, col_bias, j));
+  }
+}
+
+// One rounded output element plus one residual element, rounded again (x + linear(...)).
+__device__ __forceinline__ uint16_t add_residual16(uint16_t y, uint16_t r, int out_dt) {
+  if (out_dt == VQ_BF16) {
+    const float s = __fadd_rn(__uint_as_float((uint32_t)y << 16), __uint_as_float((uint32_t)r << 16));
+    return __bfloat16_as_ushort(__float2bfloat16_rn(s));
+  }
+  const float s = __fadd_rn(__half2float(__ushort_as_half(y)), __half2float(__ushort_as_half(r)));
+  return __half_as_ushort(__float2half_rn(s));
+}
+__device__ __forceinline__ uint32_t add_residual_word(uint32_t y, uint32_t r, int out_dt) {
+  if (out_dt == VQ_F32) return __float_as_uint(__fadd_rn(__uint_as_float(y), __uint_as_float(r)));
+  return (uint32_t)add_residual16((uint16_t)(y & 0xFFFFu), (uint16_t)(r & 0xFFFFu), out_dt) |
+         ((uint32_t)add_residual16((uint16_t)(y >> 16), (uint16_t)(r >> 16), out_dt) << 16);
+}
+
 // Epilogue for 32 consecutive accumulator columns of one output row:
 // alpha, bias, one rounding, 16-byte stores where the row allows.
-__device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t (&v)[32], uint8_t* c_row, int row,
-                                            int col0, bool has_alpha, float alpha) {
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t (&v)[32], uint8_t* c_row,
+                                            const uint8_t* r_row, int row, int col0, bool has_alpha, float alpha) {
+  float f[32];
+  scale_chunk(p, v, f, col0, has_alpha, alpha);   // warp-wide: before the per-row guard
   if (row < p.M && col0 < p.N) {
-    float f[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float x = __uint_as_float(v[j]);
-      if (has_alpha) x = __fmul_rn(x, alpha);
-      f[j] = x;
-    }
-    if (p.bias != nullptr) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) f[j] = __fadd_rn(f[j], load_param(p.bias, col0 + j, p.bias_dt));
-    }
     const bool full = (col0 + 32 <= p.N);
     if (p.out_dt == VQ_F32) {
       float* dst = reinterpret_cast<float*>(c_row) + col0;
+      if (r_row != nullptr) {
+        const float* res = reinterpret_cast<const float*>(r_row) + col0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) f[j] = __fadd_rn(f[j], res[j]);
+      }
       if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
       } else {
+#pragma unroll
         for (int j = 0; j < 32; ++j)
           if (col0 + j < p.N) dst[j] = f[j];
       }
@@ -105,11 +147,21 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t 
         }
       }
       uint16_t* dst = reinterpret_cast<uint16_t*>(c_row) + col0;
+      if (r_row != nullptr) {
+        const uint16_t* res = reinterpret_cast<const uint16_t*>(r_row) + col0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < p.N) {
+            const uint16_t y = add_residual16((uint16_t)(packed[j >> 1] >> (16 * (j & 1))), res[j], p.out_dt);
+            packed[j >> 1] = (packed[j >> 1] & ~(0xFFFFu << (16 * (j & 1)))) | ((uint32_t)y << (16 * (j & 1)));
+          }
+      }
       if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
         for (int j = 0; j < 16; j += 4)
           *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
       } else {
+#pragma unroll
         for (int j = 0; j < 32; ++j)
           if (col0 + j < p.N) dst[j] = (uint16_t)(packed[j >> 1] >> (16 * (j & 1)));
       }
@@ -117,99 +169,224 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t 
   }
 }
 
-// The epilogue of one warp for one tile: its 32 accumulator rows x BN columns.
-// A thread owns a row in tensor memory, which would make every 16-byte store of a
-// warp touch 32 different rows of C.  Rows are therefore staged in shared memory
-// (32 rows x 128 bytes, 16-byte units XOR-swizzled by the row so that both phases
-// are conflict-free) and written back with eight consecutive lanes covering 128
-// contiguous bytes of one row.  Unaligned outputs fall back to per-row stores.
-__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, uint32_t taddr, uint8_t* stage, int row0,
-                                                   int lane, int n0, int b, bool has_alpha, float alpha, int c_begin,
-                                                   int c_end) {
+// Ask L2 for the residual values one warp's part of a tile will add (32 rows x
+// [c_begin, c_end) columns), while the tile's accumulator is still being computed.
+__device__ __forceinline__ void prefetch_residual(const GemmParams& p, int row0, int lane, int n0, int b, int c_begin,
+                                                  int c_end) {
+  if (p.residual == nullptr) return;
   const int esz = p.out_dt == VQ_F32 ? 4 : 2;
-  const int64_t row_stride = p.ldc * esz;
-  uint8_t* c_batch = static_cast<uint8_t*>(p.C) + (int64_t)b * p.strideC * esz;
-  const bool staged = ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)row_stride | (uintptr_t)(p.strideC * esz)) & 15) == 0;
+  const int row = row0 + lane;
+  if (row >= p.M) return;
+  const uint8_t* base = static_cast<const uint8_t*>(p.residual) +
+                        ((int64_t)b * p.strideR + (int64_t)row * p.ldr) * esz;
+  const int64_t row_bytes = (int64_t)p.N * esz;
+  for (int64_t off = (int64_t)(n0 + c_begin) * esz; off < (int64_t)(n0 + c_end) * esz && off < row_bytes; off += 128)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+}
+
+template <int OUT_DT>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b) {
+  if (OUT_DT == VQ_BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Phase 1 of the staged epilogue: this thread's 32 scaled values of one row go to
+// its row of the warp's staging buffer (16-byte units XOR-swizzled by the row).
+template <int OUT_DT>
+__device__ __forceinline__ void stage_chunk(const GemmParams& p, const uint32_t (&v)[32], uint8_t* srow, int lane,
+                                            int col0, int half, bool has_alpha, float alpha) {
+  float f[32];
+  scale_chunk(p, v, f, col0, has_alpha, alpha);
+  if (OUT_DT == VQ_F32) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      *reinterpret_cast<float4*>(srow + ((u ^ (lane & 7)) << 4)) =
+          make_float4(f[4 * u], f[4 * u + 1], f[4 * u + 2], f[4 * u + 3]);
+  } else {
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (lane & 7)) << 4)) =
+          make_uint4(pack_pair<OUT_DT>(f[8 * u], f[8 * u + 1]), pack_pair<OUT_DT>(f[8 * u + 2], f[8 * u + 3]),
+                     pack_pair<OUT_DT>(f[8 * u + 4], f[8 * u + 5]), pack_pair<OUT_DT>(f[8 * u + 6], f[8 * u + 7]));
+  }
+}
+
+// Phase 2: the staged 32 rows x 128 bytes go to C, eight consecutive lanes writing
+// 128 contiguous bytes of one row.  `interior` (warp-uniform): every row and column
+// of the block lies inside C, so no element needs a bounds check.
+template <int OUT_DT>
+__device__ __forceinline__ void flush_stage(const GemmParams& p, const uint8_t* stage, uint8_t* c_batch,
+                                            const uint8_t* r_batch, int64_t row_stride, int64_t r_row_stride,
+                                            bool r_wide, int row0, int lane, int round_col0, bool interior) {
+  constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
+  constexpr int UNIT_COLS = 16 / ESZ;
+  const int u = lane & 7;
+  const int rq = lane >> 3;
+  const int col = round_col0 + u * UNIT_COLS;
+  if (interior && r_batch == nullptr) {
+    uint8_t* dst = c_batch + (int64_t)(row0 + rq) * row_stride + (int64_t)col * ESZ;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = 4 * i + rq;
+      *reinterpret_cast<uint4*>(dst + (int64_t)(4 * i) * row_stride) =
+          *reinterpret_cast<const uint4*>(stage + r * 128 + ((u ^ (r & 7)) << 4));
+    }
+    return;
+  }
+  // general path: bounds-checked, with the residual.  Two groups of four rows per lane; a group's
+  // residual loads are all in flight before its first store (coalesced like the stores).
+#pragma unroll 1
+  for (int i0 = 0; i0 < 8; i0 += 4) {
+    uint4 rv[4];
+    if (r_batch != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = row0 + 4 * (i0 + i) + rq;
+        rv[i] = make_uint4(0, 0, 0, 0);
+        if (row < p.M && col < p.N) {
+          const uint8_t* rsrc = r_batch + (int64_t)row * r_row_stride + (int64_t)col * ESZ;
+          if (r_wide && col + UNIT_COLS <= p.N) {
+            rv[i] = *reinterpret_cast<const uint4*>(rsrc);
+          } else {
+            uint32_t w[4] = {0, 0, 0, 0};
+            const int valid = p.N - col < UNIT_COLS ? p.N - col : UNIT_COLS;
+            if (ESZ == 4) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (e < valid) w[e] = reinterpret_cast<const uint32_t*>(rsrc)[e];
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (e < valid) w[e >> 1] |= (uint32_t)reinterpret_cast<const uint16_t*>(rsrc)[e] << (16 * (e & 1));
+            }
+            rv[i] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * (i0 + i) + rq;
+      const int row = row0 + r;
+      if (row < p.M && col < p.N) {
+        uint4 val = *reinterpret_cast<const uint4*>(stage + r * 128 + ((u ^ (r & 7)) << 4));
+        uint8_t* dst = c_batch + (int64_t)row * row_stride + (int64_t)col * ESZ;
+        if (r_batch != nullptr) {
+          val.x = add_residual_word(val.x, rv[i].x, OUT_DT);
+          val.y = add_residual_word(val.y, rv[i].y, OUT_DT);
+          val.z = add_residual_word(val.z, rv[i].z, OUT_DT);
+          val.w = add_residual_word(val.w, rv[i].w, OUT_DT);
+        }
+        if (col + UNIT_COLS <= p.N) {
+          *reinterpret_cast<uint4*>(dst) = val;
+        } else {
+          const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+          const int valid = p.N - col;
+          if (ESZ == 4) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (e < valid) reinterpret_cast<uint32_t*>(dst)[e] = w[e];
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              if (e < valid) reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(w[e >> 1] >> (16 * (e & 1)));
+          }
+        }
+      }
+    }
+  }
+}
+
+// The epilogue of one warp for one tile: its 32 accumulator rows x [c_begin, c_end)
+// columns.  A thread owns a row in tensor memory, which would make every 16-byte
+// store of a warp touch 32 different rows of C.  Rows are therefore staged in shared
+// memory (32 rows x 128 bytes, conflict-free in both phases) and written back with
+// eight consecutive lanes covering 128 contiguous bytes of one row.  The tensor-memory
+// load of the next 32 columns is in flight while the current ones are processed.
+// Outputs that are not 16-byte aligned fall back to per-row stores.
+// Epilogue for an output that is not 16-byte aligned: every thread stores its own row.
+__device__ __noinline__ void epilogue_warp_tile_unstaged(const GemmParams& p, uint32_t taddr, int row0, int lane, int n0,
+                                                         int b, bool has_alpha, float alpha, int c_begin, int c_end) {
+  const int esz = p.out_dt == VQ_F32 ? 4 : 2;
   const int my_row = row0 + lane;
-  const int cols_per_round = 128 / esz;  // output columns per 128-byte staged row
+  uint8_t* c_row = static_cast<uint8_t*>(p.C) + ((int64_t)b * p.strideC + (int64_t)my_row * p.ldc) * esz;
+  const uint8_t* r_row = p.residual == nullptr
+                             ? nullptr
+                             : static_cast<const uint8_t*>(p.residual) + ((int64_t)b * p.strideR + (int64_t)my_row * p.ldr) * esz;
 #pragma unroll 1
   for (int c0 = c_begin; c0 < c_end; c0 += 32) {
     uint32_t v[32];
     tmem_ld_32x32(taddr + (uint32_t)c0, v);
     tmem_ld_wait();
-    const int col0 = n0 + c0;
-    if (col0 >= p.N) continue;  // warp-uniform
-    if (!staged) {
-      store_chunk(p, v, c_batch + (int64_t)my_row * row_stride, my_row, col0, has_alpha, alpha);
-      continue;
-    }
-    float f[32];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float x = __uint_as_float(v[j]);
-      if (has_alpha) x = __fmul_rn(x, alpha);
-      f[j] = x;
-    }
-    if (p.bias != nullptr) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) f[j] = __fadd_rn(f[j], load_param(p.bias, col0 + j, p.bias_dt));
-    }
-    // ---- phase 1: this thread's row -> shared memory ----
-    uint8_t* srow = stage + lane * 128;
-    if (esz == 4) {
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        *reinterpret_cast<float4*>(srow + ((u ^ (lane & 7)) << 4)) =
-            make_float4(f[4 * u], f[4 * u + 1], f[4 * u + 2], f[4 * u + 3]);
-    } else {
-      const int half = (c0 >> 5) & 1;  // a 128-byte row holds two 32-column chunks
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint32_t w[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          if (p.out_dt == VQ_BF16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(f[8 * u + 2 * k], f[8 * u + 2 * k + 1]);
-            w[k] = *reinterpret_cast<uint32_t*>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(f[8 * u + 2 * k], f[8 * u + 2 * k + 1]);
-            w[k] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        }
-        *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-      // wait for the second chunk of the row unless it lies beyond N
-      if (half == 0 && col0 + 32 < p.N) continue;
-    }
-    __syncwarp();
-    // ---- phase 2: eight lanes per row write 128 contiguous bytes ----
-    const int round_col0 = esz == 4 ? col0 : col0 - (((c0 >> 5) & 1) << 5);
-    const int unit_cols = 16 / esz;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int r = 4 * i + (lane >> 3);
-      const int u = lane & 7;
-      const int row = row0 + r;
-      const int col = round_col0 + u * unit_cols;
-      if (row < p.M && col < p.N) {
-        const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 128 + ((u ^ (r & 7)) << 4));
-        uint8_t* dst = c_batch + (int64_t)row * row_stride + (int64_t)col * esz;
-        if (col + unit_cols <= p.N) {
-          *reinterpret_cast<uint4*>(dst) = val;
-        } else {
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(&val);
-          for (int e = 0; e < (p.N - col) * esz; ++e) dst[e] = src[e];
-        }
-      }
-    }
-    __syncwarp();
-    (void)cols_per_round;
+    if (n0 + c0 >= p.N) continue;  // warp-uniform
+    store_chunk(p, v, c_row, r_row, my_row, n0 + c0, has_alpha, alpha);
   }
 }
 
+template <int OUT_DT>
+__device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, uint32_t taddr, uint8_t* stage, int row0,
+                                                     int lane, int n0, int b, bool has_alpha, float alpha, int c_begin,
+                                                     int c_end) {
+  constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
+  constexpr int ROUND_COLS = 128 / ESZ;   // output columns per 128-byte staged row
+  const int64_t row_stride = p.ldc * ESZ;
+  uint8_t* c_batch = static_cast<uint8_t*>(p.C) + (int64_t)b * p.strideC * ESZ;
+  const int64_t r_row_stride = p.ldr * ESZ;
+  const uint8_t* r_batch = p.residual == nullptr ? nullptr
+                                                 : static_cast<const uint8_t*>(p.residual) + (int64_t)b * p.strideR * ESZ;
+  const bool r_wide = ((reinterpret_cast<uintptr_t>(p.residual) | (uintptr_t)r_row_stride | (uintptr_t)(p.strideR * ESZ)) & 15) == 0;
+  const bool rows_inside = row0 + 32 <= p.M;
+  uint8_t* srow = stage + lane * 128;
+
+  // one 32-column chunk: scale, stage, and flush when its 128-byte round is complete
+  auto process = [&](const uint32_t (&v)[32], int c0) {
+    const int col0 = n0 + c0;
+    if (col0 >= p.N) return;  // warp-uniform
+    const int half = ESZ == 4 ? 0 : (c0 >> 5) & 1;   // a 128-byte row holds two 32-column chunks of 16-bit values
+    stage_chunk<OUT_DT>(p, v, srow, lane, col0, half, has_alpha, alpha);
+    if (ESZ != 4 && half == 0 && col0 + 32 < p.N && c0 + 32 < c_end) return;  // the round's second chunk follows
+    __syncwarp();
+    const int round_col0 = col0 - half * 32;
+    flush_stage<OUT_DT>(p, stage, c_batch, r_batch, row_stride, r_row_stride, r_wide, row0, lane, round_col0,
+                        rows_inside && round_col0 + ROUND_COLS <= p.N);
+    __syncwarp();
+  };
+
+  uint32_t va[32], vb[32];
+  tmem_ld_32x32(taddr + (uint32_t)c_begin, va);
+#pragma unroll 1
+  for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+    const bool has_b = c0 + 32 < c_end;   // warp-uniform
+    tmem_ld_wait();
+    if (has_b) tmem_ld_32x32(taddr + (uint32_t)(c0 + 32), vb);
+    process(va, c0);
+    if (has_b) {
+      tmem_ld_wait();
+      if (c0 + 64 < c_end) tmem_ld_32x32(taddr + (uint32_t)(c0 + 64), va);
+      process(vb, c0 + 32);
+    }
+  }
+}
+
+template <int OUT_DT>
+__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, uint32_t taddr, uint8_t* stage, int row0,
+                                                   int lane, int n0, int b, bool has_alpha, float alpha, int c_begin,
+                                                   int c_end) {
+  constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
+  if (((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * ESZ) | (uintptr_t)(p.strideC * ESZ)) & 15) != 0) {
+    epilogue_warp_tile_unstaged(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
+    return;
+  }
+  epilogue_warp_tile_t<OUT_DT>(p, taddr, stage, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
+}
+
+template <int OUT_DT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -327,11 +504,12 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int m_blk = (int)(tile % tiles_m);
       const int n_blk = (int)((tile / tiles_m) % tiles_n);
       const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      prefetch_residual(p, m_blk * BM + quarter * 32, lane, n_blk * BN, b, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       // The warp must stay convergent for the .sync.aligned TMEM loads below.
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * BN, b,
+      epilogue_warp_tile<OUT_DT>(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * BN, b,
                          has_alpha, alpha, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -364,8 +542,9 @@ constexpr int P_A_BYTES = 128 * BK_BYTES;  // 16 KB
 constexpr int P_B_BYTES = 128 * BK_BYTES;  // 16 KB (half of the tile's B rows)
 constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256 + EPI_STAGE_BYTES;
 
+template <int OUT_DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
@@ -484,10 +663,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m_blk = (int)(tile % tiles_m);
       const int n_blk = (int)((tile / tiles_m) % tiles_n);
       const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      prefetch_residual(p, m_blk * 2 * BM + (int)rank * BM + quarter * 32, lane, n_blk * BN, b, chalf * (BN / 2),
+                        (chalf + 1) * (BN / 2));
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * 2 * BM + (int)rank * BM + quarter * 32,
+      epilogue_warp_tile<OUT_DT>(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * 2 * BM + (int)rank * BM + quarter * 32,
                          lane, n_blk * BN, b, has_alpha, alpha, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -532,8 +713,9 @@ struct ScaledOperands {
   int64_t sfa_batch_stride, sfb_batch_stride;  // bytes
 };
 
+template <int OUT_DT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p,
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ GemmParams p,
                   ScaledOperands sf) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -658,7 +840,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * Q_BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * Q_BN, b,
+      epilogue_warp_tile<OUT_DT>(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * Q_BN, b,
                          has_alpha, alpha, chalf * (Q_BN / 2), (chalf + 1) * (Q_BN / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -712,6 +894,18 @@ int make_operand_map(CUtensorMap* map, const void* base, int elem_kind, int elem
   return VQ_OK;
 }
 
+// Kernel instantiation for an output dtype (the epilogue is compiled per dtype).
+#define VQ_FOR_OUT_DTYPE(dt, KERNEL) ((dt) == VQ_BF16 ? KERNEL<VQ_BF16> : (dt) == VQ_F16 ? KERNEL<VQ_F16> : KERNEL<VQ_F32>)
+
+template <typename Kernel>
+int allow_big_smem(Kernel k_bf16, Kernel k_f16, Kernel k_f32, size_t bytes) {
+  for (Kernel k : {k_bf16, k_f16, k_f32}) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  }
+  return VQ_OK;
+}
+
 }  // namespace
 }  // namespace vq
 
@@ -723,6 +917,14 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
                int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA, int64_t strideB,
                int64_t strideC, const void* alpha, int alpha_dtype, const void* bias, int bias_dtype,
                void* stream) {
+  return vq_gemm_tn_ex(A, B, C, in_kind, out_dtype, M, N, K, lda, ldb, ldc, batch, strideA, strideB, strideC, alpha,
+                       alpha_dtype, bias, bias_dtype, nullptr, stream);
+}
+
+int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dtype, int64_t M, int64_t N, int64_t K,
+                  int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA, int64_t strideB,
+                  int64_t strideC, const void* alpha, int alpha_dtype, const void* bias, int bias_dtype,
+                  const VqGemmEpilogue* epi, void* stream) {
   VQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && batch >= 0, "vq_gemm_tn: negative extent");
   if (M == 0 || N == 0 || batch == 0) return VQ_OK;
   VQ_REQUIRE(A && B && C, "vq_gemm_tn: null operand");
@@ -749,6 +951,17 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
   p.bias = bias; p.bias_dt = bias_dtype;
   p.out_dt = out_dtype;
   p.kind_f8 = eb == 1;
+  if (epi != nullptr) {
+    if (epi->alpha_cols != nullptr) {
+      VQ_REQUIRE(epi->alpha_cols_dtype >= VQ_BF16 && epi->alpha_cols_dtype <= VQ_F32, "vq_gemm_tn_ex: bad alpha_cols dtype");
+      p.alpha_cols = epi->alpha_cols; p.alpha_cols_dt = epi->alpha_cols_dtype;
+    }
+    if (epi->residual != nullptr) {
+      VQ_REQUIRE(epi->ldr >= N, "vq_gemm_tn_ex: residual leading dimension smaller than the row");
+      VQ_REQUIRE(epi->residual != C, "vq_gemm_tn_ex: the residual must not alias the output");
+      p.residual = epi->residual; p.ldr = epi->ldr; p.strideR = epi->strideR;
+    }
+  }
   const int fmt = in_kind == VQ_IN_BF16 ? 1 : in_kind == VQ_IN_F16 ? 0 : in_kind == VQ_IN_E4M3 ? 0 : 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
@@ -760,9 +973,10 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
     const char* env = getenv("VQ_GEMM_PAIR");
     pair_mode = (env && env[0] == '0') ? 0 : 1;
     if (pair_mode) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)P_SMEM_BYTES);
-      if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      if (int rc = allow_big_smem(gemm_tn_pair_kernel<VQ_BF16>, gemm_tn_pair_kernel<VQ_F16>,
+                                  gemm_tn_pair_kernel<VQ_F32>, P_SMEM_BYTES))
+        return rc;
+      cudaError_t e;
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(kSmCount, 1, 1);
       cfg.blockDim = dim3(NUM_THREADS, 1, 1);
@@ -773,7 +987,7 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
       cfg.attrs = &attr;
       cfg.numAttrs = 1;
       int n = 0;
-      e = cudaOccupancyMaxActiveClusters(&n, gemm_tn_pair_kernel, &cfg);
+      e = cudaOccupancyMaxActiveClusters(&n, gemm_tn_pair_kernel<VQ_BF16>, &cfg);
       if (e != cudaSuccess || n < 1) {
         (void)cudaGetLastError();
         pair_mode = 0;
@@ -789,7 +1003,7 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
     p.idesc = sm100::make_idesc(2 * BM, BN, fmt, fmt, 0, 0);
     const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
     const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
-    gemm_tn_pair_kernel<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, p);
+    VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_pair_kernel)<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, p);
     return check_launch("gemm_tn_pair_kernel");
   }
 
@@ -799,13 +1013,13 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
   p.idesc = sm100::make_idesc(BM, BN, fmt, fmt, 0, 0);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-    if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    if (int rc = allow_big_smem(gemm_tn_kernel<VQ_BF16>, gemm_tn_kernel<VQ_F16>, gemm_tn_kernel<VQ_F32>, SMEM_BYTES))
+      return rc;
     configured = true;
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
-  gemm_tn_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+  VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_kernel)<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
   return check_launch("gemm_tn_kernel");
 }
 
@@ -842,13 +1056,14 @@ int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb
   sf.sfb_batch_stride = ((N + 127) / 128) * (K / 64) * 512;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Q_SMEM_BYTES);
-    if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    if (int rc = allow_big_smem(gemm_nvfp4_kernel<VQ_BF16>, gemm_nvfp4_kernel<VQ_F16>, gemm_nvfp4_kernel<VQ_F32>,
+                                Q_SMEM_BYTES))
+      return rc;
     configured = true;
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + Q_BN - 1) / Q_BN) * batch;
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
-  gemm_nvfp4_kernel<<<grid, NUM_THREADS, Q_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p, sf);
+  VQ_FOR_OUT_DTYPE(out_dtype, gemm_nvfp4_kernel)<<<grid, NUM_THREADS, Q_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p, sf);
   return check_launch("gemm_nvfp4_kernel");
 }
 

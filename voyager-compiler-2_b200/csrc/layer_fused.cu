@@ -92,12 +92,25 @@ rmsnorm_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w
 }
 
 // ---- SiLU(gate) * up + cast ---------------------------------------------------
+// gate / up: [rows, cols] with row strides ld_gate / ld_up (in 8-element vectors here).
 __global__ void __launch_bounds__(256, 4)
 silu_mul_quantize_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint2* __restrict__ out,
-                         int64_t nvec, const void* __restrict__ scale, int scale_dt) {
+                         int64_t nvec, int vecs_per_row, int64_t ld_gate, int64_t ld_up,
+                         const void* __restrict__ scale, int scale_dt) {
   const Divisor d = make_divisor(scale, scale_dt);
-  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
-    const uint4 gv = __ldg(gate + v), uv = __ldg(up + v);
+  // (row, column) of this thread's vector, advanced by the grid stride without further divisions
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t r = first / vecs_per_row;
+  int c = (int)(first - r * vecs_per_row);
+  const int64_t dr = stride / vecs_per_row;
+  const int dc = (int)(stride - dr * vecs_per_row);
+  for (int64_t v = first; v < nvec; v += stride) {
+    const int64_t gi = r * ld_gate + c, ui = r * ld_up + c;
+    r += dr;
+    c += dc;
+    if (c >= vecs_per_row) { c -= vecs_per_row; ++r; }
+    const uint4 gv = __ldg(gate + gi), uv = __ldg(up + ui);
     const uint32_t g[4] = {gv.x, gv.y, gv.z, gv.w};
     const uint32_t u[4] = {uv.x, uv.y, uv.z, uv.w};
     uint32_t o[2] = {0, 0};
@@ -165,8 +178,8 @@ rope_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv
 template <bool E4M3>
 __global__ void __launch_bounds__(256)
 transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out, uint8_t* __restrict__ codes,
-                          int* __restrict__ amax_bits, int T, int heads, int d, const void* __restrict__ scale,
-                          int scale_dt) {
+                          int* __restrict__ amax_bits, int T, int heads, int d, int64_t ldx,
+                          const void* __restrict__ scale, int scale_dt) {
   __shared__ __align__(16) uint8_t tile[64][64 + 4];
   __shared__ int block_max;
   const Divisor dv = make_divisor(scale, scale_dt);
@@ -178,8 +191,8 @@ transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
     const int tt = i >> 6, jj = i & 63;
     uint32_t q = 0;
     if (t0 + tt < T && j0 + jj < d) {
-      const int64_t at = ((int64_t)(t0 + tt) * heads + h) * d + j0 + jj;
-      const uint16_t raw = reinterpret_cast<const uint16_t*>(x)[at];
+      const int64_t at = ((int64_t)(t0 + tt) * heads + h) * d + j0 + jj;          // dense position
+      const uint16_t raw = reinterpret_cast<const uint16_t*>(x)[(int64_t)(t0 + tt) * ldx + (int64_t)h * d + j0 + jj];
       local_max = max(local_max, (int)(raw & 0x7FFFu));
       q = fp8_pair<E4M3>(quot(__uint_as_float((uint32_t)raw << 16), dv), 0.0f) & 0xFFu;
       if (codes != nullptr) codes[at] = (uint8_t)q;
@@ -248,17 +261,21 @@ extern "C" int vq_rmsnorm_quantize_fp8(const void* x, const void* weight, void* 
   return check_launch("rmsnorm_quantize_kernel");
 }
 
-extern "C" int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* out, int64_t n, const void* scale,
-                                        int scale_dtype, void* stream) {
-  VQ_REQUIRE(n >= 0, "vq_silu_mul_quantize_fp8: negative size");
-  if (n == 0) return VQ_OK;
+extern "C" int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
+                                        int64_t ld_gate, int64_t ld_up, const void* scale, int scale_dtype,
+                                        void* stream) {
+  VQ_REQUIRE(rows >= 0 && cols >= 0, "vq_silu_mul_quantize_fp8: negative size");
+  if (rows == 0 || cols == 0) return VQ_OK;
   VQ_REQUIRE(gate && up && out && scale, "vq_silu_mul_quantize_fp8: null argument");
-  VQ_REQUIRE(n % 8 == 0, "vq_silu_mul_quantize_fp8: the element count must be a multiple of 8");
+  VQ_REQUIRE(cols % 8 == 0 && ld_gate % 8 == 0 && ld_up % 8 == 0 && ld_gate >= cols && ld_up >= cols,
+             "vq_silu_mul_quantize_fp8: the row length and strides must be multiples of 8, strides at least a row");
+  VQ_REQUIRE(cols < (1ll << 31), "vq_silu_mul_quantize_fp8: row too long");
   VQ_REQUIRE(((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0 &&
              (reinterpret_cast<uintptr_t>(out) & 7) == 0, "vq_silu_mul_quantize_fp8: misaligned buffers");
-  silu_mul_quantize_kernel<<<stream_grid(n / 8, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint2*>(out), n / 8, scale,
-      scale_dtype);
+  const int64_t nvec = rows * (cols / 8);
+  silu_mul_quantize_kernel<<<stream_grid(nvec, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint2*>(out), nvec, (int)(cols / 8),
+      ld_gate / 8, ld_up / 8, scale, scale_dtype);
   return check_launch("silu_mul_quantize_kernel");
 }
 
@@ -286,21 +303,23 @@ extern "C" int vq_rope_quantize_fp8(const void* x, const void* cosv, const void*
 }
 
 extern "C" int vq_transpose_quantize_fp8(const void* x, void* out, void* codes, void* amax_bits, int format, int64_t T,
-                                         int64_t heads, int64_t d, const void* scale, int scale_dtype, void* stream) {
+                                         int64_t heads, int64_t d, int64_t ldx, const void* scale, int scale_dtype,
+                                         void* stream) {
   VQ_REQUIRE(T >= 0 && heads >= 0 && d >= 0, "vq_transpose_quantize_fp8: bad extent");
   if (T == 0 || heads == 0 || d == 0) return VQ_OK;
   VQ_REQUIRE(x && out && scale, "vq_transpose_quantize_fp8: null argument");
   VQ_REQUIRE(format == VQ_IN_E4M3 || format == VQ_IN_E5M2, "vq_transpose_quantize_fp8: format must be e4m3 or e5m2");
   VQ_REQUIRE(T < (1ll << 31) && heads < 65536 && d < (1 << 22), "vq_transpose_quantize_fp8: extent too large");
+  VQ_REQUIRE(ldx >= heads * d, "vq_transpose_quantize_fp8: row stride smaller than a row");
   dim3 grid((unsigned)((T + 63) / 64), (unsigned)((d + 63) / 64), (unsigned)heads);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (format == VQ_IN_E4M3)
     transpose_quantize_kernel<true><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(out),
                                                           static_cast<uint8_t*>(codes), static_cast<int*>(amax_bits),
-                                                          (int)T, (int)heads, (int)d, scale, scale_dtype);
+                                                          (int)T, (int)heads, (int)d, ldx, scale, scale_dtype);
   else
     transpose_quantize_kernel<false><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(out),
                                                            static_cast<uint8_t*>(codes), static_cast<int*>(amax_bits),
-                                                           (int)T, (int)heads, (int)d, scale, scale_dtype);
+                                                           (int)T, (int)heads, (int)d, ldx, scale, scale_dtype);
   return check_launch("transpose_quantize_kernel");
 }

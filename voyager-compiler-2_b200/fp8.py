@@ -18,11 +18,19 @@ import torch
 from . import _native as N
 from .ops import _DTYPE_ID, _dtype_id, _ptr, _stream, gemm_tn
 
-_FORMATS = {"fp8_e4m3": N.IN_E4M3, "fp8_e5m2": N.IN_E5M2}
+_FORMATS = {"fp8_e4m3": N.IN_E4M3, "fp8_e5m2": N.IN_E5M2,
+            torch.float8_e4m3fn: N.IN_E4M3, torch.float8_e5m2: N.IN_E5M2}
 
 
-def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype: str = "fp8_e4m3") -> torch.Tensor:
-    """Cast ``x / scale`` to FP8 bytes (``uint8`` tensor of ``x``'s shape).
+def _typed(codes: torch.Tensor, dtype):
+    """Bytes for a format named by a string; the torch FP8 dtype when that is what was asked for
+    (the reference's casts return float8 tensors)."""
+    return codes.view(dtype) if isinstance(dtype, torch.dtype) else codes
+
+
+def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torch.Tensor:
+    """Cast ``x / scale`` to FP8 (reference ``backend/gpu/fp8.py:253-261``): a ``uint8`` tensor of
+    ``x``'s shape for ``dtype`` ``"fp8_e4m3"`` / ``"fp8_e5m2"``, a float8 tensor for a torch dtype.
 
     ``scale`` holds one element, or one per row of the last axis
     (shape ``[..., 1]``, per-channel weights).
@@ -46,22 +54,55 @@ def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype: str = "fp8_e4m3") 
         raise NotImplementedError("quantize_fp8 needs element counts that are multiples of 16")
     N.check(N.lib().vq_quantize_fp8(x.data_ptr(), scale.data_ptr(), _dtype_id(scale.dtype), out.data_ptr(),
                                     _FORMATS[dtype], n, per, _stream()), "vq_quantize_fp8")
-    return out
+    return _typed(out, dtype)
 
 
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, alpha: Optional[torch.Tensor] = None,
-             bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, dtype: str = "fp8_e4m3") -> torch.Tensor:
-    """``alpha * (a @ b^T) + bias`` for FP8 byte operands ``a [*batch, M, K]`` and
-    ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation, one rounding."""
-    return gemm_tn(a, b, out_dtype=out_dtype, alpha=alpha, bias=bias, in_kind=_FORMATS[dtype])
+             bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, dtype: str = "fp8_e4m3",
+             alpha_cols: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``alpha * alpha_cols[n] * (a @ b^T) + bias`` (+ ``residual`` after the rounding) for FP8 byte
+    operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation."""
+    return gemm_tn(a, b, out_dtype=out_dtype, alpha=alpha, bias=bias, in_kind=_FORMATS[dtype],
+                   alpha_cols=alpha_cols, residual=residual)
 
 
-def fp8_linear(x8: torch.Tensor, w8: torch.Tensor, scale_a: torch.Tensor, scale_w: torch.Tensor,
-               bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
-    """One FP8 linear: ``(x8 @ w8^T) * (scale_a * scale_w) + bias`` with tensor-wise scales
-    (reference ``backend/gpu/fp8.py:372-400``)."""
-    alpha = (scale_a * scale_w).reshape(())
-    return fp8_gemm(x8, w8, alpha, bias, out_dtype)
+def _as_bytes(t: torch.Tensor):
+    """FP8 tensors (torch float8 dtypes or raw bytes) as ``(uint8 view, format name)``."""
+    if t.dtype == torch.float8_e5m2:
+        return t.view(torch.uint8), "fp8_e5m2"
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8), "fp8_e4m3"
+    if t.dtype == torch.uint8:
+        return t, "fp8_e4m3"
+    raise NotImplementedError(f"FP8 operands are float8 tensors or their bytes, not {t.dtype}")
+
+
+def fp8_linear(input: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor,
+               bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``input @ weight.T * scale + bias`` in bfloat16 as one FP8 GEMM (reference
+    ``backend/gpu/fp8.py:372-400``).  ``input [..., K]`` and ``weight [N, K]`` are FP8;
+    ``scale`` is a float32 scalar or ``[1, N]`` per output channel; ``bias [N]`` bfloat16."""
+    a, fmt = _as_bytes(input)
+    w, fmt_w = _as_bytes(weight)
+    if fmt != fmt_w:
+        raise NotImplementedError("both operands of the FP8 GEMM share one format")
+    if scale.dim() == 0 or scale.numel() == 1 and scale.dim() < 2:
+        return fp8_gemm(a, w, scale.reshape(()), bias, dtype=fmt)
+    if scale.numel() != w.shape[0]:
+        raise ValueError(f"scale of shape {tuple(scale.shape)} is neither a scalar nor one per output channel")
+    return fp8_gemm(a, w, None, bias, dtype=fmt, alpha_cols=scale)
+
+
+def fp8_bmm(input: torch.Tensor, other: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """``input @ other * scale`` in bfloat16 over shared batch dimensions (reference
+    ``backend/gpu/fp8.py:403-429``): ``input [..., M, K]``, ``other [..., K, N]``, float32 scalar."""
+    a, fmt = _as_bytes(input)
+    b, fmt_b = _as_bytes(other)
+    if fmt != fmt_b:
+        raise NotImplementedError("both operands of the FP8 GEMM share one format")
+    if a.shape[:-2] != b.shape[:-2]:
+        raise ValueError("fp8_bmm operands share their batch dimensions")
+    return fp8_gemm(a, b.transpose(-2, -1).contiguous(), scale.reshape(()), dtype=fmt)
 
 
 def softmax_quantize_fp8(scores: torch.Tensor, score_scale: float, out_scale: torch.Tensor,
@@ -113,31 +154,59 @@ def rmsnorm_quantize_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, scal
     return out
 
 
+def _rows_view(name: str, t: torch.Tensor):
+    """``t`` as ``(tensor, rows, cols, row stride)``: dense, or a column slice of a wider matrix."""
+    if t.dtype != torch.bfloat16:
+        raise NotImplementedError(f"{name} takes bfloat16 input")
+    if t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1] and t.stride(0) % 8 == 0 \
+            and t.data_ptr() % 16 == 0:
+        return t, t.shape[0], t.shape[1], t.stride(0)
+    t = t.contiguous()
+    cols = t.shape[-1] if t.dim() else 1
+    return t, t.numel() // max(cols, 1), cols, cols
+
+
 def silu_mul_quantize_fp8(gate: torch.Tensor, up: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
-    """e4m3 bytes of ``(silu(gate) * up) / scale`` in one pass."""
-    gate, up, scale = _bf16_input("silu_mul_quantize_fp8", gate), _bf16_input("silu_mul_quantize_fp8", up), _scale_arg(scale)
+    """e4m3 bytes of ``(silu(gate) * up) / scale`` in one pass.  ``gate`` and ``up`` may be
+    column slices of one wider matrix (the two halves of a merged projection)."""
     if gate.shape != up.shape:
         raise ValueError("gate and up differ in shape")
+    scale = _scale_arg(scale)
+    g, rows, cols, ldg = _rows_view("silu_mul_quantize_fp8", gate)
+    u, _, _, ldu = _rows_view("silu_mul_quantize_fp8", up)
     out = torch.empty(gate.shape, dtype=torch.uint8, device=gate.device)
-    N.check(N.lib().vq_silu_mul_quantize_fp8(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(),
+    N.check(N.lib().vq_silu_mul_quantize_fp8(g.data_ptr(), u.data_ptr(), out.data_ptr(), rows, cols, ldg, ldu,
                                              scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
             "vq_silu_mul_quantize_fp8")
     return out
+
+
+def _heads_view(name: str, x: torch.Tensor):
+    """``x [T, heads, d]`` as ``(tensor, token stride)``: dense, or head columns sliced out of a
+    wider ``[T, *]`` matrix (unit stride along d, d between heads)."""
+    if x.dtype != torch.bfloat16:
+        raise NotImplementedError(f"{name} takes bfloat16 input")
+    T, heads, d = x.shape
+    if x.stride(2) == 1 and x.stride(1) == d and x.stride(0) >= heads * d and x.stride(0) % 8 == 0 \
+            and x.data_ptr() % 16 == 0:
+        return x, x.stride(0)
+    return x.contiguous(), heads * d
 
 
 def rope_quantize_fp8(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                       scale: torch.Tensor) -> torch.Tensor:
     """e4m3 bytes of the rotary embedding of ``x [T, heads, d]`` (rotate-half form, ``cos`` /
     ``sin`` ``[T, d]``; ``None`` skips the rotation), laid out head-major ``[heads, T, d]``."""
-    x, scale = _bf16_input("rope_quantize_fp8", x), _scale_arg(scale)
+    scale = _scale_arg(scale)
     T, heads, d = x.shape
+    x, ldx = _heads_view("rope_quantize_fp8", x)
     if cos is not None:
         cos, sin = _bf16_input("rope_quantize_fp8", cos), _bf16_input("rope_quantize_fp8", sin)
         if tuple(cos.shape) != (T, d) or tuple(sin.shape) != (T, d):
             raise ValueError("cos / sin must be [T, head_dim]")
     out = torch.empty((heads, T, d), dtype=torch.uint8, device=x.device)
     N.check(N.lib().vq_rope_quantize_fp8(x.data_ptr(), _ptr(cos), _ptr(sin), out.data_ptr(), T, heads, d,
-                                         heads * d, d, d, T * d, scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
+                                         ldx, d, d, T * d, scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
             "vq_rope_quantize_fp8")
     return out
 
@@ -153,18 +222,19 @@ def transpose_heads_quantize_fp8(x: torch.Tensor, scale: torch.Tensor) -> torch.
     return out
 
 
-def transpose_quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype: str = "fp8_e4m3") -> torch.Tensor:
+def transpose_quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torch.Tensor:
     """FP8 bytes of ``x [T, heads, d] / scale`` laid out ``[heads, d, T]``."""
-    x, scale = _bf16_input("transpose_quantize_fp8", x), _scale_arg(scale)
+    scale = _scale_arg(scale)
     T, heads, d = x.shape
+    x, ldx = _heads_view("transpose_quantize_fp8", x)
     out = torch.empty((heads, d, T), dtype=torch.uint8, device=x.device)
     N.check(N.lib().vq_transpose_quantize_fp8(x.data_ptr(), out.data_ptr(), None, None, _FORMATS[dtype], T, heads, d,
-                                              scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
+                                              ldx, scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
             "vq_transpose_quantize_fp8")
-    return out
+    return _typed(out, dtype)
 
 
-def quantize_fp8_transpose(input: torch.Tensor, scale: torch.Tensor, dtype: str = "fp8_e4m3"):
+def quantize_fp8_transpose(input: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3"):
     """``(codes [M, N], transpose [N, M], amax)`` of a matrix in one pass over it: the FP8 bytes
     of ``input / scale`` in both layouts and ``amax(|input|)`` as a 0-d tensor of ``input``'s dtype
     (reference ``backend/gpu/fp8.py:342-369``)."""
@@ -176,7 +246,7 @@ def quantize_fp8_transpose(input: torch.Tensor, scale: torch.Tensor, dtype: str 
     transpose = torch.empty((cols, rows), dtype=torch.uint8, device=x.device)
     amax = torch.zeros((), dtype=torch.int32, device=x.device)
     N.check(N.lib().vq_transpose_quantize_fp8(x.data_ptr(), transpose.data_ptr(), codes.data_ptr(), amax.data_ptr(),
-                                              _FORMATS[dtype], rows, 1, cols, scale.data_ptr(),
+                                              _FORMATS[dtype], rows, 1, cols, cols, scale.data_ptr(),
                                               _dtype_id(scale.dtype), _stream()),
             "vq_transpose_quantize_fp8")
-    return codes, transpose, amax.to(torch.int16).view(torch.bfloat16)
+    return _typed(codes, dtype), _typed(transpose, dtype), amax.to(torch.int16).view(torch.bfloat16)

@@ -571,9 +571,14 @@ def _parse_layout(layout: str):
     return act, wgt, out
 
 
-def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None):
+def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None,
+            alpha_cols=None, residual=None):
     """``out[..., m, n] = alpha * sum_k a[..., m, k] * b[..., n, k] + bias[n]`` on the
     tensor cores (fp32 accumulation, one rounding to ``out_dtype``).
+
+    ``alpha_cols [N]`` multiplies column ``n`` after ``alpha`` (per-output-channel scales);
+    ``residual`` (the output's shape and dtype) is added after the rounding and the sum is
+    rounded again, as ``residual + linear(...)`` would be.
 
     ``a`` is ``[*batch, M, K]`` and ``b`` ``[*batch, N, K]`` or ``[N, K]``; both are
     used K-contiguous.  ``in_kind`` overrides the operand element kind for 8-bit
@@ -610,14 +615,31 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
     out = torch.empty((batch, rows, n), dtype=out_dtype, device=a.device)
     if bias is not None:
         bias = bias.contiguous()
+    epi = None
+    if alpha_cols is not None or residual is not None:
+        epi = N.VqGemmEpilogue()
+        if alpha_cols is not None:
+            alpha_cols = alpha_cols.reshape(-1).contiguous()
+            if alpha_cols.numel() != n or alpha_cols.dtype not in _DTYPE_ID:
+                raise ValueError(f"alpha_cols must hold {n} bfloat16/float16/float32 values")
+            epi.alpha_cols, epi.alpha_cols_dtype = alpha_cols.data_ptr(), _dtype_id(alpha_cols.dtype)
+        if residual is not None:
+            if residual.dtype != out_dtype or residual.numel() != out.numel():
+                raise ValueError("the residual must have the output's shape and dtype")
+            residual = residual.contiguous()
+            epi.residual, epi.ldr, epi.strideR = residual.data_ptr(), n, rows * n
     if out.numel():
         if k == 0:
-            out.zero_()
+            out.zero_()   # an empty sum; the epilogue's additions are all that is left
+            if bias is not None:
+                out += bias.to(out_dtype)
+            if residual is not None:
+                out += residual.reshape(out.shape)
         else:
-            N.check(N.lib().vq_gemm_tn(
+            N.check(N.lib().vq_gemm_tn_ex(
                 a2.data_ptr(), b2.data_ptr(), out.data_ptr(), in_kind, _dtype_id(out_dtype), rows, n, k, k, k, n,
                 batch, stride_a, stride_b, rows * n, _ptr(alpha), 0 if alpha is None else _dtype_id(alpha.dtype),
-                _ptr(bias), 0 if bias is None else _dtype_id(bias.dtype), _stream()), "vq_gemm_tn")
+                _ptr(bias), 0 if bias is None else _dtype_id(bias.dtype), epi, _stream()), "vq_gemm_tn_ex")
     return out.reshape(*batch_shape, m, n) if b.dim() > 2 else out.reshape(*a.shape[:-1], n)
 
 

@@ -136,8 +136,9 @@ def calibrate_fp8_scales(x, params, shape: LlamaShape):
 class Fp8DecoderLayer:
     """FP8 per-tensor decoder layer on the CUDA kernels (prefill, batch 1)."""
 
-    def __init__(self, params, scales, shape: LlamaShape):
+    def __init__(self, params, scales, shape: LlamaShape, merge_qkv=True, merge_gate_up=True, fuse_residual=True):
         self.shape = shape
+        self.merge_qkv, self.merge_gate_up, self.fuse_residual = merge_qkv, merge_gate_up, fuse_residual
         self.scales = scales
         self.ln1, self.ln2 = params["ln1"], params["ln2"]
         # weights are cast once, as convert_pt2e bakes them
@@ -147,11 +148,18 @@ class Fp8DecoderLayer:
                       (("q", "h"), ("k", "h"), ("v", "h"), ("o", "ctx"), ("gate", "h2"), ("up", "h2"), ("down", "act"))}
         self.alpha_qk = (s["q"] * s["k"]).reshape(())
         self.alpha_pv = (s["p"] * s["v"]).reshape(())
+        # linears that read one quantized input run as one GEMM; each keeps its own scale per column
+        def merged(names):
+            w = torch.cat([self.w8[n] for n in names], 0)
+            a = torch.cat([self.alpha[n].float().expand(self.w8[n].shape[0]) for n in names]).contiguous()
+            return w, a
+        self.w8_qkv, self.alpha_qkv = merged(("q", "k", "v"))
+        self.w8_gate_up, self.alpha_gate_up = merged(("gate", "up"))
         self._rope = None
         self._mask = None
 
-    #: kernels of this package launched per forward (7 fused casts + softmax + 9 GEMMs)
-    LAUNCHES = 7 + 1 + 9
+    #: kernels of this package launched per forward (7 fused casts + softmax + 6 GEMMs)
+    LAUNCHES = 7 + 1 + 6
 
     def _tables(self, T, device):
         if self._rope is None or self._rope[0].shape[0] != T:
@@ -164,10 +172,16 @@ class Fp8DecoderLayer:
         sh, s = self.shape, self.scales
         T = x.shape[0]
         (cos, sin), _ = self._tables(T, x.device)
+        nq, nkv = sh.heads * sh.head_dim, sh.kv_heads * sh.head_dim
         h8 = FP8.rmsnorm_quantize_fp8(x, self.ln1, sh.eps, s["h"])
-        q = FP8.fp8_gemm(h8, self.w8["q"], self.alpha["q"]).view(T, sh.heads, sh.head_dim)
-        k = FP8.fp8_gemm(h8, self.w8["k"], self.alpha["k"]).view(T, sh.kv_heads, sh.head_dim)
-        v = FP8.fp8_gemm(h8, self.w8["v"], self.alpha["v"]).view(T, sh.kv_heads, sh.head_dim)
+        if self.merge_qkv:
+            qkv = FP8.fp8_gemm(h8, self.w8_qkv, alpha_cols=self.alpha_qkv)  # [T, (heads + 2 kv) * d]
+            q, k, v = qkv[:, :nq], qkv[:, nq:nq + nkv], qkv[:, nq + nkv:]
+        else:
+            q, k, v = (FP8.fp8_gemm(h8, self.w8[n], self.alpha[n]) for n in ("q", "k", "v"))
+        q = q.unflatten(1, (sh.heads, sh.head_dim))
+        k = k.unflatten(1, (sh.kv_heads, sh.head_dim))
+        v = v.unflatten(1, (sh.kv_heads, sh.head_dim))
         # query heads of one KV group are stacked along the rows: [kv, groups*T, d]
         q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(sh.kv_heads, sh.groups * T, sh.head_dim)
         k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                     # [kv, T, d]
@@ -178,10 +192,19 @@ class Fp8DecoderLayer:
         ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv)                          # [kv, groups*T, d]
         # the cast of the context undoes the head-major layout: [kv*groups, T, d] -> [T, heads*d]
         ctx8 = FP8.transpose_heads_quantize_fp8(ctx.view(sh.heads, T, sh.head_dim), s["ctx"])
-        x1 = x + FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"])
+        if self.fuse_residual:
+            x1 = FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"], residual=x)   # x + o_proj(ctx)
+        else:
+            x1 = x + FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"])
         h28 = FP8.rmsnorm_quantize_fp8(x1, self.ln2, sh.eps, s["h2"])
-        act8 = FP8.silu_mul_quantize_fp8(FP8.fp8_gemm(h28, self.w8["gate"], self.alpha["gate"]),
-                                         FP8.fp8_gemm(h28, self.w8["up"], self.alpha["up"]), s["act"])
+        if self.merge_gate_up:
+            gu = FP8.fp8_gemm(h28, self.w8_gate_up, alpha_cols=self.alpha_gate_up)   # [T, 2 * intermediate]
+            gate, up = gu[:, :sh.intermediate], gu[:, sh.intermediate:]
+        else:
+            gate, up = (FP8.fp8_gemm(h28, self.w8[n], self.alpha[n]) for n in ("gate", "up"))
+        act8 = FP8.silu_mul_quantize_fp8(gate, up, s["act"])
+        if self.fuse_residual:
+            return FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"], residual=x1)
         return x1 + FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"])
 
     def forward_unfused(self, x):
