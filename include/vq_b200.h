@@ -225,12 +225,21 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
  * output dtype with leading dimension ldr and batch stride strideR, may be NULL,
  * must not alias C) is added after the rounding to out_dtype and the sum is
  * rounded again, which is `x + linear(...)` of a decoder layer in one pass.
+ * causal_mode / causal_period describe the two matmuls of causal attention, where
+ * row r of A and C belongs to position t = r % causal_period of a sequence:
+ *   1  elements C[r][n] with n > t are never read by the caller (the masked scores
+ *      of Q K^T): tiles made only of such elements may be left unwritten;
+ *   2  A[r][k] is zero for k > t (the probabilities of P V): the contraction of a
+ *      tile may stop after the largest t among its rows.
+ * Both are permissions, not requests: results the caller may read are unchanged.
  * epi == NULL is vq_gemm_tn. */
 typedef struct VqGemmEpilogue {
   const void* alpha_cols;
   int32_t alpha_cols_dtype;
   const void* residual;
   int64_t ldr, strideR;
+  int32_t causal_mode;
+  int64_t causal_period;
 } VqGemmEpilogue;
 int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dtype, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA,

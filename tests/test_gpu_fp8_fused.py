@@ -229,3 +229,40 @@ def test_fused_casts_read_column_slices():
                        vb.fp8.rope_quantize_fp8(heads.contiguous(), cos, sin, scale))
     assert torch.equal(vb.fp8.transpose_quantize_fp8(heads, scale),
                        vb.fp8.transpose_quantize_fp8(heads.contiguous(), scale))
+
+
+@pytest.mark.parametrize("T,groups,batch", [(512, 2, 2), (768, 1, 1), (300, 2, 1)])
+def test_gemm_causal_hints_leave_read_results_unchanged(T, groups, batch):
+    """Q K^T with unread (masked) tiles skipped, and P V with the contraction cut at the diagonal."""
+    vb = _vb()
+    g = torch.Generator().manual_seed(T)
+    d = 64
+    q = torch.randn(batch, groups * T, d, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    k = torch.randn(batch, T, d, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    alpha = torch.tensor(0.5, dtype=torch.float32).cuda()
+    full = vb.fp8.fp8_gemm(q, k, alpha)
+    hinted = vb.fp8.fp8_gemm(q, k, alpha, causal=("scores", T))
+    rows = torch.arange(groups * T, device="cuda") % T
+    read = torch.arange(T, device="cuda")[None, :] <= rows[:, None]           # what softmax reads
+    assert torch.equal(torch.where(read, hinted, 0), torch.where(read, full, 0))
+    # probabilities: zero above the diagonal
+    p = torch.rand(batch, groups * T, T, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    p = torch.where(read, p, 0)
+    if T % 16:
+        return  # K rows must be multiples of 16 bytes for this operand without padding
+    vt = torch.randn(batch, 128, T, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    assert torch.equal(vb.fp8.fp8_gemm(p, vt, alpha, causal=("probabilities", T)), vb.fp8.fp8_gemm(p, vt, alpha))
+    vb.ops.gemm_status()
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 128, 256), (300, 64, 128), (1024, 100, 512), (257, 8, 64)])
+def test_gemm_narrow_outputs(m, n, k):
+    """Outputs of at most 128 columns run on half-width tiles."""
+    vb = _vb()
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b = torch.randn(n, k, generator=g).bfloat16()
+    want = a.double() @ b.double().t()
+    got = vb.ops.gemm_tn(a.cuda(), b.cuda()).cpu()
+    vb.ops.gemm_status()
+    assert float((got.double() - want).abs().max() / want.abs().max()) <= 1e-2

@@ -70,6 +70,7 @@ class VqGemmEpilogue(ctypes.Structure):
     _fields_ = [
         ("alpha_cols", ctypes.c_void_p), ("alpha_cols_dtype", ctypes.c_int32),
         ("residual", ctypes.c_void_p), ("ldr", ctypes.c_int64), ("strideR", ctypes.c_int64),
+        ("causal_mode", ctypes.c_int32), ("causal_period", ctypes.c_int64),
     ]
 
 

@@ -57,6 +57,9 @@ struct GemmParams {
   int alpha_cols_dt;
   const void* residual;     // [batch, M, N] of the output dtype added after the first rounding, or null
   int64_t ldr, strideR;
+  int causal_period;        // > 0: row r belongs to position t = r % period of a causal sequence
+  int causal_mode;          // 1: tiles whose columns all exceed t are not computed; 2: A is zero beyond column t
+  int bn;                   // CTA-pair kernel: tile width, 256 or 128
   int out_dt;
   uint32_t idesc;
   int kind_f8;
@@ -564,11 +567,25 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
+  const int bn = p.bn;
   const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
-  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_n = (p.N + bn - 1) / bn;
   const int64_t num_tiles = (int64_t)tiles_m * tiles_n * p.batch;
   const int k_elems_per_stage = BK_BYTES / p.elem_bytes;
   const int k_blocks = (p.K + k_elems_per_stage - 1) / k_elems_per_stage;
+  const uint32_t stage_tx_bytes = 2u * (uint32_t)(P_A_BYTES + (bn / 2) * BK_BYTES);
+
+  // Causal hints: the number of K blocks a tile needs (0 = the tile is not computed at all).
+  // The three roles evaluate this identically, so they walk the same tile sequence.
+  auto tile_k_blocks = [&](int m_blk, int n_blk) -> int {
+    if (p.causal_period <= 0) return k_blocks;
+    const int t_lo = (m_blk * 2 * BM) % p.causal_period;
+    int t_hi = t_lo + 2 * BM - 1;                       // largest position among the tile's rows
+    if (t_hi >= p.causal_period) t_hi = p.causal_period - 1;   // the tile runs into the next sequence
+    if (p.causal_mode == 1) return n_blk * bn > t_hi ? 0 : k_blocks;
+    const int need = (t_hi + k_elems_per_stage) / k_elems_per_stage;   // ceil((t_hi + 1) / k per stage)
+    return need < k_blocks ? need : k_blocks;
+  };
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -605,11 +622,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int n_blk = (int)((tile / tiles_m) % tiles_n);
         const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
         const int m0 = m_blk * 2 * BM + (int)rank * BM;
-        const int n0 = n_blk * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int n0 = n_blk * bn + (int)rank * (bn / 2);
+        const int kb_end = tile_k_blocks(m_blk, n_blk);
+        for (int kb = 0; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           // the even CTA arms its barrier for the bytes of both CTAs
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (P_A_BYTES + P_B_BYTES));
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], stage_tx_bytes);
           const uint32_t leader_full = map_to_cta(&full_bar[stage], 0);
           tma_load_3d_pair(smem_a + stage * P_A_BYTES, &map_a, leader_full, kb * k_elems_per_stage, m0, b);
           tma_load_3d_pair(smem_b + stage * P_B_BYTES, &map_b, leader_full, kb * k_elems_per_stage, n0, b);
@@ -626,10 +644,12 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int kb_end = tile_k_blocks((int)(tile % tiles_m), (int)((tile / tiles_m) % tiles_n));
+        if (kb_end == 0) continue;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < kb_end; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem_a + stage * P_A_BYTES);
@@ -663,13 +683,14 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m_blk = (int)(tile % tiles_m);
       const int n_blk = (int)((tile / tiles_m) % tiles_n);
       const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
-      prefetch_residual(p, m_blk * 2 * BM + (int)rank * BM + quarter * 32, lane, n_blk * BN, b, chalf * (BN / 2),
-                        (chalf + 1) * (BN / 2));
+      if (tile_k_blocks(m_blk, n_blk) == 0) continue;
+      prefetch_residual(p, m_blk * 2 * BM + (int)rank * BM + quarter * 32, lane, n_blk * bn, b, chalf * (bn / 2),
+                        (chalf + 1) * (bn / 2));
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
       epilogue_warp_tile<OUT_DT>(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * 2 * BM + (int)rank * BM + quarter * 32,
-                         lane, n_blk * BN, b, has_alpha, alpha, chalf * (BN / 2), (chalf + 1) * (BN / 2));
+                         lane, n_blk * bn, b, has_alpha, alpha, chalf * (bn / 2), (chalf + 1) * (bn / 2));
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
@@ -961,6 +982,11 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
       VQ_REQUIRE(epi->residual != C, "vq_gemm_tn_ex: the residual must not alias the output");
       p.residual = epi->residual; p.ldr = epi->ldr; p.strideR = epi->strideR;
     }
+    if (epi->causal_mode != 0) {
+      VQ_REQUIRE((epi->causal_mode == 1 || epi->causal_mode == 2) && epi->causal_period > 0 &&
+                 epi->causal_period < (1ll << 31), "vq_gemm_tn_ex: causal_mode is 0, 1 or 2 and needs a positive period");
+      p.causal_mode = epi->causal_mode; p.causal_period = (int)epi->causal_period;
+    }
   }
   const int fmt = in_kind == VQ_IN_BF16 ? 1 : in_kind == VQ_IN_F16 ? 0 : in_kind == VQ_IN_E4M3 ? 0 : 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -999,9 +1025,10 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
   if (pair_mode == 1 && M > BM) {
     CUtensorMap map_a, map_b;
     if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
-    if (int e = make_operand_map(&map_b, B, kind, eb, N, K, ldb, batch, strideB, BN / 2)) return e;
-    p.idesc = sm100::make_idesc(2 * BM, BN, fmt, fmt, 0, 0);
-    const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
+    p.bn = N <= BN / 2 ? BN / 2 : BN;   // a narrow output takes half-width tiles instead of multiplying zero padding
+    if (int e = make_operand_map(&map_b, B, kind, eb, N, K, ldb, batch, strideB, p.bn / 2)) return e;
+    p.idesc = sm100::make_idesc(2 * BM, p.bn, fmt, fmt, 0, 0);
+    const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + p.bn - 1) / p.bn) * batch;
     const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
     VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_pair_kernel)<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, p);
     return check_launch("gemm_tn_pair_kernel");
@@ -1066,6 +1093,7 @@ int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb
   VQ_FOR_OUT_DTYPE(out_dtype, gemm_nvfp4_kernel)<<<grid, NUM_THREADS, Q_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p, sf);
   return check_launch("gemm_nvfp4_kernel");
 }
+
 
 int vq_gemm_status(int reset) {
   int value = 0;

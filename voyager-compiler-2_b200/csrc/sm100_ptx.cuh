@@ -83,8 +83,11 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
   return r;
 }
+// Arrive on a barrier of this or the pair's other CTA.  CTA-scope release (the default): the
+// arrival orders this thread's tensor-memory reads, which the tcgen05 fences cover; a
+// cluster-scope release would also wait for every global store of the thread to drain.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // 3-D tiled load issued by either CTA of a pair: data lands in this CTA's shared
 // memory, completion bytes are counted on `bar_cluster_addr`, which may be a

@@ -59,11 +59,13 @@ def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torc
 
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, alpha: Optional[torch.Tensor] = None,
              bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, dtype: str = "fp8_e4m3",
-             alpha_cols: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+             alpha_cols: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+             causal=None) -> torch.Tensor:
     """``alpha * alpha_cols[n] * (a @ b^T) + bias`` (+ ``residual`` after the rounding) for FP8 byte
-    operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation."""
+    operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation;
+    ``causal`` as for ``ops.gemm_tn``."""
     return gemm_tn(a, b, out_dtype=out_dtype, alpha=alpha, bias=bias, in_kind=_FORMATS[dtype],
-                   alpha_cols=alpha_cols, residual=residual)
+                   alpha_cols=alpha_cols, residual=residual, causal=causal)
 
 
 def _as_bytes(t: torch.Tensor):

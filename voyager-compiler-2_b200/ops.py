@@ -572,13 +572,16 @@ def _parse_layout(layout: str):
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None,
-            alpha_cols=None, residual=None):
+            alpha_cols=None, residual=None, causal=None):
     """``out[..., m, n] = alpha * sum_k a[..., m, k] * b[..., n, k] + bias[n]`` on the
     tensor cores (fp32 accumulation, one rounding to ``out_dtype``).
 
     ``alpha_cols [N]`` multiplies column ``n`` after ``alpha`` (per-output-channel scales);
     ``residual`` (the output's shape and dtype) is added after the rounding and the sum is
-    rounded again, as ``residual + linear(...)`` would be.
+    rounded again, as ``residual + linear(...)`` would be.  ``causal=("scores", T)`` says
+    that ``out[..., r, n]`` with ``n > r % T`` is never read (tiles of only such elements may
+    stay unwritten); ``causal=("probabilities", T)`` that ``a[..., r, k]`` is zero for
+    ``k > r % T`` (the contraction may stop early).
 
     ``a`` is ``[*batch, M, K]`` and ``b`` ``[*batch, N, K]`` or ``[N, K]``; both are
     used K-contiguous.  ``in_kind`` overrides the operand element kind for 8-bit
@@ -616,8 +619,11 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
     if bias is not None:
         bias = bias.contiguous()
     epi = None
-    if alpha_cols is not None or residual is not None:
+    if alpha_cols is not None or residual is not None or causal is not None:
         epi = N.VqGemmEpilogue()
+        if causal is not None:
+            epi.causal_mode = {"scores": 1, "probabilities": 2}[causal[0]]
+            epi.causal_period = int(causal[1])
         if alpha_cols is not None:
             alpha_cols = alpha_cols.reshape(-1).contiguous()
             if alpha_cols.numel() != n or alpha_cols.dtype not in _DTYPE_ID:

@@ -186,10 +186,11 @@ class Fp8DecoderLayer:
         q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(sh.kv_heads, sh.groups * T, sh.head_dim)
         k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                     # [kv, T, d]
         vt8 = FP8.transpose_quantize_fp8(v, s["v"])                         # [kv, d, T]
-        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk)                        # [kv, groups*T, T]
+        # masked scores are neither computed nor read; masked probabilities are zero codes
+        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk, causal=("scores", T))  # [kv, groups*T, T]
         # scale, causal mask, softmax and the FP8 cast of the probabilities in one pass
         p8 = FP8.softmax_quantize_fp8(scores, 1.0 / math.sqrt(sh.head_dim), s["p"], causal_period=T)
-        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv)                          # [kv, groups*T, d]
+        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv, causal=("probabilities", T))   # [kv, groups*T, d]
         # the cast of the context undoes the head-major layout: [kv*groups, T, d] -> [T, heads*d]
         ctx8 = FP8.transpose_heads_quantize_fp8(ctx.view(sh.heads, T, sh.head_dim), s["ctx"])
         if self.fuse_residual:
