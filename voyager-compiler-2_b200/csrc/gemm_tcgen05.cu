@@ -19,6 +19,7 @@
 // in a device flag, drains, frees TMEM and exits.
 
 #include <cstdlib>
+#include <cstring>
 
 #include "sm100_ptx.cuh"
 #include "vq_common.cuh"
@@ -60,6 +61,7 @@ struct GemmParams {
   int causal_period;        // > 0: row r belongs to position t = r % period of a causal sequence
   int causal_mode;          // 1: tiles whose columns all exceed t are not computed; 2: A is zero beyond column t
   int bn;                   // CTA-pair kernel: tile width, 256 or 128
+  int tma_store;            // the output has a tensor map: staged rows leave shared memory as TMA stores
   int out_dt;
   uint32_t idesc;
   int kind_f8;
@@ -331,9 +333,9 @@ __device__ __noinline__ void epilogue_warp_tile_unstaged(const GemmParams& p, ui
 }
 
 template <int OUT_DT>
-__device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, uint32_t taddr, uint8_t* stage, int row0,
-                                                     int lane, int n0, int b, bool has_alpha, float alpha, int c_begin,
-                                                     int c_end) {
+__device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
+                                                     uint8_t* stage, int row0, int lane, int n0, int b, bool has_alpha,
+                                                     float alpha, int c_begin, int c_end) {
   constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
   constexpr int ROUND_COLS = 128 / ESZ;   // output columns per 128-byte staged row
   const int64_t row_stride = p.ldc * ESZ;
@@ -344,16 +346,32 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, uint32
   const bool r_wide = ((reinterpret_cast<uintptr_t>(p.residual) | (uintptr_t)r_row_stride | (uintptr_t)(p.strideR * ESZ)) & 15) == 0;
   const bool rows_inside = row0 + 32 <= p.M;
   uint8_t* srow = stage + lane * 128;
+  // With a tensor map for C (and no residual to add) a finished 32 x 128-byte block leaves
+  // shared memory as one TMA store issued by lane 0; the hardware clips it at the edges of C.
+  const bool by_tma = p.tma_store != 0 && r_batch == nullptr;
 
   // one 32-column chunk: scale, stage, and flush when its 128-byte round is complete
   auto process = [&](const uint32_t (&v)[32], int c0) {
     const int col0 = n0 + c0;
     if (col0 >= p.N) return;  // warp-uniform
     const int half = ESZ == 4 ? 0 : (c0 >> 5) & 1;   // a 128-byte row holds two 32-column chunks of 16-bit values
+    if (by_tma && half == 0) {   // the previous block's store must have read the staging buffer
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+    }
     stage_chunk<OUT_DT>(p, v, srow, lane, col0, half, has_alpha, alpha);
     if (ESZ != 4 && half == 0 && col0 + 32 < p.N && c0 + 32 < c_end) return;  // the round's second chunk follows
-    __syncwarp();
     const int round_col0 = col0 - half * 32;
+    if (by_tma) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && row0 < p.M) {   // a block entirely below C has nothing to store
+        tma_store_3d(map_c, stage, round_col0, row0, b);
+        tma_store_commit();
+      }
+      return;
+    }
+    __syncwarp();
     flush_stage<OUT_DT>(p, stage, c_batch, r_batch, row_stride, r_row_stride, r_wide, row0, lane, round_col0,
                         rows_inside && round_col0 + ROUND_COLS <= p.N);
     __syncwarp();
@@ -376,32 +394,33 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, uint32
 }
 
 template <int OUT_DT>
-__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, uint32_t taddr, uint8_t* stage, int row0,
-                                                   int lane, int n0, int b, bool has_alpha, float alpha, int c_begin,
-                                                   int c_end) {
+__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
+                                                   uint8_t* stage, int row0, int lane, int n0, int b, bool has_alpha,
+                                                   float alpha, int c_begin, int c_end) {
   constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
   if (((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * ESZ) | (uintptr_t)(p.strideC * ESZ)) & 15) != 0) {
     epilogue_warp_tile_unstaged(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
     return;
   }
-  epilogue_warp_tile_t<OUT_DT>(p, taddr, stage, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
+  epilogue_warp_tile_t<OUT_DT>(p, map_c, taddr, stage, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
 }
 
 template <int OUT_DT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ GemmParams p) {
+gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                    const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  uint8_t* epi_stage = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);   // 1024-byte aligned: TMA stores read it with the 128-byte swizzle
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + EPI_STAGE_BYTES);
   uint64_t* full_bar = bars;                 // [STAGES]
   uint64_t* empty_bar = bars + STAGES;       // [STAGES]
   uint64_t* acc_full = bars + 2 * STAGES;    // [2]
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint8_t* epi_stage = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -512,7 +531,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile<OUT_DT>(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * BN, b,
+      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * BN, b,
                          has_alpha, alpha, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -521,6 +540,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
 
+  if (warp >= 2 && lane == 0) tma_store_wait_read();   // staging buffers stay valid until their stores have read them
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
   if (warp == 1) {
@@ -547,19 +567,20 @@ constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256 
 
 template <int OUT_DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ GemmParams p) {
+gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                    const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + P_STAGES * P_A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * (P_A_BYTES + P_B_BYTES));
+  uint8_t* epi_stage = smem + P_STAGES * (P_A_BYTES + P_B_BYTES);   // 1024-byte aligned: TMA stores read it with the 128-byte swizzle
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * (P_A_BYTES + P_B_BYTES) + EPI_STAGE_BYTES);
   uint64_t* full_bar = bars;                        // [P_STAGES] (used in the even CTA)
   uint64_t* empty_bar = bars + P_STAGES;            // [P_STAGES]
   uint64_t* acc_full = bars + 2 * P_STAGES;         // [2]
   uint64_t* acc_empty = bars + 2 * P_STAGES + 2;    // [2] (used in the even CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint8_t* epi_stage = smem + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -689,7 +710,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile<OUT_DT>(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * 2 * BM + (int)rank * BM + quarter * 32,
+      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * 2 * BM + (int)rank * BM + quarter * 32,
                          lane, n_blk * bn, b, has_alpha, alpha, chalf * (bn / 2), (chalf + 1) * (bn / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -698,6 +719,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   }
 
+  if (warp >= 2 && lane == 0) tma_store_wait_read();   // staging buffers stay valid until their stores have read them
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
   cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its tiles
@@ -736,7 +758,8 @@ struct ScaledOperands {
 
 template <int OUT_DT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ GemmParams p,
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                    const __grid_constant__ GemmParams p,
                   ScaledOperands sf) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -744,14 +767,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint8_t* smem_b = smem_a + Q_STAGES * Q_A_BYTES;
   uint8_t* smem_sfa = smem_b + Q_STAGES * Q_B_BYTES;
   uint8_t* smem_sfb = smem_sfa + Q_STAGES * Q_SF_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_STAGES * Q_STAGE_BYTES);
+  uint8_t* epi_stage = smem + Q_STAGES * Q_STAGE_BYTES;   // 1024-byte aligned: TMA stores read it with the 128-byte swizzle
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_STAGES * Q_STAGE_BYTES + EPI_STAGE_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Q_STAGES;
   uint64_t* acc_full = bars + 2 * Q_STAGES;
   uint64_t* acc_empty = bars + 2 * Q_STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Q_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint8_t* epi_stage = smem + Q_STAGES * Q_STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -861,7 +884,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * Q_BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile<OUT_DT>(p, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * Q_BN, b,
+      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * Q_BN, b,
                          has_alpha, alpha, chalf * (Q_BN / 2), (chalf + 1) * (Q_BN / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -870,6 +893,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
   }
 
+  if (warp >= 2 && lane == 0) tma_store_wait_read();   // staging buffers stay valid until their stores have read them
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
   if (warp == 1) {
@@ -912,6 +936,32 @@ int make_operand_map(CUtensorMap* map, const void* base, int elem_kind, int elem
   CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return VQ_OK;
+}
+
+// Tensor map over the output [batch, M, N] for the epilogue's TMA stores: boxes of 32 rows x 128
+// bytes in the 128-byte swizzle.  `*usable` is 0 (and the map zeroed) when C is not 16-byte
+// aligned in base and strides; the epilogue then stores with ordinary instructions.
+int make_output_map(CUtensorMap* map, int* usable, void* C, int out_dtype, int64_t M, int64_t N, int64_t ldc,
+                    int64_t batch, int64_t strideC) {
+  memset(map, 0, sizeof(*map));
+  *usable = 0;
+  const int esz = out_dtype == VQ_F32 ? 4 : 2;
+  const int64_t batch_stride = batch > 1 ? strideC : ldc * M;
+  if (((reinterpret_cast<uintptr_t>(C) | (uintptr_t)(ldc * esz) | (uintptr_t)(batch_stride * esz)) & 15) != 0) return VQ_OK;
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMapDataType dt = out_dtype == VQ_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                               : (out_dtype == VQ_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)(ldc * esz), (cuuint64_t)(batch_stride * esz)};
+  cuuint32_t box[3] = {(cuuint32_t)(128 / esz), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, dt, 3, C, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
+  *usable = 1;
   return VQ_OK;
 }
 
@@ -1022,6 +1072,8 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
       }
     }
   }
+  CUtensorMap map_c;
+  if (int e = make_output_map(&map_c, &p.tma_store, C, out_dtype, M, N, ldc, batch, strideC)) return e;
   if (pair_mode == 1 && M > BM) {
     CUtensorMap map_a, map_b;
     if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
@@ -1030,7 +1082,7 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
     p.idesc = sm100::make_idesc(2 * BM, p.bn, fmt, fmt, 0, 0);
     const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + p.bn - 1) / p.bn) * batch;
     const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
-    VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_pair_kernel)<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, p);
+    VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_pair_kernel)<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
     return check_launch("gemm_tn_pair_kernel");
   }
 
@@ -1046,7 +1098,7 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
-  VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_kernel)<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, p);
+  VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_kernel)<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
   return check_launch("gemm_tn_kernel");
 }
 
@@ -1076,6 +1128,8 @@ int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb
   p.bias = bias; p.bias_dt = bias_dtype;
   p.out_dt = out_dtype;
   p.idesc = sm100::make_idesc_nvfp4(BM, Q_BN);
+  CUtensorMap map_c;
+  if (int e = make_output_map(&map_c, &p.tma_store, C, out_dtype, M, N, ldc, batch, strideC)) return e;
   ScaledOperands sf{};
   sf.sfa = static_cast<const uint8_t*>(sfa);
   sf.sfb = static_cast<const uint8_t*>(sfb);
@@ -1090,7 +1144,7 @@ int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + Q_BN - 1) / Q_BN) * batch;
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
-  VQ_FOR_OUT_DTYPE(out_dtype, gemm_nvfp4_kernel)<<<grid, NUM_THREADS, Q_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p, sf);
+  VQ_FOR_OUT_DTYPE(out_dtype, gemm_nvfp4_kernel)<<<grid, NUM_THREADS, Q_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_c, p, sf);
   return check_launch("gemm_nvfp4_kernel");
 }
 

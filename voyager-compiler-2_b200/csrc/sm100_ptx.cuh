@@ -68,6 +68,19 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+// 3-D tiled store of a shared-memory box (laid out as the tensor map's swizzle mode says) to
+// global memory; elements outside the tensor are not written.  x * elem_size must be a
+// multiple of 16 bytes and no coordinate may be negative.  Completion is tracked per thread
+// in bulk groups: commit, then wait before the shared-memory box is overwritten.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's committed stores have finished reading shared memory
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // ---- thread-block clusters / CTA pairs ---------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -101,6 +114,7 @@ __device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m
 }
 
 // ---- proxies / tcgen05 fences ----------------------------------------------
+// generic-proxy writes to shared memory become visible to the async proxy (TMA, tcgen05)
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
