@@ -21,17 +21,35 @@ namespace {
 constexpr int kWarpsPerCta = 4;
 
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// two floats rounded to bfloat16 by one instruction: `lo` in bits [0,16), `hi` in bits [16,32)
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float ex2_approx(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
 
 // VPL = 16-byte vectors (8 columns) per lane; a row has up to 32 * 8 * VPL columns.
-template <int VPL, bool E4M3>
+// WPR warps share a row (its vectors interleaved between them, so a causal row's live part is
+// split evenly); with WPR = 2 a thread keeps half as many values in registers, which doubles
+// the warps resident per SM, and the two warps combine their maximum and sum through shared memory.
+template <int VPL, int WPR, bool E4M3>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 softmax_quantize_kernel(const uint4* __restrict__ scores, uint2* __restrict__ out, int64_t rows, int cols,
                         float score_scale, const __nv_bfloat16* __restrict__ mask, int64_t mask_rows,
                         int causal_period, const void* __restrict__ out_scale, int out_scale_dt) {
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int vecs = cols >> 3;
+  __shared__ float part_max[kWarpsPerCta], part_sum[kWarpsPerCta];
+  constexpr int kStride = 32 * WPR;                    // vectors between a thread's consecutive vectors
+  const int lane = threadIdx.x % kStride;              // position among the row's threads
+  const int warp = threadIdx.x >> 5;
+  const int64_t row_raw = (int64_t)blockIdx.x * (kWarpsPerCta / WPR) + threadIdx.x / kStride;
+  const bool row_ok = row_raw < rows;
+  if (WPR == 1 && !row_ok) return;
+  const int64_t row = row_ok ? row_raw : rows - 1;     // with WPR > 1 every thread reaches the block barriers
+  const int vecs = row_ok ? cols >> 3 : 0;
   const float sp = loadp(out_scale, 0, out_scale_dt);
   // columns [0, limit) can be non-zero
   int limit = cols;
@@ -39,65 +57,93 @@ softmax_quantize_kernel(const uint4* __restrict__ scores, uint2* __restrict__ ou
   const uint4* src = scores + row * vecs;
   const __nv_bfloat16* mrow = mask ? mask + (row % mask_rows) * (int64_t)cols : nullptr;
 
+  // A lane's vectors are live up to a lane-dependent count; dead vectors (past the row's end or
+  // wholly past the diagonal) are never touched.  Only a row's last live vector can straddle
+  // the diagonal and needs per-element masking.
   float x[VPL][8];
   float mx = -INFINITY;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int v = lane + 32 * i;
+    const int v = lane + kStride * i;
     const int c0 = v << 3;
-    const bool live = v < vecs && c0 < limit;  // a vector past the diagonal is neither read nor computed
-    if (live) {
+    if (v < vecs && c0 < limit) {
       const uint4 raw = __ldg(src + v);
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float s = __uint_as_float((j & 1) ? (w[j >> 1] & 0xFFFF0000u) : (w[j >> 1] << 16));
-        s = bf16r(__fmul_rn(s, score_scale));
-        if (mrow) s = bf16r(__fadd_rn(s, __bfloat162float(mrow[c0 + j])));
-        if (c0 + j >= limit) s = -INFINITY;
-        x[i][j] = s;
-        mx = fmaxf(mx, s);
+      for (int j = 0; j < 4; ++j) {
+        // s = bf16(score * scale) for the word's two elements with one packed conversion
+        const uint32_t pk = pack_bf16x2(__fmul_rn(__uint_as_float(w[j] << 16), score_scale),
+                                        __fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), score_scale));
+        x[i][2 * j] = __uint_as_float(pk << 16);
+        x[i][2 * j + 1] = __uint_as_float(pk & 0xFFFF0000u);
       }
-    } else {
+      if (mrow) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[i][j] = -INFINITY;
+        for (int j = 0; j < 8; ++j) x[i][j] = bf16r(__fadd_rn(x[i][j], __bfloat162float(mrow[c0 + j])));
+      }
+      if (c0 + 8 > limit) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (c0 + j >= limit) x[i][j] = -INFINITY;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, x[i][j]);
     }
   }
   for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+  if (WPR > 1) {
+    if ((threadIdx.x & 31) == 0) part_max[warp] = mx;
+    __syncthreads();
+    const int w0 = warp - warp % WPR;
+#pragma unroll
+    for (int k = 0; k < WPR; ++k) mx = fmaxf(mx, part_max[w0 + k]);
+  }
+  // exp(s - max) = 2^(s * log2(e) - max * log2(e)): one fused multiply-add and one ex2 per element.
+  // exp(-inf) = 0 for masked entries; a fully masked row (max = -inf) yields NaN, as torch.softmax does.
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float shift = -mx * kLog2e;
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int c0 = (lane + 32 * i) << 3;
-    if (c0 < limit && (lane + 32 * i) < vecs) {
+    const int v = lane + kStride * i;
+    if (v < vecs && (v << 3) < limit) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        // exp(-inf) = 0 for masked entries; a fully masked row (max = -inf) yields NaN, as torch.softmax does
-        const float e = __expf(x[i][j] - mx);
+        const float e = ex2_approx(fmaf(x[i][j], kLog2e, shift));
         x[i][j] = e;
         sum += e;
       }
     }
   }
   for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+  if (WPR > 1) {
+    if ((threadIdx.x & 31) == 0) part_sum[warp] = sum;
+    __syncthreads();
+    const int w0 = warp - warp % WPR;
+    sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < WPR; ++k) sum += part_sum[w0 + k];   // same order in both warps
+  }
 
   // p = bf16(e / sum), code = fp8(bf16(p / s_p)): both quotients are taken as products
   // with the correctly rounded reciprocal (within an ulp of the division before the
-  // bfloat16 rounding, like the exponential itself).
+  // bfloat16 rounding, like the exponential itself).  p >= 0, so no -0 can arise.
   const float rsum = __frcp_rn(sum), rsp = __frcp_rn(sp);
   uint2* dst = out + row * vecs;
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int v = lane + 32 * i;
+    const int v = lane + kStride * i;
     if (v >= vecs) continue;
     uint32_t o[2] = {0u, 0u};
     if ((v << 3) < limit) {
 #pragma unroll
       for (int j = 0; j < 8; j += 2) {
-        const float p0 = bf16r(__fmul_rn(bf16r(__fmul_rn(x[i][j], rsum)), rsp));
-        const float p1 = bf16r(__fmul_rn(bf16r(__fmul_rn(x[i][j + 1], rsum)), rsp));
-        const float2 f = make_float2(__fadd_rn(p0, 0.0f), __fadd_rn(p1, 0.0f));
-        const uint32_t q = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
-        o[j >> 2] |= q << (16 * ((j >> 1) & 1));
+        const uint32_t p = pack_bf16x2(__fmul_rn(x[i][j], rsum), __fmul_rn(x[i][j + 1], rsum));
+        const uint32_t q = pack_bf16x2(__fmul_rn(__uint_as_float(p << 16), rsp),
+                                       __fmul_rn(__uint_as_float(p & 0xFFFF0000u), rsp));
+        const float2 f = make_float2(__uint_as_float(q << 16), __uint_as_float(q & 0xFFFF0000u));
+        const uint32_t code = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, E4M3 ? __NV_E4M3 : __NV_E5M2);
+        o[j >> 2] |= code << (16 * ((j >> 1) & 1));
       }
     } else if (sum != sum) {
       o[0] = o[1] = E4M3 ? 0x7F7F7F7Fu : 0x7E7E7E7Eu;  // NaN row
@@ -107,21 +153,32 @@ softmax_quantize_kernel(const uint4* __restrict__ scores, uint2* __restrict__ ou
 }
 
 template <bool E4M3>
-int launch(int vpl, const void* scores, void* out, int64_t rows, int cols, float score_scale, const void* mask,
+int launch(int vecs, const void* scores, void* out, int64_t rows, int cols, float score_scale, const void* mask,
            int64_t mask_rows, int causal_period, const void* out_scale, int out_scale_dt, cudaStream_t st) {
-  const int64_t grid = (rows + kWarpsPerCta - 1) / kWarpsPerCta;
   const uint4* s = static_cast<const uint4*>(scores);
   uint2* o = static_cast<uint2*>(out);
   const __nv_bfloat16* m = static_cast<const __nv_bfloat16*>(mask);
-#define VQ_SM_CASE(V)                                                                                          \
-  case V:                                                                                                      \
-    softmax_quantize_kernel<V, E4M3><<<(unsigned)grid, kWarpsPerCta * 32, 0, st>>>(                          \
-        s, o, rows, cols, score_scale, m, mask_rows, causal_period, out_scale, out_scale_dt);                  \
-    break;
-  switch (vpl) {
-    VQ_SM_CASE(1) VQ_SM_CASE(2) VQ_SM_CASE(4) VQ_SM_CASE(8) VQ_SM_CASE(16)
-    default:
-      return fail(VQ_EUNSUPPORTED, "softmax row too long");
+  // rows of more than 1024 columns are shared by the four warps of a CTA
+  const int wpr = vecs > 128 ? 4 : 1;
+  int vpl = 1;
+  while (vpl * 32 * wpr < vecs) vpl <<= 1;
+  const int64_t rows_per_cta = kWarpsPerCta / wpr;
+  const int64_t grid = (rows + rows_per_cta - 1) / rows_per_cta;
+#define VQ_SM_CASE(V, W)                                                                                       \
+  softmax_quantize_kernel<V, W, E4M3><<<(unsigned)grid, kWarpsPerCta * 32, 0, st>>>(                         \
+      s, o, rows, cols, score_scale, m, mask_rows, causal_period, out_scale, out_scale_dt)
+  if (wpr == 1) {
+    switch (vpl) {
+      case 1: VQ_SM_CASE(1, 1); break;
+      case 2: VQ_SM_CASE(2, 1); break;
+      default: VQ_SM_CASE(4, 1); break;
+    }
+  } else {
+    switch (vpl) {
+      case 2: VQ_SM_CASE(2, 4); break;
+      case 4: VQ_SM_CASE(4, 4); break;
+      default: return fail(VQ_EUNSUPPORTED, "softmax row too long");
+    }
   }
 #undef VQ_SM_CASE
   return check_launch("softmax_quantize_kernel");
@@ -147,12 +204,10 @@ extern "C" int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t ro
   VQ_REQUIRE(((reinterpret_cast<uintptr_t>(scores) & 15) | (reinterpret_cast<uintptr_t>(out) & 7)) == 0,
              "vq_softmax_quantize_fp8: misaligned buffers");
   const int vecs = (int)(cols / 8);
-  int vpl = 1;
-  while (vpl * 32 < vecs) vpl <<= 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (format == VQ_IN_E4M3)
-    return launch<true>(vpl, scores, out, rows, (int)cols, score_scale, mask, mask_rows, (int)causal_period,
+    return launch<true>(vecs, scores, out, rows, (int)cols, score_scale, mask, mask_rows, (int)causal_period,
                         out_scale, out_scale_dtype, st);
-  return launch<false>(vpl, scores, out, rows, (int)cols, score_scale, mask, mask_rows, (int)causal_period,
+  return launch<false>(vecs, scores, out, rows, (int)cols, score_scale, mask, mask_rows, (int)causal_period,
                        out_scale, out_scale_dtype, st);
 }
