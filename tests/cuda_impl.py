@@ -53,3 +53,9 @@ CudaImpl.sdpa_mx = staticmethod(_wrap(Q.sdpa_mx))
 CudaImpl.quantize_mx_transpose = staticmethod(_wrap(Q.quantize_mx_transpose))
 CudaImpl.hadamard_rotate = staticmethod(_wrap(voyager_b200.ops.hadamard_rotate))
 CudaImpl.hadamard_matrix = staticmethod(voyager_b200.ops.hadamard_matrix)
+
+FQ = torch.ops.quantization
+CudaImpl.fake_quant = staticmethod(_wrap(FQ.fake_quant))
+CudaImpl.group_wise_affine_fake_quant = staticmethod(_wrap(FQ.group_wise_affine_fake_quant))
+CudaImpl.mx_fake_quant = staticmethod(_wrap(FQ.mx_fake_quant))
+CudaImpl.hadamard_amax = staticmethod(_wrap(FQ.hadamard_amax))

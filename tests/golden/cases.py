@@ -245,6 +245,30 @@ def build_cases(table):
     h2, t2 = hess(97, 96, 160, 4)  # rank-deficient -> damping escalation; partial last block
     add("gptq_partial_block", "gptq", randn(98, 16, 160, std=0.02, dtype=torch.float32), h2, t2,
         spec=dict(qmap=nf4, scale_qmap=e5m3, qmax=31.0, bs=64, damping=0.01, act_order=False, shrink=False))
+
+    # ---- fake-quant ops (quantization/ops.py) --------------------------------------------
+    xf = randn(120, 6, 48, 64, std=1.5, outliers=0.002)
+    add("fq_tensor_e4m3", "fake_quant", xf, e4m3, torch.tensor(0.011, dtype=BF16))
+    add("fq_tensor_f32_scale", "fake_quant", xf, int8, torch.tensor(0.0437, dtype=torch.float32))
+    add("fq_channel_int8", "fake_quant", randn(121, 40, 96, std=0.02),
+        int8, (randn(122, 40, 1, std=1.0).abs() * 4e-4 + 1e-4))
+    add("fq_f32_input", "fake_quant", randn(123, 5, 77, dtype=torch.float32), int6, torch.tensor(0.09))
+    add("gwa_uint4_bs32", "group_wise_affine_fake_quant", randn(124, 3, 16, 128), [-1], 32, 0.0, 15.0, None)
+    add("gwa_uint2_rows_e5m3", "group_wise_affine_fake_quant", randn(125, 1, 2, 128, 64), [-2], 64, 0.0, 3.0, e5m3)
+    add("gwa_partial_block", "group_wise_affine_fake_quant", randn(126, 5, 40), [-1], 16, 0.0, 255.0, None)
+    add("gwa_edges", "group_wise_affine_fake_quant", edge_blocks(), [-1], 16, 0.0, 15.0, e5m3)
+    add("mxfq_int8_pot", "mx_fake_quant", xf, int8, [-1], 16, 127.0, True, None, None, None, None, None)
+    add("mxfq_e2m1_e4m3_global", "mx_fake_quant", xf, e2m1, [-1], 16, 6.0, False, e4m3, None,
+        torch.tensor(0.0021, dtype=BF16), None, None)
+    add("mxfq_nf4_e5m3_rows", "mx_fake_quant", randn(127, 2, 128, 48), nf4, [-2], 64, 31.0, False, e5m3, None, None,
+        None, None)
+    add("mxfq_hadamard", "mx_fake_quant", randn(128, 3, 8, 40), e2m1, [-1], 16, 6.0, False, e4m3, None,
+        torch.tensor(0.002, dtype=BF16), "hadamard", -1)
+    add("mxfq_edges", "mx_fake_quant", edge_blocks(), int8, [-1], 16, 127.0, True, None, None, None, None, None)
+    add("mxfq_stochastic", "mx_fake_quant", randn(129, 4, 64, std=3.0), torch.arange(-7.0, 8.0).to(BF16), [-1], 16, 7.0,
+        True, None, torch.tensor(1234, dtype=torch.int64), None, None, None)
+    add("hadamard_amax_last", "hadamard_amax", randn(130, 3, 8, 40), -1, "hadamard")
+    add("hadamard_amax_rows", "hadamard_amax", randn(131, 3, 24, 8), -2, "hadamard")
     return cases
 
 

@@ -52,6 +52,11 @@ class ReferenceImpl:
                      "quantize_affine", "linear_mx", "matmul_mx", "sdpa_mx", "hadamard_rotate",
                      "quantize_mx_transpose"):
             setattr(self, name, getattr(q, name))
+        import importlib
+
+        fake_quant_ops = importlib.import_module("voyager_compiler.quantization.ops")
+        for name in ("fake_quant", "group_wise_affine_fake_quant", "mx_fake_quant", "hadamard_amax"):
+            setattr(self, name, getattr(fake_quant_ops, name))
         self.calculate_global_scale = self.fq.calculate_global_scale
         self.hadamard_matrix = self.fq.hadamard_matrix
         self.dense_linear = torch.nn.functional.linear

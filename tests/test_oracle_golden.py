@@ -5,6 +5,7 @@ import torch
 
 import cases as C
 from golden_io import bits_equal, describe_mismatch, golden_cases, golden_tables
+from oracle import fake_quant as fq_oracle
 from oracle import gemm, gptq, quantizers, tables
 
 
@@ -25,6 +26,10 @@ class OracleImpl:
     sdpa_mx = staticmethod(gemm.sdpa_mx)
     dense_linear = staticmethod(torch.nn.functional.linear)
     compensate_weight = staticmethod(gptq.compensate_weight)
+    fake_quant = staticmethod(fq_oracle.fake_quant)
+    group_wise_affine_fake_quant = staticmethod(fq_oracle.group_wise_affine_fake_quant)
+    mx_fake_quant = staticmethod(fq_oracle.mx_fake_quant)
+    hadamard_amax = staticmethod(fq_oracle.hadamard_amax)
 
 
 @pytest.mark.parametrize("name", sorted(golden_tables()))
