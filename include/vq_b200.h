@@ -104,6 +104,24 @@ int vq_dequantize(const void* in, const void* scale, const void* zero_point, voi
                   int param_dtype, const VqBroadcast* geom, const VqRound* round_in,
                   const VqRound* round_out, void* stream);
 
+/* Packed integer codes for a 2-bit (or 4-bit) KV cache: the storage form of the
+ * codes quantized_ops::quantize_affine yields for a KIVI cache
+ * (examples/language_modeling/quantization_configs.py:171-207; the reference keeps
+ * them as bfloat16-valued tensors and its quant_folding pass,
+ * codegen/transform/quant_folding.py:2391-2547, reads them back through one fused
+ * dequantize).  Element i of the row-major tensor sits in byte i / (8 / bits) at
+ * bit bits * (i % (8 / bits)).
+ *
+ * vq_pack_codes: `codes` holds n integers in [0, 2^bits) as values of `dtype`.
+ * vq_unpack_dequantize: out = round_out((code - zero_point) * scale), bit for bit
+ * what vq_dequantize gives on the unpacked codes (the fused decode + re-encode of
+ * quant_folding.py:2524-2527 when round_out is the re-encoding table); geom,
+ * param_dtype and the roundings are as for vq_dequantize; `dtype` is out's. */
+int vq_pack_codes(const void* codes, int dtype, void* packed, int bits, int64_t n, void* stream);
+int vq_unpack_dequantize(const void* packed, int bits, const void* scale, const void* zero_point, void* out,
+                         int dtype, int param_dtype, const VqBroadcast* geom, const VqRound* round_out,
+                         void* stream);
+
 /* Microscaling block geometry: the input is a dense [O, A, M, B, I] tensor
  * whose blocks span block_a consecutive indices of A and block_b of B (1 =
  * axis not blocked); scales are dense [O, ceil(A/block_a), M, ceil(B/block_b), I]. */

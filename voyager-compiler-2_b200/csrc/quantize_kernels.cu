@@ -211,6 +211,63 @@ generic_map_kernel(const void* __restrict__ in, const void* __restrict__ scale, 
   }
 }
 
+// ---------------------------------------------------------------------------
+// packed integer codes (a KIVI-style 2- or 4-bit cache)
+// ---------------------------------------------------------------------------
+// Element i (row-major flat index) lives in byte i / (8 / BITS), at bit BITS * (i % (8 / BITS)).
+// A thread handles 8 consecutive elements: BITS bytes of packed codes.
+template <int DT, int BITS>
+__global__ void __launch_bounds__(kThreads)
+pack_codes_kernel(const void* __restrict__ codes, uint8_t* __restrict__ packed, int64_t n) {
+  const int64_t groups = (n + 7) / 8;
+  for (int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < groups; gi += (int64_t)gridDim.x * blockDim.x) {
+    uint64_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t i = gi * 8 + j;
+      if (i < n) {
+        const int c = __float2int_rn(load1<DT>(codes, i));
+        word |= (uint64_t)((uint32_t)c & ((1u << BITS) - 1u)) << (BITS * j);
+      }
+    }
+    const int64_t nbytes = (n * BITS + 7) / 8;
+#pragma unroll
+    for (int b = 0; b < BITS; ++b)
+      if (gi * BITS + b < nbytes) packed[gi * BITS + b] = (uint8_t)(word >> (8 * b));
+  }
+}
+
+// out = round_out((code - zero_point) * scale), the dequantize of the codes' bf16-valued form.
+template <int DT, int BITS>
+__global__ void __launch_bounds__(kThreads, 4)
+unpack_dequantize_kernel(const uint8_t* __restrict__ packed, const void* __restrict__ scale,
+                         const void* __restrict__ zp, void* __restrict__ out, Geom g, Round r_out, int64_t n,
+                         int pdt) {
+  __shared__ uint16_t s_steps[2][2 * VQ_MAX_STEPS];
+  Round none{};
+  none.mode = VQ_ROUND_NONE;
+  stage_steps(r_out, s_steps[1]);
+  const bool has_z = zp != nullptr;
+  const int64_t groups = (n + 7) / 8;
+  const int64_t nbytes = (n * BITS + 7) / 8;
+  for (int64_t gi = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gi < groups; gi += (int64_t)gridDim.x * blockDim.x) {
+    uint64_t word = 0;
+#pragma unroll
+    for (int b = 0; b < BITS; ++b)
+      if (gi * BITS + b < nbytes) word |= (uint64_t)packed[gi * BITS + b] << (8 * b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int64_t i = gi * 8 + j;
+      if (i >= n) break;
+      const float code = (float)((word >> (BITS * j)) & ((1u << BITS) - 1u));
+      const int64_t pi = param_index(g, i);
+      const float s = loadp(scale, pi, pdt);
+      const float z = has_z ? loadp(zp, pi, pdt) : 0.0f;
+      store1<DT>(out, i, map_one<DT, 1>(code, s, z, has_z, none, r_out, i));
+    }
+  }
+}
+
 // Fastest path: blocks along the contiguous last axis and K a whole number of
 // blocks, so the tensor is a flat run of blocks: vector v belongs to block
 // v / G (G = block / V lanes, a power of two) and no row arithmetic is needed.
@@ -817,6 +874,40 @@ int vq_dequantize(const void* in, const void* scale, const void* zero_point, voi
                   int param_dtype, const VqBroadcast* geom, const VqRound* round_in, const VqRound* round_out,
                   void* stream) {
   return scale_map(1, in, scale, zero_point, out, dtype, param_dtype, geom, round_in, round_out, stream);
+}
+
+int vq_pack_codes(const void* codes, int dtype, void* packed, int bits, int64_t n, void* stream) {
+  VQ_REQUIRE(n >= 0, "vq_pack_codes: negative size");
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(codes && packed, "vq_pack_codes: null argument");
+  VQ_REQUIRE(bits == 2 || bits == 4 || bits == 8, "vq_pack_codes: bits must be 2, 4 or 8");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for((n + 7) / 8, kThreads, 8);
+#define VQ_PACK(B) VQ_DISPATCH_DTYPE(dtype, (pack_codes_kernel<DT, B><<<grid, kThreads, 0, st>>>(codes, static_cast<uint8_t*>(packed), n)))
+  if (bits == 2) { VQ_PACK(2); } else if (bits == 4) { VQ_PACK(4); } else { VQ_PACK(8); }
+#undef VQ_PACK
+  return check_launch("pack_codes_kernel");
+}
+
+int vq_unpack_dequantize(const void* packed, int bits, const void* scale, const void* zero_point, void* out,
+                         int dtype, int param_dtype, const VqBroadcast* geom, const VqRound* round_out,
+                         void* stream) {
+  Geom g;
+  int64_t n;
+  if (int e = to_geom(geom, &g, &n)) return e;
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(packed && scale && out, "vq_unpack_dequantize: null argument");
+  VQ_REQUIRE(bits == 2 || bits == 4 || bits == 8, "vq_unpack_dequantize: bits must be 2, 4 or 8");
+  VQ_REQUIRE(param_dtype >= VQ_BF16 && param_dtype <= VQ_F32, "vq_unpack_dequantize: bad parameter dtype");
+  if (int e = validate_round(round_out, "output rounding")) return e;
+  Round ro = make_round(round_out);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for((n + 7) / 8, kThreads, 8);
+  const uint8_t* src = static_cast<const uint8_t*>(packed);
+#define VQ_UNPACK(B) VQ_DISPATCH_DTYPE(dtype, (unpack_dequantize_kernel<DT, B><<<grid, kThreads, 0, st>>>(src, scale, zero_point, out, g, ro, n, param_dtype)))
+  if (bits == 2) { VQ_UNPACK(2); } else if (bits == 4) { VQ_UNPACK(4); } else { VQ_UNPACK(8); }
+#undef VQ_UNPACK
+  return check_launch("unpack_dequantize_kernel");
 }
 
 static inline bool empty_blocks(const VqBlocks* b) {

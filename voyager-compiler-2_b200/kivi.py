@@ -1,0 +1,85 @@
+"""A packed KIVI key/value cache on the CUDA kernels.
+
+The reference quantizes a decode KV cache the KIVI way -- unsigned 2-bit (or 4-bit) codes
+with one scale and zero point per group of 64, keys grouped along the sequence
+(``ax=-2``), values along the head dimension (``ax=-1``), qparams rounded to FP8
+(``examples/language_modeling/quantization_configs.py:171-207``) -- with
+``quantized_ops::quantize_affine``, keeps the codes as bfloat16-valued tensors (2 bytes per
+2-bit code) and reads them back through one fused ``quantized_ops::dequantize`` that also
+re-encodes them for the attention matmul (``codegen/transform/quant_folding.py:2391-2547``).
+
+Here the same codes are stored packed (four 2-bit codes per byte, an eighth of the bytes the
+decode step reads), and ``read`` is that fused dequantize straight from the packed bytes:
+bit for bit what the operators give on the unpacked codes.
+"""
+
+import dataclasses
+from typing import List, Optional
+
+import torch
+
+from . import _native as N
+from . import rounding as R
+from .ops import _broadcast_geometry, _dtype_id, _prepare_params, _ptr, _stream
+
+Q = torch.ops.quantized_ops
+
+
+def pack_codes(codes: torch.Tensor, bits: int) -> torch.Tensor:
+    """Integer codes in ``[0, 2**bits)`` (values of a float tensor) as packed bytes: element ``i`` of
+    the row-major tensor sits in byte ``i // (8 // bits)`` at bit ``bits * (i % (8 // bits))``."""
+    codes = codes.contiguous()
+    n = codes.numel()
+    packed = torch.empty((n * bits + 7) // 8, dtype=torch.uint8, device=codes.device)
+    N.check(N.lib().vq_pack_codes(codes.data_ptr(), _dtype_id(codes.dtype), packed.data_ptr(), bits, n, _stream()),
+            "vq_pack_codes")
+    return packed
+
+
+def unpack_dequantize(packed: torch.Tensor, bits: int, shape, scale: torch.Tensor,
+                      zero_point: Optional[torch.Tensor] = None, block_size: Optional[int] = None,
+                      output_qmap: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``round_out((code - zero_point) * scale)`` for packed codes of a tensor of ``shape``: what
+    ``quantized_ops::dequantize(codes, scale, zero_point, axes, block_size, None, output_qmap)``
+    returns for the unpacked codes (reference ``ops/quantized.py:527-571``)."""
+    # the codes count as a tensor of the parameters' dtype, as the stored bfloat16-valued codes are
+    like = torch.empty(0, dtype=scale.dtype, device=scale.device)
+    _, scale, zero_point = _prepare_params(like, scale, zero_point)
+    out = torch.empty(tuple(shape), dtype=scale.dtype, device=packed.device)
+    geom = _broadcast_geometry(tuple(shape), scale, block_size)
+    r_out = R.none_round() if output_qmap is None else R.table_round(output_qmap)
+    N.check(N.lib().vq_unpack_dequantize(packed.data_ptr(), bits, scale.data_ptr(), _ptr(zero_point), out.data_ptr(),
+                                         _dtype_id(out.dtype), _dtype_id(scale.dtype), geom, r_out.ref, _stream()),
+            "vq_unpack_dequantize")
+    return out
+
+
+@dataclasses.dataclass
+class PackedCache:
+    """One quantized cache tensor: packed codes plus per-group scale and zero point."""
+
+    packed: torch.Tensor          # uint8, ceil(numel * bits / 8) bytes
+    scale: torch.Tensor           # one per group, the tensor's dtype
+    zero_point: torch.Tensor
+    shape: tuple
+    axes: List[int]
+    block_size: int
+    bits: int
+
+    @property
+    def nbytes(self) -> int:
+        return self.packed.numel() + self.scale.numel() * self.scale.element_size() * 2
+
+    def read(self, output_qmap: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The cache's values, optionally re-encoded through ``output_qmap`` in the same pass."""
+        return unpack_dequantize(self.packed, self.bits, self.shape, self.scale, self.zero_point, self.block_size,
+                                 output_qmap)
+
+
+def quantize_cache(x: torch.Tensor, qmap: torch.Tensor, axis: int, block_size: int, bits: int,
+                   scale_qmap: Optional[torch.Tensor] = None) -> PackedCache:
+    """Quantize ``x`` in groups of ``block_size`` along ``axis`` to unsigned ``bits``-bit codes
+    (``quantize_affine``, reference ``ops/quantized.py:1227-1283``) and pack them."""
+    axes = [axis]
+    scale, zero_point, codes = Q.quantize_affine(x, qmap, axes, block_size, 0.0, float(2 ** bits - 1), scale_qmap)
+    return PackedCache(pack_codes(codes, bits), scale, zero_point, tuple(x.shape), axes, block_size, bits)
