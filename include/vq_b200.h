@@ -250,6 +250,14 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
  *   2  A[r][k] is zero for k > t (the probabilities of P V): the contraction of a
  *      tile may stop after the largest t among its rows.
  * Both are permissions, not requests: results the caller may read are unchanged.
+ * gate_scale (device scalar of gate_scale_dtype, may be NULL) selects the gated
+ * (SwiGLU) epilogue for a B whose rows interleave 32 rows of the gate projection
+ * with the matching 32 rows of the up projection: C is then [batch, M, N / 2]
+ * e4m3 bytes (ldc and strideC in bytes, rows 16-byte aligned) holding
+ *   e4m3(bf16(bf16(bf16(silu(g)) * u) / gate_scale)),  g, u = bf16(alpha * alpha_cols * acc)
+ * -- gate/up linears, SiLU, product and the FP8 cast of the next linear's input
+ * (backend/gpu/fp8.py:253-261) in one kernel, with every bfloat16 rounding of the
+ * unfused sequence.  out_dtype must be VQ_BF16, N a multiple of 64, no bias or residual.
  * epi == NULL is vq_gemm_tn. */
 typedef struct VqGemmEpilogue {
   const void* alpha_cols;
@@ -258,6 +266,8 @@ typedef struct VqGemmEpilogue {
   int64_t ldr, strideR;
   int32_t causal_mode;
   int64_t causal_period;
+  const void* gate_scale;
+  int32_t gate_scale_dtype;
 } VqGemmEpilogue;
 int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dtype, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA,

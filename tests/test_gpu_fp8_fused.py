@@ -266,3 +266,22 @@ def test_gemm_narrow_outputs(m, n, k):
     got = vb.ops.gemm_tn(a.cuda(), b.cuda()).cpu()
     vb.ops.gemm_status()
     assert float((got.double() - want).abs().max() / want.abs().max()) <= 1e-2
+
+
+@pytest.mark.parametrize("m,inter,k", [(300, 96, 128), (512, 256, 256), (64, 64, 64)])
+def test_gated_gemm_equals_gemm_then_silu_mul_cast(m, inter, k):
+    """The SwiGLU epilogue gives the bytes of the unfused sequence: merged GEMM, then SiLU * up + cast."""
+    vb = _vb()
+    g = torch.Generator().manual_seed(m + inter)
+    x = torch.randn(m, k, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    wg = torch.randn(inter, k, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    wu = torch.randn(inter, k, generator=g).to(torch.float8_e4m3fn).view(torch.uint8).cuda()
+    cols = torch.cat([torch.full((inter,), 0.011), torch.full((inter,), 0.017)]).cuda()
+    merged = vb.fp8.fp8_gemm(x, torch.cat([wg, wu]), alpha_cols=cols)
+    scale = ((torch.nn.functional.silu(merged[:, :inter]) * merged[:, inter:]).abs().amax() / 448.0).to(torch.bfloat16)
+    want = vb.fp8.silu_mul_quantize_fp8(merged[:, :inter], merged[:, inter:], scale)
+    got = vb.fp8.fp8_gemm(x, vb.fp8.interleave_gate_up(wg, wu),
+                          alpha_cols=vb.fp8.interleave_gate_up(cols[:inter], cols[inter:]), gated_scale=scale)
+    vb.ops.gemm_status()
+    assert got.shape == (m, inter) and got.dtype == torch.uint8
+    assert torch.equal(got, want)

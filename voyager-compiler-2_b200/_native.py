@@ -71,6 +71,7 @@ class VqGemmEpilogue(ctypes.Structure):
         ("alpha_cols", ctypes.c_void_p), ("alpha_cols_dtype", ctypes.c_int32),
         ("residual", ctypes.c_void_p), ("ldr", ctypes.c_int64), ("strideR", ctypes.c_int64),
         ("causal_mode", ctypes.c_int32), ("causal_period", ctypes.c_int64),
+        ("gate_scale", ctypes.c_void_p), ("gate_scale_dtype", ctypes.c_int32),
     ]
 
 

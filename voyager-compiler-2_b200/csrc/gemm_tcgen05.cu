@@ -21,6 +21,9 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <cuda_fp8.h>
+
+#include "quantize_shared.cuh"
 #include "sm100_ptx.cuh"
 #include "vq_common.cuh"
 
@@ -62,6 +65,8 @@ struct GemmParams {
   int causal_mode;          // 1: tiles whose columns all exceed t are not computed; 2: A is zero beyond column t
   int bn;                   // CTA-pair kernel: tile width, 256 or 128
   int tma_store;            // the output has a tensor map: staged rows leave shared memory as TMA stores
+  const void* gate_scale;   // gated mode (SwiGLU): per-tensor scale of the e4m3 output, or null
+  int gate_scale_dt;
   int out_dt;
   uint32_t idesc;
   int kind_f8;
@@ -393,11 +398,73 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
   }
 }
 
+// Gated epilogue (SwiGLU): the tile's columns alternate between 32 gate columns and their 32 up
+// columns (the caller interleaved the two weight matrices that way), so a warp's consecutive
+// 32-column chunks are a (gate, up) pair.  Per pair and row:
+//   g = bf16(gate), u = bf16(up)            the two linears' outputs as a bfloat16 GEMM rounds them
+//   a = bf16(bf16(silu(g)) * u)             the activation, every rounding of the unfused graph kept
+//   C = e4m3(bf16(a / scale))               32 bytes per row: one full sector per lane, stored directly
+// C is [M, N / 2] bytes.
+__device__ __forceinline__ void epilogue_warp_tile_gated(const GemmParams& p, uint32_t taddr, int row0, int lane,
+                                                         int n0, int b, bool has_alpha, float alpha, int c_begin,
+                                                         int c_end) {
+  const int my_row = row0 + lane;
+  uint8_t* out_row = static_cast<uint8_t*>(p.C) + (int64_t)b * p.strideC + (int64_t)my_row * p.ldc;
+  const float s_out = load_param(p.gate_scale, 0, p.gate_scale_dt);
+  const bool ordinary = ordinary_divisor(s_out);
+  const float r_out = __frcp_rn(s_out);
+  uint32_t va[32], vb[32];
+  tmem_ld_32x32(taddr + (uint32_t)c_begin, va);
+#pragma unroll 1
+  for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+    tmem_ld_wait();
+    tmem_ld_32x32(taddr + (uint32_t)(c0 + 32), vb);
+    float f[32];
+    scale_chunk(p, va, f, n0 + c0, has_alpha, alpha);
+    uint32_t g[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) g[j] = pack_pair<VQ_BF16>(f[2 * j], f[2 * j + 1]);
+    tmem_ld_wait();
+    if (c0 + 64 < c_end) tmem_ld_32x32(taddr + (uint32_t)(c0 + 64), va);
+    scale_chunk(p, vb, f, n0 + c0 + 32, has_alpha, alpha);
+    uint32_t q[8];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t u = pack_pair<VQ_BF16>(f[2 * j], f[2 * j + 1]);
+      const float g0 = __uint_as_float(g[j] << 16), g1 = __uint_as_float(g[j] & 0xFFFF0000u);
+      const uint32_t sl = pack_pair<VQ_BF16>(__fdividef(g0, 1.0f + __expf(-g0)), __fdividef(g1, 1.0f + __expf(-g1)));
+      const uint32_t a = pack_pair<VQ_BF16>(__fmul_rn(__uint_as_float(sl << 16), __uint_as_float(u << 16)),
+                                            __fmul_rn(__uint_as_float(sl & 0xFFFF0000u), __uint_as_float(u & 0xFFFF0000u)));
+      const float a0 = __uint_as_float(a << 16), a1 = __uint_as_float(a & 0xFFFF0000u);
+      float y0, y1;
+      if (ordinary) {
+        y0 = div_to_bf16(a0, s_out, r_out);
+        y1 = div_to_bf16(a1, s_out, r_out);
+      } else {
+        y0 = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(a0, s_out)));
+        y1 = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(a1, s_out)));
+      }
+      const uint32_t code = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fadd_rn(y0, 0.0f), __fadd_rn(y1, 0.0f)),
+                                                               __NV_SATFINITE, __NV_E4M3);
+      if (j & 1) q[j >> 1] |= code << 16; else q[j >> 1] = code;
+    }
+    if (my_row < p.M && n0 + c0 < p.N) {
+      uint4* dst = reinterpret_cast<uint4*>(out_row + ((n0 + c0) >> 1));
+      dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
+      dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
+    }
+  }
+}
+
 template <int OUT_DT>
 __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
                                                    uint8_t* stage, int row0, int lane, int n0, int b, bool has_alpha,
                                                    float alpha, int c_begin, int c_end) {
   constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
+  if (OUT_DT == VQ_BF16 && p.gate_scale != nullptr) {   // gated launches use the bfloat16 instantiation
+    epilogue_warp_tile_gated(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
+    return;
+  }
   if (((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * ESZ) | (uintptr_t)(p.strideC * ESZ)) & 15) != 0) {
     epilogue_warp_tile_unstaged(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
     return;
@@ -1008,7 +1075,8 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
              "vq_gemm_tn: operands must be 16-byte aligned");
   VQ_REQUIRE((lda * eb) % 16 == 0 && (ldb * eb) % 16 == 0 && (strideA * eb) % 16 == 0 && (strideB * eb) % 16 == 0,
              "vq_gemm_tn: leading dimensions and batch strides must be multiples of 16 bytes");
-  VQ_REQUIRE(lda >= K && ldb >= K && ldc >= N, "vq_gemm_tn: leading dimension smaller than the row");
+  VQ_REQUIRE(lda >= K && ldb >= K && (ldc >= N || (epi != nullptr && epi->gate_scale != nullptr)),
+             "vq_gemm_tn: leading dimension smaller than the row");
   VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && batch < (1ll << 31), "vq_gemm_tn: extent too large");
 
   const int kind = in_kind == VQ_IN_F16 ? VQ_F16 : VQ_BF16;
@@ -1031,6 +1099,15 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
       VQ_REQUIRE(epi->ldr >= N, "vq_gemm_tn_ex: residual leading dimension smaller than the row");
       VQ_REQUIRE(epi->residual != C, "vq_gemm_tn_ex: the residual must not alias the output");
       p.residual = epi->residual; p.ldr = epi->ldr; p.strideR = epi->strideR;
+    }
+    if (epi->gate_scale != nullptr) {
+      VQ_REQUIRE(out_dtype == VQ_BF16 && bias == nullptr && epi->residual == nullptr,
+                 "vq_gemm_tn_ex: the gated epilogue takes out_dtype VQ_BF16 (of the two linears), no bias, no residual");
+      VQ_REQUIRE(N % 64 == 0, "vq_gemm_tn_ex: the gated epilogue needs N (gate and up columns together) to be a multiple of 64");
+      VQ_REQUIRE(ldc >= N / 2 && ldc % 16 == 0 && strideC % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0,
+                 "vq_gemm_tn_ex: the gated output is [M, N/2] bytes, 16-byte aligned rows");
+      VQ_REQUIRE(epi->gate_scale_dtype >= VQ_BF16 && epi->gate_scale_dtype <= VQ_F32, "vq_gemm_tn_ex: bad gate scale dtype");
+      p.gate_scale = epi->gate_scale; p.gate_scale_dt = epi->gate_scale_dtype;
     }
     if (epi->causal_mode != 0) {
       VQ_REQUIRE((epi->causal_mode == 1 || epi->causal_mode == 2) && epi->causal_period > 0 &&
@@ -1073,7 +1150,11 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
     }
   }
   CUtensorMap map_c;
-  if (int e = make_output_map(&map_c, &p.tma_store, C, out_dtype, M, N, ldc, batch, strideC)) return e;
+  if (p.gate_scale != nullptr) {
+    memset(&map_c, 0, sizeof(map_c));   // the gated epilogue stores from registers
+  } else if (int e = make_output_map(&map_c, &p.tma_store, C, out_dtype, M, N, ldc, batch, strideC)) {
+    return e;
+  }
   if (pair_mode == 1 && M > BM) {
     CUtensorMap map_a, map_b;
     if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;

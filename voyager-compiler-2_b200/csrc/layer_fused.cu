@@ -139,11 +139,23 @@ rope_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv
   const int vpd = d >> 3;          // 8-element vectors per head row; strides are in vectors here
   const int half = vpd >> 1;
   const int64_t total = (int64_t)T * heads * vpd;
+  // vpd a power of two (head_dim 64, 128, ...): the vector within the head row is a mask of the
+  // thread index and one 32-bit division splits the head row's index into (t, h)
+  const bool pow2 = (vpd & (vpd - 1)) == 0 && (int64_t)T * heads < (1ll << 31);
+  const int vshift = 31 - __clz(vpd);
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
-    const int v = (int)(idx % vpd);
-    const int h = (int)((idx / vpd) % heads);
-    const int t = (int)(idx / ((int64_t)vpd * heads));
+    int v, h, t;
+    if (pow2) {
+      v = (int)(idx & (vpd - 1));
+      const uint32_t r = (uint32_t)(idx >> vshift);
+      t = (int)(r / (uint32_t)heads);
+      h = (int)(r - (uint32_t)t * (uint32_t)heads);
+    } else {
+      v = (int)(idx % vpd);
+      h = (int)((idx / vpd) % heads);
+      t = (int)(idx / ((int64_t)vpd * heads));
+    }
     const uint4* row = x + t * in_t + h * in_h;
     const uint4 xv = __ldg(row + v);
     uint32_t o[2] = {0, 0};

@@ -60,12 +60,22 @@ def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torc
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, alpha: Optional[torch.Tensor] = None,
              bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, dtype: str = "fp8_e4m3",
              alpha_cols: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-             causal=None) -> torch.Tensor:
+             causal=None, gated_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``alpha * alpha_cols[n] * (a @ b^T) + bias`` (+ ``residual`` after the rounding) for FP8 byte
     operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation;
-    ``causal`` as for ``ops.gemm_tn``."""
+    ``causal`` and ``gated_scale`` as for ``ops.gemm_tn``."""
     return gemm_tn(a, b, out_dtype=out_dtype, alpha=alpha, bias=bias, in_kind=_FORMATS[dtype],
-                   alpha_cols=alpha_cols, residual=residual, causal=causal)
+                   alpha_cols=alpha_cols, residual=residual, causal=causal, gated_scale=gated_scale)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, chunk: int = 32) -> torch.Tensor:
+    """Rows of two ``[I, ...]`` tensors (weights, or per-row scales) alternating in runs of ``chunk``:
+    the row order the gated GEMM epilogue expects of its B operand and of ``alpha_cols``."""
+    if gate.shape != up.shape or gate.shape[0] % chunk:
+        raise ValueError("gate and up must have one shape with a multiple of 32 rows")
+    g = gate.reshape(gate.shape[0] // chunk, 1, chunk, *gate.shape[1:])
+    u = up.reshape(up.shape[0] // chunk, 1, chunk, *up.shape[1:])
+    return torch.cat([g, u], 1).reshape(2 * gate.shape[0], *gate.shape[1:]).contiguous()
 
 
 def _as_bytes(t: torch.Tensor):

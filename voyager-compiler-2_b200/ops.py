@@ -572,7 +572,7 @@ def _parse_layout(layout: str):
 
 
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None,
-            alpha_cols=None, residual=None, causal=None):
+            alpha_cols=None, residual=None, causal=None, gated_scale=None):
     """``out[..., m, n] = alpha * sum_k a[..., m, k] * b[..., n, k] + bias[n]`` on the
     tensor cores (fp32 accumulation, one rounding to ``out_dtype``).
 
@@ -581,7 +581,9 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
     rounded again, as ``residual + linear(...)`` would be.  ``causal=("scores", T)`` says
     that ``out[..., r, n]`` with ``n > r % T`` is never read (tiles of only such elements may
     stay unwritten); ``causal=("probabilities", T)`` that ``a[..., r, k]`` is zero for
-    ``k > r % T`` (the contraction may stop early).
+    ``k > r % T`` (the contraction may stop early).  ``gated_scale`` selects the SwiGLU epilogue:
+    ``b``'s rows interleave 32 gate rows with their 32 up rows and the result is the ``[..., N / 2]``
+    e4m3 bytes of ``(silu(gate) * up) / gated_scale``.
 
     ``a`` is ``[*batch, M, K]`` and ``b`` ``[*batch, N, K]`` or ``[N, K]``; both are
     used K-contiguous.  ``in_kind`` overrides the operand element kind for 8-bit
@@ -615,12 +617,23 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
         batch, rows = a2.shape[0], m
         stride_a, stride_b = m * k, n * k
     out_dtype = out_dtype or (a.dtype if a.dtype in _DTYPE_ID else torch.bfloat16)
-    out = torch.empty((batch, rows, n), dtype=out_dtype, device=a.device)
+    n_out = n
+    if gated_scale is not None:
+        if n % 64 or out_dtype != torch.bfloat16 or bias is not None or residual is not None or k == 0:
+            raise NotImplementedError("the gated epilogue takes bfloat16 linears with N a multiple of 64, no bias, "
+                                      "no residual")
+        n_out = n // 2
+        out = torch.empty((batch, rows, n_out), dtype=torch.uint8, device=a.device)
+    else:
+        out = torch.empty((batch, rows, n), dtype=out_dtype, device=a.device)
     if bias is not None:
         bias = bias.contiguous()
     epi = None
-    if alpha_cols is not None or residual is not None or causal is not None:
+    if alpha_cols is not None or residual is not None or causal is not None or gated_scale is not None:
         epi = N.VqGemmEpilogue()
+        if gated_scale is not None:
+            gated_scale = _as_scalar_param(gated_scale, a.device)
+            epi.gate_scale, epi.gate_scale_dtype = gated_scale.data_ptr(), _dtype_id(gated_scale.dtype)
         if causal is not None:
             epi.causal_mode = {"scores": 1, "probabilities": 2}[causal[0]]
             epi.causal_period = int(causal[1])
@@ -643,10 +656,10 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
                 out += residual.reshape(out.shape)
         else:
             N.check(N.lib().vq_gemm_tn_ex(
-                a2.data_ptr(), b2.data_ptr(), out.data_ptr(), in_kind, _dtype_id(out_dtype), rows, n, k, k, k, n,
-                batch, stride_a, stride_b, rows * n, _ptr(alpha), 0 if alpha is None else _dtype_id(alpha.dtype),
+                a2.data_ptr(), b2.data_ptr(), out.data_ptr(), in_kind, _dtype_id(out_dtype), rows, n, k, k, k, n_out,
+                batch, stride_a, stride_b, rows * n_out, _ptr(alpha), 0 if alpha is None else _dtype_id(alpha.dtype),
                 _ptr(bias), 0 if bias is None else _dtype_id(bias.dtype), epi, _stream()), "vq_gemm_tn_ex")
-    return out.reshape(*batch_shape, m, n) if b.dim() > 2 else out.reshape(*a.shape[:-1], n)
+    return out.reshape(*batch_shape, m, n_out) if b.dim() > 2 else out.reshape(*a.shape[:-1], n_out)
 
 
 def _as_scalar_param(t, device):

@@ -136,9 +136,11 @@ def calibrate_fp8_scales(x, params, shape: LlamaShape):
 class Fp8DecoderLayer:
     """FP8 per-tensor decoder layer on the CUDA kernels (prefill, batch 1)."""
 
-    def __init__(self, params, scales, shape: LlamaShape, merge_qkv=True, merge_gate_up=True, fuse_residual=True):
+    def __init__(self, params, scales, shape: LlamaShape, merge_qkv=True, merge_gate_up=True, fuse_residual=True,
+                 fuse_swiglu=True):
         self.shape = shape
         self.merge_qkv, self.merge_gate_up, self.fuse_residual = merge_qkv, merge_gate_up, fuse_residual
+        self.fuse_swiglu = fuse_swiglu
         self.scales = scales
         self.ln1, self.ln2 = params["ln1"], params["ln2"]
         # weights are cast once, as convert_pt2e bakes them
@@ -155,11 +157,15 @@ class Fp8DecoderLayer:
             return w, a
         self.w8_qkv, self.alpha_qkv = merged(("q", "k", "v"))
         self.w8_gate_up, self.alpha_gate_up = merged(("gate", "up"))
+        # the same two linears with rows interleaved in runs of 32, for the GEMM whose epilogue is SiLU * up + cast
+        inter = shape.intermediate
+        self.w8_swiglu = FP8.interleave_gate_up(self.w8["gate"], self.w8["up"])
+        self.alpha_swiglu = FP8.interleave_gate_up(self.alpha_gate_up[:inter], self.alpha_gate_up[inter:])
         self._rope = None
         self._mask = None
 
-    #: kernels of this package launched per forward (7 fused casts + softmax + 6 GEMMs)
-    LAUNCHES = 7 + 1 + 6
+    #: kernels of this package launched per forward (6 fused casts + softmax + 6 GEMMs)
+    LAUNCHES = 6 + 1 + 6
 
     def _tables(self, T, device):
         if self._rope is None or self._rope[0].shape[0] != T:
@@ -198,12 +204,16 @@ class Fp8DecoderLayer:
         else:
             x1 = x + FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"])
         h28 = FP8.rmsnorm_quantize_fp8(x1, self.ln2, sh.eps, s["h2"])
-        if self.merge_gate_up:
-            gu = FP8.fp8_gemm(h28, self.w8_gate_up, alpha_cols=self.alpha_gate_up)   # [T, 2 * intermediate]
-            gate, up = gu[:, :sh.intermediate], gu[:, sh.intermediate:]
+        if self.fuse_swiglu and sh.intermediate % 32 == 0:
+            # gate and up linears, SiLU, product and the cast of down_proj's input in one GEMM
+            act8 = FP8.fp8_gemm(h28, self.w8_swiglu, alpha_cols=self.alpha_swiglu, gated_scale=s["act"])
         else:
-            gate, up = (FP8.fp8_gemm(h28, self.w8[n], self.alpha[n]) for n in ("gate", "up"))
-        act8 = FP8.silu_mul_quantize_fp8(gate, up, s["act"])
+            if self.merge_gate_up:
+                gu = FP8.fp8_gemm(h28, self.w8_gate_up, alpha_cols=self.alpha_gate_up)   # [T, 2 * intermediate]
+                gate, up = gu[:, :sh.intermediate], gu[:, sh.intermediate:]
+            else:
+                gate, up = (FP8.fp8_gemm(h28, self.w8[n], self.alpha[n]) for n in ("gate", "up"))
+            act8 = FP8.silu_mul_quantize_fp8(gate, up, s["act"])
         if self.fuse_residual:
             return FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"], residual=x1)
         return x1 + FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"])
