@@ -42,7 +42,7 @@ sys.path.insert(0, ROOT)
 # ncu-measured DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, bytes per
 # launch) of each workload's dominant kernel, from the captures summarised under
 # profiles/; None until one has been taken.
-NCU_TRAFFIC_BYTES = {"c1": 53.9e6, "c2": 94.4e6}
+NCU_TRAFFIC_BYTES = {"c1": 53.5e6, "c2": 145.2e6}
 
 
 def measured_peaks():

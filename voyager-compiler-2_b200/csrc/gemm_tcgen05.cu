@@ -337,10 +337,10 @@ __device__ __noinline__ void epilogue_warp_tile_unstaged(const GemmParams& p, ui
   }
 }
 
-template <int OUT_DT>
+template <int OUT_DT, int EPI_BUFS>
 __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
-                                                     uint8_t* stage, int row0, int lane, int n0, int b, bool has_alpha,
-                                                     float alpha, int c_begin, int c_end) {
+                                                     uint8_t* stage0, uint32_t& buf, int row0, int lane, int n0, int b,
+                                                     bool has_alpha, float alpha, int c_begin, int c_end) {
   constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
   constexpr int ROUND_COLS = 128 / ESZ;   // output columns per 128-byte staged row
   const int64_t row_stride = p.ldc * ESZ;
@@ -350,6 +350,9 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
                                                  : static_cast<const uint8_t*>(p.residual) + (int64_t)b * p.strideR * ESZ;
   const bool r_wide = ((reinterpret_cast<uintptr_t>(p.residual) | (uintptr_t)r_row_stride | (uintptr_t)(p.strideR * ESZ)) & 15) == 0;
   const bool rows_inside = row0 + 32 <= p.M;
+  // With EPI_BUFS = 2 the warp alternates between two 4 KB staging buffers (`buf`, which lives
+  // across tiles), so the TMA store of one block drains while the next block is being staged.
+  uint8_t* stage = stage0 + (EPI_BUFS == 2 ? buf * (32 * 128) : 0);
   uint8_t* srow = stage + lane * 128;
   // With a tensor map for C (and no residual to add) a finished 32 x 128-byte block leaves
   // shared memory as one TMA store issued by lane 0; the hardware clips it at the edges of C.
@@ -360,8 +363,10 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
     const int col0 = n0 + c0;
     if (col0 >= p.N) return;  // warp-uniform
     const int half = ESZ == 4 ? 0 : (c0 >> 5) & 1;   // a 128-byte row holds two 32-column chunks of 16-bit values
-    if (by_tma && half == 0) {   // the previous block's store must have read the staging buffer
-      if (lane == 0) tma_store_wait_read();
+    if (by_tma && half == 0) {   // the store that last used this staging buffer must have read it
+      if (lane == 0) {
+        if (EPI_BUFS == 2) tma_store_wait_read_but_one(); else tma_store_wait_read();
+      }
       __syncwarp();
     }
     stage_chunk<OUT_DT>(p, v, srow, lane, col0, half, has_alpha, alpha);
@@ -370,9 +375,14 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
     if (by_tma) {
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && row0 < p.M) {   // a block entirely below C has nothing to store
-        tma_store_3d(map_c, stage, round_col0, row0, b);
-        tma_store_commit();
+      if (lane == 0) {
+        if (row0 < p.M) tma_store_3d(map_c, stage, round_col0, row0, b);   // a block entirely below C stores nothing
+        tma_store_commit();                                                 // (an empty group keeps the count in step)
+      }
+      if (EPI_BUFS == 2) {
+        buf ^= 1u;
+        stage = stage0 + buf * (32 * 128);
+        srow = stage + lane * 128;
       }
       return;
     }
@@ -456,10 +466,10 @@ __device__ __forceinline__ void epilogue_warp_tile_gated(const GemmParams& p, ui
   }
 }
 
-template <int OUT_DT>
+template <int OUT_DT, int EPI_BUFS = 1>
 __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
-                                                   uint8_t* stage, int row0, int lane, int n0, int b, bool has_alpha,
-                                                   float alpha, int c_begin, int c_end) {
+                                                   uint8_t* stage, uint32_t& buf, int row0, int lane, int n0, int b,
+                                                   bool has_alpha, float alpha, int c_begin, int c_end) {
   constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
   if (OUT_DT == VQ_BF16 && p.gate_scale != nullptr) {   // gated launches use the bfloat16 instantiation
     epilogue_warp_tile_gated(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
@@ -469,7 +479,8 @@ __device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CU
     epilogue_warp_tile_unstaged(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
     return;
   }
-  epilogue_warp_tile_t<OUT_DT>(p, map_c, taddr, stage, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
+  epilogue_warp_tile_t<OUT_DT, EPI_BUFS>(p, map_c, taddr, stage, buf, row0, lane, n0, b, has_alpha, alpha, c_begin,
+                                         c_end);
 }
 
 template <int OUT_DT>
@@ -587,6 +598,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    uint32_t epi_buf = 0;   // which staging buffer this warp fills next
     const bool has_alpha = p.alpha != nullptr;
     const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -598,7 +610,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * BN, b,
+      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), epi_buf, m_blk * BM + quarter * 32, lane, n_blk * BN, b,
                          has_alpha, alpha, chalf * (BN / 2), (chalf + 1) * (BN / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -628,9 +640,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 //   acc_empty     : lives in the even CTA; 8 arrivals (4 epilogue warps x 2 CTAs)
 // ---------------------------------------------------------------------------
 constexpr int P_STAGES = 6;
+constexpr int P_EPI_BUFS = 1;              // staging buffers per epilogue warp (2 was measured: no gain, and it costs a pipeline stage)
 constexpr int P_A_BYTES = 128 * BK_BYTES;  // 16 KB
 constexpr int P_B_BYTES = 128 * BK_BYTES;  // 16 KB (half of the tile's B rows)
-constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256 + EPI_STAGE_BYTES;
+constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256 + P_EPI_BUFS * EPI_STAGE_BYTES;
 
 template <int OUT_DT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -641,7 +654,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + P_STAGES * P_A_BYTES;
   uint8_t* epi_stage = smem + P_STAGES * (P_A_BYTES + P_B_BYTES);   // 1024-byte aligned: TMA stores read it with the 128-byte swizzle
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * (P_A_BYTES + P_B_BYTES) + EPI_STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * (P_A_BYTES + P_B_BYTES) + P_EPI_BUFS * EPI_STAGE_BYTES);
   uint64_t* full_bar = bars;                        // [P_STAGES] (used in the even CTA)
   uint64_t* empty_bar = bars + P_STAGES;            // [P_STAGES]
   uint64_t* acc_full = bars + 2 * P_STAGES;         // [2]
@@ -765,6 +778,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    uint32_t epi_buf = 0;   // which staging buffer this warp fills next
     const bool has_alpha = p.alpha != nullptr;
     const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
@@ -777,7 +791,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * 2 * BM + (int)rank * BM + quarter * 32,
+      epilogue_warp_tile<OUT_DT, P_EPI_BUFS>(p, &map_c, taddr, epi_stage + (warp - 2) * (P_EPI_BUFS * 32 * 128), epi_buf,
+                                             m_blk * 2 * BM + (int)rank * BM + quarter * 32,
                          lane, n_blk * bn, b, has_alpha, alpha, chalf * (bn / 2), (chalf + 1) * (bn / 2));
       tc_fence_before_sync();
       __syncwarp();
@@ -942,6 +957,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    uint32_t epi_buf = 0;   // which staging buffer this warp fills next
     const bool has_alpha = p.alpha != nullptr;
     const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -951,7 +967,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * Q_BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), m_blk * BM + quarter * 32, lane, n_blk * Q_BN, b,
+      epilogue_warp_tile<OUT_DT>(p, &map_c, taddr, epi_stage + (warp - 2) * (32 * 128), epi_buf, m_blk * BM + quarter * 32, lane, n_blk * Q_BN, b,
                          has_alpha, alpha, chalf * (Q_BN / 2), (chalf + 1) * (Q_BN / 2));
       tc_fence_before_sync();
       __syncwarp();
