@@ -402,6 +402,7 @@ def run_ours(args, rank, world, local_rank):
         wl.step(i)
     wl.vb.ops.gemm_status()
 
+    barrier()   # NCCL communicators come up here, not inside the sampled region
     with ClockSampler(local_rank) as clocks:
         elapsed = time_region(wl.step, args.steps, barrier)
     wl.vb.ops.gemm_status()
