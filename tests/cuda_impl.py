@@ -59,3 +59,19 @@ CudaImpl.fake_quant = staticmethod(_wrap(FQ.fake_quant))
 CudaImpl.group_wise_affine_fake_quant = staticmethod(_wrap(FQ.group_wise_affine_fake_quant))
 CudaImpl.mx_fake_quant = staticmethod(_wrap(FQ.mx_fake_quant))
 CudaImpl.hadamard_amax = staticmethod(_wrap(FQ.hadamard_amax))
+
+
+def _amax_observer(sequence, dtype, quant_max, history_len, ch_axis, power_2_scale):
+    Q = voyager_b200.QScheme
+    scheme = Q.PER_TENSOR_SYMMETRIC if ch_axis is None else Q.PER_CHANNEL_SYMMETRIC
+    module = voyager_b200.observers.FusedAmaxObsFakeQuantize(dtype, scheme, quant_max, history_len, ch_axis,
+                                                             power_2_scale, device=DEV)
+    outs, scales = [], []
+    for x in sequence.to(DEV):
+        outs.append(module(x))
+        scales.append(module.scale.clone())
+    torch.cuda.synchronize()
+    return torch.stack(outs).cpu(), torch.stack(scales).cpu()
+
+
+CudaImpl.amax_observer = staticmethod(_amax_observer)

@@ -269,6 +269,16 @@ def build_cases(table):
         True, None, torch.tensor(1234, dtype=torch.int64), None, None, None)
     add("hadamard_amax_last", "hadamard_amax", randn(130, 3, 8, 40), -1, "hadamard")
     add("hadamard_amax_rows", "hadamard_amax", randn(131, 3, 24, 8), -2, "hadamard")
+
+    # ---- delayed-scaling observer (fake_quantize.py:406-437): a sequence of inputs through one module ----
+    seq = torch.stack([randn(140 + i, 6, 32, std=0.5 * (i + 1)) for i in range(5)])
+    add("observer_tensor_e4m3", "amax_observer", seq, "fp8_e4m3", 448.0, 3, None, False)
+    add("observer_tensor_int8_pow2", "amax_observer", seq, "int8", 127.0, 2, None, True)
+    add("observer_channel_e4m3", "amax_observer", seq, "fp8_e4m3", 448.0, 4, 0, False)
+    zeros_first = seq.clone()
+    zeros_first[0] = 0
+    zeros_first[2, 0, 0] = float("inf")
+    add("observer_zero_and_inf", "amax_observer", zeros_first, "fp8_e4m3", 448.0, 2, None, False)
     return cases
 
 

@@ -64,6 +64,17 @@ class ReferenceImpl:
     def table(self, name):
         return self.fq.get_quantization_map(name)
 
+    def amax_observer(self, sequence, dtype, quant_max, history_len, ch_axis, power_2_scale):
+        """Feed ``sequence[i]`` through one FusedAmaxObsFakeQuantize; outputs and scales after each call."""
+        Q = self.fq.QScheme
+        scheme = Q.PER_TENSOR_SYMMETRIC if ch_axis is None else Q.PER_CHANNEL_SYMMETRIC
+        module = self.fq.FusedAmaxObsFakeQuantize(dtype, scheme, quant_max, history_len, ch_axis, power_2_scale)
+        outs, scales = [], []
+        for x in sequence:
+            outs.append(module(x))
+            scales.append(module.scale.clone())
+        return torch.stack(outs), torch.stack(scales)
+
     def compensate_weight(self, w, h, tokens, qmap, scale_qmap, qmax, bs, damping, act_order, within_block, shrink):
         fake_quant = types.SimpleNamespace(block_size=bs, ch_axis=-1, qmap=qmap, scale_qmap=scale_qmap,
                                            quant_max=qmax)

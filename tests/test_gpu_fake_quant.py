@@ -10,7 +10,7 @@ from oracle import tables as OT
 
 pytestmark = pytest.mark.gpu
 
-FAKE_QUANT_OPS = {"fake_quant", "group_wise_affine_fake_quant", "mx_fake_quant", "hadamard_amax"}
+FAKE_QUANT_OPS = {"fake_quant", "group_wise_affine_fake_quant", "mx_fake_quant", "hadamard_amax", "amax_observer"}
 _CASES = {k: v for k, v in golden_cases(OT.quantization_map).items() if v[0] in FAKE_QUANT_OPS}
 
 

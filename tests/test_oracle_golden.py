@@ -6,6 +6,7 @@ import torch
 import cases as C
 from golden_io import bits_equal, describe_mismatch, golden_cases, golden_tables
 from oracle import fake_quant as fq_oracle
+from oracle import observers as obs_oracle
 from oracle import gemm, gptq, quantizers, tables
 
 
@@ -30,6 +31,7 @@ class OracleImpl:
     group_wise_affine_fake_quant = staticmethod(fq_oracle.group_wise_affine_fake_quant)
     mx_fake_quant = staticmethod(fq_oracle.mx_fake_quant)
     hadamard_amax = staticmethod(fq_oracle.hadamard_amax)
+    amax_observer = staticmethod(obs_oracle.amax_observer)
 
 
 @pytest.mark.parametrize("name", sorted(golden_tables()))

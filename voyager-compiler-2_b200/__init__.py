@@ -14,6 +14,7 @@ from . import parallel  # noqa: F401
 from . import nvfp4  # noqa: F401
 from . import fake_quant  # noqa: F401  (registers torch.ops.quantization.*)
 from . import kivi  # noqa: F401
+from . import observers  # noqa: F401
 from ._native import build  # noqa: F401
 from .formats import (  # noqa: F401
     QScheme,
