@@ -122,6 +122,30 @@ int vq_unpack_dequantize(const void* packed, int bits, const void* scale, const 
                          int dtype, int param_dtype, const VqBroadcast* geom, const VqRound* round_out,
                          void* stream);
 
+/* Outlier side stream -- quantized_ops::filter_outlier (ops/quantized.py:1323-1373)
+ * and quantized_ops::spmm_csr (:1574-1644), built on the device with no host read
+ * (the reference calls .item() and is not graph-capturable).
+ *
+ * An element is an outlier when |x| >= threshold (threshold already rounded to the
+ * tensor's dtype).  Per [rows, cols] matrix the stored outliers (zero values are not
+ * stored) form a CSR matrix of fixed capacity: data / indices hold `capacity` entries
+ * (caller pre-fills 0 and -1), entries beyond the capacity are dropped in row-major order.
+ *
+ * vq_outlier_count: counts[row] for the [rows_total, cols] view of the input.
+ * vq_outlier_fill: row_start is [batches, rows + 1], the exclusive prefix sums of the
+ *   counts per matrix (not clamped); writes data, indices and inlier = x with outliers zeroed.
+ * vq_spmm_csr: out[b][r][n] = sum_e data[b][e] * B[b][indices[b][e]][n] over row r's
+ *   entries, float32 accumulation in entry order, rounded to out_dtype.  Row pointers are
+ *   rebased on indptr[b][0] and clamped to the stored span; B element (k, n) of batch b is
+ *   at B[b * strideB + k * ld_k + n * ld_n] (strideB = 0 shares one B). */
+int vq_outlier_count(const void* in, int dtype, int32_t* counts, int64_t rows_total, int64_t cols, float threshold,
+                     void* stream);
+int vq_outlier_fill(const void* in, int dtype, void* inlier, void* data, int32_t* indices, const int32_t* row_start,
+                    int64_t batches, int64_t rows, int64_t cols, float threshold, int64_t capacity, void* stream);
+int vq_spmm_csr(const void* data, int data_dtype, const int32_t* indices, const int32_t* indptr, const void* B,
+                int b_dtype, void* out, int out_dtype, int64_t batches, int64_t rows, int64_t N, int64_t K,
+                int64_t capacity, int64_t strideB, int64_t ld_k, int64_t ld_n, void* stream);
+
 /* Microscaling block geometry: the input is a dense [O, A, M, B, I] tensor
  * whose blocks span block_a consecutive indices of A and block_b of B (1 =
  * axis not blocked); scales are dense [O, ceil(A/block_a), M, ceil(B/block_b), I]. */

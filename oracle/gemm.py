@@ -61,8 +61,8 @@ def _read(x, scale, code, block_size):
 
 
 def linear_mx(x, w, bias=None, *, input_scale=None, weight_scale=None, block_size=None,
-              input_code=None, weight_code=None, alpha=None, layout="xc,kc->xk",
-              out_dtype=None):
+              input_code=None, weight_code=None, alpha=None, A_data=None, A_indices=None, A_indptr=None,
+              layout="xc,kc->xk", out_dtype=None):
     act, wgt, out = parse_layout(layout)
     a = _read(x, input_scale, input_code, block_size)
     b = _read(w, weight_scale, weight_code, block_size)
@@ -73,6 +73,10 @@ def linear_mx(x, w, bias=None, *, input_scale=None, weight_scale=None, block_siz
         y = y * alpha
         if bias is not None:
             y = y + bias
+    if A_data is not None:   # the outliers' product joins the float32 sum before the one rounding
+        from .outliers import spmm_csr
+
+        y = y + spmm_csr(A_data, A_indices, A_indptr, w, weight_scale, weight_code, block_size, wgt, out_dtype=acc)
     y = y.to(dtype)
     return y.mT.contiguous() if out != "xk" else y
 

@@ -75,3 +75,8 @@ def _amax_observer(sequence, dtype, quant_max, history_len, ch_axis, power_2_sca
 
 
 CudaImpl.amax_observer = staticmethod(_amax_observer)
+
+CudaImpl.filter_outlier = staticmethod(_wrap(Q.filter_outlier))
+CudaImpl.quantize_mx_outlier = staticmethod(_wrap(Q.quantize_mx_outlier))
+CudaImpl.slice_csr_tensor = staticmethod(_wrap(Q.slice_csr_tensor))
+CudaImpl.spmm_csr = staticmethod(_wrap(Q.spmm_csr))

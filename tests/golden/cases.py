@@ -279,6 +279,19 @@ def build_cases(table):
     zeros_first[0] = 0
     zeros_first[2, 0, 0] = float("inf")
     add("observer_zero_and_inf", "amax_observer", zeros_first, "fp8_e4m3", 448.0, 2, None, False)
+
+    # ---- outlier side stream (ops/quantized.py:1286-1644) ------------------------------------
+    xo = randn(150, 2, 24, 64, outliers=0.02)
+    add("outlier_filter", "filter_outlier", xo, 6.0, 0.05)
+    add("outlier_filter_overflow", "filter_outlier", xo, 2.0, 0.02)          # more outliers than capacity
+    add("outlier_filter_f32_2d", "filter_outlier", randn(151, 16, 40, dtype=torch.float32, outliers=0.03), 5.0, 0.1)
+    add("outlier_quantize_mx", "quantize_mx_outlier", xo, int8, [-1], 16, 127.0, True, None, None, 6.0, 0.05, 3)
+    add("outlier_slice_rows", "slice_csr_chain", xo[0], 6.0, 0.05, 0, 5, 17, 1.0)
+    add("outlier_slice_cols", "slice_csr_chain", xo[0], 6.0, 0.05, 1, 16, 48, 0.5)
+    add("outlier_spmm_kc", "spmm_chain", xo, randn(152, 40, 64, std=0.05), "kc", spec=dict(qmap=int8, bs=16, qmax=127.0, pot=True))
+    add("outlier_spmm_ck", "spmm_chain", xo[0], randn(153, 64, 40, std=0.05), "ck", spec=dict(qmap=int8, bs=16, qmax=127.0, pot=True))
+    add("outlier_linear_mx", "linear_mx_outlier_chain", randn(154, 48, 128, outliers=0.01), randn(155, 72, 128, std=0.02),
+        spec=dict(qmap=int8, bs=16, qmax=127.0, pot=True, threshold=6.0, max_pct=0.03))
     return cases
 
 
@@ -334,6 +347,24 @@ def run_case(impl, op, args, kwargs):
         y = impl.dense_linear(cx, cw)
         out = impl.dequantize(y, sa * sw, None, None, None, None, spec["out_map"])
         return cx, cw, y, out
+    if op == "slice_csr_chain":
+        x, threshold, max_pct, dim, start, end, size_factor = args
+        data, indices, indptr, _ = impl.filter_outlier(x, threshold, max_pct)
+        return tuple(impl.slice_csr_tensor(data, indices, indptr, dim, start, end, size_factor))
+    if op == "spmm_chain":
+        x, w, weight_layout = args
+        data, indices, indptr, _ = impl.filter_outlier(x, 6.0, 0.05)
+        sw, cw, _ = qmx(w, (-1,) if weight_layout == "kc" else (-2,))
+        return (impl.spmm_csr(data, indices, indptr, cw, sw, None, spec["bs"], weight_layout, out_dtype=torch.float32),)
+    if op == "linear_mx_outlier_chain":
+        x, w = args
+        data, indices, indptr, sx, cx = impl.quantize_mx_outlier(x, spec["qmap"], [-1], spec["bs"], spec["qmax"],
+                                                                  spec["pot"], None, None, spec["threshold"],
+                                                                  spec["max_pct"])
+        sw, cw, _ = qmx(w)
+        y = impl.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=spec["bs"], A_data=data,
+                           A_indices=indices, A_indptr=indptr)
+        return data, indices, indptr, sx, cx, y
     if op == "gptq":
         w, h, tokens = args
         return (impl.compensate_weight(w, h.clone(), tokens, spec["qmap"], spec["scale_qmap"], spec["qmax"],

@@ -50,7 +50,7 @@ class ReferenceImpl:
         self.gptq = ref.gptq
         for name in ("vmap", "quantize", "dequantize", "calculate_mx_qparam", "quantize_mx", "dequantize_mx",
                      "quantize_affine", "linear_mx", "matmul_mx", "sdpa_mx", "hadamard_rotate",
-                     "quantize_mx_transpose"):
+                     "quantize_mx_transpose", "filter_outlier", "quantize_mx_outlier", "slice_csr_tensor", "spmm_csr"):
             setattr(self, name, getattr(q, name))
         import importlib
 

@@ -7,6 +7,7 @@ import cases as C
 from golden_io import bits_equal, describe_mismatch, golden_cases, golden_tables
 from oracle import fake_quant as fq_oracle
 from oracle import observers as obs_oracle
+from oracle import outliers as out_oracle
 from oracle import gemm, gptq, quantizers, tables
 
 
@@ -32,6 +33,10 @@ class OracleImpl:
     mx_fake_quant = staticmethod(fq_oracle.mx_fake_quant)
     hadamard_amax = staticmethod(fq_oracle.hadamard_amax)
     amax_observer = staticmethod(obs_oracle.amax_observer)
+    filter_outlier = staticmethod(out_oracle.filter_outlier)
+    quantize_mx_outlier = staticmethod(out_oracle.quantize_mx_outlier)
+    slice_csr_tensor = staticmethod(out_oracle.slice_csr_tensor)
+    spmm_csr = staticmethod(out_oracle.spmm_csr)
 
 
 @pytest.mark.parametrize("name", sorted(golden_tables()))

@@ -15,6 +15,7 @@ from . import nvfp4  # noqa: F401
 from . import fake_quant  # noqa: F401  (registers torch.ops.quantization.*)
 from . import kivi  # noqa: F401
 from . import observers  # noqa: F401
+from . import outliers  # noqa: F401  (adds the outlier operators to torch.ops.quantized_ops)
 from ._native import build  # noqa: F401
 from .formats import (  # noqa: F401
     QScheme,

@@ -105,6 +105,9 @@ SIGNATURES = {
     "vq_dequantize_mx": [_P, _P, _P, ctypes.c_int32, _P, _I, _P, _I, ctypes.POINTER(VqBroadcast), _P],
     "vq_amax": [_P, _I, _I64, _P, _P],
     "vq_pack_codes": [_P, _I, _P, _I, _I64, _P],
+    "vq_outlier_count": [_P, _I, _P, _I64, _I64, _F, _P],
+    "vq_outlier_fill": [_P, _I, _P, _P, _P, _P, _I64, _I64, _I64, _F, _I64, _P],
+    "vq_spmm_csr": [_P, _I, _P, _P, _P, _I, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P],
     "vq_unpack_dequantize": [_P, _I, _P, _P, _P, _I, _I, ctypes.POINTER(VqBroadcast), ctypes.POINTER(VqRound), _P],
     "vq_gemm_tn": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
     "vq_gemm_tn_ex": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I,

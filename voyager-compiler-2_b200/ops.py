@@ -757,14 +757,24 @@ def _read_operand(x, scale, code, block_size):
 
 def _mx_gemm(native, a, b, bias, input_scale, weight_scale, block_size, input_code, weight_code, alpha, outliers,
              layout, out_dtype):
-    if any(t is not None for t in outliers):
-        raise NotImplementedError("the outlier CSR side stream (A_data / A_indices / A_indptr) is not built")
     a = _read_operand(a, input_scale, input_code, block_size)
     b = _read_operand(b, weight_scale, weight_code, block_size)
     dtype = a.dtype if out_dtype is None else out_dtype
     if dtype not in _DTYPE_ID:
         raise NotImplementedError(f"output dtype {dtype}")
-    return _gemm_in_layout(native, a, b, layout, dtype, bias, _as_scalar_param(alpha, a.device))
+    if all(t is None for t in outliers):
+        return _gemm_in_layout(native, a, b, layout, dtype, bias, _as_scalar_param(alpha, a.device))
+    if any(t is None for t in outliers):
+        raise ValueError("A_data, A_indices and A_indptr come together")
+    # The outliers' product joins the float32 sum of product, alpha and bias before the one rounding
+    # (reference quantized.py:688-722); it is computed [tokens, out] and stored as `layout` says last.
+    act, wgt, out_l = _parse_layout(layout)
+    n_out = _parse_layout(native)[2]
+    y = _gemm_in_layout(native, a, b, f"{act},{wgt}->{n_out}", torch.float32, bias, _as_scalar_param(alpha, a.device))
+    data, indices, indptr = outliers
+    y = y + torch.ops.quantized_ops.spmm_csr(data, indices, indptr, b, None, None, None, wgt, out_dtype=torch.float32)
+    y = y.to(dtype)
+    return y.mT.contiguous() if out_l != n_out else y
 
 
 def linear_mx(input, weight, bias=None, *, input_scale=None, weight_scale=None, block_size=None, input_code=None,
