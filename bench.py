@@ -348,7 +348,70 @@ class C2:
         return OL.fp8_decoder_layer(*state)
 
 
-WORKLOADS = {"c1": C1, "c2": C2}
+# ---------------------------------------------------------------------------
+# workload q1: the MX quantizer alone on an activation larger than L2 (HBM roofline)
+# ---------------------------------------------------------------------------
+class Q1:
+    name = "q1"
+    description = ("q1: quantize_mx (int8, bs=16, power-of-two scales) of a [16384,4096] bfloat16 activation per GPU: "
+                   "the C1 quantizer at 8x C1's rows, so that the kernel is HBM-bound rather than launch-bound")
+    tokens = 16384
+    K, BLOCK, QMAX = 4096, 16, 127.0
+    launches_per_step = 1
+    n_sets = 3
+    dtype = "bf16"
+    cpu_tokens = 2048
+    cpu_sample = "quantize_mx calls on 2048 of the step's 16384 rows"
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        self.Q = torch.ops.quantized_ops
+        self.table = voyager_b200.get_quantization_map("int8", dev)
+        g = torch.Generator().manual_seed(77 + rank)
+        self.x = [torch.randn(self.tokens, self.K, generator=g).bfloat16().to(dev) for _ in range(self.n_sets)]
+        self.h2d_bytes = self.tokens * self.K * 2
+        self.d2h_bytes = self.tokens * self.K * 2
+        self._run(self.x[0])
+        self.graphs = [capture(lambda x=x: self._run(x)) for x in self.x]
+        self.pipeline = HostPipeline(self.x, [x.cpu().pin_memory() for x in self.x], self.graphs)
+
+    def _run(self, x):
+        return self.Q.quantize_mx(x, self.table, [-1], self.BLOCK, self.QMAX, True)[1]
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def roofline(self, peaks, reps):
+        # the step's graphs hold this one kernel: replaying them times it without host launch gaps
+        secs = time_region(self.step, reps, torch.cuda.synchronize) / reps
+        nbytes = self.tokens * self.K * (2 + 2 + 2 / self.BLOCK)      # input + codes + one scale per block
+        achieved = nbytes / secs / 1e9
+        return secs, {"kernel": "mx_flat_bf16_kernel (quantize_mx int8, block 16, power-of-two scales, 16384x4096)",
+                      "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                      "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth",
+                      "traffic": None}
+
+    @staticmethod
+    def cpu_setup():
+        from oracle import tables as OT
+
+        g = torch.Generator().manual_seed(77)
+        return torch.randn(Q1.cpu_tokens, Q1.K, generator=g).bfloat16(), OT.quantization_map("int8")
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import quantizers as OQ
+
+        x, table = state
+        return OQ.quantize_mx(x, table, [-1], Q1.BLOCK, Q1.QMAX, True)
+
+
+WORKLOADS = {"c1": C1, "c2": C2, "q1": Q1}
 
 
 def time_cpu_baseline(workload, reps):
