@@ -48,7 +48,7 @@ def test_fused_cast_matches_quantize_mx(rows, k, seed):
     x = C.randn(seed, rows, k, outliers=0.002)
     x[0, :16] = 0  # an all-zero block
     t, scale, codes = reference_quantize(x)
-    packed = vb.nvfp4.quantize_nvfp4(x.cuda(), t.cuda())
+    packed = vb.nvfp4.cast_nvfp4(x.cuda(), t.cuda())
     val, sc = unpack(packed, rows, k)
     assert torch.equal(sc, scale.float())
     assert torch.equal(val, codes.float())
@@ -75,8 +75,8 @@ def test_native_gemm_matches_linear_mx(m, n, k):
     alpha = tx * tw
     bias = C.randn(5, n, std=0.1)
     want = OG.linear_mx(cx, cw, bias, input_scale=sx, weight_scale=sw, block_size=16, alpha=alpha)
-    a = vb.nvfp4.quantize_nvfp4(x.cuda(), tx.cuda())
-    b = vb.nvfp4.quantize_nvfp4(w.cuda(), tw.cuda())
+    a = vb.nvfp4.cast_nvfp4(x.cuda(), tx.cuda())
+    b = vb.nvfp4.cast_nvfp4(w.cuda(), tw.cuda())
     got = vb.nvfp4.nvfp4_gemm(a, b, alpha.cuda(), bias.cuda()).cpu()
     vb.ops.gemm_status()
     assert got.shape == want.shape and got.dtype == want.dtype
@@ -88,3 +88,44 @@ def test_native_gemm_matches_linear_mx(m, n, k):
     ref = da @ db.T
     err32 = float((got32.double() - ref).abs().max() / ref.abs().max())
     assert err32 <= 1e-4, err32
+
+
+@pytest.mark.parametrize("shape,axis", [((3, 40, 128), -1), ((128, 256), 0), ((200, 64), -1)])
+def test_reference_signatures(shape, axis):
+    """quantize_nvfp4 / unpack_nvfp4 / nvfp4_linear / emulate_nvfp4_linear as the reference spells them."""
+    vb = _vb()
+    x = C.randn(sum(shape), *shape, outliers=0.002)
+    codes, scales, t = vb.nvfp4.quantize_nvfp4(x.cuda(), axis)
+    moved = x.movedim(axis, -1)
+    t_want, scale_want, codes_want = reference_quantize(moved.contiguous())
+    assert torch.equal(t.cpu(), t_want) and t.dtype == torch.bfloat16 and t.ndim == 0
+    assert codes.shape == (*moved.shape[:-1], moved.shape[-1] // 2) and codes.dtype == torch.uint8
+    values, block_scales = vb.nvfp4.unpack_nvfp4(codes, scales)
+    assert torch.equal(values.cpu().float(), codes_want.float())
+    assert torch.equal(block_scales.cpu().float(), scale_want.float())
+    # the linear, packed against its emulation through linear_mx
+    n = 72
+    w = C.randn(7, n, moved.shape[-1], std=0.02)
+    w_codes, w_scales, tw = vb.nvfp4.quantize_nvfp4(w.cuda())
+    alpha = (t * tw).float()
+    bias = C.randn(8, n, std=0.1).cuda()
+    one = torch.ones((), device="cuda")
+    got = vb.nvfp4.nvfp4_linear(codes, scales, w_codes, w_scales, alpha, one, bias)
+    want = vb.nvfp4.emulate_nvfp4_linear(codes, scales, w_codes, w_scales, alpha, one, bias)
+    vb.ops.gemm_status()
+    assert got.shape == (*moved.shape[:-1], n) and got.dtype == torch.bfloat16
+    err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+    assert err <= 1e-2, err
+
+
+def test_quantize_nvfp4_stochastic_uses_the_operator():
+    vb = _vb()
+    x = C.randn(31, 64, 128)
+    seed = torch.tensor(99, dtype=torch.int64)
+    codes, scales, t = vb.nvfp4.quantize_nvfp4(x.cuda(), -1, seed.cuda())
+    values, block_scales = vb.nvfp4.unpack_nvfp4(codes, scales)
+    levels = OT.grid_levels(OT.quantization_map("fp4_e2m1"))
+    s_want, c_want = OQ.quantize_mx(x, levels, [-1], 16, 6.0, False, OT.quantization_map("fp8_e4m3"), None, seed,
+                                    OQ.calculate_global_scale(x, 6.0, 448.0))
+    assert torch.equal(values.cpu().float(), c_want.float())
+    assert torch.equal(block_scales.cpu().float(), s_want.float())

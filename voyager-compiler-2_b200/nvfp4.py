@@ -1,11 +1,15 @@
 """NVFP4 on the tensor cores' native block-scaled MMA.
 
-The counterpart of the reference's ``backend/gpu/nvfp4.py`` (``quantize_nvfp4:890``,
-``pack_nvfp4:1045``, ``nvfp4_linear:1101``): an NVFP4 site of a converted graph
-(``quantize_mx`` with an e2m1 table, block 16, e4m3 scales and a global scale,
-feeding ``linear_mx`` with ``alpha``) is executed as one fused cast to packed
-operands and one ``kind::mxf4nvf4`` GEMM.  The cast reproduces the operator's
-codes and scales bit for bit; the GEMM accumulates the same products in fp32.
+The counterpart of the reference's ``backend/gpu/nvfp4.py``: an NVFP4 site of a converted
+graph (``quantize_mx`` with an e2m1 table, block 16, e4m3 scales and a global scale, feeding
+``linear_mx`` with ``alpha``) is executed as one fused cast to packed operands and one
+``kind::mxf4nvf4`` GEMM.  The cast reproduces the operator's codes and scales bit for bit;
+the GEMM accumulates the same products in fp32.
+
+``quantize_nvfp4``, ``pack_nvfp4``, ``unpack_nvfp4``, ``nvfp4_linear`` and
+``emulate_nvfp4_linear`` keep the reference's names, arguments and return values
+(``backend/gpu/nvfp4.py:890-950, 1045-1091, 1101-1152, 1190-1227``); ``cast_nvfp4`` and
+``nvfp4_gemm`` are the kernels underneath.
 """
 
 from typing import NamedTuple, Optional
@@ -16,12 +20,22 @@ from . import _native as N
 from .ops import _DTYPE_ID, _dtype_id, _ptr, _stream
 
 
+BLOCK_SIZE = 16
+FP4_MAX, E4M3_MAX = 6.0, 448.0
+
+
 class PackedNVFP4(NamedTuple):
-    """``codes``: uint8 ``[*batch, rows, K/2]``; ``scales``: uint8 tiles; ``shape``: logical ``(*batch, rows, K)``."""
+    """``codes``: uint8 ``[*batch, rows, K/2]`` (two e2m1 codes per byte, even element in the low
+    nibble); ``scales``: uint8 e4m3 block scales in 128x4 tiles (512 bytes each, the layout the
+    block-scaled MMA reads).  Unpacks as ``codes, scales = packed`` like the reference's pair."""
 
     codes: torch.Tensor
     scales: torch.Tensor
-    shape: tuple
+
+    @property
+    def shape(self) -> tuple:
+        """Logical ``(*batch, rows, K)``."""
+        return (*self.codes.shape[:-1], self.codes.shape[-1] * 2)
 
 
 def _alloc(shape, device):
@@ -37,10 +51,11 @@ def _alloc(shape, device):
     return codes, scales, nb, rows, k, per
 
 
-def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor) -> PackedNVFP4:
-    """Cast bfloat16 ``x [*batch, rows, K]`` (blocks of 16 along K) to packed NVFP4."""
+def cast_nvfp4(x: torch.Tensor, global_scale: torch.Tensor) -> PackedNVFP4:
+    """Cast bfloat16 ``x [*batch, rows, K]`` (blocks of 16 along K) to packed NVFP4 against a given
+    global scale, one pass (the role of the reference's ``cast_nvfp4`` kernels, ``nvfp4.py:683-739``)."""
     if x.dtype != torch.bfloat16:
-        raise NotImplementedError("quantize_nvfp4 takes bfloat16 input")
+        raise NotImplementedError("cast_nvfp4 takes bfloat16 input")
     x = x.contiguous()
     codes, scales, nb, rows, k, per = _alloc(tuple(x.shape), x.device)
     gs = global_scale if global_scale.dtype in _DTYPE_ID else global_scale.float()
@@ -49,7 +64,7 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor) -> PackedNVFP4:
     for b in range(nb):
         N.check(lib.vq_quantize_nvfp4(xb[b].data_ptr(), gs.data_ptr(), _dtype_id(gs.dtype), cb[b].data_ptr(),
                                       scales[b].data_ptr(), rows, k, stream), "vq_quantize_nvfp4")
-    return PackedNVFP4(codes, scales, tuple(x.shape))
+    return PackedNVFP4(codes, scales)
 
 
 def pack_nvfp4(codes: torch.Tensor, scale: torch.Tensor, check: bool = True) -> PackedNVFP4:
@@ -67,7 +82,7 @@ def pack_nvfp4(codes: torch.Tensor, scale: torch.Tensor, check: bool = True) -> 
                                   k, bad.data_ptr(), stream), "vq_pack_nvfp4")
     if check and int(bad.item()):
         raise ValueError("pack_nvfp4: codes are not all e2m1 values or scales are not all e4m3 values")
-    return PackedNVFP4(out, scales, tuple(codes.shape))
+    return PackedNVFP4(out, scales)
 
 
 def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = None,
@@ -104,9 +119,82 @@ def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = N
     return out.reshape(*abatch, m, n)
 
 
-def nvfp4_linear(x: torch.Tensor, weight: PackedNVFP4, x_global_scale: torch.Tensor, w_global_scale: torch.Tensor,
-                 bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
-    """One NVFP4 linear: cast ``x`` and multiply; ``alpha = x_global_scale * w_global_scale`` in the scales'
-    dtype, as the converted graph forms it."""
+def nvfp4_linear_from_bf16(x: torch.Tensor, weight: PackedNVFP4, x_global_scale: torch.Tensor,
+                           w_global_scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                           out_dtype=torch.bfloat16) -> torch.Tensor:
+    """One NVFP4 linear on a bfloat16 activation: cast ``x`` and multiply; ``alpha = x_global_scale *
+    w_global_scale`` in the scales' dtype, as the converted graph forms it."""
     alpha = x_global_scale * w_global_scale
-    return nvfp4_gemm(quantize_nvfp4(x, x_global_scale), weight, alpha, bias, out_dtype)
+    return nvfp4_gemm(cast_nvfp4(x, x_global_scale), weight, alpha, bias, out_dtype)
+
+
+# ---------------------------------------------------------------------------
+# the reference's functions, by name and signature
+# ---------------------------------------------------------------------------
+_E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def quantize_nvfp4(input: torch.Tensor, axis: int = -1, seed: Optional[torch.Tensor] = None,
+                   hadamard: Optional[torch.Tensor] = None):
+    """``(codes, scales, t)``: ``input`` quantized to NVFP4 along ``axis`` as the fake-quantizer does
+    (optional random Hadamard transform, global scale ``t`` from the tensor's amax, e4m3 block
+    scales, e2m1 elements), packed for ``nvfp4_linear``; codes have ``axis`` moved last; the axis must be a
+    multiple of 64 long here (the reference pads its scale tiles and takes multiples of 16)
+    (reference ``backend/gpu/nvfp4.py:890-950``)."""
+    from . import ops as O
+
+    axis %= input.ndim
+    if hadamard is not None:
+        input = O.hadamard_rotate(input, axis, hadamard)
+    t = O.calculate_global_scale(input, FP4_MAX, E4M3_MAX)
+    moved = input.movedim(axis, -1).contiguous()
+    rows = moved.reshape(-1, moved.shape[-1])
+    if seed is None:
+        packed = cast_nvfp4(rows, t)
+    else:
+        from .formats import get_quantization_map, qmap_levels
+
+        levels = qmap_levels(get_quantization_map("fp4_e2m1", input.device))
+        scale_qmap = get_quantization_map("fp8_e4m3", input.device)
+        # random bits are drawn for a tensor of the input's own shape, so quantize in place and move after
+        scale, values = torch.ops.quantized_ops.quantize_mx(input, levels, [axis], BLOCK_SIZE, FP4_MAX, False,
+                                                            scale_qmap, None, seed, t)
+        packed = pack_nvfp4(values.movedim(axis, -1).reshape(rows.shape).contiguous(),
+                            scale.movedim(axis, -1).reshape(rows.shape[0], -1).contiguous(), check=False)
+    return packed.codes.view(*moved.shape[:-1], -1), packed.scales, t
+
+
+def unpack_nvfp4(codes: torch.Tensor, scales: torch.Tensor):
+    """``(values, block_scales)`` in bfloat16, ``[..., K]`` and ``[..., K / 16]``: the inverse of
+    ``pack_nvfp4`` (reference ``backend/gpu/nvfp4.py:1073-1091``)."""
+    table = torch.tensor(_E2M1_VALUES, dtype=torch.bfloat16, device=codes.device)
+    nibbles = torch.stack([codes & 0xF, codes >> 4], -1).flatten(-2).long()
+    values = table[nibbles]
+    *lead, k = values.shape
+    rows = values.numel() // max(k, 1)
+    r = torch.arange(rows, device=codes.device)[:, None]
+    kb = torch.arange(k // BLOCK_SIZE, device=codes.device)[None, :]
+    offset = ((r // 128) * (k // 64) + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + kb % 4
+    block_scales = scales.reshape(-1)[offset].view(torch.float8_e4m3fn).to(torch.bfloat16)
+    return values, block_scales.reshape(*lead, -1)
+
+
+def nvfp4_linear(input: torch.Tensor, input_scale: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor,
+                 alpha: torch.Tensor, one: Optional[torch.Tensor] = None,
+                 bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``input @ weight.T * alpha + bias`` in bfloat16 on packed NVFP4 operands (``[..., K / 2]`` and
+    ``[N, K / 2]`` codes with their packed block scales); ``alpha`` holds the product of the two
+    global scales and is applied to the float32 product inside the GEMM; ``one`` is taken for the
+    signature only (reference ``backend/gpu/nvfp4.py:1101-1152``)."""
+    a = PackedNVFP4(input.reshape(-1, input.shape[-1]), input_scale)
+    out = nvfp4_gemm(a, PackedNVFP4(weight, weight_scale), alpha, bias, torch.bfloat16)
+    return out.reshape(*input.shape[:-1], -1)
+
+
+def emulate_nvfp4_linear(input, input_scale, weight, weight_scale, alpha, one=None, bias=None) -> torch.Tensor:
+    """``nvfp4_linear`` as the converted graph computes it: operands unpacked to bfloat16 and
+    multiplied by ``linear_mx`` (reference ``backend/gpu/nvfp4.py:1190-1227``)."""
+    input, input_scale = unpack_nvfp4(input, input_scale)
+    weight, weight_scale = unpack_nvfp4(weight, weight_scale)
+    return torch.ops.quantized_ops.linear_mx(input, weight, bias, input_scale=input_scale, weight_scale=weight_scale,
+                                             block_size=BLOCK_SIZE, alpha=alpha)
