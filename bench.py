@@ -411,7 +411,94 @@ class Q1:
         return OQ.quantize_mx(x, table, [-1], Q1.BLOCK, Q1.QMAX, True)
 
 
-WORKLOADS = {"c1": C1, "c2": C2, "q1": Q1}
+# ---------------------------------------------------------------------------
+# workload c4: one NVFP4 linear (fused cast to packed e2m1 + e4m3 block scales, block-scaled GEMM)
+# ---------------------------------------------------------------------------
+class C4:
+    name = "c4"
+    description = ("c4: NVFP4 (e2m1, bs=16, e4m3 block scales, bf16 global scale) linear of a Llama-3.1-8B-shaped "
+                   "up projection: cast X[2048,4096] per step, packed W[14336,4096] resident, "
+                   "kind::mxf4nvf4 block-scaled tensor-core GEMM")
+    tokens = 2048
+    K, N = 4096, 14336
+    launches_per_step = 3   # amax of the activation, cast, GEMM
+    n_sets = 4
+    dtype = "fp4_e2m1 x fp8_e4m3 block scales (fp32 accumulate)"
+    cpu_tokens = 256
+    cpu_sample = "quantize_mx + linear_mx on 256 of the step's 2048 tokens (weight quantized once outside)"
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        NV = voyager_b200.nvfp4
+        g = torch.Generator().manual_seed(40 + rank)
+        w = (torch.randn(self.N, self.K, generator=g) * 0.02).bfloat16().to(dev)
+        self.w_codes, self.w_scales, self.tw = NV.quantize_nvfp4(w)
+        del w
+        self.x = [torch.randn(self.tokens, self.K, generator=g).bfloat16().to(dev) for _ in range(self.n_sets)]
+        self.one = torch.ones((), device=dev)
+        self.h2d_bytes = self.tokens * self.K * 2
+        self.d2h_bytes = self.tokens * self.N * 2
+        self._run(self.x[0])
+        self.graphs = [capture(lambda x=x: self._run(x)) for x in self.x]
+        self.pipeline = HostPipeline(self.x, [x.cpu().pin_memory() for x in self.x], self.graphs)
+
+    def _run(self, x):
+        NV = self.vb.nvfp4
+        codes, scales, t = NV.quantize_nvfp4(x)
+        return NV.nvfp4_linear(codes, scales, self.w_codes, self.w_scales, (t * self.tw).float(), self.one, None)
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def roofline(self, peaks, reps):
+        NV = self.vb.nvfp4
+        packed = [NV.quantize_nvfp4(x) for x in self.x]
+        alpha = [(t * self.tw).float() for _, _, t in packed]
+
+        def gemm(i):
+            codes, scales, _ = packed[i % len(packed)]
+            return NV.nvfp4_linear(codes, scales, self.w_codes, self.w_scales, alpha[i % len(packed)], self.one, None)
+
+        for i in range(3):
+            gemm(i)
+        secs = time_region(gemm, reps, torch.cuda.synchronize) / reps
+        achieved = 2.0 * self.tokens * self.N * self.K / secs / 1e12
+        peak = 4.0 * peaks["bf16_tflops"]
+        return secs, {"kernel": "gemm_nvfp4_kernel (tcgen05 kind::mxf4nvf4.block_scale, 2048x14336x4096)",
+                      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                      "peak_source": f"4 x {peaks['source']} bf16 cuBLAS burst (no FP4 peak was measured)",
+                      "traffic": None}
+
+    @staticmethod
+    def cpu_setup():
+        from oracle import quantizers as OQ
+        from oracle import tables as OT
+
+        g = torch.Generator().manual_seed(40)
+        w = (torch.randn(C4.N, C4.K, generator=g) * 0.02).bfloat16()
+        x = torch.randn(C4.cpu_tokens, C4.K, generator=g).bfloat16()
+        e2m1, e4m3 = OT.quantization_map("fp4_e2m1"), OT.quantization_map("fp8_e4m3")
+        tw = OQ.calculate_global_scale(w, 6.0, 448.0)
+        sw, cw = OQ.quantize_mx(w, e2m1, [-1], 16, 6.0, False, e4m3, None, None, tw)
+        return x, cw, sw, tw, e2m1, e4m3
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import gemm as OG
+        from oracle import quantizers as OQ
+
+        x, cw, sw, tw, e2m1, e4m3 = state
+        t = OQ.calculate_global_scale(x, 6.0, 448.0)
+        sx, cx = OQ.quantize_mx(x, e2m1, [-1], 16, 6.0, False, e4m3, None, None, t)
+        return OG.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=16, alpha=t * tw)
+
+
+WORKLOADS = {"c1": C1, "c2": C2, "c4": C4, "q1": Q1}
 
 
 def time_cpu_baseline(workload, reps):
