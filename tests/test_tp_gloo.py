@@ -38,3 +38,65 @@ def test_shard_bounds_respect_blocks():
     assert c.shape == (4, 4) and s.shape == (4, 1) and float(s[0, 0]) == 1.0
     c, s = P.shard_weight(codes, scale, "column", 1, 2, 4)
     assert c.shape == (2, 8) and s.shape == (2, 2)
+
+
+def test_lpt_schedule_balances_llama_linears():
+    import voyager_b200
+
+    P = voyager_b200.parallel
+    shapes = [(4096, 4096), (1024, 4096), (1024, 4096), (4096, 4096), (14336, 4096), (14336, 4096), (4096, 14336)] * 32
+    costs = [P.gptq_cost(262144, o, k) for o, k in shapes]
+    plan = P.lpt_schedule(costs, 8)
+    assert sorted(i for part in plan for i in part) == list(range(len(shapes)))
+    loads = [sum(costs[i] for i in part) for part in plan]
+    assert max(loads) <= 1.02 * (sum(costs) / 8)          # within 2 % of a perfect split
+    assert P.lpt_schedule(costs, 8) == plan               # deterministic: every rank derives the same table
+
+
+def _gptq_rank(rank, world, port, results):
+    import os
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import voyager_b200
+    from oracle import gptq as OG
+    from oracle import tables as OT
+
+    g = torch.Generator().manual_seed(5)
+    problems = []
+    for out_f, in_f in ((16, 128), (8, 64), (24, 128), (8, 64), (16, 64)):
+        x = torch.randn(256, in_f, generator=g)
+        problems.append(dict(weight=torch.randn(out_f, in_f, generator=g) * 0.02, hessian=x.T @ x, tokens=256))
+    calls = []
+
+    def solve(p):
+        calls.append(tuple(p["weight"].shape))
+        fq = type("FQ", (), dict(block_size=32, ch_axis=-1, qmap=OT.quantization_map("int4"),
+                                 scale_qmap=OT.quantization_map("fp8_e5m3"), quant_max=7.0))
+        return OG.compensate_weight(p["weight"], p["hessian"].clone(), p["tokens"], fq.qmap, fq.scale_qmap, fq.quant_max,
+                                    fq.block_size, 0.01, False, True, False)
+
+    out = voyager_b200.parallel.gptq_layer_parallel(problems, solve)
+    results[rank] = (len(calls), [o.clone() for o in out])
+    dist.destroy_process_group()
+
+
+def test_gptq_layer_parallel_two_ranks():
+    from oracle import gptq as OG
+    from oracle import tables as OT
+
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_gptq_rank, args=(2, 29613, results), nprocs=2, join=True)
+    (n0, out0), (n1, out1) = results[0], results[1]
+    assert n0 + n1 == 5 and n0 >= 2 and n1 >= 2          # the work was split, nobody solved everything
+    for a, b in zip(out0, out1):
+        assert torch.equal(a, b)                          # every rank ends with every compensated weight
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(256, 128, generator=g)
+    w = torch.randn(16, 128, generator=g) * 0.02
+    want = OG.compensate_weight(w, x.T @ x, 256, OT.quantization_map("int4"), OT.quantization_map("fp8_e5m3"), 7.0, 32,
+                                0.01, False, True, False)
+    assert torch.equal(out0[0], want)

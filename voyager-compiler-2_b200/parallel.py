@@ -184,3 +184,55 @@ class TensorParallelMLP:
                                    scatter_output=scatter_output, group=self.group, ops=self.ops)
 
     __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# GPTQ over several GPUs: the linears of a model are independent problems
+# ---------------------------------------------------------------------------
+def gptq_cost(tokens: int, out_features: int, in_features: int) -> float:
+    """Relative cost of one GPTQ problem: the Hessian ``X^T X`` (tokens * K^2), its Cholesky
+    factorisations (K^3) and the column sweep with its trailing updates (out * K^2)."""
+    k = float(in_features)
+    return float(tokens) * k * k + k ** 3 + float(out_features) * k * k
+
+
+def lpt_schedule(costs, world: int):
+    """Longest-processing-time assignment of problems to ``world`` ranks: problems in descending
+    cost, each to the rank with the least work so far (ties to the lower rank, so every rank
+    computes the same table without communicating).  Returns one list of problem indices per rank."""
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    load = [0.0] * world
+    assignment = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda q: (load[q], q))
+        assignment[r].append(i)
+        load[r] += costs[i]
+    return assignment
+
+
+def gptq_layer_parallel(problems, solve, group=None):
+    """Run independent GPTQ problems across the ranks of ``group`` and give every rank all results.
+
+    ``problems`` is the same list on every rank, each item a dict with ``weight [out, in]``,
+    ``tokens`` and whatever ``solve(problem) -> Tensor`` needs (its Hessian or calibration
+    activations); ``solve`` is called only for the problems this rank owns under the LPT schedule
+    (cost ``gptq_cost``).  The reference walks a model's linears one after another
+    (``quantization/gptq.py:560-707``); with calibration activations given per linear they do not
+    depend on each other, and the only exchange is handing the compensated weights round at the end."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    costs = [gptq_cost(p["tokens"], p["weight"].shape[0], p["weight"].shape[1]) for p in problems]
+    mine = lpt_schedule(costs, world)[rank]
+    local = {i: solve(problems[i]) for i in mine}
+    if world == 1:
+        return [local[i] for i in range(len(problems))]
+    owner = {}
+    for r, indices in enumerate(lpt_schedule(costs, world)):
+        for i in indices:
+            owner[i] = r
+    results = []
+    for i, p in enumerate(problems):
+        out = local[i] if owner[i] == rank else torch.empty_like(p["weight"])
+        dist.broadcast(out, src=dist.get_global_rank(group, owner[i]) if group is not None else owner[i], group=group)
+        results.append(out)
+    return results
