@@ -1,7 +1,7 @@
 """Generate the golden fixtures from the reference's own CPU code.
 
-Run in a container that has the reference checkout (default
-``/root/reference``; override with ``VOYAGER_REFERENCE_ROOT``)::
+Run where the reference checkout is available (``reference_shim.REFERENCE_ROOT``;
+set ``VOYAGER_REFERENCE_ROOT`` to point elsewhere)::
 
     python tests/golden/make_golden.py
 
