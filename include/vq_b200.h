@@ -323,6 +323,28 @@ int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t rows, int64_t
                             const void* mask, int64_t mask_rows, int64_t causal_period,
                             const void* out_scale, int out_scale_dtype, int format, void* stream);
 
+/* Causal self-attention of a per-tensor FP8 decoder layer in one kernel: the two
+ * attention matmuls (backend/gpu/fp8.py:253-309, fp8_bmm) with the scale / causal
+ * mask / softmax / FP8 cast of the probabilities between them and the FP8 cast
+ * of the context after them, every bfloat16 rounding of the separate operators
+ * kept:
+ *   scores = bf16(q8 k8^T * alpha_qk); s = bf16(scores * score_scale), keys > query masked
+ *   p8 = e4m3(bf16(bf16(softmax_fp32(s)) / p_scale))
+ *   ctx = bf16(p8 v8 * alpha_pv); out8 = e4m3(bf16(ctx / ctx_scale))
+ * q8: e4m3 [kv_heads, groups * T, 128], the query heads of a KV group stacked
+ * along the rows; k8: e4m3 [kv_heads, T, 128]; vt8: e4m3 [kv_heads, 128, T].
+ * out8 (or NULL): e4m3 [T, ld8], head h = kv * groups + g at columns [128 h, +128);
+ * out16 (or NULL): bfloat16 ctx [kv_heads, groups * T, 128].  The scalars are
+ * device pointers of the given dtypes.  head_dim must be 128 and T a multiple of
+ * 128, else VQ_EUNSUPPORTED.  vq_attention_status reports (and optionally
+ * clears) VQ_ETIMEOUT if a wait inside the kernel ran out; it synchronises. */
+int vq_attention_fp8(const void* q8, const void* k8, const void* vt8, void* out8, int64_t ld8, void* out16,
+                     int64_t T, int64_t kv_heads, int64_t groups, int64_t head_dim, const void* alpha_qk,
+                     int alpha_qk_dtype, float score_scale, const void* p_scale, int p_scale_dtype,
+                     const void* alpha_pv, int alpha_pv_dtype, const void* ctx_scale, int ctx_scale_dtype,
+                     void* stream);
+int vq_attention_status(int reset);
+
 /* FP8 casts fused with the bfloat16 operation that feeds them in a per-tensor FP8
  * decoder layer.  The reference's converted graph runs the producer (RMSNorm,
  * rotary embedding, SiLU * up, a transpose) as separate aten nodes and then

@@ -1,0 +1,498 @@
+// Causal self-attention on per-tensor FP8 operands in one kernel:
+//     scores = bf16(q8 k8^T * alpha_qk)                  (the FP8 GEMM's rounding)
+//     s      = bf16(scores * score_scale), causal mask
+//     p      = bf16(softmax_fp32(s)),  p8 = fp8(bf16(p / s_p))
+//     ctx    = bf16(p8 v8 * alpha_pv), ctx8 = fp8(bf16(ctx / s_ctx))
+// which an eager graph runs as GEMM, softmax + cast, GEMM, cast, writing and re-reading
+// the [heads * T, T] score and probability matrices.  Here neither leaves the SM.
+//
+// One CTA owns 128 query rows of one head.  Because p8 is the FP8 code of the
+// normalised probability, the row maximum and sum must be final before the first
+// code can be formed, so the CTA walks its key blocks twice:
+//   pass A: S_j = Q K_j^T in tensor memory; running row maximum and sum
+//   pass B: S_j again (bit-identical), probabilities and their FP8 codes written to
+//           shared memory in the MMA operand layout, O += P_j V_j
+// Every rounding step of the unfused sequence is kept.  The exponential and the
+// reciprocal products are within an ulp of the unfused ones before they are rounded
+// to bfloat16 and the row sum is accumulated in another order, so a probability code
+// differs by one FP8 step only when a value sits on a rounding boundary.
+//
+// Warps: 0 TMA producer, 1 MMA issuer, 2-5 and 6-9 two softmax groups.  A softmax
+// thread owns one query row (one tensor-memory lane), so row statistics need no
+// shuffles; group w takes key blocks j = w, w + 2, ... and the two groups merge their
+// statistics once, between the passes.  Every wait is bounded.
+
+#include <cuda.h>
+
+#include <cstring>
+
+#include "fp8_cast.cuh"
+#include "sm100_ptx.cuh"
+
+namespace vq {
+namespace {
+
+using namespace sm100;
+
+constexpr int AT_BLK = 128;                 // query rows per CTA, keys per block, head_dim
+constexpr int AT_TILE = AT_BLK * AT_BLK;    // bytes of one FP8 operand tile
+constexpr int AT_STAGES = 4;                // K / V tiles in flight
+constexpr int AT_THREADS = 320;
+constexpr int AT_TMEM_COLS = 512;           // S0 [0,128), S1 [128,256), O [256,384)
+constexpr uint32_t AT_O_COL = 256;
+constexpr int AT_STATS_BYTES = 2 * 2 * AT_BLK * 4;   // (max, sum) x two groups x 128 rows
+constexpr size_t AT_SMEM_BYTES = 1024 + (1 + AT_STAGES + 2) * AT_TILE + AT_STATS_BYTES + 256;
+
+__device__ int g_attention_error = 0;
+
+struct AttnParams {
+  int T, groups, kv_heads;
+  const void* alpha_qk;
+  int alpha_qk_dt;
+  float score_scale;
+  const void* p_scale;
+  int p_scale_dt;
+  const void* alpha_pv;
+  int alpha_pv_dt;
+  const void* ctx_scale;   // scale of the FP8 output
+  int ctx_scale_dt;
+  uint8_t* out8;           // [T, ld8] e4m3, head h at columns [h * 128, +128), or null
+  int64_t ld8;
+  __nv_bfloat16* out16;    // [kv_heads, groups * T, 128], or null
+};
+
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+__device__ __forceinline__ uint32_t pack2(float2 v) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 round2(float2 v) { return unpack2(pack2(v)); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float ex2(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ void group_barrier_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// s = bf16(bf16(acc * alpha_qk) * score_scale) for 32 accumulator columns, as 16 pairs.
+// In the diagonal block, column c of the block is masked for row r when c > r.
+template <bool DIAG>
+__device__ __forceinline__ void scores_of_chunk(const uint32_t (&v)[32], float2 (&s)[16], float alpha, float scale,
+                                                int col0, int r) {
+  const float2 a2 = make_float2(alpha, alpha), s2 = make_float2(scale, scale);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float2 x = make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+    x = round2(__fmul2_rn(x, a2));
+    x = round2(__fmul2_rn(x, s2));
+    if (DIAG) {
+      if (col0 + 2 * i > r) x.x = -INFINITY;
+      if (col0 + 2 * i + 1 > r) x.y = -INFINITY;
+    }
+    s[i] = x;
+  }
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_q = smem;
+  uint8_t* ring = smem + AT_TILE;                              // [AT_STAGES] K or V tiles
+  uint8_t* smem_p = ring + AT_STAGES * AT_TILE;                // [2] probability tiles, one per softmax group
+  float* stats = reinterpret_cast<float*>(smem_p + 2 * AT_TILE);   // [2 groups][max, sum][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_p + 2 * AT_TILE + AT_STATS_BYTES);
+  uint64_t* q_full = bars;                        // [1]
+  uint64_t* kv_full = bars + 1;                   // [AT_STAGES]
+  uint64_t* kv_empty = kv_full + AT_STAGES;       // [AT_STAGES]
+  uint64_t* s_full = kv_empty + AT_STAGES;        // [2] score tile complete in tensor memory
+  uint64_t* s_empty = s_full + 2;                 // [2] score tile read by its group (4 warps arrive)
+  uint64_t* p_full = s_empty + 2;                 // [2] probability tile written (4 warps arrive)
+  uint64_t* p_empty = p_full + 2;                 // [2] probability tile read by the MMA
+  uint64_t* o_full = p_empty + 2;                 // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Work item: CTAs with the most key blocks come first in launch order.
+  const int nb = p.T / AT_BLK;
+  const int per_level = p.kv_heads * p.groups;
+  const int jd = nb - 1 - (int)(blockIdx.x / per_level);      // the diagonal block; blocks 0..jd are live
+  const int rest = (int)(blockIdx.x % per_level);
+  const int kvh = rest / p.groups, g = rest % p.groups;
+  const int qrow0 = g * p.T + jd * AT_BLK;                    // first query row within the KV head's [groups * T]
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < AT_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&s_empty[b], 4);
+      mbar_init(&p_full[b], 4);
+      mbar_init(&p_empty[b], 1);
+    }
+    mbar_init(o_full, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, AT_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_q);
+      prefetch_tensormap(&map_k);
+      prefetch_tensormap(&map_v);
+      mbar_arrive_expect_tx(q_full, AT_TILE);
+      tma_load_3d(smem_q, &map_q, q_full, 0, qrow0, kvh);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      auto load = [&](const CUtensorMap* map, int x, int y) {
+        if (!ok) return;
+        if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag)) { ok = false; return; }
+        mbar_arrive_expect_tx(&kv_full[stage], AT_TILE);
+        tma_load_3d(ring + stage * AT_TILE, map, &kv_full[stage], x, y, kvh);
+        if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
+      };
+      for (int j = 0; j <= jd; ++j) load(&map_k, 0, j * AT_BLK);          // pass A
+      // pass B, in the order the MMA warp consumes: K0, K1, then V_j and K_{j+2} alternating
+      load(&map_k, 0, 0);
+      if (jd >= 1) load(&map_k, 0, AT_BLK);
+      for (int j = 0; j <= jd; ++j) {
+        load(&map_v, j * AT_BLK, 0);
+        if (j + 2 <= jd) load(&map_k, 0, (j + 2) * AT_BLK);
+      }
+      if (!ok) {
+        // Drain: let copies already issued land before the CTA's shared memory goes away.
+        for (int s = 0; s < AT_STAGES; ++s)
+          for (int spin = 0; spin < (1 << 14); ++spin)
+            if (mbar_try_wait(&kv_full[s], 0) || mbar_try_wait(&kv_full[s], 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(AT_BLK, AT_BLK, 0, 0, 0, 0);   // e4m3 x e4m3, M = N = 128
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t s_uses[2] = {0, 0}, p_uses[2] = {0, 0};
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      const uint32_t q_addr = smem_u32(smem_q);
+      // S[j & 1] = Q K_j^T
+      auto issue_scores = [&](int j) {
+        if (!ok) return;
+        const int b = j & 1;
+        if (!mbar_wait(&kv_full[stage], phase, abort_flag) ||
+            !mbar_wait(&s_empty[b], (s_uses[b] & 1) ^ 1, abort_flag)) { ok = false; return; }
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(ring + stage * AT_TILE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f8f6f4_ss(tmem_base + (uint32_t)(b * AT_BLK), smem_desc_k_major_sw128(q_addr + k * 32),
+                        smem_desc_k_major_sw128(k_addr + k * 32), idesc, k > 0 ? 1u : 0u);
+        mma_commit(&kv_empty[stage]);
+        mma_commit(&s_full[b]);
+        ++s_uses[b];
+        if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
+      };
+      // O += P_j V_j
+      auto issue_context = [&](int j) {
+        if (!ok) return;
+        const int b = j & 1;
+        if (!mbar_wait(&kv_full[stage], phase, abort_flag) ||
+            !mbar_wait(&p_full[b], p_uses[b] & 1, abort_flag)) { ok = false; return; }
+        tc_fence_after_sync();
+        const uint32_t p_addr = smem_u32(smem_p + b * AT_TILE);
+        const uint32_t v_addr = smem_u32(ring + stage * AT_TILE);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f8f6f4_ss(tmem_base + AT_O_COL, smem_desc_k_major_sw128(p_addr + k * 32),
+                        smem_desc_k_major_sw128(v_addr + k * 32), idesc, (j > 0 || k > 0) ? 1u : 0u);
+        mma_commit(&kv_empty[stage]);
+        mma_commit(&p_empty[b]);
+        ++p_uses[b];
+        if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
+      };
+      for (int j = 0; j <= jd; ++j) issue_scores(j);                       // pass A
+      issue_scores(0);                                                     // pass B
+      if (jd >= 1) issue_scores(1);
+      for (int j = 0; j <= jd; ++j) {
+        issue_context(j);
+        if (j + 2 <= jd) issue_scores(j + 2);
+      }
+      if (ok) mma_commit(o_full);
+    }
+  } else {
+    // ------------------------------ softmax groups ----------------------------
+    const int w = (warp - 2) >> 2;                 // group: key blocks j = w, w + 2, ...
+    const int quarter = warp & 3;                  // tensor-memory lanes [32 * quarter, +32) are this warp's
+    const int r = quarter * 32 + lane;             // this thread's query row within the block
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const float alpha = loadp(p.alpha_qk, 0, p.alpha_qk_dt);
+    uint32_t s_uses = 0, p_uses = 0;               // tiles taken from S[w], tiles written to P[w]
+    bool ok = true;
+    uint32_t v[32];
+    float2 s[16];
+
+    // ---- pass A: running maximum m and sum l of exp(s - m) over this group's blocks ----
+    float m = -INFINITY, l = 0.0f;
+    for (int j = w; j <= jd && ok; j += 2) {
+      // The warp must stay convergent for the .sync.aligned tensor-memory loads below.
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s_full[w], s_uses & 1, abort_flag))) { ok = false; break; }
+      ++s_uses;
+      tc_fence_after_sync();
+      const bool diag = j == jd;
+      // in the diagonal block a chunk whose first column exceeds the warp's last row is masked for the whole warp
+      const int chunks = diag ? quarter + 1 : 4;
+      for (int c = 0; c < chunks; ++c) {
+        tmem_ld_32x32(lane_addr + (uint32_t)(w * AT_BLK + c * 32), v);
+        tmem_ld_wait();
+        if (diag) scores_of_chunk<true>(v, s, alpha, p.score_scale, c * 32, r);
+        else scores_of_chunk<false>(v, s, alpha, p.score_scale, c * 32, r);
+        float cmax = m;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) cmax = max3(cmax, s[i].x, s[i].y);
+        // column 0 of every live block is at or before the row, so cmax is finite from the first chunk on
+        const float shift = -cmax * kLog2e;
+        const float2 shift2 = make_float2(shift, shift), log2e2 = make_float2(kLog2e, kLog2e);
+        float2 sum2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 a = __ffma2_rn(s[i], log2e2, shift2);
+          sum2 = __fadd2_rn(sum2, make_float2(ex2(a.x), ex2(a.y)));
+        }
+        l = fmaf(l, ex2(fmaf(m, kLog2e, shift)), sum2.x + sum2.y);   // m = -inf only while l = 0
+        m = cmax;
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[w]);
+    }
+
+    // ---- merge the two groups' statistics (every softmax thread reaches this barrier) ----
+    stats[(w * 2 + 0) * AT_BLK + r] = m;
+    stats[(w * 2 + 1) * AT_BLK + r] = l;
+    group_barrier_256();
+    if (*abort_flag) ok = false;
+    const float m0 = stats[0 * AT_BLK + r], l0 = stats[1 * AT_BLK + r];
+    const float m1 = stats[2 * AT_BLK + r], l1 = stats[3 * AT_BLK + r];   // (-inf, 0) when the group had no block
+    const float mf = fmaxf(m0, m1);
+    const float lf = fmaf(l1, ex2((m1 - mf) * kLog2e), l0 * ex2((m0 - mf) * kLog2e));
+    // p = bf16(e / sum), code = fp8(bf16(p / s_p)): both quotients as products with the correctly
+    // rounded reciprocal.  p >= 0, so no -0 can arise.
+    const float rl = __frcp_rn(lf), rsp = __frcp_rn(loadp(p.p_scale, 0, p.p_scale_dt));
+    const float2 rl2 = make_float2(rl, rl), rsp2 = make_float2(rsp, rsp);
+    const float2 log2e2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mf * kLog2e, -mf * kLog2e);
+
+    // ---- pass B: probabilities of this group's blocks as FP8 codes in the MMA operand layout ----
+    // Row r of a K-major tile with the 128-byte swizzle: 16-byte chunk a sits at chunk a ^ (r % 8).
+    uint8_t* p_row = smem_p + w * AT_TILE + (r >> 3) * 1024 + (r & 7) * 128;
+    for (int j = w; j <= jd && ok; j += 2) {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s_full[w], s_uses & 1, abort_flag) &&
+                                       mbar_wait(&p_empty[w], (p_uses & 1) ^ 1, abort_flag))) { ok = false; break; }
+      ++s_uses;
+      ++p_uses;
+      tc_fence_after_sync();
+      const bool diag = j == jd;
+      const int chunks = diag ? quarter + 1 : 4;
+      for (int c = 0; c < 4; ++c) {
+        uint32_t codes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (c < chunks) {
+          tmem_ld_32x32(lane_addr + (uint32_t)(w * AT_BLK + c * 32), v);
+          tmem_ld_wait();
+          if (diag) scores_of_chunk<true>(v, s, alpha, p.score_scale, c * 32, r);
+          else scores_of_chunk<false>(v, s, alpha, p.score_scale, c * 32, r);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float2 a = __ffma2_rn(s[i], log2e2, shift2);
+            const float2 prob = round2(__fmul2_rn(make_float2(ex2(a.x), ex2(a.y)), rl2));
+            const float2 f = round2(__fmul2_rn(prob, rsp2));
+            const uint32_t code = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+            codes[i >> 1] |= code << (16 * (i & 1));
+          }
+        }
+        *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+        *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[w]);
+        mbar_arrive(&p_full[w]);
+      }
+    }
+
+    // ---- output: group w converts accumulator columns [64 w, 64 w + 64) of its rows ----
+    if (ok && !__all_sync(0xFFFFFFFFu, mbar_wait(o_full, 0, abort_flag))) ok = false;
+    if (ok) {
+      tc_fence_after_sync();
+      const float alpha_pv = loadp(p.alpha_pv, 0, p.alpha_pv_dt);
+      const int t = jd * AT_BLK + r;                         // position in the sequence
+      const int head = kvh * p.groups + g;
+      Divisor dv;
+      if (p.out8 != nullptr) dv = make_divisor(p.ctx_scale, p.ctx_scale_dt);
+      for (int c = 0; c < 2; ++c) {
+        const int col0 = w * 64 + c * 32;
+        tmem_ld_32x32(lane_addr + AT_O_COL + (uint32_t)col0, v);
+        tmem_ld_wait();
+        uint32_t words[16];   // ctx = bf16(acc * alpha_pv), two per word
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          words[i] = pack2(__fmul2_rn(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])),
+                                      make_float2(alpha_pv, alpha_pv)));
+        if (p.out16 != nullptr) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out16 + ((int64_t)kvh * p.groups * p.T + qrow0 + r) * AT_BLK + col0);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) dst[q] = make_uint4(words[4 * q], words[4 * q + 1], words[4 * q + 2], words[4 * q + 3]);
+        }
+        if (p.out8 != nullptr) {
+          uint32_t codes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            codes[i >> 1] |= fp8_pair<true>(quot(lo_of(words[i]), dv), quot(hi_of(words[i]), dv)) << (16 * (i & 1));
+          uint4* dst = reinterpret_cast<uint4*>(p.out8 + (int64_t)t * p.ld8 + head * AT_BLK + col0);
+          dst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+          dst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+        }
+      }
+      tc_fence_before_sync();
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_attention_error, VQ_ETIMEOUT);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, AT_TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// Tensor map over a [batch, rows, cols] byte matrix, cols contiguous; boxes of 128 rows x 128 bytes
+// in the 128-byte swizzle (the K-major MMA operand layout).
+int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t batch) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)cols, (cuuint64_t)(rows * cols)};
+  cuuint32_t box[3] = {AT_BLK, AT_BLK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return VQ_OK;
+}
+
+}  // namespace
+}  // namespace vq
+
+using namespace vq;
+
+extern "C" int vq_attention_fp8(const void* q8, const void* k8, const void* vt8, void* out8, int64_t ld8, void* out16,
+                                int64_t T, int64_t kv_heads, int64_t groups, int64_t head_dim, const void* alpha_qk,
+                                int alpha_qk_dtype, float score_scale, const void* p_scale, int p_scale_dtype,
+                                const void* alpha_pv, int alpha_pv_dtype, const void* ctx_scale, int ctx_scale_dtype,
+                                void* stream) {
+  VQ_REQUIRE(T >= 0 && kv_heads >= 0 && groups >= 0, "vq_attention_fp8: negative extent");
+  if (T == 0 || kv_heads == 0 || groups == 0) return VQ_OK;
+  if (head_dim != AT_BLK || T % AT_BLK != 0)
+    return fail(VQ_EUNSUPPORTED, "vq_attention_fp8: head_dim must be 128 and T a multiple of 128");
+  VQ_REQUIRE(q8 && k8 && vt8 && alpha_qk && p_scale && alpha_pv, "vq_attention_fp8: null argument");
+  VQ_REQUIRE(out8 || out16, "vq_attention_fp8: no output");
+  VQ_REQUIRE(!out8 || (ctx_scale && ld8 >= kv_heads * groups * AT_BLK && ld8 % 16 == 0),
+             "vq_attention_fp8: the FP8 output needs its scale and a row stride of at least heads * 128, a multiple of 16");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(q8) | reinterpret_cast<uintptr_t>(k8) | reinterpret_cast<uintptr_t>(vt8) |
+               reinterpret_cast<uintptr_t>(out8) | reinterpret_cast<uintptr_t>(out16)) & 15) == 0,
+             "vq_attention_fp8: misaligned buffers");
+  const int64_t items = kv_heads * groups * (T / AT_BLK);
+  VQ_REQUIRE(T < (1ll << 24) && groups * T < (1ll << 31) && kv_heads < 65536 && items < (1ll << 31),
+             "vq_attention_fp8: extent too large");
+  CUtensorMap map_q, map_k, map_v;
+  int rc;
+  if ((rc = make_tile_map(&map_q, q8, groups * T, AT_BLK, kv_heads)) != VQ_OK) return rc;
+  if ((rc = make_tile_map(&map_k, k8, T, AT_BLK, kv_heads)) != VQ_OK) return rc;
+  if ((rc = make_tile_map(&map_v, vt8, AT_BLK, T, kv_heads)) != VQ_OK) return rc;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.T = (int)T;
+  p.groups = (int)groups;
+  p.kv_heads = (int)kv_heads;
+  p.alpha_qk = alpha_qk;
+  p.alpha_qk_dt = alpha_qk_dtype;
+  p.score_scale = score_scale;
+  p.p_scale = p_scale;
+  p.p_scale_dt = p_scale_dtype;
+  p.alpha_pv = alpha_pv;
+  p.alpha_pv_dt = alpha_pv_dtype;
+  p.ctx_scale = ctx_scale;
+  p.ctx_scale_dt = ctx_scale_dtype;
+  p.out8 = static_cast<uint8_t*>(out8);
+  p.ld8 = ld8;
+  p.out16 = static_cast<__nv_bfloat16*>(out16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)AT_SMEM_BYTES);
+    if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  attention_fp8_kernel<<<(unsigned)items, AT_THREADS, AT_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_q, map_k,
+                                                                                                         map_v, p);
+  return check_launch("attention_fp8_kernel");
+}
+
+// A wait inside the kernel ran out (VQ_ETIMEOUT) since the last reset, else VQ_OK.  Synchronises the device.
+extern "C" int vq_attention_status(int reset) {
+  int v = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(VQ_ECUDA, "vq_attention_status: %s", cudaGetErrorString(e));
+  cudaMemcpyFromSymbol(&v, g_attention_error, sizeof(int));
+  if (reset) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attention_error, &zero, sizeof(int));
+  }
+  return v;
+}

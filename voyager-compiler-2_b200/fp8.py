@@ -143,6 +143,42 @@ def softmax_quantize_fp8(scores: torch.Tensor, score_scale: float, out_scale: to
     return out
 
 
+def attention_fp8(q8: torch.Tensor, k8: torch.Tensor, vt8: torch.Tensor, alpha_qk: torch.Tensor, score_scale: float,
+                  p_scale: torch.Tensor, alpha_pv: torch.Tensor, ctx_scale: Optional[torch.Tensor] = None):
+    """Causal attention on FP8 operands in one kernel: ``fp8_gemm(q8, k8, alpha_qk)``,
+    ``softmax_quantize_fp8(.., score_scale, p_scale, causal_period=T)``, ``fp8_gemm(p8, vt8, alpha_pv)``
+    and, with ``ctx_scale``, the cast of the context, with the same rounding steps.
+    ``q8``: ``[kv_heads, groups * T, 128]`` (a KV group's query heads stacked along the rows),
+    ``k8``: ``[kv_heads, T, 128]``, ``vt8``: ``[kv_heads, 128, T]``, all e4m3 codes.
+    Returns the e4m3 context ``[T, heads * 128]`` when ``ctx_scale`` is given, else the
+    bfloat16 context ``[kv_heads, groups * T, 128]``."""
+    kv, rows, d = q8.shape
+    T = k8.shape[1]
+    groups = rows // T
+    if k8.shape != (kv, T, d) or vt8.shape != (kv, d, T) or groups * T != rows:
+        raise ValueError("attention_fp8: operand shapes do not agree")
+    q8, k8, vt8 = q8.contiguous(), k8.contiguous(), vt8.contiguous()
+    scalars = [_scale_arg(t) for t in (alpha_qk, p_scale, alpha_pv)]
+    out8 = out16 = None
+    if ctx_scale is not None:
+        ctx_scale = _scale_arg(ctx_scale)
+        out8 = torch.empty((T, kv * groups * d), dtype=torch.uint8, device=q8.device)
+    else:
+        out16 = torch.empty((kv, rows, d), dtype=torch.bfloat16, device=q8.device)
+    N.check(N.lib().vq_attention_fp8(q8.data_ptr(), k8.data_ptr(), vt8.data_ptr(), _ptr(out8), kv * groups * d,
+                                     _ptr(out16), T, kv, groups, d, scalars[0].data_ptr(), _dtype_id(scalars[0].dtype),
+                                     float(score_scale), scalars[1].data_ptr(), _dtype_id(scalars[1].dtype),
+                                     scalars[2].data_ptr(), _dtype_id(scalars[2].dtype), _ptr(ctx_scale),
+                                     _dtype_id(ctx_scale.dtype) if ctx_scale is not None else 0, _stream()),
+            "vq_attention_fp8")
+    return out8 if out8 is not None else out16
+
+
+def attention_status(reset: bool = True) -> int:
+    """0, or the timeout code if a bounded wait inside ``attention_fp8`` ran out since the last reset."""
+    return N.lib().vq_attention_status(int(reset))
+
+
 def _scale_arg(scale: torch.Tensor) -> torch.Tensor:
     if scale.numel() != 1:
         raise ValueError("the fused FP8 casts take one per-tensor scale")
