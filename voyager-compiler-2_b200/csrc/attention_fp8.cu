@@ -17,10 +17,11 @@
 // to bfloat16 and the row sum is accumulated in another order, so a probability code
 // differs by one FP8 step only when a value sits on a rounding boundary.
 //
-// Warps: 0 TMA producer, 1 MMA issuer, 2-5 and 6-9 two softmax groups.  A softmax
-// thread owns one query row (one tensor-memory lane), so row statistics need no
-// shuffles; group w takes key blocks j = w, w + 2, ... and the two groups merge their
-// statistics once, between the passes.  Every wait is bounded.
+// Warps: 0 TMA producer, 1 MMA issuer, then four softmax groups of four warps.  A
+// softmax thread owns one query row (one tensor-memory lane) of 64 columns, so row
+// statistics need no shuffles: a group takes the key blocks of one parity and one half
+// of their columns, and the groups merge their statistics once, between the passes.
+// Every wait is bounded.
 
 #include <cuda.h>
 
@@ -36,12 +37,17 @@ using namespace sm100;
 
 constexpr int AT_BLK = 128;                 // query rows per CTA, keys per block, head_dim
 constexpr int AT_TILE = AT_BLK * AT_BLK;    // bytes of one FP8 operand tile
-constexpr int AT_STAGES = 4;                // K / V tiles in flight
-constexpr int AT_THREADS = 320;
-constexpr int AT_TMEM_COLS = 512;           // S0 [0,128), S1 [128,256), O [256,384)
-constexpr uint32_t AT_O_COL = 256;
-constexpr int AT_STATS_BYTES = 2 * 2 * AT_BLK * 4;   // (max, sum) x two groups x 128 rows
-constexpr size_t AT_SMEM_BYTES = 1024 + (1 + AT_STAGES + 2) * AT_TILE + AT_STATS_BYTES + 256;
+constexpr int AT_STAGES = 3;                // K / V tiles in flight
+constexpr int AT_SBUFS = 1;                 // score tiles in tensor memory (and probability tiles in shared memory)
+constexpr int AT_GROUPS = 2;                // softmax groups of four warps: (score buffer) x (column part)
+constexpr int AT_PARTS = AT_GROUPS / AT_SBUFS;   // column parts of a score tile
+constexpr int AT_CPT = 4 / AT_PARTS;        // 32-column chunks per thread and tile
+constexpr int AT_THREADS = 64 + AT_GROUPS * 128;
+constexpr int AT_CTAS_PER_SM = 2;           // two CTAs share an SM: one computes while the other waits or starts up
+constexpr int AT_TMEM_COLS = AT_SBUFS == 1 ? 256 : 512;   // score tiles, then the context accumulator
+constexpr uint32_t AT_O_COL = AT_SBUFS * AT_BLK;
+constexpr int AT_STATS_BYTES = AT_GROUPS * 2 * AT_BLK * 4;   // (max, sum) x groups x 128 rows
+constexpr size_t AT_SMEM_BYTES = 1024 + (1 + AT_STAGES + AT_SBUFS) * AT_TILE + AT_STATS_BYTES + 256;
 
 __device__ int g_attention_error = 0;
 
@@ -79,7 +85,7 @@ __device__ __forceinline__ float ex2(float v) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
   return r;
 }
-__device__ __forceinline__ void group_barrier_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(AT_GROUPS * 128) : "memory"); }
 
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -102,24 +108,66 @@ __device__ __forceinline__ void scores_of_chunk(const uint32_t (&v)[32], float2 
   }
 }
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// Pass A on one chunk: the running maximum m and the sum l of exp(s - m) take in 32 more columns.
+template <bool DIAG>
+__device__ __forceinline__ void accumulate_chunk(const uint32_t (&v)[32], float alpha, float scale, int col0, int r,
+                                                 float& m, float& l) {
+  float2 s[16];
+  scores_of_chunk<DIAG>(v, s, alpha, scale, col0, r);
+  float cmax = m;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) cmax = max3(cmax, s[i].x, s[i].y);
+  // a live chunk's first column is at or before the warp's first row, so cmax is finite
+  const float shift = -cmax * kLog2e;
+  const float2 shift2 = make_float2(shift, shift), log2e2 = make_float2(kLog2e, kLog2e);
+  float2 sum2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 a = __ffma2_rn(s[i], log2e2, shift2);
+    sum2 = __fadd2_rn(sum2, make_float2(ex2(a.x), ex2(a.y)));
+  }
+  l = fmaf(l, ex2(fmaf(m, kLog2e, shift)), sum2.x + sum2.y);   // m = -inf only while l = 0
+  m = cmax;
+}
+
+// Pass B on one chunk: the 32 probabilities' FP8 codes.  p = bf16(e / sum), code = fp8(bf16(p / s_p)),
+// both quotients as products with the correctly rounded reciprocal; p >= 0, so no -0 can arise.
+template <bool DIAG>
+__device__ __forceinline__ void codes_of_chunk(const uint32_t (&v)[32], uint32_t (&codes)[8], float alpha, float scale,
+                                               int col0, int r, float shift, float rl, float rsp) {
+  float2 s[16];
+  scores_of_chunk<DIAG>(v, s, alpha, scale, col0, r);
+  const float2 log2e2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(shift, shift);
+  const float2 rl2 = make_float2(rl, rl), rsp2 = make_float2(rsp, rsp);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 a = __ffma2_rn(s[i], log2e2, shift2);
+    const float2 prob = round2(__fmul2_rn(make_float2(ex2(a.x), ex2(a.y)), rl2));
+    const float2 f = round2(__fmul2_rn(prob, rsp2));
+    const uint32_t code = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
+    if ((i & 1) == 0) codes[i >> 1] = code;
+    else codes[i >> 1] |= code << 16;
+  }
+}
+
+__global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM)
 attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_q = smem;
   uint8_t* ring = smem + AT_TILE;                              // [AT_STAGES] K or V tiles
-  uint8_t* smem_p = ring + AT_STAGES * AT_TILE;                // [2] probability tiles, one per softmax group
-  float* stats = reinterpret_cast<float*>(smem_p + 2 * AT_TILE);   // [2 groups][max, sum][128 rows]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_p + 2 * AT_TILE + AT_STATS_BYTES);
+  uint8_t* smem_p = ring + AT_STAGES * AT_TILE;                // [AT_SBUFS] probability tiles
+  float* stats = reinterpret_cast<float*>(smem_p + AT_SBUFS * AT_TILE);   // [groups][max, sum][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_p + AT_SBUFS * AT_TILE + AT_STATS_BYTES);
   uint64_t* q_full = bars;                        // [1]
   uint64_t* kv_full = bars + 1;                   // [AT_STAGES]
   uint64_t* kv_empty = kv_full + AT_STAGES;       // [AT_STAGES]
-  uint64_t* s_full = kv_empty + AT_STAGES;        // [2] score tile complete in tensor memory
-  uint64_t* s_empty = s_full + 2;                 // [2] score tile read by its group (4 warps arrive)
-  uint64_t* p_full = s_empty + 2;                 // [2] probability tile written (4 warps arrive)
-  uint64_t* p_empty = p_full + 2;                 // [2] probability tile read by the MMA
-  uint64_t* o_full = p_empty + 2;                 // [1]
+  uint64_t* s_full = kv_empty + AT_STAGES;        // [AT_SBUFS] score tile complete in tensor memory
+  uint64_t* s_empty = s_full + AT_SBUFS;          // [AT_SBUFS] score tile read by its groups
+  uint64_t* p_full = s_empty + AT_SBUFS;          // [AT_SBUFS] probability tile written
+  uint64_t* p_empty = p_full + AT_SBUFS;          // [AT_SBUFS] probability tile read by the MMA
+  uint64_t* o_full = p_empty + AT_SBUFS;          // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -141,10 +189,10 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < AT_SBUFS; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 4);
-      mbar_init(&p_full[b], 4);
+      mbar_init(&s_empty[b], 4 * AT_PARTS);   // the warps of the groups that share the tile
+      mbar_init(&p_full[b], 4 * AT_PARTS);
       mbar_init(&p_empty[b], 1);
     }
     mbar_init(o_full, 1);
@@ -178,12 +226,11 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
       };
       for (int j = 0; j <= jd; ++j) load(&map_k, 0, j * AT_BLK);          // pass A
-      // pass B, in the order the MMA warp consumes: K0, K1, then V_j and K_{j+2} alternating
-      load(&map_k, 0, 0);
-      if (jd >= 1) load(&map_k, 0, AT_BLK);
+      // pass B, in the order the MMA warp consumes: the first K blocks, then V_j and K_{j + AT_SBUFS} alternating
+      for (int j = 0; j < AT_SBUFS && j <= jd; ++j) load(&map_k, 0, j * AT_BLK);
       for (int j = 0; j <= jd; ++j) {
         load(&map_v, j * AT_BLK, 0);
-        if (j + 2 <= jd) load(&map_k, 0, (j + 2) * AT_BLK);
+        if (j + AT_SBUFS <= jd) load(&map_k, 0, (j + AT_SBUFS) * AT_BLK);
       }
       if (!ok) {
         // Drain: let copies already issued land before the CTA's shared memory goes away.
@@ -198,13 +245,13 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       constexpr uint32_t idesc = make_idesc(AT_BLK, AT_BLK, 0, 0, 0, 0);   // e4m3 x e4m3, M = N = 128
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t s_uses[2] = {0, 0}, p_uses[2] = {0, 0};
+      uint32_t s_uses[AT_SBUFS] = {}, p_uses[AT_SBUFS] = {};
       bool ok = mbar_wait(q_full, 0, abort_flag);
       const uint32_t q_addr = smem_u32(smem_q);
-      // S[j & 1] = Q K_j^T
+      // S[j % AT_SBUFS] = Q K_j^T
       auto issue_scores = [&](int j) {
         if (!ok) return;
-        const int b = j & 1;
+        const int b = j % AT_SBUFS;
         if (!mbar_wait(&kv_full[stage], phase, abort_flag) ||
             !mbar_wait(&s_empty[b], (s_uses[b] & 1) ^ 1, abort_flag)) { ok = false; return; }
         tc_fence_after_sync();
@@ -221,7 +268,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       // O += P_j V_j
       auto issue_context = [&](int j) {
         if (!ok) return;
-        const int b = j & 1;
+        const int b = j % AT_SBUFS;
         if (!mbar_wait(&kv_full[stage], phase, abort_flag) ||
             !mbar_wait(&p_full[b], p_uses[b] & 1, abort_flag)) { ok = false; return; }
         tc_fence_after_sync();
@@ -237,17 +284,18 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
       };
       for (int j = 0; j <= jd; ++j) issue_scores(j);                       // pass A
-      issue_scores(0);                                                     // pass B
-      if (jd >= 1) issue_scores(1);
+      for (int j = 0; j < AT_SBUFS && j <= jd; ++j) issue_scores(j);       // pass B
       for (int j = 0; j <= jd; ++j) {
         issue_context(j);
-        if (j + 2 <= jd) issue_scores(j + 2);
+        if (j + AT_SBUFS <= jd) issue_scores(j + AT_SBUFS);
       }
       if (ok) mma_commit(o_full);
     }
   } else {
     // ------------------------------ softmax groups ----------------------------
-    const int w = (warp - 2) >> 2;                 // group: key blocks j = w, w + 2, ...
+    const int group = (warp - 2) >> 2;
+    const int w = group % AT_SBUFS;                // key blocks j = w, w + AT_SBUFS, ...
+    const int part = group / AT_SBUFS;             // columns [32 AT_CPT part, +32 AT_CPT) of each block
     const int quarter = warp & 3;                  // tensor-memory lanes [32 * quarter, +32) are this warp's
     const int r = quarter * 32 + lane;             // this thread's query row within the block
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -255,98 +303,94 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint32_t s_uses = 0, p_uses = 0;               // tiles taken from S[w], tiles written to P[w]
     bool ok = true;
     uint32_t v[32];
-    float2 s[16];
 
-    // ---- pass A: running maximum m and sum l of exp(s - m) over this group's blocks ----
+    // ---- pass A: running maximum m and sum l of exp(s - m) over this group's part of the scores ----
     float m = -INFINITY, l = 0.0f;
-    for (int j = w; j <= jd && ok; j += 2) {
+    for (int j = w; j <= jd && ok; j += AT_SBUFS) {
       // The warp must stay convergent for the .sync.aligned tensor-memory loads below.
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s_full[w], s_uses & 1, abort_flag))) { ok = false; break; }
       ++s_uses;
       tc_fence_after_sync();
       const bool diag = j == jd;
       // in the diagonal block a chunk whose first column exceeds the warp's last row is masked for the whole warp
-      const int chunks = diag ? quarter + 1 : 4;
-      for (int c = 0; c < chunks; ++c) {
-        tmem_ld_32x32(lane_addr + (uint32_t)(w * AT_BLK + c * 32), v);
+      const int live = diag ? min(max(quarter + 1 - AT_CPT * part, 0), AT_CPT) : AT_CPT;
+      const uint32_t taddr = lane_addr + (uint32_t)(w * AT_BLK + part * 32 * AT_CPT);
+      for (int c = 0; c < live; ++c) {
+        const int col0 = (part * AT_CPT + c) * 32;
+        tmem_ld_32x32(taddr + 32 * c, v);
         tmem_ld_wait();
-        if (diag) scores_of_chunk<true>(v, s, alpha, p.score_scale, c * 32, r);
-        else scores_of_chunk<false>(v, s, alpha, p.score_scale, c * 32, r);
-        float cmax = m;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) cmax = max3(cmax, s[i].x, s[i].y);
-        // column 0 of every live block is at or before the row, so cmax is finite from the first chunk on
-        const float shift = -cmax * kLog2e;
-        const float2 shift2 = make_float2(shift, shift), log2e2 = make_float2(kLog2e, kLog2e);
-        float2 sum2 = make_float2(0.0f, 0.0f);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float2 a = __ffma2_rn(s[i], log2e2, shift2);
-          sum2 = __fadd2_rn(sum2, make_float2(ex2(a.x), ex2(a.y)));
+        if (c == live - 1) {   // the tile is in registers: hand it back before working on the last chunk
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_empty[w]);
         }
-        l = fmaf(l, ex2(fmaf(m, kLog2e, shift)), sum2.x + sum2.y);   // m = -inf only while l = 0
-        m = cmax;
+        if (diag) accumulate_chunk<true>(v, alpha, p.score_scale, col0, r, m, l);
+        else accumulate_chunk<false>(v, alpha, p.score_scale, col0, r, m, l);
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[w]);
+      if (live == 0) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[w]);
+      }
     }
 
     // ---- merge the two groups' statistics (every softmax thread reaches this barrier) ----
-    stats[(w * 2 + 0) * AT_BLK + r] = m;
-    stats[(w * 2 + 1) * AT_BLK + r] = l;
-    group_barrier_256();
+    stats[(group * 2 + 0) * AT_BLK + r] = m;
+    stats[(group * 2 + 1) * AT_BLK + r] = l;
+    softmax_barrier();
     if (*abort_flag) ok = false;
-    const float m0 = stats[0 * AT_BLK + r], l0 = stats[1 * AT_BLK + r];
-    const float m1 = stats[2 * AT_BLK + r], l1 = stats[3 * AT_BLK + r];   // (-inf, 0) when the group had no block
-    const float mf = fmaxf(m0, m1);
-    const float lf = fmaf(l1, ex2((m1 - mf) * kLog2e), l0 * ex2((m0 - mf) * kLog2e));
-    // p = bf16(e / sum), code = fp8(bf16(p / s_p)): both quotients as products with the correctly
-    // rounded reciprocal.  p >= 0, so no -0 can arise.
+    float mf = -INFINITY;
+#pragma unroll
+    for (int q = 0; q < AT_GROUPS; ++q) mf = fmaxf(mf, stats[(q * 2) * AT_BLK + r]);
+    float lf = 0.0f;   // a group that saw nothing holds (-inf, 0); group 0 always sees column 0
+#pragma unroll
+    for (int q = 0; q < AT_GROUPS; ++q)
+      lf = fmaf(stats[(q * 2 + 1) * AT_BLK + r], ex2((stats[(q * 2) * AT_BLK + r] - mf) * kLog2e), lf);
     const float rl = __frcp_rn(lf), rsp = __frcp_rn(loadp(p.p_scale, 0, p.p_scale_dt));
-    const float2 rl2 = make_float2(rl, rl), rsp2 = make_float2(rsp, rsp);
-    const float2 log2e2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(-mf * kLog2e, -mf * kLog2e);
+    const float shift = -mf * kLog2e;
 
     // ---- pass B: probabilities of this group's blocks as FP8 codes in the MMA operand layout ----
     // Row r of a K-major tile with the 128-byte swizzle: 16-byte chunk a sits at chunk a ^ (r % 8).
     uint8_t* p_row = smem_p + w * AT_TILE + (r >> 3) * 1024 + (r & 7) * 128;
-    for (int j = w; j <= jd && ok; j += 2) {
+    for (int j = w; j <= jd && ok; j += AT_SBUFS) {
+      // the score tile is complete and the MMA that read this buffer's previous probabilities has finished
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&s_full[w], s_uses & 1, abort_flag) &&
                                        mbar_wait(&p_empty[w], (p_uses & 1) ^ 1, abort_flag))) { ok = false; break; }
       ++s_uses;
       ++p_uses;
       tc_fence_after_sync();
       const bool diag = j == jd;
-      const int chunks = diag ? quarter + 1 : 4;
-      for (int c = 0; c < 4; ++c) {
+      const int live = diag ? min(max(quarter + 1 - AT_CPT * part, 0), AT_CPT) : AT_CPT;
+      const uint32_t taddr = lane_addr + (uint32_t)(w * AT_BLK + part * 32 * AT_CPT);
+      for (int c = 0; c < AT_CPT; ++c) {
         uint32_t codes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (c < chunks) {
-          tmem_ld_32x32(lane_addr + (uint32_t)(w * AT_BLK + c * 32), v);
+        if (c < live) {
+          const int col0 = (part * AT_CPT + c) * 32;
+          tmem_ld_32x32(taddr + 32 * c, v);
           tmem_ld_wait();
-          if (diag) scores_of_chunk<true>(v, s, alpha, p.score_scale, c * 32, r);
-          else scores_of_chunk<false>(v, s, alpha, p.score_scale, c * 32, r);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float2 a = __ffma2_rn(s[i], log2e2, shift2);
-            const float2 prob = round2(__fmul2_rn(make_float2(ex2(a.x), ex2(a.y)), rl2));
-            const float2 f = round2(__fmul2_rn(prob, rsp2));
-            const uint32_t code = __nv_cvt_float2_to_fp8x2(f, __NV_SATFINITE, __NV_E4M3);
-            codes[i >> 1] |= code << (16 * (i & 1));
+          if (c == live - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[w]);
           }
+          if (diag) codes_of_chunk<true>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp);
+          else codes_of_chunk<false>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp);
         }
-        *reinterpret_cast<uint4*>(p_row + (((2 * c) ^ (r & 7)) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-        *reinterpret_cast<uint4*>(p_row + (((2 * c + 1) ^ (r & 7)) << 4)) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+        const int chunk16 = 2 * (AT_CPT * part + c);
+        *reinterpret_cast<uint4*>(p_row + ((chunk16 ^ (r & 7)) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+        *reinterpret_cast<uint4*>(p_row + (((chunk16 + 1) ^ (r & 7)) << 4)) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
       }
-      tc_fence_before_sync();
+      if (live == 0) {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[w]);
+      }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[w]);
-        mbar_arrive(&p_full[w]);
-      }
+      if (lane == 0) mbar_arrive(&p_full[w]);
     }
 
-    // ---- output: group w converts accumulator columns [64 w, 64 w + 64) of its rows ----
+    // ---- output: each group converts its share of the accumulator columns of its rows ----
     if (ok && !__all_sync(0xFFFFFFFFu, mbar_wait(o_full, 0, abort_flag))) ok = false;
     if (ok) {
       tc_fence_after_sync();
@@ -355,8 +399,9 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const int head = kvh * p.groups + g;
       Divisor dv;
       if (p.out8 != nullptr) dv = make_divisor(p.ctx_scale, p.ctx_scale_dt);
-      for (int c = 0; c < 2; ++c) {
-        const int col0 = w * 64 + c * 32;
+      for (int c = 0; c < 4 / AT_GROUPS; ++c) {
+        const int col0 = (group * (4 / AT_GROUPS) + c) * 32;
+        uint32_t v[32];
         tmem_ld_32x32(lane_addr + AT_O_COL + (uint32_t)col0, v);
         tmem_ld_wait();
         uint32_t words[16];   // ctx = bf16(acc * alpha_pv), two per word

@@ -137,10 +137,12 @@ class Fp8DecoderLayer:
     """FP8 per-tensor decoder layer on the CUDA kernels (prefill, batch 1)."""
 
     def __init__(self, params, scales, shape: LlamaShape, merge_qkv=True, merge_gate_up=True, fuse_residual=True,
-                 fuse_swiglu=True):
+                 fuse_swiglu=True, fuse_attention=True):
         self.shape = shape
         self.merge_qkv, self.merge_gate_up, self.fuse_residual = merge_qkv, merge_gate_up, fuse_residual
         self.fuse_swiglu = fuse_swiglu
+        # one kernel for Q K^T, softmax, P V and the cast of the context (head_dim 128)
+        self.fuse_attention = fuse_attention and shape.head_dim == 128
         self.scales = scales
         self.ln1, self.ln2 = params["ln1"], params["ln2"]
         # weights are cast once, as convert_pt2e bakes them
@@ -164,8 +166,11 @@ class Fp8DecoderLayer:
         self._rope = None
         self._mask = None
 
-    #: kernels of this package launched per forward (6 fused casts + softmax + 6 GEMMs)
-    LAUNCHES = 6 + 1 + 6
+    @property
+    def LAUNCHES(self):
+        """Kernels of this package launched per forward: 5 fused casts, 4 GEMMs and the attention kernel, or
+        6 fused casts, the softmax and 6 GEMMs when the attention runs as separate kernels."""
+        return 5 + 4 + 1 if self.fuse_attention else 6 + 1 + 6
 
     def _tables(self, T, device):
         if self._rope is None or self._rope[0].shape[0] != T:
@@ -192,6 +197,10 @@ class Fp8DecoderLayer:
         q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(sh.kv_heads, sh.groups * T, sh.head_dim)
         k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                     # [kv, T, d]
         vt8 = FP8.transpose_quantize_fp8(v, s["v"])                         # [kv, d, T]
+        if self.fuse_attention and T % 128 == 0:
+            ctx8 = FP8.attention_fp8(q8, k8, vt8, self.alpha_qk, 1.0 / math.sqrt(sh.head_dim), s["p"], self.alpha_pv,
+                                     s["ctx"])                               # [T, heads*d]
+            return self._after_attention(x, ctx8)
         # masked scores are neither computed nor read; masked probabilities are zero codes
         scores = FP8.fp8_gemm(q8, k8, self.alpha_qk, causal=("scores", T))  # [kv, groups*T, T]
         # scale, causal mask, softmax and the FP8 cast of the probabilities in one pass
@@ -199,6 +208,11 @@ class Fp8DecoderLayer:
         ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv, causal=("probabilities", T))   # [kv, groups*T, d]
         # the cast of the context undoes the head-major layout: [kv*groups, T, d] -> [T, heads*d]
         ctx8 = FP8.transpose_heads_quantize_fp8(ctx.view(sh.heads, T, sh.head_dim), s["ctx"])
+        return self._after_attention(x, ctx8)
+
+    def _after_attention(self, x, ctx8):
+        """Output projection, residual, and the MLP block."""
+        sh, s = self.shape, self.scales
         if self.fuse_residual:
             x1 = FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"], residual=x)   # x + o_proj(ctx)
         else:
