@@ -280,7 +280,9 @@ class C1:
 class C2:
     name = "c2"
     description = ("c2: FP8 E4M3 per-tensor quantized Llama-3.1-8B-shaped decoder layer (hidden 4096, 32q/8kv heads "
-                   "x128, SwiGLU 14336), prefill 1x2048 tokens per GPU, 7 linears + QK^T + PV as FP8 tensor-core GEMMs")
+                   "x128, SwiGLU 14336), prefill 1x2048 tokens per GPU, 7 linears as FP8 tensor-core GEMMs, causal "
+                   "attention (QK^T, softmax, PV) as one fused FP8 tensor-core kernel")
+    fuse_attention = True
     tokens = 2048
     n_sets = 4
     dtype = "fp8_e4m3 (fp32 accumulate), bf16 elsewhere"
@@ -296,7 +298,7 @@ class C2:
         params = W.make_layer_params(7 + rank, self.shape, dev)
         self.x = [W.make_hidden_states(100 * rank + i, self.tokens, self.shape, dev) for i in range(self.n_sets)]
         scales = W.calibrate_fp8_scales(self.x[0], params, self.shape)
-        self.layer = W.Fp8DecoderLayer(params, scales, self.shape)
+        self.layer = W.Fp8DecoderLayer(params, scales, self.shape, fuse_attention=self.fuse_attention)
         del params
         self.launches_per_step = self.layer.LAUNCHES
         self.h2d_bytes = self.tokens * self.shape.hidden * 2
@@ -351,6 +353,15 @@ class C2:
 # ---------------------------------------------------------------------------
 # workload q1: the MX quantizer alone on an activation larger than L2 (HBM roofline)
 # ---------------------------------------------------------------------------
+
+class C2Separate(C2):
+    """The same layer with the attention run as separate kernels (QK^T GEMM, softmax + cast, PV GEMM, cast)."""
+    name = "c2s"
+    description = C2.description.replace("as one fused FP8 tensor-core kernel",
+                                         "as separate kernels: FP8 GEMM, softmax + cast, FP8 GEMM, cast")
+    fuse_attention = False
+
+
 class Q1:
     name = "q1"
     description = ("q1: quantize_mx (int8, bs=16, power-of-two scales) of a [16384,4096] bfloat16 activation per GPU: "
@@ -498,7 +509,7 @@ class C4:
         return OG.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=16, alpha=t * tw)
 
 
-WORKLOADS = {"c1": C1, "c2": C2, "c4": C4, "q1": Q1}
+WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "q1": Q1}
 
 
 def time_cpu_baseline(workload, reps):

@@ -26,13 +26,21 @@ rmsnorm_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w
   const int64_t row = blockIdx.x;
   const int vecs = cols >> 3;
   const Divisor d = make_divisor(scale, scale_dt);
-  uint4 raw[VPT];
-  float ss = 0.0f;
+  // the row's vectors and the weights they meet are all requested before the first is used
+  uint4 raw[VPT], wv[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + blockDim.x * i;
     raw[i] = make_uint4(0, 0, 0, 0);
-    if (v < vecs) raw[i] = __ldg(x + row * vecs + v);
+    wv[i] = make_uint4(0, 0, 0, 0);
+    if (v < vecs) {
+      raw[i] = __ldg(x + row * vecs + v);
+      wv[i] = __ldg(weight + v);
+    }
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
     const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -51,9 +59,8 @@ rmsnorm_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ w
   for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + blockDim.x * i;
     if (v >= vecs) continue;
-    const uint4 wv = __ldg(weight + v);
     const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-    const uint32_t g[4] = {wv.x, wv.y, wv.z, wv.w};
+    const uint32_t g[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
     uint32_t o[2] = {0, 0};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -173,17 +180,39 @@ transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
   const int t0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
   if (threadIdx.x == 0) block_max = 0;
   int local_max = 0;
-  for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
-    const int tt = i >> 6, jj = i & 63;
-    uint32_t q = 0;
-    if (t0 + tt < T && j0 + jj < d) {
-      const int64_t at = ((int64_t)(t0 + tt) * heads + h) * d + j0 + jj;          // dense position
-      const uint16_t raw = reinterpret_cast<const uint16_t*>(x)[(int64_t)(t0 + tt) * ldx + (int64_t)h * d + j0 + jj];
-      local_max = max(local_max, (int)(raw & 0x7FFFu));
-      q = fp8_pair<E4M3>(quot(__uint_as_float((uint32_t)raw << 16), dv), 0.0f) & 0xFFu;
-      if (codes != nullptr) codes[at] = (uint8_t)q;
+  const uint16_t* xs = reinterpret_cast<const uint16_t*>(x);
+  if ((d & 7) == 0 && (ldx & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // eight elements of a token per thread: one 16-byte load, eight codes
+    for (int i = threadIdx.x; i < 64 * 8; i += blockDim.x) {
+      const int tt = i >> 3, jv = (i & 7) << 3;
+      if (t0 + tt >= T || j0 + jv >= d) continue;   // d % 8 == 0: a vector is inside or outside as a whole
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xs + (int64_t)(t0 + tt) * ldx + (int64_t)h * d + j0 + jv));
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t packed[2] = {0, 0};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        local_max = max(local_max, max((int)(w[e] & 0x7FFFu), (int)((w[e] >> 16) & 0x7FFFu)));
+        const uint32_t pair = fp8_pair<E4M3>(quot(lo_of(w[e]), dv), quot(hi_of(w[e]), dv));
+        tile[jv + 2 * e][tt] = (uint8_t)(pair & 0xFFu);
+        tile[jv + 2 * e + 1][tt] = (uint8_t)(pair >> 8);
+        packed[e >> 1] |= pair << (16 * (e & 1));
+      }
+      if (codes != nullptr)
+        *reinterpret_cast<uint2*>(codes + ((int64_t)(t0 + tt) * heads + h) * d + j0 + jv) = make_uint2(packed[0], packed[1]);
     }
-    tile[jj][tt] = (uint8_t)q;
+  } else {
+    for (int i = threadIdx.x; i < 64 * 64; i += blockDim.x) {
+      const int tt = i >> 6, jj = i & 63;
+      uint32_t q = 0;
+      if (t0 + tt < T && j0 + jj < d) {
+        const int64_t at = ((int64_t)(t0 + tt) * heads + h) * d + j0 + jj;          // dense position
+        const uint16_t raw = xs[(int64_t)(t0 + tt) * ldx + (int64_t)h * d + j0 + jj];
+        local_max = max(local_max, (int)(raw & 0x7FFFu));
+        q = fp8_pair<E4M3>(quot(__uint_as_float((uint32_t)raw << 16), dv), 0.0f) & 0xFFu;
+        if (codes != nullptr) codes[at] = (uint8_t)q;
+      }
+      tile[jj][tt] = (uint8_t)q;
+    }
   }
   __syncthreads();
   if (amax_bits != nullptr) {
@@ -230,7 +259,9 @@ extern "C" int vq_rmsnorm_quantize_fp8(const void* x, const void* weight, void* 
   VQ_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
              (reinterpret_cast<uintptr_t>(out) & 7) == 0, "vq_rmsnorm_quantize_fp8: misaligned buffers");
   const int vecs = (int)(cols / 8);
-  int threads = ((vecs + 31) / 32) * 32;
+  // four vectors per thread where the row allows: small CTAs, so that a few thousand rows are
+  // resident at once instead of queueing behind one another
+  int threads = ((((vecs + 3) / 4) + 31) / 32) * 32;
   if (threads > 256) threads = 256;
   const int vpt = (vecs + threads - 1) / threads;   // <= 4 for cols <= 8192
   const unsigned grid = (unsigned)rows;
