@@ -74,3 +74,24 @@ def test_attention_is_deterministic_and_rejects_other_shapes():
     assert torch.equal(one, two)
     with pytest.raises(Exception):
         vb.fp8.attention_fp8(q[:, :, :64].contiguous(), k[:, :, :64].contiguous(), vt[:, :64].contiguous(), a, 0.088, s, a)
+
+
+def test_attention_matches_a_torch_restatement():
+    """Every step of the operator sequence written with torch ops on the dequantized codes."""
+    vb = _vb()
+    T, kv, groups, d = 256, 2, 2, 128
+    q, k, vt = _operands(T, kv, groups, 11)
+    alpha_qk, alpha_pv, sp, scale = 0.37, 0.9 / 448.0, 1.0 / 448.0, 1.0 / math.sqrt(d)
+    f8 = lambda t: t.view(torch.float8_e4m3fn).float()
+    scores = (torch.matmul(f8(q), f8(k).transpose(1, 2)) * alpha_qk).bfloat16()            # [kv, groups*T, T]
+    s = (scores.float() * scale).bfloat16()
+    pos = torch.arange(groups * T, device="cuda") % T
+    s = s.float().masked_fill(torch.arange(T, device="cuda")[None, :] > pos[:, None], float("-inf"))
+    p = torch.softmax(s, -1).bfloat16()
+    p8 = (p.float() / torch.tensor(sp, dtype=torch.bfloat16).float()).bfloat16().to(torch.float8_e4m3fn)
+    want = (torch.matmul(p8.float(), f8(vt).transpose(1, 2)) * alpha_pv).bfloat16().float()
+    dev = lambda v, dt: torch.tensor(v, dtype=dt).cuda()
+    got = vb.fp8.attention_fp8(q, k, vt, dev(alpha_qk, torch.float32), scale, dev(sp, torch.bfloat16),
+                               dev(alpha_pv, torch.float32)).float()
+    assert vb.fp8.attention_status() == 0
+    assert float((got - want).abs().max()) <= 1e-2 * float(want.abs().max())
