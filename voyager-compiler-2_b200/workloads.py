@@ -165,6 +165,7 @@ class Fp8DecoderLayer:
         self.alpha_swiglu = FP8.interleave_gate_up(self.alpha_gate_up[:inter], self.alpha_gate_up[inter:])
         self._rope = None
         self._mask = None
+        self._side = None
 
     @property
     def LAUNCHES(self):
@@ -194,9 +195,20 @@ class Fp8DecoderLayer:
         k = k.unflatten(1, (sh.kv_heads, sh.head_dim))
         v = v.unflatten(1, (sh.kv_heads, sh.head_dim))
         # query heads of one KV group are stacked along the rows: [kv, groups*T, d]
+        # the small K and V casts run beside the Q cast on a second stream (a fork and join that a
+        # CUDA graph capture records as parallel branches)
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x.device)
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                 # [kv, T, d]
+            vt8 = FP8.transpose_quantize_fp8(v, s["v"])                     # [kv, d, T]
         q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(sh.kv_heads, sh.groups * T, sh.head_dim)
-        k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                     # [kv, T, d]
-        vt8 = FP8.transpose_quantize_fp8(v, s["v"])                         # [kv, d, T]
+        main.wait_stream(self._side)
+        for t in (k8, vt8):
+            t.record_stream(main)
+        k.record_stream(self._side)
         if self.fuse_attention and T % 128 == 0:
             ctx8 = FP8.attention_fp8(q8, k8, vt8, self.alpha_qk, 1.0 / math.sqrt(sh.head_dim), s["p"], self.alpha_pv,
                                      s["ctx"])                               # [T, heads*d]
