@@ -345,6 +345,21 @@ int vq_attention_fp8(const void* q8, const void* k8, const void* vt8, void* out8
                      void* stream);
 int vq_attention_status(int reset);
 
+/* RMSNorm's backward of a training step: the input gradient (plus the residual stream's) and
+ * the weight gradient from one read of the rows -- the operator
+ * voyager_gpu::rmsnorm_backward(Tensor[] gradients, Tensor x, Tensor rsqrt, Tensor weight,
+ * Tensor? residual) -> (Tensor, Tensor) of backend/gpu/rmsnorm.py:133-182, whose Triton kernels
+ * (:56-135) this replaces with the same rounding steps: dy = the gradients summed (bfloat16 after
+ * each addition), dw = sum over rows of bf16(dy * bf16(x * r)), g = bf16(dy * w),
+ * dx = bf16(g * r + (sum_k g x * -0.5 * r^3 / cols) * 2 x) (+ residual).  All row tensors are
+ * contiguous bfloat16 [rows, cols]; rsqrt_rows float32 [rows]; weight and dw bfloat16 [cols];
+ * dy1, dy2 and residual may be NULL (gradients = 1..3).  partial_dw is scratch of
+ * vq_rmsnorm_backward_programs(rows) * cols floats.  cols: a multiple of 8, at most 8192. */
+int64_t vq_rmsnorm_backward_programs(int64_t rows);
+int vq_rmsnorm_backward(const void* dy0, const void* dy1, const void* dy2, int gradients, const void* x,
+                        const float* rsqrt_rows, const void* weight, const void* residual, void* dx,
+                        float* partial_dw, void* dw, int64_t rows, int64_t cols, void* stream);
+
 /* FP8 casts fused with the bfloat16 operation that feeds them in a per-tensor FP8
  * decoder layer.  The reference's converted graph runs the producer (RMSNorm,
  * rotary embedding, SiLU * up, a transpose) as separate aten nodes and then

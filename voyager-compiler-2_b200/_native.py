@@ -127,6 +127,8 @@ SIGNATURES = {
     "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],
     "vq_attention_fp8": [_P, _P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _F, _P, _I, _P, _I, _P, _I, _P],
     "vq_attention_status": [_I],
+    "vq_rmsnorm_backward_programs": [_I64],
+    "vq_rmsnorm_backward": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _P],
     "vq_rmsnorm_quantize_fp8": [_P, _P, _P, _I64, _I64, _F, _P, _I, _P],
     "vq_silu_mul_quantize_fp8": [_P, _P, _P, _I64, _I64, _I64, _I64, _P, _I, _P],
     "vq_rope_quantize_fp8": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P],
@@ -189,7 +191,7 @@ def lib():
         for name, argtypes in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
-            fn.restype = ctypes.c_int64 if name == "vq_nvfp4_scale_bytes" else ctypes.c_int
+            fn.restype = ctypes.c_int64 if name in ("vq_nvfp4_scale_bytes", "vq_rmsnorm_backward_programs") else ctypes.c_int
         handle.vq_last_error.restype = ctypes.c_char_p
         handle.vq_last_error.argtypes = []
         _lib = handle
