@@ -354,8 +354,8 @@ int vq_attention_status(int reset);
  * dx = bf16(g * r + (sum_k g x * -0.5 * r^3 / cols) * 2 x) (+ residual).  All row tensors are
  * contiguous bfloat16 [rows, cols]; rsqrt_rows float32 [rows]; weight and dw bfloat16 [cols];
  * dy1, dy2 and residual may be NULL (gradients = 1..3).  partial_dw is scratch of
- * vq_rmsnorm_backward_programs(rows) * cols floats.  cols: a multiple of 8, at most 8192. */
-int64_t vq_rmsnorm_backward_programs(int64_t rows);
+ * vq_rmsnorm_backward_programs(rows, cols) * cols floats.  cols: a multiple of 8, at most 8192. */
+int64_t vq_rmsnorm_backward_programs(int64_t rows, int64_t cols);
 int vq_rmsnorm_backward(const void* dy0, const void* dy1, const void* dy2, int gradients, const void* x,
                         const float* rsqrt_rows, const void* weight, const void* residual, void* dx,
                         float* partial_dw, void* dw, int64_t rows, int64_t cols, void* stream);

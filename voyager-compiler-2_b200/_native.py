@@ -127,7 +127,7 @@ SIGNATURES = {
     "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],
     "vq_attention_fp8": [_P, _P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _F, _P, _I, _P, _I, _P, _I, _P],
     "vq_attention_status": [_I],
-    "vq_rmsnorm_backward_programs": [_I64],
+    "vq_rmsnorm_backward_programs": [_I64, _I64],
     "vq_rmsnorm_backward": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _P],
     "vq_rmsnorm_quantize_fp8": [_P, _P, _P, _I64, _I64, _F, _P, _I, _P],
     "vq_silu_mul_quantize_fp8": [_P, _P, _P, _I64, _I64, _I64, _I64, _P, _I, _P],

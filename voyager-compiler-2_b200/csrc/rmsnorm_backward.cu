@@ -152,9 +152,10 @@ rmsnorm_dw_sum_kernel(const float* __restrict__ partial_dw, __nv_bfloat16* __res
 
 using namespace vq;
 
-extern "C" int64_t vq_rmsnorm_backward_programs(int64_t rows) {
-  // about four CTAs per SM, at least one row each
-  const int64_t target = (int64_t)kSmCount * 4;
+extern "C" int64_t vq_rmsnorm_backward_programs(int64_t rows, int64_t cols) {
+  // as many CTAs as are resident at once (registers allow 4, 3 or 1 per SM by row length), at least one row each
+  const int vpt = (int)((cols / 8 + RB_THREADS - 1) / RB_THREADS);
+  const int64_t target = (int64_t)kSmCount * (vpt <= 1 ? 4 : vpt == 2 ? 3 : 1);
   const int64_t per = rows <= target ? 1 : (rows + target - 1) / target;
   return rows <= 0 ? 0 : (rows + per - 1) / per;
 }
@@ -178,7 +179,7 @@ extern "C" int vq_rmsnorm_backward(const void* dy0, const void* dy1, const void*
                         reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(residual) |
                         reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(partial_dw);
   VQ_REQUIRE((all & 15) == 0, "vq_rmsnorm_backward: misaligned buffers");
-  const int64_t programs = vq_rmsnorm_backward_programs(rows);
+  const int64_t programs = vq_rmsnorm_backward_programs(rows, cols);
   const int rows_per_cta = (int)((rows + programs - 1) / programs);
   VQ_REQUIRE(programs < (1ll << 31), "vq_rmsnorm_backward: too many rows");
   const int vecs = (int)(cols / 8);

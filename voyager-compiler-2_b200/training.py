@@ -32,7 +32,7 @@ def _rmsnorm_backward_cuda(gradients: List[torch.Tensor], x: torch.Tensor, rsqrt
     rows = x.numel() // max(cols, 1)
     dx = torch.empty_like(x)
     dw = torch.empty(cols, dtype=weight.dtype, device=x.device)
-    programs = N.lib().vq_rmsnorm_backward_programs(rows)
+    programs = N.lib().vq_rmsnorm_backward_programs(rows, cols)
     partial = torch.empty((max(programs, 1), cols), dtype=torch.float32, device=x.device)
     grads = list(gradients) + [None] * (MAX_GRADIENTS - len(gradients))
     N.check(N.lib().vq_rmsnorm_backward(_ptr(grads[0]), _ptr(grads[1]), _ptr(grads[2]), len(gradients), x.data_ptr(),
