@@ -30,3 +30,22 @@ def rmsnorm_backward(gradients, x, rsqrt, weight, residual):
     if residual is not None:
         input_grad = residual + input_grad
     return input_grad, weight_grad
+
+
+def nvfp4_square_values(weight, fp4_table, e4m3_table, block=16, fp4_max=6.0, e4m3_max=448.0):
+    """``(values, block_scales, t)`` of the reference's 16x16-block NVFP4 weight cast before packing
+    (``src/voyager_compiler/backend/gpu/nvfp4.py:1006-1012`` with ``_block_scales``, ``:170-179``):
+    e2m1-valued elements ``[N, K]``, e4m3-valued scales ``[N / 16, K / 16]`` and the global scale.
+    Parity unpinned: the reference's own CPU path needs torchao's packing helpers, which are not
+    installed, so no vectors of it exist; the arithmetic is that of ``quantize_mx``, which is pinned."""
+    from . import quantizers as Q
+
+    t = Q.calculate_global_scale(weight, fp4_max, e4m3_max)
+    n, k = weight.shape
+    blocks = weight.reshape(n // block, block, k // block, block)
+    amax = blocks.abs().amax((1, 3))
+    scale = Q.vmap((amax / fp4_max / t).clamp(max=e4m3_max), e4m3_table)
+    scale = torch.where(scale > 0, scale, torch.ones((), dtype=scale.dtype))
+    element_scale = (scale * t)[:, None, :, None]
+    values = Q.vmap((blocks / element_scale).reshape(n, k), fp4_table)
+    return values, scale, t

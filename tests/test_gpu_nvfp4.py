@@ -129,3 +129,32 @@ def test_quantize_nvfp4_stochastic_uses_the_operator():
                                     OQ.calculate_global_scale(x, 6.0, 448.0))
     assert torch.equal(values.cpu().float(), c_want.float())
     assert torch.equal(block_scales.cpu().float(), s_want.float())
+
+
+def test_quantize_nvfp4_pair_is_the_two_casts():
+    vb = _vb()
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(128, 192, generator=g).bfloat16().cuda()
+    pair = vb.nvfp4.quantize_nvfp4_pair(x)
+    rows, cols = vb.nvfp4.quantize_nvfp4(x, -1), vb.nvfp4.quantize_nvfp4(x.mT, -1)
+    for got, want in zip(pair, (*rows, *cols)):
+        assert torch.equal(got, want)
+    assert pair[0].shape == (128, 96) and pair[3].shape == (192, 64)
+
+
+def test_quantize_nvfp4_square_matches_the_oracle():
+    vb = _vb()
+    from oracle import tables as OT
+    from oracle import training as oracle_training
+    g = torch.Generator().manual_seed(6)
+    w = (torch.randn(128, 256, generator=g) * 0.05).bfloat16()
+    w[3, 7] = 1.5                                                     # an outlier sets the global scale
+    values, scale, t = oracle_training.nvfp4_square_values(w, OT.quantization_map("fp4_e2m1"), OT.quantization_map("fp8_e4m3"))
+    codes, scales, codes_t, scales_t, t_gpu = vb.nvfp4.quantize_nvfp4_square(w.cuda())
+    assert torch.equal(t_gpu.cpu().reshape(()), t.reshape(()))
+    got, got_scale = vb.nvfp4.unpack_nvfp4(codes, scales)
+    assert torch.equal(got.cpu(), values)
+    assert torch.equal(got_scale.cpu(), scale.repeat_interleave(16, 0))
+    got_t, got_scale_t = vb.nvfp4.unpack_nvfp4(codes_t, scales_t)
+    assert torch.equal(got_t.cpu(), values.mT)
+    assert torch.equal(got_scale_t.cpu(), scale.mT.repeat_interleave(16, 0))

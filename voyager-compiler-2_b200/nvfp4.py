@@ -164,6 +164,43 @@ def quantize_nvfp4(input: torch.Tensor, axis: int = -1, seed: Optional[torch.Ten
     return packed.codes.view(*moved.shape[:-1], -1), packed.scales, t
 
 
+def quantize_nvfp4_pair(input: torch.Tensor, seed: Optional[torch.Tensor] = None,
+                        transpose_seed: Optional[torch.Tensor] = None, hadamard: Optional[torch.Tensor] = None):
+    """``quantize_nvfp4`` of a matrix ``[M, K]`` along its last axis and of its transpose along its last
+    axis (with ``hadamard`` and ``transpose_seed``): ``(codes, scales, t, codes_T, scales_T, t_T)``, what
+    a training step needs of one operand for its forward and weight-gradient GEMMs
+    (reference ``backend/gpu/nvfp4.py:953-980``).  Two casts here, each reading the matrix once."""
+    if input.ndim != 2:
+        raise ValueError("quantize_nvfp4_pair takes a matrix")
+    return (*quantize_nvfp4(input, -1, seed), *quantize_nvfp4(input.mT, -1, transpose_seed, hadamard))
+
+
+def quantize_nvfp4_square(weight: torch.Tensor):
+    """A weight ``[N, K]`` quantized to NVFP4 in 16x16 blocks, packed along K for the forward GEMM and,
+    transposed, along N for the input-gradient GEMM: ``(codes, scales, transposed_codes,
+    transposed_scales, t)`` (reference ``backend/gpu/nvfp4.py:983-1017``).  ``quantize_nvfp4``'s
+    arithmetic over square blocks: ``t`` from the weight's amax, a block's scale
+    ``e4m3(amax / 6 / t)`` (1 where that is 0), every element divided by its block's scale times
+    ``t`` and rounded to e2m1.  Both extents must be multiples of 64 here."""
+    from . import ops as O
+    from .formats import get_quantization_map
+
+    if weight.ndim != 2 or weight.dtype != torch.bfloat16:
+        raise NotImplementedError("quantize_nvfp4_square takes a bfloat16 matrix")
+    n, k = weight.shape
+    weight = weight.contiguous()
+    t = O.calculate_global_scale(weight, FP4_MAX, E4M3_MAX)
+    amax = weight.abs().view(n // BLOCK_SIZE, BLOCK_SIZE, k // BLOCK_SIZE, BLOCK_SIZE).amax((1, 3))
+    scale = torch.ops.quantized_ops.vmap((amax / FP4_MAX / t).clamp(max=E4M3_MAX),
+                                         get_quantization_map("fp8_e4m3", weight.device))
+    scale = torch.where(scale > 0, scale, torch.ones((), dtype=scale.dtype, device=scale.device))
+    values = torch.ops.quantized_ops.quantize(weight, scale * t, None, [0, 1], BLOCK_SIZE,
+                                              get_quantization_map("fp4_e2m1", weight.device))
+    rows = pack_nvfp4(values, scale.repeat_interleave(BLOCK_SIZE, 0), check=False)
+    cols = pack_nvfp4(values.mT.contiguous(), scale.mT.repeat_interleave(BLOCK_SIZE, 0).contiguous(), check=False)
+    return rows.codes, rows.scales, cols.codes, cols.scales, t
+
+
 def unpack_nvfp4(codes: torch.Tensor, scales: torch.Tensor):
     """``(values, block_scales)`` in bfloat16, ``[..., K]`` and ``[..., K / 16]``: the inverse of
     ``pack_nvfp4`` (reference ``backend/gpu/nvfp4.py:1073-1091``)."""
