@@ -28,7 +28,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // VPT 16-byte vectors (8 columns) per thread; cols <= 8 * VPT * RB_THREADS.
 template <int VPT, int GRADIENTS, bool RESIDUAL>
-__global__ void __launch_bounds__(RB_THREADS)
+__global__ void __launch_bounds__(RB_THREADS, VPT <= 2 ? 4 : 2)
 rmsnorm_backward_kernel(const uint4* __restrict__ dy0, const uint4* __restrict__ dy1, const uint4* __restrict__ dy2,
                         const uint4* __restrict__ x, const float* __restrict__ rsqrt_rows,
                         const uint4* __restrict__ weight, const uint4* __restrict__ residual, uint4* __restrict__ dx,
@@ -36,50 +36,59 @@ rmsnorm_backward_kernel(const uint4* __restrict__ dy0, const uint4* __restrict__
   __shared__ float warp_sums[2][RB_THREADS / 32];
   const int vecs = cols >> 3;
   const float inv_cols = __fdiv_rn(1.0f, (float)cols);
-  float w[VPT][8], dw[VPT][8];
+  // Weights, the summed gradient and x stay packed (two bfloat16 per register) between the row's two
+  // phases; only the weight-gradient sums are float32.  Fewer registers, more CTAs per SM.
+  uint4 w[VPT];
+  float dw[VPT][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = threadIdx.x + RB_THREADS * i;
-    uint4 wv = make_uint4(0, 0, 0, 0);
-    if (v < vecs) wv = __ldg(weight + v);
-    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    w[i] = make_uint4(0, 0, 0, 0);
+    if (v < vecs) w[i] = __ldg(weight + v);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      w[i][2 * j] = lo16(ww[j]);
-      w[i][2 * j + 1] = hi16(ww[j]);
-      dw[i][2 * j] = dw[i][2 * j + 1] = 0.0f;
-    }
+    for (int j = 0; j < 8; ++j) dw[i][j] = 0.0f;
   }
   const int64_t first = (int64_t)blockIdx.x * rows_per_cta;
   const int64_t last = min(first + rows_per_cta, rows);
   for (int64_t m = first; m < last; ++m) {
     const float r = rsqrt_rows[m];
-    float g[VPT][8], xf[VPT][8];
+    uint4 dyp[VPT], xp[VPT];   // dy (the gradients summed) and x of this thread's vectors
     float dot = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = threadIdx.x + RB_THREADS * i;
+      dyp[i] = xp[i] = make_uint4(0, 0, 0, 0);
       if (v < vecs) {
         const int64_t at = m * vecs + v;
-        const uint4 a = __ldg(dy0 + at), xv = __ldg(x + at);
+        const uint4 a = __ldg(dy0 + at);
+        xp[i] = __ldg(x + at);
         uint4 b = make_uint4(0, 0, 0, 0), c = make_uint4(0, 0, 0, 0);
         if (GRADIENTS > 1) b = __ldg(dy1 + at);
         if (GRADIENTS > 2) c = __ldg(dy2 + at);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w}, cw[4] = {c.x, c.y, c.z, c.w};
-        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+        const uint32_t xw[4] = {xp[i].x, xp[i].y, xp[i].z, xp[i].w};
+        const uint32_t ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+        uint32_t sum[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int q = j >> 1;
-          float dy = (j & 1) ? hi16(aw[q]) : lo16(aw[q]);
-          if (GRADIENTS > 1) dy = bf16_round(__fadd_rn(dy, (j & 1) ? hi16(bw[q]) : lo16(bw[q])));
-          if (GRADIENTS > 2) dy = bf16_round(__fadd_rn(dy, (j & 1) ? hi16(cw[q]) : lo16(cw[q])));
-          const float xe = (j & 1) ? hi16(xw[q]) : lo16(xw[q]);
-          dw[i][j] = __fadd_rn(dw[i][j], bf16_round(__fmul_rn(dy, bf16_round(__fmul_rn(xe, r)))));
-          const float ge = bf16_round(__fmul_rn(dy, w[i][j]));
-          g[i][j] = ge;
-          xf[i][j] = xe;
-          dot = __fadd_rn(dot, __fmul_rn(ge, xe));
+        for (int q = 0; q < 4; ++q) {
+          float dy[2] = {lo16(aw[q]), hi16(aw[q])};
+          if (GRADIENTS > 1) {
+            dy[0] = bf16_round(__fadd_rn(dy[0], lo16(bw[q])));
+            dy[1] = bf16_round(__fadd_rn(dy[1], hi16(bw[q])));
+          }
+          if (GRADIENTS > 2) {
+            dy[0] = bf16_round(__fadd_rn(dy[0], lo16(cw[q])));
+            dy[1] = bf16_round(__fadd_rn(dy[1], hi16(cw[q])));
+          }
+          sum[q] = pack_bf16(dy[0], dy[1]);   // exact: both are bfloat16 values
+          const float xe[2] = {lo16(xw[q]), hi16(xw[q])}, we[2] = {lo16(ww[q]), hi16(ww[q])};
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            dw[i][2 * q + h] = __fadd_rn(dw[i][2 * q + h], bf16_round(__fmul_rn(dy[h], bf16_round(__fmul_rn(xe[h], r)))));
+            dot = __fadd_rn(dot, __fmul_rn(bf16_round(__fmul_rn(dy[h], we[h])), xe[h]));
+          }
         }
+        dyp[i] = make_uint4(sum[0], sum[1], sum[2], sum[3]);
       }
     }
     // the row's dot product: warps, then the CTA (the two buffers alternate so one barrier per row is enough)
@@ -100,15 +109,20 @@ rmsnorm_backward_kernel(const uint4* __restrict__ dy0, const uint4* __restrict__
         uint4 rv = make_uint4(0, 0, 0, 0);
         if (RESIDUAL) rv = __ldg(residual + at);
         const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+        const uint32_t dw4[4] = {dyp[i].x, dyp[i].y, dyp[i].z, dyp[i].w};
+        const uint32_t xw[4] = {xp[i].x, xp[i].y, xp[i].z, xp[i].w};
+        const uint32_t ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
         uint32_t o[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
+          const float dy[2] = {lo16(dw4[q]), hi16(dw4[q])}, xe[2] = {lo16(xw[q]), hi16(xw[q])};
+          const float we[2] = {lo16(ww[q]), hi16(ww[q])}, re[2] = {lo16(rw[q]), hi16(rw[q])};
           float e[2];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const int j = 2 * q + h;
-            float grad = bf16_round(__fadd_rn(__fmul_rn(g[i][j], r), __fmul_rn(scale, __fmul_rn(xf[i][j], 2.0f))));
-            if (RESIDUAL) grad = __fadd_rn(grad, h ? hi16(rw[q]) : lo16(rw[q]));
+            const float g = bf16_round(__fmul_rn(dy[h], we[h]));
+            float grad = bf16_round(__fadd_rn(__fmul_rn(g, r), __fmul_rn(scale, __fmul_rn(xe[h], 2.0f))));
+            if (RESIDUAL) grad = __fadd_rn(grad, re[h]);
             e[h] = grad;
           }
           o[q] = pack_bf16(e[0], e[1]);
@@ -153,9 +167,10 @@ rmsnorm_dw_sum_kernel(const float* __restrict__ partial_dw, __nv_bfloat16* __res
 using namespace vq;
 
 extern "C" int64_t vq_rmsnorm_backward_programs(int64_t rows, int64_t cols) {
-  // as many CTAs as are resident at once (registers allow 4, 3 or 1 per SM by row length), at least one row each
+  // as many CTAs as are resident at once (the kernels are compiled for 4 per SM, 2 for rows of more than
+  // 4096 columns), at least one row each
   const int vpt = (int)((cols / 8 + RB_THREADS - 1) / RB_THREADS);
-  const int64_t target = (int64_t)kSmCount * (vpt <= 1 ? 4 : vpt == 2 ? 3 : 1);
+  const int64_t target = (int64_t)kSmCount * (vpt <= 2 ? 4 : 2);
   const int64_t per = rows <= target ? 1 : (rows + target - 1) / target;
   return rows <= 0 ? 0 : (rows + per - 1) / per;
 }
