@@ -84,6 +84,27 @@ def test_fp8_decoder_layer_matches_converted_graph():
     assert rel_err(got, ref) <= 0.15
 
 
+def test_fp8_decoder_layer_with_fused_attention_matches_converted_graph():
+    """head_dim 128 and T a multiple of 128: the attention runs in the fused kernel."""
+    vb = _vb()
+    W = vb.workloads
+    shape = W.LlamaShape(hidden=512, heads=4, kv_heads=2, head_dim=128, intermediate=1024, vocab=1024)
+    T = 256
+    params = W.make_layer_params(0, shape)
+    x = W.make_hidden_states(1, T, shape)
+    scales = W.calibrate_fp8_scales(x, params, shape)
+    want = OL.fp8_decoder_layer(x, params, scales, shape, W.rope_tables(T, shape, "cpu"), W.causal_mask(T, "cpu"))
+    layer = W.Fp8DecoderLayer({k: v.cuda() for k, v in params.items()}, {k: v.cuda() for k, v in scales.items()}, shape)
+    assert layer.fuse_attention and layer.LAUNCHES == 10
+    got = layer(x.cuda()).cpu()
+    vb.ops.gemm_status()
+    assert vb.fp8.attention_status() == 0
+    assert rel_err(got, want) <= 2e-2, rel_err(got, want)
+    layer.fuse_attention = False
+    separate = layer(x.cuda()).cpu()
+    assert rel_err(got, separate) <= 1e-2
+
+
 @pytest.mark.parametrize("rows,cols,period", [(8, 64, 0), (96, 256, 32), (64, 2048, 64), (10, 520, 0), (12, 4096, 0)])
 def test_softmax_quantize_fused_matches_unfused(rows, cols, period):
     """The fused pass against the unfused bf16 op sequence on the CPU oracle."""
