@@ -1,15 +1,15 @@
 """Benchmark of the quantized hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c2s|c1|c4|q1]
 
 One "step" is one pass of the hot path over one batch of synthetic input.
 
-Workload ``c2`` (default; BASELINE.json configs[1]): one FP8 E4M3 per-tensor
+Workload ``c2`` (default; the configuration the headline metric is quoted on): one FP8 E4M3 per-tensor
 quantized Llama-3.1-8B-shaped decoder layer, prefill of 1 x 2048 tokens,
-random-init weights ~N(0,0.02); all seven linears and both attention matmuls
-run as FP8 casts + FP8 tensor-core GEMMs, bf16 elsewhere.
+random-init weights ~N(0,0.02); all seven linears run as FP8 casts + FP8 tensor-core
+GEMMs, the causal attention as one fused FP8 kernel (``c2s``: as separate kernels), bf16 elsewhere.
 
-Workload ``c1`` (BASELINE.json configs[0]): X [2048,4096] bf16 ~N(0,1) with
+Workload ``c1`` (the reference's own CPU-runnable case): X [2048,4096] bf16 ~N(0,1) with
 0.1 % of entries x20, W [4096,4096] ~N(0,0.02); both are quantized to int8
 microscaling (block 16 along K, power-of-two scales) and multiplied to
 Y [2048,4096] bf16 -- ``quantize_mx`` x2 + ``linear_mx``.

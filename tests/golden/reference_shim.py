@@ -32,7 +32,7 @@ import types
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("VOYAGER_REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("VOYAGER_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 _SRC = os.path.join(REFERENCE_ROOT, "src")
 
 
