@@ -1,6 +1,6 @@
 """Benchmark of the quantized hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c2s|c1|c4|q1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c2s|c1|c4|q1|r1]
 
 One "step" is one pass of the hot path over one batch of synthetic input.
 
@@ -42,7 +42,7 @@ sys.path.insert(0, ROOT)
 # ncu-measured DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, bytes per
 # launch) of each workload's dominant kernel, from the captures summarised under
 # profiles/; None until one has been taken.
-NCU_TRAFFIC_BYTES = {"c1": 53.5e6, "c2": 145.2e6}
+NCU_TRAFFIC_BYTES = {"c1": 53.5e6, "c2": 145.2e6, "r1": 390.3e6}
 
 
 def measured_peaks():
@@ -423,6 +423,72 @@ class Q1:
 
 
 # ---------------------------------------------------------------------------
+# workload r1: RMSNorm's backward of a training step (three gradients summed, residual added)
+# ---------------------------------------------------------------------------
+class R1:
+    name = "r1"
+    description = ("r1: voyager_gpu::rmsnorm_backward of [8192,4096] bfloat16 rows per GPU, three gradients summed "
+                   "into dy and the input gradient added to the residual stream's")
+    tokens = 8192
+    K = 4096
+    launches_per_step = 2
+    n_sets = 2
+    dtype = "bf16 (float32 sums)"
+    cpu_tokens = 1024
+    cpu_sample = "rmsnorm_backward calls on 1024 of the step's 8192 rows"
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        g = torch.Generator().manual_seed(91 + rank)
+        make = lambda scale: (torch.randn(self.tokens, self.K, generator=g) * scale).bfloat16().to(dev)
+        self.x = [make(1.5) for _ in range(self.n_sets)]
+        self.grads = [[make(0.05) for _ in range(3)] for _ in range(self.n_sets)]
+        self.residual = [make(0.05) for _ in range(self.n_sets)]
+        self.rsqrt = [torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5) for x in self.x]
+        self.weight = (1.0 + 0.2 * torch.randn(self.K, generator=g)).bfloat16().to(dev)
+        self.h2d_bytes = self.tokens * self.K * 2
+        self.d2h_bytes = self.tokens * self.K * 2
+        self._run(0)
+        self.graphs = [capture(lambda i=i: self._run(i)) for i in range(self.n_sets)]
+        # the host supplies the norm's input and takes the input gradient back
+        self.pipeline = HostPipeline(self.x, [x.cpu().pin_memory() for x in self.x], self.graphs)
+
+    def _run(self, i):
+        return self.vb.training.rmsnorm_backward(self.grads[i], self.x[i], self.rsqrt[i], self.weight, self.residual[i])[0]
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def roofline(self, peaks, reps):
+        secs = time_region(self.step, reps, torch.cuda.synchronize) / reps
+        nbytes = self.tokens * self.K * 2 * (3 + 1 + 1 + 1)       # three gradients, x, residual in; dx out
+        achieved = nbytes / secs / 1e9
+        return secs, {"kernel": "rmsnorm_backward_kernel<2, 3, true> + rmsnorm_dw_sum_kernel (8192x4096)",
+                      "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                      "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth",
+                      "traffic": NCU_TRAFFIC_BYTES["r1"]}
+
+    @staticmethod
+    def cpu_setup():
+        g = torch.Generator().manual_seed(91)
+        make = lambda scale: (torch.randn(R1.cpu_tokens, R1.K, generator=g) * scale).bfloat16()
+        x = make(1.5)
+        return ([make(0.05) for _ in range(3)], x, torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5),
+                (1.0 + 0.2 * torch.randn(R1.K, generator=g)).bfloat16(), make(0.05))
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import training as OTR
+
+        return OTR.rmsnorm_backward(*state)
+
+
+# ---------------------------------------------------------------------------
 # workload c4: one NVFP4 linear (fused cast to packed e2m1 + e4m3 block scales, block-scaled GEMM)
 # ---------------------------------------------------------------------------
 class C4:
@@ -509,7 +575,7 @@ class C4:
         return OG.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=16, alpha=t * tw)
 
 
-WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "q1": Q1}
+WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "q1": Q1, "r1": R1}
 
 
 def time_cpu_baseline(workload, reps):
