@@ -1,9 +1,8 @@
 """Generate the golden fixtures from the reference's own CPU code.
 
-Run where the reference checkout is available (``reference_shim.REFERENCE_ROOT``;
-set ``VOYAGER_REFERENCE_ROOT`` to point elsewhere)::
+Run where a checkout of the reference is available, naming it in the environment::
 
-    python tests/golden/make_golden.py
+    VOYAGER_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py
 
 Writes, next to this script:
 

@@ -32,12 +32,13 @@ import types
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("VOYAGER_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# The checkout is named by the environment alone; without the variable the reference is "not available".
+REFERENCE_ROOT = os.environ.get("VOYAGER_REFERENCE_ROOT", "")
 _SRC = os.path.join(REFERENCE_ROOT, "src")
 
 
 def available() -> bool:
-    return os.path.isdir(os.path.join(_SRC, "voyager_compiler", "ops"))
+    return bool(REFERENCE_ROOT) and os.path.isdir(os.path.join(_SRC, "voyager_compiler", "ops"))
 
 
 def _install_shims():
@@ -89,7 +90,8 @@ class Reference:
 
     def __init__(self):
         if not available():
-            raise RuntimeError(f"no reference checkout at {REFERENCE_ROOT}")
+            raise RuntimeError("set VOYAGER_REFERENCE_ROOT to a checkout of the reference (found none at "
+                               f"{REFERENCE_ROOT!r})")
         _install_shims()
         self.ops = importlib.import_module("voyager_compiler.ops")
         self.quantized = importlib.import_module("voyager_compiler.ops.quantized")

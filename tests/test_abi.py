@@ -140,3 +140,32 @@ def test_fake_kernels_give_shapes():
     assert s.shape == (4, 3) and c.shape == (4, 40)
     s, z, c = torch.ops.quantized_ops.quantize_affine(x, t, [-1], 16, 0.0, 3.0)
     assert s.shape == z.shape == (4, 3)
+
+
+def test_voyager_gpu_operator_schemas_are_the_references():
+    """Names and schemas of the ``voyager_gpu`` call targets (reference ``backend/gpu/nvfp4.py:675-679,
+    773-778, 851-854, 1094-1097``, ``fp8.py:311-314``, ``rmsnorm.py:132-136``), and their shape functions."""
+    G = torch.ops.voyager_gpu
+    want = {
+        "cast_nvfp4": "voyager_gpu::cast_nvfp4(Tensor x, Tensor? hadamard, Tensor? seed, int axis) -> (Tensor, Tensor, Tensor)",
+        "cast_nvfp4_pair": "voyager_gpu::cast_nvfp4_pair(Tensor x, Tensor? hadamard, Tensor? seed, Tensor? transpose_seed) "
+                           "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)",
+        "cast_nvfp4_square": "voyager_gpu::cast_nvfp4_square(Tensor x) -> (Tensor, Tensor, Tensor, Tensor, Tensor)",
+        "nvfp4_linear": "voyager_gpu::nvfp4_linear(Tensor input, Tensor input_scale, Tensor weight, Tensor weight_scale, "
+                        "Tensor alpha, Tensor one, Tensor? bias) -> Tensor",
+        "cast_transpose_fp8": "voyager_gpu::cast_transpose_fp8(Tensor x, Tensor scale, ScalarType dtype) -> (Tensor, Tensor, Tensor)",
+        "rmsnorm_backward": "voyager_gpu::rmsnorm_backward(Tensor[] gradients, Tensor x, Tensor rsqrt, Tensor weight, "
+                            "Tensor? residual) -> (Tensor, Tensor)",
+    }
+    for name, schema in want.items():
+        assert str(getattr(G, name).default._schema) == schema
+    x = torch.empty(192, 128, dtype=torch.bfloat16, device="meta")
+    codes, scales, t = G.cast_nvfp4(x, None, None, 1)
+    assert codes.shape == (192, 64) and scales.shape == (256 * 8,) and t.shape == () and t.dtype == torch.bfloat16
+    codes, scales, t = G.cast_nvfp4(x, None, None, 0)
+    assert codes.shape == (128, 96) and scales.shape == (128 * 12,)
+    assert [o.shape for o in G.cast_nvfp4_square(x)][2] == (128, 96)
+    y = G.nvfp4_linear(codes, scales, codes, scales, t, t, None)
+    assert y.shape == (128, 128) and y.dtype == torch.bfloat16
+    c, ct, amax = G.cast_transpose_fp8(x, t, torch.float8_e4m3fn)
+    assert c.shape == (192, 128) and ct.shape == (128, 192) and c.dtype == torch.float8_e4m3fn

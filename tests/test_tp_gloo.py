@@ -53,7 +53,7 @@ def test_lpt_schedule_balances_llama_linears():
     assert P.lpt_schedule(costs, 8) == plan               # deterministic: every rank derives the same table
 
 
-def _gptq_rank(rank, world, port, results):
+def _gptq_rank(rank, world, port, results, weight_dtype=torch.float32):
     import os
 
     import torch.distributed as dist
@@ -68,15 +68,17 @@ def _gptq_rank(rank, world, port, results):
     problems = []
     for out_f, in_f in ((16, 128), (8, 64), (24, 128), (8, 64), (16, 64)):
         x = torch.randn(256, in_f, generator=g)
-        problems.append(dict(weight=torch.randn(out_f, in_f, generator=g) * 0.02, hessian=x.T @ x, tokens=256))
+        problems.append(dict(weight=(torch.randn(out_f, in_f, generator=g) * 0.02).to(weight_dtype), hessian=x.T @ x,
+                             tokens=256))
     calls = []
 
     def solve(p):
         calls.append(tuple(p["weight"].shape))
         fq = type("FQ", (), dict(block_size=32, ch_axis=-1, qmap=OT.quantization_map("int4"),
                                  scale_qmap=OT.quantization_map("fp8_e5m3"), quant_max=7.0))
-        return OG.compensate_weight(p["weight"], p["hessian"].clone(), p["tokens"], fq.qmap, fq.scale_qmap, fq.quant_max,
-                                    fq.block_size, 0.01, False, True, False)
+        # the solve works in float32 whatever the weight's dtype, as the reference's does
+        return OG.compensate_weight(p["weight"].float(), p["hessian"].clone(), p["tokens"], fq.qmap, fq.scale_qmap,
+                                    fq.quant_max, fq.block_size, 0.01, False, True, False)
 
     out = voyager_b200.parallel.gptq_layer_parallel(problems, solve)
     results[rank] = (len(calls), [o.clone() for o in out])
@@ -100,3 +102,24 @@ def test_gptq_layer_parallel_two_ranks():
     want = OG.compensate_weight(w, x.T @ x, 256, OT.quantization_map("int4"), OT.quantization_map("fp8_e5m3"), 7.0, 32,
                                 0.01, False, True, False)
     assert torch.equal(out0[0], want)
+
+
+def test_gptq_layer_parallel_bfloat16_weights():
+    """The solve returns float32 while the model's weights are bfloat16: owner and receivers must still agree on
+    what crosses the wire, and every rank ends with the weights in the model's dtype."""
+    from oracle import gptq as OG
+    from oracle import tables as OT
+
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_gptq_rank, args=(2, 29617, results, torch.bfloat16), nprocs=2, join=True)
+    (n0, out0), (n1, out1) = results[0], results[1]
+    assert n0 + n1 == 5
+    for a, b in zip(out0, out1):
+        assert a.dtype == torch.bfloat16 and torch.equal(a, b)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(256, 128, generator=g)
+    w = (torch.randn(16, 128, generator=g) * 0.02).bfloat16()
+    want = OG.compensate_weight(w.float(), x.T @ x, 256, OT.quantization_map("int4"), OT.quantization_map("fp8_e5m3"),
+                                7.0, 32, 0.01, False, True, False)
+    assert torch.equal(out0[0], want.bfloat16())

@@ -198,6 +198,39 @@ def lib():
     return _lib
 
 
+def _cuda_device_of(values, found):
+    for v in values:
+        if isinstance(v, (list, tuple)):
+            found = _cuda_device_of(v, found)
+        elif hasattr(v, "is_cuda") and v.is_cuda:
+            if found is None:
+                found = v.device
+            elif v.device != found:
+                raise ValueError(f"operands live on different devices: {found} and {v.device}")
+    return found
+
+
+def device_guarded(fn):
+    """Run ``fn`` with the device of its CUDA tensor arguments current, so that kernels launch on
+    that device's current stream whatever device the caller had selected (a model whose layers are
+    placed on several GPUs in one process calls operators with tensors of each of them).  Operands
+    spread over different devices are refused."""
+    import functools
+
+    import torch
+
+    @functools.wraps(fn)
+    def call(*args, **kwargs):
+        device = _cuda_device_of(args, None)
+        device = _cuda_device_of(kwargs.values(), device)
+        if device is None or device.index == torch.cuda.current_device():
+            return fn(*args, **kwargs)
+        with torch.cuda.device(device):
+            return fn(*args, **kwargs)
+
+    return call
+
+
 def check(rc, what=""):
     if rc != 0:
         msg = lib().vq_last_error().decode(errors="replace")

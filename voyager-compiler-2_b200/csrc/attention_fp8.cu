@@ -517,12 +517,11 @@ extern "C" int vq_attention_fp8(const void* q8, const void* k8, const void* vt8,
   p.out8 = static_cast<uint8_t*>(out8);
   p.ld8 = ld8;
   p.out16 = static_cast<__nv_bfloat16*>(out16);
-  static bool configured = false;
-  if (!configured) {
+  static unsigned long long configured = 0;
+  if (first_call_on_device(&configured)) {
     cudaError_t e = cudaFuncSetAttribute(attention_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)AT_SMEM_BYTES);
     if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured = true;
   }
   attention_fp8_kernel<<<(unsigned)items, AT_THREADS, AT_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_q, map_k,
                                                                                                          map_v, p);

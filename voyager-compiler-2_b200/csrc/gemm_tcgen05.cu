@@ -1135,43 +1135,47 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   // CTA pairs (256x256 tiles) when there is more than one 128-row block of output;
-  // VQ_GEMM_PAIR=0 forces the single-CTA kernel.
-  static int pair_mode = -1;        // -1 unknown, 0 off, 1 on
-  static int max_clusters = 0;
+  // VQ_GEMM_PAIR=0 forces the single-CTA kernel.  Function attributes and the cluster occupancy
+  // belong to a device, so they are set up once per device ordinal.
+  static int pair_mode = -1;        // -1 unknown, 0 off, 1 on (process-wide: the environment)
+  static int max_clusters_of[64] = {};
+  static unsigned long long pair_configured = 0;
   if (pair_mode < 0) {
     const char* env = getenv("VQ_GEMM_PAIR");
     pair_mode = (env && env[0] == '0') ? 0 : 1;
-    if (pair_mode) {
-      if (int rc = allow_big_smem(gemm_tn_pair_kernel<VQ_BF16>, gemm_tn_pair_kernel<VQ_F16>,
-                                  gemm_tn_pair_kernel<VQ_F32>, P_SMEM_BYTES))
-        return rc;
-      cudaError_t e;
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(kSmCount, 1, 1);
-      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-      cfg.dynamicSmemBytes = P_SMEM_BYTES;
-      cudaLaunchAttribute attr;
-      attr.id = cudaLaunchAttributeClusterDimension;
-      attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-      int n = 0;
-      e = cudaOccupancyMaxActiveClusters(&n, gemm_tn_pair_kernel<VQ_BF16>, &cfg);
-      if (e != cudaSuccess || n < 1) {
-        (void)cudaGetLastError();
-        pair_mode = 0;
-      } else {
-        max_clusters = n < kSmCount / 2 ? n : kSmCount / 2;
-      }
+  }
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
+  if (pair_mode == 1 && first_call_on_device(&pair_configured)) {
+    if (int rc = allow_big_smem(gemm_tn_pair_kernel<VQ_BF16>, gemm_tn_pair_kernel<VQ_F16>,
+                                gemm_tn_pair_kernel<VQ_F32>, P_SMEM_BYTES))
+      return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kSmCount, 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tn_pair_kernel<VQ_BF16>, &cfg);
+    if (e != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      max_clusters_of[device] = 0;   // this device runs the single-CTA kernel
+    } else {
+      max_clusters_of[device] = n < kSmCount / 2 ? n : kSmCount / 2;
     }
   }
+  const int max_clusters = pair_mode == 1 ? max_clusters_of[device] : 0;
   CUtensorMap map_c;
   if (p.gate_scale != nullptr) {
     memset(&map_c, 0, sizeof(map_c));   // the gated epilogue stores from registers
   } else if (int e = make_output_map(&map_c, &p.tma_store, C, out_dtype, M, N, ldc, batch, strideC)) {
     return e;
   }
-  if (pair_mode == 1 && M > BM) {
+  if (max_clusters > 0 && M > BM) {
     CUtensorMap map_a, map_b;
     if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
     p.bn = N <= BN / 2 ? BN / 2 : BN;   // a narrow output takes half-width tiles instead of multiplying zero padding
@@ -1187,11 +1191,10 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
   if (int e = make_operand_map(&map_a, A, kind, eb, M, K, lda, batch, strideA, BM)) return e;
   if (int e = make_operand_map(&map_b, B, kind, eb, N, K, ldb, batch, strideB, BN)) return e;
   p.idesc = sm100::make_idesc(BM, BN, fmt, fmt, 0, 0);
-  static bool configured = false;
-  if (!configured) {
+  static unsigned long long configured = 0;
+  if (first_call_on_device(&configured)) {
     if (int rc = allow_big_smem(gemm_tn_kernel<VQ_BF16>, gemm_tn_kernel<VQ_F16>, gemm_tn_kernel<VQ_F32>, SMEM_BYTES))
       return rc;
-    configured = true;
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
@@ -1232,12 +1235,11 @@ int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb
   sf.sfb = static_cast<const uint8_t*>(sfb);
   sf.sfa_batch_stride = ((M + 127) / 128) * (K / 64) * 512;
   sf.sfb_batch_stride = ((N + 127) / 128) * (K / 64) * 512;
-  static bool configured = false;
-  if (!configured) {
+  static unsigned long long configured = 0;
+  if (first_call_on_device(&configured)) {
     if (int rc = allow_big_smem(gemm_nvfp4_kernel<VQ_BF16>, gemm_nvfp4_kernel<VQ_F16>, gemm_nvfp4_kernel<VQ_F32>,
                                 Q_SMEM_BYTES))
       return rc;
-    configured = true;
   }
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + Q_BN - 1) / Q_BN) * batch;
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);

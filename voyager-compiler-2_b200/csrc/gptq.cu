@@ -209,11 +209,9 @@ extern "C" int vq_gptq_block(float* work, float* out, float* deltas, const float
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = (int)((rows + kRowsPerCta - 1) / kRowsPerCta);
   const size_t smem = (size_t)n * n * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
+  static unsigned long long configured = 0;
+  if (first_call_on_device(&configured))
     cudaFuncSetAttribute(gptq_block_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 128 * 4);
-    configured = true;
-  }
   if (n <= 32) gptq_block_kernel<32><<<grid, kRowsPerCta, smem, st>>>(p);
   else if (n <= 64) gptq_block_kernel<64><<<grid, kRowsPerCta, smem, st>>>(p);
   else gptq_block_kernel<128><<<grid, kRowsPerCta, smem, st>>>(p);
@@ -275,10 +273,10 @@ extern "C" int vq_gptq_block_step_static(float* work, float* out, const float* U
                                          float quant_min, float quant_max, int shrink, const VqRound* scale_round,
                                          const VqRound* round, void* stream) {
   VQ_REQUIRE(rows >= 0 && n > 0, "vq_gptq_block_step_static: bad block");
-  VQ_REQUIRE(rows * n <= kStaticDeltaFloats,
-             "vq_gptq_block_step_static: rows x block columns = %lld exceeds the built-in buffer of %lld values "
+  VQ_REQUIRE(rows <= kStaticDeltaFloats / n,   // not rows * n: an absurd row count must not wrap around
+             "vq_gptq_block_step_static: %lld rows x %lld block columns exceeds the built-in buffer of %lld values "
              "(8 MiB); split the rows or use vq_gptq_block / vq_gptq_update with your own buffer",
-             (long long)(rows * n), (long long)kStaticDeltaFloats);
+             (long long)rows, (long long)n, (long long)kStaticDeltaFloats);
   int status = VQ_OK;
   float* deltas = static_deltas_for_current_device(&status);
   if (deltas == nullptr) return status;

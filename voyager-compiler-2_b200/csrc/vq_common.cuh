@@ -27,6 +27,19 @@ int check_launch(const char* what);
 
 constexpr int kSmCount = 148;
 
+// Per-device one-time set-up (function attributes such as the dynamic shared-memory limit
+// belong to a device, not to the process).  `done` holds one bit per device ordinal; returns
+// true, and marks the bit, the first time it is called with the current device.  Racing callers
+// may both see "first": the set-up they repeat is idempotent.
+inline bool first_call_on_device(unsigned long long* done) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return true;
+  const unsigned long long bit = 1ull << device;
+  if (*done & bit) return false;
+  *done |= bit;
+  return true;
+}
+
 // ---------------------------------------------------------------------------
 // storage dtypes.  All arithmetic is exact float32 followed by one RNE
 // rounding into the storage dtype, which is what the reference's CPU ops do.

@@ -13,6 +13,7 @@ from typing import List, Optional
 import torch
 from torch.library import Library
 
+from . import _native as N
 from . import ops as O
 
 # torch itself owns a "quantization" namespace (c10d); operators are added to it as a fragment,
@@ -90,10 +91,10 @@ def hadamard_amax(input: torch.Tensor, axis: int, hadamard: torch.Tensor) -> tor
     return O.tensor_amax(O.hadamard_rotate(input, axis, hadamard)).to(input.dtype)
 
 
-quantization_lib.impl("fake_quant", fake_quant, "CUDA")
-quantization_lib.impl("group_wise_affine_fake_quant", group_wise_affine_fake_quant, "CUDA")
-quantization_lib.impl("mx_fake_quant", mx_fake_quant, "CUDA")
-quantization_lib.impl("hadamard_amax", hadamard_amax, "CUDA")
+quantization_lib.impl("fake_quant", N.device_guarded(fake_quant), "CUDA")
+quantization_lib.impl("group_wise_affine_fake_quant", N.device_guarded(group_wise_affine_fake_quant), "CUDA")
+quantization_lib.impl("mx_fake_quant", N.device_guarded(mx_fake_quant), "CUDA")
+quantization_lib.impl("hadamard_amax", N.device_guarded(hadamard_amax), "CUDA")
 
 
 # ---- shapes for tracing ---------------------------------------------------------------

@@ -28,6 +28,7 @@ def _typed(codes: torch.Tensor, dtype):
     return codes.view(dtype) if isinstance(dtype, torch.dtype) else codes
 
 
+@N.device_guarded
 def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torch.Tensor:
     """Cast ``x / scale`` to FP8 (reference ``backend/gpu/fp8.py:253-261``): a ``uint8`` tensor of
     ``x``'s shape for ``dtype`` ``"fp8_e4m3"`` / ``"fp8_e5m2"``, a float8 tensor for a torch dtype.
@@ -117,6 +118,7 @@ def fp8_bmm(input: torch.Tensor, other: torch.Tensor, scale: torch.Tensor) -> to
     return fp8_gemm(a, b.transpose(-2, -1).contiguous(), scale.reshape(()), dtype=fmt)
 
 
+@N.device_guarded
 def softmax_quantize_fp8(scores: torch.Tensor, score_scale: float, out_scale: torch.Tensor,
                          mask: Optional[torch.Tensor] = None, causal_period: int = 0,
                          dtype: str = "fp8_e4m3") -> torch.Tensor:
@@ -143,6 +145,7 @@ def softmax_quantize_fp8(scores: torch.Tensor, score_scale: float, out_scale: to
     return out
 
 
+@N.device_guarded
 def attention_fp8(q8: torch.Tensor, k8: torch.Tensor, vt8: torch.Tensor, alpha_qk: torch.Tensor, score_scale: float,
                   p_scale: torch.Tensor, alpha_pv: torch.Tensor, ctx_scale: Optional[torch.Tensor] = None):
     """Causal attention on FP8 operands in one kernel: ``fp8_gemm(q8, k8, alpha_qk)``,
@@ -191,6 +194,7 @@ def _bf16_input(name: str, t: torch.Tensor) -> torch.Tensor:
     return t.contiguous()
 
 
+@N.device_guarded
 def rmsnorm_quantize_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, scale: torch.Tensor) -> torch.Tensor:
     """e4m3 bytes of ``rms_norm(x, weight, eps) / scale`` in one pass over ``x [..., H]``."""
     x, weight, scale = _bf16_input("rmsnorm_quantize_fp8", x), _bf16_input("rmsnorm_quantize_fp8", weight), _scale_arg(scale)
@@ -214,6 +218,7 @@ def _rows_view(name: str, t: torch.Tensor):
     return t, t.numel() // max(cols, 1), cols, cols
 
 
+@N.device_guarded
 def silu_mul_quantize_fp8(gate: torch.Tensor, up: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """e4m3 bytes of ``(silu(gate) * up) / scale`` in one pass.  ``gate`` and ``up`` may be
     column slices of one wider matrix (the two halves of a merged projection)."""
@@ -241,6 +246,7 @@ def _heads_view(name: str, x: torch.Tensor):
     return x.contiguous(), heads * d
 
 
+@N.device_guarded
 def rope_quantize_fp8(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                       scale: torch.Tensor) -> torch.Tensor:
     """e4m3 bytes of the rotary embedding of ``x [T, heads, d]`` (rotate-half form, ``cos`` /
@@ -259,6 +265,7 @@ def rope_quantize_fp8(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optiona
     return out
 
 
+@N.device_guarded
 def transpose_heads_quantize_fp8(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """e4m3 bytes of a head-major ``x [heads, T, d] / scale`` laid out token-major ``[T, heads * d]``."""
     x, scale = _bf16_input("transpose_heads_quantize_fp8", x), _scale_arg(scale)
@@ -270,6 +277,7 @@ def transpose_heads_quantize_fp8(x: torch.Tensor, scale: torch.Tensor) -> torch.
     return out
 
 
+@N.device_guarded
 def transpose_quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torch.Tensor:
     """FP8 bytes of ``x [T, heads, d] / scale`` laid out ``[heads, d, T]``."""
     scale = _scale_arg(scale)
@@ -282,6 +290,7 @@ def transpose_quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3
     return _typed(out, dtype)
 
 
+@N.device_guarded
 def quantize_fp8_transpose(input: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3"):
     """``(codes [M, N], transpose [N, M], amax)`` of a matrix in one pass over it: the FP8 bytes
     of ``input / scale`` in both layouts and ``amax(|input|)`` as a 0-d tensor of ``input``'s dtype
@@ -298,3 +307,29 @@ def quantize_fp8_transpose(input: torch.Tensor, scale: torch.Tensor, dtype="fp8_
                                               _dtype_id(scale.dtype), _stream()),
             "vq_transpose_quantize_fp8")
     return _typed(codes, dtype), _typed(transpose, dtype), amax.to(torch.int16).view(torch.bfloat16)
+
+
+# ---------------------------------------------------------------------------
+# ``voyager_gpu::cast_transpose_fp8``: the operator the reference's training lowering calls
+# (``backend/gpu/fp8.py:311-340``), same name and schema, CUDA key only
+# ---------------------------------------------------------------------------
+from torch.library import Library  # noqa: E402
+
+voyager_gpu_lib = Library("voyager_gpu", "FRAGMENT")
+voyager_gpu_lib.define("cast_transpose_fp8(Tensor x, Tensor scale, ScalarType dtype) -> (Tensor, Tensor, Tensor)")
+
+
+def _cast_transpose_fp8_op(x, scale, dtype):
+    if dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise NotImplementedError(f"cast_transpose_fp8 casts to float8_e4m3fn or float8_e5m2, not {dtype}")
+    return quantize_fp8_transpose(x, scale, dtype)
+
+
+voyager_gpu_lib.impl("cast_transpose_fp8", N.device_guarded(_cast_transpose_fp8_op), "CUDA")
+
+
+@torch.library.register_fake("voyager_gpu::cast_transpose_fp8")
+def _(x, scale, dtype):
+    rows, cols = x.shape
+    return (x.new_empty((rows, cols), dtype=dtype), x.new_empty((cols, rows), dtype=dtype),
+            x.new_empty((), dtype=x.dtype))

@@ -72,6 +72,7 @@ def salience_order(hessian, columns, within_block, block_size):
     return (base * block_size + rank)[block_order].reshape(-1)
 
 
+@N.device_guarded
 def sweep(weight, hinv_chol, block_size, qmap, scale_qmap=None, quant_max=None, salience=None, shrink=False,
           affine_range=None):
     """The blocked sweep given the inverse factor.  Returns the compensated weight (fp32,

@@ -25,6 +25,7 @@ from .ops import _broadcast_geometry, _dtype_id, _prepare_params, _ptr, _stream
 Q = torch.ops.quantized_ops
 
 
+@N.device_guarded
 def pack_codes(codes: torch.Tensor, bits: int) -> torch.Tensor:
     """Integer codes in ``[0, 2**bits)`` (values of a float tensor) as packed bytes: element ``i`` of
     the row-major tensor sits in byte ``i // (8 // bits)`` at bit ``bits * (i % (8 // bits))``."""
@@ -36,6 +37,7 @@ def pack_codes(codes: torch.Tensor, bits: int) -> torch.Tensor:
     return packed
 
 
+@N.device_guarded
 def unpack_dequantize(packed: torch.Tensor, bits: int, shape, scale: torch.Tensor,
                       zero_point: Optional[torch.Tensor] = None, block_size: Optional[int] = None,
                       output_qmap: Optional[torch.Tensor] = None) -> torch.Tensor:

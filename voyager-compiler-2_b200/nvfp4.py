@@ -51,6 +51,7 @@ def _alloc(shape, device):
     return codes, scales, nb, rows, k, per
 
 
+@N.device_guarded
 def cast_nvfp4(x: torch.Tensor, global_scale: torch.Tensor) -> PackedNVFP4:
     """Cast bfloat16 ``x [*batch, rows, K]`` (blocks of 16 along K) to packed NVFP4 against a given
     global scale, one pass (the role of the reference's ``cast_nvfp4`` kernels, ``nvfp4.py:683-739``)."""
@@ -67,6 +68,7 @@ def cast_nvfp4(x: torch.Tensor, global_scale: torch.Tensor) -> PackedNVFP4:
     return PackedNVFP4(codes, scales)
 
 
+@N.device_guarded
 def pack_nvfp4(codes: torch.Tensor, scale: torch.Tensor, check: bool = True) -> PackedNVFP4:
     """Pack ``quantize_mx``'s outputs (bfloat16-valued e2m1 codes ``[*batch, rows, K]`` and e4m3-valued
     scales ``[*batch, rows, K/16]``).  ``check`` synchronises and raises if a value is not representable."""
@@ -85,6 +87,7 @@ def pack_nvfp4(codes: torch.Tensor, scale: torch.Tensor, check: bool = True) -> 
     return PackedNVFP4(out, scales)
 
 
+@N.device_guarded
 def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = None,
                bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
     """``alpha * (A @ B^T) + bias`` for packed operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (equal
@@ -235,3 +238,79 @@ def emulate_nvfp4_linear(input, input_scale, weight, weight_scale, alpha, one=No
     weight, weight_scale = unpack_nvfp4(weight, weight_scale)
     return torch.ops.quantized_ops.linear_mx(input, weight, bias, input_scale=input_scale, weight_scale=weight_scale,
                                              block_size=BLOCK_SIZE, alpha=alpha)
+
+
+# ---------------------------------------------------------------------------
+# the ``voyager_gpu`` operators a lowered graph calls
+# ---------------------------------------------------------------------------
+# Same names and schemas as the reference registers (``backend/gpu/nvfp4.py:675-679, 773-778,
+# 851-854, 1094-1097``), on the CUDA key only, so that a graph rewritten by the reference's
+# ``backend.gpu.lower`` finds its call targets here.  Packed block scales are returned flat
+# (``[ceil(rows/128) * 128 * ceil(K/64) * 4]`` bytes), as the reference's casts return them.
+from torch.library import Library  # noqa: E402
+
+voyager_gpu_lib = Library("voyager_gpu", "FRAGMENT")
+voyager_gpu_lib.define("cast_nvfp4(Tensor x, Tensor? hadamard, Tensor? seed, int axis) -> (Tensor, Tensor, Tensor)")
+voyager_gpu_lib.define("cast_nvfp4_pair(Tensor x, Tensor? hadamard, Tensor? seed, Tensor? transpose_seed) "
+                       "-> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)")
+voyager_gpu_lib.define("cast_nvfp4_square(Tensor x) -> (Tensor, Tensor, Tensor, Tensor, Tensor)")
+voyager_gpu_lib.define("nvfp4_linear(Tensor input, Tensor input_scale, Tensor weight, Tensor weight_scale, "
+                       "Tensor alpha, Tensor one, Tensor? bias) -> Tensor")
+
+
+def _matrix(x):
+    if x.ndim != 2 or x.dtype != torch.bfloat16:
+        raise NotImplementedError("the voyager_gpu NVFP4 casts take a bfloat16 matrix")
+    return x
+
+
+def _cast_nvfp4_op(x, hadamard, seed, axis):
+    codes, scales, t = quantize_nvfp4(_matrix(x), axis, seed, hadamard)
+    return codes, scales.reshape(-1), t
+
+
+def _cast_nvfp4_pair_op(x, hadamard, seed, transpose_seed):
+    c, s, t, ct, st, tt = quantize_nvfp4_pair(_matrix(x), seed, transpose_seed, hadamard)
+    return c, s.reshape(-1), t, ct, st.reshape(-1), tt
+
+
+def _cast_nvfp4_square_op(x):
+    c, s, ct, st, t = quantize_nvfp4_square(_matrix(x))
+    return c, s.reshape(-1), ct, st.reshape(-1), t
+
+
+voyager_gpu_lib.impl("cast_nvfp4", N.device_guarded(_cast_nvfp4_op), "CUDA")
+voyager_gpu_lib.impl("cast_nvfp4_pair", N.device_guarded(_cast_nvfp4_pair_op), "CUDA")
+voyager_gpu_lib.impl("cast_nvfp4_square", N.device_guarded(_cast_nvfp4_square_op), "CUDA")
+voyager_gpu_lib.impl("nvfp4_linear", N.device_guarded(nvfp4_linear), "CUDA")
+
+
+def _fake_cast_outputs(x, rows, cols):
+    padded = -(-rows // 128) * 128 * (-(-(cols // BLOCK_SIZE) // 4) * 4)
+    return (x.new_empty((rows, cols // 2), dtype=torch.uint8), x.new_empty((padded,), dtype=torch.uint8),
+            x.new_empty((), dtype=torch.bfloat16))
+
+
+@torch.library.register_fake("voyager_gpu::cast_nvfp4")
+def _(x, hadamard, seed, axis):
+    rows, cols = x.shape if axis % 2 == 1 else x.shape[::-1]
+    return _fake_cast_outputs(x, rows, cols)
+
+
+@torch.library.register_fake("voyager_gpu::cast_nvfp4_pair")
+def _(x, hadamard, seed, transpose_seed):
+    rows, cols = x.shape
+    return (*_fake_cast_outputs(x, rows, cols), *_fake_cast_outputs(x, cols, rows))
+
+
+@torch.library.register_fake("voyager_gpu::cast_nvfp4_square")
+def _(x):
+    rows, cols = x.shape
+    c, s, t = _fake_cast_outputs(x, rows, cols)
+    ct, st, _ = _fake_cast_outputs(x, cols, rows)
+    return c, s, ct, st, t
+
+
+@torch.library.register_fake("voyager_gpu::nvfp4_linear")
+def _(input, input_scale, weight, weight_scale, alpha, one, bias):
+    return input.new_empty((*input.shape[:-1], weight.shape[0]), dtype=torch.bfloat16)

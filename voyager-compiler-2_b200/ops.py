@@ -102,7 +102,7 @@ def vmap(input: torch.Tensor, qmap: torch.Tensor) -> torch.Tensor:
     return out
 
 
-quantized_ops_lib.impl("vmap", vmap, "CUDA")
+quantized_ops_lib.impl("vmap", N.device_guarded(vmap), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::vmap")
@@ -251,7 +251,7 @@ def quantize(input, scale, zero_point=None, axes=None, block_size=None, qmap=Non
     return _quantize_with(input, scale, zero_point, block_size, _element_round(qmap, output_code, seed))
 
 
-quantized_ops_lib.impl("quantize", quantize, "CUDA")
+quantized_ops_lib.impl("quantize", N.device_guarded(quantize), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::quantize")
@@ -285,7 +285,7 @@ def dequantize(input, scale, zero_point=None, axes=None, block_size=None, input_
     return out
 
 
-quantized_ops_lib.impl("dequantize", dequantize, "CUDA")
+quantized_ops_lib.impl("dequantize", N.device_guarded(dequantize), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::dequantize")
@@ -374,7 +374,7 @@ def calculate_mx_qparam(input, axes, block_size, quant_max, force_scale_power_of
     return scale
 
 
-quantized_ops_lib.impl("calculate_mx_qparam", calculate_mx_qparam, "CUDA")
+quantized_ops_lib.impl("calculate_mx_qparam", N.device_guarded(calculate_mx_qparam), "CUDA")
 
 
 def _scale_shape(shape, axes, block_size):
@@ -421,7 +421,7 @@ def quantize_mx(input, qmap, axes, block_size, quant_max, force_scale_power_of_t
     return scale, codes
 
 
-quantized_ops_lib.impl("quantize_mx", quantize_mx, "CUDA")
+quantized_ops_lib.impl("quantize_mx", N.device_guarded(quantize_mx), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::quantize_mx")
@@ -485,7 +485,7 @@ def dequantize_mx(input, scale, block_size, code=None, global_scale=None):
     return _decode_and_scale(input, scale, code, block_size, global_scale)
 
 
-quantized_ops_lib.impl("dequantize_mx", dequantize_mx, "CUDA")
+quantized_ops_lib.impl("dequantize_mx", N.device_guarded(dequantize_mx), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::dequantize_mx")
@@ -524,7 +524,7 @@ def quantize_affine(input, qmap, axes, block_size, quant_min, quant_max, scale_q
     return scale, zero, codes
 
 
-quantized_ops_lib.impl("quantize_affine", quantize_affine, "CUDA")
+quantized_ops_lib.impl("quantize_affine", N.device_guarded(quantize_affine), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::quantize_affine")
@@ -537,6 +537,7 @@ def _(input, qmap, axes, block_size, quant_min, quant_max, scale_qmap=None):
 # ---------------------------------------------------------------------------
 # tensor amax and the NVFP4 global scale
 # ---------------------------------------------------------------------------
+@N.device_guarded
 def tensor_amax(x: torch.Tensor) -> torch.Tensor:
     """``max |x|`` as a 0-d float32 tensor (one kernel, no host sync)."""
     x = x if _is_dense(x) else x.contiguous()
@@ -545,6 +546,7 @@ def tensor_amax(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@N.device_guarded
 def calculate_global_scale(input: torch.Tensor, quant_max: float, scale_max: float) -> torch.Tensor:
     """NVFP4's per-tensor scale ``amax / (quant_max * scale_max)`` in the
     input's dtype (reference ``fake_quantize.py:142-160``)."""
@@ -571,6 +573,7 @@ def _parse_layout(layout: str):
     return act, wgt, out
 
 
+@N.device_guarded
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None,
             alpha_cols=None, residual=None, causal=None, gated_scale=None):
     """``out[..., m, n] = alpha * sum_k a[..., m, k] * b[..., n, k] + bias[n]`` on the
@@ -702,8 +705,8 @@ def matmul(input, other, *, layout=MATMUL_LAYOUT, out_dtype=None):
     return _gemm_in_layout(MATMUL_LAYOUT, input, other, layout, out_dtype)
 
 
-quantized_ops_lib.impl("linear", linear, "CUDA")
-quantized_ops_lib.impl("matmul", matmul, "CUDA")
+quantized_ops_lib.impl("linear", N.device_guarded(linear), "CUDA")
+quantized_ops_lib.impl("matmul", N.device_guarded(matmul), "CUDA")
 
 
 def _gemm_out_shape(activation, weight, layout, weight_is_matrix):
@@ -796,8 +799,8 @@ def matmul_mx(self, other, *, input_scale=None, weight_scale=None, block_size=No
                     weight_code, alpha, (A_data, A_indices, A_indptr), layout, out_dtype)
 
 
-quantized_ops_lib.impl("linear_mx", linear_mx, "CUDA")
-quantized_ops_lib.impl("matmul_mx", matmul_mx, "CUDA")
+quantized_ops_lib.impl("linear_mx", N.device_guarded(linear_mx), "CUDA")
+quantized_ops_lib.impl("matmul_mx", N.device_guarded(matmul_mx), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::linear_mx")
@@ -835,6 +838,7 @@ def hadamard_matrix(device=None) -> torch.Tensor:
     return (signs[:, None] * h / math.sqrt(HADAMARD_SIZE)).to(device)
 
 
+@N.device_guarded
 def hadamard_rotate(x: torch.Tensor, axis: int, matrix: torch.Tensor) -> torch.Tensor:
     """Multiply each run of 16 elements along ``axis`` (the last or second-to-last) by
     ``matrix`` in fp32; the axis is zero padded to whole runs and keeps the padded
@@ -877,7 +881,7 @@ def quantize_mx_transpose(input, qmap, block_size, quant_max, force_scale_power_
             *quantize_mx(t, *common, transpose_seed, transpose_global_scale))
 
 
-quantized_ops_lib.impl("quantize_mx_transpose", quantize_mx_transpose, "CUDA")
+quantized_ops_lib.impl("quantize_mx_transpose", N.device_guarded(quantize_mx_transpose), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::quantize_mx_transpose")
@@ -954,7 +958,7 @@ def sdpa_mx(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, q
     return out
 
 
-quantized_ops_lib.impl("sdpa_mx", sdpa_mx, "CUDA")
+quantized_ops_lib.impl("sdpa_mx", N.device_guarded(sdpa_mx), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::sdpa_mx")

@@ -150,10 +150,10 @@ def spmm_csr(data, indices, indptr, B, B_scale=None, B_code=None, block_size=Non
     return out.reshape(*batch, rows, n_out)
 
 
-quantized_ops_lib.impl("filter_outlier", filter_outlier, "CUDA")
-quantized_ops_lib.impl("quantize_mx_outlier", quantize_mx_outlier, "CUDA")
-quantized_ops_lib.impl("slice_csr_tensor", slice_csr_tensor, "CUDA")
-quantized_ops_lib.impl("spmm_csr", spmm_csr, "CUDA")
+quantized_ops_lib.impl("filter_outlier", N.device_guarded(filter_outlier), "CUDA")
+quantized_ops_lib.impl("quantize_mx_outlier", N.device_guarded(quantize_mx_outlier), "CUDA")
+quantized_ops_lib.impl("slice_csr_tensor", N.device_guarded(slice_csr_tensor), "CUDA")
+quantized_ops_lib.impl("spmm_csr", N.device_guarded(spmm_csr), "CUDA")
 
 
 @torch.library.register_fake("quantized_ops::filter_outlier")

@@ -225,14 +225,22 @@ def gptq_layer_parallel(problems, solve, group=None):
     mine = lpt_schedule(costs, world)[rank]
     local = {i: solve(problems[i]) for i in mine}
     if world == 1:
-        return [local[i] for i in range(len(problems))]
+        return [local[i].to(problems[i]["weight"].dtype) for i in range(len(problems))]
     owner = {}
     for r, indices in enumerate(lpt_schedule(costs, world)):
         for i in indices:
             owner[i] = r
+    # One wire format on every rank: float32 (what the solve computes in, whatever the weight's dtype),
+    # the weight's shape, contiguous.  Receivers cannot know what dtype ``solve`` returned on the owner.
     results = []
     for i, p in enumerate(problems):
-        out = local[i] if owner[i] == rank else torch.empty_like(p["weight"])
+        weight = p["weight"]
+        if owner[i] == rank:
+            if local[i].shape != weight.shape:
+                raise ValueError(f"solve() returned shape {tuple(local[i].shape)} for a weight of {tuple(weight.shape)}")
+            out = local[i].to(torch.float32).contiguous()
+        else:
+            out = torch.empty(weight.shape, dtype=torch.float32, device=weight.device)
         dist.broadcast(out, src=dist.get_global_rank(group, owner[i]) if group is not None else owner[i], group=group)
-        results.append(out)
+        results.append(out.to(weight.dtype))
     return results

@@ -170,11 +170,16 @@ _levels_cache = {}
 
 def stochastic_round(qmap: torch.Tensor, seed: torch.Tensor) -> RoundSpec:
     key = (qmap.data_ptr(), qmap.device, qmap.dtype, qmap._version)
-    levels = _levels_cache.get(key)
-    if levels is None:
+    hit = _levels_cache.get(key)
+    if hit is None:
         levels = formats.qmap_levels(qmap) if qmap.numel() == formats.QMAP_SIZE else qmap.float()
         levels = levels.contiguous()
-        _levels_cache[key] = levels
+        if len(_levels_cache) > 256:
+            _levels_cache.clear()
+        # the entry holds the table itself: its address cannot be handed to another tensor while it is cached
+        _levels_cache[key] = (qmap, levels)
+    else:
+        levels = hit[1]
     if seed.dtype != torch.int64 or seed.device != qmap.device:
         seed = seed.to(device=qmap.device, dtype=torch.int64)
     c = N.VqRound()

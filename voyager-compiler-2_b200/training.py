@@ -42,7 +42,7 @@ def _rmsnorm_backward_cuda(gradients: List[torch.Tensor], x: torch.Tensor, rsqrt
     return dx, dw
 
 
-voyager_gpu_lib.impl("rmsnorm_backward", _rmsnorm_backward_cuda, "CUDA")
+voyager_gpu_lib.impl("rmsnorm_backward", N.device_guarded(_rmsnorm_backward_cuda), "CUDA")
 
 
 @torch.library.register_fake("voyager_gpu::rmsnorm_backward")
