@@ -25,6 +25,14 @@ finds its inputs cached.
 
 ``--impl reference`` times the CPU oracle (a port of the reference's CPU
 operators) on the host cores for the same workload, on a bounded sample.
+
+Beside the timed region the line carries: ``self_check`` (the GPU path run on the
+CPU leg's own inputs and compared with the CPU leg's output, plus workload-specific
+comparisons; a failed check makes the process exit non-zero), ``gpu_reference``
+(library kernels -- ``torch._scaled_mm``, cuBLAS ``torch.matmul``, ``F.scaled_mm`` --
+timed on the workload's GEMM shapes in the same process: a baseline, never the product
+path), and, for the default workload, ``secondary``: the quantizer (``q1``), the MXINT8
+linear (``c1``) and the NVFP4 linear (``c4``) measured after the main region.
 """
 
 import argparse
@@ -53,6 +61,23 @@ def measured_peaks():
         return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
                 "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# Library FP8 / FP4 GEMM throughput measured in this process (``gpu_reference``); the roofline peak
+# of the FP8 / FP4 kernels when present, else a multiple of the measured bf16 figure.
+MEASURED_LIBRARY = {}
+
+
+def fp8_peak(peaks):
+    if MEASURED_LIBRARY.get("fp8"):
+        return MEASURED_LIBRARY["fp8"], "best torch._scaled_mm FP8 GEMM over this layer's shapes, measured in this run"
+    return 2.0 * peaks["bf16_tflops"], f"2 x {peaks['source']} bf16 cuBLAS burst (no FP8 library GEMM could be timed)"
+
+
+def fp4_peak(peaks):
+    if MEASURED_LIBRARY.get("fp4"):
+        return MEASURED_LIBRARY["fp4"], "torch scaled_mm NVFP4 GEMM on this shape, measured in this run"
+    return 4.0 * peaks["bf16_tflops"], f"4 x {peaks['source']} bf16 cuBLAS burst (no FP4 library GEMM could be timed)"
 
 
 class ClockSampler:
@@ -130,6 +155,45 @@ def time_region(fn, steps, barrier, finish=None):
     stop.record()
     barrier()
     return start.elapsed_time(stop) * 1e-3
+
+
+def max_rel(got, want):
+    """Largest absolute difference over the largest magnitude of ``want`` (both moved to the CPU)."""
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def time_library(fn, n_sets, reps=40):
+    """Seconds per call of a library kernel, rotating over ``n_sets`` operand sets (beyond L2 together)."""
+    for i in range(3):
+        fn(i % n_sets)
+    return time_region(lambda i: fn(i % n_sets), reps, torch.cuda.synchronize) / reps
+
+
+def fp8_library_gemms(shapes, ours, n_sets=3):
+    """``torch._scaled_mm`` (cuBLASLt FP8, one float32 scale per operand, bfloat16 out) and this
+    package's FP8 GEMM on the same ``[M, N, K]`` shapes and the same packed operands."""
+    rows = []
+    one = torch.ones((), device="cuda")
+    for m, n, k in shapes:
+        a = [torch.randn(m, k, device="cuda").to(torch.float8_e4m3fn) for _ in range(n_sets)]
+        b = [torch.randn(n, k, device="cuda").to(torch.float8_e4m3fn) for _ in range(n_sets)]
+        row = {"mnk": [m, n, k]}
+        try:
+            t = time_library(lambda i: torch._scaled_mm(a[i], b[i].t(), scale_a=one, scale_b=one,
+                                                        out_dtype=torch.bfloat16), n_sets)
+            row["library_tflops"] = 2.0 * m * n * k / t / 1e12
+        except Exception as exc:  # the library has no kernel for this shape or build
+            row["library_tflops"] = None
+            row["library_error"] = repr(exc)[:160]
+        au, bu = [x.view(torch.uint8) for x in a], [x.view(torch.uint8) for x in b]
+        t = time_library(lambda i: ours(au[i], bu[i], one), n_sets)
+        row["ours_tflops"] = 2.0 * m * n * k / t / 1e12
+        rows.append(row)
+        del a, b, au, bu
+    best = max([r["library_tflops"] for r in rows if r.get("library_tflops")] or [None], key=lambda v: v or 0)
+    return {"library": "torch._scaled_mm (cuBLASLt FP8 e4m3, tensor-wise scales, bf16 out), same process",
+            "shapes": rows, "best_library_tflops": best}
 
 
 class HostPipeline:
@@ -251,10 +315,25 @@ class C1:
         secs = time_region(lambda i: ops.gemm_tn(*pairs[i % len(pairs)]), reps, torch.cuda.synchronize) / reps
         flops = 2.0 * self.tokens * self.N * self.K
         achieved = flops / secs / 1e12
-        return secs, {"kernel": "gemm_tn_kernel (tcgen05 kind::f16 bf16, 2048x4096x4096)", "bound": "tensor",
+        return secs, {"kernel": "gemm_tn_pair_kernel (tcgen05 kind::f16 bf16, cta_group::2, 2048x4096x4096)", "bound": "tensor",
                       "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                       "frac": achieved / peaks["bf16_tflops"],
                       "peak_source": f"{peaks['source']} bf16 cuBLAS burst", "traffic": NCU_TRAFFIC_BYTES["c1"]}
+
+    def gpu_reference(self):
+        """cuBLAS bf16 (``torch.matmul``) on the C1 GEMM shape beside this package's bf16 GEMM."""
+        m, n, k, sets = self.tokens, self.N, self.K, 6
+        a = [torch.randn(m, k, device="cuda").bfloat16() for _ in range(sets)]
+        b = [torch.randn(n, k, device="cuda").bfloat16() for _ in range(sets)]
+        lib = time_library(lambda i: torch.matmul(a[i], b[i].t()), sets)
+        ours = time_library(lambda i: self.vb.ops.gemm_tn(a[i], b[i]), sets)
+        fl = 2.0 * m * n * k / 1e12
+        return {"library": "torch.matmul bf16 (cuBLAS), same process", "shapes": [
+            {"mnk": [m, n, k], "library_tflops": fl / lib, "ours_tflops": fl / ours}], "best_library_tflops": fl / lib}
+
+    def gpu_check(self, state, cpu_out):
+        x, w, _ = state
+        return {"linear_mx_vs_cpu_oracle": (max_rel(self._run(x.cuda(), w.cuda()), cpu_out), 1e-2)}
 
     @staticmethod
     def cpu_setup():
@@ -286,8 +365,9 @@ class C2:
     tokens = 2048
     n_sets = 4
     dtype = "fp8_e4m3 (fp32 accumulate), bf16 elsewhere"
-    cpu_tokens = 256
-    cpu_sample = "decoder-layer forwards of a 256-token prefill (1/8 of the GPU step's tokens)"
+    cpu_tokens = 2048
+    cpu_sample = "decoder-layer forwards of the same 2048-token prefill"
+    GEMM_SHAPES = [(2048, 6144, 4096), (2048, 4096, 4096), (2048, 28672, 4096), (2048, 4096, 14336)]
 
     def __init__(self, dev, rank):
         import voyager_b200
@@ -296,7 +376,7 @@ class C2:
         W = voyager_b200.workloads
         self.shape = W.LLAMA_8B
         params = W.make_layer_params(7 + rank, self.shape, dev)
-        self.x = [W.make_hidden_states(100 * rank + i, self.tokens, self.shape, dev) for i in range(self.n_sets)]
+        self.x = [W.make_hidden_states(1000 * rank + 100 + i, self.tokens, self.shape, dev) for i in range(self.n_sets)]
         scales = W.calibrate_fp8_scales(self.x[0], params, self.shape)
         self.layer = W.Fp8DecoderLayer(params, scales, self.shape, fuse_attention=self.fuse_attention)
         del params
@@ -326,11 +406,35 @@ class C2:
                            torch.cuda.synchronize) / reps
         flops = 2.0 * self.tokens * 2 * sh.intermediate * sh.hidden
         achieved = flops / secs / 1e12
-        peak = 2.0 * peaks["bf16_tflops"]
+        peak, source = fp8_peak(peaks)
         return secs, {"kernel": "gemm_tn_pair_kernel (tcgen05 kind::f8f6f4 e4m3, cta_group::2, 2048x28672x4096 merged gate/up projection, SwiGLU + FP8 cast epilogue)",
                       "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                      "peak_source": f"2 x {peaks['source']} bf16 cuBLAS burst (no FP8 peak was measured)",
-                      "traffic": NCU_TRAFFIC_BYTES["c2"]}
+                      "peak_source": source, "traffic": NCU_TRAFFIC_BYTES["c2"]}
+
+    def gpu_reference(self):
+        """``torch._scaled_mm`` on the layer's four GEMM shapes beside this package's FP8 GEMM."""
+        return fp8_library_gemms(self.GEMM_SHAPES, lambda a, b, one: self.vb.fp8.fp8_gemm(a, b, one))
+
+    def self_check(self):
+        """One graph replay against the same layer run kernel by kernel with torch producers."""
+        self.graphs[0][0].replay()
+        fused = self.graphs[0][1].clone()
+        # torch's rsqrt / exp producers differ from the fused kernels' in the last bit on a few elements; the FP8
+        # re-quantizations downstream turn that into the same few-percent tail as against the CPU oracle
+        return {"graph_replay_vs_unfused_kernels": (max_rel(fused, self.layer.forward_unfused(self.x[0])), 6e-2)}
+
+    def gpu_check(self, state, cpu_out):
+        """The CPU leg's layer (its weights, scales and input) on the GPU kernels against the CPU leg's output."""
+        x, params, scales, shape, _, _ = state
+        W = self.vb.workloads
+        layer = W.Fp8DecoderLayer({k: v.cuda() for k, v in params.items()}, {k: v.cuda() for k, v in scales.items()},
+                                  shape, fuse_attention=self.fuse_attention)
+        got = layer(x.cuda()).double().cpu()
+        want = cpu_out.double()
+        rms = float((got - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt())
+        # kernel by kernel the layer reproduces the converted graph to summation order (tests/); end to end that
+        # noise passes five FP8 re-quantizations, each flipped code moving a value by up to 1/8
+        return {"layer_vs_cpu_oracle_max": (max_rel(got, want), 6e-2), "layer_vs_cpu_oracle_rms": (rms, 2e-2)}
 
     @staticmethod
     def cpu_setup():
@@ -339,7 +443,7 @@ class C2:
         W = voyager_b200.workloads
         shape = W.LLAMA_8B
         params = W.make_layer_params(7, shape)
-        x = W.make_hidden_states(100, C2.cpu_tokens, shape)
+        x = W.make_hidden_states(100, C2.cpu_tokens, shape)   # rank 0's first input set
         scales = W.calibrate_fp8_scales(x, params, shape)
         return x, params, scales, shape, W.rope_tables(C2.cpu_tokens, shape, "cpu"), W.causal_mask(C2.cpu_tokens, "cpu")
 
@@ -407,6 +511,15 @@ class Q1:
                       "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth",
                       "traffic": None}
 
+    def gpu_check(self, state, cpu_out):
+        """Codes and scales are compared bit for bit: the figure is the fraction of differing values."""
+        x, _ = state
+        scale, codes = self.Q.quantize_mx(x.cuda(), self.table, [-1], self.BLOCK, self.QMAX, True)
+        want_scale, want_codes = cpu_out
+        bad = (codes.cpu().view(torch.int16) != want_codes.view(torch.int16)).float().mean() + \
+            (scale.cpu().view(torch.int16) != want_scale.view(torch.int16)).float().mean()
+        return {"codes_and_scales_differing_from_cpu_oracle": (float(bad), 0.0)}
+
     @staticmethod
     def cpu_setup():
         from oracle import tables as OT
@@ -472,6 +585,12 @@ class R1:
                       "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                       "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth",
                       "traffic": NCU_TRAFFIC_BYTES["r1"]}
+
+    def gpu_check(self, state, cpu_out):
+        grads, x, rsqrt, weight, residual = state
+        dx, dw = self.vb.training.rmsnorm_backward([t.cuda() for t in grads], x.cuda(), rsqrt.cuda(), weight.cuda(),
+                                                   residual.cuda())
+        return {"dx_vs_cpu_oracle": (max_rel(dx, cpu_out[0]), 2e-2), "dw_vs_cpu_oracle": (max_rel(dw, cpu_out[1]), 2e-2)}
 
     @staticmethod
     def cpu_setup():
@@ -545,11 +664,57 @@ class C4:
             gemm(i)
         secs = time_region(gemm, reps, torch.cuda.synchronize) / reps
         achieved = 2.0 * self.tokens * self.N * self.K / secs / 1e12
-        peak = 4.0 * peaks["bf16_tflops"]
+        peak, source = fp4_peak(peaks)
         return secs, {"kernel": "gemm_nvfp4_kernel (tcgen05 kind::mxf4nvf4.block_scale, 2048x14336x4096)",
                       "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                      "peak_source": f"4 x {peaks['source']} bf16 cuBLAS burst (no FP4 peak was measured)",
-                      "traffic": None}
+                      "peak_source": source, "traffic": None}
+
+    def gpu_reference(self):
+        """The library's block-scaled NVFP4 GEMM (``torch.nn.functional.scaled_mm``, the call the reference's
+        ``nvfp4_linear`` makes) on this shape and these packed operands, beside this package's kernel."""
+        import torch.nn.functional as F
+
+        NV = self.vb.nvfp4
+        packed = [NV.quantize_nvfp4(x) for x in self.x]
+        alpha = [(t * self.tw).float() for _, _, t in packed]
+        fl = 2.0 * self.tokens * self.N * self.K / 1e12
+        ours = time_library(lambda i: NV.nvfp4_linear(packed[i][0], packed[i][1], self.w_codes, self.w_scales,
+                                                      alpha[i], self.one, None), len(packed))
+        row = {"mnk": [self.tokens, self.N, self.K], "ours_tflops": fl / ours, "library_tflops": None}
+        try:
+            from torch.nn.functional import ScalingType, SwizzleType
+
+            b4 = self.w_codes.view(torch.float4_e2m1fn_x2).t()
+            sb = self.w_scales.reshape(-1).view(torch.float8_e4m3fn)
+            block, tensor = ScalingType.BlockWise1x16, ScalingType.TensorWise
+            swz, none = SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE
+
+            def lib(i):
+                codes, scales, _ = packed[i]
+                return F.scaled_mm(codes.view(torch.float4_e2m1fn_x2), b4,
+                                   [scales.reshape(-1).view(torch.float8_e4m3fn), alpha[i]], [block, tensor],
+                                   [sb, self.one], [block, tensor], swizzle_a=[swz, none], swizzle_b=[swz, none],
+                                   output_dtype=torch.bfloat16)
+
+            row["library_vs_ours_max_rel"] = max_rel(lib(0), NV.nvfp4_linear(packed[0][0], packed[0][1], self.w_codes,
+                                                                             self.w_scales, alpha[0], self.one, None))
+            row["library_tflops"] = fl / time_library(lib, len(packed))
+        except Exception as exc:  # this torch build has no block-scaled FP4 GEMM
+            row["library_error"] = repr(exc)[:160]
+        return {"library": "torch.nn.functional.scaled_mm NVFP4 (BlockWise1x16 e4m3 scales + tensor-wise alpha), same process",
+                "shapes": [row], "best_library_tflops": row["library_tflops"]}
+
+    def gpu_check(self, state, cpu_out):
+        x = state[0]
+        return {"nvfp4_linear_vs_cpu_oracle": (max_rel(self._run_with(x.cuda(), state), cpu_out), 1e-2)}
+
+    def _run_with(self, x, state):
+        """The CPU leg's weight (its codes, scales and global scale) packed for the GPU kernel."""
+        NV = self.vb.nvfp4
+        _, cw, sw, tw, _, _ = state
+        w = NV.pack_nvfp4(cw.cuda(), sw.cuda())
+        codes, scales, t = NV.quantize_nvfp4(x)
+        return NV.nvfp4_linear(codes, scales, w.codes, w.scales, (t * tw.cuda()).float(), self.one, None)
 
     @staticmethod
     def cpu_setup():
@@ -575,28 +740,129 @@ class C4:
         return OG.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=16, alpha=t * tw)
 
 
+class EagerStep:
+    """Stands in for a captured graph when a step cannot be captured: ``replay()`` runs it again into the
+    same output buffer."""
+
+    def __init__(self, fn, out):
+        self.fn, self.out = fn, out
+
+    def replay(self):
+        self.out.copy_(self.fn())
+
+
+class C2TP:
+    """Workload c2 over N GPUs as ONE tensor-parallel layer (strong scaling): the same 2048-token prefill,
+    q/k/v and gate/up column-parallel, attention head-parallel, o_proj / down_proj row-parallel with float32
+    partial sums reduce-scattered over NCCL, activations sharded by token rows between the blocks."""
+    name = "c2"
+    tokens = 2048
+    n_sets = 4
+    dtype = C2.dtype
+    cpu_tokens = C2.cpu_tokens
+    cpu_sample = C2.cpu_sample
+
+    def __init__(self, dev, rank, world):
+        import torch.distributed as dist
+
+        import voyager_b200
+
+        self.vb = voyager_b200
+        W, P = voyager_b200.workloads, voyager_b200.parallel
+        self.shape = W.LLAMA_8B
+        self.description = C2.description.replace("per GPU", f"split over {world} GPUs (tensor parallel: column-parallel "
+                                                  "QKV and gate/up, head-parallel attention, row-parallel o_proj and "
+                                                  "down_proj, NCCL all-gather of FP8 codes and reduce-scatter of float32 "
+                                                  "partial sums)")
+        params = W.make_layer_params(7, self.shape, dev)                 # every rank holds the slices it needs
+        full = [W.make_hidden_states(100 + i, self.tokens, self.shape, dev) for i in range(self.n_sets)]
+        scales = W.calibrate_fp8_scales(full[0], params, self.shape)
+        for name in sorted(scales):                                       # one set of scales on every rank
+            dist.broadcast(scales[name], src=0)
+        self.layer = P.Fp8DecoderLayerTP(params, scales, self.shape)
+        del params
+        lo, hi = P.shard_bounds(self.tokens, rank, world)
+        self.x = [x[lo:hi].contiguous() for x in full]
+        del full
+        self.launches_per_step = self.layer.LAUNCHES
+        self.h2d_bytes = (hi - lo) * self.shape.hidden * 2
+        self.d2h_bytes = (hi - lo) * self.shape.hidden * 2
+        for x in self.x[:2]:
+            self.layer(x)
+        torch.cuda.synchronize()
+        self.launch = "CUDA graph replay per step (collectives captured)"
+        try:
+            self.graphs = [capture(lambda x=x: self.layer(x)) for x in self.x]
+        except Exception as exc:  # the collectives could not be captured on this build: launch every kernel
+            torch.cuda.synchronize()
+            self.launch = f"eager launches per step (graph capture refused: {type(exc).__name__})"
+            self.graphs = [(EagerStep(lambda x=x: self.layer(x), self.layer(x)),) for x in self.x]
+            self.graphs = [(g[0], g[0].out) for g in self.graphs]
+        self.pipeline = HostPipeline(self.x, [x.cpu().pin_memory() for x in self.x], self.graphs)
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def collective_share(self, steps):
+        """Share of an (uncaptured) step's device time spent inside the four collectives, from CUDA events
+        around them; a collective's span includes waiting for the slowest rank."""
+        for i in range(3):
+            self.layer(self.x[i % self.n_sets])
+        self.layer.timed = True
+        self.layer.collective_events = []
+        elapsed = time_region(lambda i: self.layer(self.x[i % self.n_sets]), steps, torch.cuda.synchronize)
+        inside = self.layer.collective_seconds()
+        self.layer.timed = False
+        return {"share": inside / elapsed, "collective_ms_per_step": inside / steps * 1e3,
+                "eager_ms_per_step": elapsed / steps * 1e3, "collectives_per_step": self.layer.COLLECTIVES,
+                "what": "2 x all-gather of FP8 codes [T, 4096] bytes, 2 x reduce-scatter of float32 [T, 4096] partial sums"}
+
+    def roofline(self, peaks, reps):
+        """This rank's slice of the gate/up GEMM with the SwiGLU epilogue: [2048, 4096] x [2 * 14336 / N, 4096]^T."""
+        FP8 = self.vb.fp8
+        sh, s, L = self.shape, self.layer.scales, self.layer
+        full = [torch.randn(self.tokens, sh.hidden, device="cuda").bfloat16() for _ in range(3)]
+        acts = [FP8.quantize_fp8(torch.nn.functional.rms_norm(x, (sh.hidden,)), s["h2"]) for x in full]
+        run = lambda i: FP8.fp8_gemm(acts[i % len(acts)], L.w8_swiglu, alpha_cols=L.alpha_swiglu, gated_scale=s["act"],
+                                     round_acc=True)
+        for i in range(3):
+            run(i)
+        secs = time_region(run, reps, torch.cuda.synchronize) / reps
+        n = L.w8_swiglu.shape[0]
+        achieved = 2.0 * self.tokens * n * sh.hidden / secs / 1e12
+        peak, source = fp8_peak(peaks)
+        return secs, {"kernel": f"gemm_tn_pair_kernel (tcgen05 kind::f8f6f4 e4m3, cta_group::2, 2048x{n}x4096: this rank's "
+                                "columns of the merged gate/up projection, SwiGLU + FP8 cast epilogue)",
+                      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                      "peak_source": source, "traffic": None}
+
+
 WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "q1": Q1, "r1": R1}
 
 
 def time_cpu_baseline(workload, reps):
-    """The CPU port of the reference operators on the host cores."""
+    """The CPU port of the reference operators on the host cores.  Returns
+    ``(tok/s, seconds per step, threads, setup state, last output)``."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     state = workload.cpu_setup()
-    workload.cpu_step(state)
+    out = workload.cpu_step(state)          # warm-up: tables built, pages touched
     t0 = time.perf_counter()
     for _ in range(reps):
-        workload.cpu_step(state)
+        out = workload.cpu_step(state)
     dt = (time.perf_counter() - t0) / reps
-    return workload.cpu_tokens / dt, dt, cores
+    return workload.cpu_tokens / dt, dt, cores, state, out
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
     wl = WORKLOADS[args.workload]
-    reps = max(1, min(args.steps, 5))
-    value, dt, cores = time_cpu_baseline(wl, reps)
+    reps = max(1, min(args.steps, 3))
+    value, dt, cores, _, _ = time_cpu_baseline(wl, reps)
     sample = f"{reps} {wl.cpu_sample} after 1 warm-up"
     print(json.dumps({
         "impl": "reference", "metric": "tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": reps,
@@ -606,6 +872,49 @@ def run_reference(args, rank):
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
+
+
+def timed_roofline(wl, peaks, reps, device_index):
+    """The dominant kernel alone over ``reps`` launches, with the SM clock sampled meanwhile."""
+    with ClockSampler(device_index) as clocks:
+        secs, roof = wl.roofline(peaks, reps)
+    mhz = clocks.summary()["sm_mhz"]
+    roof.update({"launches_timed": reps, "us_per_launch": secs * 1e6, "sm_mhz_median": mhz,
+                 "us_x_mhz": None if mhz is None else secs * 1e6 * mhz})
+    return roof
+
+
+def library_leg(wl, kind=None):
+    """``wl.gpu_reference()`` if the workload has one; its best figure becomes the measured FP8 / FP4 peak."""
+    if not hasattr(wl, "gpu_reference"):
+        return None
+    ref = wl.gpu_reference()
+    if kind and ref.get("best_library_tflops"):
+        MEASURED_LIBRARY[kind] = ref["best_library_tflops"]
+    return ref
+
+
+LIBRARY_KIND = {"c2": "fp8", "c2s": "fp8", "c4": "fp4"}
+
+
+def run_secondary(name, dev, rank, peaks, steps, device_index):
+    """A further workload measured after the main region: device-timed throughput, its dominant kernel's
+    roofline and its library baseline."""
+    wl = WORKLOADS[name](dev, rank)
+    for i in range(3):
+        wl.step(i)
+    elapsed = time_region(wl.step, steps, torch.cuda.synchronize)
+    ref = library_leg(wl, LIBRARY_KIND.get(name))
+    entry = {"workload": wl.description, "name": name, "metric": "tok/s", "value": wl.tokens * steps / elapsed,
+             "ms_per_step": elapsed / steps * 1e3, "steps": steps, "dtype": wl.dtype,
+             "gpu_launches": wl.launches_per_step * steps,
+             "roofline": timed_roofline(wl, peaks, 200, device_index)}
+    if ref is not None:
+        entry["gpu_reference"] = ref
+    wl.vb.ops.gemm_status()
+    del wl
+    torch.cuda.empty_cache()
+    return entry
 
 
 def run_ours(args, rank, world, local_rank):
@@ -623,7 +932,8 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    wl = WORKLOADS[args.workload](dev, rank)
+    tensor_parallel = world > 1 and args.workload == "c2" and not args.replicas
+    wl = C2TP(dev, rank, world) if tensor_parallel else WORKLOADS[args.workload](dev, rank)
     warmup = max(args.warmup, 3)
     for i in range(warmup):
         wl.step(i)
@@ -639,22 +949,37 @@ def run_ours(args, rank, world, local_rank):
     e2e_elapsed = time_region(wl.e2e_step, args.steps, barrier, wl.pipeline.finish)
 
     peaks = measured_peaks()
-    kernel_s, roof = wl.roofline(peaks, max(12, min(args.steps, 50)))
+    reference = library_leg(wl, LIBRARY_KIND.get(args.workload)) if rank == 0 else None
+    roof = timed_roofline(wl, peaks, 200, local_rank)
+    collectives = wl.collective_share(min(args.steps, 50)) if tensor_parallel else None
+    replicas_elapsed = 0.0
+    if tensor_parallel:
+        # the same layer as N independent replicas (one full 2048-token batch per GPU, no exchange)
+        del wl.graphs, wl.pipeline
+        rep = C2(dev, rank)
+        for i in range(3):
+            rep.step(i)
+        replicas_elapsed = time_region(rep.step, args.steps, barrier)
+        del rep
+        torch.cuda.empty_cache()
 
-    times = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=dev)
+    times = torch.tensor([elapsed, e2e_elapsed, replicas_elapsed], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed, e2e_elapsed = times.tolist()
+    elapsed, e2e_elapsed, replicas_elapsed = times.tolist()
 
+    failed = False
     if rank == 0:
-        tokens_total = wl.tokens * args.steps * world
+        tokens_total = wl.tokens * args.steps * (1 if tensor_parallel else world)
         line = {
             "metric": "tok/s", "value": tokens_total / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-            "warmup": warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong" if tensor_parallel else "weak",
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
             "config": {"workload": wl.description,
+                       "parallelism": f"tp{world}" if tensor_parallel else (f"{world} replicas" if world > 1 else "1 GPU"),
                        "l2": f"{wl.n_sets} rotating input sets; tensors touched per step exceed the 126 MB L2",
-                       "launch": "CUDA graph replay per step",
+                       "launch": getattr(wl, "launch", "CUDA graph replay per step"),
                        "e2e": "pinned host input copied in, graph replayed, result copied out to pinned host memory "
                               "every step; copies on their own streams overlap neighbouring steps' compute"},
             "e2e": {"value": tokens_total / e2e_elapsed, "unit": "tok/s", "h2d_bytes_per_step": wl.h2d_bytes,
@@ -663,13 +988,35 @@ def run_ours(args, rank, world, local_rank):
             "roofline": roof,
             "clocks": clocks.summary(),
         }
+        if reference is not None:
+            line["gpu_reference"] = reference
+        if tensor_parallel:
+            line["collectives"] = collectives
+            line["replicas"] = {"value": wl.tokens * args.steps * world / replicas_elapsed, "unit": "tok/s",
+                                "scaling": "weak", "ms_per_step": replicas_elapsed / args.steps * 1e3,
+                                "what": "the same layer as independent replicas, one 2048-token batch per GPU, no exchange"}
+        checks = dict(wl.self_check()) if hasattr(wl, "self_check") else {}
         if world == 1:
-            value, dt, cores = time_cpu_baseline(WORKLOADS[args.workload], 3)
+            reps = 2 if wl.cpu_tokens >= 2048 and args.workload.startswith("c2") else 3
+            value, dt, cores, state, cpu_out = time_cpu_baseline(WORKLOADS[args.workload], reps)
             line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port",
-                                    "sample": f"3 {wl.cpu_sample} after 1 warm-up"}
+                                    "sample": f"{reps} {wl.cpu_sample} after 1 warm-up"}
+            checks.update(wl.gpu_check(state, cpu_out))
+            del state, cpu_out
+        line["self_check"] = {"max_rel": max((v for v, _ in checks.values()), default=None),
+                              "ok": all(v <= tol for v, tol in checks.values()),
+                              "checks": {k: {"value": v, "tolerance": tol} for k, (v, tol) in checks.items()}}
+        failed = not line["self_check"]["ok"]
+        wl.vb.ops.gemm_status()
+        if world == 1 and args.workload == "c2" and not args.no_secondary:
+            del wl
+            torch.cuda.empty_cache()
+            line["secondary"] = [run_secondary(name, dev, rank, peaks, 50, local_rank) for name in ("q1", "c1", "c4")]
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit("self_check failed: the benchmarked path disagrees with its reference beyond the tolerance")
 
 
 def main():
@@ -679,6 +1026,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--replicas", action="store_true",
+                    help="with N > 1 GPUs run N independent replicas instead of one tensor-parallel layer")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the q1 / c1 / c4 measurements that follow the default workload's line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

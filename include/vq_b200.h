@@ -193,6 +193,19 @@ int vq_dequantize_mx(const void* in, const void* scale, const void* code, int32_
  * be zeroed by the caller; NaN inputs give NaN. */
 int vq_amax(const void* in, int dtype, int64_t n, float* out, void* stream);
 
+/* One step of the delayed-scaling observer, FusedAmaxObsFakeQuantize._update_amax_scale
+ * (quantization/fake_quantize.py:406-437), on device state.  ring: [length, channels] of
+ * `dtype`, the last `length` absolute maxima per channel in ring order; position: [channels]
+ * int32, where each channel writes next (start both zeroed); scale: [channels] of `dtype`
+ * (start at 1).  The call sets scale from the ring as it stood before this tensor
+ * (max / quant_max in `dtype`; unchanged while that max is 0, infinite or NaN; rounded up to a
+ * power of two when power_of_two != 0), then stores this tensor's amax (one value of
+ * amax_dtype shared by all channels when amax_count == 1, else one per channel) and advances
+ * the ring.  No host state: the call can be captured in a CUDA graph. */
+int vq_amax_history_update(void* ring, int dtype, int64_t length, int64_t channels, int32_t* position,
+                           const void* amax, int amax_dtype, int64_t amax_count, float quant_max,
+                           int power_of_two, void* scale, void* stream);
+
 /* hadamard_rotate -- ops/quantized.py:1038-1067: each run of 16 elements along the
  * middle axis of a dense [O, A, I] tensor is multiplied by the float32 16x16
  * `matrix` (device, row-major; out_j = sum_k in_k * matrix[k][j]) in fp32; A is
@@ -282,6 +295,12 @@ int vq_gemm_tn(const void* A, const void* B, void* C, int in_kind, int out_dtype
  * -- gate/up linears, SiLU, product and the FP8 cast of the next linear's input
  * (backend/gpu/fp8.py:253-261) in one kernel, with every bfloat16 rounding of the
  * unfused sequence.  out_dtype must be VQ_BF16, N a multiple of 64, no bias or residual.
+ * round_acc != 0 rounds the float32 accumulator to out_dtype before alpha, alpha_cols and
+ * the bias are applied: the two roundings of a converted per-tensor graph, which runs
+ * `aten.linear` / `aten.matmul` on the codes (one rounding to the tensor dtype) and then
+ * `dequantize` by s_a * s_w (a second one; quantization/quantize_pt2e.py:563-626).  With
+ * round_acc == 0 the product is rounded once, as fp8_linear's scaled GEMM does
+ * (backend/gpu/fp8.py:372-400).
  * epi == NULL is vq_gemm_tn. */
 typedef struct VqGemmEpilogue {
   const void* alpha_cols;
@@ -292,6 +311,7 @@ typedef struct VqGemmEpilogue {
   int64_t causal_period;
   const void* gate_scale;
   int32_t gate_scale_dtype;
+  int32_t round_acc;
 } VqGemmEpilogue;
 int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dtype, int64_t M, int64_t N,
                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch, int64_t strideA,
@@ -331,6 +351,9 @@ int vq_softmax_quantize_fp8(const void* scores, void* out, int64_t rows, int64_t
  *   scores = bf16(q8 k8^T * alpha_qk); s = bf16(scores * score_scale), keys > query masked
  *   p8 = e4m3(bf16(bf16(softmax_fp32(s)) / p_scale))
  *   ctx = bf16(p8 v8 * alpha_pv); out8 = e4m3(bf16(ctx / ctx_scale))
+ * With round_acc != 0 both products are first rounded to bfloat16 and then scaled,
+ * scores = bf16(bf16(q8 k8^T) * alpha_qk) and ctx = bf16(bf16(p8 v8) * alpha_pv): the
+ * matmul-then-dequantize pair of a converted graph (see VqGemmEpilogue.round_acc).
  * q8: e4m3 [kv_heads, groups * T, 128], the query heads of a KV group stacked
  * along the rows; k8: e4m3 [kv_heads, T, 128]; vt8: e4m3 [kv_heads, 128, T].
  * out8 (or NULL): e4m3 [T, ld8], head h = kv * groups + g at columns [128 h, +128);
@@ -342,7 +365,7 @@ int vq_attention_fp8(const void* q8, const void* k8, const void* vt8, void* out8
                      int64_t T, int64_t kv_heads, int64_t groups, int64_t head_dim, const void* alpha_qk,
                      int alpha_qk_dtype, float score_scale, const void* p_scale, int p_scale_dtype,
                      const void* alpha_pv, int alpha_pv_dtype, const void* ctx_scale, int ctx_scale_dtype,
-                     void* stream);
+                     int round_acc, void* stream);
 int vq_attention_status(int reset);
 
 /* RMSNorm's backward of a training step: the input gradient (plus the residual stream's) and

@@ -21,9 +21,13 @@ from . import quantizers as OQ
 from . import tables as OT
 
 
-def fp8_decoder_layer(x, params, scales, shape, rope, mask):
+def fp8_decoder_layer(x, params, scales, shape, rope, mask, record=None):
     """x: [T, hidden] bfloat16 on the CPU.  ``scales``: bfloat16 0-d tensors keyed
-    'h','q','k','v','p','ctx','h2','act' and 'w_<linear>'.  ``rope`` = (cos, sin)."""
+    'h','q','k','v','p','ctx','h2','act' and 'w_<linear>'.  ``rope`` = (cos, sin).
+    ``record(name, tensor)`` sees the graph's intermediate tensors (codes are bfloat16-valued):
+    'h8', 'q_lin'/'k_lin'/'v_lin' [T, heads, d], 'q8' [heads, T, d], 'k8' [kv, T, d], 'v8' [kv, d, T],
+    'ctx' [T, heads * d], 'ctx8', 'x1', 'h28', 'act8'."""
+    rec = record or (lambda name, t: None)
     e4m3 = OT.quantization_map("fp8_e4m3")
     ident = OT.quantization_map(None)
     T = x.shape[0]
@@ -44,12 +48,15 @@ def fp8_decoder_layer(x, params, scales, shape, rope, mask):
         return t * cos[:, None, :] + rot * sin[:, None, :]
 
     h = quant(F.rms_norm(x, (shape.hidden,), params["ln1"], shape.eps), "h")
+    rec("h8", h)
     q = qlinear(h, "h", "q").view(T, shape.heads, shape.head_dim)
     k = qlinear(h, "h", "k").view(T, shape.kv_heads, shape.head_dim)
     v = qlinear(h, "h", "v").view(T, shape.kv_heads, shape.head_dim)
+    rec("q_lin", q), rec("k_lin", k), rec("v_lin", v)
     q, k = rope_apply(q), rope_apply(k)
     g = shape.heads // shape.kv_heads
     qh = quant(q.transpose(0, 1), "q")                                # [heads, T, d]
+    rec("q8", qh), rec("k8", quant(k.transpose(0, 1), "k")), rec("v8", quant(v.permute(1, 2, 0), "v"))
     kt = quant(k.repeat_interleave(g, 1).permute(1, 2, 0), "k")       # [heads, d, T]
     vh = quant(v.repeat_interleave(g, 1).transpose(0, 1), "v")        # [heads, T, d]
     scores = OQ.dequantize(torch.matmul(qh, kt), scales["q"] * scales["k"], None, None, None, None, ident)
@@ -57,7 +64,12 @@ def fp8_decoder_layer(x, params, scales, shape, rope, mask):
     p = quant(torch.softmax(scores.float(), -1).to(x.dtype), "p")
     ctx = OQ.dequantize(torch.matmul(p, vh), scales["p"] * scales["v"], None, None, None, None, ident)
     ctx = ctx.transpose(0, 1).reshape(T, shape.heads * shape.head_dim)
-    x1 = x + qlinear(quant(ctx, "ctx"), "ctx", "o")
+    ctx8 = quant(ctx, "ctx")
+    rec("ctx", ctx), rec("ctx8", ctx8)
+    x1 = x + qlinear(ctx8, "ctx", "o")
     h2 = quant(F.rms_norm(x1, (shape.hidden,), params["ln2"], shape.eps), "h2")
+    rec("x1", x1), rec("h28", h2)
     act = F.silu(qlinear(h2, "h2", "gate")) * qlinear(h2, "h2", "up")
-    return x1 + qlinear(quant(act, "act"), "act", "down")
+    act8 = quant(act, "act")
+    rec("act8", act8)
+    return x1 + qlinear(act8, "act", "down")

@@ -123,3 +123,23 @@ def test_gptq_layer_parallel_bfloat16_weights():
     want = OG.compensate_weight(w.float(), x.T @ x, 256, OT.quantization_map("int4"), OT.quantization_map("fp8_e5m3"),
                                 7.0, 32, 0.01, False, True, False)
     assert torch.equal(out0[0], want.bfloat16())
+
+
+def test_fp8_layer_shards_tile_the_layer():
+    """Every weight element of a decoder layer belongs to exactly one rank's slice, heads stay whole, and the
+    gate/up slices keep whole 32-row runs (the SwiGLU epilogue's interleave)."""
+    import voyager_b200
+
+    W, P = voyager_b200.workloads, voyager_b200.parallel
+    shape = W.LlamaShape(hidden=256, heads=8, kv_heads=4, head_dim=32, intermediate=512, vocab=64)
+    params = W.make_layer_params(1, shape)
+    for world in (1, 2, 4):
+        shards = [P.shard_fp8_layer(params, shape, r, world) for r in range(world)]
+        assert all(h == (8 // world, 4 // world) for _, h in shards)
+        for name in ("q", "k", "v", "gate", "up"):
+            assert torch.equal(torch.cat([s[name] for s, _ in shards], 0), params[name])
+        for name in ("o", "down"):
+            assert torch.equal(torch.cat([s[name] for s, _ in shards], 1), params[name])
+        assert all(s["gate"].shape[0] % 32 == 0 for s, _ in shards)
+    with pytest.raises(ValueError):
+        P.shard_fp8_layer(params, shape, 0, 8)          # more ranks than KV heads

@@ -77,3 +77,41 @@ def single_process_reference(scheme):
     x, gate, up, down, spec = problem(scheme)
     mlp = P.TensorParallelMLP(gate, up, down, spec, spec, ops=oracle_ops())
     return mlp(x)
+
+
+def fp8_layer_problem(seed=3):
+    import voyager_b200
+
+    W = voyager_b200.workloads
+    shape = W.LlamaShape(hidden=512, heads=8, kv_heads=4, head_dim=128, intermediate=1024, vocab=1024)
+    tokens = 256
+    params = W.make_layer_params(seed, shape)
+    x = W.make_hidden_states(seed + 1, tokens, shape)
+    scales = W.calibrate_fp8_scales(x, params, shape)
+    return shape, tokens, params, x, scales
+
+
+def run_rank_fp8_layer(rank, world, port, results):
+    """The tensor- and sequence-parallel FP8 decoder layer on ``world`` GPUs; rank 0 gathers the output rows."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        import voyager_b200
+
+        P = voyager_b200.parallel
+        dev = f"cuda:{rank}"
+        shape, tokens, params, x, scales = fp8_layer_problem()
+        layer = P.Fp8DecoderLayerTP({k: v.to(dev) for k, v in params.items()}, {k: v.to(dev) for k, v in scales.items()},
+                                    shape)
+        lo, hi = P.shard_bounds(tokens, rank, world)
+        rows = layer(x[lo:hi].to(dev))
+        out = P.all_gather_rows(rows)
+        voyager_b200.ops.gemm_status()
+        assert voyager_b200.fp8.attention_status() == 0
+        if rank == 0:
+            results["out"] = out.cpu()
+    finally:
+        dist.destroy_process_group()

@@ -72,6 +72,7 @@ class VqGemmEpilogue(ctypes.Structure):
         ("residual", ctypes.c_void_p), ("ldr", ctypes.c_int64), ("strideR", ctypes.c_int64),
         ("causal_mode", ctypes.c_int32), ("causal_period", ctypes.c_int64),
         ("gate_scale", ctypes.c_void_p), ("gate_scale_dtype", ctypes.c_int32),
+        ("round_acc", ctypes.c_int32),
     ]
 
 
@@ -104,6 +105,7 @@ SIGNATURES = {
                            ctypes.POINTER(VqRound), _P],
     "vq_dequantize_mx": [_P, _P, _P, ctypes.c_int32, _P, _I, _P, _I, ctypes.POINTER(VqBroadcast), _P],
     "vq_amax": [_P, _I, _I64, _P, _P],
+    "vq_amax_history_update": [_P, _I, _I64, _I64, _P, _P, _I, _I64, _F, _I, _P, _P],
     "vq_pack_codes": [_P, _I, _P, _I, _I64, _P],
     "vq_outlier_count": [_P, _I, _P, _I64, _I64, _F, _P],
     "vq_outlier_fill": [_P, _I, _P, _P, _P, _P, _I64, _I64, _I64, _F, _I64, _P],
@@ -125,7 +127,7 @@ SIGNATURES = {
     "vq_hadamard_rotate": [_P, _P, _I, _P, _I64, _I64, _I64, _P],
     "vq_quantize_fp8": [_P, _P, _I, _P, _I, _I64, _I64, _P],
     "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],
-    "vq_attention_fp8": [_P, _P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _F, _P, _I, _P, _I, _P, _I, _P],
+    "vq_attention_fp8": [_P, _P, _P, _P, _I64, _P, _I64, _I64, _I64, _I64, _P, _I, _F, _P, _I, _P, _I, _P, _I, _I, _P],
     "vq_attention_status": [_I],
     "vq_rmsnorm_backward_programs": [_I64, _I64],
     "vq_rmsnorm_backward": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _P],

@@ -65,6 +65,7 @@ struct AttnParams {
   uint8_t* out8;           // [T, ld8] e4m3, head h at columns [h * 128, +128), or null
   int64_t ld8;
   __nv_bfloat16* out16;    // [kv_heads, groups * T, 128], or null
+  int round_acc;           // both products are rounded to bfloat16 before their scale is applied
 };
 
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
@@ -93,11 +94,17 @@ constexpr float kLog2e = 1.4426950408889634f;
 // In the diagonal block, column c of the block is masked for row r when c > r.
 template <bool DIAG>
 __device__ __forceinline__ void scores_of_chunk(const uint32_t (&v)[32], float2 (&s)[16], float alpha, float scale,
-                                                int col0, int r) {
+                                                int col0, int r, bool round_acc) {
   const float2 a2 = make_float2(alpha, alpha), s2 = make_float2(scale, scale);
 #pragma unroll
+  for (int i = 0; i < 16; ++i) s[i] = make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+  if (round_acc) {   // bf16(q8 k8^T) first: the matmul's own rounding (warp-uniform)
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s[i] = round2(s[i]);
+  }
+#pragma unroll
   for (int i = 0; i < 16; ++i) {
-    float2 x = make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+    float2 x = s[i];
     x = round2(__fmul2_rn(x, a2));
     x = round2(__fmul2_rn(x, s2));
     if (DIAG) {
@@ -111,9 +118,9 @@ __device__ __forceinline__ void scores_of_chunk(const uint32_t (&v)[32], float2 
 // Pass A on one chunk: the running maximum m and the sum l of exp(s - m) take in 32 more columns.
 template <bool DIAG>
 __device__ __forceinline__ void accumulate_chunk(const uint32_t (&v)[32], float alpha, float scale, int col0, int r,
-                                                 float& m, float& l) {
+                                                 float& m, float& l, bool round_acc) {
   float2 s[16];
-  scores_of_chunk<DIAG>(v, s, alpha, scale, col0, r);
+  scores_of_chunk<DIAG>(v, s, alpha, scale, col0, r, round_acc);
   float cmax = m;
 #pragma unroll
   for (int i = 0; i < 16; ++i) cmax = max3(cmax, s[i].x, s[i].y);
@@ -134,9 +141,9 @@ __device__ __forceinline__ void accumulate_chunk(const uint32_t (&v)[32], float 
 // both quotients as products with the correctly rounded reciprocal; p >= 0, so no -0 can arise.
 template <bool DIAG>
 __device__ __forceinline__ void codes_of_chunk(const uint32_t (&v)[32], uint32_t (&codes)[8], float alpha, float scale,
-                                               int col0, int r, float shift, float rl, float rsp) {
+                                               int col0, int r, float shift, float rl, float rsp, bool round_acc) {
   float2 s[16];
-  scores_of_chunk<DIAG>(v, s, alpha, scale, col0, r);
+  scores_of_chunk<DIAG>(v, s, alpha, scale, col0, r, round_acc);
   const float2 log2e2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(shift, shift);
   const float2 rl2 = make_float2(rl, rl), rsp2 = make_float2(rsp, rsp);
 #pragma unroll
@@ -300,6 +307,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int r = quarter * 32 + lane;             // this thread's query row within the block
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const float alpha = loadp(p.alpha_qk, 0, p.alpha_qk_dt);
+    const bool round_acc = p.round_acc != 0;
     uint32_t s_uses = 0, p_uses = 0;               // tiles taken from S[w], tiles written to P[w]
     bool ok = true;
     uint32_t v[32];
@@ -324,8 +332,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           __syncwarp();
           if (lane == 0) mbar_arrive(&s_empty[w]);
         }
-        if (diag) accumulate_chunk<true>(v, alpha, p.score_scale, col0, r, m, l);
-        else accumulate_chunk<false>(v, alpha, p.score_scale, col0, r, m, l);
+        if (diag) accumulate_chunk<true>(v, alpha, p.score_scale, col0, r, m, l, round_acc);
+        else accumulate_chunk<false>(v, alpha, p.score_scale, col0, r, m, l, round_acc);
       }
       if (live == 0) {
         tc_fence_before_sync();
@@ -373,8 +381,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[w]);
           }
-          if (diag) codes_of_chunk<true>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp);
-          else codes_of_chunk<false>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp);
+          if (diag) codes_of_chunk<true>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp, round_acc);
+          else codes_of_chunk<false>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp, round_acc);
         }
         const int chunk16 = 2 * (AT_CPT * part + c);
         *reinterpret_cast<uint4*>(p_row + ((chunk16 ^ (r & 7)) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
@@ -404,11 +412,13 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         uint32_t v[32];
         tmem_ld_32x32(lane_addr + AT_O_COL + (uint32_t)col0, v);
         tmem_ld_wait();
-        uint32_t words[16];   // ctx = bf16(acc * alpha_pv), two per word
+        uint32_t words[16];   // ctx = bf16(acc * alpha_pv), or bf16(bf16(acc) * alpha_pv), two per word
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          words[i] = pack2(__fmul2_rn(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])),
-                                      make_float2(alpha_pv, alpha_pv)));
+        for (int i = 0; i < 16; ++i) {
+          float2 acc = make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+          if (p.round_acc) acc = round2(acc);
+          words[i] = pack2(__fmul2_rn(acc, make_float2(alpha_pv, alpha_pv)));
+        }
         if (p.out16 != nullptr) {
           uint4* dst = reinterpret_cast<uint4*>(p.out16 + ((int64_t)kvh * p.groups * p.T + qrow0 + r) * AT_BLK + col0);
 #pragma unroll
@@ -480,7 +490,7 @@ extern "C" int vq_attention_fp8(const void* q8, const void* k8, const void* vt8,
                                 int64_t T, int64_t kv_heads, int64_t groups, int64_t head_dim, const void* alpha_qk,
                                 int alpha_qk_dtype, float score_scale, const void* p_scale, int p_scale_dtype,
                                 const void* alpha_pv, int alpha_pv_dtype, const void* ctx_scale, int ctx_scale_dtype,
-                                void* stream) {
+                                int round_acc, void* stream) {
   VQ_REQUIRE(T >= 0 && kv_heads >= 0 && groups >= 0, "vq_attention_fp8: negative extent");
   if (T == 0 || kv_heads == 0 || groups == 0) return VQ_OK;
   if (head_dim != AT_BLK || T % AT_BLK != 0)
@@ -517,6 +527,7 @@ extern "C" int vq_attention_fp8(const void* q8, const void* k8, const void* vt8,
   p.out8 = static_cast<uint8_t*>(out8);
   p.ld8 = ld8;
   p.out16 = static_cast<__nv_bfloat16*>(out16);
+  p.round_acc = round_acc != 0;
   static unsigned long long configured = 0;
   if (first_call_on_device(&configured)) {
     cudaError_t e = cudaFuncSetAttribute(attention_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

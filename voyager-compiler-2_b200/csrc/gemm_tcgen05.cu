@@ -68,6 +68,7 @@ struct GemmParams {
   const void* gate_scale;   // gated mode (SwiGLU): per-tensor scale of the e4m3 output, or null
   int gate_scale_dt;
   int out_dt;
+  int round_acc;            // round the accumulator to out_dt before alpha / alpha_cols / bias
   uint32_t idesc;
   int kind_f8;
 };
@@ -89,10 +90,24 @@ __device__ __forceinline__ void scale_chunk(const GemmParams& p, const uint32_t 
   if (p.alpha_cols != nullptr && col0 + lane < p.N) col_factor = load_param(p.alpha_cols, col0 + lane, p.alpha_cols_dt);
   if (p.bias != nullptr && col0 + lane < p.N) col_bias = load_param(p.bias, col0 + lane, p.bias_dt);
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float x = __uint_as_float(v[j]);
-    if (has_alpha) x = __fmul_rn(x, alpha);
-    f[j] = x;
+  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+  if (p.round_acc) {   // the matmul's own rounding, before the dequantize's scale
+    if (p.out_dt == VQ_BF16) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(f[j], f[j + 1]);
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(&h);
+        f[j] = __uint_as_float(w << 16);
+        f[j + 1] = __uint_as_float(w & 0xFFFF0000u);
+      }
+    } else if (p.out_dt == VQ_F16) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = __half2float(__float2half_rn(f[j]));
+    }
+  }
+  if (has_alpha) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(f[j], alpha);
   }
   if (p.alpha_cols != nullptr) {
 #pragma unroll
@@ -1125,6 +1140,7 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
       VQ_REQUIRE(epi->gate_scale_dtype >= VQ_BF16 && epi->gate_scale_dtype <= VQ_F32, "vq_gemm_tn_ex: bad gate scale dtype");
       p.gate_scale = epi->gate_scale; p.gate_scale_dt = epi->gate_scale_dtype;
     }
+    p.round_acc = epi->round_acc != 0;
     if (epi->causal_mode != 0) {
       VQ_REQUIRE((epi->causal_mode == 1 || epi->causal_mode == 2) && epi->causal_period > 0 &&
                  epi->causal_period < (1ll << 31), "vq_gemm_tn_ex: causal_mode is 0, 1 or 2 and needs a positive period");

@@ -61,12 +61,13 @@ def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torc
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, alpha: Optional[torch.Tensor] = None,
              bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, dtype: str = "fp8_e4m3",
              alpha_cols: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-             causal=None, gated_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+             causal=None, gated_scale: Optional[torch.Tensor] = None, round_acc: bool = False) -> torch.Tensor:
     """``alpha * alpha_cols[n] * (a @ b^T) + bias`` (+ ``residual`` after the rounding) for FP8 byte
     operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation;
-    ``causal`` and ``gated_scale`` as for ``ops.gemm_tn``."""
+    ``causal``, ``gated_scale`` and ``round_acc`` as for ``ops.gemm_tn``."""
     return gemm_tn(a, b, out_dtype=out_dtype, alpha=alpha, bias=bias, in_kind=_FORMATS[dtype],
-                   alpha_cols=alpha_cols, residual=residual, causal=causal, gated_scale=gated_scale)
+                   alpha_cols=alpha_cols, residual=residual, causal=causal, gated_scale=gated_scale,
+                   round_acc=round_acc)
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, chunk: int = 32) -> torch.Tensor:
@@ -147,14 +148,16 @@ def softmax_quantize_fp8(scores: torch.Tensor, score_scale: float, out_scale: to
 
 @N.device_guarded
 def attention_fp8(q8: torch.Tensor, k8: torch.Tensor, vt8: torch.Tensor, alpha_qk: torch.Tensor, score_scale: float,
-                  p_scale: torch.Tensor, alpha_pv: torch.Tensor, ctx_scale: Optional[torch.Tensor] = None):
+                  p_scale: torch.Tensor, alpha_pv: torch.Tensor, ctx_scale: Optional[torch.Tensor] = None,
+                  round_acc: bool = False):
     """Causal attention on FP8 operands in one kernel: ``fp8_gemm(q8, k8, alpha_qk)``,
     ``softmax_quantize_fp8(.., score_scale, p_scale, causal_period=T)``, ``fp8_gemm(p8, vt8, alpha_pv)``
     and, with ``ctx_scale``, the cast of the context, with the same rounding steps.
     ``q8``: ``[kv_heads, groups * T, 128]`` (a KV group's query heads stacked along the rows),
     ``k8``: ``[kv_heads, T, 128]``, ``vt8``: ``[kv_heads, 128, T]``, all e4m3 codes.
     Returns the e4m3 context ``[T, heads * 128]`` when ``ctx_scale`` is given, else the
-    bfloat16 context ``[kv_heads, groups * T, 128]``."""
+    bfloat16 context ``[kv_heads, groups * T, 128]``.  ``round_acc``: both GEMMs as
+    ``fp8_gemm(..., round_acc=True)``."""
     kv, rows, d = q8.shape
     T = k8.shape[1]
     groups = rows // T
@@ -172,7 +175,8 @@ def attention_fp8(q8: torch.Tensor, k8: torch.Tensor, vt8: torch.Tensor, alpha_q
                                      _ptr(out16), T, kv, groups, d, scalars[0].data_ptr(), _dtype_id(scalars[0].dtype),
                                      float(score_scale), scalars[1].data_ptr(), _dtype_id(scalars[1].dtype),
                                      scalars[2].data_ptr(), _dtype_id(scalars[2].dtype), _ptr(ctx_scale),
-                                     _dtype_id(ctx_scale.dtype) if ctx_scale is not None else 0, _stream()),
+                                     _dtype_id(ctx_scale.dtype) if ctx_scale is not None else 0, int(bool(round_acc)),
+                                     _stream()),
             "vq_attention_fp8")
     return out8 if out8 is not None else out16
 

@@ -1,21 +1,28 @@
-"""Delayed-scaling fake-quantizer for the per-tensor and per-channel schemes on the CUDA kernels.
+"""Delayed-scaling fake-quantizer for the per-tensor and per-channel schemes, state on the device.
 
-Mirror of the reference's ``FusedAmaxObsFakeQuantize``
-(``src/voyager_compiler/quantization/fake_quantize.py:330-447``): same constructor
-arguments, buffers (``qmap``, ``scale``, ``amax_history``) and methods.  The module keeps
-the absolute maxima of the last ``amax_history_len`` inputs, one per tensor or one per
-channel along ``ch_axis``, and scales by the largest; an input is quantized before its own
-amax joins the history, so the first call uses scale 1.  History and scale take the dtype of
-the tensor quantized.  The amax of a whole tensor is one pass of ``vq_amax``; the
-fake-quantize is ``torch.ops.quantization.fake_quant``.
+The counterpart of the reference's ``FusedAmaxObsFakeQuantize``
+(``src/voyager_compiler/quantization/fake_quantize.py:330-447``): same class name, constructor
+arguments, switches and ``scale`` / ``qmap`` / ``amax_history`` buffers, so code that builds
+observers from a spec string finds the same interface.  What it computes: the module remembers
+the absolute maxima of the last ``amax_history_len`` tensors it saw (one per tensor, or one per
+channel along ``ch_axis``) and scales by the largest of them; a tensor is quantized with the
+scale of its predecessors, before its own maximum counts, so the first call uses scale 1.
+
+How it is kept here: ``amax_history`` is a ring ``[length, channels]`` with a device-side write
+position per channel, and one small kernel (``vq_amax_history_update``) takes the ring's
+maximum, derives the scale and stores the new amax.  A forward is three launches -- the tensor's
+amax (``vq_amax``), the ring update, the fake-quantize -- with no host read, so it can sit
+inside a captured CUDA graph.  (The reference rolls the whole history tensor every call; only the
+order of the rows differs, the set of remembered maxima and therefore every scale is the same.)
 """
 
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 
+from . import _native as N
 from .formats import QScheme, get_quantization_map
-from .ops import tensor_amax
+from .ops import _dtype_id, _stream, tensor_amax
 
 
 class FusedAmaxObsFakeQuantize(torch.nn.Module):
@@ -23,6 +30,8 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
                  ch_axis: Optional[int] = None, power_2_scale: bool = False, device=None, **unused) -> None:
         if qscheme not in (QScheme.PER_TENSOR_SYMMETRIC, QScheme.PER_CHANNEL_SYMMETRIC):
             raise ValueError(f"{qscheme} is not a per-tensor or per-channel scheme")
+        if amax_history_len < 1:
+            raise ValueError("amax_history_len must be at least 1")
         super().__init__()
         self.dtype = dtype
         self.qscheme, self.quant_max = qscheme, quant_max
@@ -31,11 +40,12 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
         self.register_buffer("qmap", get_quantization_map(dtype, device), persistent=False)
         self.register_buffer("scale", torch.tensor([1.0], dtype=torch.float, device=device))
         self.register_buffer("amax_history", torch.tensor([], dtype=torch.float, device=device))
+        self.register_buffer("ring_position", torch.zeros(0, dtype=torch.int32, device=device), persistent=False)
         self.register_buffer("fake_quant_enabled", torch.tensor([1], dtype=torch.uint8))
         self.register_buffer("observer_enabled", torch.tensor([1], dtype=torch.uint8))
+        # host copies of the two switches: forward never reads a device value
         self._observe, self._quantize = True, True
 
-    # the enable switches are host flags as well, so that forward never reads a device value
     def enable_observer(self, enabled: bool = True) -> None:
         self._observe = enabled
         self.observer_enabled[0] = int(enabled)
@@ -50,42 +60,43 @@ class FusedAmaxObsFakeQuantize(torch.nn.Module):
     def disable_fake_quant(self) -> None:
         self.enable_fake_quant(False)
 
-    def start_history(self, shape: Tuple[int, ...], dtype) -> None:
-        """Size the history and the scale as before any input (``fake_quantize.py:389-403``)."""
-        device = self.scale.device
-        self.amax_history = torch.zeros((self.amax_history_len, *shape), dtype=dtype, device=device)
-        self.scale = torch.ones(shape, dtype=dtype, device=device)
+    def _allocate(self, amax_shape, dtype, device) -> None:
+        """Empty ring, write positions at 0 and scale 1, shaped for the first tensor seen."""
+        self.amax_history = torch.zeros((self.amax_history_len, *amax_shape), dtype=dtype, device=device)
+        self.scale = torch.ones(tuple(amax_shape), dtype=dtype, device=device)
+        self.ring_position = torch.zeros(max(self.scale.numel(), 1), dtype=torch.int32, device=device)
+
+    def _tensor_amax(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.is_per_channel:
+            return tensor_amax(x)                                   # 0-d float32, one pass, no |x| temporary
+        axis = self.ch_axis % x.ndim
+        return x.abs().amax(dim=[i for i in range(x.ndim) if i != axis], keepdim=True)
 
     @torch.no_grad()
-    def _update_amax_scale(self, x: torch.Tensor) -> None:
-        """Recompute ``scale`` from the history, then fold ``x``'s amax into the history
-        (``fake_quantize.py:406-437``)."""
-        if self.is_per_channel:
-            ch_axis = self.ch_axis % x.ndim
-            dim = tuple(i for i in range(x.ndim) if i != ch_axis)
-            amax_cur = torch.amax(torch.abs(x), dim=dim, keepdim=True)
-        elif x.is_cuda:
-            amax_cur = tensor_amax(x).to(x.dtype)        # one pass, no |x| temporary
-        else:
-            amax_cur = torch.amax(torch.abs(x))
-        if self.amax_history.numel() == 0:
-            self.start_history(amax_cur.shape, x.dtype)
-        amax = torch.amax(self.amax_history, dim=0)
-        self.amax_history.copy_(torch.roll(self.amax_history, -1, 0))
-        self.amax_history[0] = amax_cur
-        sf = amax / self.quant_max
-        sf = torch.where(amax > 0.0, sf, self.scale)
-        sf = torch.where(torch.isfinite(amax), sf, self.scale)
-        if self.power_2_scale:
-            sf = torch.pow(2, torch.ceil(torch.log2(sf)))
-        self.scale.copy_(sf)
+    def observe(self, x: torch.Tensor) -> None:
+        """Derive ``scale`` from the maxima remembered so far, then remember ``x``'s."""
+        if not x.is_cuda:
+            raise NotImplementedError("the delayed-scaling observer runs on CUDA tensors; there is no CPU path")
+        now = self._tensor_amax(x)
+        if self.amax_history.numel() == 0 or self.amax_history.dtype != x.dtype:
+            self._allocate(now.shape, x.dtype, x.device)
+        channels = self.scale.numel()
+        N.check(N.lib().vq_amax_history_update(self.amax_history.data_ptr(), _dtype_id(x.dtype), self.amax_history_len,
+                                               channels, self.ring_position.data_ptr(), now.data_ptr(),
+                                               _dtype_id(now.dtype), now.numel(), float(self.quant_max),
+                                               int(self.power_2_scale), self.scale.data_ptr(), _stream()),
+                "vq_amax_history_update")
+
+    # the reference's name for the same step
+    _update_amax_scale = observe
 
     def calculate_qparams(self):
         return self.scale
 
+    @N.device_guarded
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self._observe:
-            self._update_amax_scale(x)
+            self.observe(x)
         if not self._quantize:
             return x
         return torch.ops.quantization.fake_quant(x, self.qmap, self.scale)

@@ -575,7 +575,7 @@ def _parse_layout(layout: str):
 
 @N.device_guarded
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None,
-            alpha_cols=None, residual=None, causal=None, gated_scale=None):
+            alpha_cols=None, residual=None, causal=None, gated_scale=None, round_acc=False):
     """``out[..., m, n] = alpha * sum_k a[..., m, k] * b[..., n, k] + bias[n]`` on the
     tensor cores (fp32 accumulation, one rounding to ``out_dtype``).
 
@@ -586,7 +586,9 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
     stay unwritten); ``causal=("probabilities", T)`` that ``a[..., r, k]`` is zero for
     ``k > r % T`` (the contraction may stop early).  ``gated_scale`` selects the SwiGLU epilogue:
     ``b``'s rows interleave 32 gate rows with their 32 up rows and the result is the ``[..., N / 2]``
-    e4m3 bytes of ``(silu(gate) * up) / gated_scale``.
+    e4m3 bytes of ``(silu(gate) * up) / gated_scale``.  ``round_acc`` rounds the accumulator to
+    ``out_dtype`` before ``alpha`` / ``alpha_cols`` / ``bias`` (matmul, then dequantize: the two
+    roundings of a converted per-tensor graph).
 
     ``a`` is ``[*batch, M, K]`` and ``b`` ``[*batch, N, K]`` or ``[N, K]``; both are
     used K-contiguous.  ``in_kind`` overrides the operand element kind for 8-bit
@@ -632,8 +634,9 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
     if bias is not None:
         bias = bias.contiguous()
     epi = None
-    if alpha_cols is not None or residual is not None or causal is not None or gated_scale is not None:
+    if alpha_cols is not None or residual is not None or causal is not None or gated_scale is not None or round_acc:
         epi = N.VqGemmEpilogue()
+        epi.round_acc = int(bool(round_acc))
         if gated_scale is not None:
             gated_scale = _as_scalar_param(gated_scale, a.device)
             epi.gate_scale, epi.gate_scale_dtype = gated_scale.data_ptr(), _dtype_id(gated_scale.dtype)

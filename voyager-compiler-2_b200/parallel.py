@@ -244,3 +244,131 @@ def gptq_layer_parallel(problems, solve, group=None):
         dist.broadcast(out, src=dist.get_global_rank(group, owner[i]) if group is not None else owner[i], group=group)
         results.append(out.to(weight.dtype))
     return results
+
+
+# ---------------------------------------------------------------------------
+# The per-tensor FP8 decoder layer, tensor- and sequence-parallel
+# ---------------------------------------------------------------------------
+def shard_fp8_layer(params, shape, rank: int, world: int):
+    """The slices of one decoder layer's weights that ``rank`` of ``world`` holds: q/k/v by whole heads
+    (rows), gate/up by rows, o and down by the matching input columns.  Returns ``(weights, heads)``
+    with ``heads = (query heads, kv heads)`` on this rank."""
+    if shape.kv_heads % world or shape.heads % world or shape.intermediate % (32 * world):
+        raise ValueError(f"{shape.heads}/{shape.kv_heads} heads and {shape.intermediate} hidden units do not split "
+                         f"over {world} ranks in whole heads and whole 32-row runs")
+    d = shape.head_dim
+    hq, hkv = shape.heads // world, shape.kv_heads // world
+    lo_q, lo_kv = rank * hq * d, rank * hkv * d
+    lo_i, hi_i = shard_bounds(shape.intermediate, rank, world, 32)
+    w = {"q": params["q"][lo_q:lo_q + hq * d], "k": params["k"][lo_kv:lo_kv + hkv * d],
+         "v": params["v"][lo_kv:lo_kv + hkv * d], "o": params["o"][:, lo_q:lo_q + hq * d],
+         "gate": params["gate"][lo_i:hi_i], "up": params["up"][lo_i:hi_i], "down": params["down"][:, lo_i:hi_i]}
+    return {k: v.contiguous() for k, v in w.items()}, (hq, hkv)
+
+
+class Fp8DecoderLayerTP:
+    """``workloads.Fp8DecoderLayer`` over the ranks of a process group.
+
+    Activations between the blocks are sharded by token rows (``[T / world, hidden]``); q/k/v and
+    gate/up are column-parallel (whole attention heads per rank: 4 query + 1 KV head at 8 ranks),
+    o_proj and down_proj row-parallel:
+
+        RMSNorm + FP8 cast on the rank's rows -> all-gather of the FP8 codes (1 byte per element)
+        -> merged QKV GEMM (this rank's heads) -> RoPE + casts -> fused attention over its heads
+        -> o_proj on its input columns, float32 partial sums -> reduce-scatter over token rows
+        -> round, scale, add the residual rows -> RMSNorm + FP8 cast -> all-gather of the codes
+        -> gate/up GEMM with the SwiGLU epilogue (its hidden units) -> down_proj partial sums
+        -> reduce-scatter -> round, scale, add the residual rows.
+
+    Per-tensor scales are those of the unsharded layer, so every FP8 code equals the single-GPU
+    one; the row-parallel sums differ from it in float32 summation order only.  The collectives are
+    NCCL's (``torch.distributed``); remote data always lands in this GPU's memory before a kernel
+    reads it.  ``collective_seconds`` accumulates CUDA-event time around them when ``timed`` is set.
+    """
+
+    def __init__(self, params, scales, shape, group=None, graph_rounding=True):
+        from . import fp8 as FP8
+
+        self.FP8, self.shape, self.group, self.scales = FP8, shape, group, scales
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.ra = bool(graph_rounding)
+        w, (self.hq, self.hkv) = shard_fp8_layer(params, shape, self.rank, self.world)
+        s = scales
+        self.ln1, self.ln2 = params["ln1"], params["ln2"]
+        w8 = {n: FP8.quantize_fp8(w[n], s["w_" + n]) for n in w}
+        alpha = {n: (s[src] * s["w_" + n]).reshape(()) for n, src in
+                 (("q", "h"), ("k", "h"), ("v", "h"), ("o", "ctx"), ("gate", "h2"), ("up", "h2"), ("down", "act"))}
+        self.w8_qkv = torch.cat([w8["q"], w8["k"], w8["v"]], 0)
+        self.alpha_qkv = torch.cat([alpha[n].float().expand(w8[n].shape[0]) for n in ("q", "k", "v")]).contiguous()
+        self.w8_swiglu = FP8.interleave_gate_up(w8["gate"], w8["up"])
+        rows = w8["gate"].shape[0]
+        self.alpha_swiglu = FP8.interleave_gate_up(alpha["gate"].float().expand(rows).contiguous(),
+                                                   alpha["up"].float().expand(rows).contiguous())
+        self.w8_o, self.w8_down = w8["o"], w8["down"]
+        self.alpha_o, self.alpha_down = alpha["o"], alpha["down"]
+        self.alpha_qk = (s["q"] * s["k"]).reshape(())
+        self.alpha_pv = (s["p"] * s["v"]).reshape(())
+        self._rope = None
+        self.timed = False
+        self.collective_events = []
+
+    # kernels of this package per forward: 2 norm+cast, 3 rope/transpose casts, attention, 4 GEMMs
+    LAUNCHES = 10
+    COLLECTIVES = 4
+
+    def _collective(self, fn, t):
+        if not self.timed:
+            return fn(t, self.group)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = fn(t, self.group)
+        stop.record()
+        self.collective_events.append((start, stop))
+        return out
+
+    def collective_seconds(self):
+        """Device time spent inside the collectives since ``timed`` was set (synchronises)."""
+        torch.cuda.synchronize()
+        total = sum(a.elapsed_time(b) for a, b in self.collective_events) * 1e-3
+        self.collective_events = []
+        return total
+
+    def _finish_row_parallel(self, partial, alpha, residual_rows):
+        """Reduce-scatter the float32 partial sums over token rows, then what the single-GPU epilogue
+        does: round the sum (the matmul's rounding), scale (the dequantize), add the residual rows."""
+        total = self._collective(reduce_scatter_rows, partial)
+        y = total.to(torch.bfloat16) * alpha if self.ra else (total * alpha.float()).to(torch.bfloat16)
+        return residual_rows + y
+
+    def forward(self, x_rows):
+        """``x_rows``: this rank's ``[T / world, hidden]`` rows.  Returns its rows of the layer output."""
+        import math
+
+        from .workloads import rope_tables
+
+        FP8, sh, s = self.FP8, self.shape, self.scales
+        T = x_rows.shape[0] * self.world
+        if self._rope is None or self._rope[0].shape[0] != T:
+            self._rope = rope_tables(T, sh, x_rows.device)
+        cos, sin = self._rope
+        d, hq, hkv = sh.head_dim, self.hq, self.hkv
+        h8 = self._collective(all_gather_rows, FP8.rmsnorm_quantize_fp8(x_rows, self.ln1, sh.eps, s["h"]))
+        qkv = FP8.fp8_gemm(h8, self.w8_qkv, alpha_cols=self.alpha_qkv, round_acc=self.ra)
+        q = qkv[:, :hq * d].unflatten(1, (hq, d))
+        k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
+        v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, d))
+        k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])
+        vt8 = FP8.transpose_quantize_fp8(v, s["v"])
+        q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(hkv, (hq // hkv) * T, d)
+        ctx8 = FP8.attention_fp8(q8, k8, vt8, self.alpha_qk, 1.0 / math.sqrt(d), s["p"], self.alpha_pv, s["ctx"],
+                                 round_acc=self.ra)                                   # [T, hq * d]
+        partial = FP8.fp8_gemm(ctx8, self.w8_o, out_dtype=torch.float32)              # [T, hidden], this rank's K
+        x1 = self._finish_row_parallel(partial, self.alpha_o, x_rows)
+        h28 = self._collective(all_gather_rows, FP8.rmsnorm_quantize_fp8(x1, self.ln2, sh.eps, s["h2"]))
+        act8 = FP8.fp8_gemm(h28, self.w8_swiglu, alpha_cols=self.alpha_swiglu, gated_scale=s["act"],
+                            round_acc=self.ra)                                        # [T, intermediate / world]
+        partial = FP8.fp8_gemm(act8, self.w8_down, out_dtype=torch.float32)
+        return self._finish_row_parallel(partial, self.alpha_down, x1)
+
+    __call__ = forward

@@ -137,8 +137,12 @@ class Fp8DecoderLayer:
     """FP8 per-tensor decoder layer on the CUDA kernels (prefill, batch 1)."""
 
     def __init__(self, params, scales, shape: LlamaShape, merge_qkv=True, merge_gate_up=True, fuse_residual=True,
-                 fuse_swiglu=True, fuse_attention=True):
+                 fuse_swiglu=True, fuse_attention=True, graph_rounding=True):
         self.shape = shape
+        # The converted graph rounds each matmul to bfloat16 and then multiplies by s_a * s_w in its
+        # dequantize (two roundings); ``graph_rounding`` keeps both inside the GEMM epilogues.  Without
+        # it every product is rounded once, as the reference's scaled-GEMM replacement does.
+        self.ra = bool(graph_rounding)
         self.merge_qkv, self.merge_gate_up, self.fuse_residual = merge_qkv, merge_gate_up, fuse_residual
         self.fuse_swiglu = fuse_swiglu
         # one kernel for Q K^T, softmax, P V and the cast of the context (head_dim 128)
@@ -187,10 +191,10 @@ class Fp8DecoderLayer:
         nq, nkv = sh.heads * sh.head_dim, sh.kv_heads * sh.head_dim
         h8 = FP8.rmsnorm_quantize_fp8(x, self.ln1, sh.eps, s["h"])
         if self.merge_qkv:
-            qkv = FP8.fp8_gemm(h8, self.w8_qkv, alpha_cols=self.alpha_qkv)  # [T, (heads + 2 kv) * d]
+            qkv = FP8.fp8_gemm(h8, self.w8_qkv, alpha_cols=self.alpha_qkv, round_acc=self.ra)  # [T, (heads + 2 kv) * d]
             q, k, v = qkv[:, :nq], qkv[:, nq:nq + nkv], qkv[:, nq + nkv:]
         else:
-            q, k, v = (FP8.fp8_gemm(h8, self.w8[n], self.alpha[n]) for n in ("q", "k", "v"))
+            q, k, v = (FP8.fp8_gemm(h8, self.w8[n], self.alpha[n], round_acc=self.ra) for n in ("q", "k", "v"))
         q = q.unflatten(1, (sh.heads, sh.head_dim))
         k = k.unflatten(1, (sh.kv_heads, sh.head_dim))
         v = v.unflatten(1, (sh.kv_heads, sh.head_dim))
@@ -211,13 +215,13 @@ class Fp8DecoderLayer:
         k.record_stream(self._side)
         if self.fuse_attention and T % 128 == 0:
             ctx8 = FP8.attention_fp8(q8, k8, vt8, self.alpha_qk, 1.0 / math.sqrt(sh.head_dim), s["p"], self.alpha_pv,
-                                     s["ctx"])                               # [T, heads*d]
+                                     s["ctx"], round_acc=self.ra)            # [T, heads*d]
             return self._after_attention(x, ctx8)
         # masked scores are neither computed nor read; masked probabilities are zero codes
-        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk, causal=("scores", T))  # [kv, groups*T, T]
+        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk, causal=("scores", T), round_acc=self.ra)  # [kv, groups*T, T]
         # scale, causal mask, softmax and the FP8 cast of the probabilities in one pass
         p8 = FP8.softmax_quantize_fp8(scores, 1.0 / math.sqrt(sh.head_dim), s["p"], causal_period=T)
-        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv, causal=("probabilities", T))   # [kv, groups*T, d]
+        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv, causal=("probabilities", T), round_acc=self.ra)   # [kv, groups*T, d]
         # the cast of the context undoes the head-major layout: [kv*groups, T, d] -> [T, heads*d]
         ctx8 = FP8.transpose_heads_quantize_fp8(ctx.view(sh.heads, T, sh.head_dim), s["ctx"])
         return self._after_attention(x, ctx8)
@@ -226,23 +230,24 @@ class Fp8DecoderLayer:
         """Output projection, residual, and the MLP block."""
         sh, s = self.shape, self.scales
         if self.fuse_residual:
-            x1 = FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"], residual=x)   # x + o_proj(ctx)
+            x1 = FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"], residual=x, round_acc=self.ra)   # x + o_proj(ctx)
         else:
-            x1 = x + FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"])
+            x1 = x + FP8.fp8_gemm(ctx8, self.w8["o"], self.alpha["o"], round_acc=self.ra)
         h28 = FP8.rmsnorm_quantize_fp8(x1, self.ln2, sh.eps, s["h2"])
         if self.fuse_swiglu and sh.intermediate % 32 == 0:
             # gate and up linears, SiLU, product and the cast of down_proj's input in one GEMM
-            act8 = FP8.fp8_gemm(h28, self.w8_swiglu, alpha_cols=self.alpha_swiglu, gated_scale=s["act"])
+            act8 = FP8.fp8_gemm(h28, self.w8_swiglu, alpha_cols=self.alpha_swiglu, gated_scale=s["act"],
+                                round_acc=self.ra)
         else:
             if self.merge_gate_up:
-                gu = FP8.fp8_gemm(h28, self.w8_gate_up, alpha_cols=self.alpha_gate_up)   # [T, 2 * intermediate]
+                gu = FP8.fp8_gemm(h28, self.w8_gate_up, alpha_cols=self.alpha_gate_up, round_acc=self.ra)   # [T, 2 * intermediate]
                 gate, up = gu[:, :sh.intermediate], gu[:, sh.intermediate:]
             else:
-                gate, up = (FP8.fp8_gemm(h28, self.w8[n], self.alpha[n]) for n in ("gate", "up"))
+                gate, up = (FP8.fp8_gemm(h28, self.w8[n], self.alpha[n], round_acc=self.ra) for n in ("gate", "up"))
             act8 = FP8.silu_mul_quantize_fp8(gate, up, s["act"])
         if self.fuse_residual:
-            return FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"], residual=x1)
-        return x1 + FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"])
+            return FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"], residual=x1, round_acc=self.ra)
+        return x1 + FP8.fp8_gemm(act8, self.w8["down"], self.alpha["down"], round_acc=self.ra)
 
     def forward_unfused(self, x):
         """The same layer with every producer run by torch and a plain cast after it."""
@@ -250,22 +255,22 @@ class Fp8DecoderLayer:
         T = x.shape[0]
         (cos, sin), mask = self._tables(T, x.device)
         h8 = FP8.quantize_fp8(F.rms_norm(x, (sh.hidden,), self.ln1, sh.eps), s["h"])
-        q = FP8.fp8_gemm(h8, self.w8["q"], self.alpha["q"]).view(T, sh.heads, sh.head_dim)
-        k = FP8.fp8_gemm(h8, self.w8["k"], self.alpha["k"]).view(T, sh.kv_heads, sh.head_dim)
-        v = FP8.fp8_gemm(h8, self.w8["v"], self.alpha["v"]).view(T, sh.kv_heads, sh.head_dim)
+        q = FP8.fp8_gemm(h8, self.w8["q"], self.alpha["q"], round_acc=self.ra).view(T, sh.heads, sh.head_dim)
+        k = FP8.fp8_gemm(h8, self.w8["k"], self.alpha["k"], round_acc=self.ra).view(T, sh.kv_heads, sh.head_dim)
+        v = FP8.fp8_gemm(h8, self.w8["v"], self.alpha["v"], round_acc=self.ra).view(T, sh.kv_heads, sh.head_dim)
         q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
         q8 = FP8.quantize_fp8(q.view(T, sh.kv_heads, sh.groups, sh.head_dim).permute(1, 2, 0, 3)
                               .reshape(sh.kv_heads, sh.groups * T, sh.head_dim), s["q"])
         k8 = FP8.quantize_fp8(k.transpose(0, 1), s["k"])                    # [kv, T, d]
         vt8 = FP8.quantize_fp8(v.permute(1, 2, 0), s["v"])                  # [kv, d, T]
-        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk)                        # [kv, groups*T, T]
+        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk, round_acc=self.ra)                        # [kv, groups*T, T]
         p8 = FP8.softmax_quantize_fp8(scores, 1.0 / math.sqrt(sh.head_dim), s["p"], causal_period=T)
-        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv)                          # [kv, groups*T, d]
+        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv, round_acc=self.ra)                          # [kv, groups*T, d]
         ctx = ctx.view(sh.kv_heads, sh.groups, T, sh.head_dim).permute(2, 0, 1, 3).reshape(T, sh.heads * sh.head_dim)
-        x1 = x + FP8.fp8_gemm(FP8.quantize_fp8(ctx, s["ctx"]), self.w8["o"], self.alpha["o"])
+        x1 = x + FP8.fp8_gemm(FP8.quantize_fp8(ctx, s["ctx"]), self.w8["o"], self.alpha["o"], round_acc=self.ra)
         h28 = FP8.quantize_fp8(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps), s["h2"])
-        act = F.silu(FP8.fp8_gemm(h28, self.w8["gate"], self.alpha["gate"])) * \
-            FP8.fp8_gemm(h28, self.w8["up"], self.alpha["up"])
-        return x1 + FP8.fp8_gemm(FP8.quantize_fp8(act, s["act"]), self.w8["down"], self.alpha["down"])
+        act = F.silu(FP8.fp8_gemm(h28, self.w8["gate"], self.alpha["gate"], round_acc=self.ra)) * \
+            FP8.fp8_gemm(h28, self.w8["up"], self.alpha["up"], round_acc=self.ra)
+        return x1 + FP8.fp8_gemm(FP8.quantize_fp8(act, s["act"]), self.w8["down"], self.alpha["down"], round_acc=self.ra)
 
     __call__ = forward
