@@ -806,6 +806,20 @@ class C2TP:
     def e2e_step(self, i):
         self.pipeline.step(i)
 
+    def self_check(self):
+        """This rank's output rows from one graph replay against the same rows of the unsharded layer run on
+        this GPU alone (same weights, scales and input)."""
+        W = self.vb.workloads
+        self.graphs[0][0].replay()
+        rows = self.graphs[0][1].clone()
+        params = W.make_layer_params(7, self.shape, rows.device)
+        single = W.Fp8DecoderLayer(params, self.layer.scales, self.shape)
+        del params
+        full = single(W.make_hidden_states(100, self.tokens, self.shape, rows.device))
+        n = rows.shape[0]
+        lo = self.layer.rank * n
+        return {"tensor_parallel_rows_vs_one_gpu_layer": (max_rel(rows, full[lo:lo + n]), 6e-2)}
+
     def collective_share(self, steps):
         """Share of an (uncaptured) step's device time spent inside the four collectives, from CUDA events
         around them; a collective's span includes waiting for the slowest rank."""

@@ -454,6 +454,15 @@ int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb
                   int64_t M, int64_t N, int64_t K, int64_t ldc, int64_t batch, int64_t strideC,
                   const void* alpha, int alpha_dtype, const void* bias, int bias_dtype, void* stream);
 
+/* vq_gemm_nvfp4 with one more factor per output column (device [N] of alpha_cols_dtype, may be
+ * NULL), applied after alpha: linears that read one packed activation but carry different
+ * weight global scales (q/k/v, gate/up of a decoder layer) run as one GEMM, column n scaled by
+ * its own linear's alpha (backend/gpu/nvfp4.py:1101-1152 applies one alpha per linear). */
+int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int out_dtype, int64_t M,
+                     int64_t N, int64_t K, int64_t ldc, int64_t batch, int64_t strideC, const void* alpha,
+                     int alpha_dtype, const void* bias, int bias_dtype, const void* alpha_cols, int alpha_cols_dtype,
+                     void* stream);
+
 /* Synchronising health check for the GEMM kernels: returns VQ_ETIMEOUT if any
  * launch since the last reset gave up on a bounded barrier wait (its output is
  * then invalid).  No counterpart in the reference. */

@@ -73,3 +73,49 @@ def fp8_decoder_layer(x, params, scales, shape, rope, mask, record=None):
     act8 = quant(act, "act")
     rec("act8", act8)
     return x1 + qlinear(act8, "act", "down")
+
+
+def nvfp4_decoder_layer(x, params, shape, rope, mask):
+    """A Llama decoder layer whose seven linears are NVFP4 sites of a converted microscaling graph
+    (reference ``quantization/quantize_pt2e.py:700-1142``): the activation goes through the in-graph
+    global scale ``clamp_min(amax(abs(x)) / (6 * 448), tiny)`` (``:881-901``) and
+    ``quantize_mx(x, e2m1, (-1,), 16, 6.0, False, e4m3, None, None, t)``; the weight is quantized the same
+    way once (``:805-856``); the consumer is ``linear_mx(codes, w_codes, input_scale=, weight_scale=,
+    block_size=16, alpha=t_x * t_w)`` (``:1025-1057``).  The attention matmuls are not annotated in that
+    recipe and run as HF eager attention in bfloat16; RMSNorm, RoPE and SwiGLU are plain bfloat16 ops."""
+    from . import gemm as OG
+
+    e2m1, e4m3 = OT.quantization_map("fp4_e2m1"), OT.quantization_map("fp8_e4m3")
+    T = x.shape[0]
+    cos, sin = rope
+
+    def quant(t):
+        g = OQ.calculate_global_scale(t, 6.0, 448.0)
+        s, c = OQ.quantize_mx(t, e2m1, [-1], 16, 6.0, False, e4m3, None, None, g)
+        return s, c, g
+
+    weights = {n: quant(params[n]) for n in ("q", "k", "v", "o", "gate", "up", "down")}
+
+    def qlinear(act, name):
+        s, c, g = act
+        sw, cw, gw = weights[name]
+        return OG.linear_mx(c, cw, None, input_scale=s, weight_scale=sw, block_size=16, alpha=g * gw)
+
+    def rope_apply(t):
+        half = t.shape[-1] // 2
+        rot = torch.cat([-t[..., half:], t[..., :half]], -1)
+        return t * cos[:, None, :] + rot * sin[:, None, :]
+
+    h = quant(F.rms_norm(x, (shape.hidden,), params["ln1"], shape.eps))      # one quantize node feeds q, k and v
+    q = rope_apply(qlinear(h, "q").view(T, shape.heads, shape.head_dim))
+    k = rope_apply(qlinear(h, "k").view(T, shape.kv_heads, shape.head_dim))
+    v = qlinear(h, "v").view(T, shape.kv_heads, shape.head_dim)
+    g = shape.heads // shape.kv_heads
+    scores = torch.matmul(q.transpose(0, 1), k.repeat_interleave(g, 1).permute(1, 2, 0))
+    scores = scores * (1.0 / math.sqrt(shape.head_dim)) + mask
+    p = torch.softmax(scores.float(), -1).to(x.dtype)
+    ctx = torch.matmul(p, v.repeat_interleave(g, 1).transpose(0, 1)).transpose(0, 1).reshape(T, -1)
+    x1 = x + qlinear(quant(ctx), "o")
+    h2 = quant(F.rms_norm(x1, (shape.hidden,), params["ln2"], shape.eps))
+    act = F.silu(qlinear(h2, "gate")) * qlinear(h2, "up")
+    return x1 + qlinear(quant(act), "down")

@@ -158,3 +158,26 @@ def test_quantize_nvfp4_square_matches_the_oracle():
     got_t, got_scale_t = vb.nvfp4.unpack_nvfp4(codes_t, scales_t)
     assert torch.equal(got_t.cpu(), values.mT)
     assert torch.equal(got_scale_t.cpu(), scale.mT.repeat_interleave(16, 0))
+
+
+@pytest.mark.parametrize("merge", [True, False])
+def test_nvfp4_decoder_layer_matches_converted_graph(merge):
+    """Seven NVFP4 linears of a Llama-shaped layer (casts + native block-scaled GEMMs, merged QKV and
+    gate/up with per-column alphas) against the converted microscaling graph on the CPU oracle."""
+    from oracle import layers as OL
+
+    vb = _vb()
+    W = vb.workloads
+    shape = W.LlamaShape(hidden=512, heads=4, kv_heads=2, head_dim=128, intermediate=1024, vocab=1024)
+    T = 256
+    params = W.make_layer_params(3, shape)
+    x = W.make_hidden_states(4, T, shape)
+    want = OL.nvfp4_decoder_layer(x, params, shape, W.rope_tables(T, shape, "cpu"), W.causal_mask(T, "cpu")).float()
+    layer = W.Nvfp4DecoderLayer({k: v.cuda() for k, v in params.items()}, shape, merge=merge)
+    got = layer(x.cuda()).float().cpu()
+    vb.ops.gemm_status()
+    err = (got - want).abs()
+    # 4-bit re-quantization after every block amplifies summation-order noise: a code that moves changes a
+    # value by up to a third
+    assert float(err.max()) <= 6e-2 * float(want.abs().max()), float(err.max() / want.abs().max())
+    assert float(err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) <= 2e-2

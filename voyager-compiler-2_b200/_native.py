@@ -119,6 +119,7 @@ SIGNATURES = {
     "vq_quantize_nvfp4": [_P, _P, _I, _P, _P, _I64, _I64, _P],
     "vq_pack_nvfp4": [_P, _P, _P, _P, _I64, _I64, _P, _P],
     "vq_gemm_nvfp4": [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
+    "vq_gemm_nvfp4_ex": [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _I, _P],
     "vq_gptq_block": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _F, _F, _I, ctypes.POINTER(VqRound),
                       ctypes.POINTER(VqRound), _P],
     "vq_gptq_update": [_P, _P, _P, _I64, _I64, _I64, _I64, _P],

@@ -1221,6 +1221,14 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
 int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int out_dtype, int64_t M,
                   int64_t N, int64_t K, int64_t ldc, int64_t batch, int64_t strideC, const void* alpha,
                   int alpha_dtype, const void* bias, int bias_dtype, void* stream) {
+  return vq_gemm_nvfp4_ex(A, sfa, B, sfb, C, out_dtype, M, N, K, ldc, batch, strideC, alpha, alpha_dtype, bias,
+                          bias_dtype, nullptr, 0, stream);
+}
+
+int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int out_dtype, int64_t M,
+                     int64_t N, int64_t K, int64_t ldc, int64_t batch, int64_t strideC, const void* alpha,
+                     int alpha_dtype, const void* bias, int bias_dtype, const void* alpha_cols, int alpha_cols_dtype,
+                     void* stream) {
   VQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && batch >= 0, "vq_gemm_nvfp4: negative extent");
   if (M == 0 || N == 0 || batch == 0) return VQ_OK;
   VQ_REQUIRE(A && B && C && sfa && sfb, "vq_gemm_nvfp4: null operand");
@@ -1243,6 +1251,10 @@ int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb
   p.alpha = alpha; p.alpha_dt = alpha_dtype;
   p.bias = bias; p.bias_dt = bias_dtype;
   p.out_dt = out_dtype;
+  if (alpha_cols != nullptr) {
+    VQ_REQUIRE(alpha_cols_dtype >= VQ_BF16 && alpha_cols_dtype <= VQ_F32, "vq_gemm_nvfp4_ex: bad alpha_cols dtype");
+    p.alpha_cols = alpha_cols; p.alpha_cols_dt = alpha_cols_dtype;
+  }
   p.idesc = sm100::make_idesc_nvfp4(BM, Q_BN);
   CUtensorMap map_c;
   if (int e = make_output_map(&map_c, &p.tma_store, C, out_dtype, M, N, ldc, batch, strideC)) return e;

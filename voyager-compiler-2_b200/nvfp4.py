@@ -89,9 +89,10 @@ def pack_nvfp4(codes: torch.Tensor, scale: torch.Tensor, check: bool = True) -> 
 
 @N.device_guarded
 def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = None,
-               bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
-    """``alpha * (A @ B^T) + bias`` for packed operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (equal
-    batch shapes; a 2-D ``b`` with a batched ``a`` folds the batch into the rows)."""
+               bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+               alpha_cols: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``alpha * alpha_cols[n] * (A @ B^T) + bias`` for packed operands ``a [*batch, M, K]`` and
+    ``b [*batch, N, K]`` (equal batch shapes; a 2-D ``b`` with a batched ``a`` folds the batch into the rows)."""
     *abatch, m, k = a.shape
     *bbatch, n, kb = b.shape
     if k != kb:
@@ -115,10 +116,16 @@ def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = N
         alpha = alpha.reshape(()) if alpha.dtype in _DTYPE_ID else alpha.float().reshape(())
     if bias is not None:
         bias = bias.contiguous()
-    N.check(N.lib().vq_gemm_nvfp4(a_codes.data_ptr(), a_scales.data_ptr(), b.codes.data_ptr(), b.scales.data_ptr(),
-                                  out.data_ptr(), _dtype_id(out_dtype), m_eff, n, k, n, batch, m_eff * n,
-                                  _ptr(alpha), 0 if alpha is None else _dtype_id(alpha.dtype), _ptr(bias),
-                                  0 if bias is None else _dtype_id(bias.dtype), _stream()), "vq_gemm_nvfp4")
+    if alpha_cols is not None:
+        alpha_cols = alpha_cols.reshape(-1).contiguous()
+        if alpha_cols.numel() != n or alpha_cols.dtype not in _DTYPE_ID:
+            raise ValueError(f"alpha_cols must hold {n} bfloat16/float16/float32 values")
+    N.check(N.lib().vq_gemm_nvfp4_ex(a_codes.data_ptr(), a_scales.data_ptr(), b.codes.data_ptr(), b.scales.data_ptr(),
+                                     out.data_ptr(), _dtype_id(out_dtype), m_eff, n, k, n, batch, m_eff * n,
+                                     _ptr(alpha), 0 if alpha is None else _dtype_id(alpha.dtype), _ptr(bias),
+                                     0 if bias is None else _dtype_id(bias.dtype), _ptr(alpha_cols),
+                                     0 if alpha_cols is None else _dtype_id(alpha_cols.dtype), _stream()),
+            "vq_gemm_nvfp4_ex")
     return out.reshape(*abatch, m, n)
 
 

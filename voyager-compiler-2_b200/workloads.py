@@ -274,3 +274,79 @@ class Fp8DecoderLayer:
         return x1 + FP8.fp8_gemm(FP8.quantize_fp8(act, s["act"]), self.w8["down"], self.alpha["down"], round_acc=self.ra)
 
     __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# NVFP4 decoder layer (e2m1, blocks of 16 along K, e4m3 block scales, one global scale per tensor)
+# ---------------------------------------------------------------------------
+class Nvfp4DecoderLayer:
+    """A Llama-shaped decoder layer whose seven linears run as NVFP4 casts + native block-scaled
+    GEMMs -- the sites the reference's ``backend/gpu/nvfp4.py`` rewrites (``quantize_mx`` with an
+    e2m1 table, block 16, e4m3 scales and a global scale, feeding ``linear_mx`` with ``alpha``).
+    Everything else (RMSNorm, RoPE, attention, SiLU, residual adds) is not quantized in that graph
+    and stays bfloat16 torch operators.
+
+    Weights are quantized once, each with its own global scale, exactly as ``convert_pt2e`` bakes
+    them (``quantization/quantize_pt2e.py:805-856``).  Linears that read one activation share one
+    cast and one GEMM (q/k/v, gate/up): the activation is quantized once in the graph as well
+    (shared fake-quantizer), and column ``n`` of the merged product is scaled by its own linear's
+    ``alpha = bf16(t_activation * t_weight)``.
+    """
+
+    def __init__(self, params, shape: LlamaShape, merge=True):
+        from . import nvfp4 as NV
+
+        self.NV, self.shape, self.merge = NV, shape, merge
+        self.ln1, self.ln2 = params["ln1"], params["ln2"]
+        packed = {n: NV.quantize_nvfp4(params[n]) for n in LINEARS}
+        self.w = {n: (c, s) for n, (c, s, t) in packed.items()}
+        self.tw = {n: t for n, (c, s, t) in packed.items()}
+        self.one = torch.ones((), device=self.ln1.device)
+
+        def merged(names):
+            # scale tiles cover 128 rows each: whole tiles concatenate along the rows
+            assert all(self.w[n][0].shape[0] % 128 == 0 for n in names)
+            codes = torch.cat([self.w[n][0] for n in names], 0)
+            scales = torch.cat([self.w[n][1].reshape(-1) for n in names])
+            tw = torch.cat([self.tw[n].reshape(1).expand(self.w[n][0].shape[0]) for n in names]).contiguous()
+            return codes, scales, tw
+
+        self.merged = {"qkv": merged(("q", "k", "v")), "gate_up": merged(("gate", "up"))} if merge else {}
+        self._rope = None
+
+    # kernels of this package per forward (merged): 4 x (amax + cast) and 4 GEMMs
+    LAUNCHES = 12
+
+    def _linear(self, x, names):
+        """``[linear(x, W_n) for n in names]`` through one cast of ``x``."""
+        NV = self.NV
+        codes, scales, t = NV.quantize_nvfp4(x)
+        if len(names) > 1 and self.merge:
+            wc, ws, tw = self.merged["qkv" if names[0] == "q" else "gate_up"]
+            alpha_cols = (t * tw).float()                     # bf16(t_x * t_w) per column, widened
+            y = NV.nvfp4_gemm(NV.PackedNVFP4(codes, scales), NV.PackedNVFP4(wc, ws), None, None, torch.bfloat16,
+                              alpha_cols=alpha_cols)
+            sizes = [self.w[n][0].shape[0] for n in names]
+            return list(torch.split(y, sizes, dim=-1))
+        return [NV.nvfp4_linear(codes, scales, *self.w[n], (t * self.tw[n]).float(), self.one, None) for n in names]
+
+    def forward(self, x):
+        sh = self.shape
+        T = x.shape[0]
+        if self._rope is None or self._rope[0].shape[0] != T:
+            self._rope = rope_tables(T, sh, x.device)
+        cos, sin = self._rope
+        h = F.rms_norm(x, (sh.hidden,), self.ln1, sh.eps)
+        q, k, v = self._linear(h, ("q", "k", "v"))
+        q = apply_rope(q.reshape(T, sh.heads, sh.head_dim), cos, sin)
+        k = apply_rope(k.reshape(T, sh.kv_heads, sh.head_dim), cos, sin)
+        v = v.reshape(T, sh.kv_heads, sh.head_dim)
+        ctx = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
+                                             is_causal=True, enable_gqa=True)[0]
+        ctx = ctx.transpose(0, 1).reshape(T, sh.heads * sh.head_dim)
+        x1 = x + self._linear(ctx, ("o",))[0]
+        h2 = F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps)
+        gate, up = self._linear(h2, ("gate", "up"))
+        return x1 + self._linear(F.silu(gate) * up, ("down",))[0]
+
+    __call__ = forward
