@@ -740,6 +740,274 @@ class C4:
         return OG.linear_mx(cx, cw, None, input_scale=sx, weight_scale=sw, block_size=16, alpha=t * tw)
 
 
+# ---------------------------------------------------------------------------
+# workload c4m: NVFP4 prefill of a full 32-layer Llama-3.1-8B-shaped model, 1 x 8192 tokens
+# ---------------------------------------------------------------------------
+class C4Model:
+    name = "c4m"
+    description = ("c4m: NVFP4 (e2m1, bs=16, e4m3 block scales, bf16 global scale on activations and weights) prefill of a "
+                   "full 32-layer Llama-3.1-8B-shaped model, 1 x 8192 tokens per GPU: 7 linears per layer as fused casts "
+                   "+ kind::mxf4nvf4 block-scaled tensor-core GEMMs (q/k/v and gate/up merged), bf16 RMSNorm / RoPE / "
+                   "causal attention / SwiGLU as torch operators, final norm + NVFP4 lm_head on the last position")
+    tokens = 8192
+    layers = 32
+    n_sets = 2
+    dtype = "fp4_e2m1 x fp8_e4m3 block scales (fp32 accumulate), bf16 elsewhere"
+    cpu_tokens = 64           # 2048 tokens through one of 32 layers
+    cpu_rows = 2048
+    cpu_sample = ("forwards of ONE decoder layer on 2048 tokens, a quarter of the prefill (the model is 32 such layers: "
+                  "tok/s = 2048 / (32 x layer time); the eager attention of 8192 tokens needs 13 GB of host scores)")
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        W = voyager_b200.workloads
+        self.shape = W.LLAMA_8B
+        self.model = W.Nvfp4Model(self.layers, self.shape, dev, seed=50 + 100 * rank)
+        self.x = [W.make_hidden_states(300 + 10 * rank + i, self.tokens, self.shape, dev) for i in range(self.n_sets)]
+        self.launches_per_step = self.model.LAUNCHES
+        self.h2d_bytes = self.tokens * self.shape.hidden * 2
+        self.d2h_bytes = self.shape.vocab * 2
+        self.model(self.x[0])
+        self.graphs = [capture(lambda x=x: self.model(x)) for x in self.x]
+        self.pipeline = HostPipeline(self.x, [x.cpu().pin_memory() for x in self.x], self.graphs)
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def roofline(self, peaks, reps):
+        """The dominant kernel: the NVFP4 GEMM of the merged gate/up projection, 8192 x 28672 x 4096."""
+        NV = self.vb.nvfp4
+        layer = self.model.layers[0]
+        acts = [torch.randn(self.tokens, self.shape.hidden, device="cuda").bfloat16() for _ in range(2)]
+        packed = [NV.quantize_nvfp4(a) for a in acts]
+        wc, ws, tw = layer.merged["gate_up"]
+        cols = [(t * tw).float() for _, _, t in packed]
+        run = lambda i: NV.nvfp4_gemm(NV.PackedNVFP4(packed[i % 2][0], packed[i % 2][1]), NV.PackedNVFP4(wc, ws), None, None,
+                                      torch.bfloat16, alpha_cols=cols[i % 2])
+        for i in range(3):
+            run(i)
+        reps = min(reps, 50)
+        secs = time_region(run, reps, torch.cuda.synchronize) / reps
+        n = wc.shape[0]
+        achieved = 2.0 * self.tokens * n * self.shape.hidden / secs / 1e12
+        peak, source = fp4_peak(peaks)
+        return secs, {"kernel": f"gemm_nvfp4 (tcgen05 kind::mxf4nvf4.block_scale, 8192x{n}x4096 merged gate/up projection)",
+                      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                      "peak_source": source, "traffic": None}
+
+    def gpu_reference(self):
+        """``torch.nn.functional.scaled_mm`` NVFP4 on the model's four GEMM shapes beside this package's kernel."""
+        import torch.nn.functional as F
+        from torch.nn.functional import ScalingType, SwizzleType
+
+        NV = self.vb.nvfp4
+        one = torch.ones((), device="cuda")
+        rows = []
+        block, tensor = ScalingType.BlockWise1x16, ScalingType.TensorWise
+        swz, none = SwizzleType.SWIZZLE_32_4_4, SwizzleType.NO_SWIZZLE
+        for m, n, k in [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336)]:
+            a = NV.quantize_nvfp4(torch.randn(m, k, device="cuda").bfloat16())
+            b = NV.quantize_nvfp4((torch.randn(n, k, device="cuda") * 0.02).bfloat16())
+            alpha = (a[2] * b[2]).float()
+            fl = 2.0 * m * n * k / 1e12
+            row = {"mnk": [m, n, k], "library_tflops": None,
+                   "ours_tflops": fl / time_library(lambda i: NV.nvfp4_linear(a[0], a[1], b[0], b[1], alpha, one, None), 1, 20)}
+            try:
+                lib = lambda i: F.scaled_mm(a[0].view(torch.float4_e2m1fn_x2), b[0].view(torch.float4_e2m1fn_x2).t(),
+                                            [a[1].reshape(-1).view(torch.float8_e4m3fn), alpha], [block, tensor],
+                                            [b[1].reshape(-1).view(torch.float8_e4m3fn), one], [block, tensor],
+                                            swizzle_a=[swz, none], swizzle_b=[swz, none], output_dtype=torch.bfloat16)
+                row["library_tflops"] = fl / time_library(lib, 1, 20)
+            except Exception as exc:  # this torch build has no block-scaled FP4 GEMM
+                row["library_error"] = repr(exc)[:160]
+            rows.append(row)
+        best = max([r["library_tflops"] for r in rows if r["library_tflops"]] or [None], key=lambda v: v or 0)
+        return {"library": "torch.nn.functional.scaled_mm NVFP4 (BlockWise1x16 e4m3 scales + tensor-wise alpha), same process",
+                "shapes": rows, "best_library_tflops": best}
+
+    def gpu_check(self, state, cpu_out):
+        """The CPU leg's layer (its weights and input) on the GPU kernels against the CPU leg's output."""
+        x, params, shape, _, _ = state
+        W = self.vb.workloads
+        layer = W.Nvfp4DecoderLayer({k: v.cuda() for k, v in params.items()}, shape)
+        got, want = layer(x.cuda()).double().cpu(), cpu_out.double()
+        rms = float((got - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt())
+        # 4-bit re-quantization after every block amplifies summation-order noise (a moved code changes a value by
+        # up to a third), and the GPU attention is a fused bfloat16 kernel where the graph's is eager
+        return {"layer_vs_cpu_oracle_max": (max_rel(got, want), 1e-1), "layer_vs_cpu_oracle_rms": (rms, 3e-2)}
+
+    @staticmethod
+    def cpu_setup():
+        import voyager_b200  # host-side workload definitions only; no kernel runs on this path
+
+        W = voyager_b200.workloads
+        shape = W.LLAMA_8B
+        params = W.make_layer_params(50, shape)
+        x = W.make_hidden_states(300, C4Model.cpu_rows, shape)
+        return x, params, shape, W.rope_tables(C4Model.cpu_rows, shape, "cpu"), W.causal_mask(C4Model.cpu_rows, "cpu")
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import layers as OL
+
+        return OL.nvfp4_decoder_layer(*state)
+
+
+# ---------------------------------------------------------------------------
+# workload c5: GPTQ of one decoder layer's seven linears at the real calibration size
+# ---------------------------------------------------------------------------
+class C5:
+    name = "c5"
+    LINEARS = (("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 4096, 4096), ("gate", 14336, 4096),
+               ("up", 14336, 4096), ("down", 4096, 14336))
+    calibration = 128 * 2048
+    chunk = 16384
+    description = ("c5: GPTQ 4-bit asymmetric group-wise quantization (group 128, damp 0.01, act-order off) of ONE "
+                   "Llama-3.1-8B-shaped decoder layer's 7 linears per step (the model is 32 such layers, 224 linears), "
+                   "calibration 128 x 2048 = 262144 tokens per linear, N(0,1) mixed with a rank-64 component: per linear "
+                   "the Hessian X^T X on the tensor cores streamed in 16384-row chunks, damped Cholesky inverse "
+                   "(torch.linalg on the device), blocked column sweep + trailing updates (CUDA kernels). tok/s = "
+                   "calibration tokens / (32 x the layer's time)")
+    tokens = calibration // 32
+    n_sets = 1
+    launches_per_step = None
+    dtype = "fp32 solve, bf16 tensor-core Hessian (fp32 accumulate)"
+    cpu_sample = ("GPTQ solves of ONE 4096x4096 linear with 16384 calibration rows; scaled to the layer's seven linears at "
+                  "262144 rows by the cost model T K^2 + K^3 + N K^2 (factor 206.6)")
+    cpu_tokens = (128 * 2048 // 32) / 206.6
+
+    @staticmethod
+    def calibration_rows(seed, rows, k, device):
+        g = torch.Generator(device=device).manual_seed(seed)
+        base = torch.randn(rows, k, generator=g, device=device)
+        low = torch.randn(rows, 64, generator=g, device=device) @ torch.randn(64, k, generator=g, device=device)
+        return (0.7 * base + 0.3 * low / 8).bfloat16()
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        self.qmap = voyager_b200.get_quantization_map("uint4", dev)
+        g = torch.Generator(device=dev).manual_seed(60 + rank)
+        sizes = [n * k for _, n, k in self.LINEARS]
+        self.flat_in = (torch.randn(sum(sizes), generator=g, device=dev) * 0.02).bfloat16()
+        self.flat_out = torch.empty_like(self.flat_in)
+        self.offsets = [0]
+        for sz in sizes:
+            self.offsets.append(self.offsets[-1] + sz)
+        # calibration activations per input width, resident in HBM (2.1 GB and 7.5 GB), drawn in slices
+        self.x = {}
+        for k in (4096, 14336):
+            self.x[k] = torch.cat([self.calibration_rows(600 + k + i, self.chunk, k, dev)
+                                   for i in range(self.calibration // self.chunk)])
+        self.h2d_bytes = self.flat_in.numel() * 2
+        self.d2h_bytes = self.flat_out.numel() * 2
+        self.parts = {"hessian": 0.0, "cholesky": 0.0, "sweep": 0.0}
+        self.events = []
+        self.launches = 0
+        self._run()
+        self.launches_per_step = self.launches
+        step = EagerStep(self._run, self.flat_out)
+        step.replay = self._run          # the step writes its output buffer itself
+        self.graphs = [(step, self.flat_out)]
+        self.pipeline = HostPipeline([self.flat_in], [self.flat_in.cpu().pin_memory()], self.graphs)
+
+    def _mark(self, name):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.events.append((name, e))
+
+    def _run(self):
+        G = self.vb.gptq
+        self.launches = 0
+        for i, (name, n, k) in enumerate(self.LINEARS):
+            w = self.flat_in[self.offsets[i]:self.offsets[i + 1]].view(n, k)
+            self._mark("start")
+            h = None
+            for chunk in self.x[k].split(self.chunk):
+                h = G.accumulate_hessian(h, chunk)
+                self.launches += 1
+            self._mark("hessian")
+            hinv = G.hessian_inverse_chol(h, self.calibration, 0.01)
+            del h
+            self._mark("cholesky")
+            out = G.sweep(w, hinv, 128, self.qmap, affine_range=(0.0, 15.0))
+            self.launches += 2 * (k // 128) - 1
+            self.flat_out[self.offsets[i]:self.offsets[i + 1]].view(n, k).copy_(out)
+            self._mark("sweep")
+        return self.flat_out
+
+    def parts_ms(self, steps):
+        """Device time per step spent in the three phases, from the events recorded during the steps."""
+        torch.cuda.synchronize()
+        total = {"hessian": 0.0, "cholesky": 0.0, "sweep": 0.0}
+        for (_, a), (name, b) in zip(self.events, self.events[1:]):
+            if name != "start":
+                total[name] += a.elapsed_time(b)
+        self.events = []
+        return {k: v / steps for k, v in total.items()}
+
+    def step(self, i):
+        self._run()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def roofline(self, peaks, reps):
+        """The dominant kernel: the Hessian GEMM X^T X of the down projection, 14336 x 14336 x 16384 per chunk."""
+        ops = self.vb.ops
+        xt = self.x[14336][:self.chunk].T.contiguous()
+        for _ in range(2):
+            ops.gemm_tn(xt, xt, out_dtype=torch.float32)
+        reps = min(reps, 20)
+        secs = time_region(lambda i: ops.gemm_tn(xt, xt, out_dtype=torch.float32), reps, torch.cuda.synchronize) / reps
+        achieved = 2.0 * 14336 * 14336 * self.chunk / secs / 1e12
+        return secs, {"kernel": "gemm_tn_pair_kernel (tcgen05 kind::f16 bf16, cta_group::2, 14336x14336x16384 Hessian chunk, fp32 out)",
+                      "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                      "frac": achieved / peaks["bf16_tflops"], "peak_source": f"{peaks['source']} bf16 cuBLAS burst",
+                      "traffic": None}
+
+    def gpu_check(self, state, cpu_out):
+        """The CPU leg's problem solved on the device: the reconstruction error tr(D H D^T) of the two solutions
+        (the figure is the relative excess of the device's; LAPACK and the device factorisation are not bit-identical)."""
+        w, h, tokens = state
+        G = self.vb.gptq
+        got = G.compensate_weight_affine(w.cuda(), h.cuda().clone(), tokens, self.qmap, 0.0, 15.0, 128, 0.01).cpu()
+
+        def loss(q):
+            d = (q - w).double()
+            return float(((d @ h.double()) * d).sum())
+
+        # a group's scale and zero point are continuous (they follow the compensated values), so equal codes give
+        # values that agree to rounding, not bit for bit: count values that moved by more than a quarter of a step
+        step = float(w.abs().max()) * 2.0 / 15.0
+        moved = float(((got - cpu_out).abs() > 0.25 * step).float().mean())
+        return {"reconstruction_error_excess_over_cpu_oracle": (max(loss(got) / loss(cpu_out) - 1.0, 0.0), 2e-2),
+                "grid_values_a_quarter_step_from_cpu_oracle": (moved, 5e-2)}
+
+    @staticmethod
+    def cpu_setup():
+        tokens = 16384
+        x = C5.calibration_rows(604096, tokens, 4096, "cpu").float()
+        g = torch.Generator().manual_seed(61)
+        w = (torch.randn(4096, 4096, generator=g) * 0.02).bfloat16().float()
+        return w, x.T @ x, tokens
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import gptq as OGP
+        from oracle import tables as OT
+
+        w, h, tokens = state
+        hinv = OGP.hessian_inverse_chol(h.clone(), tokens, 0.01)
+        return OGP.sweep_affine(w, hinv, OT.quantization_map("uint4"), 0.0, 15.0, 128)
+
+
 class EagerStep:
     """Stands in for a captured graph when a step cannot be captured: ``replay()`` runs it again into the
     same output buffer."""
@@ -854,7 +1122,7 @@ class C2TP:
                       "peak_source": source, "traffic": None}
 
 
-WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "q1": Q1, "r1": R1}
+WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "c4m": C4Model, "c5": C5, "q1": Q1, "r1": R1}
 
 
 def time_cpu_baseline(workload, reps):
@@ -908,7 +1176,7 @@ def library_leg(wl, kind=None):
     return ref
 
 
-LIBRARY_KIND = {"c2": "fp8", "c2s": "fp8", "c4": "fp4"}
+LIBRARY_KIND = {"c2": "fp8", "c2s": "fp8", "c4": "fp4", "c4m": "fp4"}
 
 
 def run_secondary(name, dev, rank, peaks, steps, device_index):
@@ -954,8 +1222,11 @@ def run_ours(args, rank, world, local_rank):
     wl.vb.ops.gemm_status()
 
     barrier()   # NCCL communicators come up here, not inside the sampled region
+    if hasattr(wl, "parts_ms"):
+        wl.parts_ms(1)                      # drop the warm-up's events
     with ClockSampler(local_rank) as clocks:
         elapsed = time_region(wl.step, args.steps, barrier)
+    phases = wl.parts_ms(args.steps) if hasattr(wl, "parts_ms") else None
     wl.vb.ops.gemm_status()
 
     for i in range(3):
@@ -967,6 +1238,7 @@ def run_ours(args, rank, world, local_rank):
     roof = timed_roofline(wl, peaks, 200, local_rank)
     collectives = wl.collective_share(min(args.steps, 50)) if tensor_parallel else None
     replicas_elapsed = 0.0
+    checks = dict(wl.self_check()) if rank == 0 and hasattr(wl, "self_check") else {}
     if tensor_parallel:
         # the same layer as N independent replicas (one full 2048-token batch per GPU, no exchange)
         del wl.graphs, wl.pipeline
@@ -1004,12 +1276,13 @@ def run_ours(args, rank, world, local_rank):
         }
         if reference is not None:
             line["gpu_reference"] = reference
+        if hasattr(wl, "parts_ms"):
+            line["phases_ms_per_step"] = phases
         if tensor_parallel:
             line["collectives"] = collectives
             line["replicas"] = {"value": wl.tokens * args.steps * world / replicas_elapsed, "unit": "tok/s",
                                 "scaling": "weak", "ms_per_step": replicas_elapsed / args.steps * 1e3,
                                 "what": "the same layer as independent replicas, one 2048-token batch per GPU, no exchange"}
-        checks = dict(wl.self_check()) if hasattr(wl, "self_check") else {}
         if world == 1:
             reps = 2 if wl.cpu_tokens >= 2048 and args.workload.startswith("c2") else 3
             value, dt, cores, state, cpu_out = time_cpu_baseline(WORKLOADS[args.workload], reps)

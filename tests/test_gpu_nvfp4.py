@@ -65,7 +65,8 @@ def test_packer_rejects_unrepresentable_values():
         vb.nvfp4.pack_nvfp4(codes, scale)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (64, 48, 64), (300, 264, 320), (256, 512, 4096), (2048, 1024, 1024)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (64, 48, 64), (300, 264, 320), (256, 512, 4096), (2048, 1024, 1024),
+                                   (129, 72, 64), (520, 1000, 448), (1024, 4096, 2048)])
 def test_native_gemm_matches_linear_mx(m, n, k):
     vb = _vb()
     x = C.randn(10 + m, m, k, outliers=0.002)
@@ -160,8 +161,8 @@ def test_quantize_nvfp4_square_matches_the_oracle():
     assert torch.equal(got_scale_t.cpu(), scale.mT.repeat_interleave(16, 0))
 
 
-@pytest.mark.parametrize("merge", [True, False])
-def test_nvfp4_decoder_layer_matches_converted_graph(merge):
+@pytest.mark.parametrize("merge,attention", [(True, "eager"), (False, "eager"), (True, "sdpa")])
+def test_nvfp4_decoder_layer_matches_converted_graph(merge, attention):
     """Seven NVFP4 linears of a Llama-shaped layer (casts + native block-scaled GEMMs, merged QKV and
     gate/up with per-column alphas) against the converted microscaling graph on the CPU oracle."""
     from oracle import layers as OL
@@ -173,7 +174,7 @@ def test_nvfp4_decoder_layer_matches_converted_graph(merge):
     params = W.make_layer_params(3, shape)
     x = W.make_hidden_states(4, T, shape)
     want = OL.nvfp4_decoder_layer(x, params, shape, W.rope_tables(T, shape, "cpu"), W.causal_mask(T, "cpu")).float()
-    layer = W.Nvfp4DecoderLayer({k: v.cuda() for k, v in params.items()}, shape, merge=merge)
+    layer = W.Nvfp4DecoderLayer({k: v.cuda() for k, v in params.items()}, shape, merge=merge, attention=attention)
     got = layer(x.cuda()).float().cpu()
     vb.ops.gemm_status()
     err = (got - want).abs()

@@ -1001,6 +1001,255 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 }
 
 // ---------------------------------------------------------------------------
+// NVFP4 block-scaled GEMM on CTA pairs: two CTAs (a cluster of 2) share a 256x256 tile.
+// Each CTA loads its 128 rows of A, its 128 of the tile's 256 B rows, the block scales of its
+// A rows and the block scales of all 256 B rows (every CTA's tensor core multiplies its rows by
+// all of B); the even CTA's thread issues tcgen05.cp.cta_group::2 (each CTA's scale tiles go
+// from its own shared memory into its own tensor memory) and tcgen05.mma.cta_group::2
+// kind::mxf4nvf4 (M = 256, N = 256, K = 64).  Per byte fetched from L2 this does twice the
+// arithmetic of the 128x128 single-CTA kernel.
+//
+// Tensor memory (512 columns per CTA) cannot hold two 256-column accumulators next to the scale
+// columns, so the two accumulators overlap: accumulator 0 is columns [0, 256), accumulator 1 is
+// [192, 448), scales live in [448, 512).  The epilogue of a tile drains the 64 shared columns
+// first and says so on `ovl_free`; the next tile's first MMA waits for that instead of for the
+// whole accumulator, so only that short drain is not overlapped with tensor work.
+//   full barrier  : in the even CTA; both CTAs' operand loads complete on it
+//   sf_full       : in the even CTA; both CTAs' scale loads complete on it.  The scale tiles of a stage are
+//                   small and land before its operands, so the MMA thread copies them into tensor memory
+//                   (tcgen05.cp, about 40 ns each, twelve per stage, in order with the MMAs) while it would
+//                   otherwise sit waiting for the stage's operands: the kernel is bound by the operand feed
+//                   from L2, and the copies fill the tensor pipe's idle time instead of adding to it
+//   empty barrier : per CTA, released by tcgen05.commit sent to both CTAs
+//   acc_full      : per CTA, same mechanism
+//   acc_empty     : in the even CTA; 16 arrivals (8 epilogue warps x 2 CTAs)
+//   ovl_free      : in the even CTA; 8 arrivals (the 4 warps that drain the shared columns x 2 CTAs)
+// ---------------------------------------------------------------------------
+constexpr int QP_STAGES = 5;
+constexpr int QP_A_BYTES = 128 * BK_BYTES;      // 16 KB: this CTA's A rows, 256 elements of K
+constexpr int QP_B_BYTES = 128 * BK_BYTES;      // 16 KB: this CTA's half of the tile's B rows
+constexpr int QP_SFA_BYTES = 4 * 512;           // 128 rows x 16 scales
+constexpr int QP_SFB_BYTES = 8 * 512;           // 256 rows x 16 scales
+constexpr int QP_STAGE_BYTES = QP_A_BYTES + QP_B_BYTES + QP_SFA_BYTES + QP_SFB_BYTES;
+constexpr size_t QP_SMEM_BYTES = 1024 + QP_STAGES * QP_STAGE_BYTES + 256 + EPI_STAGE_BYTES;
+constexpr uint32_t QP_ACC1_COL = 192, QP_SF_COL = 448;   // scales: four 16-column groups, one per K64 step of a stage
+constexpr int QP_OVERLAP = 64;                  // columns shared by the two accumulators
+
+template <int OUT_DT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                       const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem_a + QP_STAGES * QP_A_BYTES;
+  uint8_t* smem_sfa = smem_b + QP_STAGES * QP_B_BYTES;
+  uint8_t* smem_sfb = smem_sfa + QP_STAGES * QP_SFA_BYTES;
+  uint8_t* epi_stage = smem + QP_STAGES * QP_STAGE_BYTES;   // 1024-byte aligned (the stage size is a multiple of 1024)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
+  uint64_t* full_bar = bars;                          // [QP_STAGES] (used in the even CTA)
+  uint64_t* empty_bar = bars + QP_STAGES;             // [QP_STAGES]
+  uint64_t* acc_full = bars + 2 * QP_STAGES;          // [2]
+  uint64_t* acc_empty = bars + 2 * QP_STAGES + 2;     // [2] (used in the even CTA)
+  uint64_t* ovl_free = bars + 2 * QP_STAGES + 4;      // [2] (used in the even CTA)
+  uint64_t* sf_full = bars + 2 * QP_STAGES + 6;       // [QP_STAGES] (used in the even CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * QP_STAGES + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n * p.batch;
+  const int k64_total = p.K / 64;               // K is a multiple of 64
+  const int k_blocks = (k64_total + 3) / 4;     // stages of 256 elements
+  const int m_blocks128 = (p.M + 127) / 128;    // 128-row scale blocks per batch entry
+  const int n_blocks128 = (p.N + 127) / 128;
+  const uint32_t operand_tx_bytes = 2u * (uint32_t)(QP_A_BYTES + QP_B_BYTES);
+  const uint32_t scale_tx_bytes = 2u * (uint32_t)(QP_SFA_BYTES + QP_SFB_BYTES);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < QP_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&sf_full[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);
+      mbar_init(&ovl_free[a], EPI_WARPS);   // 4 warps per CTA
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      prefetch_tensormap(&map_sfa);
+      prefetch_tensormap(&map_sfb);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m_blk = (int)(tile % tiles_m);
+        const int n_blk = (int)((tile / tiles_m) % tiles_n);
+        const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+        const int m0 = m_blk * 2 * BM + (int)rank * BM;
+        const int n0 = n_blk * BN + (int)rank * (BN / 2);
+        const int sfa_blk = b * m_blocks128 + m_blk * 2 + (int)rank;   // this CTA's 128 rows of A
+        const int sfb_blk = b * n_blocks128 + n_blk * 2;               // both 128-row blocks of the B tile
+        // a scale block past the last row block of its batch entry does not exist: reading the next entry's
+        // (or nothing) is harmless, its operand rows are zero-filled -- but keep the coordinate in range
+        const bool sfa_in = m_blk * 2 + (int)rank < m_blocks128;
+        const bool sfb1_in = n_blk * 2 + 1 < n_blocks128;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (rank == 0) {
+            mbar_arrive_expect_tx(&sf_full[stage], scale_tx_bytes);
+            mbar_arrive_expect_tx(&full_bar[stage], operand_tx_bytes);
+          }
+          const uint32_t leader_sf = map_to_cta(&sf_full[stage], 0);
+          const uint32_t leader_full = map_to_cta(&full_bar[stage], 0);
+          // scale tiles first: [row block][K / 64][128 words]; a box is four K64 steps of one row block (2 KB)
+          tma_load_3d_pair(smem_sfa + stage * QP_SFA_BYTES, &map_sfa, leader_sf, 0, kb * 4,
+                           sfa_in ? sfa_blk : 0x7FFFFFF0);
+          tma_load_3d_pair(smem_sfb + stage * QP_SFB_BYTES, &map_sfb, leader_sf, 0, kb * 4, sfb_blk);
+          tma_load_3d_pair(smem_sfb + stage * QP_SFB_BYTES + QP_SFA_BYTES, &map_sfb, leader_sf, 0, kb * 4,
+                           sfb1_in ? sfb_blk + 1 : 0x7FFFFFF0);
+          tma_load_3d_pair(smem_a + stage * QP_A_BYTES, &map_a, leader_full, kb * BK_BYTES, m0, b);
+          tma_load_3d_pair(smem_b + stage * QP_B_BYTES, &map_b, leader_full, kb * BK_BYTES, n0, b);
+          if (++stage == QP_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      int64_t done = 0;   // tiles issued so far
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++done) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        // the other accumulator's shared columns must have been read out of tensor memory: its tile was
+        // issued just before this one, as use number (done - 1) / 2 of that buffer
+        if (done > 0 && !mbar_wait(&ovl_free[acc ^ 1], (uint32_t)(((done - 1) >> 1) & 1), abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + (acc ? QP_ACC1_COL : 0u);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          const int steps = min(4, k64_total - kb * 4);
+          const uint32_t a_addr = smem_u32(smem_a + stage * QP_A_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + stage * QP_B_BYTES);
+          const uint32_t sfa_addr = smem_u32(smem_sfa + stage * QP_SFA_BYTES);
+          const uint32_t sfb_addr = smem_u32(smem_sfb + stage * QP_SFB_BYTES);
+          // One 16-column group of tensor memory per K64 step: [B scales 8 | A scales 4 | unused 4].  The copies
+          // are issued as soon as the scale tiles are there, ahead of the wait for the operands; tcgen05
+          // operations of one thread execute in order, so they cannot overtake the previous stage's MMAs.
+          if (!mbar_wait(&sf_full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          for (int k = 0; k < steps; ++k) {
+            const uint32_t grp = tmem_base + QP_SF_COL + 16 * k;
+            tmem_copy_sf_pair(grp, smem_desc_sf_chunk(sfb_addr + k * 512));
+            tmem_copy_sf_pair(grp + 4, smem_desc_sf_chunk(sfb_addr + QP_SFA_BYTES + k * 512));
+            tmem_copy_sf_pair(grp + 8, smem_desc_sf_chunk(sfa_addr + k * 512));
+          }
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          for (int k = 0; k < steps; ++k) {
+            const uint32_t grp = tmem_base + QP_SF_COL + 16 * k;
+            const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
+            const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
+            mma_nvfp4_ss_pair(tmem_acc, da, db, p.idesc, grp + 8, grp, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit_pair(&empty_bar[stage], 0x3);
+          if (++stage == QP_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit_pair(&acc_full[acc], 0x3);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ----------------------
+    const int quarter = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    uint32_t epi_buf = 0;
+    const bool has_alpha = p.alpha != nullptr;
+    const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int m_blk = (int)(tile % tiles_m);
+      const int n_blk = (int)((tile / tiles_m) % tiles_n);
+      const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (acc ? QP_ACC1_COL : 0u) + ((uint32_t)(quarter * 32) << 16);
+      const int row0 = m_blk * 2 * BM + (int)rank * BM + quarter * 32;
+      uint8_t* stage = epi_stage + (warp - 2) * (32 * 128);
+      // Tile columns shared with the other accumulator: the last 64 of accumulator 0, the first 64 of
+      // accumulator 1.  The four warps of column half 0 drain them first, announce it, then take 64 more
+      // columns; the warps of half 1 take the 128 columns at the other end.
+      const int ovl0 = acc ? 0 : BN - QP_OVERLAP;
+      int seg_begin[2], seg_end[2];
+      if (chalf == 0) {
+        seg_begin[0] = ovl0;
+        seg_begin[1] = acc ? QP_OVERLAP : BN - 2 * QP_OVERLAP;
+        seg_end[0] = seg_begin[0] + QP_OVERLAP;
+        seg_end[1] = seg_begin[1] + QP_OVERLAP;
+      } else {
+        seg_begin[0] = acc ? BN / 2 : 0;
+        seg_end[0] = seg_begin[0] + BN / 2;
+        seg_begin[1] = seg_end[1] = 0;
+      }
+#pragma unroll 1
+      for (int seg = 0; seg < 2 - chalf; ++seg) {
+        epilogue_warp_tile<OUT_DT, 1>(p, &map_c, taddr, stage, epi_buf, row0, lane, n_blk * BN, b, has_alpha, alpha,
+                                      seg_begin[seg], seg_end[seg]);
+        if (chalf == 0 && seg == 0) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(&ovl_free[acc], 0));
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  if (warp >= 2 && lane == 0) tma_store_wait_read();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1060,6 +1309,23 @@ int make_output_map(CUtensorMap* map, int* usable, void* C, int out_dtype, int64
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled (output) failed with code %d", (int)r);
   *usable = 1;
+  return VQ_OK;
+}
+
+// Tensor map over packed NVFP4 block scales, [row blocks][K / 64][512 bytes] seen as 32-bit words:
+// a box is four K64 steps of one 128-row block (2 KB, no swizzle).  Boxes that reach past the
+// last K step or the last row block read as zero.
+int make_scale_map(CUtensorMap* map, const void* base, int64_t k64_total, int64_t row_blocks) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {128, (cuuint64_t)k64_total, (cuuint64_t)row_blocks};
+  cuuint64_t strides[2] = {512, (cuuint64_t)k64_total * 512};
+  cuuint32_t box[3] = {128, 4, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled (scales) failed with code %d", (int)r);
   return VQ_OK;
 }
 
@@ -1241,7 +1507,15 @@ int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* 
   const int64_t row_bytes = K / 2;
   CUtensorMap map_a, map_b;
   if (int e = make_operand_map(&map_a, A, VQ_BF16, 1, M, row_bytes, row_bytes, batch, M * row_bytes, BM)) return e;
-  if (int e = make_operand_map(&map_b, B, VQ_BF16, 1, N, row_bytes, row_bytes, batch, N * row_bytes, Q_BN)) return e;
+  // More than one 128-row block of output: CTA pairs on 256x256 tiles (VQ_NVFP4_PAIR=0 keeps the single-CTA kernel).
+  static int pair_mode = -1;
+  if (pair_mode < 0) {
+    const char* env = getenv("VQ_NVFP4_PAIR");
+    pair_mode = (env && env[0] == '0') ? 0 : 1;
+  }
+  const bool pair = pair_mode == 1 && M > BM;
+  if (int e = make_operand_map(&map_b, B, VQ_BF16, 1, N, row_bytes, row_bytes, batch, N * row_bytes, pair ? BN / 2 : Q_BN))
+    return e;
   GemmParams p{};
   p.C = C;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
@@ -1263,6 +1537,23 @@ int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* 
   sf.sfb = static_cast<const uint8_t*>(sfb);
   sf.sfa_batch_stride = ((M + 127) / 128) * (K / 64) * 512;
   sf.sfb_batch_stride = ((N + 127) / 128) * (K / 64) * 512;
+  if (pair) {
+    CUtensorMap map_sfa, map_sfb;
+    if (int e = make_scale_map(&map_sfa, sfa, K / 64, ((M + 127) / 128) * batch)) return e;
+    if (int e = make_scale_map(&map_sfb, sfb, K / 64, ((N + 127) / 128) * batch)) return e;
+    p.idesc = sm100::make_idesc_nvfp4(2 * BM, BN);
+    static unsigned long long pair_configured = 0;
+    if (first_call_on_device(&pair_configured)) {
+      if (int rc = allow_big_smem(gemm_nvfp4_pair_kernel<VQ_BF16>, gemm_nvfp4_pair_kernel<VQ_F16>,
+                                  gemm_nvfp4_pair_kernel<VQ_F32>, QP_SMEM_BYTES))
+        return rc;
+    }
+    const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
+    const int clusters = (int)(tiles < kSmCount / 2 ? tiles : kSmCount / 2);
+    VQ_FOR_OUT_DTYPE(out_dtype, gemm_nvfp4_pair_kernel)<<<2 * clusters, NUM_THREADS, QP_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+        map_a, map_b, map_sfa, map_sfb, map_c, p);
+    return check_launch("gemm_nvfp4_pair_kernel");
+  }
   static unsigned long long configured = 0;
   if (first_call_on_device(&configured)) {
     if (int rc = allow_big_smem(gemm_nvfp4_kernel<VQ_BF16>, gemm_nvfp4_kernel<VQ_F16>, gemm_nvfp4_kernel<VQ_F32>,

@@ -20,7 +20,7 @@ namespace {
 
 constexpr float kEps = 1e-12f;  // the reference's EPS clamp on scales and pivots
 constexpr int kMaxBlock = 128;
-constexpr int kRowsPerCta = 64;
+constexpr int kRowsPerCta = 32;   // one warp per CTA: twice the CTAs of a 64-row split, and up to 3 CTAs share an SM at 64 KB of shared memory each
 constexpr int kShrinkCandidates = 5;
 
 struct GptqBlockParams {

@@ -293,10 +293,17 @@ class Nvfp4DecoderLayer:
     ``alpha = bf16(t_activation * t_weight)``.
     """
 
-    def __init__(self, params, shape: LlamaShape, merge=True):
+    def __init__(self, params, shape: LlamaShape, merge=True, attention="eager"):
         from . import nvfp4 as NV
 
         self.NV, self.shape, self.merge = NV, shape, merge
+        # "eager": the graph's own attention operators (matmul, scale + mask, softmax, matmul: HF eager
+        # attention, every intermediate a bfloat16 tensor).  "sdpa": torch's fused kernel, which keeps the
+        # scores in float32; the two differ by the bfloat16 rounding of the scores (half a unit at 64..128),
+        # which the 4-bit casts downstream amplify to quantization-noise level.
+        if attention not in ("eager", "sdpa"):
+            raise ValueError(attention)
+        self.attention = attention
         self.ln1, self.ln2 = params["ln1"], params["ln2"]
         packed = {n: NV.quantize_nvfp4(params[n]) for n in LINEARS}
         self.w = {n: (c, s) for n, (c, s, t) in packed.items()}
@@ -313,6 +320,7 @@ class Nvfp4DecoderLayer:
 
         self.merged = {"qkv": merged(("q", "k", "v")), "gate_up": merged(("gate", "up"))} if merge else {}
         self._rope = None
+        self._mask = None
 
     # kernels of this package per forward (merged): 4 x (amax + cast) and 4 GEMMs
     LAUNCHES = 12
@@ -330,6 +338,25 @@ class Nvfp4DecoderLayer:
             return list(torch.split(y, sizes, dim=-1))
         return [NV.nvfp4_linear(codes, scales, *self.w[n], (t * self.tw[n]).float(), self.one, None) for n in names]
 
+    def _attention(self, q, k, v):
+        """Causal attention of ``q [T, heads, d]``, ``k`` / ``v`` ``[T, kv_heads, d]`` -> ``[T, heads * d]``."""
+        sh = self.shape
+        T = q.shape[0]
+        if self.attention == "sdpa":
+            ctx = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
+                                                 v.transpose(0, 1)[None], is_causal=True, enable_gqa=True)[0]
+            return ctx.transpose(0, 1).reshape(T, sh.heads * sh.head_dim)
+        if self._mask is None or self._mask.shape[0] != T:
+            self._mask = causal_mask(T, q.device)
+        # a KV group's query heads share its keys: [kv, groups, T, d] x [kv, 1, d, T], no repeated K / V
+        qg = q.reshape(T, sh.kv_heads, sh.groups, sh.head_dim).permute(1, 2, 0, 3)
+        scores = torch.matmul(qg, k.permute(1, 2, 0)[:, None])                       # [kv, groups, T, T] bfloat16
+        # mask + scores / sqrt(d): the mask is 0 or -inf, so one rounding here equals the graph's two
+        scores = torch.add(self._mask, scores, alpha=1.0 / math.sqrt(sh.head_dim))
+        p = torch.softmax(scores, -1)                                                # float32 inside, rounded once
+        ctx = torch.matmul(p, v.transpose(0, 1)[:, None])                            # [kv, groups, T, d]
+        return ctx.permute(2, 0, 1, 3).reshape(T, sh.heads * sh.head_dim)
+
     def forward(self, x):
         sh = self.shape
         T = x.shape[0]
@@ -341,12 +368,62 @@ class Nvfp4DecoderLayer:
         q = apply_rope(q.reshape(T, sh.heads, sh.head_dim), cos, sin)
         k = apply_rope(k.reshape(T, sh.kv_heads, sh.head_dim), cos, sin)
         v = v.reshape(T, sh.kv_heads, sh.head_dim)
-        ctx = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
-                                             is_causal=True, enable_gqa=True)[0]
-        ctx = ctx.transpose(0, 1).reshape(T, sh.heads * sh.head_dim)
+        ctx = self._attention(q, k, v)
         x1 = x + self._linear(ctx, ("o",))[0]
         h2 = F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps)
         gate, up = self._linear(h2, ("gate", "up"))
         return x1 + self._linear(F.silu(gate) * up, ("down",))[0]
+
+    __call__ = forward
+
+
+def make_layer_params_on_device(seed: int, shape: LlamaShape, device):
+    """``make_layer_params`` drawn by the device's generator (for many-layer benchmarks, where drawing
+    billions of normals on the host would dominate set-up; the values differ from the host generator's)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    params = {name: (torch.randn(*dims, generator=g, device=device) * 0.02).bfloat16()
+              for name, dims in linear_shapes(shape).items()}
+    params["ln1"] = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+    params["ln2"] = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+    return params
+
+
+class Nvfp4Model:
+    """``layers`` NVFP4 decoder layers, a final RMSNorm and an NVFP4 ``lm_head`` applied to the last position
+    (what a prefill hands to sampling): the shape of a converted Llama-3.1-8B graph with
+    ``fp4_e2m1,qs=microscaling,bs=16,scale=fp8_e4m3,gs=1`` on activations and weights of every linear."""
+
+    def __init__(self, layers: int, shape: LlamaShape, device, seed: int = 0, layer_cls=None, **layer_args):
+        from . import nvfp4 as NV
+
+        self.NV, self.shape = NV, shape
+        cls = layer_cls or Nvfp4DecoderLayer
+        self.layers = []
+        for i in range(layers):
+            params = make_layer_params_on_device(seed + i, shape, device)
+            self.layers.append(cls(params, shape, **layer_args))
+            del params
+        g = torch.Generator(device=device).manual_seed(seed + layers)
+        head = (torch.randn(shape.vocab, shape.hidden, generator=g, device=device) * 0.02).bfloat16()
+        self.head = NV.quantize_nvfp4(head)
+        del head
+        self.norm = torch.ones(shape.hidden, dtype=torch.bfloat16, device=device)
+        self.one = torch.ones((), device=device)
+
+    @property
+    def LAUNCHES(self):
+        return sum(layer.LAUNCHES for layer in self.layers) + 3
+
+    def forward(self, x):
+        for layer in self.layers:
+            x = layer(x)
+        return self.logits(x[-1:])
+
+    def logits(self, last):
+        """``last``: the final position's hidden state ``[1, hidden]`` -> ``[1, vocab]``."""
+        NV = self.NV
+        codes, scales, t = NV.quantize_nvfp4(F.rms_norm(last, (self.shape.hidden,), self.norm, self.shape.eps))
+        wc, ws, tw = self.head
+        return NV.nvfp4_linear(codes, scales, wc, ws, (t * tw).float(), self.one, None)
 
     __call__ = forward
