@@ -859,6 +859,185 @@ class C4Model:
 
 
 # ---------------------------------------------------------------------------
+# workload c3: MXNF4 decode step over a KIVI cache, full 32-layer model
+# ---------------------------------------------------------------------------
+class C3:
+    name = "c3"
+    batch, cached, recent, layers = 16, 4096, 128, 32
+    description = ("c3: MXNF4 decode step of a full 32-layer Llama-3.1-8B-shaped model, batch 16 (one new token per "
+                   "sequence), 4096 positions cached: weights lut4_to_int6 (NF4 levels) bs=64 with fp8_e5m3 scales, stored "
+                   "packed (0.53 B/parameter) and read by the weight-streaming linear; activations quantize_mx'd the same "
+                   "way every step; residual adds through a per-tensor fp8_e4m3 cast; KV cache KIVI 2-bit (keys per channel, "
+                   "values per token, groups of 64, packed) with the newest 128 positions in bf16, read by the fused unpack + "
+                   "dequantize kernel; bf16 attention as torch operators; final norm + lm_head")
+    tokens = 16
+    n_sets = 2
+    dtype = "bf16 operands decoded from 4-bit codes x e5m3 block scales (fp32 accumulate)"
+    cpu_tokens = 16 / 32
+    cpu_sample = ("decode steps of ONE decoder layer, batch 16, 4096 cached positions (the model is 32 such layers: "
+                  "tok/s = 16 / (32 x layer time); lm_head not included)")
+
+    @staticmethod
+    def layer_state(seed, shape, tables, device, batch, cached, recent):
+        """Weights (index codes + block scales), the KIVI cache and the recent window of one layer, drawn from
+        N(0, 0.02) weights and N(0, 1) keys / values through the real quantizers."""
+        import voyager_b200
+
+        Q = torch.ops.quantized_ops
+        g = torch.Generator(device=device).manual_seed(seed)
+        d, hq, hkv, h, inter = shape.head_dim, shape.heads, shape.kv_heads, shape.hidden, shape.intermediate
+        rows = {"qkv": ((hq + 2 * hkv) * d, h), "o": (h, hq * d), "gate_up": (2 * inter, h), "down": (h, inter)}
+        weights = {}
+        for name, (n, k) in rows.items():
+            w = (torch.randn(n, k, generator=g, device=device) * 0.02).bfloat16()
+            s, c = Q.quantize_mx(w, tables["index"], [-1], 64, 31.0, False, tables["e5m3"], tables["mid"])
+            weights[name] = (c, s)
+        weights["ln1"] = torch.ones(h, dtype=torch.bfloat16, device=device)
+        weights["ln2"] = torch.ones(h, dtype=torch.bfloat16, device=device)
+        main = cached - recent
+        kv = lambda t: torch.randn(batch, hkv, t, d, generator=g, device=device).bfloat16()
+        K = voyager_b200.kivi
+        cache = {"k": K.quantize_cache(kv(main), tables["uint2"], -2, 64, 2, tables["e4m3"]),
+                 "v": K.quantize_cache(kv(main), tables["uint2"], -1, 64, 2, tables["e4m3"]),
+                 "k_res": kv(recent), "v_res": kv(recent)}
+        return weights, cache
+
+    def __init__(self, dev, rank):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        W, P = voyager_b200.workloads, voyager_b200.packed
+        self.shape = W.LLAMA_8B
+        self.tables = W.nf4_tables(dev)
+        t = self.tables
+        self.scale = torch.tensor(8.0 / 448.0, dtype=torch.bfloat16, device=dev)          # residual stream within +-8
+        self.model = []
+        self.weight_bytes = self.cache_bytes = 0
+        for i in range(self.layers):
+            weights, cache = self.layer_state(700 + 100 * rank + i, self.shape, t, dev, self.batch, self.cached, self.recent)
+            packed = {n: P.pack_lut4_weight(*weights[n], t["levels"], 64, check=False)
+                      for n in ("qkv", "o", "gate_up", "down")}
+            packed["ln1"], packed["ln2"] = weights["ln1"], weights["ln2"]
+            del weights
+            self.model.append(W.Mxnf4DecodeLayer(packed, t, cache, self.scale, self.shape))
+            self.weight_bytes += sum(v.nbytes for k, v in packed.items() if k not in ("ln1", "ln2"))
+            self.cache_bytes += cache["k"].nbytes + cache["v"].nbytes + 2 * cache["k_res"].numel() * 2
+        g = torch.Generator(device=dev).manual_seed(699 + rank)
+        head = (torch.randn(self.shape.vocab, self.shape.hidden, generator=g, device=dev) * 0.02).bfloat16()
+        s, c = torch.ops.quantized_ops.quantize_mx(head, t["index"], [-1], 64, 31.0, False, t["e5m3"], t["mid"])
+        self.head = P.pack_lut4_weight(c, s, t["levels"], 64, check=False)
+        del head, s, c
+        self.weight_bytes += self.head.nbytes
+        self.norm = torch.ones(self.shape.hidden, dtype=torch.bfloat16, device=dev)
+        cos, sin = W.rope_tables(self.cached, self.shape, dev)
+        self.rope = (cos[-1].contiguous(), sin[-1].contiguous())
+        self.x = [W.make_hidden_states(800 + 10 * rank + i, self.batch, self.shape, dev) for i in range(self.n_sets)]
+        self.launches_per_step = self.layers * W.Mxnf4DecodeLayer.LAUNCHES + 2
+        self.h2d_bytes = self.batch * self.shape.hidden * 2
+        self.d2h_bytes = self.batch * self.shape.vocab * 2
+        self._run(self.x[0])
+        self.graphs = [capture(lambda x=x: self._run(x)) for x in self.x]
+        self.pipeline = HostPipeline(self.x, [x.cpu().pin_memory() for x in self.x], self.graphs)
+
+    def _run(self, x):
+        P, t = self.vb.packed, self.tables
+        for layer in self.model:
+            x = layer(x, self.rope)
+        h = torch.nn.functional.rms_norm(x, (self.shape.hidden,), self.norm, self.shape.eps)
+        s, c = torch.ops.quantized_ops.quantize_mx(h, t["index"], [-1], 64, 31.0, False, t["e5m3"], t["mid"])
+        return P.linear_lut4(c, self.head, input_scale=s, input_code=t["levels"])
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def roofline(self, peaks, reps):
+        """The step against the bytes it must read: packed weights + packed cache (what an HBM-bound decode step
+        costs at best), and the weight-streaming kernel alone on the merged gate/up projection."""
+        P, t = self.vb.packed, self.tables
+        ws = [layer.w["gate_up"] for layer in self.model[:8]]                      # 8 x 62 MB: beyond L2
+        x = torch.randint(0, 16, (self.batch, self.shape.hidden), device="cuda").bfloat16()
+        sx = torch.full((self.batch, self.shape.hidden // 64), 0.05, dtype=torch.bfloat16, device="cuda")
+        run = lambda i: P.linear_lut4(x, ws[i % len(ws)], input_scale=sx, input_code=t["levels"])
+        for i in range(3):
+            run(i)
+        secs = time_region(run, reps, torch.cuda.synchronize) / reps
+        achieved = ws[0].nbytes / secs / 1e9
+        step_secs = time_region(self.step, 10, torch.cuda.synchronize) / 10
+        return secs, {"kernel": "gemm_lut4_kernel (packed 4-bit codes + block scales -> bf16 mma.sync, 16 x 28672 x 4096 merged gate/up)",
+                      "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                      "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} copy bandwidth", "traffic": None,
+                      "whole_step": {"algorithmic_bytes": self.weight_bytes + self.cache_bytes,
+                                     "weight_bytes": self.weight_bytes, "cache_bytes": self.cache_bytes,
+                                     "achieved_gbs": (self.weight_bytes + self.cache_bytes) / step_secs / 1e9,
+                                     "frac": (self.weight_bytes + self.cache_bytes) / step_secs / 1e9 / peaks["hbm_gbs"]}}
+
+    def gpu_check(self, state, cpu_out):
+        """The CPU leg's layer (its weights, cache and input) on the GPU kernels against the CPU leg's output."""
+        x, weights, tables, cache, rope, scale, shape = state
+        W, P, K = self.vb.workloads, self.vb.packed, self.vb.kivi
+        t = self.tables
+        packed = {n: P.pack_lut4_weight(weights[n][0].cuda(), weights[n][1].cuda(), t["levels"], 64)
+                  for n in ("qkv", "o", "gate_up", "down")}
+        packed["ln1"], packed["ln2"] = weights["ln1"].cuda(), weights["ln2"].cuda()
+        dev_cache = {}
+        for name, axis in (("k", -2), ("v", -1)):
+            codes, sc, zp = cache[name]
+            dev_cache[name] = K.PackedCache(K.pack_codes(codes.cuda(), 2), sc.cuda(), zp.cuda(), tuple(codes.shape),
+                                            [axis], 64, 2)
+        dev_cache["k_res"], dev_cache["v_res"] = cache["k_res"].cuda().clone(), cache["v_res"].cuda().clone()
+        layer = W.Mxnf4DecodeLayer(packed, t, dev_cache, scale.cuda(), shape)
+        got = layer(x.cuda(), (rope[0].cuda(), rope[1].cuda())).double().cpu()
+        want = cpu_out.double()
+        rms = float((got - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt())
+        # 4-bit activation casts after every block amplify summation-order noise (a moved code changes a value by a third)
+        return {"layer_vs_cpu_oracle_max": (max_rel(got, want), 1e-1), "layer_vs_cpu_oracle_rms": (rms, 3e-2)}
+
+    @staticmethod
+    def cpu_setup():
+        import voyager_b200  # host-side definitions only
+        from oracle import quantizers as OQ
+        from oracle import tables as OT
+
+        W = voyager_b200.workloads
+        shape = W.LLAMA_8B
+        nf4 = OT.quantization_map("lut4_to_int6")
+        levels = torch.unique(nf4)
+        tables = {"levels": levels, "index": torch.searchsorted(levels, nf4).to(torch.int64),
+                  "mid": (levels[:-1] + levels[1:]) / 2, "e5m3": OT.quantization_map("fp8_e5m3"),
+                  "e4m3": OT.quantization_map("fp8_e4m3"), "uint2": OT.quantization_map("uint2")}
+        g = torch.Generator().manual_seed(700)
+        d, hq, hkv, h, inter = shape.head_dim, shape.heads, shape.kv_heads, shape.hidden, shape.intermediate
+        weights = {}
+        for name, (n, k) in {"qkv": ((hq + 2 * hkv) * d, h), "o": (h, hq * d), "gate_up": (2 * inter, h),
+                             "down": (h, inter)}.items():
+            w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+            s, c = OQ.quantize_mx(w, tables["index"], [-1], 64, 31.0, False, tables["e5m3"], tables["mid"])
+            weights[name] = (c, s)
+        weights["ln1"] = torch.ones(h, dtype=torch.bfloat16)
+        weights["ln2"] = torch.ones(h, dtype=torch.bfloat16)
+        main = C3.cached - C3.recent
+        kv = lambda t: torch.randn(C3.batch, hkv, t, d, generator=g).bfloat16()
+        cache = {}
+        for name, axis in (("k", -2), ("v", -1)):
+            sc, zp, codes = OQ.quantize_affine(kv(main), tables["uint2"], [axis], 64, 0.0, 3.0, tables["e4m3"])
+            cache[name] = (codes, sc, zp)
+        cache["k_res"], cache["v_res"] = kv(C3.recent), kv(C3.recent)
+        x = W.make_hidden_states(800, C3.batch, shape)
+        cos, sin = W.rope_tables(C3.cached, shape, "cpu")
+        return x, weights, tables, cache, (cos[-1], sin[-1]), torch.tensor(8.0 / 448.0, dtype=torch.bfloat16), shape
+
+    @staticmethod
+    def cpu_step(state):
+        from oracle import layers as OL
+
+        x, weights, tables, cache, rope, scale, shape = state
+        return OL.mxnf4_decode_layer(x, weights, tables, cache, rope, scale, shape)
+
+
+# ---------------------------------------------------------------------------
 # workload c5: GPTQ of one decoder layer's seven linears at the real calibration size
 # ---------------------------------------------------------------------------
 class C5:
@@ -1122,7 +1301,7 @@ class C2TP:
                       "peak_source": source, "traffic": None}
 
 
-WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "c4m": C4Model, "c5": C5, "q1": Q1, "r1": R1}
+WORKLOADS = {"c1": C1, "c2": C2, "c2s": C2Separate, "c4": C4, "c3": C3, "c4m": C4Model, "c5": C5, "q1": Q1, "r1": R1}
 
 
 def time_cpu_baseline(workload, reps):

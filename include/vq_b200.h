@@ -468,6 +468,41 @@ int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* 
  * then invalid).  No counterpart in the reference. */
 int vq_gemm_status(int reset);
 
+/* The KIVI cache read for 2-bit codes of a bfloat16 [outer, T, D] tensor: quantized_ops::dequantize(
+ * codes, scale, zero_point, axes, block) (ops/quantized.py:527-571; codegen/transform/
+ * quant_folding.py:2391-2547) straight from packed bytes (element i of the row-major tensor in
+ * byte i / 4 at bit 2 (i % 4)), out = bf16(bf16(code - zero_point) * scale).  along_channels == 0:
+ * groups of `block` positions per channel (keys; parameters [outer, T / block, D]); != 0: groups of
+ * `block` channels per position (values; parameters [outer, T, D / block]).  The general layouts,
+ * other widths and the fused re-encode stay with vq_unpack_dequantize. */
+int vq_kivi_read_2bit(const void* packed, const void* scale, const void* zero_point, void* out, int64_t outer,
+                      int64_t T, int64_t D, int along_channels, int64_t block, void* stream);
+
+/* Weight-streaming microscaling linear for a decode step (M <= 32 activation rows), on a weight
+ * stored packed: w_packed [N, K / 2] holds two 4-bit codebook indices per byte (even element in
+ * the low nibble), w_scale [N, K / block_size] its bfloat16 block scales, w_levels the 16
+ * bfloat16 codebook entries.  It computes quantized_ops::linear_mx (ops/quantized.py:662-723)
+ * for such a weight -- both operands read back as bf16(level * scale) (:574-591), float32
+ * products and sum, alpha, bias, one rounding -- without ever materialising the weight's
+ * bfloat16-valued index tensor (0.53 bytes per parameter from memory instead of 2).  The
+ * activation a [M, K] (row pitch lda, bfloat16) holds values, or codebook indices when a_levels
+ * (n_a_levels bfloat16 entries) is given; a_scale [M, K / block_size] may be NULL.
+ * K is a multiple of 128; block_size a multiple of 32 dividing K.  workspace is
+ * vq_gemm_lut4_workspace_floats(M, N, K) floats of device scratch (contents irrelevant);
+ * counters is vq_gemm_lut4_counters(N) ints that must be zero before the first call and are
+ * left zero by every call (calls sharing them must not overlap on the device). */
+int64_t vq_gemm_lut4_workspace_floats(int64_t M, int64_t N, int64_t K);
+int64_t vq_gemm_lut4_counters(int64_t N);
+int vq_gemm_lut4(const void* a, int64_t lda, const void* a_scale, const void* a_levels, int n_a_levels, int64_t M,
+                 const void* w_packed, const void* w_scale, const void* w_levels, int block_size, void* out,
+                 int out_dtype, int64_t N, int64_t K, const void* alpha, int alpha_dtype, const void* bias,
+                 int bias_dtype, float* workspace, int* counters, void* stream);
+
+/* Packs bfloat16-valued codebook indices codes [rows, K] (each 0..15, what quantize_mx returns
+ * for a lookup format with an index table, quantize_pt2e.py:754-791) into vq_gemm_lut4's
+ * w_packed layout.  *bad (device int, zeroed by the caller) is set if a value is not such an index. */
+int vq_pack_lut4(const void* codes, void* packed, int64_t rows, int64_t K, int* bad, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

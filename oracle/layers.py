@@ -119,3 +119,64 @@ def nvfp4_decoder_layer(x, params, shape, rope, mask):
     h2 = quant(F.rms_norm(x1, (shape.hidden,), params["ln2"], shape.eps))
     act = F.silu(qlinear(h2, "gate")) * qlinear(h2, "up")
     return x1 + qlinear(quant(act), "down")
+
+
+def mxnf4_decode_layer(x, weights, tables, cache, rope, residual_scale, shape):
+    """One decode step of a Llama decoder layer in the MXNF4 recipe with a KIVI cache, as the converted
+    graph's operators compute it (batch ``B``, one new token per sequence).
+
+    Linears (``quantize_pt2e.py:700-1142``): the activation goes through ``quantize_mx(x, index_table,
+    (-1,), 64, 31.0, False, e5m3, midpoints)``, the weight is baked as codebook indices + block scales, the
+    consumer is ``linear_mx(..., block_size=64, input_code=levels, weight_code=levels)``.  q/k/v (and
+    gate/up) read one shared quantize node.  Residual adds take their earlier operand through a per-tensor
+    ``fp8_e4m3`` quantize / dequantize.  The cached keys and values are KIVI codes (``quantize_affine``,
+    uint2, groups of 64: keys along the sequence, values along the head dimension) read back with
+    ``dequantize(codes, scale, zero_point, axes, 64)``; the newest ``R`` positions (the last one is this
+    step's token) are kept in bfloat16.  Attention is eager bfloat16 over [main | residual] keys.
+
+    ``weights``: name -> (index codes [N, K], scale [N, K / 64]) for 'qkv', 'o', 'gate_up', 'down' and
+    'ln1', 'ln2' gains.  ``tables``: dict with 'levels', 'index', 'mid', 'e5m3', 'e4m3'.  ``cache``: dict
+    with 'k' / 'v' -> (codes, scale, zero_point) of shape [B, kv, Tm, d] and 'k_res' / 'v_res'
+    [B, kv, R, d] whose last position is overwritten by this step.  ``rope`` = (cos, sin) [d] of the new position."""
+    from . import gemm as OG
+
+    t = tables
+    B = x.shape[0]
+    d, hq, hkv = shape.head_dim, shape.heads, shape.kv_heads
+    cos, sin = rope
+
+    def qlinear(act, name):
+        s, c = OQ.quantize_mx(act, t["index"], [-1], 64, 31.0, False, t["e5m3"], t["mid"])
+        cw, sw = weights[name]
+        return OG.linear_mx(c, cw, None, input_scale=s, weight_scale=sw, block_size=64, input_code=t["levels"],
+                            weight_code=t["levels"])
+
+    def through_fp8(v):
+        q = OQ.quantize(v, residual_scale, None, None, None, t["e4m3"])
+        return OQ.dequantize(q, residual_scale)
+
+    def rope_apply(v):
+        half = d // 2
+        rot = torch.cat([-v[..., half:], v[..., :half]], -1)
+        return v * cos + rot * sin
+
+    qkv = qlinear(F.rms_norm(x, (shape.hidden,), weights["ln1"], shape.eps), "qkv")
+    q = rope_apply(qkv[:, :hq * d].reshape(B, hq, d))
+    k = rope_apply(qkv[:, hq * d:(hq + hkv) * d].reshape(B, hkv, d))
+    v = qkv[:, (hq + hkv) * d:].reshape(B, hkv, d)
+    k_res, v_res = cache["k_res"].clone(), cache["v_res"].clone()
+    k_res[:, :, -1] = k
+    v_res[:, :, -1] = v
+    k_main = OQ.dequantize(*cache["k"], [-2], 64)
+    v_main = OQ.dequantize(*cache["v"], [-1], 64)
+    qg = q.reshape(B, hkv, hq // hkv, d)
+    scale = 1.0 / math.sqrt(d)
+    scores = torch.cat([torch.matmul(qg, k_main.transpose(-1, -2)), torch.matmul(qg, k_res.transpose(-1, -2))], -1)
+    p = torch.softmax((scores * scale).float(), -1).to(x.dtype)
+    tm = k_main.shape[-2]
+    ctx = torch.matmul(p[..., :tm], v_main) + torch.matmul(p[..., tm:], v_res)
+    x1 = through_fp8(x) + qlinear(ctx.reshape(B, hq * d), "o")
+    gu = qlinear(F.rms_norm(x1, (shape.hidden,), weights["ln2"], shape.eps), "gate_up")
+    inter = gu.shape[-1] // 2
+    act = F.silu(gu[:, :inter]) * gu[:, inter:]
+    return through_fp8(x1) + qlinear(act, "down")

@@ -47,3 +47,24 @@ def test_two_gpu_fp8_decoder_layer_matches_one_gpu_and_the_oracle():
     want = OL.fp8_decoder_layer(x, params, scales, shape, W.rope_tables(tokens, shape, "cpu"),
                                 W.causal_mask(tokens, "cpu"))
     assert float((got.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
+
+
+def test_two_gpu_layer_parallel_gptq_with_the_device_solve():
+    """Five GPTQ problems dealt to two GPUs by cost, each solved by the CUDA sweep on its owner, the
+    compensated weights broadcast over NCCL (bfloat16 model weights, float32 on the wire)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from oracle import gptq as OG
+    from oracle import tables as OT
+
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(tp_common.run_rank_gptq, args=(2, 29627, results), nprocs=2, join=True)
+    (n0, out0), (n1, out1) = results[0], results[1]
+    assert n0 + n1 == 5 and n0 >= 2 and n1 >= 2
+    for a, b in zip(out0, out1):
+        assert a.dtype == torch.bfloat16 and torch.equal(a, b)
+    for got, p in zip(out0, tp_common.gptq_problems()):
+        want = OG.compensate_weight(p["weight"].float(), p["hessian"], p["tokens"], OT.quantization_map("int4"),
+                                    OT.quantization_map("fp8_e5m3"), 7.0, 32, 0.01, False, True, False)
+        assert float((got.float() == want.bfloat16().float()).float().mean()) >= 0.99

@@ -115,3 +115,39 @@ def run_rank_fp8_layer(rank, world, port, results):
             results["out"] = out.cpu()
     finally:
         dist.destroy_process_group()
+
+
+def gptq_problems(device="cpu"):
+    g = torch.Generator().manual_seed(5)
+    problems = []
+    for out_f, in_f in ((64, 256), (32, 128), (96, 256), (32, 128), (64, 128)):
+        x = torch.randn(1024, in_f, generator=g)
+        problems.append(dict(weight=(torch.randn(out_f, in_f, generator=g) * 0.02).bfloat16().to(device),
+                             hessian=(x.T @ x).to(device), tokens=1024))
+    return problems
+
+
+def run_rank_gptq(rank, world, port, results):
+    """Layer-parallel GPTQ with the device solve on every rank's own GPU, results exchanged over NCCL."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        import voyager_b200
+
+        dev = f"cuda:{rank}"
+        G, P = voyager_b200.gptq, voyager_b200.parallel
+        fq = G.grid_of(OT.quantization_map("int4").to(dev), OT.quantization_map("fp8_e5m3").to(dev), 7.0, 32)
+        solved = []
+
+        def solve(p):
+            solved.append(tuple(p["weight"].shape))
+            return G.compensate_weight(p["weight"].float(), p["hessian"].clone(), p["tokens"], fq, 0.01, act_order=False)
+
+        out = P.gptq_layer_parallel(gptq_problems(dev), solve)
+        torch.cuda.synchronize()
+        results[rank] = (len(solved), [o.cpu() for o in out])
+    finally:
+        dist.destroy_process_group()

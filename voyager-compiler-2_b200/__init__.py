@@ -14,6 +14,7 @@ from . import parallel  # noqa: F401
 from . import nvfp4  # noqa: F401
 from . import fake_quant  # noqa: F401  (registers torch.ops.quantization.*)
 from . import kivi  # noqa: F401
+from . import packed  # noqa: F401
 from . import training  # noqa: F401  (registers torch.ops.voyager_gpu.rmsnorm_backward)
 from . import observers  # noqa: F401
 from . import outliers  # noqa: F401  (adds the outlier operators to torch.ops.quantized_ops)

@@ -120,6 +120,11 @@ SIGNATURES = {
     "vq_pack_nvfp4": [_P, _P, _P, _P, _I64, _I64, _P, _P],
     "vq_gemm_nvfp4": [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
     "vq_gemm_nvfp4_ex": [_P, _P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _I, _P],
+    "vq_gemm_lut4_workspace_floats": [_I64, _I64, _I64],
+    "vq_gemm_lut4_counters": [_I64],
+    "vq_gemm_lut4": [_P, _I64, _P, _P, _I, _I64, _P, _P, _P, _I, _P, _I, _I64, _I64, _P, _I, _P, _I, _P, _P, _P],
+    "vq_pack_lut4": [_P, _P, _I64, _I64, _P, _P],
+    "vq_kivi_read_2bit": [_P, _P, _P, _P, _I64, _I64, _I64, _I, _I64, _P],
     "vq_gptq_block": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _F, _F, _I, ctypes.POINTER(VqRound),
                       ctypes.POINTER(VqRound), _P],
     "vq_gptq_update": [_P, _P, _P, _I64, _I64, _I64, _I64, _P],
@@ -138,6 +143,8 @@ SIGNATURES = {
     "vq_transpose_quantize_fp8": [_P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _P, _I, _P],
 }
 IN_BF16, IN_F16, IN_E4M3, IN_E5M2 = range(4)
+_INT64_RESULTS = ("vq_nvfp4_scale_bytes", "vq_rmsnorm_backward_programs", "vq_gemm_lut4_workspace_floats",
+                  "vq_gemm_lut4_counters")
 
 
 def sources():
@@ -194,7 +201,7 @@ def lib():
         for name, argtypes in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
-            fn.restype = ctypes.c_int64 if name in ("vq_nvfp4_scale_bytes", "vq_rmsnorm_backward_programs") else ctypes.c_int
+            fn.restype = ctypes.c_int64 if name in _INT64_RESULTS else ctypes.c_int
         handle.vq_last_error.restype = ctypes.c_char_p
         handle.vq_last_error.argtypes = []
         _lib = handle

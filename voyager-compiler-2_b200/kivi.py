@@ -74,8 +74,41 @@ class PackedCache:
 
     def read(self, output_qmap: Optional[torch.Tensor] = None) -> torch.Tensor:
         """The cache's values, optionally re-encoded through ``output_qmap`` in the same pass."""
+        fast = self._fast_layout() if output_qmap is None else None
+        if fast is not None:
+            return _read_2bit(self, *fast)
         return unpack_dequantize(self.packed, self.bits, self.shape, self.scale, self.zero_point, self.block_size,
                                  output_qmap)
+
+    def _fast_layout(self):
+        """``(outer, T, D, along_channels)`` when the streaming 2-bit kernel applies: bfloat16 parameters,
+        groups along one of the last two axes, whole groups, channels a multiple of 8."""
+        if self.bits != 2 or self.scale.dtype != torch.bfloat16 or self.zero_point.dtype != torch.bfloat16 \
+                or len(self.shape) < 2 or len(self.axes) != 1:
+            return None
+        nd = len(self.shape)
+        axis = self.axes[0] % nd
+        T, D = self.shape[-2], self.shape[-1]
+        outer = 1
+        for extent in self.shape[:-2]:
+            outer *= extent
+        bs = self.block_size
+        if D % 8 or not self.scale.is_contiguous() or not self.zero_point.is_contiguous():
+            return None
+        if axis == nd - 1 and bs >= 8 and bs & (bs - 1) == 0 and D % bs == 0:
+            return outer, T, D, 1
+        if axis == nd - 2 and T % bs == 0:
+            return outer, T, D, 0
+        return None
+
+
+@N.device_guarded
+def _read_2bit(cache: "PackedCache", outer, T, D, along_channels) -> torch.Tensor:
+    out = torch.empty(cache.shape, dtype=torch.bfloat16, device=cache.packed.device)
+    N.check(N.lib().vq_kivi_read_2bit(cache.packed.data_ptr(), cache.scale.data_ptr(), cache.zero_point.data_ptr(),
+                                      out.data_ptr(), outer, T, D, along_channels, cache.block_size, _stream()),
+            "vq_kivi_read_2bit")
+    return out
 
 
 def quantize_cache(x: torch.Tensor, qmap: torch.Tensor, axis: int, block_size: int, bits: int,

@@ -427,3 +427,80 @@ class Nvfp4Model:
         return NV.nvfp4_linear(codes, scales, wc, ws, (t * tw).float(), self.one, None)
 
     __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# MXNF4 decode step with a KIVI cache
+# ---------------------------------------------------------------------------
+class Mxnf4DecodeLayer:
+    """One decode step of a decoder layer in the MXNF4 recipe (``lut4_to_int6`` with NF4 levels, blocks
+    of 64, ``fp8_e5m3`` scales on weights and activations; residual adds through a per-tensor
+    ``fp8_e4m3`` cast; KIVI 2-bit cache with the newest positions in bfloat16) for a batch of sequences
+    that each add one token.
+
+    Weights live packed (``packed.PackedLUT4Weight``, q/k/v and gate/up merged row-wise: microscaling
+    weights carry only per-block scales, so stacking rows changes nothing) and every linear is one
+    activation ``quantize_mx`` plus the weight-streaming ``linear_lut4``.  The cached keys and values
+    are packed 2-bit codes read back by the fused unpack + dequantize kernel; the attention itself is
+    bfloat16 torch operators over [cache | recent] keys, as in the graph.
+    """
+
+    def __init__(self, weights, tables, cache, residual_scale, shape: LlamaShape):
+        self.w, self.t, self.cache, self.shape = weights, tables, cache, shape
+        self.residual_scale = residual_scale
+        self.ln1, self.ln2 = weights["ln1"], weights["ln2"]
+
+    # kernels of this package per step: 4 quantize_mx, 4 linears, 2 cache reads, 2 x (quantize + dequantize)
+    LAUNCHES = 14
+
+    def _linear(self, x, name):
+        from . import packed as P
+
+        t = self.t
+        s, c = torch.ops.quantized_ops.quantize_mx(x, t["index"], [-1], 64, 31.0, False, t["e5m3"], t["mid"])
+        return P.linear_lut4(c, self.w[name], input_scale=s, input_code=t["levels"])
+
+    def _through_fp8(self, x):
+        q = torch.ops.quantized_ops.quantize(x, self.residual_scale, None, None, None, self.t["e4m3"])
+        return torch.ops.quantized_ops.dequantize(q, self.residual_scale)
+
+    def forward(self, x, rope):
+        """``x [B, hidden]``; ``rope = (cos, sin)`` of the new position, ``[head_dim]`` each."""
+        sh = self.shape
+        B, d, hq, hkv = x.shape[0], sh.head_dim, sh.heads, sh.kv_heads
+        cos, sin = rope
+        half = d // 2
+
+        def rotate(v):
+            return v * cos + torch.cat([-v[..., half:], v[..., :half]], -1) * sin
+
+        qkv = self._linear(F.rms_norm(x, (sh.hidden,), self.ln1, sh.eps), "qkv")
+        q = rotate(qkv[:, :hq * d].reshape(B, hq, d))
+        k = rotate(qkv[:, hq * d:(hq + hkv) * d].reshape(B, hkv, d))
+        v = qkv[:, (hq + hkv) * d:].reshape(B, hkv, d)
+        k_res, v_res = self.cache["k_res"], self.cache["v_res"]
+        k_res[:, :, -1].copy_(k)                   # this step's token takes the last recent slot
+        v_res[:, :, -1].copy_(v)
+        k_main, v_main = self.cache["k"].read(), self.cache["v"].read()
+        qg = q.reshape(B, hkv, hq // hkv, d)
+        scores = torch.cat([torch.matmul(qg, k_main.transpose(-1, -2)), torch.matmul(qg, k_res.transpose(-1, -2))], -1)
+        p = torch.softmax(scores * (1.0 / math.sqrt(d)), -1, dtype=torch.float32).to(x.dtype)
+        tm = k_main.shape[-2]
+        ctx = torch.matmul(p[..., :tm], v_main) + torch.matmul(p[..., tm:], v_res)
+        x1 = self._through_fp8(x) + self._linear(ctx.reshape(B, hq * d), "o")
+        gu = self._linear(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps), "gate_up")
+        inter = gu.shape[-1] // 2
+        return self._through_fp8(x1) + self._linear(F.silu(gu[:, :inter]) * gu[:, inter:], "down")
+
+    __call__ = forward
+
+
+def nf4_tables(device):
+    """The lookup tables of ``lut4_to_int6`` as a converted graph holds them (``quantize_pt2e.py:754-791``):
+    the 16 levels, the 65 536-entry index table, the midpoints, plus the scale and residual tables."""
+    nf4 = formats.get_quantization_map("lut4_to_int6", device)
+    index, levels = formats.index_table(nf4)
+    return {"levels": levels, "index": index, "mid": (levels[:-1] + levels[1:]) / 2,
+            "e5m3": formats.get_quantization_map("fp8_e5m3", device),
+            "e4m3": formats.get_quantization_map("fp8_e4m3", device),
+            "uint2": formats.get_quantization_map("uint2", device)}
