@@ -318,6 +318,21 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
                   int64_t strideB, int64_t strideC, const void* alpha, int alpha_dtype, const void* bias,
                   int bias_dtype, const VqGemmEpilogue* epi, void* stream);
 
+/* The contraction of linear_mx / matmul_mx (ops/quantized.py:662-805) taken straight from
+ * the block-scaled operands: C = alpha * (bf16(A * a_scale) . bf16(B * b_scale)^T) + bias with
+ * A [batch, M, K] and B [batch or 1, N, K] bfloat16 codes, K contiguous, and one bfloat16 scale
+ * per `block_size` consecutive elements of K ([batch, M, ceil(K / block_size)] and
+ * [batch or 1, N, ceil(K / block_size)], contiguous; a null scale pointer takes that operand
+ * as it is).  The product code * scale is rounded to bfloat16 once, as _decode_and_scale
+ * (ops/quantized.py:574-591) does, but inside the GEMM's main loop: the dequantized
+ * operands are never written to device memory.  block_size is a power of two >= 8.
+ * Alignment rules, alpha and bias as vq_gemm_tn.  VQ_EUNSUPPORTED on a device that cannot
+ * co-schedule CTA pairs (the caller then dequantizes and calls vq_gemm_tn). */
+int vq_gemm_mx(const void* A, const void* a_scale, const void* B, const void* b_scale, int64_t block_size, void* C,
+               int out_dtype, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch,
+               int64_t strideA, int64_t strideB, int64_t strideC, const void* alpha, int alpha_dtype,
+               const void* bias, int bias_dtype, void* stream);
+
 /* Real FP8 codes for the tensor-core GEMM, the cast the reference's GPU backend
  * makes before torch._scaled_mm (backend/gpu/fp8.py:253-309): out[i] is the
  * e4m3 / e5m2 byte of round_bf16(in[i] / scale), i.e. the byte encoding of the

@@ -99,3 +99,102 @@ def test_linear_mx_config1_shape():
     a = OQ.decode_and_scale(cx, sx, None, 16).double()
     b = OQ.decode_and_scale(cw, sw, None, 16).double()
     assert rel_err(y32, a @ b.T) <= 2e-5
+
+
+# ---------------------------------------------------------------------------
+# Block scales applied inside the GEMM's main loop (vq_gemm_mx): the same operands, tiles and
+# summation order as dequantize-then-GEMM, so the two must agree bit for bit.
+# ---------------------------------------------------------------------------
+def _mx_problem(batch, m, n, k, bs, seed, scaled=("a", "b"), batched_weight=False):
+    import voyager_b200
+
+    g = torch.Generator().manual_seed(seed)
+    table = voyager_b200.get_quantization_map("int8").cuda()
+    a = torch.randn(*batch, m, k, generator=g).bfloat16().cuda()
+    b = (torch.randn(*(batch if batched_weight else ()), n, k, generator=g) * 0.05).bfloat16().cuda()
+    q = torch.ops.quantized_ops.quantize_mx
+    sa, ca = q(a, table, [-1], bs, 127.0, True) if "a" in scaled else (None, a)
+    sb, cb = q(b, table, [-1], bs, 127.0, True) if "b" in scaled else (None, b)
+    return ca, sa, cb, sb
+
+
+@pytest.mark.parametrize("batch,m,n,k,bs", [
+    ((), 300, 200, 264, 8), ((), 129, 8, 64, 32), ((), 2048, 4096, 4096, 32), ((), 1000, 520, 200, 32),
+    ((), 512, 384, 1024, 16), ((), 640, 256, 512, 64), ((), 257, 136, 768, 128), ((), 384, 640, 1024, 256),
+    ((3,), 200, 264, 128, 32), ((2, 2), 160, 96, 320, 16),
+])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_mx_gemm_in_mainloop_equals_dequantize_then_gemm(batch, m, n, k, bs, out_dtype, monkeypatch):
+    import voyager_b200
+    from voyager_b200 import ops
+
+    monkeypatch.setattr(ops, "MX_IN_MAINLOOP", "always")
+    ca, sa, cb, sb = _mx_problem(batch, m, n, k, bs, seed=m + n + k + bs)
+    bias = torch.randn(n, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    alpha = torch.tensor(0.75, device="cuda")
+    got = torch.ops.quantized_ops.linear_mx(ca, cb, bias, input_scale=sa, weight_scale=sb, block_size=bs,
+                                            alpha=alpha, out_dtype=out_dtype)
+    da = ops._decode_and_scale(ca, sa, None, bs)
+    db = ops._decode_and_scale(cb, sb, None, bs)
+    want = ops.gemm_tn(da, db, out_dtype=out_dtype, alpha=alpha, bias=bias)
+    _status()
+    assert got.shape == want.shape and got.dtype == want.dtype
+    assert torch.equal(got, want), describe_mismatch(got.cpu(), want.cpu())
+    ref = 0.75 * (da.double() @ db.double().mT) + bias.double()
+    assert rel_err(got, ref) <= (2e-5 if out_dtype == torch.float32 else REL_TOL)
+
+
+@pytest.mark.parametrize("scaled", [("a",), ("b",)])
+def test_mx_gemm_in_mainloop_one_scaled_operand(scaled, monkeypatch):
+    from voyager_b200 import ops
+
+    monkeypatch.setattr(ops, "MX_IN_MAINLOOP", "always")
+    ca, sa, cb, sb = _mx_problem((), 384, 320, 512, 32, seed=5, scaled=scaled)
+    got = torch.ops.quantized_ops.linear_mx(ca, cb, None, input_scale=sa, weight_scale=sb, block_size=32)
+    want = ops.gemm_tn(ops._read_operand(ca, sa, None, 32), ops._read_operand(cb, sb, None, 32))
+    _status()
+    assert torch.equal(got, want)
+
+
+def test_mx_gemm_in_mainloop_batched_weight(monkeypatch):
+    from voyager_b200 import ops
+
+    monkeypatch.setattr(ops, "MX_IN_MAINLOOP", "always")
+    ca, sa, cb, sb = _mx_problem((4,), 256, 192, 128, 32, seed=9, batched_weight=True)
+    got = ops._mx_gemm_in_mainloop(ops.LINEAR_LAYOUT, ca, cb, None, sa, sb, 32, None, ops.LINEAR_LAYOUT, torch.bfloat16)
+    assert got is not None
+    want = ops.gemm_tn(ops._decode_and_scale(ca, sa, None, 32), ops._decode_and_scale(cb, sb, None, 32))
+    _status()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("m", [1, 16, 100, 128])
+def test_mx_gemm_in_mainloop_few_rows(m, monkeypatch):
+    """At most 128 rows: the second CTA of each pair multiplies zero padding; the result is the same."""
+    from voyager_b200 import ops
+
+    monkeypatch.setattr(ops, "MX_IN_MAINLOOP", "always")
+    ca, sa, cb, sb = _mx_problem((), m, 520, 1024, 32, seed=m)
+    got = torch.ops.quantized_ops.linear_mx(ca, cb, None, input_scale=sa, weight_scale=sb, block_size=32,
+                                            out_dtype=torch.float32)
+    da, db = ops._decode_and_scale(ca, sa, None, 32), ops._decode_and_scale(cb, sb, None, 32)
+    _status()
+    assert rel_err(got, da.double() @ db.double().T) <= 2e-5
+
+
+def test_mx_gemm_in_mainloop_is_the_path_a_weight_bound_linear_mx_takes(monkeypatch):
+    """A K-contiguous block-scaled bfloat16 linear whose read-back would cost more than the transform warps do
+    launches no read-back kernel; a compute-bound one keeps the read-back."""
+    from voyager_b200 import ops
+
+    calls = []
+    real = ops._decode_and_scale
+    monkeypatch.setattr(ops, "_decode_and_scale", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    ca, sa, cb, sb = _mx_problem((), 256, 4096, 1024, 32, seed=2)
+    torch.ops.quantized_ops.linear_mx(ca, cb, None, input_scale=sa, weight_scale=sb, block_size=32)
+    assert not calls
+    ca, sa, cb, sb = _mx_problem((), 4096, 4096, 1024, 32, seed=3)
+    torch.ops.quantized_ops.linear_mx(ca, cb, None, input_scale=sa, weight_scale=sb, block_size=32)
+    assert len(calls) == 2
+    assert not ops._in_mainloop_pays(2048, 4096, 4096, 1, True, True, True)
+    assert ops._in_mainloop_pays(16, 4096, 4096, 1, True, True, True)

@@ -114,6 +114,8 @@ SIGNATURES = {
     "vq_gemm_tn": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P],
     "vq_gemm_tn_ex": [_P, _P, _P, _I, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I,
                       ctypes.POINTER(VqGemmEpilogue), _P],
+    "vq_gemm_mx": [_P, _P, _P, _P, _I64, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I,
+                   _P],
     "vq_gemm_status": [_I],
     "vq_nvfp4_scale_bytes": [_I64, _I64],
     "vq_quantize_nvfp4": [_P, _P, _I, _P, _P, _I64, _I64, _P],

@@ -12,13 +12,15 @@
 // the result differs from the operator's dequantize-then-matmul in summation order only.
 //
 // The kernel is bound by HBM (the weight bytes) and, next, by instruction issue (decoding a weight
-// is a table lookup and a multiply).  A CTA owns 128 weight rows x one K slice of 1024:
+// is a table lookup and a multiply).  A CTA owns 256 weight rows x one K slice (1024, or 512 for small weights):
 //   * prologue: the activation slice is decoded into shared memory once (M x 1024 bfloat16, the
 //     four elements a lane needs per MMA step stored so that a warp's loads touch every bank once)
 //     and a 256-entry table maps a packed byte to its two codebook values as a bfloat16 pair --
-//     one copy per lane, because the lookups are what the loop does most and 32 random indices
-//     into a single table would collide on banks about 3.5-fold;
-//   * eight warps of 16 rows each stream the weight slice with 16-byte loads (32 weights per
+//     one copy per lane (32 random indices into a single table would collide on banks about
+//     3.5-fold), rows 256 bytes apart at a 64 KB-aligned shared address, because the lookups are
+//     what the loop does most and this makes a lookup three instructions: byte-permute (address),
+//     load, packed multiply (scale);
+//   * sixteen warps of 16 rows each stream the weight slice with 16-byte loads (32 weights per
 //     lane and load, two rows per lane in flight), look both nibbles of a byte up with one
 //     shared-memory load, scale them with one packed multiply and feed mma.sync m16n8k16 --
 //     M = 16 activation rows is exactly the instruction's height, the tensor-core form that fits a
@@ -36,11 +38,15 @@ namespace vq {
 namespace {
 
 constexpr int L4_ROWS_PER_WARP = 16;
-constexpr int L4_WARPS = 8;
-constexpr int L4_ROWS = L4_ROWS_PER_WARP * L4_WARPS;   // 128 weight rows per CTA
-constexpr int L4_KC = 1024;                            // K slice per CTA
+constexpr int L4_WARPS = 16;
+constexpr int L4_ROWS = L4_ROWS_PER_WARP * L4_WARPS;   // 256 weight rows per CTA
+constexpr int L4_KC = 1024;                            // longest K slice per CTA
 constexpr int L4_THREADS = 32 * L4_WARPS;
-constexpr int L4_TABLE_BYTES = 256 * 32 * 4;          // the per-lane copies of the byte table
+// The byte table: one 256-byte row per byte value, lane l reading word l of the row.  It sits at
+// shared-memory address 0x10000, so that a lookup address is the lane's base address with its second
+// byte replaced by the packed byte -- one byte-permute instruction, no shift, mask or add.
+constexpr uint32_t L4_TABLE_ADDR = 0x10000u;
+constexpr int L4_TABLE_BYTES = 256 * 256;
 constexpr int L4_APAD = 16;                            // bfloat16 elements of padding per activation row (bank spread)
 
 struct Lut4Params {
@@ -62,6 +68,8 @@ struct Lut4Params {
   float* workspace;         // [k_slices][row_tiles][M_pad][128]
   int* counters;            // [row_tiles], zero between launches
   int k_slices, row_tiles;
+  int kc;                   // K slice length (a multiple of 128, at most L4_KC)
+  int a_after_table;        // the activation slice lies behind the table (two row tiles of activations)
 };
 
 __device__ __forceinline__ float lparam(const void* p, int64_t i, int dt) {
@@ -87,13 +95,16 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t v, uint32_t s) {
 
 // MT: 16-row activation tiles (1 or 2).
 template <int MT>
-__global__ void __launch_bounds__(L4_THREADS, 2)
+__global__ void __launch_bounds__(L4_THREADS, 1)
 gemm_lut4_kernel(Lut4Params p) {
   extern __shared__ __align__(16) uint8_t l4_smem[];
-  // byte -> its two codebook values, one copy per lane ([256][32] words): lane l only ever reads bank l, so
-  // a warp's 32 lookups of 32 different bytes are one conflict-free shared-memory access
-  uint32_t* table = reinterpret_cast<uint32_t*>(l4_smem);
-  __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(l4_smem + L4_TABLE_BYTES);  // [MT * 16][L4_KC + pad]
+  // dynamic shared memory starts a little above the window's first kilobyte; the table is placed so that
+  // its shared address is exactly L4_TABLE_ADDR, the activation slice before it (or behind it when large)
+  const uint32_t dyn_base = (uint32_t)__cvta_generic_to_shared(l4_smem);
+  const uint32_t table_offset = L4_TABLE_ADDR - dyn_base;
+  uint32_t* table = reinterpret_cast<uint32_t*>(l4_smem + table_offset);           // [256][64 words], 32 used
+  __nv_bfloat16* sa = reinterpret_cast<__nv_bfloat16*>(
+      l4_smem + (p.a_after_table ? table_offset + L4_TABLE_BYTES : ((16u - (dyn_base & 15u)) & 15u)));   // [MT * 16][L4_KC + pad]
   constexpr int SA_LD = L4_KC + L4_APAD;
   __shared__ int s_last;
   __shared__ float a_levels[256];                                                  // the activation's codebook
@@ -101,8 +112,8 @@ gemm_lut4_kernel(Lut4Params p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int slice = blockIdx.y;
-  const int k0 = slice * L4_KC;
-  const int kc = min(L4_KC, p.K - k0);                                             // a multiple of 128
+  const int k0 = slice * p.kc;
+  const int kc = min(p.kc, p.K - k0);                                              // a multiple of 128
 
   // ---- prologue: byte table and the decoded activation slice ----
   __shared__ uint16_t w_levels[16];
@@ -112,7 +123,7 @@ gemm_lut4_kernel(Lut4Params p) {
   __syncthreads();
   for (int i = threadIdx.x; i < 256 * 32; i += L4_THREADS) {
     const int byte = i >> 5;
-    table[i] = (uint32_t)w_levels[byte & 15] | ((uint32_t)w_levels[byte >> 4] << 16);   // even element in the low half
+    table[byte * 64 + (i & 31)] = (uint32_t)w_levels[byte & 15] | ((uint32_t)w_levels[byte >> 4] << 16);   // even element low
   }
   {
     const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.a);
@@ -177,8 +188,8 @@ gemm_lut4_kernel(Lut4Params p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[mt][j][e] = 0.0f;
 
-  // Shared-memory addresses as 32-bit offsets: the table copy of this lane, and this lane's activation rows.
-  const uint32_t tb_lane = (uint32_t)__cvta_generic_to_shared(table) + 4u * lane;
+  // This lane's column of the table as a 32-bit shared address; its second byte is zero.
+  const uint32_t tb_lane = L4_TABLE_ADDR + 4u * lane;
   const int row_bytes = p.K >> 1;
   const int blocks_per_row = p.K / p.bs;
   const int bs_shift = 31 - __clz(p.bs);                  // the block size is a power of two (32, 64, 128, ...)
@@ -204,9 +215,10 @@ gemm_lut4_kernel(Lut4Params p) {
       v.s[j] = h | (h << 16);
     }
   };
-  auto lookup = [&](uint32_t offset) {
+  // the table entry of byte `which` (0..3) of `word`: address = tb_lane with byte 1 replaced by that byte
+  auto lookup = [&](uint32_t word, int which) {
     uint32_t r;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(tb_lane + offset));
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(__byte_perm(word, tb_lane, 0x7604u | ((uint32_t)which << 4))));
     return r;
   };
   // the eight MMA steps of one iteration: step s takes bytes 2 s and 2 s + 1 of each row's 16-byte vector
@@ -224,11 +236,8 @@ gemm_lut4_kernel(Lut4Params p) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const uint32_t word = s < 2 ? v.w[j].x : s < 4 ? v.w[j].y : s < 6 ? v.w[j].z : v.w[j].w;
-        // a byte's table row starts 128 bytes after the previous byte's: (byte << 7), taken straight from the word
-        const uint32_t off0 = (s & 1) ? ((word >> 9) & 0x7F80u) : ((word << 7) & 0x7F80u);
-        const uint32_t off1 = (s & 1) ? ((word >> 17) & 0x7F80u) : ((word >> 1) & 0x7F80u);
-        const uint32_t b0 = mul_bf16x2(lookup(off0), v.s[j]);                      // weights k, k + 1
-        const uint32_t b1 = mul_bf16x2(lookup(off1), v.s[j]);                      // weights k + 2, k + 3
+        const uint32_t b0 = mul_bf16x2(lookup(word, 2 * (s & 1)), v.s[j]);         // weights k, k + 1
+        const uint32_t b1 = mul_bf16x2(lookup(word, 2 * (s & 1) + 1), v.s[j]);     // weights k + 2, k + 3
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) mma_bf16_16816(acc[mt][j], af[mt][0], af[mt][1], af[mt][2], af[mt][3], b0, b1);
       }
@@ -313,10 +322,17 @@ using namespace vq;
 
 extern "C" {
 
+// K slice length: 1024, or 512 when the weight has too few 256-row tiles to give every SM a CTA
+static int lut4_slice_length(int64_t N, int64_t K) {
+  const int64_t tiles = (N + L4_ROWS - 1) / L4_ROWS;
+  return tiles * ((K + L4_KC - 1) / L4_KC) < kSmCount && K > 512 ? 512 : L4_KC;
+}
+
 int64_t vq_gemm_lut4_workspace_floats(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const int64_t m_pad = M <= 16 ? 16 : 32;
-  const int64_t slices = (K + L4_KC - 1) / L4_KC, tiles = (N + L4_ROWS - 1) / L4_ROWS;
+  const int64_t kc = lut4_slice_length(N, K);
+  const int64_t slices = (K + kc - 1) / kc, tiles = (N + L4_ROWS - 1) / L4_ROWS;
   return slices * tiles * m_pad * L4_ROWS;
 }
 
@@ -357,21 +373,27 @@ int vq_gemm_lut4(const void* a, int64_t lda, const void* a_scale, const void* a_
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.bs = block_size; p.lda = lda;
   p.alpha = alpha; p.alpha_dt = alpha_dtype; p.bias = bias; p.bias_dt = bias_dtype;
   p.workspace = workspace; p.counters = counters;
-  p.k_slices = (int)((K + L4_KC - 1) / L4_KC);
+  p.kc = lut4_slice_length(N, K);
+  p.k_slices = (int)((K + p.kc - 1) / p.kc);
   p.row_tiles = (int)((N + L4_ROWS - 1) / L4_ROWS);
   VQ_REQUIRE(p.k_slices <= 65535, "vq_gemm_lut4: K too large");
   const int mt = M <= 16 ? 1 : 2;
-  const size_t smem = L4_TABLE_BYTES + (size_t)mt * 16 * (L4_KC + L4_APAD) * sizeof(__nv_bfloat16);
+  // Shared memory: the table must sit at shared address L4_TABLE_ADDR.  Dynamic memory starts somewhere in
+  // [1 KB, 4 KB) of the window (system + static variables), so reserving up to the table's end measured from
+  // 1 KB always suffices; one row tile of activations (33 KB) fits before the table, two go behind it.
+  const int a_bytes = mt * 16 * (L4_KC + L4_APAD) * (int)sizeof(__nv_bfloat16);
+  p.a_after_table = mt == 2;
+  const size_t smem = (size_t)L4_TABLE_ADDR + L4_TABLE_BYTES - 1024 + (p.a_after_table ? a_bytes : 0);
   static unsigned long long configured = 0;
   if (first_call_on_device(&configured)) {
     cudaFuncSetAttribute(gemm_lut4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         L4_TABLE_BYTES + 16 * (L4_KC + L4_APAD) * 2);
+                         (int)L4_TABLE_ADDR + L4_TABLE_BYTES - 1024);
     cudaFuncSetAttribute(gemm_lut4_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         L4_TABLE_BYTES + 32 * (L4_KC + L4_APAD) * 2);
+                         (int)L4_TABLE_ADDR + L4_TABLE_BYTES - 1024 + 32 * (L4_KC + L4_APAD) * 2);
   }
-  // about four CTAs per SM in all; with many row tiles a CTA takes several of them, one after the other, and
-  // decodes its activation slice once
-  const int per_slice = (4 * kSmCount + p.k_slices - 1) / p.k_slices;
+  // about two CTAs' worth of row tiles per SM in all; with many row tiles a CTA takes several of them, one
+  // after the other, and decodes its activation slice once
+  const int per_slice = (2 * kSmCount + p.k_slices - 1) / p.k_slices;
   dim3 grid((unsigned)(p.row_tiles < per_slice ? p.row_tiles : per_slice), (unsigned)p.k_slices);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (mt == 1) gemm_lut4_kernel<1><<<grid, L4_THREADS, smem, st>>>(p);

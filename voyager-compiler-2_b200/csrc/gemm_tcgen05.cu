@@ -827,6 +827,330 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------
+// Block-scaled (MX) operands dequantized inside the main loop.  The GEMM of
+// linear_mx / matmul_mx multiplies bf16(code * scale) values, the scale shared by
+// `block` consecutive elements of K.  This kernel is the CTA-pair kernel above with
+// one more role: four "transform" warps per CTA take each stage as TMA delivers it
+// (the raw codes), multiply it in place by the rows' block scales (mul.rn.bf16x2:
+// the one bfloat16 rounding the separate read-back pass applies) and only then hand
+// it to the MMA thread.  The dequantized operands never exist in device memory.
+//   full_bar[s]  : per CTA; its own producer arms it with the CTA's own bytes
+//   ready_bar[s] : lives in the even CTA; 8 arrivals (4 transform warps x 2 CTAs)
+//   empty_bar[s], acc_full, acc_empty: as in the pair kernel
+// A transform thread owns one row of the CTA's A tile and the same row of its B half; a row
+// of a stage is eight 16-byte chunks, chunk c of row r sitting at ((c ^ (r & 7)) << 4) under
+// the 128-byte swizzle.  Every stage costs a tile's CTA 64 KB of shared-memory traffic on top of
+// the 32 KB the tensor core reads, and is repeated for every tile that shares the operand rows: this
+// kernel wins where the read-back pass it replaces is a large part of the time (weight-bound
+// shapes, a single wave of tiles) and loses on compute-bound ones; the caller chooses.
+// ---------------------------------------------------------------------------
+constexpr int MX_XFORM_WARPS = 4;
+constexpr int MX_ROWS_PER_THREAD = 128 / (32 * MX_XFORM_WARPS);
+// Four warpgroups: {TMA warp, MMA warp, two idle warps}, two epilogue warpgroups (one per half of the
+// tile's columns; a warp's position in its group is its tensor-memory lane quarter), the transform warps.
+// The kernel starts with 128 registers per thread and redistributes them by role: 40 / 184 / 184 / 104.
+constexpr int MX_THREADS = 512;
+constexpr int MX_EPI_WARP0 = 4;            // first epilogue warp
+constexpr int MX_XFORM_WARP0 = 12;         // first transform warp
+
+struct MxScales {
+  const __nv_bfloat16* a;   // [batch, M, lds_a] or null (operand taken as is)
+  const __nv_bfloat16* b;   // [batch, N, lds_b] or null
+  int64_t lds_a, lds_b, stride_a, stride_b;
+  int shift;                // block size = 1 << shift elements of K
+};
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// Scales of one row for the stage starting at element k0: one per 16-byte chunk, duplicated into
+// both halves of a word.  `count` scales exist in the row; indices past the end (the zero-filled
+// tail of K) reuse the last one.
+__device__ __forceinline__ void load_row_scales(const __nv_bfloat16* row, int64_t count, int k0, int shift,
+                                                uint32_t (&s)[8]) {
+  const unsigned short* r16 = reinterpret_cast<const unsigned short*>(row);
+  if (shift >= 6) {
+    int64_t i = k0 >> shift;
+    if (i >= count) i = count - 1;
+    const uint32_t v = __ldg(r16 + i);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) s[c] = v | (v << 16);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      int64_t i = (k0 + 8 * c) >> shift;
+      if (i >= count) i = count - 1;
+      const uint32_t v = __ldg(r16 + i);
+      s[c] = v | (v << 16);
+    }
+  }
+}
+
+// The same from a 16-byte group of eight consecutive scales of the row (`q`, scales 8g .. 8g + 7, loaded
+// once per group instead of once per chunk): `sidx` is the index of the stage's first scale.
+__device__ __forceinline__ uint32_t dup_half(uint32_t w, int hi) { return __byte_perm(w, 0, hi ? 0x3232 : 0x1010); }
+__device__ __forceinline__ uint32_t pick_word(const uint4& q, int i) {
+  return i == 0 ? q.x : i == 1 ? q.y : i == 2 ? q.z : q.w;
+}
+__device__ __forceinline__ void chunk_scales(const uint4& q, int sidx, int shift, uint32_t (&s)[8]) {
+  const int base = sidx & 7;
+  const uint32_t w0 = pick_word(q, base >> 1);
+  if (shift == 3) {          // 8 scales per stage: the whole group
+#pragma unroll
+    for (int c = 0; c < 8; ++c) s[c] = dup_half(pick_word(q, c >> 1), c & 1);
+  } else if (shift == 4) {   // 4 per stage: two words
+    const uint32_t w1 = pick_word(q, (base >> 1) + 1);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) s[c] = dup_half(c < 4 ? w0 : w1, (c >> 1) & 1);
+  } else if (shift == 5) {   // 2 per stage: one word
+#pragma unroll
+    for (int c = 0; c < 8; ++c) s[c] = dup_half(w0, c >> 2);
+  } else {                   // one scale for the stage (and for 2^(shift-6) stages in a row)
+    const uint32_t v = dup_half(w0, base & 1);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) s[c] = v;
+  }
+}
+
+__device__ __forceinline__ void scale_row_in_place(uint8_t* tile, int r, const uint32_t (&s)[8]) {
+  uint8_t* row = tile + r * BK_BYTES;
+  uint4 v[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) v[c] = *reinterpret_cast<const uint4*>(row + ((c ^ (r & 7)) << 4));
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    v[c].x = mul_bf16x2(v[c].x, s[c]);
+    v[c].y = mul_bf16x2(v[c].y, s[c]);
+    v[c].z = mul_bf16x2(v[c].z, s[c]);
+    v[c].w = mul_bf16x2(v[c].w, s[c]);
+    *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = v[c];
+  }
+}
+
+template <int OUT_DT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MX_THREADS, 1)
+gemm_mx_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
+                    const __grid_constant__ GemmParams p, const __grid_constant__ MxScales sc) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + P_STAGES * P_A_BYTES;
+  uint8_t* epi_stage = smem + P_STAGES * (P_A_BYTES + P_B_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + P_STAGES * (P_A_BYTES + P_B_BYTES) + P_EPI_BUFS * EPI_STAGE_BYTES);
+  uint64_t* full_bar = bars;                        // [P_STAGES] per CTA
+  uint64_t* empty_bar = bars + P_STAGES;            // [P_STAGES]
+  uint64_t* ready_bar = bars + 2 * P_STAGES;        // [P_STAGES] (used in the even CTA)
+  uint64_t* acc_full = bars + 3 * P_STAGES;         // [2]
+  uint64_t* acc_empty = bars + 3 * P_STAGES + 2;    // [2] (used in the even CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * P_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int bn = p.bn;
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + bn - 1) / bn;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n * p.batch;
+  constexpr int k_per_stage = BK_BYTES / 2;
+  const int k_blocks = (p.K + k_per_stage - 1) / k_per_stage;
+  const uint32_t stage_tx_bytes = (uint32_t)(P_A_BYTES + (bn / 2) * BK_BYTES);   // this CTA's own loads
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+      mbar_init(&ready_bar[s], 2 * MX_XFORM_WARPS);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < MX_EPI_WARP0) {
+  reg_dealloc<40>();
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------
+    if (lane == 0) {
+      prefetch_tensormap(&map_a);
+      prefetch_tensormap(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m_blk = (int)(tile % tiles_m);
+        const int n_blk = (int)((tile / tiles_m) % tiles_n);
+        const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+        const int m0 = m_blk * 2 * BM + (int)rank * BM;
+        const int n0 = n_blk * bn + (int)rank * (bn / 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(&full_bar[stage], stage_tx_bytes);
+          tma_load_3d(smem_a + stage * P_A_BYTES, &map_a, &full_bar[stage], kb * k_per_stage, m0, b);
+          tma_load_3d(smem_b + stage * P_B_BYTES, &map_b, &full_bar[stage], kb * k_per_stage, n0, b);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&ready_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem_a + stage * P_A_BYTES);
+          const uint32_t b_addr = smem_u32(smem_b + stage * P_B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK_BYTES / MMA_K_BYTES; ++k) {
+            const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
+            const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
+            mma_f16_ss_pair(tmem_acc, da, db, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          mma_commit_pair(&empty_bar[stage], 0x3);
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit_pair(&acc_full[acc], 0x3);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  }
+  } else if (warp < MX_XFORM_WARP0) {
+    reg_alloc<184>();
+    // ------------------------------ epilogue (both CTAs) ----------------------
+    const int quarter = warp & 3;
+    const int chalf = (warp - MX_EPI_WARP0) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    uint32_t epi_buf = 0;
+    const bool has_alpha = p.alpha != nullptr;
+    const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int m_blk = (int)(tile % tiles_m);
+      const int n_blk = (int)((tile / tiles_m) % tiles_n);
+      const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
+      epilogue_warp_tile<OUT_DT, P_EPI_BUFS>(p, &map_c, taddr, epi_stage + (warp - MX_EPI_WARP0) * (P_EPI_BUFS * 32 * 128), epi_buf,
+                                             m_blk * 2 * BM + (int)rank * BM + quarter * 32, lane, n_blk * bn, b,
+                                             has_alpha, alpha, chalf * (bn / 2), (chalf + 1) * (bn / 2));
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  } else {
+    reg_dealloc<104>();
+    // ------------------------------ transform (both CTAs) ---------------------
+    const int t = threadIdx.x - MX_XFORM_WARP0 * 32;   // row of the tile (and the next after 32 x warps rows)
+    const int64_t count_a = sc.lds_a, count_b = sc.lds_b;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int m_blk = (int)(tile % tiles_m);
+      const int n_blk = (int)((tile / tiles_m) % tiles_n);
+      const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      const int m0 = m_blk * 2 * BM + (int)rank * BM;
+      const int n0 = n_blk * bn + (int)rank * (bn / 2);
+      const __nv_bfloat16* row_a[MX_ROWS_PER_THREAD];
+      const __nv_bfloat16* row_b[MX_ROWS_PER_THREAD];
+#pragma unroll
+      for (int h = 0; h < MX_ROWS_PER_THREAD; ++h) {
+        const int r = t + 32 * MX_XFORM_WARPS * h;
+        row_a[h] = (sc.a != nullptr && m0 + r < p.M) ? sc.a + b * sc.stride_a + (int64_t)(m0 + r) * sc.lds_a : nullptr;
+        row_b[h] = (sc.b != nullptr && r < bn / 2 && n0 + r < p.N) ? sc.b + b * sc.stride_b + (int64_t)(n0 + r) * sc.lds_b
+                                                                  : nullptr;
+      }
+      // Scale rows whose length is a multiple of eight are read 16 bytes (eight scales) at a time, one
+      // group ahead of its use; other lengths take one 2-byte load per chunk.
+      const bool grouped = ((count_a | count_b) & 7) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(sc.a) | reinterpret_cast<uintptr_t>(sc.b)) & 15) == 0;
+      uint4 cur[2 * MX_ROWS_PER_THREAD] = {}, nxt[2 * MX_ROWS_PER_THREAD] = {};
+      int cur_grp = -1;
+      auto load_group = [&](uint4 (&dst)[2 * MX_ROWS_PER_THREAD], int grp) {
+#pragma unroll
+        for (int h = 0; h < MX_ROWS_PER_THREAD; ++h) {
+          if (row_a[h] && (int64_t)grp * 8 < count_a) dst[h] = __ldg(reinterpret_cast<const uint4*>(row_a[h]) + grp);
+          if (row_b[h] && (int64_t)grp * 8 < count_b) dst[MX_ROWS_PER_THREAD + h] = __ldg(reinterpret_cast<const uint4*>(row_b[h]) + grp);
+        }
+      };
+      if (grouped) load_group(nxt, 0);
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        const int k0 = kb * k_per_stage;
+        const int sidx = k0 >> sc.shift;
+        if (grouped && (sidx >> 3) != cur_grp) {
+          cur_grp = sidx >> 3;
+#pragma unroll
+          for (int i = 0; i < 2 * MX_ROWS_PER_THREAD; ++i) cur[i] = nxt[i];
+          load_group(nxt, cur_grp + 1);
+        }
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&full_bar[stage], phase, abort_flag))) { ok = false; break; }
+        // one row at a time: the eight chunk scales live only while their row is in registers
+#pragma unroll
+        for (int h = 0; h < MX_ROWS_PER_THREAD; ++h) {
+          const int r = t + 32 * MX_XFORM_WARPS * h;
+          if (row_a[h]) {
+            uint32_t s8[8];
+            if (grouped) chunk_scales(cur[h], sidx, sc.shift, s8);
+            else load_row_scales(row_a[h], count_a, k0, sc.shift, s8);
+            scale_row_in_place(smem_a + stage * P_A_BYTES, r, s8);
+          }
+          if (row_b[h]) {
+            uint32_t s8[8];
+            if (grouped) chunk_scales(cur[MX_ROWS_PER_THREAD + h], sidx, sc.shift, s8);
+            else load_row_scales(row_b[h], count_b, k0, sc.shift, s8);
+            scale_row_in_place(smem_b + stage * P_B_BYTES, r, s8);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(&ready_bar[stage], 0));
+        if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
+  if (warp >= MX_EPI_WARP0 && warp < MX_XFORM_WARP0 && lane == 0) tma_store_wait_read();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // NVFP4 block-scaled GEMM: packed e2m1 operands (two per byte, K-contiguous), one
 // ue4m3 scale per 16 elements, multiplied by the tensor cores' native
 // kind::mxf4nvf4 MMA (K = 64 per instruction).  128x128 tiles, one CTA per SM.
@@ -1482,6 +1806,86 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
   const int grid = (int)(tiles < kSmCount ? tiles : kSmCount);
   VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_kernel)<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
   return check_launch("gemm_tn_kernel");
+}
+
+int vq_gemm_mx(const void* A, const void* a_scale, const void* B, const void* b_scale, int64_t block_size, void* C,
+               int out_dtype, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch,
+               int64_t strideA, int64_t strideB, int64_t strideC, const void* alpha, int alpha_dtype, const void* bias,
+               int bias_dtype, void* stream) {
+  VQ_REQUIRE(M >= 0 && N >= 0 && K >= 0 && batch >= 0, "vq_gemm_mx: negative extent");
+  if (M == 0 || N == 0 || batch == 0) return VQ_OK;
+  VQ_REQUIRE(A && B && C, "vq_gemm_mx: null operand");
+  VQ_REQUIRE(a_scale || b_scale, "vq_gemm_mx: neither operand has scales (use vq_gemm_tn)");
+  VQ_REQUIRE(K > 0, "vq_gemm_mx: empty contraction");
+  VQ_REQUIRE(block_size >= 8 && (block_size & (block_size - 1)) == 0,
+             "vq_gemm_mx: the block size must be a power of two, 8 or more");
+  VQ_REQUIRE(out_dtype == VQ_BF16 || out_dtype == VQ_F16 || out_dtype == VQ_F32, "vq_gemm_mx: bad output dtype");
+  VQ_REQUIRE((reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0,
+             "vq_gemm_mx: operands must be 16-byte aligned");
+  VQ_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && strideA % 8 == 0 && strideB % 8 == 0,
+             "vq_gemm_mx: leading dimensions and batch strides must be multiples of 16 bytes");
+  VQ_REQUIRE(lda >= K && ldb >= K && ldc >= N, "vq_gemm_mx: leading dimension smaller than the row");
+  VQ_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && batch < (1ll << 31), "vq_gemm_mx: extent too large");
+
+  static int max_clusters_of[64] = {};
+  static unsigned long long configured = 0;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
+  if (first_call_on_device(&configured)) {
+    if (int rc = allow_big_smem(gemm_mx_pair_kernel<VQ_BF16>, gemm_mx_pair_kernel<VQ_F16>, gemm_mx_pair_kernel<VQ_F32>,
+                                P_SMEM_BYTES))
+      return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kSmCount, 1, 1);
+    cfg.blockDim = dim3(MX_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_mx_pair_kernel<VQ_BF16>, &cfg);
+    if (e != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      max_clusters_of[device] = 0;
+    } else {
+      max_clusters_of[device] = n < kSmCount / 2 ? n : kSmCount / 2;
+    }
+  }
+  const int max_clusters = max_clusters_of[device];
+  if (max_clusters < 1) return vq::fail(VQ_EUNSUPPORTED, "vq_gemm_mx: this device cannot co-schedule CTA pairs");
+
+  GemmParams p{};
+  p.C = C;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.elem_bytes = 2;
+  p.ldc = ldc; p.strideC = strideC;
+  p.batch = (int)batch;
+  p.alpha = alpha; p.alpha_dt = alpha_dtype;
+  p.bias = bias; p.bias_dt = bias_dtype;
+  p.out_dt = out_dtype;
+  p.kind_f8 = false;
+  MxScales sc{};
+  sc.a = static_cast<const __nv_bfloat16*>(a_scale);
+  sc.b = static_cast<const __nv_bfloat16*>(b_scale);
+  sc.lds_a = sc.lds_b = (K + block_size - 1) / block_size;
+  sc.stride_a = M * sc.lds_a;
+  sc.stride_b = strideB == 0 ? 0 : N * sc.lds_b;
+  sc.shift = 0;
+  while ((1ll << sc.shift) < block_size) ++sc.shift;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap map_a, map_b, map_c;
+  if (int e = make_output_map(&map_c, &p.tma_store, C, out_dtype, M, N, ldc, batch, strideC)) return e;
+  if (int e = make_operand_map(&map_a, A, VQ_BF16, 2, M, K, lda, batch, strideA, BM)) return e;
+  p.bn = N <= BN / 2 ? BN / 2 : BN;
+  if (int e = make_operand_map(&map_b, B, VQ_BF16, 2, N, K, ldb, batch, strideB, p.bn / 2)) return e;
+  p.idesc = sm100::make_idesc(2 * BM, p.bn, 1, 1, 0, 0);
+  const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + p.bn - 1) / p.bn) * batch;
+  const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
+  VQ_FOR_OUT_DTYPE(out_dtype, gemm_mx_pair_kernel)<<<2 * clusters, MX_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, map_c, p, sc);
+  return check_launch("gemm_mx_pair_kernel");
 }
 
 int vq_gemm_nvfp4(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int out_dtype, int64_t M,

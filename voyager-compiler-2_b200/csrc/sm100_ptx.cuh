@@ -115,6 +115,18 @@ __device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* m
       : "memory");
 }
 
+// ---- register redistribution between warpgroups -----------------------------
+// Every warp of a warpgroup (four consecutive warps) executes the same one.  The counts are multiples
+// of 8; a group that asks for more waits until others have released enough.
+template <int REGS>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+template <int REGS>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
+}
+
 // ---- proxies / tcgen05 fences ----------------------------------------------
 // generic-proxy writes to shared memory become visible to the async proxy (TMA, tcgen05)
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -761,8 +761,88 @@ def _read_operand(x, scale, code, block_size):
     return _decode_and_scale(x, scale, code, block_size)
 
 
+# "auto": apply block scales inside the GEMM's main loop when that is estimated to be faster than a
+# read-back pass followed by the plain GEMM; "always" / "never" force the choice (tests, measurements).
+MX_IN_MAINLOOP = "auto"
+
+
+def _in_mainloop_pays(rows, n, k, batch, scaled_a, scaled_b, shared_weight):
+    """Measured on a B200 (N = 4096 .. 28672, K = 4096 .. 14336, 16 .. 2048 rows): the transform warps
+    add about 0.38 us per 64 elements of K to every wave of 74 CTA-pair tiles, while a separate read-back costs
+    its bytes (2 read + 2 written per element of a scaled operand) at about 4.5 TB/s plus 3 us per launch,
+    and at most 128 rows the plain GEMM falls back to its slower single-CTA tiles (about 15 us)."""
+    tiles = -(-rows // 256) * -(-n // 256) * batch
+    cost = 0.38 * -(-k // 64) * -(-tiles // 74)
+    elements = (rows * batch if scaled_a else 0) + (n * (1 if shared_weight else batch) if scaled_b else 0)
+    gain = 4.0 * elements * k / 4.5e6 + 3.0 * (int(scaled_a) + int(scaled_b)) + (15.0 if rows <= 128 else 0.0)
+    return cost < gain
+
+
+def _scales_per_row(x, scale, block_size):
+    """True when ``scale`` is contiguous bfloat16 with one value per ``block_size`` elements of ``x``'s last dimension."""
+    if scale is None:
+        return True
+    want = (*x.shape[:-1], -(-x.shape[-1] // block_size))
+    return scale.dtype == torch.bfloat16 and tuple(scale.shape) == want and scale.is_contiguous()
+
+
+def _mx_gemm_in_mainloop(native, a, b, bias, input_scale, weight_scale, block_size, alpha, layout, dtype):
+    """The contraction straight from block-scaled bfloat16 codes (``vq_gemm_mx``), or ``None`` when the call is
+    not of the shape that kernel takes (both operands K-contiguous with scales along K, a shared 2-D weight or
+    equal batches) or a separate read-back is estimated to be faster (``_in_mainloop_pays``)."""
+    act, wgt, out_l = _parse_layout(layout)
+    if act != "xc" or wgt != "kc" or out_l != _parse_layout(native)[2]:
+        return None
+    if input_scale is None and weight_scale is None:
+        return None
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.dim() < 2 or b.dim() < 2:
+        return None
+    if not isinstance(block_size, int) or block_size < 8 or block_size & (block_size - 1):
+        return None
+    k, n = a.shape[-1], b.shape[-2]
+    if b.shape[-1] != k or k % 8 or k == 0:
+        return None
+    if not (_scales_per_row(a, input_scale, block_size) and _scales_per_row(b, weight_scale, block_size)):
+        return None
+    if b.dim() == 2:
+        a2, b2 = a.reshape(-1, k), b
+        batch, rows, stride_a, stride_b = 1, a2.shape[0], 0, 0
+        out_shape = (*a.shape[:-1], n)
+    else:
+        if a.shape[:-2] != b.shape[:-2]:
+            return None
+        m = a.shape[-2]
+        a2, b2 = a.reshape(-1, m, k), b.reshape(-1, n, k)
+        batch, rows, stride_a, stride_b = a2.shape[0], m, m * k, n * k
+        out_shape = (*a.shape[:-2], m, n)
+    if batch == 0 or n == 0 or rows == 0 or MX_IN_MAINLOOP == "never":
+        return None
+    if MX_IN_MAINLOOP != "always" and not _in_mainloop_pays(rows, n, k, batch, input_scale is not None,
+                                                            weight_scale is not None, b.dim() == 2):
+        return None
+    a2, b2 = a2.contiguous(), b2.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    out = torch.empty((batch, rows, n), dtype=dtype, device=a.device)
+    rc = N.lib().vq_gemm_mx(a2.data_ptr(), _ptr(input_scale), b2.data_ptr(), _ptr(weight_scale), block_size,
+                            out.data_ptr(), _dtype_id(dtype), rows, n, k, k, k, n, batch, stride_a, stride_b, rows * n,
+                            _ptr(alpha), 0 if alpha is None else _dtype_id(alpha.dtype), _ptr(bias),
+                            0 if bias is None else _dtype_id(bias.dtype), _stream())
+    if rc == -3:   # VQ_EUNSUPPORTED: no CTA pairs on this device
+        return None
+    N.check(rc, "vq_gemm_mx")
+    return out.reshape(out_shape)
+
+
 def _mx_gemm(native, a, b, bias, input_scale, weight_scale, block_size, input_code, weight_code, alpha, outliers,
              layout, out_dtype):
+    if input_code is None and weight_code is None and all(t is None for t in outliers):
+        dtype = a.dtype if out_dtype is None else out_dtype
+        if dtype in _DTYPE_ID:
+            y = _mx_gemm_in_mainloop(native, a, b, bias, input_scale, weight_scale, block_size,
+                                     _as_scalar_param(alpha, a.device), layout, dtype)
+            if y is not None:
+                return y
     a = _read_operand(a, input_scale, input_code, block_size)
     b = _read_operand(b, weight_scale, weight_code, block_size)
     dtype = a.dtype if out_dtype is None else out_dtype

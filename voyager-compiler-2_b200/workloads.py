@@ -263,15 +263,16 @@ class Fp8DecoderLayer:
                               .reshape(sh.kv_heads, sh.groups * T, sh.head_dim), s["q"])
         k8 = FP8.quantize_fp8(k.transpose(0, 1), s["k"])                    # [kv, T, d]
         vt8 = FP8.quantize_fp8(v.permute(1, 2, 0), s["v"])                  # [kv, d, T]
-        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk, round_acc=self.ra)                        # [kv, groups*T, T]
+        scores = FP8.fp8_gemm(q8, k8, self.alpha_qk, round_acc=self.ra)     # [kv, groups*T, T]
         p8 = FP8.softmax_quantize_fp8(scores, 1.0 / math.sqrt(sh.head_dim), s["p"], causal_period=T)
-        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv, round_acc=self.ra)                          # [kv, groups*T, d]
+        ctx = FP8.fp8_gemm(p8, vt8, self.alpha_pv, round_acc=self.ra)       # [kv, groups*T, d]
         ctx = ctx.view(sh.kv_heads, sh.groups, T, sh.head_dim).permute(2, 0, 1, 3).reshape(T, sh.heads * sh.head_dim)
         x1 = x + FP8.fp8_gemm(FP8.quantize_fp8(ctx, s["ctx"]), self.w8["o"], self.alpha["o"], round_acc=self.ra)
         h28 = FP8.quantize_fp8(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps), s["h2"])
         act = F.silu(FP8.fp8_gemm(h28, self.w8["gate"], self.alpha["gate"], round_acc=self.ra)) * \
             FP8.fp8_gemm(h28, self.w8["up"], self.alpha["up"], round_acc=self.ra)
-        return x1 + FP8.fp8_gemm(FP8.quantize_fp8(act, s["act"]), self.w8["down"], self.alpha["down"], round_acc=self.ra)
+        return x1 + FP8.fp8_gemm(FP8.quantize_fp8(act, s["act"]), self.w8["down"], self.alpha["down"],
+                                 round_acc=self.ra)
 
     __call__ = forward
 
