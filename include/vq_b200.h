@@ -383,6 +383,22 @@ int vq_attention_fp8(const void* q8, const void* k8, const void* vt8, void* out8
                      int round_acc, void* stream);
 int vq_attention_status(int reset);
 
+/* Causal self-attention on bfloat16 operands in one kernel: the matmul / scale + mask / softmax /
+ * matmul nodes of an eager attention in a converted graph whose attention matmuls stay in
+ * bfloat16 (the recipes that quantize only the linears: aten.matmul or quantized_ops::matmul,
+ * ops/layout.py:281-290, around aten.softmax), every bfloat16 rounding of the separate nodes kept:
+ *   scores = bf16(q k^T); s = bf16(scores * score_scale), keys > query masked
+ *   p = bf16(softmax_fp32(s)); out = bf16(p v)
+ * (round_acc == 0 skips the first rounding: the scores stay in float32 until they are scaled).
+ * q: [kv_heads, groups * T, 128], the query heads of a KV group stacked along the rows;
+ * k: [kv_heads, T, 128]; vt: [kv_heads, 128, T] (V transposed); out: [T, ldo] with head
+ * h = kv * groups + g at columns [128 h, +128).  head_dim must be 128 and T a multiple of 128,
+ * else VQ_EUNSUPPORTED.  The score and probability matrices never leave the SM.
+ * vq_attention_status covers this kernel too. */
+int vq_attention_bf16(const void* q, const void* k, const void* vt, void* out, int64_t ldo, int64_t T,
+                      int64_t kv_heads, int64_t groups, int64_t head_dim, float score_scale, int round_acc,
+                      void* stream);
+
 /* RMSNorm's backward of a training step: the input gradient (plus the residual stream's) and
  * the weight gradient from one read of the rows -- the operator
  * voyager_gpu::rmsnorm_backward(Tensor[] gradients, Tensor x, Tensor rsqrt, Tensor weight,

@@ -95,3 +95,71 @@ def test_attention_matches_a_torch_restatement():
                                dev(alpha_pv, torch.float32)).float()
     assert vb.fp8.attention_status() == 0
     assert float((got - want).abs().max()) <= 1e-2 * float(want.abs().max())
+
+
+# ---------------------------------------------------------------------------
+# bfloat16 operands: the eager attention of a graph whose attention matmuls are not quantized
+# ---------------------------------------------------------------------------
+def _eager_bf16_attention(q, k, v, round_scores=True):
+    """matmul -> scale + mask -> softmax -> matmul on bfloat16 tensors (float32 accumulation, every node's
+    output rounded to bfloat16), computed per KV group in float64-free plain torch."""
+    T, heads, d = q.shape
+    kv = k.shape[1]
+    groups = heads // kv
+    mask = torch.full((T, T), float("-inf"), device=q.device).triu(1)
+    qg = q.reshape(T, kv, groups, d).permute(1, 2, 0, 3).float()
+    scores = torch.matmul(qg, k.permute(1, 2, 0)[:, None].float())
+    if round_scores:
+        scores = scores.bfloat16().float()
+    s = (scores * (1.0 / d ** 0.5) + mask).bfloat16().float()
+    p = torch.softmax(s, -1).bfloat16().float()
+    ctx = torch.matmul(p, v.transpose(0, 1)[:, None].float()).bfloat16()
+    return ctx.permute(2, 0, 1, 3).reshape(T, heads * d)
+
+
+@pytest.mark.parametrize("T,kv,groups", [(128, 1, 1), (256, 2, 2), (384, 1, 4), (1024, 2, 4), (2048, 8, 4)])
+@pytest.mark.parametrize("round_acc", [True, False])
+def test_attention_bf16_matches_the_eager_graph(T, kv, groups, round_acc):
+    from voyager_b200 import fp8 as F8
+
+    g = torch.Generator().manual_seed(T + kv + groups)
+    q = (torch.randn(T, kv * groups, 128, generator=g) * 1.5).bfloat16().cuda()
+    k = (torch.randn(T, kv, 128, generator=g) * 1.5).bfloat16().cuda()
+    v = torch.randn(T, kv, 128, generator=g).bfloat16().cuda()
+    got = F8.attention_bf16(q, k, v, round_acc=round_acc)
+    assert F8.attention_status() == 0
+    want = _eager_bf16_attention(q, k, v, round_scores=round_acc)
+    assert got.shape == want.shape and got.dtype == torch.bfloat16
+    diff = (got.float() - want.float()).abs()
+    # probabilities that sit on a bfloat16 rounding boundary may flip by one step (ex2.approx against expf, the
+    # row sum in another order); the context then differs by at most a few of its own rounding steps
+    assert float(diff.max()) <= 2e-2 * float(want.float().abs().max()), float(diff.max())
+    assert float(diff.pow(2).mean().sqrt()) <= 2e-3 * float(want.float().pow(2).mean().sqrt())
+    assert float((got != want).float().mean()) <= 0.25
+    again = F8.attention_bf16(q, k, v, round_acc=round_acc)
+    assert torch.equal(got, again)
+
+
+def test_attention_bf16_first_rows_are_exact():
+    """Row 0 attends to key 0 only: p = 1 and the context is v[0], bit for bit."""
+    from voyager_b200 import fp8 as F8
+
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(256, 4, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(256, 2, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(256, 2, 128, generator=g).bfloat16().cuda()
+    got = F8.attention_bf16(q, k, v).reshape(256, 4, 128)
+    assert F8.attention_status() == 0
+    for h in range(4):
+        assert torch.equal(got[0, h], v[0, h // 2])
+
+
+def test_attention_bf16_rejects_other_shapes():
+    from voyager_b200 import fp8 as F8
+
+    q = torch.zeros(100, 2, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        F8.attention_bf16(q, q, q)
+    q = torch.zeros(128, 2, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        F8.attention_bf16(q, q, q)

@@ -161,7 +161,7 @@ def test_quantize_nvfp4_square_matches_the_oracle():
     assert torch.equal(got_scale_t.cpu(), scale.mT.repeat_interleave(16, 0))
 
 
-@pytest.mark.parametrize("merge,attention", [(True, "eager"), (False, "eager"), (True, "sdpa")])
+@pytest.mark.parametrize("merge,attention", [(True, "fused"), (True, "eager"), (False, "eager"), (True, "sdpa")])
 def test_nvfp4_decoder_layer_matches_converted_graph(merge, attention):
     """Seven NVFP4 linears of a Llama-shaped layer (casts + native block-scaled GEMMs, merged QKV and
     gate/up with per-column alphas) against the converted microscaling graph on the CPU oracle."""

@@ -36,18 +36,28 @@ namespace {
 using namespace sm100;
 
 constexpr int AT_BLK = 128;                 // query rows per CTA, keys per block, head_dim
-constexpr int AT_TILE = AT_BLK * AT_BLK;    // bytes of one FP8 operand tile
 constexpr int AT_STAGES = 3;                // K / V tiles in flight
-constexpr int AT_SBUFS = 1;                 // score tiles in tensor memory (and probability tiles in shared memory)
-constexpr int AT_GROUPS = 2;                // softmax groups of four warps: (score buffer) x (column part)
-constexpr int AT_PARTS = AT_GROUPS / AT_SBUFS;   // column parts of a score tile
-constexpr int AT_CPT = 4 / AT_PARTS;        // 32-column chunks per thread and tile
-constexpr int AT_THREADS = 64 + AT_GROUPS * 128;
-constexpr int AT_CTAS_PER_SM = 2;           // two CTAs share an SM: one computes while the other waits or starts up
-constexpr int AT_TMEM_COLS = AT_SBUFS == 1 ? 256 : 512;   // score tiles, then the context accumulator
-constexpr uint32_t AT_O_COL = AT_SBUFS * AT_BLK;
-constexpr int AT_STATS_BYTES = AT_GROUPS * 2 * AT_BLK * 4;   // (max, sum) x groups x 128 rows
-constexpr size_t AT_SMEM_BYTES = 1024 + (1 + AT_STAGES + AT_SBUFS) * AT_TILE + AT_STATS_BYTES + 256;
+
+// FP8 operands: 16 KB tiles, one score tile in tensor memory, two softmax groups, two CTAs per SM (one
+// computes while the other waits or starts up).  bfloat16 operands: 32 KB tiles (two 128-byte-swizzled
+// halves of 64 contraction elements each), so one CTA per SM, which overlaps the tensor core with the
+// softmax inside itself instead: two score / probability tiles and four softmax groups.
+template <bool BF16>
+struct AtCfg {
+  static constexpr int TILE = AT_BLK * AT_BLK * (BF16 ? 2 : 1);   // bytes of one operand tile
+  static constexpr int HALF = TILE / 2;                          // bfloat16: bytes of one 64-element half
+  static constexpr int KSTEPS = 4 * (BF16 ? 2 : 1);              // MMA instructions per tile (32 bytes of K each)
+  static constexpr int SBUFS = BF16 ? 2 : 1;                     // score tiles in tensor memory (and probability tiles in shared memory)
+  static constexpr int GROUPS = BF16 ? 4 : 2;                    // softmax groups of four warps: (score buffer) x (column part)
+  static constexpr int PARTS = GROUPS / SBUFS;                   // column parts of a score tile
+  static constexpr int CPT = 4 / PARTS;                          // 32-column chunks per thread and tile
+  static constexpr int THREADS = 64 + GROUPS * 128;
+  static constexpr int CTAS_PER_SM = BF16 ? 1 : 2;
+  static constexpr int TMEM_COLS = SBUFS == 1 ? 256 : 512;       // score tiles, then the context accumulator
+  static constexpr uint32_t O_COL = SBUFS * AT_BLK;
+  static constexpr int STATS_BYTES = GROUPS * 2 * AT_BLK * 4;    // (max, sum) x groups x 128 rows
+  static constexpr size_t SMEM_BYTES = 1024 + (1 + AT_STAGES + SBUFS) * TILE + STATS_BYTES + 256;
+};
 
 __device__ int g_attention_error = 0;
 
@@ -64,7 +74,8 @@ struct AttnParams {
   int ctx_scale_dt;
   uint8_t* out8;           // [T, ld8] e4m3, head h at columns [h * 128, +128), or null
   int64_t ld8;
-  __nv_bfloat16* out16;    // [kv_heads, groups * T, 128], or null
+  __nv_bfloat16* out16;    // [kv_heads, groups * T, 128] (ld16 = 0) or [T, ld16] with head h at columns [h * 128, +128); or null
+  int64_t ld16;
   int round_acc;           // both products are rounded to bfloat16 before their scale is applied
 };
 
@@ -86,13 +97,16 @@ __device__ __forceinline__ float ex2(float v) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
   return r;
 }
-__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(AT_GROUPS * 128) : "memory"); }
+template <int THREADS>
+__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(THREADS) : "memory"); }
 
 constexpr float kLog2e = 1.4426950408889634f;
 
 // s = bf16(bf16(acc * alpha_qk) * score_scale) for 32 accumulator columns, as 16 pairs.
 // In the diagonal block, column c of the block is masked for row r when c > r.
-template <bool DIAG>
+// ALPHA = false (bfloat16 operands: the product has no dequantization factor) skips that step, so that
+// without round_acc the scores meet their first rounding only after the scale.
+template <bool DIAG, bool ALPHA = true>
 __device__ __forceinline__ void scores_of_chunk(const uint32_t (&v)[32], float2 (&s)[16], float alpha, float scale,
                                                 int col0, int r, bool round_acc) {
   const float2 a2 = make_float2(alpha, alpha), s2 = make_float2(scale, scale);
@@ -105,7 +119,7 @@ __device__ __forceinline__ void scores_of_chunk(const uint32_t (&v)[32], float2 
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     float2 x = s[i];
-    x = round2(__fmul2_rn(x, a2));
+    if (ALPHA) x = round2(__fmul2_rn(x, a2));
     x = round2(__fmul2_rn(x, s2));
     if (DIAG) {
       if (col0 + 2 * i > r) x.x = -INFINITY;
@@ -116,11 +130,11 @@ __device__ __forceinline__ void scores_of_chunk(const uint32_t (&v)[32], float2 
 }
 
 // Pass A on one chunk: the running maximum m and the sum l of exp(s - m) take in 32 more columns.
-template <bool DIAG>
+template <bool DIAG, bool ALPHA = true>
 __device__ __forceinline__ void accumulate_chunk(const uint32_t (&v)[32], float alpha, float scale, int col0, int r,
                                                  float& m, float& l, bool round_acc) {
   float2 s[16];
-  scores_of_chunk<DIAG>(v, s, alpha, scale, col0, r, round_acc);
+  scores_of_chunk<DIAG, ALPHA>(v, s, alpha, scale, col0, r, round_acc);
   float cmax = m;
 #pragma unroll
   for (int i = 0; i < 16; ++i) cmax = max3(cmax, s[i].x, s[i].y);
@@ -157,9 +171,29 @@ __device__ __forceinline__ void codes_of_chunk(const uint32_t (&v)[32], uint32_t
   }
 }
 
-__global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM)
-attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+// Pass B on one chunk of bfloat16 attention: the 32 probabilities p = bf16(e / sum) as 16 packed pairs.
+template <bool DIAG>
+__device__ __forceinline__ void probs_of_chunk(const uint32_t (&v)[32], uint32_t (&words)[16], float alpha, float scale,
+                                               int col0, int r, float shift, float rl, bool round_acc) {
+  float2 s[16];
+  scores_of_chunk<DIAG, false>(v, s, alpha, scale, col0, r, round_acc);
+  const float2 log2e2 = make_float2(kLog2e, kLog2e), shift2 = make_float2(shift, shift);
+  const float2 rl2 = make_float2(rl, rl);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 a = __ffma2_rn(s[i], log2e2, shift2);
+    words[i] = pack2(__fmul2_rn(make_float2(ex2(a.x), ex2(a.y)), rl2));
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(AtCfg<BF16>::THREADS, AtCfg<BF16>::CTAS_PER_SM)
+attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams p) {
+  using C = AtCfg<BF16>;
+  constexpr int AT_TILE = C::TILE, AT_SBUFS = C::SBUFS, AT_GROUPS = C::GROUPS, AT_PARTS = C::PARTS, AT_CPT = C::CPT;
+  constexpr int AT_STATS_BYTES = C::STATS_BYTES, AT_TMEM_COLS = C::TMEM_COLS;
+  constexpr uint32_t AT_O_COL = C::O_COL;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_q = smem;
@@ -220,8 +254,13 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_k);
       prefetch_tensormap(&map_v);
+      // a bfloat16 tile arrives as two boxes of 64 contraction elements (x is the contraction coordinate)
+      auto load_tile = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+        tma_load_3d(dst, map, bar, x, y, kvh);
+        if (BF16) tma_load_3d(dst + C::HALF, map, bar, x + 64, y, kvh);
+      };
       mbar_arrive_expect_tx(q_full, AT_TILE);
-      tma_load_3d(smem_q, &map_q, q_full, 0, qrow0, kvh);
+      load_tile(smem_q, &map_q, q_full, 0, qrow0);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -229,7 +268,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (!ok) return;
         if (!mbar_wait(&kv_empty[stage], phase ^ 1, abort_flag)) { ok = false; return; }
         mbar_arrive_expect_tx(&kv_full[stage], AT_TILE);
-        tma_load_3d(ring + stage * AT_TILE, map, &kv_full[stage], x, y, kvh);
+        load_tile(ring + stage * AT_TILE, map, &kv_full[stage], x, y);
         if (++stage == AT_STAGES) { stage = 0; phase ^= 1; }
       };
       for (int j = 0; j <= jd; ++j) load(&map_k, 0, j * AT_BLK);          // pass A
@@ -249,7 +288,15 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(AT_BLK, AT_BLK, 0, 0, 0, 0);   // e4m3 x e4m3, M = N = 128
+      // e4m3 x e4m3 or bfloat16 x bfloat16, M = N = 128; step k of a tile covers 32 bytes of K
+      constexpr uint32_t idesc = BF16 ? make_idesc(AT_BLK, AT_BLK, 1, 1, 0, 0) : make_idesc(AT_BLK, AT_BLK, 0, 0, 0, 0);
+      auto operand = [](uint32_t tile_addr, int k) {
+        return smem_desc_k_major_sw128(tile_addr + (BF16 ? (uint32_t)((k >> 2) * C::HALF) : 0u) + (uint32_t)((k & 3) * 32));
+      };
+      auto mma = [&](uint32_t d, uint32_t a_addr, uint32_t b_addr, int k, uint32_t accumulate) {
+        if (BF16) mma_f16_ss(d, operand(a_addr, k), operand(b_addr, k), idesc, accumulate);
+        else mma_f8f6f4_ss(d, operand(a_addr, k), operand(b_addr, k), idesc, accumulate);
+      };
       int stage = 0;
       uint32_t phase = 0;
       uint32_t s_uses[AT_SBUFS] = {}, p_uses[AT_SBUFS] = {};
@@ -264,9 +311,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(ring + stage * AT_TILE);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f8f6f4_ss(tmem_base + (uint32_t)(b * AT_BLK), smem_desc_k_major_sw128(q_addr + k * 32),
-                        smem_desc_k_major_sw128(k_addr + k * 32), idesc, k > 0 ? 1u : 0u);
+        for (int k = 0; k < C::KSTEPS; ++k) mma(tmem_base + (uint32_t)(b * AT_BLK), q_addr, k_addr, k, k > 0 ? 1u : 0u);
         mma_commit(&kv_empty[stage]);
         mma_commit(&s_full[b]);
         ++s_uses[b];
@@ -282,9 +327,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t p_addr = smem_u32(smem_p + b * AT_TILE);
         const uint32_t v_addr = smem_u32(ring + stage * AT_TILE);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f8f6f4_ss(tmem_base + AT_O_COL, smem_desc_k_major_sw128(p_addr + k * 32),
-                        smem_desc_k_major_sw128(v_addr + k * 32), idesc, (j > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < C::KSTEPS; ++k) mma(tmem_base + AT_O_COL, p_addr, v_addr, k, (j > 0 || k > 0) ? 1u : 0u);
         mma_commit(&kv_empty[stage]);
         mma_commit(&p_empty[b]);
         ++p_uses[b];
@@ -306,7 +349,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int quarter = warp & 3;                  // tensor-memory lanes [32 * quarter, +32) are this warp's
     const int r = quarter * 32 + lane;             // this thread's query row within the block
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    const float alpha = loadp(p.alpha_qk, 0, p.alpha_qk_dt);
+    const float alpha = p.alpha_qk != nullptr ? loadp(p.alpha_qk, 0, p.alpha_qk_dt) : 1.0f;
     const bool round_acc = p.round_acc != 0;
     uint32_t s_uses = 0, p_uses = 0;               // tiles taken from S[w], tiles written to P[w]
     bool ok = true;
@@ -332,8 +375,8 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           __syncwarp();
           if (lane == 0) mbar_arrive(&s_empty[w]);
         }
-        if (diag) accumulate_chunk<true>(v, alpha, p.score_scale, col0, r, m, l, round_acc);
-        else accumulate_chunk<false>(v, alpha, p.score_scale, col0, r, m, l, round_acc);
+        if (diag) accumulate_chunk<true, !BF16>(v, alpha, p.score_scale, col0, r, m, l, round_acc);
+        else accumulate_chunk<false, !BF16>(v, alpha, p.score_scale, col0, r, m, l, round_acc);
       }
       if (live == 0) {
         tc_fence_before_sync();
@@ -345,7 +388,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // ---- merge the two groups' statistics (every softmax thread reaches this barrier) ----
     stats[(group * 2 + 0) * AT_BLK + r] = m;
     stats[(group * 2 + 1) * AT_BLK + r] = l;
-    softmax_barrier();
+    softmax_barrier<AT_GROUPS * 128>();
     if (*abort_flag) ok = false;
     float mf = -INFINITY;
 #pragma unroll
@@ -354,7 +397,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
     for (int q = 0; q < AT_GROUPS; ++q)
       lf = fmaf(stats[(q * 2 + 1) * AT_BLK + r], ex2((stats[(q * 2) * AT_BLK + r] - mf) * kLog2e), lf);
-    const float rl = __frcp_rn(lf), rsp = __frcp_rn(loadp(p.p_scale, 0, p.p_scale_dt));
+    const float rl = __frcp_rn(lf), rsp = BF16 ? 1.0f : __frcp_rn(loadp(p.p_scale, 0, p.p_scale_dt));
     const float shift = -mf * kLog2e;
 
     // ---- pass B: probabilities of this group's blocks as FP8 codes in the MMA operand layout ----
@@ -371,9 +414,10 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const int live = diag ? min(max(quarter + 1 - AT_CPT * part, 0), AT_CPT) : AT_CPT;
       const uint32_t taddr = lane_addr + (uint32_t)(w * AT_BLK + part * 32 * AT_CPT);
       for (int c = 0; c < AT_CPT; ++c) {
-        uint32_t codes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (c < live) {
-          const int col0 = (part * AT_CPT + c) * 32;
+        const int cidx = AT_CPT * part + c;        // 32-column chunk of the tile
+        const int col0 = cidx * 32;
+        const bool have = c < live;
+        if (have) {
           tmem_ld_32x32(taddr + 32 * c, v);
           tmem_ld_wait();
           if (c == live - 1) {
@@ -381,12 +425,29 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[w]);
           }
-          if (diag) codes_of_chunk<true>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp, round_acc);
-          else codes_of_chunk<false>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp, round_acc);
         }
-        const int chunk16 = 2 * (AT_CPT * part + c);
-        *reinterpret_cast<uint4*>(p_row + ((chunk16 ^ (r & 7)) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-        *reinterpret_cast<uint4*>(p_row + (((chunk16 + 1) ^ (r & 7)) << 4)) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+        if (BF16) {
+          // 32 probabilities = 64 bytes = four 16-byte chunks of the half tile holding keys [64 (cidx / 2), +64)
+          uint32_t words[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+          if (have) {
+            if (diag) probs_of_chunk<true>(v, words, alpha, p.score_scale, col0, r, shift, rl, round_acc);
+            else probs_of_chunk<false>(v, words, alpha, p.score_scale, col0, r, shift, rl, round_acc);
+          }
+          uint8_t* half_row = p_row + (cidx >> 1) * C::HALF;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(half_row + ((((cidx & 1) * 4 + q) ^ (r & 7)) << 4)) =
+                make_uint4(words[4 * q], words[4 * q + 1], words[4 * q + 2], words[4 * q + 3]);
+        } else {
+          uint32_t codes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          if (have) {
+            if (diag) codes_of_chunk<true>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp, round_acc);
+            else codes_of_chunk<false>(v, codes, alpha, p.score_scale, col0, r, shift, rl, rsp, round_acc);
+          }
+          const int chunk16 = 2 * cidx;
+          *reinterpret_cast<uint4*>(p_row + ((chunk16 ^ (r & 7)) << 4)) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+          *reinterpret_cast<uint4*>(p_row + (((chunk16 + 1) ^ (r & 7)) << 4)) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+        }
       }
       if (live == 0) {
         tc_fence_before_sync();
@@ -402,7 +463,7 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (ok && !__all_sync(0xFFFFFFFFu, mbar_wait(o_full, 0, abort_flag))) ok = false;
     if (ok) {
       tc_fence_after_sync();
-      const float alpha_pv = loadp(p.alpha_pv, 0, p.alpha_pv_dt);
+      const float alpha_pv = p.alpha_pv != nullptr ? loadp(p.alpha_pv, 0, p.alpha_pv_dt) : 1.0f;
       const int t = jd * AT_BLK + r;                         // position in the sequence
       const int head = kvh * p.groups + g;
       Divisor dv;
@@ -420,7 +481,9 @@ attention_fp8_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           words[i] = pack2(__fmul2_rn(acc, make_float2(alpha_pv, alpha_pv)));
         }
         if (p.out16 != nullptr) {
-          uint4* dst = reinterpret_cast<uint4*>(p.out16 + ((int64_t)kvh * p.groups * p.T + qrow0 + r) * AT_BLK + col0);
+          uint4* dst = reinterpret_cast<uint4*>(
+              p.ld16 > 0 ? p.out16 + (int64_t)t * p.ld16 + head * AT_BLK + col0
+                         : p.out16 + ((int64_t)kvh * p.groups * p.T + qrow0 + r) * AT_BLK + col0);
 #pragma unroll
           for (int q = 0; q < 4; ++q) dst[q] = make_uint4(words[4 * q], words[4 * q + 1], words[4 * q + 2], words[4 * q + 3]);
         }
@@ -465,16 +528,16 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-// Tensor map over a [batch, rows, cols] byte matrix, cols contiguous; boxes of 128 rows x 128 bytes
-// in the 128-byte swizzle (the K-major MMA operand layout).
-int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t batch) {
+// Tensor map over a [batch, rows, cols] matrix of 1- or 2-byte elements, cols contiguous; boxes of
+// 128 rows x 128 bytes in the 128-byte swizzle (the K-major MMA operand layout).
+int make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int64_t batch, int elem_bytes = 1) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)cols, (cuuint64_t)(rows * cols)};
-  cuuint32_t box[3] = {AT_BLK, AT_BLK, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)(cols * elem_bytes), (cuuint64_t)(rows * cols * elem_bytes)};
+  cuuint32_t box[3] = {(cuuint32_t)(AT_BLK / elem_bytes), AT_BLK, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(VQ_ECUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -530,13 +593,53 @@ extern "C" int vq_attention_fp8(const void* q8, const void* k8, const void* vt8,
   p.round_acc = round_acc != 0;
   static unsigned long long configured = 0;
   if (first_call_on_device(&configured)) {
-    cudaError_t e = cudaFuncSetAttribute(attention_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)AT_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)AtCfg<false>::SMEM_BYTES);
     if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   }
-  attention_fp8_kernel<<<(unsigned)items, AT_THREADS, AT_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(map_q, map_k,
-                                                                                                         map_v, p);
-  return check_launch("attention_fp8_kernel");
+  attention_kernel<false><<<(unsigned)items, AtCfg<false>::THREADS, AtCfg<false>::SMEM_BYTES,
+                            static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, p);
+  return check_launch("attention_kernel<fp8>");
+}
+
+extern "C" int vq_attention_bf16(const void* q, const void* k, const void* vt, void* out, int64_t ldo, int64_t T,
+                                 int64_t kv_heads, int64_t groups, int64_t head_dim, float score_scale, int round_acc,
+                                 void* stream) {
+  VQ_REQUIRE(T >= 0 && kv_heads >= 0 && groups >= 0, "vq_attention_bf16: negative extent");
+  if (T == 0 || kv_heads == 0 || groups == 0) return VQ_OK;
+  if (head_dim != AT_BLK || T % AT_BLK != 0)
+    return fail(VQ_EUNSUPPORTED, "vq_attention_bf16: head_dim must be 128 and T a multiple of 128");
+  VQ_REQUIRE(q && k && vt && out, "vq_attention_bf16: null argument");
+  VQ_REQUIRE(ldo >= kv_heads * groups * AT_BLK && ldo % 8 == 0,
+             "vq_attention_bf16: the output's row stride must be at least heads * 128 and a multiple of 8 elements");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(vt) |
+               reinterpret_cast<uintptr_t>(out)) & 15) == 0, "vq_attention_bf16: misaligned buffers");
+  const int64_t items = kv_heads * groups * (T / AT_BLK);
+  VQ_REQUIRE(T < (1ll << 24) && groups * T < (1ll << 31) && kv_heads < 65536 && items < (1ll << 31),
+             "vq_attention_bf16: extent too large");
+  CUtensorMap map_q, map_k, map_v;
+  int rc;
+  if ((rc = make_tile_map(&map_q, q, groups * T, AT_BLK, kv_heads, 2)) != VQ_OK) return rc;
+  if ((rc = make_tile_map(&map_k, k, T, AT_BLK, kv_heads, 2)) != VQ_OK) return rc;
+  if ((rc = make_tile_map(&map_v, vt, AT_BLK, T, kv_heads, 2)) != VQ_OK) return rc;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.T = (int)T;
+  p.groups = (int)groups;
+  p.kv_heads = (int)kv_heads;
+  p.score_scale = score_scale;
+  p.out16 = static_cast<__nv_bfloat16*>(out);
+  p.ld16 = ldo;
+  p.round_acc = round_acc != 0;
+  static unsigned long long configured = 0;
+  if (first_call_on_device(&configured)) {
+    cudaError_t e = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)AtCfg<true>::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(VQ_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  }
+  attention_kernel<true><<<(unsigned)items, AtCfg<true>::THREADS, AtCfg<true>::SMEM_BYTES,
+                           static_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, p);
+  return check_launch("attention_kernel<bf16>");
 }
 
 // A wait inside the kernel ran out (VQ_ETIMEOUT) since the last reset, else VQ_OK.  Synchronises the device.

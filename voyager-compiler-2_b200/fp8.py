@@ -11,6 +11,7 @@ MMA with fp32 accumulation whose epilogue applies ``scale_a * scale_b`` and the
 bias before a single rounding.
 """
 
+import math
 from typing import Optional
 
 import torch
@@ -181,8 +182,33 @@ def attention_fp8(q8: torch.Tensor, k8: torch.Tensor, vt8: torch.Tensor, alpha_q
     return out8 if out8 is not None else out16
 
 
+@N.device_guarded
+def attention_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, score_scale: Optional[float] = None,
+                   round_acc: bool = True) -> torch.Tensor:
+    """Causal self-attention on bfloat16 operands in one kernel, with the roundings of the eager graph
+    (``matmul`` -> scale + mask -> ``softmax`` -> ``matmul``, every intermediate a bfloat16 tensor):
+    ``q [T, heads, 128]``, ``k`` / ``v`` ``[T, kv_heads, 128]`` -> ``[T, heads * 128]``.  ``round_acc=False``
+    keeps the scores in float32 until they are scaled (a fused-attention library's semantics)."""
+    T, heads, d = q.shape
+    kv = k.shape[1]
+    if k.shape != (T, kv, d) or v.shape != (T, kv, d) or heads % kv:
+        raise ValueError("attention_bf16: operand shapes do not agree")
+    if any(t.dtype != torch.bfloat16 for t in (q, k, v)):
+        raise NotImplementedError("attention_bf16 takes bfloat16 operands")
+    groups = heads // kv
+    # a KV group's query heads stacked along the rows; V transposed (the P V product contracts over keys)
+    qg = q.reshape(T, kv, groups, d).permute(1, 2, 0, 3).contiguous()
+    kk = k.permute(1, 0, 2).contiguous()
+    vt = v.permute(1, 2, 0).contiguous()
+    out = torch.empty((T, heads * d), dtype=torch.bfloat16, device=q.device)
+    scale = 1.0 / math.sqrt(d) if score_scale is None else float(score_scale)
+    N.check(N.lib().vq_attention_bf16(qg.data_ptr(), kk.data_ptr(), vt.data_ptr(), out.data_ptr(), heads * d, T, kv,
+                                      groups, d, scale, int(bool(round_acc)), _stream()), "vq_attention_bf16")
+    return out
+
+
 def attention_status(reset: bool = True) -> int:
-    """0, or the timeout code if a bounded wait inside ``attention_fp8`` ran out since the last reset."""
+    """0, or the timeout code if a bounded wait inside ``attention_fp8`` / ``attention_bf16`` ran out since the last reset."""
     return N.lib().vq_attention_status(int(reset))
 
 

@@ -294,15 +294,17 @@ class Nvfp4DecoderLayer:
     ``alpha = bf16(t_activation * t_weight)``.
     """
 
-    def __init__(self, params, shape: LlamaShape, merge=True, attention="eager"):
+    def __init__(self, params, shape: LlamaShape, merge=True, attention="fused"):
         from . import nvfp4 as NV
 
         self.NV, self.shape, self.merge = NV, shape, merge
         # "eager": the graph's own attention operators (matmul, scale + mask, softmax, matmul: HF eager
-        # attention, every intermediate a bfloat16 tensor).  "sdpa": torch's fused kernel, which keeps the
-        # scores in float32; the two differ by the bfloat16 rounding of the scores (half a unit at 64..128),
-        # which the 4-bit casts downstream amplify to quantization-noise level.
-        if attention not in ("eager", "sdpa"):
+        # attention, every intermediate a bfloat16 tensor).  "fused": the same roundings inside this package's
+        # one-kernel attention (head_dim 128, T a multiple of 128; other shapes run "eager").  "sdpa": torch's
+        # fused kernel, which keeps the scores in float32; it differs from the other two by the bfloat16
+        # rounding of the scores (half a unit at 64..128), which the 4-bit casts downstream amplify to
+        # quantization-noise level.
+        if attention not in ("eager", "fused", "sdpa"):
             raise ValueError(attention)
         self.attention = attention
         self.ln1, self.ln2 = params["ln1"], params["ln2"]
@@ -323,8 +325,8 @@ class Nvfp4DecoderLayer:
         self._rope = None
         self._mask = None
 
-    # kernels of this package per forward (merged): 4 x (amax + cast) and 4 GEMMs
-    LAUNCHES = 12
+    # kernels of this package per forward (merged): 4 x (amax + cast), 4 GEMMs, the attention
+    LAUNCHES = 13
 
     def _linear(self, x, names):
         """``[linear(x, W_n) for n in names]`` through one cast of ``x``."""
@@ -347,6 +349,10 @@ class Nvfp4DecoderLayer:
             ctx = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None],
                                                  v.transpose(0, 1)[None], is_causal=True, enable_gqa=True)[0]
             return ctx.transpose(0, 1).reshape(T, sh.heads * sh.head_dim)
+        if self.attention == "fused" and sh.head_dim == 128 and T % 128 == 0:
+            from . import fp8 as F8
+
+            return F8.attention_bf16(q, k, v)
         if self._mask is None or self._mask.shape[0] != T:
             self._mask = causal_mask(T, q.device)
         # a KV group's query heads share its keys: [kv, groups, T, d] x [kv, 1, d, T], no repeated K / V
