@@ -509,6 +509,25 @@ int vq_gemm_status(int reset);
 int vq_kivi_read_2bit(const void* packed, const void* scale, const void* zero_point, void* out, int64_t outer,
                       int64_t T, int64_t D, int along_channels, int64_t block, void* stream);
 
+/* One decode step's attention straight from the packed KIVI cache, for every (sequence, KV head) pair
+ * `outer`: the nodes
+ *   k = dequantize(k_codes, k_scale, k_zero); v = dequantize(v_codes, v_scale, v_zero)   (as vq_kivi_read_2bit)
+ *   scores = cat(matmul(q, k^T), matmul(q, k_res^T)); p = bf16(softmax_fp32(bf16(scores * score_scale)))
+ *   out = bf16(matmul(p[:, :Tm], v)) + bf16(matmul(p[:, Tm:], v_res))
+ * of the graph (quantized_ops::dequantize, ops/quantized.py:527-571, emitted for the cache by
+ * codegen/transform/quant_folding.py:2391-2547, and the eager attention around it) with every node's
+ * bfloat16 rounding, without writing the dequantized cache.  q, out: bfloat16 [outer, G, 128] (the G query
+ * heads of the KV head); k_packed / v_packed: 2-bit codes [outer, Tm, 128] (four per byte); k_scale,
+ * k_zero: bfloat16 [outer, Tm / k_block, 128]; v_scale, v_zero: bfloat16 [outer, Tm, 128 / v_block];
+ * k_res, v_res: the newest R positions in bfloat16, [outer, R, 128].  VQ_EUNSUPPORTED unless D == 128,
+ * G <= 8, k_block a multiple of 64 dividing Tm, v_block 32, 64 or 128, R a multiple of 16 and
+ * G * (Tm + R) * 6 + 86 KB of shared memory fit in 227 KB (the caller then reads the cache with
+ * vq_kivi_read_2bit and runs the nodes one by one). */
+int vq_kivi_decode_attention(const void* q, const void* k_packed, const void* k_scale, const void* k_zero,
+                             const void* v_packed, const void* v_scale, const void* v_zero, const void* k_res,
+                             const void* v_res, void* out, int64_t outer, int64_t G, int64_t Tm, int64_t R, int64_t D,
+                             int64_t k_block, int64_t v_block, float score_scale, void* stream);
+
 /* Weight-streaming microscaling linear for a decode step (M <= 32 activation rows), on a weight
  * stored packed: w_packed [N, K / 2] holds two 4-bit codebook indices per byte (even element in
  * the low nibble), w_scale [N, K / block_size] its bfloat16 block scales, w_levels the 16

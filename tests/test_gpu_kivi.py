@@ -73,3 +73,71 @@ def test_pack_codes_tail_and_dtypes():
     out = vb.kivi.unpack_dequantize(vb.kivi.pack_codes(codes.cuda(), 2), 2, (37,), scale).cpu()
     assert torch.equal(out.float(), codes.float() * 0.5)
     assert vb.kivi.pack_codes(torch.empty(0, dtype=torch.bfloat16).cuda(), 2).numel() == 0
+
+
+# ---------------------------------------------------------------------------
+# decode-step attention straight from the packed cache
+# ---------------------------------------------------------------------------
+def _decode_problem(B, hkv, G, Tm, R, k_block, v_block, seed):
+    vb = _vb()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    d = 128
+    uint2 = vb.get_quantization_map("uint2").cuda()
+    e4m3 = vb.get_quantization_map("fp8_e4m3").cuda()
+    rnd = lambda *s: torch.randn(*s, generator=g, device="cuda").bfloat16()
+    keys = vb.kivi.quantize_cache(rnd(B, hkv, Tm, d), uint2, -2, k_block, 2, e4m3)
+    values = vb.kivi.quantize_cache(rnd(B, hkv, Tm, d), uint2, -1, v_block, 2, e4m3)
+    return rnd(B, hkv, G, d), keys, values, rnd(B, hkv, R, d), rnd(B, hkv, R, d)
+
+
+def _decode_by_operators(q, keys, values, k_res, v_res):
+    """read() + the graph's matmul / scale / softmax / matmul nodes on bfloat16 tensors."""
+    k_main, v_main = keys.read(), values.read()
+    scores = torch.cat([torch.matmul(q, k_main.transpose(-1, -2)), torch.matmul(q, k_res.transpose(-1, -2))], -1)
+    p = torch.softmax(scores * (1.0 / 128 ** 0.5), -1, dtype=torch.float32).to(q.dtype)
+    tm = k_main.shape[-2]
+    ctx = torch.matmul(p[..., :tm], v_main) + torch.matmul(p[..., tm:], v_res)
+    return ctx.reshape(q.shape[0], -1)
+
+
+@pytest.mark.parametrize("B,hkv,G,Tm,R,k_block,v_block", [
+    (1, 1, 1, 64, 16, 64, 64), (2, 2, 4, 512, 128, 64, 64), (1, 2, 4, 1088, 32, 64, 32), (1, 1, 8, 640, 16, 128, 128),
+    (16, 8, 4, 3968, 128, 64, 64), (1, 2, 3, 192, 144, 64, 64),
+])
+def test_decode_attention_matches_the_operators(B, hkv, G, Tm, R, k_block, v_block):
+    vb = _vb()
+    q, keys, values, k_res, v_res = _decode_problem(B, hkv, G, Tm, R, k_block, v_block, seed=Tm + R + G)
+    got = vb.kivi.decode_attention(q, keys, values, k_res, v_res)
+    assert got is not None and got.shape == (B, hkv * G * 128) and got.dtype == torch.bfloat16
+    want = _decode_by_operators(q, keys, values, k_res, v_res)
+    diff = (got.float() - want.float()).abs()
+    # the dequantized operands are bit-identical; sums run in another order and a probability on a bfloat16
+    # rounding boundary may move by one step
+    assert float(diff.max()) <= 2e-2 * float(want.float().abs().max()), float(diff.max())
+    assert float(diff.pow(2).mean().sqrt()) <= 3e-3 * float(want.float().pow(2).mean().sqrt())
+    assert torch.equal(got, vb.kivi.decode_attention(q, keys, values, k_res, v_res))
+
+
+def test_decode_attention_one_hot_rows_return_a_dequantized_value():
+    """A query that puts all its weight on one cached position returns that position's dequantized values:
+    the in-register decode equals read() bit for bit."""
+    vb = _vb()
+    q, keys, values, k_res, v_res = _decode_problem(1, 1, 4, 256, 16, 64, 64, seed=11)
+    k_main, v_main = keys.read(), values.read()
+    targets = [3, 77, 130, 255]
+    for i, pos in enumerate(targets):
+        q[0, 0, i] = k_main[0, 0, pos] * 64.0          # a huge score on its own key
+    want = _decode_by_operators(q, keys, values, k_res, v_res).reshape(4, 128)
+    got = vb.kivi.decode_attention(q, keys, values, k_res, v_res).reshape(4, 128)
+    assert torch.equal(got, want)
+    hit = sum(bool(torch.equal(got[i], v_main[0, 0, pos])) for i, pos in enumerate(targets))
+    assert hit >= 3      # (a row whose own key is not its best match proves nothing)
+
+
+def test_decode_attention_declines_other_layouts():
+    vb = _vb()
+    q, keys, values, k_res, v_res = _decode_problem(1, 1, 2, 96, 16, 32, 64, seed=5)   # key groups of 32 positions
+    assert vb.kivi.decode_attention(q, keys, values, k_res, v_res) is None
+    q, keys, values, k_res, v_res = _decode_problem(1, 1, 2, 128, 16, 64, 64, seed=5)
+    assert vb.kivi.decode_attention(q, values, keys, k_res, v_res) is None              # keys / values swapped
+    assert vb.kivi.decode_attention(q, keys, values, k_res[..., :8, :], v_res[..., :8, :]) is None   # R = 8

@@ -126,6 +126,7 @@ SIGNATURES = {
     "vq_gemm_lut4_counters": [_I64],
     "vq_gemm_lut4": [_P, _I64, _P, _P, _I, _I64, _P, _P, _P, _I, _P, _I, _I64, _I64, _P, _I, _P, _I, _P, _P, _P],
     "vq_pack_lut4": [_P, _P, _I64, _I64, _P, _P],
+    "vq_kivi_decode_attention": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P],
     "vq_kivi_read_2bit": [_P, _P, _P, _P, _I64, _I64, _I64, _I, _I64, _P],
     "vq_gptq_block": [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I, _F, _F, _I, ctypes.POINTER(VqRound),
                       ctypes.POINTER(VqRound), _P],

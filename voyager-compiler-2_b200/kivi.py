@@ -118,3 +118,42 @@ def quantize_cache(x: torch.Tensor, qmap: torch.Tensor, axis: int, block_size: i
     axes = [axis]
     scale, zero_point, codes = Q.quantize_affine(x, qmap, axes, block_size, 0.0, float(2 ** bits - 1), scale_qmap)
     return PackedCache(pack_codes(codes, bits), scale, zero_point, tuple(x.shape), axes, block_size, bits)
+
+
+def decode_attention(q: torch.Tensor, keys: PackedCache, values: PackedCache, k_recent: torch.Tensor,
+                     v_recent: torch.Tensor, score_scale: Optional[float] = None) -> Optional[torch.Tensor]:
+    """One decode step's attention over ``[packed cache | recent window]`` in one kernel.
+
+    ``q [B, kv_heads, G, 128]`` (the query heads of each KV head); ``keys`` / ``values``: 2-bit caches of
+    ``[B, kv_heads, Tm, 128]`` grouped along the positions / the channels; ``k_recent`` / ``v_recent``
+    ``[B, kv_heads, R, 128]`` bfloat16.  Returns ``[B, kv_heads * G * 128]`` with the roundings of
+    ``read()`` + ``matmul`` / ``softmax`` / ``matmul`` on bfloat16 tensors, or ``None`` when the kernel
+    does not take this configuration (the caller then runs those operators)."""
+    B, hkv, G, d = q.shape
+    kf, vf = keys._fast_layout(), values._fast_layout()
+    if kf is None or vf is None or kf[3] != 0 or vf[3] != 1 or q.dtype != torch.bfloat16:
+        return None
+    outer, Tm, D, _ = kf
+    R = k_recent.shape[-2]
+    if outer != B * hkv or vf[:3] != (outer, Tm, D) or d != D or tuple(k_recent.shape) != (B, hkv, R, D) \
+            or tuple(v_recent.shape) != (B, hkv, R, D) or k_recent.dtype != torch.bfloat16 \
+            or v_recent.dtype != torch.bfloat16:
+        return None
+    return _decode_attention(q.contiguous(), keys, values, k_recent.contiguous(), v_recent.contiguous(),
+                             1.0 / d ** 0.5 if score_scale is None else float(score_scale))
+
+
+@N.device_guarded
+def _decode_attention(q, keys, values, k_recent, v_recent, score_scale):
+    B, hkv, G, d = q.shape
+    Tm, R = keys.shape[-2], k_recent.shape[-2]
+    out = torch.empty((B, hkv * G * d), dtype=torch.bfloat16, device=q.device)
+    rc = N.lib().vq_kivi_decode_attention(
+        q.data_ptr(), keys.packed.data_ptr(), keys.scale.data_ptr(), keys.zero_point.data_ptr(),
+        values.packed.data_ptr(), values.scale.data_ptr(), values.zero_point.data_ptr(), k_recent.data_ptr(),
+        v_recent.data_ptr(), out.data_ptr(), B * hkv, G, Tm, R, d, keys.block_size, values.block_size, score_scale,
+        _stream())
+    if rc == -3:   # VQ_EUNSUPPORTED
+        return None
+    N.check(rc, "vq_kivi_decode_attention")
+    return out

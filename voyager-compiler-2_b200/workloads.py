@@ -448,17 +448,19 @@ class Mxnf4DecodeLayer:
     Weights live packed (``packed.PackedLUT4Weight``, q/k/v and gate/up merged row-wise: microscaling
     weights carry only per-block scales, so stacking rows changes nothing) and every linear is one
     activation ``quantize_mx`` plus the weight-streaming ``linear_lut4``.  The cached keys and values
-    are packed 2-bit codes read back by the fused unpack + dequantize kernel; the attention itself is
-    bfloat16 torch operators over [cache | recent] keys, as in the graph.
+    are packed 2-bit codes; the attention over [cache | recent] keys is one kernel that decodes them in
+    registers (``kivi.decode_attention``; ``fused_attention=False`` reads the cache back to bfloat16 and runs
+    the graph's matmul / softmax / matmul as torch operators).
     """
 
-    def __init__(self, weights, tables, cache, residual_scale, shape: LlamaShape):
+    def __init__(self, weights, tables, cache, residual_scale, shape: LlamaShape, fused_attention=True):
         self.w, self.t, self.cache, self.shape = weights, tables, cache, shape
+        self.fused_attention = fused_attention
         self.residual_scale = residual_scale
         self.ln1, self.ln2 = weights["ln1"], weights["ln2"]
 
-    # kernels of this package per step: 4 quantize_mx, 4 linears, 2 cache reads, 2 x (quantize + dequantize)
-    LAUNCHES = 14
+    # kernels of this package per step: 4 quantize_mx, 4 linears, the attention, 2 x (quantize + dequantize)
+    LAUNCHES = 13
 
     def _linear(self, x, name):
         from . import packed as P
@@ -488,12 +490,18 @@ class Mxnf4DecodeLayer:
         k_res, v_res = self.cache["k_res"], self.cache["v_res"]
         k_res[:, :, -1].copy_(k)                   # this step's token takes the last recent slot
         v_res[:, :, -1].copy_(v)
-        k_main, v_main = self.cache["k"].read(), self.cache["v"].read()
         qg = q.reshape(B, hkv, hq // hkv, d)
-        scores = torch.cat([torch.matmul(qg, k_main.transpose(-1, -2)), torch.matmul(qg, k_res.transpose(-1, -2))], -1)
-        p = torch.softmax(scores * (1.0 / math.sqrt(d)), -1, dtype=torch.float32).to(x.dtype)
-        tm = k_main.shape[-2]
-        ctx = torch.matmul(p[..., :tm], v_main) + torch.matmul(p[..., tm:], v_res)
+        ctx = None
+        if self.fused_attention:
+            from . import kivi as KV
+
+            ctx = KV.decode_attention(qg, self.cache["k"], self.cache["v"], k_res, v_res)
+        if ctx is None:
+            k_main, v_main = self.cache["k"].read(), self.cache["v"].read()
+            scores = torch.cat([torch.matmul(qg, k_main.transpose(-1, -2)), torch.matmul(qg, k_res.transpose(-1, -2))], -1)
+            p = torch.softmax(scores * (1.0 / math.sqrt(d)), -1, dtype=torch.float32).to(x.dtype)
+            tm = k_main.shape[-2]
+            ctx = torch.matmul(p[..., :tm], v_main) + torch.matmul(p[..., tm:], v_res)
         x1 = self._through_fp8(x) + self._linear(ctx.reshape(B, hq * d), "o")
         gu = self._linear(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps), "gate_up")
         inter = gu.shape[-1] // 2
