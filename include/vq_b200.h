@@ -520,8 +520,9 @@ int vq_kivi_read_2bit(const void* packed, const void* scale, const void* zero_po
  * heads of the KV head); k_packed / v_packed: 2-bit codes [outer, Tm, 128] (four per byte); k_scale,
  * k_zero: bfloat16 [outer, Tm / k_block, 128]; v_scale, v_zero: bfloat16 [outer, Tm, 128 / v_block];
  * k_res, v_res: the newest R positions in bfloat16, [outer, R, 128].  VQ_EUNSUPPORTED unless D == 128,
- * G <= 8, k_block a multiple of 64 dividing Tm, v_block 32, 64 or 128, R a multiple of 16 and
- * G * (Tm + R) * 6 + 86 KB of shared memory fit in 227 KB (the caller then reads the cache with
+ * G <= 8, k_block a multiple of 64 dividing Tm, v_block 32, 64 or 128, R a multiple of 16 and the
+ * G * (Tm + R) * 6 bytes of scores fit in shared memory beside two staged chunks (G = 4: about 4600
+ * positions) (the caller then reads the cache with
  * vq_kivi_read_2bit and runs the nodes one by one). */
 int vq_kivi_decode_attention(const void* q, const void* k_packed, const void* k_scale, const void* k_zero,
                              const void* v_packed, const void* v_scale, const void* v_zero, const void* k_res,

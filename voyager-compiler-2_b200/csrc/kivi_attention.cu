@@ -11,7 +11,7 @@
 // (quantized_ops::dequantize, ops/quantized.py:527-571, as emitted for the KIVI cache by
 // codegen/transform/quant_folding.py:2391-2547, then the eager attention nodes), every node's
 // output rounded to bfloat16.  Here one CTA owns one (sequence, KV head): it streams the 2-bit codes
-// and their parameters through shared memory with cp.async (two 512-position chunks in flight),
+// and their parameters through shared memory with cp.async (two 1024-position chunks in flight),
 // decodes them in registers into mma.sync.m16n8k16 operand fragments with two packed bfloat16
 // instructions per pair of values -- bf16(bf16(code - zero) * scale), the operator's own two
 // roundings -- and keeps the scores and probabilities of its G rows in shared memory, so the
@@ -30,12 +30,15 @@ namespace {
 
 constexpr int KA_D = 128;                  // head_dim
 constexpr int KA_ROW = KA_D / 4;           // packed bytes per position
-constexpr int KA_THREADS = 256;
+constexpr int KA_THREADS = 512;
 constexpr int KA_WARPS = KA_THREADS / 32;
 constexpr int KA_WKEYS = 64;               // positions a warp takes from a chunk
-constexpr int KA_CHUNK = KA_WARPS * KA_WKEYS;   // 512 positions per chunk
-constexpr int KA_PARAM_BYTES = 8192;       // per chunk: key parameters (8 x 128 x 2 tensors x 2 B) or value parameters (512 x 4 groups x 2 tensors x 2 B at most)
-constexpr int KA_STAGE_BYTES = KA_CHUNK * KA_ROW + KA_PARAM_BYTES;   // 24 KB
+constexpr int KA_CHUNK = KA_WARPS * KA_WKEYS;   // 1024 positions per chunk
+// A stage buffer: the chunk's packed rows, then its parameters -- keys: one 512-byte row (128 scales, 128 zero
+// points) per 64 positions; values: NGRP scales per position, then NGRP zero points per position.
+__host__ __device__ constexpr int ka_stage_bytes(int ngrp) {
+  return KA_CHUNK * KA_ROW + (KA_CHUNK * ngrp * 4 > KA_CHUNK * 8 ? KA_CHUNK * ngrp * 4 : KA_CHUNK * 8);
+}
 constexpr int KA_RES_LD = KA_D + 8;        // padded row of the staged recent values (bank spread)
 constexpr int KA_MAX_G = 8;
 
@@ -91,9 +94,10 @@ kivi_decode_attention_kernel(const KaParams p) {
   const int N = p.Tm + p.R;                                   // keys per row
   float* scores = reinterpret_cast<float*>(ka_smem);                                  // [G][N]
   __nv_bfloat16* probs = reinterpret_cast<__nv_bfloat16*>(scores + (size_t)p.G * N);   // [G][N]
+  constexpr int KA_STAGE_BYTES = ka_stage_bytes(NGRP);
   uint8_t* stage = reinterpret_cast<uint8_t*>(probs + (size_t)p.G * N);               // [2][KA_STAGE_BYTES]; N is a multiple of 8
-  float* red = reinterpret_cast<float*>(stage + 2 * KA_STAGE_BYTES);                  // [KA_WARPS][KA_MAX_G][128]
-  float* row_stat = red + KA_WARPS * KA_MAX_G * KA_D;                                 // [KA_WARPS]
+  float* red = reinterpret_cast<float*>(stage + 2 * KA_STAGE_BYTES);                  // [KA_WARPS][G][128]
+  float* row_stat = red + KA_WARPS * p.G * KA_D;                                      // [KA_WARPS]
   float* main_out = row_stat + KA_WARPS;                                              // [KA_MAX_G][128]
   uint32_t* lut = reinterpret_cast<uint32_t*>(main_out + KA_MAX_G * KA_D);            // [16] bf16x2 of a pair of codes
 
@@ -143,7 +147,7 @@ kivi_decode_attention_kernel(const KaParams p) {
       const __nv_bfloat16* z = p.v_zero + (outer * p.Tm + key0) * NGRP;
       for (int i = threadIdx.x; i < bytes / 16; i += KA_THREADS) {
         cp_async16(pdst + i * 16, reinterpret_cast<const uint8_t*>(s) + i * 16);
-        cp_async16(pdst + KA_PARAM_BYTES / 2 + i * 16, reinterpret_cast<const uint8_t*>(z) + i * 16);
+        cp_async16(pdst + KA_CHUNK * NGRP * 2 + i * 16, reinterpret_cast<const uint8_t*>(z) + i * 16);
       }
     }
     cp_async_commit();
@@ -267,7 +271,7 @@ kivi_decode_attention_kernel(const KaParams p) {
     if (warp * KA_WKEYS < count) {
       const uint8_t* buf = stage + (c & 1) * KA_STAGE_BYTES;
       const uint16_t* vs = reinterpret_cast<const uint16_t*>(buf + KA_CHUNK * KA_ROW);
-      const uint16_t* vz = reinterpret_cast<const uint16_t*>(buf + KA_CHUNK * KA_ROW + KA_PARAM_BYTES / 2);
+      const uint16_t* vz = reinterpret_cast<const uint16_t*>(buf + KA_CHUNK * KA_ROW + KA_CHUNK * NGRP * 2);
 #pragma unroll 1
       for (int ks = 0; ks < KA_WKEYS / 16; ++ks) {
         const int kl = warp * KA_WKEYS + ks * 16;
@@ -315,7 +319,7 @@ kivi_decode_attention_kernel(const KaParams p) {
     if (row_live) {
 #pragma unroll
       for (int nb = 0; nb < 16; ++nb)
-        *reinterpret_cast<float2*>(red + ((size_t)warp * KA_MAX_G + g) * KA_D + nb * 8 + 2 * t) =
+        *reinterpret_cast<float2*>(red + ((size_t)warp * p.G + g) * KA_D + nb * 8 + 2 * t) =
             make_float2(acc[nb][0], acc[nb][1]);
     }
     __syncthreads();
@@ -323,7 +327,7 @@ kivi_decode_attention_kernel(const KaParams p) {
       const int r = i / KA_D, ch = i - r * KA_D;
       float s = 0.0f;
 #pragma unroll
-      for (int w = 0; w < KA_WARPS; ++w) s += red[((size_t)w * KA_MAX_G + r) * KA_D + ch];
+      for (int w = 0; w < KA_WARPS; ++w) s += red[((size_t)w * p.G + r) * KA_D + ch];
       s = bf16_round(s);
       if (add_rounded) p.out[(outer * p.G + r) * KA_D + ch] = __float2bfloat16_rn(dst[r * KA_D + ch] + s);
       else dst[r * KA_D + ch] = s;
@@ -380,15 +384,16 @@ extern "C" int vq_kivi_decode_attention(const void* q, const void* k_packed, con
   VQ_REQUIRE(Tm + R > 0, "vq_kivi_decode_attention: no keys");
   VQ_REQUIRE(q && out && (Tm == 0 || (k_packed && k_scale && k_zero && v_packed && v_scale && v_zero)) &&
                  (R == 0 || (k_res && v_res)), "vq_kivi_decode_attention: null argument");
-  const size_t smem = (size_t)G * (Tm + R) * 6 + 2 * KA_STAGE_BYTES + (KA_WARPS * KA_MAX_G * KA_D + KA_WARPS +
-                                                                       KA_MAX_G * KA_D) * 4 + 64;
+  const int ngrp = v_block > 0 && v_block <= KA_D ? (int)(KA_D / v_block) : 1;
+  const size_t smem = (size_t)G * (Tm + R) * 6 + 2 * (size_t)ka_stage_bytes(ngrp) +
+                      (size_t)(KA_WARPS * G * KA_D + KA_WARPS + KA_MAX_G * KA_D) * 4 + 64;
   if (D != KA_D || G > KA_MAX_G || k_block <= 0 || k_block % KA_WKEYS != 0 || Tm % k_block != 0 || R % 16 != 0 ||
       (v_block != 32 && v_block != 64 && v_block != 128) || smem > 227 * 1024 || outer >= (1ll << 31) ||
       Tm >= (1ll << 24) || R >= (1ll << 24))
     return fail(VQ_EUNSUPPORTED,
                 "vq_kivi_decode_attention: needs head_dim 128, at most 8 query heads per KV head, key groups of a "
                 "multiple of 64 positions, value groups of 32, 64 or 128 channels, a multiple of 16 recent positions "
-                "and G * (Tm + R) * 6 + 86 KB of shared memory within 227 KB");
+                "and G * (Tm + R) * 6 bytes of scores beside two staged chunks within 227 KB of shared memory");
   VQ_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_packed) | reinterpret_cast<uintptr_t>(k_scale) |
                reinterpret_cast<uintptr_t>(k_zero) | reinterpret_cast<uintptr_t>(v_packed) | reinterpret_cast<uintptr_t>(v_scale) |
                reinterpret_cast<uintptr_t>(v_zero) | reinterpret_cast<uintptr_t>(k_res) | reinterpret_cast<uintptr_t>(v_res)) & 15) == 0,
@@ -407,7 +412,6 @@ extern "C" int vq_kivi_decode_attention(const void* q, const void* k_packed, con
   p.G = (int)G; p.Tm = (int)Tm; p.R = (int)R; p.k_block = (int)k_block;
   p.score_scale = score_scale;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int ngrp = (int)(KA_D / v_block);
   static unsigned long long configured = 0;
   if (first_call_on_device(&configured)) {
     const int limit = 227 * 1024;
