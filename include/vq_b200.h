@@ -414,6 +414,15 @@ int vq_rmsnorm_backward(const void* dy0, const void* dy1, const void* dy2, int g
                         const float* rsqrt_rows, const void* weight, const void* residual, void* dx,
                         float* partial_dw, void* dw, int64_t rows, int64_t cols, void* stream);
 
+/* A per-tensor e4m3 cast applied and undone, plus an optional addend, in one pass:
+ *   out = bf16(dequantize(quantize(x, scale, qmap = fp8_e4m3), scale) + y)
+ * -- the quantize -> dequantize pair a converted graph puts on a residual stream
+ * (quantized_ops::quantize / ::dequantize, ops/quantized.py:458-571) followed by aten.add, with each
+ * node's bfloat16 rounding: q = e4m3(bf16(x / s)) saturating at 448, d = bf16(q * s), out = bf16(d + y).
+ * x, y (or NULL), out: bfloat16, n elements (a multiple of 8), 16-byte aligned. */
+int vq_fp8_roundtrip_add(const void* x, const void* y, void* out, int64_t n, const void* scale, int scale_dtype,
+                         void* stream);
+
 /* FP8 casts fused with the bfloat16 operation that feeds them in a per-tensor FP8
  * decoder layer.  The reference's converted graph runs the producer (RMSNorm,
  * rotary embedding, SiLU * up, a transpose) as separate aten nodes and then

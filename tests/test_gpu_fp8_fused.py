@@ -285,3 +285,25 @@ def test_gated_gemm_equals_gemm_then_silu_mul_cast(m, inter, k):
     vb.ops.gemm_status()
     assert got.shape == (m, inter) and got.dtype == torch.uint8
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("shape", [(16, 4096), (3, 8), (257, 1024)])
+@pytest.mark.parametrize("with_y", [True, False])
+def test_roundtrip_add_equals_quantize_dequantize_add(shape, with_y):
+    """One kernel against the three graph nodes it replaces, bit for bit (values beyond +-448 saturate)."""
+    import voyager_b200 as vb
+
+    g = torch.Generator().manual_seed(shape[0])
+    x = (torch.randn(*shape, generator=g) * 3).bfloat16().cuda()
+    x.view(-1)[::97] *= 40.0                                    # some values past the e4m3 range at this scale
+    y = torch.randn(*shape, generator=g).bfloat16().cuda() if with_y else None
+    scale = torch.tensor(8.0 / 448.0, dtype=torch.bfloat16, device="cuda")
+    e4m3 = vb.get_quantization_map("fp8_e4m3").cuda()
+    q = torch.ops.quantized_ops.quantize(x, scale, None, None, None, e4m3)
+    want = torch.ops.quantized_ops.dequantize(q, scale)
+    if with_y:
+        want = want + y
+    got = vb.fp8.roundtrip_add(x, scale, y)
+    assert torch.equal(got, want)
+    got32 = vb.fp8.roundtrip_add(x, scale.float(), y)
+    assert torch.equal(got32, want)

@@ -239,6 +239,39 @@ transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
   }
 }
 
+// out = bf16(dequantize(quantize(x)) + y): the value x keeps after a per-tensor e4m3 cast,
+//   q = e4m3(bf16(x / s)) (saturating), d = bf16(q * s),
+// added to y (or alone when y is null).  Eight elements per thread.
+__device__ __forceinline__ float e4m3_byte_to_float(uint32_t byte) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)byte, __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+__global__ void __launch_bounds__(256)
+fp8_roundtrip_add_kernel(const uint4* __restrict__ x, const uint4* __restrict__ y, uint4* __restrict__ out, int64_t nvec,
+                         const void* __restrict__ scale, int scale_dt) {
+  const Divisor dv = make_divisor(scale, scale_dt);
+  for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 xv = __ldg(x + v);
+    uint4 yv = make_uint4(0, 0, 0, 0);
+    if (y != nullptr) yv = __ldg(y + v);
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, yw[4] = {yv.x, yv.y, yv.z, yv.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t codes = fp8_pair<true>(quot(lo_of(xw[j]), dv), quot(hi_of(xw[j]), dv));
+      float d0 = bf16r(__fmul_rn(e4m3_byte_to_float(codes & 0xFFu), dv.s));
+      float d1 = bf16r(__fmul_rn(e4m3_byte_to_float((codes >> 8) & 0xFFu), dv.s));
+      if (y != nullptr) {
+        d0 = __fadd_rn(d0, lo_of(yw[j]));
+        d1 = __fadd_rn(d1, hi_of(yw[j]));
+      }
+      const __nv_bfloat162 h = __floats2bfloat162_rn(d0, d1);
+      ow[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    out[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+
 inline int stream_grid(int64_t items, int threads, int per_sm) {
   int64_t blocks = (items + threads - 1) / threads;
   const int64_t cap = (int64_t)kSmCount * per_sm;
@@ -294,6 +327,21 @@ extern "C" int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* 
       static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint2*>(out), nvec, (int)(cols / 8),
       ld_gate / 8, ld_up / 8, scale, scale_dtype);
   return check_launch("silu_mul_quantize_kernel");
+}
+
+extern "C" int vq_fp8_roundtrip_add(const void* x, const void* y, void* out, int64_t n, const void* scale,
+                                    int scale_dtype, void* stream) {
+  VQ_REQUIRE(n >= 0, "vq_fp8_roundtrip_add: negative size");
+  if (n == 0) return VQ_OK;
+  VQ_REQUIRE(x && out && scale, "vq_fp8_roundtrip_add: null argument");
+  VQ_REQUIRE(scale_dtype >= VQ_BF16 && scale_dtype <= VQ_F32, "vq_fp8_roundtrip_add: bad scale dtype");
+  VQ_REQUIRE(n % 8 == 0, "vq_fp8_roundtrip_add: the element count must be a multiple of 8");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15) == 0,
+             "vq_fp8_roundtrip_add: buffers must be 16-byte aligned");
+  const int64_t nvec = n / 8;
+  fp8_roundtrip_add_kernel<<<stream_grid(nvec, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(y), static_cast<uint4*>(out), nvec, scale, scale_dtype);
+  return check_launch("fp8_roundtrip_add_kernel");
 }
 
 extern "C" int vq_rope_quantize_fp8(const void* x, const void* cosv, const void* sinv, void* out, int64_t T,

@@ -183,6 +183,24 @@ def attention_fp8(q8: torch.Tensor, k8: torch.Tensor, vt8: torch.Tensor, alpha_q
 
 
 @N.device_guarded
+def roundtrip_add(x: torch.Tensor, scale: torch.Tensor, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``dequantize(quantize(x, scale, qmap=fp8_e4m3), scale) [+ y]`` in one kernel, each node's bfloat16
+    rounding kept: what a per-tensor e4m3 cast leaves of a residual stream, added to the branch output."""
+    x = _bf16_input("x", x)
+    scale = _scale_arg(scale)
+    if y is not None:
+        y = _bf16_input("y", y)
+        if y.shape != x.shape:
+            raise ValueError("roundtrip_add: x and y differ in shape")
+    if x.numel() % 8:
+        raise NotImplementedError("roundtrip_add takes a multiple of 8 elements")
+    out = torch.empty_like(x)
+    N.check(N.lib().vq_fp8_roundtrip_add(x.data_ptr(), _ptr(y), out.data_ptr(), x.numel(), scale.data_ptr(),
+                                         _dtype_id(scale.dtype), _stream()), "vq_fp8_roundtrip_add")
+    return out
+
+
+@N.device_guarded
 def attention_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, score_scale: Optional[float] = None,
                    round_acc: bool = True) -> torch.Tensor:
     """Causal self-attention on bfloat16 operands in one kernel, with the roundings of the eager graph

@@ -456,11 +456,12 @@ class Mxnf4DecodeLayer:
     def __init__(self, weights, tables, cache, residual_scale, shape: LlamaShape, fused_attention=True):
         self.w, self.t, self.cache, self.shape = weights, tables, cache, shape
         self.fused_attention = fused_attention
+        self.fused_residual = fused_attention      # the three residual nodes (quantize, dequantize, add) as one kernel
         self.residual_scale = residual_scale
         self.ln1, self.ln2 = weights["ln1"], weights["ln2"]
 
-    # kernels of this package per step: 4 quantize_mx, 4 linears, the attention, 2 x (quantize + dequantize)
-    LAUNCHES = 13
+    # kernels of this package per step: 4 quantize_mx, 4 linears, the attention, 2 residual casts + adds
+    LAUNCHES = 11
 
     def _linear(self, x, name):
         from . import packed as P
@@ -472,6 +473,14 @@ class Mxnf4DecodeLayer:
     def _through_fp8(self, x):
         q = torch.ops.quantized_ops.quantize(x, self.residual_scale, None, None, None, self.t["e4m3"])
         return torch.ops.quantized_ops.dequantize(q, self.residual_scale)
+
+    def _residual_add(self, x, branch):
+        """``dequantize(quantize(x)) + branch``: the residual stream through its per-tensor e4m3 cast."""
+        if self.fused_residual:
+            from . import fp8 as F8
+
+            return F8.roundtrip_add(x, self.residual_scale, branch)
+        return self._through_fp8(x) + branch
 
     def forward(self, x, rope):
         """``x [B, hidden]``; ``rope = (cos, sin)`` of the new position, ``[head_dim]`` each."""
@@ -502,10 +511,10 @@ class Mxnf4DecodeLayer:
             p = torch.softmax(scores * (1.0 / math.sqrt(d)), -1, dtype=torch.float32).to(x.dtype)
             tm = k_main.shape[-2]
             ctx = torch.matmul(p[..., :tm], v_main) + torch.matmul(p[..., tm:], v_res)
-        x1 = self._through_fp8(x) + self._linear(ctx.reshape(B, hq * d), "o")
+        x1 = self._residual_add(x, self._linear(ctx.reshape(B, hq * d), "o"))
         gu = self._linear(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps), "gate_up")
         inter = gu.shape[-1] // 2
-        return self._through_fp8(x1) + self._linear(F.silu(gu[:, :inter]) * gu[:, inter:], "down")
+        return self._residual_add(x1, self._linear(F.silu(gu[:, :inter]) * gu[:, inter:], "down"))
 
     __call__ = forward
 
