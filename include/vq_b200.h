@@ -414,6 +414,17 @@ int vq_rmsnorm_backward(const void* dy0, const void* dy1, const void* dy2, int g
                         const float* rsqrt_rows, const void* weight, const void* residual, void* dx,
                         float* partial_dw, void* dw, int64_t rows, int64_t cols, void* stream);
 
+/* One decode step's RoPE and cache append on the merged q/k/v projection qkv [B, (q_heads + 2 kv_heads) * d]
+ * (bfloat16): query head h, rotated, to q_out [B, q_heads, d]; key head h, rotated, to
+ * k_dst + (b * kv_heads + h) * kv_stride; value head h, unchanged, to v_dst + (b * kv_heads + h) * kv_stride
+ * -- k_dst / v_dst point at this step's slot of a [B, kv_heads, R, d] window, kv_stride = R * d elements.
+ * cos / sin: bfloat16 [d] shared by all sequences (cs_stride = 0) or one row per sequence (cs_stride elements
+ * apart).  y = bf16(bf16(x * cos) + bf16(rot(x) * sin)), rot(x) = (-x[d/2:], x[:d/2]): HF rotate_half
+ * RoPE as the graph's mul / cat / neg / add nodes compute it, then the index-copy of the cache update. */
+int vq_rope_decode_append(const void* qkv, const void* cosv, const void* sinv, void* q_out, void* k_dst, void* v_dst,
+                          int64_t B, int64_t q_heads, int64_t kv_heads, int64_t d, int64_t kv_stride,
+                          int64_t cs_stride, void* stream);
+
 /* A per-tensor e4m3 cast applied and undone, plus an optional addend, in one pass:
  *   out = bf16(dequantize(quantize(x, scale, qmap = fp8_e4m3), scale) + y)
  * -- the quantize -> dequantize pair a converted graph puts on a residual stream

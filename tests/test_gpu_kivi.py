@@ -141,3 +141,23 @@ def test_decode_attention_declines_other_layouts():
     q, keys, values, k_res, v_res = _decode_problem(1, 1, 2, 128, 16, 64, 64, seed=5)
     assert vb.kivi.decode_attention(q, values, keys, k_res, v_res) is None              # keys / values swapped
     assert vb.kivi.decode_attention(q, keys, values, k_res[..., :8, :], v_res[..., :8, :]) is None   # R = 8
+
+
+@pytest.mark.parametrize("per_sequence", [False, True])
+def test_rope_append_equals_the_graph_nodes(per_sequence):
+    vb = _vb()
+    B, hq, hkv, d, R = 3, 8, 2, 128, 16
+    g = torch.Generator(device="cuda").manual_seed(1)
+    qkv = torch.randn(B, (hq + 2 * hkv) * d, generator=g, device="cuda").bfloat16()
+    cos = torch.randn((B, d) if per_sequence else (d,), generator=g, device="cuda").bfloat16()
+    sin = torch.randn((B, d) if per_sequence else (d,), generator=g, device="cuda").bfloat16()
+    k_win = torch.randn(B, hkv, R, d, generator=g, device="cuda").bfloat16()
+    v_win = torch.randn(B, hkv, R, d, generator=g, device="cuda").bfloat16()
+    want_k, want_v = k_win.clone(), v_win.clone()
+    c, s = (cos[:, None], sin[:, None]) if per_sequence else (cos, sin)
+    rotate = lambda v: v * c + torch.cat([-v[..., d // 2:], v[..., :d // 2]], -1) * s
+    want_q = rotate(qkv[:, :hq * d].reshape(B, hq, d))
+    want_k[:, :, 5].copy_(rotate(qkv[:, hq * d:(hq + hkv) * d].reshape(B, hkv, d)))
+    want_v[:, :, 5].copy_(qkv[:, (hq + hkv) * d:].reshape(B, hkv, d))
+    got_q = vb.kivi.rope_append(qkv, cos, sin, hq, k_win, v_win, 5)
+    assert torch.equal(got_q, want_q) and torch.equal(k_win, want_k) and torch.equal(v_win, want_v)

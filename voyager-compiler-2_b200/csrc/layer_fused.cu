@@ -239,6 +239,49 @@ transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
   }
 }
 
+// One decode step's RoPE and cache append.  qkv: [B, (hq + 2 hkv) * d] bfloat16, the merged projection's
+// output.  Query head h goes, rotated, to q_out[b, h, :]; key head h, rotated, to k_dst + (b * hkv + h) *
+// kv_stride; value head h, as it is, to v_dst + (b * hkv + h) * kv_stride (the slot of this step's
+// position in a [B, hkv, R, d] window: kv_stride = R * d).  cos / sin: [d] (cs_stride = 0) or one row per
+// sequence.  y = bf16(bf16(x * cos) + bf16(rot(x) * sin)), rot(x) = (-x[d/2:], x[:d/2]): the graph's
+// four elementwise nodes with their roundings.  One thread per 8 elements.
+__global__ void __launch_bounds__(256)
+rope_decode_append_kernel(const uint4* __restrict__ qkv, const uint4* __restrict__ cosv, const uint4* __restrict__ sinv,
+                          uint4* __restrict__ q_out, uint4* __restrict__ k_dst, uint4* __restrict__ v_dst, int B, int hq,
+                          int hkv, int d, int64_t kv_stride, int64_t cs_stride) {
+  const int vpd = d >> 3, half = vpd >> 1;
+  const int heads = hq + 2 * hkv;
+  const int64_t total = (int64_t)B * heads * vpd;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % vpd);
+    const int h = (int)((idx / vpd) % heads);
+    const int b = (int)(idx / ((int64_t)vpd * heads));
+    const uint4* row = qkv + ((int64_t)b * heads + h) * vpd;
+    const uint4 xv = __ldg(row + v);
+    if (h >= hq + hkv) {   // a value head: appended unrotated
+      v_dst[((int64_t)b * hkv + (h - hq - hkv)) * kv_stride + v] = xv;
+      continue;
+    }
+    const uint4 pvv = __ldg(row + (v < half ? v + half : v - half));
+    const uint4 cv = __ldg(cosv + b * cs_stride + v), sv = __ldg(sinv + b * cs_stride + v);
+    const uint32_t a[4] = {xv.x, xv.y, xv.z, xv.w}, p[4] = {pvv.x, pvv.y, pvv.z, pvv.w};
+    const uint32_t c[4] = {cv.x, cv.y, cv.z, cv.w}, s[4] = {sv.x, sv.y, sv.z, sv.w};
+    const float sign = v < half ? -1.0f : 1.0f;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float y0 = __fadd_rn(bf16r(__fmul_rn(lo_of(a[j]), lo_of(c[j]))), bf16r(__fmul_rn(sign * lo_of(p[j]), lo_of(s[j]))));
+      const float y1 = __fadd_rn(bf16r(__fmul_rn(hi_of(a[j]), hi_of(c[j]))), bf16r(__fmul_rn(sign * hi_of(p[j]), hi_of(s[j]))));
+      const __nv_bfloat162 hh = __floats2bfloat162_rn(y0, y1);
+      o[j] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+    const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+    if (h < hq) q_out[((int64_t)b * hq + h) * vpd + v] = ov;
+    else k_dst[((int64_t)b * hkv + (h - hq)) * kv_stride + v] = ov;
+  }
+}
+
 // out = bf16(dequantize(quantize(x)) + y): the value x keeps after a per-tensor e4m3 cast,
 //   q = e4m3(bf16(x / s)) (saturating), d = bf16(q * s),
 // added to y (or alone when y is null).  Eight elements per thread.
@@ -327,6 +370,28 @@ extern "C" int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* 
       static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint2*>(out), nvec, (int)(cols / 8),
       ld_gate / 8, ld_up / 8, scale, scale_dtype);
   return check_launch("silu_mul_quantize_kernel");
+}
+
+extern "C" int vq_rope_decode_append(const void* qkv, const void* cosv, const void* sinv, void* q_out, void* k_dst,
+                                     void* v_dst, int64_t B, int64_t q_heads, int64_t kv_heads, int64_t d,
+                                     int64_t kv_stride, int64_t cs_stride, void* stream) {
+  VQ_REQUIRE(B >= 0 && q_heads >= 0 && kv_heads >= 0 && d > 0, "vq_rope_decode_append: bad extent");
+  if (B == 0 || q_heads + kv_heads == 0) return VQ_OK;
+  VQ_REQUIRE(qkv && cosv && sinv && (q_heads == 0 || q_out) && (kv_heads == 0 || (k_dst && v_dst)),
+             "vq_rope_decode_append: null argument");
+  VQ_REQUIRE(d % 16 == 0 && d < (1 << 20), "vq_rope_decode_append: head_dim must be a multiple of 16");
+  VQ_REQUIRE(kv_stride % 8 == 0 && kv_stride >= d && cs_stride % 8 == 0 && cs_stride >= 0,
+             "vq_rope_decode_append: strides are multiples of 8 elements, the window's at least one head row");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(cosv) | reinterpret_cast<uintptr_t>(sinv) |
+               reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_dst) | reinterpret_cast<uintptr_t>(v_dst)) & 15) == 0,
+             "vq_rope_decode_append: buffers must be 16-byte aligned");
+  VQ_REQUIRE(B < (1ll << 31) && q_heads + 2 * kv_heads < (1 << 20), "vq_rope_decode_append: extent too large");
+  const int64_t total = B * (q_heads + 2 * kv_heads) * (d / 8);
+  rope_decode_append_kernel<<<stream_grid(total, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(qkv), static_cast<const uint4*>(cosv), static_cast<const uint4*>(sinv),
+      static_cast<uint4*>(q_out), static_cast<uint4*>(k_dst), static_cast<uint4*>(v_dst), (int)B, (int)q_heads,
+      (int)kv_heads, (int)d, kv_stride / 8, cs_stride / 8);
+  return check_launch("rope_decode_append_kernel");
 }
 
 extern "C" int vq_fp8_roundtrip_add(const void* x, const void* y, void* out, int64_t n, const void* scale,

@@ -157,3 +157,29 @@ def _decode_attention(q, keys, values, k_recent, v_recent, score_scale):
         return None
     N.check(rc, "vq_kivi_decode_attention")
     return out
+
+
+@N.device_guarded
+def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, q_heads: int, k_window: torch.Tensor,
+                v_window: torch.Tensor, slot: int = -1) -> torch.Tensor:
+    """RoPE on a decode step's merged projection ``qkv [B, (q_heads + 2 kv_heads) * d]`` and the cache append in
+    one kernel: returns the rotated queries ``[B, q_heads, d]`` and writes the rotated keys and the values into
+    position ``slot`` of the ``[B, kv_heads, R, d]`` windows.  ``cos`` / ``sin``: ``[d]`` or ``[B, d]``."""
+    B, hkv, R, d = k_window.shape
+    if qkv.shape != (B, (q_heads + 2 * hkv) * d) or v_window.shape != k_window.shape:
+        raise ValueError("rope_append: shapes do not agree")
+    if any(t.dtype != torch.bfloat16 for t in (qkv, cos, sin, k_window, v_window)):
+        raise NotImplementedError("rope_append takes bfloat16 tensors")
+    if not (k_window.is_contiguous() and v_window.is_contiguous()):
+        raise ValueError("rope_append: the windows must be contiguous")
+    qkv, cos, sin = qkv.contiguous(), cos.contiguous(), sin.contiguous()
+    if cos.shape != sin.shape or cos.shape not in ((d,), (B, d)):
+        raise ValueError("rope_append: cos / sin are [d] or [B, d]")
+    slot = slot % R
+    q_out = torch.empty((B, q_heads, d), dtype=torch.bfloat16, device=qkv.device)
+    esz = 2
+    N.check(N.lib().vq_rope_decode_append(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), q_out.data_ptr(),
+                                          k_window.data_ptr() + slot * d * esz, v_window.data_ptr() + slot * d * esz,
+                                          B, q_heads, hkv, d, R * d, d if cos.dim() == 2 else 0, _stream()),
+            "vq_rope_decode_append")
+    return q_out

@@ -460,8 +460,8 @@ class Mxnf4DecodeLayer:
         self.residual_scale = residual_scale
         self.ln1, self.ln2 = weights["ln1"], weights["ln2"]
 
-    # kernels of this package per step: 4 quantize_mx, 4 linears, the attention, 2 residual casts + adds
-    LAUNCHES = 11
+    # kernels of this package per step: 4 quantize_mx, 4 linears, RoPE + append, the attention, 2 residual casts + adds
+    LAUNCHES = 12
 
     def _linear(self, x, name):
         from . import packed as P
@@ -493,12 +493,17 @@ class Mxnf4DecodeLayer:
             return v * cos + torch.cat([-v[..., half:], v[..., :half]], -1) * sin
 
         qkv = self._linear(F.rms_norm(x, (sh.hidden,), self.ln1, sh.eps), "qkv")
-        q = rotate(qkv[:, :hq * d].reshape(B, hq, d))
-        k = rotate(qkv[:, hq * d:(hq + hkv) * d].reshape(B, hkv, d))
-        v = qkv[:, (hq + hkv) * d:].reshape(B, hkv, d)
         k_res, v_res = self.cache["k_res"], self.cache["v_res"]
-        k_res[:, :, -1].copy_(k)                   # this step's token takes the last recent slot
-        v_res[:, :, -1].copy_(v)
+        if self.fused_attention:
+            from . import kivi as KV
+
+            q = KV.rope_append(qkv, cos, sin, hq, k_res, v_res, -1)   # this step's token takes the last recent slot
+        else:
+            q = rotate(qkv[:, :hq * d].reshape(B, hq, d))
+            k = rotate(qkv[:, hq * d:(hq + hkv) * d].reshape(B, hkv, d))
+            v = qkv[:, (hq + hkv) * d:].reshape(B, hkv, d)
+            k_res[:, :, -1].copy_(k)
+            v_res[:, :, -1].copy_(v)
         qg = q.reshape(B, hkv, hq // hkv, d)
         ctx = None
         if self.fused_attention:
