@@ -218,7 +218,9 @@ gemm_lut4_kernel(Lut4Params p) {
   // the table entry of byte `which` (0..3) of `word`: address = tb_lane with byte 1 replaced by that byte
   auto lookup = [&](uint32_t word, int which) {
     uint32_t r;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(__byte_perm(word, tb_lane, 0x7604u | ((uint32_t)which << 4))));
+    // not volatile: the table is constant once the CTA has passed its barrier, and the scheduler may then
+    // hoist an iteration's lookups ahead of the MMAs that consume them
+    asm("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(__byte_perm(word, tb_lane, 0x7604u | ((uint32_t)which << 4))));
     return r;
   };
   // the eight MMA steps of one iteration: step s takes bytes 2 s and 2 s + 1 of each row's 16-byte vector
