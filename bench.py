@@ -747,8 +747,9 @@ class C4Model:
     name = "c4m"
     description = ("c4m: NVFP4 (e2m1, bs=16, e4m3 block scales, bf16 global scale on activations and weights) prefill of a "
                    "full 32-layer Llama-3.1-8B-shaped model, 1 x 8192 tokens per GPU: 7 linears per layer as fused casts "
-                   "+ kind::mxf4nvf4 block-scaled tensor-core GEMMs (q/k/v and gate/up merged), bf16 RMSNorm / RoPE / "
-                   "causal attention / SwiGLU as torch operators, final norm + NVFP4 lm_head on the last position")
+                   "+ kind::mxf4nvf4 block-scaled tensor-core GEMMs (q/k/v and gate/up merged), the graph's bf16 causal attention "
+                   "as one tcgen05 kernel with its roundings, bf16 RMSNorm / RoPE / SwiGLU as torch operators, final norm + "
+                   "NVFP4 lm_head on the last position")
     tokens = 8192
     layers = 32
     n_sets = 2
@@ -868,8 +869,8 @@ class C3:
                    "sequence), 4096 positions cached: weights lut4_to_int6 (NF4 levels) bs=64 with fp8_e5m3 scales, stored "
                    "packed (0.53 B/parameter) and read by the weight-streaming linear; activations quantize_mx'd the same "
                    "way every step; residual adds through a per-tensor fp8_e4m3 cast; KV cache KIVI 2-bit (keys per channel, "
-                   "values per token, groups of 64, packed) with the newest 128 positions in bf16, read by the fused unpack + "
-                   "dequantize kernel; bf16 attention as torch operators; final norm + lm_head")
+                   "values per token, groups of 64, packed) with the newest 128 positions in bf16; RoPE + append, the attention "
+                   "straight from the 2-bit codes and the residual casts as one kernel each; final norm + lm_head")
     tokens = 16
     n_sets = 2
     dtype = "bf16 operands decoded from 4-bit codes x e5m3 block scales (fp32 accumulate)"
