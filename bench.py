@@ -1478,7 +1478,10 @@ def run_ours(args, rank, world, local_rank):
         if world == 1 and args.workload == "c2" and not args.no_secondary:
             del wl
             torch.cuda.empty_cache()
-            line["secondary"] = [run_secondary(name, dev, rank, peaks, 50, local_rank) for name in ("q1", "c1", "c4")]
+            # every other BASELINE configuration, so that the default run's line carries them all (their CPU legs
+            # and self-checks run when they are the --workload)
+            line["secondary"] = [run_secondary(name, dev, rank, peaks, steps, local_rank)
+                                 for name, steps in (("q1", 50), ("c1", 50), ("c4", 50), ("c3", 10), ("c4m", 3), ("c5", 2))]
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
