@@ -1359,6 +1359,139 @@ def library_leg(wl, kind=None):
 LIBRARY_KIND = {"c2": "fp8", "c2s": "fp8", "c4": "fp4", "c4m": "fp4"}
 
 
+class C4TP:
+    """Workload c4m over N GPUs, tensor-parallel (strong scaling): the same 8192-token prefill of 32 NVFP4
+    decoder layers, q/k/v and gate/up column-parallel, attention head-parallel, o_proj / down_proj row-parallel
+    with float32 partial products reduce-scattered over NCCL, activations sharded by token rows between the
+    blocks and gathered as packed NVFP4 codes + scale tiles; final norm + lm_head on the rank that holds the last
+    position."""
+    name = "c4m"
+    tokens = C4Model.tokens
+    layers = C4Model.layers
+    n_sets = 2
+    dtype = C4Model.dtype
+    cpu_tokens = C4Model.cpu_tokens
+    cpu_sample = C4Model.cpu_sample
+
+    def __init__(self, dev, rank, world):
+        import voyager_b200
+
+        self.vb = voyager_b200
+        W, P, NV = voyager_b200.workloads, voyager_b200.parallel, voyager_b200.nvfp4
+        self.shape, self.rank, self.world = W.LLAMA_8B, rank, world
+        self.description = C4Model.description.replace("1 x 8192 tokens per GPU", f"1 x 8192 tokens split over {world} GPUs "
+                                                       "(tensor parallel: column-parallel QKV and gate/up, head-parallel "
+                                                       "attention, row-parallel o_proj and down_proj; NCCL all-gather of "
+                                                       "packed NVFP4 codes + scale tiles, amax all-reduce, reduce-scatter "
+                                                       "of float32 partial products)")
+        self.model = []
+        for i in range(self.layers):                 # the same seeds on every rank: each quantizes, then keeps its slices
+            params = W.make_layer_params_on_device(50 + i, self.shape, dev)
+            self.model.append(P.Nvfp4DecoderLayerTP(params, self.shape))
+            del params
+        self.last = rank == world - 1
+        if self.last:
+            g = torch.Generator(device=dev).manual_seed(50 + self.layers)
+            head = (torch.randn(self.shape.vocab, self.shape.hidden, generator=g, device=dev) * 0.02).bfloat16()
+            self.head = NV.quantize_nvfp4(head)
+            del head
+            self.norm = torch.ones(self.shape.hidden, dtype=torch.bfloat16, device=dev)
+            self.one = torch.ones((), device=dev)
+        full = [W.make_hidden_states(300 + i, self.tokens, self.shape, dev) for i in range(self.n_sets)]
+        lo, hi = P.shard_bounds(self.tokens, rank, world)
+        self.lo, self.hi = lo, hi
+        self.x = [x[lo:hi].contiguous() for x in full]
+        del full
+        self.launches_per_step = self.layers * P.Nvfp4DecoderLayerTP.LAUNCHES + (3 if self.last else 0)
+        self.h2d_bytes = (hi - lo) * self.shape.hidden * 2
+        self.d2h_bytes = (hi - lo) * self.shape.hidden * 2
+        self.forward(self.x[0])
+        torch.cuda.synchronize()
+        self.launch = "CUDA graph replay per step (collectives captured)"
+        try:
+            self.graphs = [capture(lambda x=x: self.forward(x)) for x in self.x]
+        except Exception as exc:  # the collectives could not be captured on this build: launch every kernel
+            torch.cuda.synchronize()
+            self.launch = f"eager launches per step (graph capture refused: {type(exc).__name__})"
+            self.graphs = [(EagerStep(lambda x=x: self.forward(x), self.forward(x)),) for x in self.x]
+            self.graphs = [(g[0], g[0].out) for g in self.graphs]
+        self.pipeline = HostPipeline(self.x, [x.cpu().pin_memory() for x in self.x], self.graphs)
+
+    def forward(self, rows):
+        import torch.nn.functional as F
+
+        for layer in self.model:
+            rows = layer(rows)
+        if self.last:
+            NV = self.vb.nvfp4
+            h = F.rms_norm(rows[-1:], (self.shape.hidden,), self.norm, self.shape.eps)
+            codes, scales, t = NV.quantize_nvfp4(h)
+            self.logits = NV.nvfp4_linear(codes, scales, self.head[0], self.head[1], (t * self.head[2]).float(), self.one, None)
+        return rows
+
+    def step(self, i):
+        self.graphs[i % self.n_sets][0].replay()
+
+    def e2e_step(self, i):
+        self.pipeline.step(i)
+
+    def self_check(self):
+        """This rank's rows out of the FIRST tensor-parallel layer against the same rows of the unsharded layer run
+        on this GPU alone (same weights and input; the full model's 32 layers compound 4-bit code flips)."""
+        W = self.vb.workloads
+        rows = self.model[0](self.x[0])
+        params = W.make_layer_params_on_device(50, self.shape, rows.device)
+        single = W.Nvfp4DecoderLayer(params, self.shape)
+        del params
+        full = single(W.make_hidden_states(300, self.tokens, self.shape, rows.device))
+        want = full[self.lo:self.hi].float()
+        rms = float((rows.float() - want).pow(2).mean().sqrt() / want.pow(2).mean().sqrt())
+        return {"tensor_parallel_rows_vs_one_gpu_layer_max": (max_rel(rows, full[self.lo:self.hi]), 1e-1),
+                "tensor_parallel_rows_vs_one_gpu_layer_rms": (rms, 2e-2)}
+
+    def collective_share(self, steps):
+        """Share of an (uncaptured) step's device time spent inside the collectives, from CUDA events around them;
+        a collective's span includes waiting for the slowest rank."""
+        steps = min(steps, 3)
+        self.forward(self.x[0])
+        for layer in self.model:
+            layer.timed = True
+            layer.collective_events = []
+        elapsed = time_region(lambda i: self.forward(self.x[i % self.n_sets]), steps, torch.cuda.synchronize)
+        inside = sum(layer.collective_seconds() for layer in self.model)
+        for layer in self.model:
+            layer.timed = False
+        per_layer = self.vb.parallel.Nvfp4DecoderLayerTP.COLLECTIVES
+        return {"share": inside / elapsed, "collective_ms_per_step": inside / steps * 1e3,
+                "eager_ms_per_step": elapsed / steps * 1e3, "collectives_per_step": per_layer * self.layers,
+                "what": "per layer: 4 x all-reduce(max) of one amax, 2 x (all-gather of packed codes [T, 2048] bytes + "
+                        "scale tiles), 2 x reduce-scatter of float32 [T, 4096] partial products"}
+
+    def roofline(self, peaks, reps):
+        """This rank's rows of the merged gate/up NVFP4 GEMM: [8192, 4096] x [2 * 14336 / N, 4096]^T."""
+        NV = self.vb.nvfp4
+        layer = self.model[0]
+        acts = [torch.randn(self.tokens, self.shape.hidden, device="cuda").bfloat16() for _ in range(2)]
+        packed = [NV.quantize_nvfp4(a) for a in acts]
+        cols = [(t * layer.tw_gu).float() for _, _, t in packed]
+        run = lambda i: NV.nvfp4_gemm(NV.PackedNVFP4(packed[i % 2][0], packed[i % 2][1]), layer.w_gu, None, None,
+                                      torch.bfloat16, alpha_cols=cols[i % 2])
+        for i in range(3):
+            run(i)
+        reps = min(reps, 50)
+        secs = time_region(run, reps, torch.cuda.synchronize) / reps
+        n = layer.w_gu.codes.shape[0]
+        achieved = 2.0 * self.tokens * n * self.shape.hidden / secs / 1e12
+        peak, source = fp4_peak(peaks)
+        return secs, {"kernel": f"gemm_nvfp4 (tcgen05 kind::mxf4nvf4.block_scale, 8192x{n}x4096: this rank's columns of the "
+                                "merged gate/up projection)",
+                      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                      "peak_source": source, "traffic": None}
+
+
+TENSOR_PARALLEL = {"c2": C2TP, "c4m": C4TP}
+
+
 def run_secondary(name, dev, rank, peaks, steps, device_index):
     """A further workload measured after the main region: device-timed throughput, its dominant kernel's
     roofline and its library baseline."""
@@ -1387,6 +1520,14 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # The communicator's ranks show in NCCL's log.  NCCL writes it to the C stdout: point that at stderr and
+        # keep the real stdout for the one JSON line.
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+        sys.stdout.flush()
+        real_stdout = os.dup(1)
+        os.dup2(2, 1)
+        sys.stdout = os.fdopen(real_stdout, "w")
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
@@ -1394,8 +1535,8 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    tensor_parallel = world > 1 and args.workload == "c2" and not args.replicas
-    wl = C2TP(dev, rank, world) if tensor_parallel else WORKLOADS[args.workload](dev, rank)
+    tensor_parallel = world > 1 and args.workload in TENSOR_PARALLEL and not args.replicas
+    wl = TENSOR_PARALLEL[args.workload](dev, rank, world) if tensor_parallel else WORKLOADS[args.workload](dev, rank)
     warmup = max(args.warmup, 3)
     for i in range(warmup):
         wl.step(i)
@@ -1418,11 +1559,15 @@ def run_ours(args, rank, world, local_rank):
     roof = timed_roofline(wl, peaks, 200, local_rank)
     collectives = wl.collective_share(min(args.steps, 50)) if tensor_parallel else None
     replicas_elapsed = 0.0
-    checks = dict(wl.self_check()) if rank == 0 and hasattr(wl, "self_check") else {}
+    # a tensor-parallel self-check runs collectives: every rank takes part, rank 0 reports
+    checks = dict(wl.self_check()) if hasattr(wl, "self_check") and (rank == 0 or tensor_parallel) else {}
     if tensor_parallel:
-        # the same layer as N independent replicas (one full 2048-token batch per GPU, no exchange)
+        # the same workload as N independent replicas (one full batch per GPU, no exchange)
         del wl.graphs, wl.pipeline
-        rep = C2(dev, rank)
+        if hasattr(wl, "model"):
+            del wl.model
+        torch.cuda.empty_cache()
+        rep = WORKLOADS[args.workload](dev, rank)
         for i in range(3):
             rep.step(i)
         replicas_elapsed = time_region(rep.step, args.steps, barrier)
@@ -1462,7 +1607,7 @@ def run_ours(args, rank, world, local_rank):
             line["collectives"] = collectives
             line["replicas"] = {"value": wl.tokens * args.steps * world / replicas_elapsed, "unit": "tok/s",
                                 "scaling": "weak", "ms_per_step": replicas_elapsed / args.steps * 1e3,
-                                "what": "the same layer as independent replicas, one 2048-token batch per GPU, no exchange"}
+                                "what": f"the same workload as independent replicas, one {wl.tokens}-token batch per GPU, no exchange"}
         if world == 1:
             reps = 2 if wl.cpu_tokens >= 2048 and args.workload.startswith("c2") else 3
             value, dt, cores, state, cpu_out = time_cpu_baseline(WORKLOADS[args.workload], reps)
@@ -1482,7 +1627,7 @@ def run_ours(args, rank, world, local_rank):
             # and self-checks run when they are the --workload)
             line["secondary"] = [run_secondary(name, dev, rank, peaks, steps, local_rank)
                                  for name, steps in (("q1", 50), ("c1", 50), ("c4", 50), ("c3", 10), ("c4m", 3), ("c5", 2))]
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
     if failed:

@@ -49,6 +49,45 @@ def test_two_gpu_fp8_decoder_layer_matches_one_gpu_and_the_oracle():
     assert float((got.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
 
 
+def test_two_gpu_nvfp4_decoder_layer():
+    """The NVFP4 layer sharded over two GPUs (packed codes and scale tiles gathered, amax all-reduced, float32
+    partial products reduce-scattered) against the same layer on one GPU and against the CPU oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import voyager_b200
+    from oracle import layers as OL
+
+    W = voyager_b200.workloads
+    shape, tokens, params, x = tp_common.nvfp4_layer_problem()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(tp_common.run_rank_nvfp4_layer, args=(2, 29629, results), nprocs=2, join=True)
+    got = results["out"].float()
+    single = W.Nvfp4DecoderLayer({k: v.cuda() for k, v in params.items()}, shape)(x.cuda()).float().cpu()
+    # every weight code and global scale equals the single-GPU one; float32 summation order differs in the
+    # row-parallel linears, and a 4-bit code that flips downstream moves a value by up to a third
+    err = (got - single).abs()
+    assert float(err.max()) <= 6e-2 * float(single.abs().max())
+    assert float(err.pow(2).mean().sqrt() / single.pow(2).mean().sqrt()) <= 1e-2
+    want = OL.nvfp4_decoder_layer(x, params, shape, W.rope_tables(tokens, shape, "cpu"), W.causal_mask(tokens, "cpu")).float()
+    err = (got - want).abs()
+    assert float(err.max()) <= 6e-2 * float(want.abs().max())
+    assert float(err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) <= 2e-2
+
+
+def test_nvfp4_tensor_parallel_layer_on_one_rank_is_the_layer():
+    """World size 1 (no process group): the sharding code paths with whole tensors give the single-GPU layer."""
+    import voyager_b200
+
+    W, P = voyager_b200.workloads, voyager_b200.parallel
+    shape, tokens, params, x = tp_common.nvfp4_layer_problem()
+    dev = {k: v.cuda() for k, v in params.items()}
+    got = P.Nvfp4DecoderLayerTP(dev, shape)(x.cuda())
+    want = W.Nvfp4DecoderLayer(dev, shape)(x.cuda())
+    voyager_b200.ops.gemm_status()
+    assert torch.equal(got, want)
+
+
 def test_two_gpu_layer_parallel_gptq_with_the_device_solve():
     """Five GPTQ problems dealt to two GPUs by cost, each solved by the CUDA sweep on its owner, the
     compensated weights broadcast over NCCL (bfloat16 model weights, float32 on the wire)."""

@@ -117,6 +117,40 @@ def run_rank_fp8_layer(rank, world, port, results):
         dist.destroy_process_group()
 
 
+def nvfp4_layer_problem(seed=7):
+    import voyager_b200
+
+    W = voyager_b200.workloads
+    shape = W.LlamaShape(hidden=512, heads=8, kv_heads=4, head_dim=128, intermediate=1024, vocab=1024)
+    tokens = 256
+    return shape, tokens, W.make_layer_params(seed, shape), W.make_hidden_states(seed + 1, tokens, shape)
+
+
+def run_rank_nvfp4_layer(rank, world, port, results):
+    """The tensor-parallel NVFP4 decoder layer on ``world`` GPUs; rank 0 gathers the output rows."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    try:
+        import voyager_b200
+
+        P = voyager_b200.parallel
+        dev = f"cuda:{rank}"
+        shape, tokens, params, x = nvfp4_layer_problem()
+        layer = P.Nvfp4DecoderLayerTP({k: v.to(dev) for k, v in params.items()}, shape)
+        lo, hi = P.shard_bounds(tokens, rank, world)
+        rows = layer(x[lo:hi].to(dev))
+        out = P.all_gather_rows(rows)
+        voyager_b200.ops.gemm_status()
+        assert voyager_b200.fp8.attention_status() == 0
+        if rank == 0:
+            results["out"] = out.cpu()
+    finally:
+        dist.destroy_process_group()
+
+
 def gptq_problems(device="cpu"):
     g = torch.Generator().manual_seed(5)
     problems = []

@@ -550,9 +550,15 @@ def tensor_amax(x: torch.Tensor) -> torch.Tensor:
 def calculate_global_scale(input: torch.Tensor, quant_max: float, scale_max: float) -> torch.Tensor:
     """NVFP4's per-tensor scale ``amax / (quant_max * scale_max)`` in the
     input's dtype (reference ``fake_quantize.py:142-160``)."""
-    amax = tensor_amax(input).to(input.dtype).reshape(1)
+    return global_scale_of_amax(tensor_amax(input), input.dtype, quant_max, scale_max)
+
+
+def global_scale_of_amax(amax: torch.Tensor, dtype, quant_max: float, scale_max: float) -> torch.Tensor:
+    """``calculate_global_scale`` from a tensor's ``max |x|`` (a 0-d float32 tensor; a sharded tensor's after an
+    all-reduce), in the tensor's ``dtype``."""
+    amax = amax.to(dtype).reshape(1)
     # A correctly rounded division by the float32 divisor, as the CPU op does.
-    divisor = torch.full((), float(quant_max * scale_max), dtype=torch.float32, device=input.device)
+    divisor = torch.full((), float(quant_max * scale_max), dtype=torch.float32, device=amax.device)
     ratio = _quantize_with(amax, divisor, None, None, R.none_round()).reshape(())
     return ratio.clamp_min(torch.finfo(torch.float32).tiny)
 

@@ -372,3 +372,153 @@ class Fp8DecoderLayerTP:
         return self._finish_row_parallel(partial, self.alpha_down, x1)
 
     __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# NVFP4 decoder layer, tensor-parallel
+# ---------------------------------------------------------------------------
+def _slice_packed_nvfp4(codes, scales, n, k, rows=None, cols=None):
+    """Rows ``[r0, r1)`` (multiples of 128) or contraction columns ``[c0, c1)`` (multiples of 64) of a packed
+    NVFP4 matrix ``[n, k]``: codes ``[n, k / 2]`` and 512-byte scale tiles ``[n / 128, k / 64]``."""
+    tiles = scales.reshape(-1).view(n // 128, k // 64, 512)
+    if rows is not None:
+        r0, r1 = rows
+        if r0 % 128 or r1 % 128:
+            raise ValueError("row shards of a packed NVFP4 matrix are whole 128-row scale tiles")
+        return codes[r0:r1].contiguous(), tiles[r0 // 128:r1 // 128].contiguous().reshape(-1)
+    c0, c1 = cols
+    if c0 % 64 or c1 % 64:
+        raise ValueError("column shards of a packed NVFP4 matrix are whole 64-element scale tiles")
+    return codes[:, c0 // 2:c1 // 2].contiguous(), tiles[:, c0 // 64:c1 // 64].contiguous().reshape(-1)
+
+
+class Nvfp4DecoderLayerTP:
+    """``workloads.Nvfp4DecoderLayer`` over the ranks of a process group (north_star's column / row split).
+
+    Activations between the blocks are sharded by token rows.  q/k/v and gate/up are column-parallel
+    (whole heads / whole 128-row scale tiles per rank), o_proj and down_proj row-parallel:
+
+        RMSNorm on the rank's rows -> amax all-reduce (one scalar: the global scale, hence every code, equals the
+        single-GPU one) -> NVFP4 cast of its rows -> all-gather of packed codes and scale tiles (0.56 byte per
+        element) -> merged QKV GEMM (its heads) -> RoPE -> fused bfloat16 attention over its heads
+        -> amax all-reduce of the K-sharded context -> cast -> o_proj on its input columns, float32 partial
+        products -> reduce-scatter over token rows -> round, add the residual rows; the MLP likewise.
+
+    Weights are quantized unsharded (global scale from the whole weight) and then sliced, so every weight code
+    equals the single-GPU one; the row-parallel sums differ in float32 summation order only.
+    """
+
+    LAUNCHES = 13
+    COLLECTIVES = 10
+
+    def __init__(self, params, shape, group=None):
+        from . import nvfp4 as NV
+
+        self.NV, self.shape, self.group = NV, shape, group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        w, d = self.world, shape.head_dim
+        if shape.kv_heads % w or shape.heads % w or shape.intermediate % (128 * w) or (shape.kv_heads // w * d) % 128:
+            raise ValueError("heads and hidden units must split over the ranks in whole heads and whole 128-row tiles")
+        self.hq, self.hkv = shape.heads // w, shape.kv_heads // w
+        hq, hkv, r = self.hq, self.hkv, self.rank
+        inter = shape.intermediate // w
+        self.ln1, self.ln2 = params["ln1"], params["ln2"]
+        hidden = shape.hidden
+
+        def packed(name):
+            codes, scales, t = NV.quantize_nvfp4(params[name])
+            return codes, scales, t, params[name].shape[0], params[name].shape[1]
+
+        def rows_of(name, r0, r1):
+            codes, scales, t, n, k = packed(name)
+            c, s = _slice_packed_nvfp4(codes, scales, n, k, rows=(r0, r1))
+            return c, s, t
+
+        def cols_of(name, c0, c1):
+            codes, scales, t, n, k = packed(name)
+            c, s = _slice_packed_nvfp4(codes, scales, n, k, cols=(c0, c1))
+            return NV.PackedNVFP4(c, s), t
+
+        def merged(parts):
+            codes = torch.cat([c for c, _, _ in parts], 0)
+            scales = torch.cat([s for _, s, _ in parts])
+            tw = torch.cat([t.reshape(1).expand(c.shape[0]) for c, _, t in parts]).contiguous()
+            return NV.PackedNVFP4(codes, scales), tw
+
+        self.w_qkv, self.tw_qkv = merged([rows_of("q", r * hq * d, (r + 1) * hq * d),
+                                          rows_of("k", r * hkv * d, (r + 1) * hkv * d),
+                                          rows_of("v", r * hkv * d, (r + 1) * hkv * d)])
+        self.w_gu, self.tw_gu = merged([rows_of("gate", r * inter, (r + 1) * inter),
+                                        rows_of("up", r * inter, (r + 1) * inter)])
+        self.w_o, self.t_o = cols_of("o", r * hq * d, (r + 1) * hq * d)
+        self.w_down, self.t_down = cols_of("down", r * inter, (r + 1) * inter)
+        self.hidden, self.inter = hidden, inter
+        self._rope = None
+        self.timed = False
+        self.collective_events = []
+
+    _collective = Fp8DecoderLayerTP._collective
+    collective_seconds = Fp8DecoderLayerTP.collective_seconds
+
+    def _global_scale(self, x):
+        """NVFP4's per-tensor scale of a tensor sharded over the group: the amax is all-reduced first."""
+        from . import ops as O
+        from .nvfp4 import E4M3_MAX, FP4_MAX
+
+        amax = O.tensor_amax(x)
+        if self.world > 1:
+            def reduce_max(t, group):
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+                return t
+            amax = self._collective(reduce_max, amax)
+        return O.global_scale_of_amax(amax, x.dtype, FP4_MAX, E4M3_MAX)
+
+    def _gathered_cast(self, x_rows):
+        """This rank's rows cast to NVFP4 with the whole tensor's global scale, then every rank's rows gathered."""
+        NV = self.NV
+        t = self._global_scale(x_rows)
+        mine = NV.cast_nvfp4(x_rows, t)
+        rows, k = x_rows.shape
+        if rows % 128:
+            raise ValueError("a rank's token rows must be whole 128-row scale tiles")
+        if self.world == 1:
+            return mine, t
+        codes = self._collective(all_gather_rows, mine.codes)
+        tiles = self._collective(all_gather_rows, mine.scales.reshape(-1).view(rows // 128, -1))
+        return NV.PackedNVFP4(codes, tiles.reshape(-1)), t
+
+    def _row_parallel(self, x_cols, weight, t_w, residual_rows):
+        """``x_cols``: all token rows, this rank's slice of the contraction: float32 partial products are
+        reduce-scattered over token rows, rounded once and added to the residual rows."""
+        NV = self.NV
+        t = self._global_scale(x_cols)
+        partial = NV.nvfp4_gemm(NV.cast_nvfp4(x_cols, t), weight, (t * t_w).float(), None, torch.float32)
+        total = partial if self.world == 1 else self._collective(reduce_scatter_rows, partial)
+        return residual_rows + total.to(torch.bfloat16)
+
+    def forward(self, x_rows):
+        """``x_rows``: this rank's ``[T / world, hidden]`` rows.  Returns its rows of the layer output."""
+        import torch.nn.functional as F
+
+        from . import fp8 as F8
+        from .workloads import apply_rope, rope_tables
+
+        NV, sh = self.NV, self.shape
+        T = x_rows.shape[0] * self.world
+        if self._rope is None or self._rope[0].shape[0] != T:
+            self._rope = rope_tables(T, sh, x_rows.device)
+        cos, sin = self._rope
+        d, hq, hkv = sh.head_dim, self.hq, self.hkv
+        act, t = self._gathered_cast(F.rms_norm(x_rows, (sh.hidden,), self.ln1, sh.eps))
+        qkv = NV.nvfp4_gemm(act, self.w_qkv, None, None, torch.bfloat16, alpha_cols=(t * self.tw_qkv).float())
+        q = apply_rope(qkv[:, :hq * d].reshape(T, hq, d), cos, sin)
+        k = apply_rope(qkv[:, hq * d:(hq + hkv) * d].reshape(T, hkv, d), cos, sin)
+        v = qkv[:, (hq + hkv) * d:].reshape(T, hkv, d)
+        ctx = F8.attention_bf16(q, k, v)
+        x1 = self._row_parallel(ctx, self.w_o, self.t_o, x_rows)
+        act, t = self._gathered_cast(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps))
+        gu = NV.nvfp4_gemm(act, self.w_gu, None, None, torch.bfloat16, alpha_cols=(t * self.tw_gu).float())
+        return self._row_parallel(F.silu(gu[:, :self.inter]) * gu[:, self.inter:], self.w_down, self.t_down, x1)
+
+    __call__ = forward
