@@ -1520,14 +1520,7 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # The communicator's ranks show in NCCL's log.  NCCL writes it to the C stdout: point that at stderr and
-        # keep the real stdout for the one JSON line.
-        os.environ.setdefault("NCCL_DEBUG", "INFO")
-        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
-        sys.stdout.flush()
-        real_stdout = os.dup(1)
-        os.dup2(2, 1)
-        sys.stdout = os.fdopen(real_stdout, "w")
+        # NCCL's own log settings (NCCL_DEBUG and friends) are left as the caller's environment has them
         dist.init_process_group("nccl", device_id=dev)
 
     def barrier():
