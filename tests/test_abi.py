@@ -169,3 +169,24 @@ def test_voyager_gpu_operator_schemas_are_the_references():
     assert y.shape == (128, 128) and y.dtype == torch.bfloat16
     c, ct, amax = G.cast_transpose_fp8(x, t, torch.float8_e4m3fn)
     assert c.shape == (192, 128) and ct.shape == (128, 192) and c.dtype == torch.float8_e4m3fn
+
+
+def test_convolution_operator_schemas_are_the_references():
+    """``conv2d_mx`` (reference ``ops/quantized.py:596-604``) and the layout twin ``conv2d`` (``ops/layout.py:175-181``)
+    as the dispatcher normalises them, and their shape functions."""
+    Q = torch.ops.quantized_ops
+    assert str(Q.conv2d_mx.default._schema) == (
+        "quantized_ops::conv2d_mx(Tensor input, Tensor weight, Tensor? bias=None, SymInt[2] stride=[1, 1], "
+        "SymInt[2] padding=[0, 0], SymInt[2] dilation=[1, 1], SymInt groups=1, *, Tensor? input_scale=None, "
+        "Tensor? weight_scale=None, int? block_size=None, Tensor? input_code=None, Tensor? weight_code=None, "
+        'str layout="nchw", ScalarType? out_dtype=None) -> Tensor')
+    assert str(Q.conv2d.default._schema) == (
+        "quantized_ops::conv2d(Tensor input, Tensor weight, Tensor? bias=None, SymInt[2] stride=[1, 1], "
+        'SymInt[2] padding=[0, 0], SymInt[2] dilation=[1, 1], SymInt groups=1, *, str layout="nchw", '
+        "ScalarType? out_dtype=None) -> Tensor")
+    x = torch.empty(2, 16, 10, 10, dtype=torch.bfloat16, device="meta")
+    w = torch.empty(8, 16, 3, 3, dtype=torch.bfloat16, device="meta")
+    assert Q.conv2d_mx(x, w, None, [1, 1], [1, 1]).shape == (2, 8, 10, 10)
+    y = Q.conv2d(x.permute(0, 2, 3, 1), w.permute(2, 3, 1, 0), None, [2, 2], [1, 1], [1, 1], 1, layout="nhwc",
+                 out_dtype=torch.float32)
+    assert y.shape == (2, 5, 5, 8) and y.dtype == torch.float32

@@ -56,3 +56,32 @@ def test_sdpa_mx():
     g, w = got[0].float(), expected[0].float()
     assert g.shape == w.shape
     assert float((g - w).abs().max() / w.abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("layout", ["nchw", "nhwc"])
+def test_conv2d_mx_reads_its_operands_back_and_convolves(layout):
+    """``conv2d_mx`` = ``dequantize_mx`` of both operands (bit-exact kernels) + the convolution, in either layout."""
+    import torch.nn.functional as F
+
+    import voyager_b200 as vb
+
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(2, 32, 9, 9, generator=g).bfloat16().cuda()
+    w = (torch.randn(16, 32, 3, 3, generator=g) * 0.1).bfloat16().cuda()
+    bias = torch.randn(16, generator=g).bfloat16().cuda()
+    table = vb.get_quantization_map("int8").cuda()
+    Q = torch.ops.quantized_ops
+    xs, ws = (x.permute(0, 2, 3, 1).contiguous(), w.permute(2, 3, 1, 0).contiguous()) if layout == "nhwc" else (x, w)
+    axis_x, axis_w = (-1, -2) if layout == "nhwc" else (1, 1)            # blocks along the input channels
+    sx, cx = Q.quantize_mx(xs, table, [axis_x], 16, 127.0, True)
+    sw, cw = Q.quantize_mx(ws, table, [axis_w], 16, 127.0, True)
+    got = Q.conv2d_mx(cx, cw, bias, [1, 1], [1, 1], [1, 1], 1, input_scale=sx, weight_scale=sw, block_size=16,
+                      layout=layout, out_dtype=torch.float32)
+    dx, dw = Q.dequantize_mx(cx, sx, 16), Q.dequantize_mx(cw, sw, 16)
+    if layout == "nhwc":
+        dx, dw = dx.permute(0, 3, 1, 2), dw.permute(3, 2, 0, 1)
+    want = F.conv2d(dx.float(), dw.float(), bias.float(), 1, 1)
+    if layout == "nhwc":
+        want = want.permute(0, 2, 3, 1)
+    assert got.shape == want.shape and got.dtype == torch.float32
+    assert float((got - want).abs().max()) <= 1e-3 * float(want.abs().max())

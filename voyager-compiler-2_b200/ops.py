@@ -869,6 +869,89 @@ def _mx_gemm(native, a, b, bias, input_scale, weight_scale, block_size, input_co
     return y.mT.contiguous() if out_l != n_out else y
 
 
+# ---------------------------------------------------------------------------
+# convolutions (a converted CNN graph's call targets; not a tuned path)
+# ---------------------------------------------------------------------------
+TENSOR_LAYOUT = "nchw"
+quantized_ops_lib.define(
+    "conv2d(Tensor input, Tensor weight, Tensor? bias=None, SymInt[2] stride=[1, 1], SymInt[2] padding=[0, 0], "
+    f'SymInt[2] dilation=[1, 1], SymInt groups=1, *, str layout="{TENSOR_LAYOUT}", ScalarType? out_dtype=None) '
+    "-> Tensor"
+)
+quantized_ops_lib.define(
+    "conv2d_mx(Tensor input, Tensor weight, Tensor? bias=None, SymInt[2] stride=1, SymInt[2] padding=0, "
+    "SymInt[2] dilation=1, SymInt groups=1, *, Tensor? input_scale=None, Tensor? weight_scale=None, "
+    f'int? block_size=None, Tensor? input_code=None, Tensor? weight_code=None, str layout="{TENSOR_LAYOUT}", '
+    "ScalarType? out_dtype=None) -> Tensor"
+)
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+def conv2d(input, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, *,
+           layout=TENSOR_LAYOUT, out_dtype=None):
+    """``aten.conv2d`` on feature maps stored as ``layout`` says (reference ``ops/layout.py:170-218``): under
+    ``"nhwc"`` input and result are channels-last and a dense convolution's weight is ``[H, W, in, out]``;
+    ``out_dtype`` sums in float32 and returns that dtype.  The convolution itself is the library's (cuDNN)."""
+    if layout not in ("nchw", "nhwc"):
+        raise ValueError(f"unknown tensor layout {layout!r}")
+    nhwc = layout == "nhwc"
+    if nhwc:
+        input = input.permute(0, 3, 1, 2)
+        if groups == 1:
+            weight = weight.permute(3, 2, 0, 1)
+    if out_dtype is not None:
+        input, weight = input.float(), weight.float()
+        bias = None if bias is None else bias.float()
+    out = torch.nn.functional.conv2d(input, weight, bias, _pair(stride), _pair(padding), _pair(dilation), groups)
+    if out_dtype is not None:
+        out = out.to(out_dtype)
+    return out.permute(0, 2, 3, 1) if nhwc else out
+
+
+def conv2d_mx(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, *, input_scale=None,
+              weight_scale=None, block_size=None, input_code=None, weight_code=None, layout=TENSOR_LAYOUT,
+              out_dtype=None):
+    """The convolution of block-scaled operands (reference ``ops/quantized.py:596-645``): both are read back
+    (``code[x] * scale``, this package's kernel) and handed to ``conv2d``."""
+    input = _read_operand(input, input_scale, input_code, block_size)
+    weight = _read_operand(weight, weight_scale, weight_code, block_size)
+    return conv2d(input, weight, bias, stride, padding, dilation, groups, layout=layout, out_dtype=out_dtype)
+
+
+quantized_ops_lib.impl("conv2d", N.device_guarded(conv2d), "CUDA")
+quantized_ops_lib.impl("conv2d_mx", N.device_guarded(conv2d_mx), "CUDA")
+
+
+def _conv_out_shape(input, weight, stride, padding, dilation, groups, layout):
+    nhwc = layout == "nhwc"
+    n, h, w = (input.shape[0], input.shape[1], input.shape[2]) if nhwc else (input.shape[0], input.shape[2], input.shape[3])
+    if nhwc and groups == 1:
+        kh, kw, out_c = weight.shape[0], weight.shape[1], weight.shape[3]
+    else:
+        out_c, kh, kw = weight.shape[0], weight.shape[2], weight.shape[3]
+    (sh, sw), (ph, pw), (dh, dw) = _pair(stride), _pair(padding), _pair(dilation)
+    oh = (h + 2 * ph - dh * (kh - 1) - 1) // sh + 1
+    ow = (w + 2 * pw - dw * (kw - 1) - 1) // sw + 1
+    return (n, oh, ow, out_c) if nhwc else (n, out_c, oh, ow)
+
+
+@torch.library.register_fake("quantized_ops::conv2d")
+def _(input, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, *, layout=TENSOR_LAYOUT,
+      out_dtype=None):
+    return input.new_empty(_conv_out_shape(input, weight, stride, padding, dilation, groups, layout),
+                           dtype=out_dtype or input.dtype)
+
+
+@torch.library.register_fake("quantized_ops::conv2d_mx")
+def _(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, *, input_scale=None, weight_scale=None,
+      block_size=None, input_code=None, weight_code=None, layout=TENSOR_LAYOUT, out_dtype=None):
+    return input.new_empty(_conv_out_shape(input, weight, stride, padding, dilation, groups, layout),
+                           dtype=out_dtype or input.dtype)
+
+
 def linear_mx(input, weight, bias=None, *, input_scale=None, weight_scale=None, block_size=None, input_code=None,
               weight_code=None, alpha=None, A_data=None, A_indices=None, A_indptr=None, layout=LINEAR_LAYOUT,
               out_dtype=None):
