@@ -1574,6 +1574,260 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 }
 
 // ---------------------------------------------------------------------------
+// NVFP4 GEMM on CTA pairs, scale factors written into tensor memory by warps.
+// The kernel above moves a stage's twelve scale tiles with tcgen05.cp from the MMA thread; those
+// copies execute in the tensor pipe in order with the MMAs and cost as much time as the MMAs do.
+// Here four "scale" warps per CTA read the tiles from shared memory (one 16-byte row per lane)
+// and store them into tensor memory with tcgen05.st -- the same lane / column placement as the
+// 32x128b.warpx4 copy, each warp writing its own lane quadrant -- into one of two 64-column
+// buffers, ahead of the MMAs that read them; the MMA thread only issues MMAs.
+//   Tensor memory: accumulator 0 at [0,256), accumulator 1 at [128,384) (they share 128 columns:
+//   the half the first four epilogue warps drain first), scale buffers at [384,448) and [448,512),
+//   each four 16-column groups [B scales 8 | A scales 4 | unused 4], one per K64 step.
+//   sf_full[s]   : per CTA, its own scale tiles of stage s have landed
+//   sf_ready[b]  : even CTA; 8 arrivals (4 scale warps x 2 CTAs): buffer b holds the next stage's scales
+//   sf_free[b]   : per CTA; the MMAs that read buffer b have completed (tcgen05.commit)
+//   the other barriers as in the kernel above
+// Four warpgroups as in gemm_mx_pair_kernel: registers 40 / 184 / 184 / 104.
+// ---------------------------------------------------------------------------
+constexpr int QS_THREADS = 512;
+constexpr int QS_EPI_WARP0 = 4, QS_SF_WARP0 = 12;
+constexpr uint32_t QS_ACC1_COL = 128, QS_SF_COL = 384, QS_SF_BUF_COLS = 64;
+constexpr int QS_OVERLAP = 128;
+
+__device__ __forceinline__ void tmem_st_32x32_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int OUT_DT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(QS_THREADS, 1)
+gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                      const __grid_constant__ CUtensorMap map_c, const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem_a + QP_STAGES * QP_A_BYTES;
+  uint8_t* smem_sfa = smem_b + QP_STAGES * QP_B_BYTES;
+  uint8_t* smem_sfb = smem_sfa + QP_STAGES * QP_SFA_BYTES;
+  uint8_t* epi_stage = smem + QP_STAGES * QP_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + EPI_STAGE_BYTES);
+  uint64_t* full_bar = bars;                          // [QP_STAGES] (used in the even CTA)
+  uint64_t* empty_bar = bars + QP_STAGES;             // [QP_STAGES]
+  uint64_t* sf_full = bars + 2 * QP_STAGES;           // [QP_STAGES] per CTA
+  uint64_t* acc_full = bars + 3 * QP_STAGES;          // [2]
+  uint64_t* acc_empty = bars + 3 * QP_STAGES + 2;     // [2] (used in the even CTA)
+  uint64_t* ovl_free = bars + 3 * QP_STAGES + 4;      // [2] (used in the even CTA)
+  uint64_t* sf_ready = bars + 3 * QP_STAGES + 6;      // [2] (used in the even CTA)
+  uint64_t* sf_free = bars + 3 * QP_STAGES + 8;       // [2] per CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * QP_STAGES + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  const int tiles_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n * p.batch;
+  const int k64_total = p.K / 64;
+  const int k_blocks = (k64_total + 3) / 4;
+  const int m_blocks128 = (p.M + 127) / 128;
+  const int n_blocks128 = (p.N + 127) / 128;
+  const uint32_t operand_tx_bytes = 2u * (uint32_t)(QP_A_BYTES + QP_B_BYTES);
+  const uint32_t scale_tx_bytes = (uint32_t)(QP_SFA_BYTES + QP_SFB_BYTES);   // this CTA's own tiles
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < QP_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&sf_full[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 2 * EPI_WARPS);
+      mbar_init(&ovl_free[a], EPI_WARPS);     // the four warps of column half 0, both CTAs
+      mbar_init(&sf_ready[a], 8);
+      mbar_init(&sf_free[a], 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < QS_EPI_WARP0) {
+    reg_dealloc<40>();
+    if (warp == 0) {
+      // ------------------------------ TMA producer (both CTAs) ------------------
+      if (lane == 0) {
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        prefetch_tensormap(&map_sfa);
+        prefetch_tensormap(&map_sfb);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+          const int m_blk = (int)(tile % tiles_m);
+          const int n_blk = (int)((tile / tiles_m) % tiles_n);
+          const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+          const int m0 = m_blk * 2 * BM + (int)rank * BM;
+          const int n0 = n_blk * BN + (int)rank * (BN / 2);
+          const int sfa_blk = b * m_blocks128 + m_blk * 2 + (int)rank;
+          const int sfb_blk = b * n_blocks128 + n_blk * 2;
+          const bool sfa_in = m_blk * 2 + (int)rank < m_blocks128;
+          const bool sfb1_in = n_blk * 2 + 1 < n_blocks128;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+            mbar_arrive_expect_tx(&sf_full[stage], scale_tx_bytes);
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], operand_tx_bytes);
+            const uint32_t leader_full = map_to_cta(&full_bar[stage], 0);
+            tma_load_3d(smem_sfa + stage * QP_SFA_BYTES, &map_sfa, &sf_full[stage], 0, kb * 4,
+                        sfa_in ? sfa_blk : 0x7FFFFFF0);
+            tma_load_3d(smem_sfb + stage * QP_SFB_BYTES, &map_sfb, &sf_full[stage], 0, kb * 4, sfb_blk);
+            tma_load_3d(smem_sfb + stage * QP_SFB_BYTES + QP_SFA_BYTES, &map_sfb, &sf_full[stage], 0, kb * 4,
+                        sfb1_in ? sfb_blk + 1 : 0x7FFFFFF0);
+            tma_load_3d_pair(smem_a + stage * QP_A_BYTES, &map_a, leader_full, kb * BK_BYTES, m0, b);
+            tma_load_3d_pair(smem_b + stage * QP_B_BYTES, &map_b, leader_full, kb * BK_BYTES, n0, b);
+            if (++stage == QP_STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------ MMA issuer (even CTA only) ----------------
+      if (lane == 0 && rank == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        int64_t done = 0;   // tiles issued so far
+        uint32_t it = 0;    // stages issued so far: scale buffer it & 1, its use number it >> 1
+        for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++done) {
+          if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+          if (done > 0 && !mbar_wait(&ovl_free[acc ^ 1], (uint32_t)(((done - 1) >> 1) & 1), abort_flag)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t tmem_acc = tmem_base + (acc ? QS_ACC1_COL : 0u);
+          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int steps = min(4, k64_total - kb * 4);
+            const uint32_t buf = it & 1u;
+            const uint32_t a_addr = smem_u32(smem_a + stage * QP_A_BYTES);
+            const uint32_t b_addr = smem_u32(smem_b + stage * QP_B_BYTES);
+            if (!mbar_wait(&sf_ready[buf], (it >> 1) & 1u, abort_flag) ||
+                !mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            for (int k = 0; k < steps; ++k) {
+              const uint32_t grp = tmem_base + QS_SF_COL + buf * QS_SF_BUF_COLS + 16 * k;
+              const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
+              const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
+              mma_nvfp4_ss_pair(tmem_acc, da, db, p.idesc, grp + 8, grp, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            mma_commit_pair(&empty_bar[stage], 0x3);
+            mma_commit_pair(&sf_free[buf], 0x3);
+            if (++stage == QP_STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          mma_commit_pair(&acc_full[acc], 0x3);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp < QS_SF_WARP0) {
+    reg_alloc<184>();
+    // ------------------------------ epilogue (both CTAs) ----------------------
+    const int quarter = warp & 3;
+    const int chalf = (warp - QS_EPI_WARP0) >> 2;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    uint32_t epi_buf = 0;
+    const bool has_alpha = p.alpha != nullptr;
+    const float alpha = has_alpha ? load_param(p.alpha, 0, p.alpha_dt) : 1.0f;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int m_blk = (int)(tile % tiles_m);
+      const int n_blk = (int)((tile / tiles_m) % tiles_n);
+      const int b = (int)(tile / ((int64_t)tiles_m * tiles_n));
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (acc ? QS_ACC1_COL : 0u) + ((uint32_t)(quarter * 32) << 16);
+      const int row0 = m_blk * 2 * BM + (int)rank * BM + quarter * 32;
+      uint8_t* stage = epi_stage + (warp - QS_EPI_WARP0) * (32 * 128);
+      // The tile's columns shared with the other accumulator (the last 128 of accumulator 0, the first 128 of
+      // accumulator 1) go to the warps of column half 0, which announce when they have read them.
+      const int shared0 = acc ? 0 : BN - QS_OVERLAP;
+      const int begin = chalf == 0 ? shared0 : (BN - QS_OVERLAP) - shared0;
+      epilogue_warp_tile<OUT_DT, 1>(p, &map_c, taddr, stage, epi_buf, row0, lane, n_blk * BN, b, has_alpha, alpha, begin,
+                                    begin + QS_OVERLAP);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (chalf == 0) mbar_arrive_cluster(map_to_cta(&ovl_free[acc], 0));
+        mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  } else {
+    reg_dealloc<104>();
+    // ------------------------------ scale warps (both CTAs) -------------------
+    const int quadrant = warp & 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const uint32_t buf = it & 1u, use = it >> 1;
+        // the tiles have landed, and the MMAs that read this buffer two stages ago have completed
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sf_full[stage], phase, abort_flag) &&
+                                         (use == 0 || mbar_wait(&sf_free[buf], (use - 1) & 1u, abort_flag)))) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint8_t* sfa = smem_sfa + stage * QP_SFA_BYTES + lane * 16;
+        const uint8_t* sfb = smem_sfb + stage * QP_SFB_BYTES + lane * 16;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quadrant * 32) << 16) + QS_SF_COL + buf * QS_SF_BUF_COLS;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint4 b0 = *reinterpret_cast<const uint4*>(sfb + k * 512);
+          const uint4 b1 = *reinterpret_cast<const uint4*>(sfb + QP_SFA_BYTES + k * 512);
+          const uint4 a0 = *reinterpret_cast<const uint4*>(sfa + k * 512);
+          const uint32_t r[16] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w, a0.x, a0.y, a0.z, a0.w, 0u, 0u, 0u, 0u};
+          tmem_st_32x32_x16(taddr + 16 * k, r);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(&sf_ready[buf], 0));
+        if (++stage == QP_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
+  if (warp >= QS_EPI_WARP0 && warp < QS_SF_WARP0 && lane == 0) tma_store_wait_read();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1911,13 +2165,14 @@ int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* 
   const int64_t row_bytes = K / 2;
   CUtensorMap map_a, map_b;
   if (int e = make_operand_map(&map_a, A, VQ_BF16, 1, M, row_bytes, row_bytes, batch, M * row_bytes, BM)) return e;
-  // More than one 128-row block of output: CTA pairs on 256x256 tiles (VQ_NVFP4_PAIR=0 keeps the single-CTA kernel).
+  // More than one 128-row block of output: CTA pairs on 256x256 tiles, scale factors stored into tensor
+  // memory by warps (VQ_NVFP4_PAIR=1: the tcgen05.cp form of the pair kernel; 0: the single-CTA kernel).
   static int pair_mode = -1;
   if (pair_mode < 0) {
     const char* env = getenv("VQ_NVFP4_PAIR");
-    pair_mode = (env && env[0] == '0') ? 0 : 1;
+    pair_mode = (env && env[0] == '0') ? 0 : (env && env[0] == '1') ? 1 : 2;
   }
-  const bool pair = pair_mode == 1 && M > BM;
+  const bool pair = pair_mode >= 1 && M > BM;
   if (int e = make_operand_map(&map_b, B, VQ_BF16, 1, N, row_bytes, row_bytes, batch, N * row_bytes, pair ? BN / 2 : Q_BN))
     return e;
   GemmParams p{};
@@ -1954,6 +2209,17 @@ int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* 
     }
     const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * batch;
     const int clusters = (int)(tiles < kSmCount / 2 ? tiles : kSmCount / 2);
+    if (pair_mode == 2) {
+      static unsigned long long sfw_configured = 0;
+      if (first_call_on_device(&sfw_configured)) {
+        if (int rc = allow_big_smem(gemm_nvfp4_sfw_kernel<VQ_BF16>, gemm_nvfp4_sfw_kernel<VQ_F16>,
+                                    gemm_nvfp4_sfw_kernel<VQ_F32>, QP_SMEM_BYTES))
+          return rc;
+      }
+      VQ_FOR_OUT_DTYPE(out_dtype, gemm_nvfp4_sfw_kernel)<<<2 * clusters, QS_THREADS, QP_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+          map_a, map_b, map_sfa, map_sfb, map_c, p);
+      return check_launch("gemm_nvfp4_sfw_kernel");
+    }
     VQ_FOR_OUT_DTYPE(out_dtype, gemm_nvfp4_pair_kernel)<<<2 * clusters, NUM_THREADS, QP_SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
         map_a, map_b, map_sfa, map_sfb, map_c, p);
     return check_launch("gemm_nvfp4_pair_kernel");
