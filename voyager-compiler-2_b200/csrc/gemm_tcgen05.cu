@@ -1582,7 +1582,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 // 32x128b.warpx4 copy, each warp writing its own lane quadrant -- into one of two 64-column
 // buffers, ahead of the MMAs that read them; the MMA thread only issues MMAs.
 //   Tensor memory: accumulator 0 at [0,256), accumulator 1 at [128,384) (they share 128 columns:
-//   the half the first four epilogue warps drain first), scale buffers at [384,448) and [448,512),
+//   the half the epilogue warps drain first), scale buffers at [384,448) and [448,512),
 //   each four 16-column groups [B scales 8 | A scales 4 | unused 4], one per K64 step.
 //   sf_full[s]   : per CTA, its own scale tiles of stage s have landed
 //   sf_ready[b]  : even CTA; 8 arrivals (4 scale warps x 2 CTAs): buffer b holds the next stage's scales
@@ -1655,7 +1655,7 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 2 * EPI_WARPS);
-      mbar_init(&ovl_free[a], EPI_WARPS);     // the four warps of column half 0, both CTAs
+      mbar_init(&ovl_free[a], 2 * EPI_WARPS);  // every epilogue warp of both CTAs
       mbar_init(&sf_ready[a], 8);
       mbar_init(&sf_free[a], 1);
     }
@@ -1769,17 +1769,24 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int row0 = m_blk * 2 * BM + (int)rank * BM + quarter * 32;
       uint8_t* stage = epi_stage + (warp - QS_EPI_WARP0) * (32 * 128);
       // The tile's columns shared with the other accumulator (the last 128 of accumulator 0, the first 128 of
-      // accumulator 1) go to the warps of column half 0, which announce when they have read them.
+      // accumulator 1) are drained first, 64 by each column half, and announced; the next tile's MMAs may
+      // then start while the warps take the other 128 columns.
       const int shared0 = acc ? 0 : BN - QS_OVERLAP;
-      const int begin = chalf == 0 ? shared0 : (BN - QS_OVERLAP) - shared0;
-      epilogue_warp_tile<OUT_DT, 1>(p, &map_c, taddr, stage, epi_buf, row0, lane, n_blk * BN, b, has_alpha, alpha, begin,
-                                    begin + QS_OVERLAP);
+      const int other0 = (BN - QS_OVERLAP) - shared0;
+#pragma unroll 1
+      for (int seg = 0; seg < 2; ++seg) {
+        const int begin = (seg == 0 ? shared0 : other0) + chalf * (QS_OVERLAP / 2);
+        epilogue_warp_tile<OUT_DT, 1>(p, &map_c, taddr, stage, epi_buf, row0, lane, n_blk * BN, b, has_alpha, alpha,
+                                      begin, begin + QS_OVERLAP / 2);
+        if (seg == 0) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(&ovl_free[acc], 0));
+        }
+      }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) {
-        if (chalf == 0) mbar_arrive_cluster(map_to_cta(&ovl_free[acc], 0));
-        mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
-      }
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
   } else {
