@@ -122,7 +122,9 @@ __device__ __noinline__ uint4 slow_vector(uint4 raw, uint32_t amax_bits, const S
 // Blocks along the contiguous axis, K a whole number of blocks: the tensor is a
 // flat run of blocks; vector v belongs to block v >> gshift (G = 1 << gshift
 // lanes per block).
-template <int FM, bool POT, bool WRITE_CODES>
+// U vectors per thread and step: kU for streaming tensors; 1 for small ones (a decode step's few rows), which
+// then spread over four times as many CTAs and have a quarter of the dependent latency per thread.
+template <int FM, bool POT, bool WRITE_CODES, int U = kU>
 __global__ void __launch_bounds__(kT, kCtasPerSm)
 mx_flat_bf16_kernel(const uint4* __restrict__ in, __nv_bfloat16* __restrict__ scale_out, uint4* __restrict__ codes_out,
                     int64_t nvec, int G, int gshift, ScaleRule rule, Round r) {
@@ -132,17 +134,17 @@ mx_flat_bf16_kernel(const uint4* __restrict__ in, __nv_bfloat16* __restrict__ sc
   float gs = 0.0f;
   const bool has_gs = rule.global_scale != nullptr;
   if (has_gs) gs = loadp(rule.global_scale, 0, rule.global_scale_dtype);
-  const int64_t chunk = (int64_t)kT * kU;
+  const int64_t chunk = (int64_t)kT * U;
   for (int64_t base = (int64_t)blockIdx.x * chunk; base < nvec; base += (int64_t)gridDim.x * chunk) {
-    uint4 x[kU];
+    uint4 x[U];
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
+    for (int u = 0; u < U; ++u) {
       int64_t v = base + u * kT + threadIdx.x;
       x[u] = make_uint4(0, 0, 0, 0);
       if (v < nvec) x[u] = __ldg(in + v);
     }
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int64_t v = base + u * kT + threadIdx.x;
       const bool active = v < nvec;
       // block amax of the bf16 magnitudes, two lanes at a time
@@ -376,6 +378,13 @@ void launch_mx_fm(bool pot, bool write, const void* in, void* scale_out, void* c
   const uint4* i = static_cast<const uint4*>(in);
   __nv_bfloat16* s = static_cast<__nv_bfloat16*>(scale_out);
   uint4* c = static_cast<uint4*>(codes_out);
+  if (FM == FAST_GENERIC && write && nvec <= (int64_t)kSmCount * kT) {
+    // a small tensor through a gathered table: latency, not bandwidth
+    const int small_grid = (int)((nvec + kT - 1) / kT);
+    if (pot) mx_flat_bf16_kernel<FM, true, true, 1><<<small_grid, kT, 0, st>>>(i, s, c, nvec, G, gshift, rule, r);
+    else mx_flat_bf16_kernel<FM, false, true, 1><<<small_grid, kT, 0, st>>>(i, s, c, nvec, G, gshift, rule, r);
+    return;
+  }
   const int grid = grid_of(nvec);
   if (pot) {
     if (write) mx_flat_bf16_kernel<FM, true, true><<<grid, kT, 0, st>>>(i, s, c, nvec, G, gshift, rule, r);
