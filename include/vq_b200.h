@@ -414,6 +414,14 @@ int vq_rmsnorm_backward(const void* dy0, const void* dy1, const void* dy2, int g
                         const float* rsqrt_rows, const void* weight, const void* residual, void* dx,
                         float* partial_dw, void* dw, int64_t rows, int64_t cols, void* stream);
 
+/* Rotate-half RoPE of x [T, heads, d] (bfloat16; element (t, h, j) at x + t * in_stride_t + h * in_stride_h + j,
+ * so a slice of a merged projection's output needs no copy) written to out + h * out_stride_h + t * out_stride_t
+ * + j: head-major for the attention kernel.  cos / sin: bfloat16 [T, d].  y = bf16(bf16(x * cos) + bf16(rot(x) *
+ * sin)), rot(x) = (-x[d/2:], x[:d/2]): the graph's mul / cat / neg / add nodes with their roundings. */
+int vq_rope_heads_bf16(const void* x, const void* cosv, const void* sinv, void* out, int64_t T, int64_t heads, int64_t d,
+                       int64_t in_stride_t, int64_t in_stride_h, int64_t out_stride_t, int64_t out_stride_h,
+                       void* stream);
+
 /* One decode step's RoPE and cache append on the merged q/k/v projection qkv [B, (q_heads + 2 kv_heads) * d]
  * (bfloat16): query head h, rotated, to q_out [B, q_heads, d]; key head h, rotated, to
  * k_dst + (b * kv_heads + h) * kv_stride; value head h, unchanged, to v_dst + (b * kv_heads + h) * kv_stride

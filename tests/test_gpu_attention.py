@@ -163,3 +163,36 @@ def test_attention_bf16_rejects_other_shapes():
     q = torch.zeros(128, 2, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError):
         F8.attention_bf16(q, q, q)
+
+
+def test_rope_heads_bf16_equals_the_elementwise_graph():
+    """One kernel against x * cos + rotate_half(x) * sin on bfloat16 tensors, bit for bit, from a strided slice of a
+    merged projection, written head-major."""
+    from voyager_b200 import fp8 as F8
+    from voyager_b200.workloads import apply_rope
+
+    g = torch.Generator().manual_seed(6)
+    T, heads, kv, d = 256, 8, 2, 128
+    qkv = torch.randn(T, (heads + 2 * kv) * d, generator=g).bfloat16().cuda()
+    cos = torch.randn(T, d, generator=g).bfloat16().cuda()
+    sin = torch.randn(T, d, generator=g).bfloat16().cuda()
+    for lo, n in ((0, heads), (heads * d, kv)):
+        x = qkv[:, lo:lo + n * d].unflatten(1, (n, d))
+        got = F8.rope_heads_bf16(x, cos, sin)
+        want = apply_rope(x, cos, sin).permute(1, 0, 2)
+        assert got.shape == (n, T, d) and torch.equal(got, want)
+
+
+def test_attention_bf16_heads_is_attention_bf16_on_prepared_operands():
+    from voyager_b200 import fp8 as F8
+
+    g = torch.Generator().manual_seed(8)
+    T = 384
+    q = torch.randn(T, 8, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(T, 2, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(T, 2, 128, generator=g).bfloat16().cuda()
+    a = F8.attention_bf16(q, k, v)
+    b = F8.attention_bf16_heads(q.permute(1, 0, 2).contiguous(), k.permute(1, 0, 2).contiguous(),
+                                v.permute(1, 2, 0).contiguous())
+    assert F8.attention_status() == 0
+    assert torch.equal(a, b)

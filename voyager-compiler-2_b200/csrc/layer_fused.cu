@@ -239,6 +239,39 @@ transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
   }
 }
 
+// Rotary embedding of x [T, heads, d] (strided: a slice of a merged projection's output) written head-major,
+// out[h * out_h + t * out_t + j], in bfloat16: y = bf16(bf16(x * cos) + bf16(rot(x) * sin)), the graph's
+// elementwise nodes with their roundings, and the layout the attention kernel reads.  Strides in 8-element vectors.
+__global__ void __launch_bounds__(256)
+rope_heads_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv, const uint4* __restrict__ sinv,
+                  uint4* __restrict__ out, int T, int heads, int d, int64_t in_t, int64_t in_h, int64_t out_t,
+                  int64_t out_h) {
+  const int vpd = d >> 3, half = vpd >> 1;
+  const int64_t total = (int64_t)T * heads * vpd;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int v = (int)(idx % vpd);
+    const int h = (int)((idx / vpd) % heads);
+    const int t = (int)(idx / ((int64_t)vpd * heads));
+    const uint4* row = x + t * in_t + h * in_h;
+    const uint4 xv = __ldg(row + v);
+    const uint4 pvv = __ldg(row + (v < half ? v + half : v - half));
+    const uint4 cv = __ldg(cosv + (int64_t)t * vpd + v), sv = __ldg(sinv + (int64_t)t * vpd + v);
+    const uint32_t a[4] = {xv.x, xv.y, xv.z, xv.w}, p[4] = {pvv.x, pvv.y, pvv.z, pvv.w};
+    const uint32_t c[4] = {cv.x, cv.y, cv.z, cv.w}, s[4] = {sv.x, sv.y, sv.z, sv.w};
+    const float sign = v < half ? -1.0f : 1.0f;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float y0 = __fadd_rn(bf16r(__fmul_rn(lo_of(a[j]), lo_of(c[j]))), bf16r(__fmul_rn(sign * lo_of(p[j]), lo_of(s[j]))));
+      const float y1 = __fadd_rn(bf16r(__fmul_rn(hi_of(a[j]), hi_of(c[j]))), bf16r(__fmul_rn(sign * hi_of(p[j]), hi_of(s[j]))));
+      const __nv_bfloat162 hh = __floats2bfloat162_rn(y0, y1);
+      o[j] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+    out[h * out_h + t * out_t + v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 // One decode step's RoPE and cache append.  qkv: [B, (hq + 2 hkv) * d] bfloat16, the merged projection's
 // output.  Query head h goes, rotated, to q_out[b, h, :]; key head h, rotated, to k_dst + (b * hkv + h) *
 // kv_stride; value head h, as it is, to v_dst + (b * hkv + h) * kv_stride (the slot of this step's
@@ -370,6 +403,26 @@ extern "C" int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* 
       static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint2*>(out), nvec, (int)(cols / 8),
       ld_gate / 8, ld_up / 8, scale, scale_dtype);
   return check_launch("silu_mul_quantize_kernel");
+}
+
+extern "C" int vq_rope_heads_bf16(const void* x, const void* cosv, const void* sinv, void* out, int64_t T, int64_t heads,
+                                  int64_t d, int64_t in_stride_t, int64_t in_stride_h, int64_t out_stride_t,
+                                  int64_t out_stride_h, void* stream) {
+  VQ_REQUIRE(T >= 0 && heads >= 0 && d > 0, "vq_rope_heads_bf16: bad extent");
+  if (T == 0 || heads == 0) return VQ_OK;
+  VQ_REQUIRE(x && cosv && sinv && out, "vq_rope_heads_bf16: null argument");
+  VQ_REQUIRE(d % 16 == 0, "vq_rope_heads_bf16: head_dim must be a multiple of 16");
+  VQ_REQUIRE(((in_stride_t | in_stride_h | out_stride_t | out_stride_h) & 7) == 0 && in_stride_t >= 0 &&
+             in_stride_h >= 0 && out_stride_t >= 0 && out_stride_h >= 0,
+             "vq_rope_heads_bf16: strides must be non-negative multiples of 8 elements");
+  VQ_REQUIRE(T < (1ll << 31) && heads < (1 << 20) && d < (1 << 20), "vq_rope_heads_bf16: extent too large");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(cosv) |
+               reinterpret_cast<uintptr_t>(sinv)) & 15) == 0, "vq_rope_heads_bf16: misaligned buffers");
+  rope_heads_kernel<<<stream_grid(T * heads * (d / 8), 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(cosv), static_cast<const uint4*>(sinv),
+      static_cast<uint4*>(out), (int)T, (int)heads, (int)d, in_stride_t / 8, in_stride_h / 8, out_stride_t / 8,
+      out_stride_h / 8);
+  return check_launch("rope_heads_kernel");
 }
 
 extern "C" int vq_rope_decode_append(const void* qkv, const void* cosv, const void* sinv, void* q_out, void* k_dst,

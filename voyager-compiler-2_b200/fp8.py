@@ -201,6 +201,42 @@ def roundtrip_add(x: torch.Tensor, scale: torch.Tensor, y: Optional[torch.Tensor
 
 
 @N.device_guarded
+def rope_heads_bf16(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half RoPE of ``x [T, heads, d]`` (any row stride: a slice of a merged projection) in one kernel, with
+    the elementwise graph's roundings, written head-major ``[heads, T, d]`` as the attention kernel reads it."""
+    T, heads, d = x.shape
+    if x.dtype != torch.bfloat16:
+        raise NotImplementedError("rope_heads_bf16 takes bfloat16 input")
+    x, ldx = _heads_view("rope_heads_bf16", x)
+    cos, sin = _bf16_input("rope_heads_bf16", cos), _bf16_input("rope_heads_bf16", sin)
+    if tuple(cos.shape) != (T, d) or tuple(sin.shape) != (T, d):
+        raise ValueError("cos / sin must be [T, head_dim]")
+    out = torch.empty((heads, T, d), dtype=torch.bfloat16, device=x.device)
+    N.check(N.lib().vq_rope_heads_bf16(x.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), T, heads, d, ldx, d,
+                                       d, T * d, _stream()), "vq_rope_heads_bf16")
+    return out
+
+
+@N.device_guarded
+def attention_bf16_heads(q_heads: torch.Tensor, k_heads: torch.Tensor, vt: torch.Tensor,
+                         score_scale: Optional[float] = None, round_acc: bool = True) -> torch.Tensor:
+    """``attention_bf16`` on operands already in the kernel's layout: ``q_heads [heads, T, 128]``, ``k_heads
+    [kv_heads, T, 128]`` (what ``rope_heads_bf16`` writes) and ``vt [kv_heads, 128, T]`` -> ``[T, heads * 128]``."""
+    heads, T, d = q_heads.shape
+    kv = k_heads.shape[0]
+    if k_heads.shape != (kv, T, d) or vt.shape != (kv, d, T) or heads % kv:
+        raise ValueError("attention_bf16_heads: operand shapes do not agree")
+    if any(t.dtype != torch.bfloat16 for t in (q_heads, k_heads, vt)):
+        raise NotImplementedError("attention_bf16_heads takes bfloat16 operands")
+    q_heads, k_heads, vt = q_heads.contiguous(), k_heads.contiguous(), vt.contiguous()
+    out = torch.empty((T, heads * d), dtype=torch.bfloat16, device=q_heads.device)
+    scale = 1.0 / math.sqrt(d) if score_scale is None else float(score_scale)
+    N.check(N.lib().vq_attention_bf16(q_heads.data_ptr(), k_heads.data_ptr(), vt.data_ptr(), out.data_ptr(), heads * d, T,
+                                      kv, heads // kv, d, scale, int(bool(round_acc)), _stream()), "vq_attention_bf16")
+    return out
+
+
+@N.device_guarded
 def attention_bf16(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, score_scale: Optional[float] = None,
                    round_acc: bool = True) -> torch.Tensor:
     """Causal self-attention on bfloat16 operands in one kernel, with the roundings of the eager graph

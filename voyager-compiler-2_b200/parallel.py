@@ -408,7 +408,7 @@ class Nvfp4DecoderLayerTP:
     equals the single-GPU one; the row-parallel sums differ in float32 summation order only.
     """
 
-    LAUNCHES = 13
+    LAUNCHES = 15
     COLLECTIVES = 10
 
     def __init__(self, params, shape, group=None):
@@ -502,7 +502,7 @@ class Nvfp4DecoderLayerTP:
         import torch.nn.functional as F
 
         from . import fp8 as F8
-        from .workloads import apply_rope, rope_tables
+        from .workloads import rope_tables
 
         NV, sh = self.NV, self.shape
         T = x_rows.shape[0] * self.world
@@ -512,10 +512,9 @@ class Nvfp4DecoderLayerTP:
         d, hq, hkv = sh.head_dim, self.hq, self.hkv
         act, t = self._gathered_cast(F.rms_norm(x_rows, (sh.hidden,), self.ln1, sh.eps))
         qkv = NV.nvfp4_gemm(act, self.w_qkv, None, None, torch.bfloat16, alpha_cols=(t * self.tw_qkv).float())
-        q = apply_rope(qkv[:, :hq * d].reshape(T, hq, d), cos, sin)
-        k = apply_rope(qkv[:, hq * d:(hq + hkv) * d].reshape(T, hkv, d), cos, sin)
-        v = qkv[:, (hq + hkv) * d:].reshape(T, hkv, d)
-        ctx = F8.attention_bf16(q, k, v)
+        ctx = F8.attention_bf16_heads(F8.rope_heads_bf16(qkv[:, :hq * d].unflatten(1, (hq, d)), cos, sin),
+                                      F8.rope_heads_bf16(qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d)), cos, sin),
+                                      qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, d)).permute(1, 2, 0).contiguous())
         x1 = self._row_parallel(ctx, self.w_o, self.t_o, x_rows)
         act, t = self._gathered_cast(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps))
         gu = NV.nvfp4_gemm(act, self.w_gu, None, None, torch.bfloat16, alpha_cols=(t * self.tw_gu).float())

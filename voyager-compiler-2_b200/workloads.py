@@ -325,8 +325,8 @@ class Nvfp4DecoderLayer:
         self._rope = None
         self._mask = None
 
-    # kernels of this package per forward (merged): 4 x (amax + cast), 4 GEMMs, the attention
-    LAUNCHES = 13
+    # kernels of this package per forward (merged): 4 x (amax + cast), 4 GEMMs, 2 RoPE, the attention
+    LAUNCHES = 15
 
     def _linear(self, x, names):
         """``[linear(x, W_n) for n in names]`` through one cast of ``x``."""
@@ -372,10 +372,19 @@ class Nvfp4DecoderLayer:
         cos, sin = self._rope
         h = F.rms_norm(x, (sh.hidden,), self.ln1, sh.eps)
         q, k, v = self._linear(h, ("q", "k", "v"))
-        q = apply_rope(q.reshape(T, sh.heads, sh.head_dim), cos, sin)
-        k = apply_rope(k.reshape(T, sh.kv_heads, sh.head_dim), cos, sin)
-        v = v.reshape(T, sh.kv_heads, sh.head_dim)
-        ctx = self._attention(q, k, v)
+        if self.attention == "fused" and sh.head_dim == 128 and T % 128 == 0:
+            # RoPE straight into the attention kernel's head-major layout (slices of the merged projection are
+            # read in place), V transposed for the P V contraction
+            from . import fp8 as F8
+
+            ctx = F8.attention_bf16_heads(F8.rope_heads_bf16(q.unflatten(1, (sh.heads, sh.head_dim)), cos, sin),
+                                          F8.rope_heads_bf16(k.unflatten(1, (sh.kv_heads, sh.head_dim)), cos, sin),
+                                          v.unflatten(1, (sh.kv_heads, sh.head_dim)).permute(1, 2, 0).contiguous())
+        else:
+            q = apply_rope(q.reshape(T, sh.heads, sh.head_dim), cos, sin)
+            k = apply_rope(k.reshape(T, sh.kv_heads, sh.head_dim), cos, sin)
+            v = v.reshape(T, sh.kv_heads, sh.head_dim)
+            ctx = self._attention(q, k, v)
         x1 = x + self._linear(ctx, ("o",))[0]
         h2 = F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps)
         gate, up = self._linear(h2, ("gate", "up"))
