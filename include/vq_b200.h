@@ -414,6 +414,13 @@ int vq_rmsnorm_backward(const void* dy0, const void* dy1, const void* dy2, int g
                         const float* rsqrt_rows, const void* weight, const void* residual, void* dx,
                         float* partial_dw, void* dw, int64_t rows, int64_t cols, void* stream);
 
+/* SwiGLU in bfloat16 with the tensor-wide amax the next cast needs: out = bf16(bf16(silu(gate)) * up) for
+ * gate / up [rows, cols] with row strides ld_gate / ld_up (the halves of a merged projection's output need no
+ * copy), out [rows, cols] dense, and *amax (float32, zero on entry) raised to max |out| by atomicMax -- aten.silu,
+ * aten.mul and the amax of calculate_global_scale (quantization/fake_quantize.py:142-160) in one pass. */
+int vq_silu_mul_amax(const void* gate, const void* up, void* out, void* amax, int64_t rows, int64_t cols,
+                     int64_t ld_gate, int64_t ld_up, void* stream);
+
 /* Rotate-half RoPE of x [T, heads, d] (bfloat16; element (t, h, j) at x + t * in_stride_t + h * in_stride_h + j,
  * so a slice of a merged projection's output needs no copy) written to out + h * out_stride_h + t * out_stride_t
  * + j: head-major for the attention kernel.  cos / sin: bfloat16 [T, d].  y = bf16(bf16(x * cos) + bf16(rot(x) *

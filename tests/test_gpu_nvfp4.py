@@ -182,3 +182,21 @@ def test_nvfp4_decoder_layer_matches_converted_graph(merge, attention):
     # value by up to a third
     assert float(err.max()) <= 6e-2 * float(want.abs().max()), float(err.max() / want.abs().max())
     assert float(err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) <= 2e-2
+
+
+def test_silu_mul_cast_nvfp4_equals_the_separate_nodes():
+    """SwiGLU + amax + cast against quantize_nvfp4(F.silu(gate) * up): the same global scale, and codes that
+    agree except where the approximate exponential moves silu by one bfloat16 step."""
+    import torch.nn.functional as F
+
+    vb = _vb()
+    g = torch.Generator().manual_seed(12)
+    gu = torch.randn(256, 2 * 1024, generator=g).bfloat16().cuda()
+    gate, up = gu[:, :1024], gu[:, 1024:]                      # strided halves of one matrix
+    codes, scales, t = vb.nvfp4.silu_mul_cast_nvfp4(gate, up)
+    want_codes, want_scales, want_t = vb.nvfp4.quantize_nvfp4(F.silu(gate) * up)
+    assert torch.equal(t, want_t)
+    got, _ = vb.nvfp4.unpack_nvfp4(codes, scales)
+    want, _ = vb.nvfp4.unpack_nvfp4(want_codes, want_scales)
+    assert float((got != want).float().mean()) < 2e-3
+    assert float((scales != want_scales).float().mean()) < 2e-3

@@ -136,6 +136,7 @@ SIGNATURES = {
     "vq_hadamard_rotate": [_P, _P, _I, _P, _I64, _I64, _I64, _P],
     "vq_quantize_fp8": [_P, _P, _I, _P, _I, _I64, _I64, _P],
     "vq_softmax_quantize_fp8": [_P, _P, _I64, _I64, _F, _P, _I64, _I64, _P, _I, _I, _P],
+    "vq_silu_mul_amax": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _P],
     "vq_rope_heads_bf16": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P],
     "vq_rope_decode_append": [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
     "vq_fp8_roundtrip_add": [_P, _P, _P, _I64, _P, _I, _P],

@@ -239,6 +239,48 @@ transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
   }
 }
 
+// out = bf16(bf16(silu(gate)) * up) in bfloat16, and max |out| over the whole tensor (atomicMax on the float bits of
+// a zero-initialised word): the SwiGLU nodes of a graph whose next node needs a tensor-wide amax (an NVFP4 cast).
+__global__ void __launch_bounds__(256, 4)
+silu_mul_amax_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, uint4* __restrict__ out,
+                     int64_t nvec, int vecs_per_row, int64_t ld_gate, int64_t ld_up, uint32_t* __restrict__ amax_bits) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t r = first / vecs_per_row;
+  int c = (int)(first - r * vecs_per_row);
+  const int64_t dr = stride / vecs_per_row;
+  const int dc = (int)(stride - dr * vecs_per_row);
+  uint32_t m = 0;
+  for (int64_t v = first; v < nvec; v += stride) {
+    const int64_t gi = r * ld_gate + c, ui = r * ld_up + c;
+    r += dr;
+    c += dc;
+    if (c >= vecs_per_row) { c -= vecs_per_row; ++r; }
+    const uint4 gv = __ldg(gate + gi), uv = __ldg(up + ui);
+    const uint32_t g[4] = {gv.x, gv.y, gv.z, gv.w};
+    const uint32_t u[4] = {uv.x, uv.y, uv.z, uv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g0 = lo_of(g[j]), g1 = hi_of(g[j]);
+      const float s0 = bf16r(__fdividef(g0, 1.0f + __expf(-g0)));
+      const float s1 = bf16r(__fdividef(g1, 1.0f + __expf(-g1)));
+      const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(s0, lo_of(u[j])), __fmul_rn(s1, hi_of(u[j])));
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+      m = max(m, max((o[j] << 16) & 0x7FFFFFFFu, o[j] & 0x7FFF0000u));
+    }
+    out[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  for (int off = 16; off; off >>= 1) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+  __shared__ uint32_t warp_max[8];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) m = max(m, warp_max[w]);
+    atomicMax(amax_bits, m);   // non-negative float bits order like unsigned integers
+  }
+}
+
 // Rotary embedding of x [T, heads, d] (strided: a slice of a merged projection's output) written head-major,
 // out[h * out_h + t * out_t + j], in bfloat16: y = bf16(bf16(x * cos) + bf16(rot(x) * sin)), the graph's
 // elementwise nodes with their roundings, and the layout the attention kernel reads.  Strides in 8-element vectors.
@@ -403,6 +445,23 @@ extern "C" int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* 
       static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint2*>(out), nvec, (int)(cols / 8),
       ld_gate / 8, ld_up / 8, scale, scale_dtype);
   return check_launch("silu_mul_quantize_kernel");
+}
+
+extern "C" int vq_silu_mul_amax(const void* gate, const void* up, void* out, void* amax, int64_t rows, int64_t cols,
+                                int64_t ld_gate, int64_t ld_up, void* stream) {
+  VQ_REQUIRE(rows >= 0 && cols >= 0, "vq_silu_mul_amax: negative size");
+  if (rows == 0 || cols == 0) return VQ_OK;
+  VQ_REQUIRE(gate && up && out && amax, "vq_silu_mul_amax: null argument");
+  VQ_REQUIRE(cols % 8 == 0 && ld_gate % 8 == 0 && ld_up % 8 == 0 && ld_gate >= cols && ld_up >= cols,
+             "vq_silu_mul_amax: the row length and strides must be multiples of 8, strides at least a row");
+  VQ_REQUIRE(cols < (1ll << 31), "vq_silu_mul_amax: row too long");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(amax) & 3) == 0, "vq_silu_mul_amax: misaligned buffers");
+  const int64_t nvec = rows * (cols / 8);
+  silu_mul_amax_kernel<<<stream_grid(nvec, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(gate), static_cast<const uint4*>(up), static_cast<uint4*>(out), nvec, (int)(cols / 8),
+      ld_gate / 8, ld_up / 8, static_cast<uint32_t*>(amax));
+  return check_launch("silu_mul_amax_kernel");
 }
 
 extern "C" int vq_rope_heads_bf16(const void* x, const void* cosv, const void* sinv, void* out, int64_t T, int64_t heads,

@@ -129,6 +129,31 @@ def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = N
     return out.reshape(*abatch, m, n)
 
 
+@N.device_guarded
+def silu_mul_cast_nvfp4(gate: torch.Tensor, up: torch.Tensor):
+    """``quantize_nvfp4(silu(gate) * up)`` with the product and its tensor-wide amax made in one pass:
+    ``(codes, scales, t)``.  ``gate`` / ``up``: ``[rows, cols]`` bfloat16, unit stride along the columns (the two
+    halves of a merged gate/up projection are read in place)."""
+    from . import ops as O
+
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.shape != up.shape or gate.dim() != 2:
+        raise NotImplementedError("silu_mul_cast_nvfp4 takes two bfloat16 matrices of one shape")
+    rows, cols = gate.shape
+
+    def strided(t):
+        ok = t.stride(1) == 1 and t.stride(0) >= cols and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+        return t if ok else t.contiguous()
+
+    gate, up = strided(gate), strided(up)
+    act = torch.empty((rows, cols), dtype=torch.bfloat16, device=gate.device)
+    amax = torch.zeros((), dtype=torch.float32, device=gate.device)
+    N.check(N.lib().vq_silu_mul_amax(gate.data_ptr(), up.data_ptr(), act.data_ptr(), amax.data_ptr(), rows, cols,
+                                     gate.stride(0), up.stride(0), _stream()), "vq_silu_mul_amax")
+    t = O.global_scale_of_amax(amax, torch.bfloat16, FP4_MAX, E4M3_MAX)
+    packed = cast_nvfp4(act, t)
+    return packed.codes, packed.scales, t
+
+
 def nvfp4_linear_from_bf16(x: torch.Tensor, weight: PackedNVFP4, x_global_scale: torch.Tensor,
                            w_global_scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
                            out_dtype=torch.bfloat16) -> torch.Tensor:

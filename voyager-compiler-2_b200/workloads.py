@@ -388,6 +388,12 @@ class Nvfp4DecoderLayer:
         x1 = x + self._linear(ctx, ("o",))[0]
         h2 = F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps)
         gate, up = self._linear(h2, ("gate", "up"))
+        if self.attention == "fused":
+            # SwiGLU, its amax and the NVFP4 cast without a separate amax pass
+            NV = self.NV
+            codes, scales, t = NV.silu_mul_cast_nvfp4(gate, up)
+            down = NV.nvfp4_linear(codes, scales, *self.w["down"], (t * self.tw["down"]).float(), self.one, None)
+            return x1 + down
         return x1 + self._linear(F.silu(gate) * up, ("down",))[0]
 
     __call__ = forward
