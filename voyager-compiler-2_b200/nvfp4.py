@@ -138,6 +138,16 @@ def silu_mul_cast_nvfp4(gate: torch.Tensor, up: torch.Tensor):
 
     if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.shape != up.shape or gate.dim() != 2:
         raise NotImplementedError("silu_mul_cast_nvfp4 takes two bfloat16 matrices of one shape")
+    act, amax = silu_mul_amax(gate, up)
+    t = O.global_scale_of_amax(amax, torch.bfloat16, FP4_MAX, E4M3_MAX)
+    packed = cast_nvfp4(act, t)
+    return packed.codes, packed.scales, t
+
+
+@N.device_guarded
+def silu_mul_amax(gate: torch.Tensor, up: torch.Tensor):
+    """``(silu(gate) * up, max |.|)`` in one pass: the bfloat16 product and a 0-d float32 amax (what a tensor-parallel
+    layer all-reduces before it casts its shard)."""
     rows, cols = gate.shape
 
     def strided(t):
@@ -149,9 +159,7 @@ def silu_mul_cast_nvfp4(gate: torch.Tensor, up: torch.Tensor):
     amax = torch.zeros((), dtype=torch.float32, device=gate.device)
     N.check(N.lib().vq_silu_mul_amax(gate.data_ptr(), up.data_ptr(), act.data_ptr(), amax.data_ptr(), rows, cols,
                                      gate.stride(0), up.stride(0), _stream()), "vq_silu_mul_amax")
-    t = O.global_scale_of_amax(amax, torch.bfloat16, FP4_MAX, E4M3_MAX)
-    packed = cast_nvfp4(act, t)
-    return packed.codes, packed.scales, t
+    return act, amax
 
 
 def nvfp4_linear_from_bf16(x: torch.Tensor, weight: PackedNVFP4, x_global_scale: torch.Tensor,

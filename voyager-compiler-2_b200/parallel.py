@@ -461,12 +461,14 @@ class Nvfp4DecoderLayerTP:
     _collective = Fp8DecoderLayerTP._collective
     collective_seconds = Fp8DecoderLayerTP.collective_seconds
 
-    def _global_scale(self, x):
-        """NVFP4's per-tensor scale of a tensor sharded over the group: the amax is all-reduced first."""
+    def _global_scale(self, x, amax=None):
+        """NVFP4's per-tensor scale of a tensor sharded over the group: the amax (computed here unless the
+        producer already has it) is all-reduced first."""
         from . import ops as O
         from .nvfp4 import E4M3_MAX, FP4_MAX
 
-        amax = O.tensor_amax(x)
+        if amax is None:
+            amax = O.tensor_amax(x)
         if self.world > 1:
             def reduce_max(t, group):
                 dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
@@ -488,11 +490,11 @@ class Nvfp4DecoderLayerTP:
         tiles = self._collective(all_gather_rows, mine.scales.reshape(-1).view(rows // 128, -1))
         return NV.PackedNVFP4(codes, tiles.reshape(-1)), t
 
-    def _row_parallel(self, x_cols, weight, t_w, residual_rows):
+    def _row_parallel(self, x_cols, weight, t_w, residual_rows, amax=None):
         """``x_cols``: all token rows, this rank's slice of the contraction: float32 partial products are
         reduce-scattered over token rows, rounded once and added to the residual rows."""
         NV = self.NV
-        t = self._global_scale(x_cols)
+        t = self._global_scale(x_cols, amax)
         partial = NV.nvfp4_gemm(NV.cast_nvfp4(x_cols, t), weight, (t * t_w).float(), None, torch.float32)
         total = partial if self.world == 1 else self._collective(reduce_scatter_rows, partial)
         return residual_rows + total.to(torch.bfloat16)
@@ -518,6 +520,7 @@ class Nvfp4DecoderLayerTP:
         x1 = self._row_parallel(ctx, self.w_o, self.t_o, x_rows)
         act, t = self._gathered_cast(F.rms_norm(x1, (sh.hidden,), self.ln2, sh.eps))
         gu = NV.nvfp4_gemm(act, self.w_gu, None, None, torch.bfloat16, alpha_cols=(t * self.tw_gu).float())
-        return self._row_parallel(F.silu(gu[:, :self.inter]) * gu[:, self.inter:], self.w_down, self.t_down, x1)
+        act, amax = NV.silu_mul_amax(gu[:, :self.inter], gu[:, self.inter:])
+        return self._row_parallel(act, self.w_down, self.t_down, x1, amax)
 
     __call__ = forward
