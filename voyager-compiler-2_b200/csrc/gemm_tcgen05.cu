@@ -352,10 +352,14 @@ __device__ __noinline__ void epilogue_warp_tile_unstaged(const GemmParams& p, ui
   }
 }
 
+// `release_bar` (a shared::cluster barrier address, or 0): arrived on by lane 0 as soon as the LAST tensor-memory
+// load of [c_begin, c_end) has completed -- before the values still in registers are converted and stored -- for
+// callers that hand the columns back to the MMA warp.
 template <int OUT_DT, int EPI_BUFS>
 __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
                                                      uint8_t* stage0, uint32_t& buf, int row0, int lane, int n0, int b,
-                                                     bool has_alpha, float alpha, int c_begin, int c_end) {
+                                                     bool has_alpha, float alpha, int c_begin, int c_end,
+                                                     uint32_t release_bar = 0) {
   constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
   constexpr int ROUND_COLS = 128 / ESZ;   // output columns per 128-byte staged row
   const int64_t row_stride = p.ldc * ESZ;
@@ -414,9 +418,16 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
     const bool has_b = c0 + 32 < c_end;   // warp-uniform
     tmem_ld_wait();
     if (has_b) tmem_ld_32x32(taddr + (uint32_t)(c0 + 32), vb);
+    const bool release_now = release_bar != 0 && c0 + 64 >= c_end;   // these are the range's last loads
+    if (release_now) {
+      if (has_b) tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(release_bar);
+    }
     process(va, c0);
     if (has_b) {
-      tmem_ld_wait();
+      if (!release_now) tmem_ld_wait();
       if (c0 + 64 < c_end) tmem_ld_32x32(taddr + (uint32_t)(c0 + 64), va);
       process(vb, c0 + 32);
     }
@@ -481,21 +492,24 @@ __device__ __forceinline__ void epilogue_warp_tile_gated(const GemmParams& p, ui
   }
 }
 
+// Returns true when `release_bar` (see epilogue_warp_tile_t) has been arrived on; otherwise the caller does it.
 template <int OUT_DT, int EPI_BUFS = 1>
-__device__ __forceinline__ void epilogue_warp_tile(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
+__device__ __forceinline__ bool epilogue_warp_tile(const GemmParams& p, const CUtensorMap* map_c, uint32_t taddr,
                                                    uint8_t* stage, uint32_t& buf, int row0, int lane, int n0, int b,
-                                                   bool has_alpha, float alpha, int c_begin, int c_end) {
+                                                   bool has_alpha, float alpha, int c_begin, int c_end,
+                                                   uint32_t release_bar = 0) {
   constexpr int ESZ = OUT_DT == VQ_F32 ? 4 : 2;
   if (OUT_DT == VQ_BF16 && p.gate_scale != nullptr) {   // gated launches use the bfloat16 instantiation
     epilogue_warp_tile_gated(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
-    return;
+    return false;
   }
   if (((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.ldc * ESZ) | (uintptr_t)(p.strideC * ESZ)) & 15) != 0) {
     epilogue_warp_tile_unstaged(p, taddr, row0, lane, n0, b, has_alpha, alpha, c_begin, c_end);
-    return;
+    return false;
   }
   epilogue_warp_tile_t<OUT_DT, EPI_BUFS>(p, map_c, taddr, stage, buf, row0, lane, n0, b, has_alpha, alpha, c_begin,
-                                         c_end);
+                                         c_end, release_bar);
+  return release_bar != 0 && c_begin < c_end;
 }
 
 template <int OUT_DT>
@@ -1776,9 +1790,11 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll 1
       for (int seg = 0; seg < 2; ++seg) {
         const int begin = (seg == 0 ? shared0 : other0) + chalf * (QS_OVERLAP / 2);
-        epilogue_warp_tile<OUT_DT, 1>(p, &map_c, taddr, stage, epi_buf, row0, lane, n_blk * BN, b, has_alpha, alpha,
-                                      begin, begin + QS_OVERLAP / 2);
-        if (seg == 0) {
+        // the shared columns are handed back as soon as they are in registers
+        const bool released = epilogue_warp_tile<OUT_DT, 1>(p, &map_c, taddr, stage, epi_buf, row0, lane, n_blk * BN, b,
+                                                            has_alpha, alpha, begin, begin + QS_OVERLAP / 2,
+                                                            seg == 0 ? map_to_cta(&ovl_free[acc], 0) : 0u);
+        if (seg == 0 && !released) {
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(map_to_cta(&ovl_free[acc], 0));
