@@ -1227,7 +1227,17 @@ class C2TP:
         scales = W.calibrate_fp8_scales(full[0], params, self.shape)
         for name in sorted(scales):                                       # one set of scales on every rank
             dist.broadcast(scales[name], src=0)
-        self.layer = P.Fp8DecoderLayerTP(params, scales, self.shape)
+        # the four exchanges of a layer as pulls over peer memory (NVLink) where the GPUs can map one another's
+        # memory, else NCCL's collectives
+        self.exchange_kind = "nccl"
+        exchange = None
+        if EXCHANGE == "peer":
+            try:
+                exchange = P.PeerExchange(self.tokens // world * self.shape.hidden, self.tokens * self.shape.hidden, dev)
+                self.exchange_kind = "peer memory (symmetric buffers, cross-rank barrier, vq_peer_gather / vq_peer_reduce_rows)"
+            except Exception as exc:  # no peer access on this box
+                self.exchange_kind = f"nccl (peer memory unavailable: {type(exc).__name__})"
+        self.layer = P.Fp8DecoderLayerTP(params, scales, self.shape, exchange=exchange)
         del params
         lo, hi = P.shard_bounds(self.tokens, rank, world)
         self.x = [x[lo:hi].contiguous() for x in full]
@@ -1280,6 +1290,7 @@ class C2TP:
         self.layer.timed = False
         return {"share": inside / elapsed, "collective_ms_per_step": inside / steps * 1e3,
                 "eager_ms_per_step": elapsed / steps * 1e3, "collectives_per_step": self.layer.COLLECTIVES,
+                "exchange": self.exchange_kind,
                 "what": "2 x all-gather of FP8 codes [T, 4096] bytes, 2 x reduce-scatter of float32 [T, 4096] partial sums"}
 
     def roofline(self, peaks, reps):
@@ -1384,10 +1395,19 @@ class C4TP:
                                                        "attention, row-parallel o_proj and down_proj; NCCL all-gather of "
                                                        "packed NVFP4 codes + scale tiles, amax all-reduce, reduce-scatter "
                                                        "of float32 partial products)")
+        self.exchange_kind = "nccl"
+        exchange = None
+        if EXCHANGE == "peer":
+            try:
+                per_rank = self.tokens // world * self.shape.hidden
+                exchange = P.PeerExchange(per_rank // 2 + per_rank // 16, self.tokens * self.shape.hidden, dev)
+                self.exchange_kind = "peer memory (symmetric buffers, cross-rank barrier, vq_peer_gather / vq_peer_reduce_rows); amax by NCCL"
+            except Exception as exc:
+                self.exchange_kind = f"nccl (peer memory unavailable: {type(exc).__name__})"
         self.model = []
         for i in range(self.layers):                 # the same seeds on every rank: each quantizes, then keeps its slices
             params = W.make_layer_params_on_device(50 + i, self.shape, dev)
-            self.model.append(P.Nvfp4DecoderLayerTP(params, self.shape))
+            self.model.append(P.Nvfp4DecoderLayerTP(params, self.shape, exchange=exchange))
             del params
         self.last = rank == world - 1
         if self.last:
@@ -1464,6 +1484,7 @@ class C4TP:
         per_layer = self.vb.parallel.Nvfp4DecoderLayerTP.COLLECTIVES
         return {"share": inside / elapsed, "collective_ms_per_step": inside / steps * 1e3,
                 "eager_ms_per_step": elapsed / steps * 1e3, "collectives_per_step": per_layer * self.layers,
+                "exchange": self.exchange_kind,
                 "what": "per layer: 4 x all-reduce(max) of one amax, 2 x (all-gather of packed codes [T, 2048] bytes + "
                         "scale tiles), 2 x reduce-scatter of float32 [T, 4096] partial products"}
 
@@ -1490,6 +1511,7 @@ class C4TP:
 
 
 TENSOR_PARALLEL = {"c2": C2TP, "c4m": C4TP}
+EXCHANGE = "peer"      # --exchange: how a tensor-parallel layer moves token rows between ranks
 
 
 def run_secondary(name, dev, rank, peaks, steps, device_index):
@@ -1636,9 +1658,14 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--replicas", action="store_true",
                     help="with N > 1 GPUs run N independent replicas instead of one tensor-parallel layer")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="tensor-parallel token-row exchanges: pulls over peer memory (default, NCCL if the GPUs cannot "
+                         "map one another's memory) or NCCL collectives")
     ap.add_argument("--no-secondary", action="store_true",
                     help="skip the q1 / c1 / c4 measurements that follow the default workload's line")
     args = ap.parse_args()
+    global EXCHANGE
+    EXCHANGE = args.exchange
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -529,6 +529,20 @@ int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* 
                      int alpha_dtype, const void* bias, int bias_dtype, const void* alpha_cols, int alpha_cols_dtype,
                      void* stream);
 
+/* Token-row exchanges of a tensor-parallel layer by plain loads from peer memory (NVLink), for ranks whose
+ * buffers are mapped into one another's address space (symmetric memory).  peer_ptrs: a HOST array of `world`
+ * device pointers, one buffer per rank (this rank's own at its index), 16-byte aligned.  Neither kernel waits on
+ * another GPU: the caller orders them after the buffers' producers with a cross-rank barrier.
+ *   vq_peer_gather      out[p * chunk_bytes + i] = peer[p][i]: all-gather of every rank's chunk (chunk_bytes a
+ *                       multiple of 16) into this GPU's `out` (world * chunk_bytes)
+ *   vq_peer_reduce_rows out[i] = sum_p peer[p][rank * chunk_floats + i], p = 0 .. world-1 in that order:
+ *                       reduce-scatter of float32 partial sums (chunk_floats a multiple of 4) into `out`
+ * They stand where ncclAllGather / ncclReduceScatter stand in the row-parallel linears of a layer short enough
+ * for the collectives' latency to dominate it. */
+int vq_peer_gather(const void* const* peer_ptrs, int64_t world, int64_t chunk_bytes, void* out, void* stream);
+int vq_peer_reduce_rows(const void* const* peer_ptrs, int64_t world, int64_t rank, int64_t chunk_floats, void* out,
+                        void* stream);
+
 /* Synchronising health check for the GEMM kernels: returns VQ_ETIMEOUT if any
  * launch since the last reset gave up on a bounded barrier wait (its output is
  * then invalid).  No counterpart in the reference. */

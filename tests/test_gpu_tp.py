@@ -49,6 +49,20 @@ def test_two_gpu_fp8_decoder_layer_matches_one_gpu_and_the_oracle():
     assert float((got.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
 
 
+def test_two_gpu_fp8_decoder_layer_over_peer_memory_equals_the_nccl_layer():
+    """The same layer with its all-gathers and reduce-scatters as pulls over peer memory: the gathered codes are
+    the same bytes and the float32 partial sums are added in rank order, as NCCL's two-rank reduction does."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    manager = mp.Manager()
+    nccl, peer = manager.dict(), manager.dict()
+    mp.spawn(tp_common.run_rank_fp8_layer, args=(2, 29631, nccl), nprocs=2, join=True)
+    mp.spawn(tp_common.run_rank_fp8_layer, args=(2, 29633, peer, True), nprocs=2, join=True)
+    a, b = nccl["out"].float(), peer["out"].float()
+    assert float((a - b).abs().max()) <= 2e-2 * float(a.abs().max())
+    assert float((a != b).float().mean()) < 0.02
+
+
 def test_two_gpu_nvfp4_decoder_layer():
     """The NVFP4 layer sharded over two GPUs (packed codes and scale tiles gathered, amax all-reduced, float32
     partial products reduce-scattered) against the same layer on one GPU and against the CPU oracle."""
@@ -73,6 +87,19 @@ def test_two_gpu_nvfp4_decoder_layer():
     err = (got - want).abs()
     assert float(err.max()) <= 6e-2 * float(want.abs().max())
     assert float(err.pow(2).mean().sqrt() / want.pow(2).mean().sqrt()) <= 2e-2
+
+
+def test_two_gpu_nvfp4_decoder_layer_over_peer_memory_equals_the_nccl_layer():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    manager = mp.Manager()
+    nccl, peer = manager.dict(), manager.dict()
+    mp.spawn(tp_common.run_rank_nvfp4_layer, args=(2, 29635, nccl), nprocs=2, join=True)
+    mp.spawn(tp_common.run_rank_nvfp4_layer, args=(2, 29637, peer, True), nprocs=2, join=True)
+    a, b = nccl["out"].float(), peer["out"].float()
+    # the same gathered bytes; two-rank float32 sums in rank order either way
+    assert float((a - b).abs().max()) <= 6e-2 * float(a.abs().max())
+    assert float((a - b).pow(2).mean().sqrt() / a.pow(2).mean().sqrt()) <= 5e-3
 
 
 def test_nvfp4_tensor_parallel_layer_on_one_rank_is_the_layer():

@@ -91,8 +91,9 @@ def fp8_layer_problem(seed=3):
     return shape, tokens, params, x, scales
 
 
-def run_rank_fp8_layer(rank, world, port, results):
-    """The tensor- and sequence-parallel FP8 decoder layer on ``world`` GPUs; rank 0 gathers the output rows."""
+def run_rank_fp8_layer(rank, world, port, results, peer=False):
+    """The tensor- and sequence-parallel FP8 decoder layer on ``world`` GPUs; rank 0 gathers the output rows.
+    ``peer``: the exchanges pull over peer memory (``PeerExchange``) instead of calling NCCL."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -104,10 +105,14 @@ def run_rank_fp8_layer(rank, world, port, results):
         P = voyager_b200.parallel
         dev = f"cuda:{rank}"
         shape, tokens, params, x, scales = fp8_layer_problem()
+        exchange = P.PeerExchange(tokens // world * shape.hidden, tokens * shape.hidden, dev) if peer else None
         layer = P.Fp8DecoderLayerTP({k: v.to(dev) for k, v in params.items()}, {k: v.to(dev) for k, v in scales.items()},
-                                    shape)
+                                    shape, exchange=exchange)
         lo, hi = P.shard_bounds(tokens, rank, world)
         rows = layer(x[lo:hi].to(dev))
+        if peer:                       # twice more: the buffers are reused across steps
+            rows = layer(x[lo:hi].to(dev))
+            rows = layer(x[lo:hi].to(dev))
         out = P.all_gather_rows(rows)
         voyager_b200.ops.gemm_status()
         assert voyager_b200.fp8.attention_status() == 0
@@ -126,7 +131,7 @@ def nvfp4_layer_problem(seed=7):
     return shape, tokens, W.make_layer_params(seed, shape), W.make_hidden_states(seed + 1, tokens, shape)
 
 
-def run_rank_nvfp4_layer(rank, world, port, results):
+def run_rank_nvfp4_layer(rank, world, port, results, peer=False):
     """The tensor-parallel NVFP4 decoder layer on ``world`` GPUs; rank 0 gathers the output rows."""
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -139,9 +144,15 @@ def run_rank_nvfp4_layer(rank, world, port, results):
         P = voyager_b200.parallel
         dev = f"cuda:{rank}"
         shape, tokens, params, x = nvfp4_layer_problem()
-        layer = P.Nvfp4DecoderLayerTP({k: v.to(dev) for k, v in params.items()}, shape)
+        exchange = None
+        if peer:
+            per_rank = tokens // world * shape.hidden
+            exchange = P.PeerExchange(per_rank // 2 + per_rank // 16, tokens * shape.hidden, dev)
+        layer = P.Nvfp4DecoderLayerTP({k: v.to(dev) for k, v in params.items()}, shape, exchange=exchange)
         lo, hi = P.shard_bounds(tokens, rank, world)
         rows = layer(x[lo:hi].to(dev))
+        if peer:
+            rows = layer(x[lo:hi].to(dev))      # the buffers are reused across steps
         out = P.all_gather_rows(rows)
         voyager_b200.ops.gemm_status()
         assert voyager_b200.fp8.attention_status() == 0

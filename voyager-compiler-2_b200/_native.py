@@ -116,6 +116,8 @@ SIGNATURES = {
                       ctypes.POINTER(VqGemmEpilogue), _P],
     "vq_gemm_mx": [_P, _P, _P, _P, _I64, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I,
                    _P],
+    "vq_peer_gather": [_P, _I64, _I64, _P, _P],
+    "vq_peer_reduce_rows": [_P, _I64, _I64, _I64, _P, _P],
     "vq_gemm_status": [_I],
     "vq_nvfp4_scale_bytes": [_I64, _I64],
     "vq_quantize_nvfp4": [_P, _P, _I, _P, _P, _I64, _I64, _P],

@@ -62,13 +62,14 @@ def quantize_fp8(x: torch.Tensor, scale: torch.Tensor, dtype="fp8_e4m3") -> torc
 def fp8_gemm(a: torch.Tensor, b: torch.Tensor, alpha: Optional[torch.Tensor] = None,
              bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, dtype: str = "fp8_e4m3",
              alpha_cols: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-             causal=None, gated_scale: Optional[torch.Tensor] = None, round_acc: bool = False) -> torch.Tensor:
+             causal=None, gated_scale: Optional[torch.Tensor] = None, round_acc: bool = False,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``alpha * alpha_cols[n] * (a @ b^T) + bias`` (+ ``residual`` after the rounding) for FP8 byte
     operands ``a [*batch, M, K]`` and ``b [*batch, N, K]`` (or ``[N, K]``), fp32 accumulation;
-    ``causal``, ``gated_scale`` and ``round_acc`` as for ``ops.gemm_tn``."""
+    ``causal``, ``gated_scale``, ``round_acc`` and ``out`` as for ``ops.gemm_tn``."""
     return gemm_tn(a, b, out_dtype=out_dtype, alpha=alpha, bias=bias, in_kind=_FORMATS[dtype],
                    alpha_cols=alpha_cols, residual=residual, causal=causal, gated_scale=gated_scale,
-                   round_acc=round_acc)
+                   round_acc=round_acc, out=out)
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, chunk: int = 32) -> torch.Tensor:
@@ -279,11 +280,18 @@ def _bf16_input(name: str, t: torch.Tensor) -> torch.Tensor:
 
 
 @N.device_guarded
-def rmsnorm_quantize_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, scale: torch.Tensor) -> torch.Tensor:
-    """e4m3 bytes of ``rms_norm(x, weight, eps) / scale`` in one pass over ``x [..., H]``."""
+def rmsnorm_quantize_fp8(x: torch.Tensor, weight: torch.Tensor, eps: float, scale: torch.Tensor,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """e4m3 bytes of ``rms_norm(x, weight, eps) / scale`` in one pass over ``x [..., H]`` (into ``out``, a dense
+    uint8 tensor of that many bytes, when given)."""
     x, weight, scale = _bf16_input("rmsnorm_quantize_fp8", x), _bf16_input("rmsnorm_quantize_fp8", weight), _scale_arg(scale)
     cols = x.shape[-1]
-    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    elif out.dtype != torch.uint8 or out.numel() != x.numel() or not out.is_contiguous():
+        raise ValueError("out must be a dense uint8 tensor with one byte per element")
+    else:
+        out = out.view(x.shape)
     N.check(N.lib().vq_rmsnorm_quantize_fp8(x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.numel() // max(cols, 1),
                                             cols, float(eps), scale.data_ptr(), _dtype_id(scale.dtype), _stream()),
             "vq_rmsnorm_quantize_fp8")

@@ -90,7 +90,7 @@ def pack_nvfp4(codes: torch.Tensor, scale: torch.Tensor, check: bool = True) -> 
 @N.device_guarded
 def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = None,
                bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
-               alpha_cols: Optional[torch.Tensor] = None) -> torch.Tensor:
+               alpha_cols: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``alpha * alpha_cols[n] * (A @ B^T) + bias`` for packed operands ``a [*batch, M, K]`` and
     ``b [*batch, N, K]`` (equal batch shapes; a 2-D ``b`` with a batched ``a`` folds the batch into the rows)."""
     *abatch, m, k = a.shape
@@ -111,7 +111,10 @@ def nvfp4_gemm(a: PackedNVFP4, b: PackedNVFP4, alpha: Optional[torch.Tensor] = N
         for d in abatch:
             batch *= d
         a_codes, a_scales, m_eff = a.codes, a.scales, m
-    out = torch.empty((batch, m_eff, n), dtype=out_dtype, device=a.codes.device)
+    if out is None:
+        out = torch.empty((batch, m_eff, n), dtype=out_dtype, device=a.codes.device)
+    elif out.dtype != out_dtype or out.numel() != batch * m_eff * n or not out.is_contiguous():
+        raise ValueError("out must be a dense tensor of the result's size and dtype")
     if alpha is not None:
         alpha = alpha.reshape(()) if alpha.dtype in _DTYPE_ID else alpha.float().reshape(())
     if bias is not None:

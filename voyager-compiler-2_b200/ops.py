@@ -581,7 +581,7 @@ def _parse_layout(layout: str):
 
 @N.device_guarded
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bias=None, in_kind=None,
-            alpha_cols=None, residual=None, causal=None, gated_scale=None, round_acc=False):
+            alpha_cols=None, residual=None, causal=None, gated_scale=None, round_acc=False, out=None):
     """``out[..., m, n] = alpha * sum_k a[..., m, k] * b[..., n, k] + bias[n]`` on the
     tensor cores (fp32 accumulation, one rounding to ``out_dtype``).
 
@@ -597,7 +597,7 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
     roundings of a converted per-tensor graph).
 
     ``a`` is ``[*batch, M, K]`` and ``b`` ``[*batch, N, K]`` or ``[N, K]``; both are
-    used K-contiguous.  ``in_kind`` overrides the operand element kind for 8-bit
+    used K-contiguous.  ``out``: a dense tensor to write the result into instead of a new one.  ``in_kind`` overrides the operand element kind for 8-bit
     operands stored as ``uint8``/``float8`` bytes.
     """
     if in_kind is None:
@@ -635,6 +635,11 @@ def gemm_tn(a: torch.Tensor, b: torch.Tensor, *, out_dtype=None, alpha=None, bia
                                       "no residual")
         n_out = n // 2
         out = torch.empty((batch, rows, n_out), dtype=torch.uint8, device=a.device)
+    elif out is not None:
+        # the caller's buffer (e.g. memory its peers can read): dense, the result's size and dtype
+        if out.dtype != out_dtype or out.numel() != batch * rows * n or not out.is_contiguous():
+            raise ValueError("out must be a dense tensor of the result's size and dtype")
+        out = out.view(batch, rows, n)
     else:
         out = torch.empty((batch, rows, n), dtype=out_dtype, device=a.device)
     if bias is not None:

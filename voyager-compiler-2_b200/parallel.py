@@ -249,6 +249,91 @@ def gptq_layer_parallel(problems, solve, group=None):
 # ---------------------------------------------------------------------------
 # The per-tensor FP8 decoder layer, tensor- and sequence-parallel
 # ---------------------------------------------------------------------------
+class PeerExchange:
+    """All-gather and reduce-scatter over token rows by plain loads from the peers' memory (NVLink) instead of
+    NCCL: each rank writes into its own symmetric-memory buffer, a cross-rank barrier orders the writes, and
+    ``vq_peer_gather`` / ``vq_peer_reduce_rows`` pull what this rank needs.  One buffer serves the gathers and one
+    the partial sums; a layer alternates gather, reduce, gather, reduce, so the barrier of the next exchange
+    also tells every rank that its peers have finished reading the buffer it is about to rewrite.
+
+    ``gather_bytes`` / ``reduce_floats``: the largest per-rank chunk of each kind.  Needs peer access between
+    the group's GPUs (``torch.distributed._symmetric_memory``)."""
+
+    def __init__(self, gather_bytes: int, reduce_floats: int, device, group=None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.gather_buf = symm.empty(max(gather_bytes, 16), dtype=torch.uint8, device=device)
+        self.reduce_buf = symm.empty(max(reduce_floats, 4), dtype=torch.float32, device=device)
+        self.gather_hdl = symm.rendezvous(self.gather_buf, self.group)
+        self.reduce_hdl = symm.rendezvous(self.reduce_buf, self.group)
+        array = ctypes.c_void_p * self.world
+        self._gather_ptrs = array(*[int(p) for p in self.gather_hdl.buffer_ptrs])
+        self._reduce_ptrs = array(*[int(p) for p in self.reduce_hdl.buffer_ptrs])
+        self._channel = 0
+
+    def gather_slot(self, nbytes: int) -> torch.Tensor:
+        """This rank's chunk of the next all-gather, to be written by the producer kernel."""
+        return self.gather_buf[:nbytes]
+
+    def reduce_slot(self, shape) -> torch.Tensor:
+        """This rank's float32 partial sums (all token rows) of the next reduce-scatter, the GEMM's output."""
+        n = 1
+        for extent in shape:
+            n *= extent
+        return self.reduce_buf[:n].view(shape)
+
+    def all_gather_rows(self, mine: torch.Tensor) -> torch.Tensor:
+        """``mine``: a view of ``gather_slot`` already written on the current stream.  Returns every rank's rows."""
+        from ._native import check, lib
+        from .ops import _stream
+
+        nbytes = mine.numel() * mine.element_size()
+        if nbytes % 16:
+            raise ValueError("a rank's chunk must be a multiple of 16 bytes")
+        out = torch.empty((self.world * mine.shape[0], *mine.shape[1:]), dtype=mine.dtype, device=mine.device)
+        self.gather_hdl.barrier(channel=0)
+        check(lib().vq_peer_gather(self._gather_ptrs, self.world, nbytes, out.data_ptr(), _stream()), "vq_peer_gather")
+        return out
+
+    def all_gather_parts(self, parts):
+        """After ONE barrier, gather several byte ranges ``(offset, nbytes)`` of every rank's ``gather_slot``
+        (each a multiple of 16 bytes at a 16-byte aligned offset): a list of flat uint8 tensors, rank-major."""
+        import ctypes
+
+        from ._native import check, lib
+        from .ops import _stream
+
+        self.gather_hdl.barrier(channel=0)
+        outs = []
+        for offset, nbytes in parts:
+            if offset % 16 or nbytes % 16:
+                raise ValueError("parts are multiples of 16 bytes at 16-byte aligned offsets")
+            ptrs = (ctypes.c_void_p * self.world)(*[int(p) + offset for p in self.gather_hdl.buffer_ptrs])
+            out = torch.empty(self.world * nbytes, dtype=torch.uint8, device=self.gather_buf.device)
+            check(lib().vq_peer_gather(ptrs, self.world, nbytes, out.data_ptr(), _stream()), "vq_peer_gather")
+            outs.append(out)
+        return outs
+
+    def reduce_scatter_rows(self, partial: torch.Tensor) -> torch.Tensor:
+        """``partial``: ``reduce_slot(shape)`` already written.  Returns this rank's rows of the sum over ranks."""
+        from ._native import check, lib
+        from .ops import _stream
+
+        rows = partial.shape[0]
+        if rows % self.world:
+            raise ValueError(f"{rows} token rows do not split over {self.world} ranks")
+        chunk = partial.numel() // self.world
+        out = torch.empty((rows // self.world, *partial.shape[1:]), dtype=torch.float32, device=partial.device)
+        self.reduce_hdl.barrier(channel=0)
+        check(lib().vq_peer_reduce_rows(self._reduce_ptrs, self.world, self.rank, chunk, out.data_ptr(), _stream()),
+              "vq_peer_reduce_rows")
+        return out
+
+
 def shard_fp8_layer(params, shape, rank: int, world: int):
     """The slices of one decoder layer's weights that ``rank`` of ``world`` holds: q/k/v by whole heads
     (rows), gate/up by rows, o and down by the matching input columns.  Returns ``(weights, heads)``
@@ -286,10 +371,11 @@ class Fp8DecoderLayerTP:
     reads it.  ``collective_seconds`` accumulates CUDA-event time around them when ``timed`` is set.
     """
 
-    def __init__(self, params, scales, shape, group=None, graph_rounding=True):
+    def __init__(self, params, scales, shape, group=None, graph_rounding=True, exchange=None):
         from . import fp8 as FP8
 
         self.FP8, self.shape, self.group, self.scales = FP8, shape, group, scales
+        self.exchange = exchange          # a PeerExchange: pulls over peer memory instead of NCCL collectives
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.ra = bool(graph_rounding)
@@ -334,10 +420,25 @@ class Fp8DecoderLayerTP:
         self.collective_events = []
         return total
 
+    def _gather(self, x_rows, ln, scale):
+        """RMSNorm + FP8 cast of this rank's rows, then every rank's codes."""
+        FP8, sh = self.FP8, self.shape
+        if self.exchange is None:
+            return self._collective(all_gather_rows, FP8.rmsnorm_quantize_fp8(x_rows, ln, sh.eps, scale))
+        mine = FP8.rmsnorm_quantize_fp8(x_rows, ln, sh.eps, scale, out=self.exchange.gather_slot(x_rows.numel()))
+        return self._collective(lambda t, group: self.exchange.all_gather_rows(t), mine)
+
+    def _partial_out(self, rows, cols):
+        """Where a row-parallel GEMM writes its float32 partial sums: memory the peers can read, or a new tensor."""
+        return None if self.exchange is None else self.exchange.reduce_slot((rows, cols))
+
     def _finish_row_parallel(self, partial, alpha, residual_rows):
         """Reduce-scatter the float32 partial sums over token rows, then what the single-GPU epilogue
         does: round the sum (the matmul's rounding), scale (the dequantize), add the residual rows."""
-        total = self._collective(reduce_scatter_rows, partial)
+        if self.exchange is None:
+            total = self._collective(reduce_scatter_rows, partial)
+        else:
+            total = self._collective(lambda t, group: self.exchange.reduce_scatter_rows(t), partial)
         y = total.to(torch.bfloat16) * alpha if self.ra else (total * alpha.float()).to(torch.bfloat16)
         return residual_rows + y
 
@@ -353,7 +454,7 @@ class Fp8DecoderLayerTP:
             self._rope = rope_tables(T, sh, x_rows.device)
         cos, sin = self._rope
         d, hq, hkv = sh.head_dim, self.hq, self.hkv
-        h8 = self._collective(all_gather_rows, FP8.rmsnorm_quantize_fp8(x_rows, self.ln1, sh.eps, s["h"]))
+        h8 = self._gather(x_rows, self.ln1, s["h"])
         qkv = FP8.fp8_gemm(h8, self.w8_qkv, alpha_cols=self.alpha_qkv, round_acc=self.ra)
         q = qkv[:, :hq * d].unflatten(1, (hq, d))
         k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
@@ -363,12 +464,13 @@ class Fp8DecoderLayerTP:
         q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(hkv, (hq // hkv) * T, d)
         ctx8 = FP8.attention_fp8(q8, k8, vt8, self.alpha_qk, 1.0 / math.sqrt(d), s["p"], self.alpha_pv, s["ctx"],
                                  round_acc=self.ra)                                   # [T, hq * d]
-        partial = FP8.fp8_gemm(ctx8, self.w8_o, out_dtype=torch.float32)              # [T, hidden], this rank's K
+        partial = FP8.fp8_gemm(ctx8, self.w8_o, out_dtype=torch.float32,
+                               out=self._partial_out(T, sh.hidden))                   # [T, hidden], this rank's K
         x1 = self._finish_row_parallel(partial, self.alpha_o, x_rows)
-        h28 = self._collective(all_gather_rows, FP8.rmsnorm_quantize_fp8(x1, self.ln2, sh.eps, s["h2"]))
+        h28 = self._gather(x1, self.ln2, s["h2"])
         act8 = FP8.fp8_gemm(h28, self.w8_swiglu, alpha_cols=self.alpha_swiglu, gated_scale=s["act"],
                             round_acc=self.ra)                                        # [T, intermediate / world]
-        partial = FP8.fp8_gemm(act8, self.w8_down, out_dtype=torch.float32)
+        partial = FP8.fp8_gemm(act8, self.w8_down, out_dtype=torch.float32, out=self._partial_out(T, sh.hidden))
         return self._finish_row_parallel(partial, self.alpha_down, x1)
 
     __call__ = forward
@@ -411,10 +513,11 @@ class Nvfp4DecoderLayerTP:
     LAUNCHES = 15
     COLLECTIVES = 10
 
-    def __init__(self, params, shape, group=None):
+    def __init__(self, params, shape, group=None, exchange=None):
         from . import nvfp4 as NV
 
         self.NV, self.shape, self.group = NV, shape, group
+        self.exchange = exchange          # a PeerExchange: row exchanges pull over peer memory instead of NCCL
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         w, d = self.world, shape.head_dim
@@ -486,6 +589,14 @@ class Nvfp4DecoderLayerTP:
             raise ValueError("a rank's token rows must be whole 128-row scale tiles")
         if self.world == 1:
             return mine, t
+        if self.exchange is not None:
+            cb, sb = mine.codes.numel(), mine.scales.numel()
+            slot = self.exchange.gather_slot(cb + sb)
+            slot[:cb].copy_(mine.codes.reshape(-1))
+            slot[cb:].copy_(mine.scales.reshape(-1))
+            codes, tiles = self._collective(lambda parts, group: self.exchange.all_gather_parts(parts),
+                                            [(0, cb), (cb, sb)])
+            return NV.PackedNVFP4(codes.view(self.world * rows, k // 2), tiles), t
         codes = self._collective(all_gather_rows, mine.codes)
         tiles = self._collective(all_gather_rows, mine.scales.reshape(-1).view(rows // 128, -1))
         return NV.PackedNVFP4(codes, tiles.reshape(-1)), t
@@ -495,8 +606,15 @@ class Nvfp4DecoderLayerTP:
         reduce-scattered over token rows, rounded once and added to the residual rows."""
         NV = self.NV
         t = self._global_scale(x_cols, amax)
-        partial = NV.nvfp4_gemm(NV.cast_nvfp4(x_cols, t), weight, (t * t_w).float(), None, torch.float32)
-        total = partial if self.world == 1 else self._collective(reduce_scatter_rows, partial)
+        peer = self.exchange is not None and self.world > 1
+        out = self.exchange.reduce_slot((x_cols.shape[0], weight.codes.shape[0])) if peer else None
+        partial = NV.nvfp4_gemm(NV.cast_nvfp4(x_cols, t), weight, (t * t_w).float(), None, torch.float32, out=out)
+        if self.world == 1:
+            total = partial
+        elif peer:
+            total = self._collective(lambda p, group: self.exchange.reduce_scatter_rows(p), partial)
+        else:
+            total = self._collective(reduce_scatter_rows, partial)
         return residual_rows + total.to(torch.bfloat16)
 
     def forward(self, x_rows):
