@@ -1401,7 +1401,7 @@ class C4TP:
             try:
                 per_rank = self.tokens // world * self.shape.hidden
                 exchange = P.PeerExchange(per_rank // 2 + per_rank // 16, self.tokens * self.shape.hidden, dev)
-                self.exchange_kind = "peer memory (symmetric buffers, cross-rank barrier, vq_peer_gather / vq_peer_reduce_rows); amax by NCCL"
+                self.exchange_kind = "peer memory (symmetric buffers, cross-rank barrier, vq_peer_gather / vq_peer_reduce_rows / vq_peer_max)"
             except Exception as exc:
                 self.exchange_kind = f"nccl (peer memory unavailable: {type(exc).__name__})"
         self.model = []

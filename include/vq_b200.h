@@ -542,6 +542,8 @@ int vq_gemm_nvfp4_ex(const void* A, const void* sfa, const void* B, const void* 
 int vq_peer_gather(const void* const* peer_ptrs, int64_t world, int64_t chunk_bytes, void* out, void* stream);
 int vq_peer_reduce_rows(const void* const* peer_ptrs, int64_t world, int64_t rank, int64_t chunk_floats, void* out,
                         void* stream);
+/* out[0] = max over ranks of the float32 at the start of each rank's buffer: all-reduce(max) of a tensor's amax. */
+int vq_peer_max(const void* const* peer_ptrs, int64_t world, void* out, void* stream);
 
 /* Synchronising health check for the GEMM kernels: returns VQ_ETIMEOUT if any
  * launch since the last reset gave up on a bounded barrier wait (its output is

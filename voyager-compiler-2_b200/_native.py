@@ -116,6 +116,7 @@ SIGNATURES = {
                       ctypes.POINTER(VqGemmEpilogue), _P],
     "vq_gemm_mx": [_P, _P, _P, _P, _I64, _P, _I, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P, _I,
                    _P],
+    "vq_peer_max": [_P, _I64, _P, _P],
     "vq_peer_gather": [_P, _I64, _I64, _P, _P],
     "vq_peer_reduce_rows": [_P, _I64, _I64, _I64, _P, _P],
     "vq_gemm_status": [_I],

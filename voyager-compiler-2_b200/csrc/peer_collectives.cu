@@ -8,6 +8,7 @@
 //   gather : out[p * chunk + i] = peer[p][i]                      all-gather of every rank's rows
 //   reduce : out[i] = sum over p = 0 .. world-1 of peer[p][rank * chunk + i]   reduce-scatter of float32 partial
 //            sums over token rows, added in rank order (every rank gets a deterministic sum)
+//   max    : out[0] = max over p of peer[p][0]                    all-reduce(max) of one non-negative scalar (an amax)
 //
 // They replace ncclAllGather / ncclReduceScatter in the row-parallel linears of parallel.py where the layer is
 // so short that the library collectives' latency dominates the step.
@@ -46,6 +47,16 @@ peer_reduce_rows_kernel(PeerPtrs peers, int world, int rank, int64_t chunk_vecs,
       if (p < world) { s.x += v[p].x; s.y += v[p].y; s.z += v[p].z; s.w += v[p].w; }
     out[i] = s;
   }
+}
+
+// out[0] = max over ranks of peer[p][0] (non-negative floats: an amax), one warp.
+__global__ void peer_max_kernel(PeerPtrs peers, int world, float* __restrict__ out) {
+  float m = 0.0f;
+#pragma unroll
+  for (int p = 0; p < kMaxPeers; ++p)
+    if (p < world && (int)threadIdx.x == p) m = *static_cast<const volatile float*>(peers.p[p]);
+  for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+  if (threadIdx.x == 0) out[0] = m;
 }
 
 int check_peers(const void* const* peer_ptrs, int64_t world, PeerPtrs* out, const char* what) {
@@ -95,4 +106,12 @@ extern "C" int vq_peer_reduce_rows(const void* const* peer_ptrs, int64_t world, 
   peer_reduce_rows_kernel<<<peer_grid(chunk_floats / 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       peers, (int)world, (int)rank, chunk_floats / 4, static_cast<float4*>(out));
   return check_launch("peer_reduce_rows_kernel");
+}
+
+extern "C" int vq_peer_max(const void* const* peer_ptrs, int64_t world, void* out, void* stream) {
+  VQ_REQUIRE(out != nullptr, "vq_peer_max: null output");
+  PeerPtrs peers{};
+  if (int e = check_peers(peer_ptrs, world, &peers, "vq_peer_max")) return e;
+  peer_max_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(peers, (int)world, static_cast<float*>(out));
+  return check_launch("peer_max_kernel");
 }

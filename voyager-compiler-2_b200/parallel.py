@@ -268,8 +268,11 @@ class PeerExchange:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.gather_buf = symm.empty(max(gather_bytes, 16), dtype=torch.uint8, device=device)
         self.reduce_buf = symm.empty(max(reduce_floats, 4), dtype=torch.float32, device=device)
+        self.scalar_buf = symm.empty(4, dtype=torch.float32, device=device)
         self.gather_hdl = symm.rendezvous(self.gather_buf, self.group)
         self.reduce_hdl = symm.rendezvous(self.reduce_buf, self.group)
+        self.scalar_hdl = symm.rendezvous(self.scalar_buf, self.group)
+        self._scalar_ptrs = (ctypes.c_void_p * self.world)(*[int(p) for p in self.scalar_hdl.buffer_ptrs])
         array = ctypes.c_void_p * self.world
         self._gather_ptrs = array(*[int(p) for p in self.gather_hdl.buffer_ptrs])
         self._reduce_ptrs = array(*[int(p) for p in self.reduce_hdl.buffer_ptrs])
@@ -297,6 +300,18 @@ class PeerExchange:
         out = torch.empty((self.world * mine.shape[0], *mine.shape[1:]), dtype=mine.dtype, device=mine.device)
         self.gather_hdl.barrier(channel=0)
         check(lib().vq_peer_gather(self._gather_ptrs, self.world, nbytes, out.data_ptr(), _stream()), "vq_peer_gather")
+        return out
+
+    def all_reduce_max(self, value: torch.Tensor) -> torch.Tensor:
+        """Max over ranks of a non-negative float32 scalar (a tensor's amax).  Uses of the scalar buffer are
+        separated by a gather or a reduce, like those of the other two buffers."""
+        from ._native import check, lib
+        from .ops import _stream
+
+        self.scalar_buf[:1].copy_(value.reshape(1))
+        out = torch.empty((), dtype=torch.float32, device=value.device)
+        self.scalar_hdl.barrier(channel=0)
+        check(lib().vq_peer_max(self._scalar_ptrs, self.world, out.data_ptr(), _stream()), "vq_peer_max")
         return out
 
     def all_gather_parts(self, parts):
@@ -572,7 +587,9 @@ class Nvfp4DecoderLayerTP:
 
         if amax is None:
             amax = O.tensor_amax(x)
-        if self.world > 1:
+        if self.world > 1 and self.exchange is not None:
+            amax = self._collective(lambda t, group: self.exchange.all_reduce_max(t), amax)
+        elif self.world > 1:
             def reduce_max(t, group):
                 dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
                 return t
