@@ -20,6 +20,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include <cuda_fp8.h>
 
@@ -83,12 +84,26 @@ __device__ __forceinline__ float load_param(const void* p, int64_t i, int dt) {
 // Every lane of a warp works on the same 32 columns (one row each): lane j fetches
 // column j's factor and bias with one coalesced load and the warp shares them by
 // shuffle.  All 32 lanes must call this together.
+// This lane's column factor and bias of the 32-column chunk at col0 (1 and 0 where there is none).
+__device__ __forceinline__ void load_col_params(const GemmParams& p, int col0, float* col_factor, float* col_bias) {
+  const int lane = threadIdx.x & 31;
+  *col_factor = 1.0f;
+  *col_bias = 0.0f;
+  if (p.alpha_cols != nullptr && col0 + lane < p.N) *col_factor = load_param(p.alpha_cols, col0 + lane, p.alpha_cols_dt);
+  if (p.bias != nullptr && col0 + lane < p.N) *col_bias = load_param(p.bias, col0 + lane, p.bias_dt);
+}
+__device__ __forceinline__ void scale_chunk_with(const GemmParams& p, const uint32_t (&v)[32], float (&f)[32],
+                                                 float col_factor, float col_bias, bool has_alpha, float alpha);
 __device__ __forceinline__ void scale_chunk(const GemmParams& p, const uint32_t (&v)[32], float (&f)[32], int col0,
                                             bool has_alpha, float alpha) {
-  const int lane = threadIdx.x & 31;
-  float col_factor = 1.0f, col_bias = 0.0f;
-  if (p.alpha_cols != nullptr && col0 + lane < p.N) col_factor = load_param(p.alpha_cols, col0 + lane, p.alpha_cols_dt);
-  if (p.bias != nullptr && col0 + lane < p.N) col_bias = load_param(p.bias, col0 + lane, p.bias_dt);
+  float col_factor, col_bias;
+  load_col_params(p, col0, &col_factor, &col_bias);
+  scale_chunk_with(p, v, f, col_factor, col_bias, has_alpha, alpha);
+}
+// The per-column parameters come from the caller, which can fetch them long before the accumulator is ready:
+// loaded here they put a trip to global memory in front of every chunk.
+__device__ __forceinline__ void scale_chunk_with(const GemmParams& p, const uint32_t (&v)[32], float (&f)[32],
+                                                 float col_factor, float col_bias, bool has_alpha, float alpha) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
   if (p.round_acc) {   // the matmul's own rounding, before the dequantize's scale
@@ -110,8 +125,15 @@ __device__ __forceinline__ void scale_chunk(const GemmParams& p, const uint32_t 
     for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(f[j], alpha);
   }
   if (p.alpha_cols != nullptr) {
+    // one factor for all 32 columns (tensor-wise scales of merged projections): no exchange per element
+    const float first = __shfl_sync(0xFFFFFFFFu, col_factor, 0);
+    if (__all_sync(0xFFFFFFFFu, col_factor == first)) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(f[j], __shfl_sync(0xFFFFFFFFu, col_factor, j));
+      for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(f[j], first);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = __fmul_rn(f[j], __shfl_sync(0xFFFFFFFFu, col_factor, j));
+    }
   }
   if (p.bias != nullptr) {
 #pragma unroll
@@ -441,6 +463,75 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
 //   a = bf16(bf16(silu(g)) * u)             the activation, every rounding of the unfused graph kept
 //   C = e4m3(bf16(a / scale))               32 bytes per row: one full sector per lane, stored directly
 // C is [M, N / 2] bytes.
+//
+// The arithmetic of a 32-column pair is written as three branch-free passes over 16 independent two-element
+// chains (activation, quotient, code), so that the compiler interleaves the chains: with a branch inside the
+// chain (the quotient's rare exact-division case) every chain ran alone and the epilogue, not the main loop,
+// set the time of the merged gate/up GEMM.  The rare cases are collected in a mask and redone after the pass.
+__device__ __forceinline__ uint32_t mul_rn_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ void store_32_bytes(uint8_t* dst, const uint32_t (&q)[8], bool aligned32) {
+  if (aligned32) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(dst), "r"(q[0]), "r"(q[1]), "r"(q[2]), "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7])
+                 : "memory");
+  } else {
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(q[0], q[1], q[2], q[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(q[4], q[5], q[6], q[7]);
+  }
+}
+// g: 32 gate values as bfloat16 pairs; f: the 32 up values (float32, scaled); q: the 32 output bytes.
+template <bool ORDINARY>
+__device__ __forceinline__ void gated_pair(const uint32_t (&g)[16], const float (&f)[32], float s_out, float r_out,
+                                           uint32_t (&q)[8]) {
+  uint32_t a[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint32_t u = pack_pair<VQ_BF16>(f[2 * j], f[2 * j + 1]);
+    const float g0 = __uint_as_float(g[j] << 16), g1 = __uint_as_float(g[j] & 0xFFFF0000u);
+    const uint32_t sl = pack_pair<VQ_BF16>(__fdividef(g0, 1.0f + __expf(-g0)), __fdividef(g1, 1.0f + __expf(-g1)));
+    a[j] = mul_rn_bf16x2(sl, u);   // the float32 product of two bfloat16 values is exact: one rounding either way
+  }
+  float y[32];
+  uint32_t slow = 0;   // bit i: element i needs the exact division
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float a0 = __uint_as_float(a[j] << 16), a1 = __uint_as_float(a[j] & 0xFFFF0000u);
+    if (ORDINARY) {
+      // div_to_bf16 without its branch; a zero numerator gives the exact (signed) zero through the product too
+      const float q0 = __fmul_rn(a0, r_out), q1 = __fmul_rn(a1, r_out);
+      const uint32_t b0 = __float_as_uint(q0), b1 = __float_as_uint(q1);
+      const uint32_t e0 = (b0 >> 23) & 0xFFu, e1 = (b1 >> 23) & 0xFFu;
+      const bool s0 = (e0 == 0u && a0 != 0.0f) || e0 == 0xFFu || ((b0 & 0xFFFFu) - 0x7FFDu) <= 6u;
+      const bool s1 = (e1 == 0u && a1 != 0.0f) || e1 == 0xFFu || ((b1 & 0xFFFFu) - 0x7FFDu) <= 6u;
+      slow |= (s0 ? 1u : 0u) << (2 * j) | (s1 ? 1u : 0u) << (2 * j + 1);
+      const uint32_t w = pack_pair<VQ_BF16>(q0, q1);
+      y[2 * j] = __uint_as_float(w << 16);
+      y[2 * j + 1] = __uint_as_float(w & 0xFFFF0000u);
+    } else {
+      y[2 * j] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(a0, s_out)));
+      y[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(a1, s_out)));
+    }
+  }
+  if (ORDINARY && slow != 0u) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (slow & (1u << (2 * j)))
+        y[2 * j] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(__uint_as_float(a[j] << 16), s_out)));
+      if (slow & (1u << (2 * j + 1)))
+        y[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(__uint_as_float(a[j] & 0xFFFF0000u), s_out)));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint32_t code = (uint32_t)__nv_cvt_float2_to_fp8x2(
+        make_float2(__fadd_rn(y[2 * j], 0.0f), __fadd_rn(y[2 * j + 1], 0.0f)), __NV_SATFINITE, __NV_E4M3);
+    if (j & 1) q[j >> 1] |= code << 16; else q[j >> 1] = code;
+  }
+}
 __device__ __forceinline__ void epilogue_warp_tile_gated(const GemmParams& p, uint32_t taddr, int row0, int lane,
                                                          int n0, int b, bool has_alpha, float alpha, int c_begin,
                                                          int c_end) {
@@ -449,6 +540,11 @@ __device__ __forceinline__ void epilogue_warp_tile_gated(const GemmParams& p, ui
   const float s_out = load_param(p.gate_scale, 0, p.gate_scale_dt);
   const bool ordinary = ordinary_divisor(s_out);
   const float r_out = __frcp_rn(s_out);
+  const bool aligned32 = ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)p.ldc | (uintptr_t)p.strideC) & 31) == 0;
+  // the column factors of the warp's (at most four) chunks, fetched before the first accumulator values arrive
+  float factor[4], unused_bias;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) load_col_params(p, n0 + c_begin + 32 * i, &factor[i], &unused_bias);
   uint32_t va[32], vb[32];
   tmem_ld_32x32(taddr + (uint32_t)c_begin, va);
 #pragma unroll 1
@@ -456,39 +552,23 @@ __device__ __forceinline__ void epilogue_warp_tile_gated(const GemmParams& p, ui
     tmem_ld_wait();
     tmem_ld_32x32(taddr + (uint32_t)(c0 + 32), vb);
     float f[32];
-    scale_chunk(p, va, f, n0 + c0, has_alpha, alpha);
+    const int round = (c0 - c_begin) >> 6;   // 0 or 1 with the kernels' 128-column ranges
+    float gate_factor = round ? factor[2] : factor[0], up_factor = round ? factor[3] : factor[1];
+    if (round > 1) {
+      load_col_params(p, n0 + c0, &gate_factor, &unused_bias);
+      load_col_params(p, n0 + c0 + 32, &up_factor, &unused_bias);
+    }
+    scale_chunk_with(p, va, f, gate_factor, 0.0f, has_alpha, alpha);
     uint32_t g[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) g[j] = pack_pair<VQ_BF16>(f[2 * j], f[2 * j + 1]);
     tmem_ld_wait();
     if (c0 + 64 < c_end) tmem_ld_32x32(taddr + (uint32_t)(c0 + 64), va);
-    scale_chunk(p, vb, f, n0 + c0 + 32, has_alpha, alpha);
+    scale_chunk_with(p, vb, f, up_factor, 0.0f, has_alpha, alpha);
     uint32_t q[8];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const uint32_t u = pack_pair<VQ_BF16>(f[2 * j], f[2 * j + 1]);
-      const float g0 = __uint_as_float(g[j] << 16), g1 = __uint_as_float(g[j] & 0xFFFF0000u);
-      const uint32_t sl = pack_pair<VQ_BF16>(__fdividef(g0, 1.0f + __expf(-g0)), __fdividef(g1, 1.0f + __expf(-g1)));
-      const uint32_t a = pack_pair<VQ_BF16>(__fmul_rn(__uint_as_float(sl << 16), __uint_as_float(u << 16)),
-                                            __fmul_rn(__uint_as_float(sl & 0xFFFF0000u), __uint_as_float(u & 0xFFFF0000u)));
-      const float a0 = __uint_as_float(a << 16), a1 = __uint_as_float(a & 0xFFFF0000u);
-      float y0, y1;
-      if (ordinary) {
-        y0 = div_to_bf16(a0, s_out, r_out);
-        y1 = div_to_bf16(a1, s_out, r_out);
-      } else {
-        y0 = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(a0, s_out)));
-        y1 = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(a1, s_out)));
-      }
-      const uint32_t code = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fadd_rn(y0, 0.0f), __fadd_rn(y1, 0.0f)),
-                                                               __NV_SATFINITE, __NV_E4M3);
-      if (j & 1) q[j >> 1] |= code << 16; else q[j >> 1] = code;
-    }
-    if (my_row < p.M && n0 + c0 < p.N) {
-      uint4* dst = reinterpret_cast<uint4*>(out_row + ((n0 + c0) >> 1));
-      dst[0] = make_uint4(q[0], q[1], q[2], q[3]);
-      dst[1] = make_uint4(q[4], q[5], q[6], q[7]);
-    }
+    if (ordinary) gated_pair<true>(g, f, s_out, r_out, q);
+    else gated_pair<false>(g, f, s_out, r_out, q);
+    if (my_row < p.M && n0 + c0 < p.N) store_32_bytes(out_row + ((n0 + c0) >> 1), q, aligned32);
   }
 }
 
@@ -510,6 +590,25 @@ __device__ __forceinline__ bool epilogue_warp_tile(const GemmParams& p, const CU
   epilogue_warp_tile_t<OUT_DT, EPI_BUFS>(p, map_c, taddr, stage, buf, row0, lane, n0, b, has_alpha, alpha, c_begin,
                                          c_end, release_bar);
   return release_bar != 0 && c_begin < c_end;
+}
+
+// The MMAs of one pipeline stage (128 bytes of K = four instructions) as straight-line code, the operand
+// kind a template parameter.  Choosing the kind at run time between consecutive tcgen05.mma instructions
+// (`if (f8) mma_f8 else mma_f16` inside the unrolled loop) was measured to cost a third of the tensor
+// throughput: 2048x28672x4096 e4m3 207 us with the choice inside the sequence, 141 us with it outside.
+template <bool F8, bool PAIR>
+__device__ __forceinline__ void issue_stage(uint32_t tmem_acc, uint32_t a_addr, uint32_t b_addr, uint32_t idesc,
+                                            bool accumulate_first) {
+#pragma unroll
+  for (int k = 0; k < BK_BYTES / MMA_K_BYTES; ++k) {
+    const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
+    const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
+    const uint32_t accumulate = (accumulate_first || k > 0) ? 1u : 0u;
+    if constexpr (F8 && PAIR) mma_f8f6f4_ss_pair(tmem_acc, da, db, idesc, accumulate);
+    else if constexpr (F8) mma_f8f6f4_ss(tmem_acc, da, db, idesc, accumulate);
+    else if constexpr (PAIR) mma_f16_ss_pair(tmem_acc, da, db, idesc, accumulate);
+    else mma_f16_ss(tmem_acc, da, db, idesc, accumulate);
+  }
 }
 
 template <int OUT_DT>
@@ -589,7 +688,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
+    auto mma_role = [&](auto kind_tag) {   // compiled once per operand kind: no branch between MMA instructions
+      constexpr bool F8 = decltype(kind_tag)::value;
+      const uint32_t idesc = p.idesc;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -602,16 +703,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem_a + stage * A_STAGE_BYTES);
-          const uint32_t b_addr = smem_u32(smem_b + stage * B_STAGE_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK_BYTES / MMA_K_BYTES; ++k) {
-            const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
-            const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
-            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            if (p.kind_f8) mma_f8f6f4_ss(tmem_acc, da, db, p.idesc, accumulate);
-            else mma_f16_ss(tmem_acc, da, db, p.idesc, accumulate);
-          }
+          issue_stage<F8, false>(tmem_acc, smem_u32(smem_a + stage * A_STAGE_BYTES), smem_u32(smem_b + stage * B_STAGE_BYTES),
+                                 idesc, kb > 0);
           mma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -619,6 +712,10 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mma_commit(&acc_full[acc]);  // accumulator complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
+    };
+    if (lane == 0) {
+      if (p.kind_f8) mma_role(std::true_type{});
+      else mma_role(std::false_type{});
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -668,6 +765,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 //   acc_full      : one per CTA, same commit mechanism
 //   acc_empty     : lives in the even CTA; 8 arrivals (4 epilogue warps x 2 CTAs)
 // ---------------------------------------------------------------------------
+constexpr int P_THREADS = 384;             // one warpgroup of {TMA warp, MMA warp, two idle warps} + two epilogue warpgroups
+constexpr int P_EPI_WARP0 = 4;             // first epilogue warp
 constexpr int P_STAGES = 6;
 constexpr int P_EPI_BUFS = 1;              // staging buffers per epilogue warp (2 was measured: no gain, and it costs a pipeline stage)
 constexpr int P_A_BYTES = 128 * BK_BYTES;  // 16 KB
@@ -675,7 +774,7 @@ constexpr int P_B_BYTES = 128 * BK_BYTES;  // 16 KB (half of the tile's B rows)
 constexpr size_t P_SMEM_BYTES = 1024 + P_STAGES * (P_A_BYTES + P_B_BYTES) + 256 + P_EPI_BUFS * EPI_STAGE_BYTES;
 
 template <int OUT_DT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c,
                     const __grid_constant__ GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -739,6 +838,11 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Register budget by warpgroup (384 threads x 168 at launch): the producer / MMA group keeps 40 per thread,
+  // the two epilogue groups take 232, so that the epilogue's double-buffered tensor-memory loads and its
+  // arithmetic fit without spilling to local memory.
+  if (warp < P_EPI_WARP0) {
+  reg_dealloc<40>();
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------
     if (lane == 0) {
@@ -767,7 +871,11 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (even CTA only) ----------------
-    if (lane == 0 && rank == 0) {
+    // The whole role is compiled once per operand kind, so that nothing but the barrier wait separates the
+    // MMA instructions of consecutive stages.
+    auto mma_role = [&](auto kind_tag) {
+      constexpr bool F8 = decltype(kind_tag)::value;
+      const uint32_t idesc = p.idesc;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -782,16 +890,8 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kb = 0; kb < kb_end; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_u32(smem_a + stage * P_A_BYTES);
-          const uint32_t b_addr = smem_u32(smem_b + stage * P_B_BYTES);
-#pragma unroll
-          for (int k = 0; k < BK_BYTES / MMA_K_BYTES; ++k) {
-            const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
-            const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
-            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            if (p.kind_f8) mma_f8f6f4_ss_pair(tmem_acc, da, db, p.idesc, accumulate);
-            else mma_f16_ss_pair(tmem_acc, da, db, p.idesc, accumulate);
-          }
+          issue_stage<F8, true>(tmem_acc, smem_u32(smem_a + stage * P_A_BYTES), smem_u32(smem_b + stage * P_B_BYTES),
+                                idesc, kb > 0);
           mma_commit_pair(&empty_bar[stage], 0x3);  // both CTAs may refill this stage
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -799,11 +899,17 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         mma_commit_pair(&acc_full[acc], 0x3);  // both CTAs' epilogues may read their rows
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
+    };
+    if (lane == 0 && rank == 0) {
+      if (p.kind_f8) mma_role(std::true_type{});
+      else mma_role(std::false_type{});
     }
+  }
   } else {
+    reg_alloc<232>();
     // ------------------------------ epilogue (both CTAs) ----------------------
     const int quarter = warp & 3;
-    const int chalf = (warp - 2) >> 2;
+    const int chalf = (warp - P_EPI_WARP0) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -820,7 +926,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(&acc_full[acc], acc_phase, abort_flag))) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(quarter * 32) << 16);
-      epilogue_warp_tile<OUT_DT, P_EPI_BUFS>(p, &map_c, taddr, epi_stage + (warp - 2) * (P_EPI_BUFS * 32 * 128), epi_buf,
+      epilogue_warp_tile<OUT_DT, P_EPI_BUFS>(p, &map_c, taddr, epi_stage + (warp - P_EPI_WARP0) * (P_EPI_BUFS * 32 * 128), epi_buf,
                                              m_blk * 2 * BM + (int)rank * BM + quarter * 32,
                          lane, n_blk * bn, b, has_alpha, alpha, chalf * (bn / 2), (chalf + 1) * (bn / 2));
       tc_fence_before_sync();
@@ -830,7 +936,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   }
 
-  if (warp >= 2 && lane == 0) tma_store_wait_read();   // staging buffers stay valid until their stores have read them
+  if (warp >= P_EPI_WARP0 && lane == 0) tma_store_wait_read();   // staging buffers stay valid until their stores have read them
   __syncthreads();
   if (threadIdx.x == 0 && *abort_flag) atomicExch(&g_gemm_error, VQ_ETIMEOUT);
   cluster_sync();  // neither CTA leaves while the other may still signal its barriers or read its tiles
@@ -1733,6 +1839,7 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         bool ok = true;
         int64_t done = 0;   // tiles issued so far
         uint32_t it = 0;    // stages issued so far: scale buffer it & 1, its use number it >> 1
+        const uint32_t idesc = p.idesc;
         for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++done) {
           if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
           if (done > 0 && !mbar_wait(&ovl_free[acc ^ 1], (uint32_t)(((done - 1) >> 1) & 1), abort_flag)) { ok = false; break; }
@@ -1746,11 +1853,17 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             if (!mbar_wait(&sf_ready[buf], (it >> 1) & 1u, abort_flag) ||
                 !mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            for (int k = 0; k < steps; ++k) {
+            auto issue = [&](int k) {
               const uint32_t grp = tmem_base + QS_SF_COL + buf * QS_SF_BUF_COLS + 16 * k;
               const uint64_t da = smem_desc_k_major_sw128(a_addr + k * MMA_K_BYTES);
               const uint64_t db = smem_desc_k_major_sw128(b_addr + k * MMA_K_BYTES);
-              mma_nvfp4_ss_pair(tmem_acc, da, db, p.idesc, grp + 8, grp, (kb > 0 || k > 0) ? 1u : 0u);
+              mma_nvfp4_ss_pair(tmem_acc, da, db, idesc, grp + 8, grp, (kb > 0 || k > 0) ? 1u : 0u);
+            };
+            if (steps == 4) {   // a full stage: four instructions as straight-line code
+#pragma unroll
+              for (int k = 0; k < 4; ++k) issue(k);
+            } else {
+              for (int k = 0; k < steps; ++k) issue(k);
             }
             mma_commit_pair(&empty_bar[stage], 0x3);
             mma_commit_pair(&sf_free[buf], 0x3);
@@ -2035,7 +2148,7 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
       return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kSmCount, 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(P_THREADS, 1, 1);
     cfg.dynamicSmemBytes = P_SMEM_BYTES;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -2066,7 +2179,7 @@ int vq_gemm_tn_ex(const void* A, const void* B, void* C, int in_kind, int out_dt
     p.idesc = sm100::make_idesc(2 * BM, p.bn, fmt, fmt, 0, 0);
     const int64_t tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + p.bn - 1) / p.bn) * batch;
     const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
-    VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_pair_kernel)<<<2 * clusters, NUM_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
+    VQ_FOR_OUT_DTYPE(out_dtype, gemm_tn_pair_kernel)<<<2 * clusters, P_THREADS, P_SMEM_BYTES, st>>>(map_a, map_b, map_c, p);
     return check_launch("gemm_tn_pair_kernel");
   }
 
