@@ -1705,13 +1705,16 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
 //   the half the epilogue warps drain first), scale buffers at [384,448) and [448,512),
 //   each four 16-column groups [B scales 8 | A scales 4 | unused 4], one per K64 step.
 //   sf_full[s]   : per CTA, its own scale tiles of stage s have landed
-//   sf_ready[b]  : even CTA; 8 arrivals (4 scale warps x 2 CTAs): buffer b holds the next stage's scales
-//   sf_free[b]   : per CTA; the MMAs that read buffer b have completed (tcgen05.commit)
+//   full_bar[s]  : even CTA; besides the operand bytes it counts 8 arrivals (4 scale warps x 2 CTAs): the
+//                  stage's scales are in tensor memory.  A scale buffer is free again when the stage that used
+//                  it two stages ago completes its empty barrier, so the MMA thread's loop is wait, four MMAs,
+//                  one commit, exactly as in the FP8 kernel: with a barrier pair of their own for the scales
+//                  (one more wait and one more commit per stage in that thread) the kernel was a fifth slower.
 //   the other barriers as in the kernel above
 // Four warpgroups as in gemm_mx_pair_kernel: registers 40 / 184 / 184 / 104.
 // ---------------------------------------------------------------------------
 constexpr int QS_THREADS = 512;
-constexpr int QS_EPI_WARP0 = 4, QS_SF_WARP0 = 12;
+constexpr int QS_EPI_WARP0 = 4, QS_SF_WARP0 = 12, QS_SF_WARPS = 4;
 constexpr uint32_t QS_ACC1_COL = 128, QS_SF_COL = 384, QS_SF_BUF_COLS = 64;
 constexpr int QS_OVERLAP = 128;
 
@@ -1744,9 +1747,7 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint64_t* acc_full = bars + 3 * QP_STAGES;          // [2]
   uint64_t* acc_empty = bars + 3 * QP_STAGES + 2;     // [2] (used in the even CTA)
   uint64_t* ovl_free = bars + 3 * QP_STAGES + 4;      // [2] (used in the even CTA)
-  uint64_t* sf_ready = bars + 3 * QP_STAGES + 6;      // [2] (used in the even CTA)
-  uint64_t* sf_free = bars + 3 * QP_STAGES + 8;       // [2] per CTA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * QP_STAGES + 10);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * QP_STAGES + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -1768,7 +1769,7 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < QP_STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
+      mbar_init(&full_bar[s], 1 + 2 * QS_SF_WARPS);   // the producer's expect_tx + the scale warps of both CTAs
       mbar_init(&sf_full[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -1776,8 +1777,6 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 2 * EPI_WARPS);
       mbar_init(&ovl_free[a], 2 * EPI_WARPS);  // every epilogue warp of both CTAs
-      mbar_init(&sf_ready[a], 8);
-      mbar_init(&sf_free[a], 1);
     }
     fence_barrier_init();
   }
@@ -1850,8 +1849,7 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const uint32_t buf = it & 1u;
             const uint32_t a_addr = smem_u32(smem_a + stage * QP_A_BYTES);
             const uint32_t b_addr = smem_u32(smem_b + stage * QP_B_BYTES);
-            if (!mbar_wait(&sf_ready[buf], (it >> 1) & 1u, abort_flag) ||
-                !mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }   // operands landed, scales stored
             tc_fence_after_sync();
             auto issue = [&](int k) {
               const uint32_t grp = tmem_base + QS_SF_COL + buf * QS_SF_BUF_COLS + 16 * k;
@@ -1865,8 +1863,7 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             } else {
               for (int k = 0; k < steps; ++k) issue(k);
             }
-            mma_commit_pair(&empty_bar[stage], 0x3);
-            mma_commit_pair(&sf_free[buf], 0x3);
+            mma_commit_pair(&empty_bar[stage], 0x3);   // frees the stage and, for the scale warps, scale buffer `buf`
             if (++stage == QP_STAGES) { stage = 0; phase ^= 1; }
           }
           if (!ok) break;
@@ -1928,10 +1925,13 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     bool ok = true;
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-        const uint32_t buf = it & 1u, use = it >> 1;
-        // the tiles have landed, and the MMAs that read this buffer two stages ago have completed
+        const uint32_t buf = it & 1u;
+        // The tiles have landed, and the MMAs that read this buffer two stages ago have completed: that is the
+        // completion of that stage's empty barrier (the same use of the ring when the stage index did not wrap).
+        const int prev = stage >= 2 ? stage - 2 : stage - 2 + QP_STAGES;
+        const uint32_t prev_phase = stage >= 2 ? phase : phase ^ 1u;
         if (!__all_sync(0xFFFFFFFFu, mbar_wait(&sf_full[stage], phase, abort_flag) &&
-                                         (use == 0 || mbar_wait(&sf_free[buf], (use - 1) & 1u, abort_flag)))) { ok = false; break; }
+                                         (it < 2 || mbar_wait(&empty_bar[prev], prev_phase, abort_flag)))) { ok = false; break; }
         tc_fence_after_sync();
         const uint8_t* sfa = smem_sfa + stage * QP_SFA_BYTES + lane * 16;
         const uint8_t* sfb = smem_sfb + stage * QP_SFB_BYTES + lane * 16;
@@ -1947,7 +1947,7 @@ gemm_nvfp4_sfw_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(&sf_ready[buf], 0));
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(&full_bar[stage], 0));
         if (++stage == QP_STAGES) { stage = 0; phase ^= 1; }
       }
     }
