@@ -485,6 +485,15 @@ int vq_silu_mul_quantize_fp8(const void* gate, const void* up, void* out, int64_
 int vq_rope_quantize_fp8(const void* x, const void* cosv, const void* sinv, void* out, int64_t T, int64_t heads,
                          int64_t d, int64_t in_stride_t, int64_t in_stride_h, int64_t out_stride_t,
                          int64_t out_stride_h, const void* scale, int scale_dtype, void* stream);
+/* The three casts between a merged q/k/v projection and vq_attention_fp8 as one launch: vq_rope_quantize_fp8 of the
+ * query heads q [T, q_heads, d] and of the key heads k [T, kv_heads, d] (head-major e4m3 outputs [heads, T, d]) and
+ * vq_transpose_quantize_fp8 of the value heads v [T, kv_heads, d] (vt_out [kv_heads, d, T]); q, k and v are bfloat16
+ * column slices of one matrix with `ld` elements between tokens, cos / sin are [T, d] bfloat16, each scale holds one
+ * element.  Results equal the three separate calls bit for bit.  d % 16 == 0, ld % 8 == 0, 16-byte aligned inputs. */
+int vq_qkv_post_fp8(const void* q, const void* k, const void* v, int64_t ld, const void* cosv, const void* sinv,
+                    void* q_out, void* k_out, void* vt_out, int64_t T, int64_t q_heads, int64_t kv_heads, int64_t d,
+                    const void* q_scale, int q_scale_dtype, const void* k_scale, int k_scale_dtype,
+                    const void* v_scale, int v_scale_dtype, void* stream);
 int vq_transpose_quantize_fp8(const void* x, void* out, void* codes, void* amax_bits, int format, int64_t T,
                               int64_t heads, int64_t d, int64_t ldx, const void* scale, int scale_dtype,
                               void* stream);

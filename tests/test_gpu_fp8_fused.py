@@ -307,3 +307,28 @@ def test_roundtrip_add_equals_quantize_dequantize_add(shape, with_y):
     assert torch.equal(got, want)
     got32 = vb.fp8.roundtrip_add(x, scale.float(), y)
     assert torch.equal(got32, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,heads,kv,d", [(256, 8, 2, 128), (192, 4, 4, 64), (130, 2, 1, 128)])
+def test_qkv_post_equals_the_separate_casts(T, heads, kv, d):
+    """One launch for RoPE + cast of q and k and the cast + transpose of v: bit-identical to the three calls."""
+    import voyager_b200 as vb
+
+    FP8 = vb.fp8
+    g = torch.Generator().manual_seed(T + heads)
+    qkv = (torch.randn(T, (heads + 2 * kv) * d, generator=g) * 2).bfloat16().cuda()
+    q = qkv[:, :heads * d].unflatten(1, (heads, d))
+    k = qkv[:, heads * d:(heads + kv) * d].unflatten(1, (kv, d))
+    v = qkv[:, (heads + kv) * d:].unflatten(1, (kv, d))
+    pos = torch.arange(T, dtype=torch.float32)[:, None] * torch.exp(-torch.arange(d // 2, dtype=torch.float32) / (d // 2) * 9.2)[None]
+    cos = torch.cat([pos.cos(), pos.cos()], 1).bfloat16().cuda()
+    sin = torch.cat([pos.sin(), pos.sin()], 1).bfloat16().cuda()
+    sq, sk, sv = (torch.tensor(x, device="cuda") for x in (0.011, 0.013, 0.017))
+    q8, k8, vt8 = FP8.qkv_post_fp8(q, k, v, cos, sin, sq, sk, sv)
+    assert torch.equal(q8, FP8.rope_quantize_fp8(q, cos, sin, sq))
+    assert torch.equal(k8, FP8.rope_quantize_fp8(k, cos, sin, sk))
+    assert torch.equal(vt8.view(torch.uint8), FP8.transpose_quantize_fp8(v, sv).view(torch.uint8))
+    # operands that are not slices of one matrix take the separate calls
+    q8b, k8b, vt8b = FP8.qkv_post_fp8(q.contiguous(), k.contiguous(), v.contiguous(), cos, sin, sq, sk, sv)
+    assert torch.equal(q8b, q8) and torch.equal(k8b, k8) and torch.equal(vt8b.view(torch.uint8), vt8.view(torch.uint8))

@@ -150,6 +150,7 @@ SIGNATURES = {
     "vq_rmsnorm_backward": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _P],
     "vq_rmsnorm_quantize_fp8": [_P, _P, _P, _I64, _I64, _F, _P, _I, _P],
     "vq_silu_mul_quantize_fp8": [_P, _P, _P, _I64, _I64, _I64, _I64, _P, _I, _P],
+    "vq_qkv_post_fp8": [_P, _P, _P, _I64, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P, _I, _P, _I, _P, _I, _P],
     "vq_rope_quantize_fp8": [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _P, _I, _P],
     "vq_transpose_quantize_fp8": [_P, _P, _P, _P, _I, _I64, _I64, _I64, _I64, _P, _I, _P],
 }

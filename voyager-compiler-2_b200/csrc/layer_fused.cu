@@ -112,10 +112,12 @@ silu_mul_quantize_kernel(const uint4* __restrict__ gate, const uint4* __restrict
 // Element (t, h, j) is read at x[t * in_t + h * in_h + j] and its byte written at
 // out[t * out_t + h * out_h + j]; cos/sin: [T, d] bf16 or absent (no rotation).
 // y = bf16(bf16(x * cos) + bf16(rot(x) * sin)), rot(x) = (-x[d/2:], x[:d/2]).
-__global__ void __launch_bounds__(256)
-rope_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv, const uint4* __restrict__ sinv,
-                     uint2* __restrict__ out, int T, int heads, int d, int64_t in_t, int64_t in_h, int64_t out_t,
-                     int64_t out_h, int apply_rope, const void* __restrict__ scale, int scale_dt) {
+// `block` of `blocks`: the caller's share of the grid (a kernel that does several jobs gives each a range of its blocks).
+__device__ __forceinline__ void rope_quantize_body(const uint4* __restrict__ x, const uint4* __restrict__ cosv,
+                                                   const uint4* __restrict__ sinv, uint2* __restrict__ out, int T,
+                                                   int heads, int d, int64_t in_t, int64_t in_h, int64_t out_t,
+                                                   int64_t out_h, int apply_rope, const void* __restrict__ scale,
+                                                   int scale_dt, int block, int blocks) {
   const Divisor dv = make_divisor(scale, scale_dt);
   const int vpd = d >> 3;          // 8-element vectors per head row; strides are in vectors here
   const int half = vpd >> 1;
@@ -124,8 +126,7 @@ rope_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv
   // thread index and one 32-bit division splits the head row's index into (t, h)
   const bool pow2 = (vpd & (vpd - 1)) == 0 && (int64_t)T * heads < (1ll << 31);
   const int vshift = 31 - __clz(vpd);
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t idx = (int64_t)block * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)blocks * blockDim.x) {
     int v, h, t;
     if (pow2) {
       v = (int)(idx & (vpd - 1));
@@ -164,20 +165,28 @@ rope_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv
     out[t * out_t + h * out_h + v] = make_uint2(o[0], o[1]);
   }
 }
+__global__ void __launch_bounds__(256)
+rope_quantize_kernel(const uint4* __restrict__ x, const uint4* __restrict__ cosv, const uint4* __restrict__ sinv,
+                     uint2* __restrict__ out, int T, int heads, int d, int64_t in_t, int64_t in_h, int64_t out_t,
+                     int64_t out_h, int apply_rope, const void* __restrict__ scale, int scale_dt) {
+  rope_quantize_body(x, cosv, sinv, out, T, heads, d, in_t, in_h, out_t, out_h, apply_rope, scale, scale_dt,
+                     (int)blockIdx.x, (int)gridDim.x);
+}
 
 // ---- cast + transpose: x [T, heads, d] bf16 -> transposed fp8 [heads, d, T] ----
 // Optionally also the codes in x's own layout and the bit pattern of max |x|
 // (bfloat16 magnitudes order as their bit patterns do, NaN above all).
+// (bx, by, bz): the 64-token tile, the 64-column tile and the head this block takes.
 template <bool E4M3>
-__global__ void __launch_bounds__(256)
-transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out, uint8_t* __restrict__ codes,
-                          int* __restrict__ amax_bits, int T, int heads, int d, int64_t ldx,
-                          const void* __restrict__ scale, int scale_dt) {
+__device__ __forceinline__ void transpose_quantize_body(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out,
+                                                        uint8_t* __restrict__ codes, int* __restrict__ amax_bits, int T,
+                                                        int heads, int d, int64_t ldx, const void* __restrict__ scale,
+                                                        int scale_dt, int bx, int by, int bz) {
   __shared__ __align__(16) uint8_t tile[64][64 + 4];
   __shared__ int block_max;
   const Divisor dv = make_divisor(scale, scale_dt);
-  const int h = blockIdx.z;
-  const int t0 = blockIdx.x * 64, j0 = blockIdx.y * 64;
+  const int h = bz;
+  const int t0 = bx * 64, j0 = by * 64;
   if (threadIdx.x == 0) block_max = 0;
   int local_max = 0;
   const uint16_t* xs = reinterpret_cast<const uint16_t*>(x);
@@ -236,6 +245,47 @@ transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restri
   if (amax_bits != nullptr) {
     __syncthreads();
     if (threadIdx.x == 0) atomicMax(amax_bits, block_max);
+  }
+}
+template <bool E4M3>
+__global__ void __launch_bounds__(256)
+transpose_quantize_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ out, uint8_t* __restrict__ codes,
+                          int* __restrict__ amax_bits, int T, int heads, int d, int64_t ldx,
+                          const void* __restrict__ scale, int scale_dt) {
+  transpose_quantize_body<E4M3>(x, out, codes, amax_bits, T, heads, d, ldx, scale, scale_dt, (int)blockIdx.x,
+                                (int)blockIdx.y, (int)blockIdx.z);
+}
+
+// The three casts between the merged q/k/v projection and the attention kernel as one launch: RoPE + cast of the
+// query heads and of the key heads (head-major outputs), cast + transpose of the value heads.  Blocks
+// [0, q_blocks) take the queries, the next k_blocks the keys, the rest one value tile each.
+struct QkvPostParams {
+  const uint4 *q, *k, *cosv, *sinv;
+  const __nv_bfloat16* v;
+  uint2 *q_out, *k_out;
+  uint8_t* vt_out;
+  int T, q_heads, kv_heads, d;
+  int64_t ld;               // elements between consecutive tokens of q, k and v (slices of one [T, *] matrix)
+  const void *q_scale, *k_scale, *v_scale;
+  int q_scale_dt, k_scale_dt, v_scale_dt;
+  int q_blocks, k_blocks, v_tiles_t, v_tiles_d;
+};
+__global__ void __launch_bounds__(256)
+qkv_post_kernel(const QkvPostParams p) {
+  const int b = (int)blockIdx.x;
+  const int vpd = p.d >> 3;
+  if (b < p.q_blocks) {
+    rope_quantize_body(p.q, p.cosv, p.sinv, p.q_out, p.T, p.q_heads, p.d, p.ld / 8, vpd, vpd, (int64_t)p.T * vpd, 1,
+                       p.q_scale, p.q_scale_dt, b, p.q_blocks);
+  } else if (b < p.q_blocks + p.k_blocks) {
+    rope_quantize_body(p.k, p.cosv, p.sinv, p.k_out, p.T, p.kv_heads, p.d, p.ld / 8, vpd, vpd, (int64_t)p.T * vpd, 1,
+                       p.k_scale, p.k_scale_dt, b - p.q_blocks, p.k_blocks);
+  } else {
+    const int i = b - p.q_blocks - p.k_blocks;
+    const int per_head = p.v_tiles_t * p.v_tiles_d;
+    const int h = i / per_head, rem = i - h * per_head;
+    transpose_quantize_body<true>(p.v, p.vt_out, nullptr, nullptr, p.T, p.kv_heads, p.d, p.ld, p.v_scale, p.v_scale_dt,
+                                  rem % p.v_tiles_t, rem / p.v_tiles_t, h);
   }
 }
 
@@ -542,6 +592,38 @@ extern "C" int vq_rope_quantize_fp8(const void* x, const void* cosv, const void*
       static_cast<uint2*>(out), (int)T, (int)heads, (int)d, in_stride_t / 8, in_stride_h / 8, out_stride_t / 8,
       out_stride_h / 8, cosv != nullptr, scale, scale_dtype);
   return check_launch("rope_quantize_kernel");
+}
+
+extern "C" int vq_qkv_post_fp8(const void* q, const void* k, const void* v, int64_t ld, const void* cosv, const void* sinv,
+                               void* q_out, void* k_out, void* vt_out, int64_t T, int64_t q_heads, int64_t kv_heads,
+                               int64_t d, const void* q_scale, int q_scale_dtype, const void* k_scale,
+                               int k_scale_dtype, const void* v_scale, int v_scale_dtype, void* stream) {
+  VQ_REQUIRE(T >= 0 && q_heads >= 0 && kv_heads >= 0 && d >= 0, "vq_qkv_post_fp8: bad extent");
+  if (T == 0 || d == 0 || (q_heads == 0 && kv_heads == 0)) return VQ_OK;
+  VQ_REQUIRE(q && k && v && cosv && sinv && q_out && k_out && vt_out && q_scale && k_scale && v_scale,
+             "vq_qkv_post_fp8: null argument");
+  VQ_REQUIRE(d % 16 == 0 && ld % 8 == 0 && ld >= d, "vq_qkv_post_fp8: head_dim must be a multiple of 16, the token stride of 8");
+  VQ_REQUIRE(T < (1ll << 31) && q_heads < 65536 && kv_heads < 65536 && d < (1 << 22), "vq_qkv_post_fp8: extent too large");
+  VQ_REQUIRE(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+               reinterpret_cast<uintptr_t>(cosv) | reinterpret_cast<uintptr_t>(sinv)) & 15) == 0 &&
+                 ((reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_out)) & 7) == 0,
+             "vq_qkv_post_fp8: misaligned buffers");
+  QkvPostParams p{};
+  p.q = static_cast<const uint4*>(q); p.k = static_cast<const uint4*>(k); p.v = static_cast<const __nv_bfloat16*>(v);
+  p.cosv = static_cast<const uint4*>(cosv); p.sinv = static_cast<const uint4*>(sinv);
+  p.q_out = static_cast<uint2*>(q_out); p.k_out = static_cast<uint2*>(k_out); p.vt_out = static_cast<uint8_t*>(vt_out);
+  p.T = (int)T; p.q_heads = (int)q_heads; p.kv_heads = (int)kv_heads; p.d = (int)d; p.ld = ld;
+  p.q_scale = q_scale; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.q_scale_dt = q_scale_dtype; p.k_scale_dt = k_scale_dtype; p.v_scale_dt = v_scale_dtype;
+  // the rope jobs get blocks in proportion to their elements, about eight blocks per SM in all
+  const int64_t q_items = T * q_heads * (d / 8), k_items = T * kv_heads * (d / 8);
+  p.q_blocks = q_items > 0 ? stream_grid(q_items, 256, 6) : 0;
+  p.k_blocks = k_items > 0 ? stream_grid(k_items, 256, 2) : 0;
+  p.v_tiles_t = (int)((T + 63) / 64); p.v_tiles_d = (int)((d + 63) / 64);
+  const int64_t v_blocks = (int64_t)p.v_tiles_t * p.v_tiles_d * kv_heads;
+  VQ_REQUIRE(v_blocks < (1ll << 30), "vq_qkv_post_fp8: too many value tiles");
+  qkv_post_kernel<<<(unsigned)(p.q_blocks + p.k_blocks + v_blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch("qkv_post_kernel");
 }
 
 extern "C" int vq_transpose_quantize_fp8(const void* x, void* out, void* codes, void* amax_bits, int format, int64_t T,

@@ -358,6 +358,35 @@ def rope_quantize_fp8(x: torch.Tensor, cos: Optional[torch.Tensor], sin: Optiona
 
 
 @N.device_guarded
+def qkv_post_fp8(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                 q_scale: torch.Tensor, k_scale: torch.Tensor, v_scale: torch.Tensor):
+    """``rope_quantize_fp8(q)``, ``rope_quantize_fp8(k)`` and ``transpose_quantize_fp8(v)`` as one launch, for
+    ``q [T, heads, d]``, ``k`` / ``v [T, kv_heads, d]`` that are column slices of one ``[T, *]`` matrix (the output
+    of a merged q/k/v projection).  Returns ``(q8 [heads, T, d], k8 [kv_heads, T, d], vt8 [kv_heads, d, T])``, equal
+    to the separate calls bit for bit; operands that are not such slices take the separate calls."""
+    T, heads, d = q.shape
+    kv = k.shape[1]
+    views = [_heads_view("qkv_post_fp8", t) for t in (q, k, v)]
+    same = all(t is o for (t, _), o in zip(views, (q, k, v))) and len({ld for _, ld in views}) == 1
+    if not same or d % 16 != 0 or tuple(k.shape) != (T, kv, d) or tuple(v.shape) != (T, kv, d):
+        return rope_quantize_fp8(q, cos, sin, q_scale), rope_quantize_fp8(k, cos, sin, k_scale), \
+            transpose_quantize_fp8(v, v_scale)
+    cos, sin = _bf16_input("qkv_post_fp8", cos), _bf16_input("qkv_post_fp8", sin)
+    if tuple(cos.shape) != (T, d) or tuple(sin.shape) != (T, d):
+        raise ValueError("cos / sin must be [T, head_dim]")
+    scales = [_scale_arg(t) for t in (q_scale, k_scale, v_scale)]
+    q8 = torch.empty((heads, T, d), dtype=torch.uint8, device=q.device)
+    k8 = torch.empty((kv, T, d), dtype=torch.uint8, device=q.device)
+    vt8 = torch.empty((kv, d, T), dtype=torch.uint8, device=q.device)
+    N.check(N.lib().vq_qkv_post_fp8(q.data_ptr(), k.data_ptr(), v.data_ptr(), views[0][1], cos.data_ptr(), sin.data_ptr(),
+                                    q8.data_ptr(), k8.data_ptr(), vt8.data_ptr(), T, heads, kv, d,
+                                    scales[0].data_ptr(), _dtype_id(scales[0].dtype), scales[1].data_ptr(),
+                                    _dtype_id(scales[1].dtype), scales[2].data_ptr(), _dtype_id(scales[2].dtype), _stream()),
+            "vq_qkv_post_fp8")
+    return q8, k8, vt8
+
+
+@N.device_guarded
 def transpose_heads_quantize_fp8(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """e4m3 bytes of a head-major ``x [heads, T, d] / scale`` laid out token-major ``[T, heads * d]``."""
     x, scale = _bf16_input("transpose_heads_quantize_fp8", x), _scale_arg(scale)

@@ -414,8 +414,8 @@ class Fp8DecoderLayerTP:
         self.timed = False
         self.collective_events = []
 
-    # kernels of this package per forward: 2 norm+cast, 3 rope/transpose casts, attention, 4 GEMMs
-    LAUNCHES = 10
+    # kernels of this package per forward: 2 norm+cast, the q/k/v casts (one launch), attention, 4 GEMMs
+    LAUNCHES = 8
     COLLECTIVES = 4
 
     def _collective(self, fn, t):
@@ -474,9 +474,8 @@ class Fp8DecoderLayerTP:
         q = qkv[:, :hq * d].unflatten(1, (hq, d))
         k = qkv[:, hq * d:(hq + hkv) * d].unflatten(1, (hkv, d))
         v = qkv[:, (hq + hkv) * d:].unflatten(1, (hkv, d))
-        k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])
-        vt8 = FP8.transpose_quantize_fp8(v, s["v"])
-        q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(hkv, (hq // hkv) * T, d)
+        q8, k8, vt8 = FP8.qkv_post_fp8(q, k, v, cos, sin, s["q"], s["k"], s["v"])
+        q8 = q8.view(hkv, (hq // hkv) * T, d)
         ctx8 = FP8.attention_fp8(q8, k8, vt8, self.alpha_qk, 1.0 / math.sqrt(d), s["p"], self.alpha_pv, s["ctx"],
                                  round_acc=self.ra)                                   # [T, hq * d]
         partial = FP8.fp8_gemm(ctx8, self.w8_o, out_dtype=torch.float32,

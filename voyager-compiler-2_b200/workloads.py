@@ -173,9 +173,12 @@ class Fp8DecoderLayer:
 
     @property
     def LAUNCHES(self):
-        """Kernels of this package launched per forward: 5 fused casts, 4 GEMMs and the attention kernel, or
-        6 fused casts, the softmax and 6 GEMMs when the attention runs as separate kernels."""
-        return 5 + 4 + 1 if self.fuse_attention else 6 + 1 + 6
+        """Kernels of this package launched per forward: 3 fused casts (5 when q, k and v come from separate
+        GEMMs), 4 GEMMs and the attention kernel, or one cast, the softmax and 2 GEMMs more when the attention runs
+        as separate kernels."""
+        casts = 2 + (1 if self.merge_qkv else 3) + (0 if self.merge_gate_up else 1)
+        gemms = 2 + (1 if self.merge_qkv else 3) + (1 if self.merge_gate_up else 2)
+        return casts + gemms + (1 if self.fuse_attention else 4)   # else: two GEMMs, the softmax, the context cast
 
     def _tables(self, T, device):
         if self._rope is None or self._rope[0].shape[0] != T:
@@ -199,20 +202,25 @@ class Fp8DecoderLayer:
         k = k.unflatten(1, (sh.kv_heads, sh.head_dim))
         v = v.unflatten(1, (sh.kv_heads, sh.head_dim))
         # query heads of one KV group are stacked along the rows: [kv, groups*T, d]
-        # the small K and V casts run beside the Q cast on a second stream (a fork and join that a
-        # CUDA graph capture records as parallel branches)
-        main = torch.cuda.current_stream()
-        if self._side is None:
-            self._side = torch.cuda.Stream(device=x.device)
-        self._side.wait_stream(main)
-        with torch.cuda.stream(self._side):
-            k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                 # [kv, T, d]
-            vt8 = FP8.transpose_quantize_fp8(v, s["v"])                     # [kv, d, T]
-        q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(sh.kv_heads, sh.groups * T, sh.head_dim)
-        main.wait_stream(self._side)
-        for t in (k8, vt8):
-            t.record_stream(main)
-        k.record_stream(self._side)
+        if self.merge_qkv:
+            # slices of one matrix: the two RoPE casts and the value transpose are one launch
+            q8, k8, vt8 = FP8.qkv_post_fp8(q, k, v, cos, sin, s["q"], s["k"], s["v"])
+            q8 = q8.view(sh.kv_heads, sh.groups * T, sh.head_dim)
+        else:
+            # the small K and V casts run beside the Q cast on a second stream (a fork and join that a
+            # CUDA graph capture records as parallel branches)
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=x.device)
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                k8 = FP8.rope_quantize_fp8(k, cos, sin, s["k"])                 # [kv, T, d]
+                vt8 = FP8.transpose_quantize_fp8(v, s["v"])                     # [kv, d, T]
+            q8 = FP8.rope_quantize_fp8(q, cos, sin, s["q"]).view(sh.kv_heads, sh.groups * T, sh.head_dim)
+            main.wait_stream(self._side)
+            for t in (k8, vt8):
+                t.record_stream(main)
+            k.record_stream(self._side)
         if self.fuse_attention and T % 128 == 0:
             ctx8 = FP8.attention_fp8(q8, k8, vt8, self.alpha_qk, 1.0 / math.sqrt(sh.head_dim), s["p"], self.alpha_pv,
                                      s["ctx"], round_acc=self.ra)            # [T, heads*d]
