@@ -243,11 +243,26 @@ __device__ __forceinline__ uint32_t pack_pair(float a, float b) {
 
 // Phase 1 of the staged epilogue: this thread's 32 scaled values of one row go to
 // its row of the warp's staging buffer (16-byte units XOR-swizzled by the row).
+// `res` (16-bit outputs only): the residual's 32 elements of this row and chunk, added to the rounded values and
+// rounded again before they are staged.
 template <int OUT_DT>
 __device__ __forceinline__ void stage_chunk(const GemmParams& p, const uint32_t (&v)[32], uint8_t* srow, int lane,
-                                            int col0, int half, bool has_alpha, float alpha) {
+                                            int col0, int half, bool has_alpha, float alpha,
+                                            const uint4 (&res)[4], bool add_res) {
   float f[32];
   scale_chunk(p, v, f, col0, has_alpha, alpha);
+  if (OUT_DT != VQ_F32 && add_res) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t r4[4] = {res[u].x, res[u].y, res[u].z, res[u].w};
+      uint32_t o4[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        o4[q] = add_residual_word(pack_pair<OUT_DT>(f[8 * u + 2 * q], f[8 * u + 2 * q + 1]), r4[q], OUT_DT);
+      *reinterpret_cast<uint4*>(srow + (((half * 4 + u) ^ (lane & 7)) << 4)) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+    }
+    return;
+  }
   if (OUT_DT == VQ_F32) {
 #pragma unroll
     for (int u = 0; u < 8; ++u)
@@ -395,12 +410,23 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
   // across tiles), so the TMA store of one block drains while the next block is being staged.
   uint8_t* stage = stage0 + (EPI_BUFS == 2 ? buf * (32 * 128) : 0);
   uint8_t* srow = stage + lane * 128;
-  // With a tensor map for C (and no residual to add) a finished 32 x 128-byte block leaves
+  // A 16-bit residual whose rows are 16-byte aligned is fetched by the lane that owns the row, 64 bytes per chunk,
+  // when the chunk's tensor-memory load is issued, and added before staging: the block then leaves like any other.
+  const bool early_res = r_batch != nullptr && ESZ == 2 && r_wide && p.tma_store != 0 && (p.N & 31) == 0;
+  // With a tensor map for C (and no residual left to add) a finished 32 x 128-byte block leaves
   // shared memory as one TMA store issued by lane 0; the hardware clips it at the edges of C.
-  const bool by_tma = p.tma_store != 0 && r_batch == nullptr;
+  const bool by_tma = p.tma_store != 0 && (r_batch == nullptr || early_res);
+  const uint8_t* r_row = early_res && row0 + lane < p.M ? r_batch + (int64_t)(row0 + lane) * r_row_stride : nullptr;
+  auto load_res = [&](uint4 (&r)[4], int c0) {
+    if (!early_res) return;
+    const bool in = r_row != nullptr && n0 + c0 < p.N;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      r[u] = in ? __ldg(reinterpret_cast<const uint4*>(r_row + (int64_t)(n0 + c0) * ESZ) + u) : make_uint4(0, 0, 0, 0);
+  };
 
   // one 32-column chunk: scale, stage, and flush when its 128-byte round is complete
-  auto process = [&](const uint32_t (&v)[32], int c0) {
+  auto process = [&](const uint32_t (&v)[32], int c0, const uint4 (&res)[4]) {
     const int col0 = n0 + c0;
     if (col0 >= p.N) return;  // warp-uniform
     const int half = ESZ == 4 ? 0 : (c0 >> 5) & 1;   // a 128-byte row holds two 32-column chunks of 16-bit values
@@ -410,7 +436,7 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
       }
       __syncwarp();
     }
-    stage_chunk<OUT_DT>(p, v, srow, lane, col0, half, has_alpha, alpha);
+    stage_chunk<OUT_DT>(p, v, srow, lane, col0, half, has_alpha, alpha, res, early_res);
     if (ESZ != 4 && half == 0 && col0 + 32 < p.N && c0 + 32 < c_end) return;  // the round's second chunk follows
     const int round_col0 = col0 - half * 32;
     if (by_tma) {
@@ -434,12 +460,17 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
   };
 
   uint32_t va[32], vb[32];
+  uint4 ra[4] = {}, rb[4] = {};
   tmem_ld_32x32(taddr + (uint32_t)c_begin, va);
+  load_res(ra, c_begin);
 #pragma unroll 1
   for (int c0 = c_begin; c0 < c_end; c0 += 64) {
     const bool has_b = c0 + 32 < c_end;   // warp-uniform
     tmem_ld_wait();
-    if (has_b) tmem_ld_32x32(taddr + (uint32_t)(c0 + 32), vb);
+    if (has_b) {
+      tmem_ld_32x32(taddr + (uint32_t)(c0 + 32), vb);
+      load_res(rb, c0 + 32);
+    }
     const bool release_now = release_bar != 0 && c0 + 64 >= c_end;   // these are the range's last loads
     if (release_now) {
       if (has_b) tmem_ld_wait();
@@ -447,11 +478,14 @@ __device__ __forceinline__ void epilogue_warp_tile_t(const GemmParams& p, const 
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(release_bar);
     }
-    process(va, c0);
+    process(va, c0, ra);
     if (has_b) {
       if (!release_now) tmem_ld_wait();
-      if (c0 + 64 < c_end) tmem_ld_32x32(taddr + (uint32_t)(c0 + 64), va);
-      process(vb, c0 + 32);
+      if (c0 + 64 < c_end) {
+        tmem_ld_32x32(taddr + (uint32_t)(c0 + 64), va);
+        load_res(ra, c0 + 64);
+      }
+      process(vb, c0 + 32, rb);
     }
   }
 }
