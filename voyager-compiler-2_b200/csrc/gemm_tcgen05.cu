@@ -872,7 +872,7 @@ gemm_tn_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Register budget by warpgroup (384 threads x 168 at launch): the producer / MMA group keeps 40 per thread,
+  // Registers by warpgroup (384 threads x 168 at launch): the producer / MMA group keeps 40 per thread,
   // the two epilogue groups take 232, so that the epilogue's double-buffered tensor-memory loads and its
   // arithmetic fit without spilling to local memory.
   if (warp < P_EPI_WARP0) {
